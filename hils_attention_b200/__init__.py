@@ -1,0 +1,12 @@
+"""B200-native (sm_100a) HiLS sparse-attention hot path.
+
+`ops` mirrors the reference's ``ops/`` call signatures on top of the C-ABI CUDA library
+(libhils_b200.so, declared in include/hils_b200.h); `attention` chains them the way the reference's
+attention module does; `cache` is the KV store used for prefill and decode.
+"""
+from . import _lib
+from .ops import (HiLS_block_M_head, chunk_attn_pool, chunk_attn_pool_tilelang, chunk_mean_pool,
+                  exact_chunk_log_z_tl, flex_attn_tl, flex_attn_tl_two_phase, online_softmax_topk_head)
+
+__all__ = ["HiLS_block_M_head", "chunk_attn_pool", "chunk_attn_pool_tilelang", "chunk_mean_pool",
+           "exact_chunk_log_z_tl", "flex_attn_tl", "flex_attn_tl_two_phase", "online_softmax_topk_head"]

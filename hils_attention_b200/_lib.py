@@ -1,0 +1,96 @@
+"""ctypes binding of libhils_b200.so (the C ABI declared in include/hils_b200.h).
+
+The library is built in-tree by ``python -m hils_attention_b200.build``; there is no CPU or
+PyTorch fallback: if the shared library is missing, or a call is made without a CUDA device,
+an error is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libhils_b200.so")
+
+F32, BF16 = 0, 1
+_P, _I, _F, _I64, _SZ = C.c_void_p, C.c_int, C.c_float, C.c_int64, C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/hils_b200.h one to one
+SIGNATURES = {
+    "hils_version": (_I, []),
+    "hils_last_error": (C.c_char_p, []),
+    "hils_pool_fwd": (_I, [_P] * 4 + [_I] * 6 + [_I64, _F, _I, _I, _P]),
+    "hils_pool_bwd": (_I, [_P] * 6 + [_I] * 6 + [_I64, _F, _I, _I, _P]),
+    "hils_meanpool_fwd": (_I, [_P, _P] + [_I] * 5 + [_I64, _I, _P]),
+    "hils_meanpool_bwd": (_I, [_P, _P] + [_I] * 6 + [_P]),
+    "hils_topk_fwd": (_I, [_P] * 10 + [_I] * 12 + [_F, _I, _I, _P]),
+    "hils_topk_bwd": (_I, [_P] * 7 + [_I] * 8 + [_F, _I, _P]),
+    "hils_sparse_attn_fwd": (_I, [_P] * 7 + [_I] * 10 + [_F, _I, _I, _P, _SZ, _P]),
+    "hils_sparse_attn_fwd_workspace_bytes": (_SZ, [_I] * 10),
+    "hils_sparse_attn_bwd": (_I, [_P] * 11 + [_I] * 10 + [_F, _I, _I, _P, _SZ, _P]),
+    "hils_sparse_attn_bwd_workspace_bytes": (_SZ, [_I] * 10),
+    "hils_chunk_logz_fwd": (_I, [_P] * 3 + [_I] * 7 + [_F, _I, _I, _P]),
+    "hils_chunk_logz_bwd": (_I, [_P] * 6 + [_I] * 7 + [_F, _I, _P]),
+    "hils_swa_fwd": (_I, [_P] * 5 + [_I] * 11 + [_F, _I, _I, _P]),
+    "hils_swa_bwd": (_I, [_P] * 10 + [_I] * 10 + [_F, _I, _P]),
+}
+
+_lib: Optional[C.CDLL] = None
+
+
+class HilsError(RuntimeError):
+    """Raised when a C-ABI call returns a non-zero status."""
+
+
+def load() -> C.CDLL:
+    """Load the shared library (once) and bind every declared symbol."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} not found: build it with `python -m hils_attention_b200.build` "
+            "(there is no fallback implementation)")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError if the .so lacks a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return BF16
+    if t.dtype == torch.float32:
+        return F32
+    raise TypeError(f"hils_b200 kernels take bfloat16 or float32 tensors, got {t.dtype}")
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError("hils_b200 kernels need CUDA tensors (no CPU fallback exists)")
+    return t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def call(name: str, *args):
+    """Invoke a status-returning entry point and raise HilsError on failure."""
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        msg = lib.hils_last_error().decode("utf-8", "replace")
+        raise HilsError(f"{name} failed with status {rc}: {msg}")
+
+
+def query(name: str, *args) -> int:
+    return int(getattr(load(), name)(*args))

@@ -1,0 +1,25 @@
+// Error text of the C ABI (one buffer per host thread) and library identification.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+namespace hils {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error("%s: CUDA error %d (%s)", what, (int)e, cudaGetErrorString(e));
+  return HILS_ERR_CUDA;
+}
+
+}  // namespace hils
+
+extern "C" int hils_version(void) { return 100; }
+extern "C" const char* hils_last_error(void) { return hils::g_err; }

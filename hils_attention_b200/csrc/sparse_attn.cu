@@ -1,0 +1,124 @@
+// C entry points of the sparse chunk attention (forward and backward) and their dispatch.
+#include "sparse_attn_generic.cuh"
+
+namespace hils {
+
+static int check_sparse(int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights,
+                        int chunk_size, int dtype) {
+  HILS_REQUIRE(B > 0 && L >= 0 && T >= 0 && h_q > 0 && h_kv > 0 && D > 0 && Dv > 0, "sparse_attn: bad size");
+  HILS_REQUIRE(h_q % h_kv == 0, "sparse_attn: h_q (%d) must be a multiple of h_kv (%d)", h_q, h_kv);
+  HILS_REQUIRE(K > 0 && num_weights >= K, "sparse_attn: need num_weights (%d) >= K (%d) > 0", num_weights, K);
+  HILS_REQUIRE(chunk_size > 0, "sparse_attn: chunk_size must be positive");
+  HILS_REQUIRE(D % 4 == 0 && Dv % 4 == 0 && D <= 256 && Dv <= 256,
+               "sparse_attn: head dims (%d, %d) must be multiples of 4 and <= 256", D, Dv);
+  HILS_REQUIRE(dtype == HILS_F32 || dtype == HILS_BF16, "sparse_attn: unknown dtype %d", dtype);
+  return HILS_OK;
+}
+
+static SparseParams make_params(const void* q, const void* k, const void* v, const void* w, const int32_t* idx,
+                                const float* slope, int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K,
+                                int num_weights, int S, float scale, int mask_last) {
+  SparseParams p;
+  p.q = q; p.k = k; p.v = v; p.w = w; p.idx = idx; p.slope = slope;
+  p.o = nullptr; p.d_o = nullptr; p.d_q = nullptr; p.d_w = nullptr; p.dk_acc = nullptr; p.dv_acc = nullptr;
+  p.B = B; p.L = L; p.T = T; p.h_q = h_q; p.h_kv = h_kv; p.D = D; p.Dv = Dv; p.K = K;
+  p.num_weights = num_weights; p.S = S; p.mask_last = mask_last; p.scale = scale;
+  return p;
+}
+
+}  // namespace hils
+
+using namespace hils;
+
+extern "C" size_t hils_sparse_attn_fwd_workspace_bytes(int B, int L, int T, int h_q, int h_kv, int D, int Dv,
+                                                       int K, int chunk_size, int dtype) {
+  (void)B; (void)L; (void)T; (void)h_q; (void)h_kv; (void)D; (void)Dv; (void)K; (void)chunk_size; (void)dtype;
+  return 0;
+}
+
+extern "C" size_t hils_sparse_attn_bwd_workspace_bytes(int B, int L, int T, int h_q, int h_kv, int D, int Dv,
+                                                       int K, int chunk_size, int dtype) {
+  (void)L; (void)h_q; (void)K; (void)chunk_size; (void)dtype;
+  return (size_t)B * T * h_kv * (size_t)(D + Dv) * sizeof(float);
+}
+
+extern "C" int hils_sparse_attn_fwd(const void* q, const void* k, const void* v, const void* weights,
+                                    const int32_t* indices, const float* slope, void* o, int B, int L, int T,
+                                    int h_q, int h_kv, int D, int Dv, int K, int num_weights, int chunk_size,
+                                    float sm_scale, int mask_last_token, int dtype, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
+  (void)workspace; (void)workspace_bytes;
+  if (int rc = check_sparse(B, L, T, h_q, h_kv, D, Dv, K, num_weights, chunk_size, dtype)) return rc;
+  if (L == 0) return HILS_OK;
+  HILS_REQUIRE(q && weights && indices && o, "sparse_attn_fwd: null pointer");
+  HILS_REQUIRE(T < chunk_size || (k && v), "sparse_attn_fwd: null k/v");
+  SparseParams p = make_params(q, k, v, weights, indices, slope, B, L, T, h_q, h_kv, D, Dv, K, num_weights,
+                               chunk_size, sm_scale, mask_last_token);
+  p.o = o;
+  const int64_t rows = (int64_t)B * L * h_q;
+  const size_t smem = 4 * (size_t)(D + chunk_size) * sizeof(float);
+  HILS_REQUIRE(smem <= 200 * 1024, "sparse_attn_fwd: chunk_size %d too large", chunk_size);
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned blocks = (unsigned)((rows + 3) / 4);
+  if (dtype == HILS_BF16) {
+    cudaFuncSetAttribute(sparse_fwd_generic_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sparse_fwd_generic_kernel<bf16><<<blocks, 128, smem, st>>>(p, rows);
+  } else {
+    cudaFuncSetAttribute(sparse_fwd_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sparse_fwd_generic_kernel<float><<<blocks, 128, smem, st>>>(p, rows);
+  }
+  HILS_LAUNCH_CHECK("sparse_attn_fwd");
+  return HILS_OK;
+}
+
+extern "C" int hils_sparse_attn_bwd(const void* q, const void* k, const void* v, const void* weights,
+                                    const int32_t* indices, const float* slope, const void* d_o, void* d_q,
+                                    void* d_k, void* d_v, void* d_w, int B, int L, int T, int h_q, int h_kv,
+                                    int D, int Dv, int K, int num_weights, int chunk_size, float sm_scale,
+                                    int mask_last_token, int dtype, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+  if (int rc = check_sparse(B, L, T, h_q, h_kv, D, Dv, K, num_weights, chunk_size, dtype)) return rc;
+  const size_t need = hils_sparse_attn_bwd_workspace_bytes(B, L, T, h_q, h_kv, D, Dv, K, chunk_size, dtype);
+  if (need > 0 && (!workspace || workspace_bytes < need)) {
+    set_error("sparse_attn_bwd: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    return HILS_ERR_WORKSPACE;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t nk = (int64_t)B * T * h_kv * D, nv = (int64_t)B * T * h_kv * Dv;
+  float* dk_acc = static_cast<float*>(workspace);
+  float* dv_acc = dk_acc + nk;
+  if (need > 0) {
+    HILS_REQUIRE(d_k && d_v, "sparse_attn_bwd: null d_k/d_v");
+    cudaError_t e = cudaMemsetAsync(workspace, 0, need, st);
+    if (e != cudaSuccess) return cuda_fail(e, "sparse_attn_bwd memset");
+  }
+  if (L > 0) {
+    HILS_REQUIRE(q && weights && indices && d_o && d_q && d_w, "sparse_attn_bwd: null pointer");
+    SparseParams p = make_params(q, k, v, weights, indices, slope, B, L, T, h_q, h_kv, D, Dv, K, num_weights,
+                                 chunk_size, sm_scale, mask_last_token);
+    p.d_o = d_o; p.d_q = d_q; p.d_w = d_w; p.dk_acc = dk_acc; p.dv_acc = dv_acc;
+    const int64_t rows = (int64_t)B * L * h_q;
+    const size_t smem = 4 * (size_t)(D + Dv + 2 * chunk_size) * sizeof(float);
+    HILS_REQUIRE(smem <= 200 * 1024, "sparse_attn_bwd: chunk_size %d too large", chunk_size);
+    const unsigned blocks = (unsigned)((rows + 3) / 4);
+    if (dtype == HILS_BF16) {
+      cudaFuncSetAttribute(sparse_bwd_generic_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      sparse_bwd_generic_kernel<bf16><<<blocks, 128, smem, st>>>(p, rows);
+    } else {
+      cudaFuncSetAttribute(sparse_bwd_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      sparse_bwd_generic_kernel<float><<<blocks, 128, smem, st>>>(p, rows);
+    }
+    HILS_LAUNCH_CHECK("sparse_attn_bwd");
+  }
+  if (need > 0) {
+    if (dtype == HILS_BF16) {
+      launch_cast_from_f32<bf16>(dk_acc, (bf16*)d_k, nk, st);
+      launch_cast_from_f32<bf16>(dv_acc, (bf16*)d_v, nv, st);
+    } else {
+      launch_cast_from_f32<float>(dk_acc, (float*)d_k, nk, st);
+      launch_cast_from_f32<float>(dv_acc, (float*)d_v, nv, st);
+    }
+    HILS_LAUNCH_CHECK("sparse_attn_bwd cast");
+  }
+  return HILS_OK;
+}

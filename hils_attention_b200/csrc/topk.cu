@@ -1,0 +1,430 @@
+// Chunk selection: chunk-score GEMM, HiLS log-sum-exp, lse_total, top-k select, ascending id sort
+// and the scores of the selected chunks, in ONE launch (the reference uses four kernels plus a
+// torch op, ops/topk_head_softmax.py:977-1038).
+//
+// Contract (ops/topk_head_softmax.py:15-154 and the kernels :192-971), for query row i at absolute
+// position t = q_offset + i, kv-head h, group member g:
+//   limit = floor((t - W + 1)/S) (W > 0) or floor(t/S); candidates c in [0, min(limit, N))
+//   v[g,c]   = fl32(fl32(<q_g, k'_c>) * scale) + bias[c,g] + gumbel[g,c]
+//   lse_hils = logsumexp_c v[g,c];  lse_total[g] = logaddexp(lse_swa[g], lse_hils[g])
+//   key[c]   = max_g (v[g,c] - lse_total[g]);  drop_mask removes candidates
+//   pick the K largest keys; ties go to the smaller chunk id; -inf is never picked
+//   ids ascending, -1 padded;  scores[g,k] = fl(<q_g,k'_id> * scale), -inf at -1
+//
+// Layout of one CTA: 4 warps, RB = 4*RW consecutive query rows of one (batch, kv-head).  Chunk keys
+// stream through shared memory in tiles of 64; scores of a tile are formed by a register-tiled
+// CUDA-core product (fp32 exact for both element types).  Each warp owns RW rows and keeps each
+// row's running top-K as a sorted list spread over its lanes (packed 64-bit items: order-preserving
+// key bits above, inverted id below, so one unsigned compare implements "greater key, then smaller
+// id").  New candidates are filtered by a warp ballot against the current K-th item.
+#include "common.cuh"
+
+namespace hils {
+
+struct TopkParams {
+  const void* q; const void* lmks; const void* lse_swa; const float* bias; const float* gumbel;
+  const int32_t* drop_mask; int32_t* indices; void* scores; float* lse_total; float* rank_keys;
+  int B, L, N, h_kv, G, D, topk, block_size, window_size, is_causal, q_offset, per_qhead, lse_dtype;
+  int RW;
+  float scale;
+};
+
+constexpr int TN = 64;  // candidates per tile
+
+__device__ __forceinline__ uint32_t order_bits(float f) {
+  uint32_t u = __float_as_uint(f + 0.0f);  // -0 -> +0
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ float log_add_exp(float a, float b) {
+  if (isinf(a) && a == b) return a;
+  float mx = fmaxf(a, b), mn = fminf(a, b);
+  return mx + log1pf(expf(mn - mx));
+}
+
+__device__ __forceinline__ int row_limit(const TopkParams& p, int l) {
+  if (l >= p.L) return 0;
+  if (!p.is_causal) return p.N;
+  int t = p.q_offset + l;
+  int lim = (p.window_size > 0) ? floor_div(t - p.window_size + 1, p.block_size) : floor_div(t, p.block_size);
+  return max(0, min(lim, p.N));
+}
+
+template <typename T, int KPL>
+__global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
+  extern __shared__ __align__(16) float smem[];
+  const int G = p.G, D = p.D, RW = p.RW, RB = 4 * RW, M = RB * G, RS = D + 4;
+  float* q_s = smem;                       // [M][D]
+  float* kt_s = q_s + (size_t)M * D;       // [TN][RS]
+  float* sc_s = kt_s + TN * RS;            // [M][TN]
+  float* lse_s = sc_s + (size_t)M * TN;    // [M] running max, later lse_total
+  float* sum_s = lse_s + M;                // [M] running sum
+  int* ids_s = reinterpret_cast<int*>(sum_s + M);  // [4][32*KPL]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int l0 = blockIdx.x * RB, h = blockIdx.y, b = blockIdx.z;
+  const T* q = static_cast<const T*>(p.q);
+  const T* lmks = static_cast<const T*>(p.lmks);
+  const int HL = p.per_qhead ? p.h_kv * G : p.h_kv;  // heads in lmks
+
+  for (int idx = tid * 4; idx < M * D; idx += 128 * 4) {
+    int m = idx / D, d = idx - m * D;
+    int l = l0 + m / G;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (l < p.L) x = load4(q + (((int64_t)b * p.L + l) * p.h_kv + h) * (int64_t)G * D + (int64_t)(m % G) * D + d);
+    *reinterpret_cast<float4*>(q_s + idx) = x;
+  }
+  for (int m = tid; m < M; m += 128) { lse_s[m] = -CUDART_INF_F; sum_s[m] = 0.f; }
+
+  const int last_row = min(l0 + RB, p.L) - 1;
+  const int cta_limit = row_limit(p, last_row);  // limits are non-decreasing in l
+  const int tx = tid & 15, ty = tid >> 4;
+
+  // scores of one 64-candidate tile into sc_s (selection logits v; -inf where not a candidate)
+  auto score_tile = [&](int c0) {
+    const int ng = p.per_qhead ? G : 1;
+    for (int g = 0; g < ng; ++g) {
+      __syncthreads();
+      for (int idx = tid * 4; idx < TN * D; idx += 128 * 4) {
+        int j = idx / D, d = idx - j * D;
+        int c = c0 + j;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < p.N) x = load4(lmks + (((int64_t)b * p.N + c) * HL + (p.per_qhead ? h * G + g : h)) * D + d);
+        *reinterpret_cast<float4*>(kt_s + j * RS + d) = x;
+      }
+      __syncthreads();
+      const int nrow = p.per_qhead ? RB : M;
+      for (int i0 = ty; i0 < nrow; i0 += 16) {
+        const int i1 = i0 + 8;
+        const int m0 = p.per_qhead ? i0 * G + g : i0;
+        const int m1 = (i1 < nrow) ? (p.per_qhead ? i1 * G + g : i1) : m0;
+        float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* q0 = q_s + (size_t)m0 * D;
+        const float* q1 = q_s + (size_t)m1 * D;
+        for (int d = 0; d < D; d += 4) {
+          float4 x0 = *reinterpret_cast<const float4*>(q0 + d);
+          float4 x1 = *reinterpret_cast<const float4*>(q1 + d);
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            float4 kv = *reinterpret_cast<const float4*>(kt_s + (tx + 16 * jj) * RS + d);
+            a0[jj] = fmaf(x0.x, kv.x, a0[jj]); a0[jj] = fmaf(x0.y, kv.y, a0[jj]);
+            a0[jj] = fmaf(x0.z, kv.z, a0[jj]); a0[jj] = fmaf(x0.w, kv.w, a0[jj]);
+            a1[jj] = fmaf(x1.x, kv.x, a1[jj]); a1[jj] = fmaf(x1.y, kv.y, a1[jj]);
+            a1[jj] = fmaf(x1.z, kv.z, a1[jj]); a1[jj] = fmaf(x1.w, kv.w, a1[jj]);
+          }
+        }
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+          if (rr == 1 && i1 >= nrow) break;
+          const int m = rr ? m1 : m0;
+          const int l = l0 + m / G, gg = m % G;
+          const int lim = row_limit(p, l);
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int c = c0 + tx + 16 * jj;
+            float v = -CUDART_INF_F;
+            if (c < lim) {
+              v = (rr ? a1[jj] : a0[jj]) * p.scale;
+              if (p.bias) v += p.bias[(((int64_t)b * p.N + c) * p.h_kv + h) * G + gg];
+              if (p.gumbel) v += p.gumbel[(int64_t)(h * G + gg) * p.N + c];
+            }
+            sc_s[(size_t)m * TN + tx + 16 * jj] = v;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  };
+
+  // ---------------- pass 1: online log-sum-exp of the selection logits ----------------------
+  for (int c0 = 0; c0 < cta_limit; c0 += TN) {
+    score_tile(c0);
+    for (int r = 0; r < RW; ++r) {
+      for (int g = 0; g < G; ++g) {
+        const int m = (warp * RW + r) * G + g;
+        float v0 = sc_s[(size_t)m * TN + lane], v1 = sc_s[(size_t)m * TN + lane + 32];
+        float tmax = warp_max(fmaxf(v0, v1));
+        float mo = lse_s[m];
+        float mn = fmaxf(mo, tmax);
+        if (mn > -CUDART_INF_F) {
+          float s = expf(v0 - mn) + expf(v1 - mn);
+          s = warp_sum(s);
+          if (lane == 0) {
+            sum_s[m] = sum_s[m] * ((mo > -CUDART_INF_F) ? expf(mo - mn) : 0.f) + s;
+            lse_s[m] = mn;
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+  __syncthreads();
+  for (int m = tid; m < M; m += 128) {
+    const int l = l0 + m / G, g = m % G;
+    if (l < p.L) {
+      float lh = (sum_s[m] > 0.f) ? lse_s[m] + logf(sum_s[m]) : -CUDART_INF_F;
+      const int64_t o = (((int64_t)b * p.L + l) * p.h_kv + h) * G + g;
+      float ls = (p.lse_dtype == HILS_BF16) ? to_f(static_cast<const bf16*>(p.lse_swa)[o])
+                                            : static_cast<const float*>(p.lse_swa)[o];
+      float lt = log_add_exp(ls, lh);
+      lse_s[m] = lt;
+      if (p.lse_total) p.lse_total[o] = lt;
+    } else {
+      lse_s[m] = 0.f;
+    }
+  }
+  __syncthreads();
+
+  // ---------------- pass 2: ranking keys and the running top-K -------------------------------
+  unsigned long long best[4][KPL];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int i = 0; i < KPL; ++i) best[r][i] = 0ull;
+  const int K = p.topk;
+  const int thr_lane = (K - 1) / KPL, thr_i = (K - 1) % KPL;
+  const int sel_limit = p.rank_keys ? p.N : cta_limit;
+  for (int c0 = 0; c0 < sel_limit; c0 += TN) {
+    score_tile(c0);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      if (r >= RW) break;
+      const int row = warp * RW + r;
+      const int l = l0 + row;
+      if (l >= p.L) continue;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int c = c0 + lane + 32 * half;
+        float key = -CUDART_INF_F;
+        for (int g = 0; g < G; ++g) {
+          float v = sc_s[(size_t)(row * G + g) * TN + lane + 32 * half];
+          if (v > -CUDART_INF_F) key = fmaxf(key, v - lse_s[row * G + g]);
+        }
+        if (p.drop_mask && c < p.N && p.drop_mask[((int64_t)b * p.L + l) * p.N + c] != 0) key = -CUDART_INF_F;
+        if (p.rank_keys && c < p.N) p.rank_keys[(((int64_t)b * p.L + l) * p.h_kv + h) * p.N + c] = key;
+        const bool cand = key > -CUDART_INF_F;  // false for NaN too
+        unsigned long long item = cand ? (((unsigned long long)order_bits(key) << 32) | (0xFFFFFFFFu - (uint32_t)c)) : 0ull;
+        unsigned long long thr = 0ull;
+#pragma unroll
+        for (int i = 0; i < KPL; ++i) {
+          unsigned long long t = __shfl_sync(0xffffffffu, best[r][i], thr_lane);
+          if (i == thr_i) thr = t;
+        }
+        unsigned mask = __ballot_sync(0xffffffffu, item > thr);
+        while (mask) {
+          const int src = __ffs(mask) - 1;
+          mask &= mask - 1;
+          const unsigned long long x = __shfl_sync(0xffffffffu, item, src);
+          if (x > thr) {
+            unsigned long long prev_last = __shfl_up_sync(0xffffffffu, best[r][KPL - 1], 1);
+            if (lane == 0) prev_last = ~0ull;
+#pragma unroll
+            for (int i = KPL - 1; i >= 0; --i) {
+              const unsigned long long prev = (i > 0) ? best[r][i - 1] : prev_last;
+              const unsigned long long cur = best[r][i];
+              best[r][i] = (cur > x) ? cur : ((prev > x) ? x : prev);
+            }
+#pragma unroll
+            for (int i = 0; i < KPL; ++i) {
+              unsigned long long t = __shfl_sync(0xffffffffu, best[r][i], thr_lane);
+              if (i == thr_i) thr = t;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------- epilogue: ascending ids, -1 padding, scores of the picked chunks ----------
+  T* scores = static_cast<T*>(p.scores);
+  int* my_ids = ids_s + warp * 32 * KPL;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    if (r >= RW) break;
+    const int row = warp * RW + r;
+    const int l = l0 + row;
+    if (l >= p.L) continue;  // warp-uniform
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < KPL; ++i) {
+      const int pos = lane * KPL + i;
+      const unsigned long long it = best[r][i];
+      my_ids[pos] = (pos < K && it != 0ull) ? (int)(0xFFFFFFFFu - (uint32_t)(it & 0xFFFFFFFFull)) : 0x7fffffff;
+    }
+    __syncwarp();
+    int32_t* out = p.indices + (((int64_t)b * p.L + l) * p.h_kv + h) * K;
+    int sorted[KPL];
+#pragma unroll
+    for (int i = 0; i < KPL; ++i) {
+      const int pos = lane * KPL + i;
+      const int mine = my_ids[pos];
+      int rank = 0;
+      for (int j = 0; j < K; ++j) {
+        const int o = my_ids[j];
+        rank += (o < mine || (o == mine && j < pos)) ? 1 : 0;
+      }
+      sorted[i] = rank;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < KPL; ++i) {
+      const int pos = lane * KPL + i;
+      const int mine = my_ids[pos];
+      if (pos < K) out[sorted[i]] = (mine == 0x7fffffff) ? -1 : mine;
+    }
+    __syncwarp();
+    // re-read the sorted ids (written by this warp) to form the scores
+    for (int kp = 0; kp < K; ++kp) {
+      const int id = out[kp];
+      for (int g = 0; g < G; ++g) {
+        float acc = 0.f;
+        if (id >= 0) {
+          const T* krow = lmks + (((int64_t)b * p.N + id) * HL + (p.per_qhead ? h * G + g : h)) * D;
+          const float* qr = q_s + (size_t)(row * G + g) * D;
+          for (int d = lane; d < D; d += 32) acc = fmaf(qr[d], to_f(krow[d]), acc);
+          acc = warp_sum(acc);
+        }
+        if (lane == 0)
+          scores[((((int64_t)b * p.L + l) * p.h_kv + h) * G + g) * K + kp] =
+              from_f<T>(id >= 0 ? acc * p.scale : -CUDART_INF_F);
+      }
+    }
+  }
+}
+
+// ---- backward of the returned scores ---------------------------------------------------------
+// dq[i,g] = scale * sum_k ds[i,g,k] k'_{id_k};  dk'_c += scale * ds[i,g,k] q[i,g]  (fp32 atomics)
+template <typename T>
+__global__ void __launch_bounds__(128) topk_bwd_kernel(
+    const T* __restrict__ ds, const int32_t* __restrict__ indices, const T* __restrict__ q,
+    const T* __restrict__ lmks, T* __restrict__ dq, float* __restrict__ dl, int L, int N, int h_kv, int G,
+    int D, int K, int per_qhead, float scale, int64_t rows) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 4 + warp;  // (b, l, h_kv, g)
+  if (row >= rows) return;
+  const int g = (int)(row % G);
+  const int64_t blh = row / G;
+  const int h = (int)(blh % h_kv);
+  const int64_t bl = blh / h_kv;
+  const int64_t b = bl / L;
+  const int HL = per_qhead ? h_kv * G : h_kv;
+  const int hl = per_qhead ? h * G + g : h;
+  const int32_t* ids = indices + blh * K;
+  const T* dsr = ds + row * K;
+  const T* qr = q + row * D;
+  for (int d0 = lane * 4; d0 < D; d0 += 128) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 qv = load4(qr + d0);
+    for (int k = 0; k < K; ++k) {
+      const int id = ids[k];
+      if (id < 0 || id >= N) continue;
+      const float s = to_f(dsr[k]) * scale;
+      const int64_t off = ((b * N + id) * HL + hl) * D + d0;
+      float4 kv = load4(lmks + off);
+      acc.x = fmaf(s, kv.x, acc.x); acc.y = fmaf(s, kv.y, acc.y);
+      acc.z = fmaf(s, kv.z, acc.z); acc.w = fmaf(s, kv.w, acc.w);
+      atomicAdd(dl + off + 0, s * qv.x); atomicAdd(dl + off + 1, s * qv.y);
+      atomicAdd(dl + off + 2, s * qv.z); atomicAdd(dl + off + 3, s * qv.w);
+    }
+    store4(dq + row * D + d0, acc);
+  }
+}
+
+template <typename T, int KPL>
+static int launch_topk(const TopkParams& p, cudaStream_t st) {
+  TopkParams pp = p;
+  // rows per warp: as many as fit in shared memory
+  size_t smem = 0;
+  int RW = 4;
+  for (; RW >= 1; RW >>= 1) {
+    int M = 4 * RW * p.G;
+    smem = ((size_t)M * p.D + (size_t)TN * (p.D + 4) + (size_t)M * TN + 2 * (size_t)M) * sizeof(float) +
+           4 * 32 * KPL * sizeof(int);
+    if (smem <= 200 * 1024) break;
+  }
+  if (RW < 1) {
+    set_error("topk_fwd: G*D = %d*%d does not fit in shared memory", p.G, p.D);
+    return HILS_ERR_UNSUPPORTED;
+  }
+  pp.RW = RW;
+  cudaError_t e = cudaFuncSetAttribute(topk_fwd_kernel<T, KPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return cuda_fail(e, "topk_fwd smem attribute");
+  dim3 grid(ceil_div(p.L, 4 * RW), p.h_kv, p.B);
+  topk_fwd_kernel<T, KPL><<<grid, 128, smem, st>>>(pp);
+  HILS_LAUNCH_CHECK("topk_fwd");
+  return HILS_OK;
+}
+
+}  // namespace hils
+
+using namespace hils;
+
+extern "C" int hils_topk_fwd(const void* q, const void* lmks, const void* lse_swa, const float* bias,
+                             const float* gumbel, const int32_t* drop_mask, int32_t* indices, void* scores,
+                             float* lse_total, float* rank_keys, int B, int L, int N, int h_kv, int G, int D,
+                             int topk, int block_size, int window_size, int is_causal, int q_offset,
+                             int per_qhead, float sm_scale, int dtype, int lse_dtype, void* stream) {
+  HILS_REQUIRE(B > 0 && L >= 0 && N >= 0 && h_kv > 0 && G > 0 && D > 0, "topk_fwd: non-positive size");
+  HILS_REQUIRE(topk > 0 && topk <= 128, "topk_fwd: topk (%d) must be in [1,128]", topk);
+  HILS_REQUIRE(block_size > 0, "topk_fwd: block_size must be positive");
+  HILS_REQUIRE(D % 4 == 0, "topk_fwd: D (%d) must be a multiple of 4", D);
+  HILS_REQUIRE(dtype == HILS_F32 || dtype == HILS_BF16, "topk_fwd: unknown dtype %d", dtype);
+  HILS_REQUIRE(lse_dtype == HILS_F32 || lse_dtype == HILS_BF16, "topk_fwd: unknown lse dtype %d", lse_dtype);
+  HILS_REQUIRE(B <= 65535 && h_kv <= 65535, "topk_fwd: B and h_kv must be <= 65535");
+  if (L == 0) return HILS_OK;
+  HILS_REQUIRE(q && lse_swa && indices && scores, "topk_fwd: null pointer");
+  HILS_REQUIRE(N == 0 || lmks, "topk_fwd: null chunk keys");
+  TopkParams p;
+  p.q = q; p.lmks = lmks; p.lse_swa = lse_swa; p.bias = bias; p.gumbel = gumbel; p.drop_mask = drop_mask;
+  p.indices = indices; p.scores = scores; p.lse_total = lse_total; p.rank_keys = rank_keys;
+  p.B = B; p.L = L; p.N = N; p.h_kv = h_kv; p.G = G; p.D = D; p.topk = topk; p.block_size = block_size;
+  p.window_size = window_size; p.is_causal = is_causal; p.q_offset = q_offset; p.per_qhead = per_qhead;
+  p.lse_dtype = lse_dtype; p.RW = 4; p.scale = sm_scale;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int kpl = (topk + 31) / 32;
+  if (dtype == HILS_BF16) {
+    if (kpl == 1) return launch_topk<bf16, 1>(p, st);
+    if (kpl == 2) return launch_topk<bf16, 2>(p, st);
+    return launch_topk<bf16, 4>(p, st);
+  }
+  if (kpl == 1) return launch_topk<float, 1>(p, st);
+  if (kpl == 2) return launch_topk<float, 2>(p, st);
+  return launch_topk<float, 4>(p, st);
+}
+
+extern "C" int hils_topk_bwd(const void* d_scores, const int32_t* indices, const void* q, const void* lmks,
+                             void* d_q, float* d_lmks_f32, void* d_lmks, int B, int L, int N, int h_kv, int G,
+                             int D, int topk, int per_qhead, float sm_scale, int dtype, void* stream) {
+  HILS_REQUIRE(B > 0 && L >= 0 && N >= 0 && h_kv > 0 && G > 0 && D > 0 && topk > 0, "topk_bwd: bad size");
+  HILS_REQUIRE(D % 4 == 0, "topk_bwd: D (%d) must be a multiple of 4", D);
+  HILS_REQUIRE(dtype == HILS_F32 || dtype == HILS_BF16, "topk_bwd: unknown dtype %d", dtype);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int HL = per_qhead ? h_kv * G : h_kv;
+  const int64_t nl = (int64_t)B * N * HL * D;
+  if (nl > 0) {
+    HILS_REQUIRE(d_lmks_f32 && d_lmks, "topk_bwd: null chunk-key gradient buffers");
+    cudaError_t e = cudaMemsetAsync(d_lmks_f32, 0, nl * sizeof(float), st);
+    if (e != cudaSuccess) return cuda_fail(e, "topk_bwd memset");
+  }
+  const int64_t rows = (int64_t)B * L * h_kv * G;
+  if (rows > 0) {
+    HILS_REQUIRE(d_scores && indices && q && d_q, "topk_bwd: null pointer");
+    const int blocks = (int)((rows + 3) / 4);
+    if (dtype == HILS_BF16)
+      topk_bwd_kernel<bf16><<<blocks, 128, 0, st>>>((const bf16*)d_scores, indices, (const bf16*)q,
+                                                   (const bf16*)lmks, (bf16*)d_q, d_lmks_f32, L, N, h_kv, G, D,
+                                                   topk, per_qhead, sm_scale, rows);
+    else
+      topk_bwd_kernel<float><<<blocks, 128, 0, st>>>((const float*)d_scores, indices, (const float*)q,
+                                                    (const float*)lmks, (float*)d_q, d_lmks_f32, L, N, h_kv, G,
+                                                    D, topk, per_qhead, sm_scale, rows);
+    HILS_LAUNCH_CHECK("topk_bwd");
+  }
+  if (nl > 0) {
+    if (dtype == HILS_BF16)
+      launch_cast_from_f32<bf16>(d_lmks_f32, (bf16*)d_lmks, nl, st);
+    else
+      launch_cast_from_f32<float>(d_lmks_f32, (float*)d_lmks, nl, st);
+    HILS_LAUNCH_CHECK("topk_bwd cast");
+  }
+  return HILS_OK;
+}

@@ -1,0 +1,160 @@
+/*
+ * hils_b200 -- C ABI of the B200 (sm_100a) HiLS sparse-attention kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and scalars; no torch types cross this
+ * boundary.  All tensors are dense row-major in the reference's layouts:
+ *     q (B, L, h_q, D)   k, v (B, T, h_kv, D)   chunk keys (B, N, h, D)
+ *     indices (B, L, h_kv, K) int32   weights (B, L, h_q, num_weights)
+ * `dtype` selects the element type of the activation tensors (HILS_BF16 or HILS_F32); all
+ * arithmetic accumulates in fp32.  `stream` is a cudaStream_t passed as void*.  Calls enqueue
+ * work on that stream and return without synchronising.
+ *
+ * Return value: 0 on success, a negative HILS_ERR_* code on an argument or launch error
+ * (hils_last_error() gives the text).  The library never allocates device memory; kernels that
+ * need scratch take a caller-provided workspace whose size the matching *_workspace_bytes()
+ * function returns.
+ *
+ * Each declaration names the reference interface (file:line within the reference project) that
+ * the entry point replaces.
+ */
+#ifndef HILS_B200_H
+#define HILS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HILS_F32 0
+#define HILS_BF16 1
+
+#define HILS_OK 0
+#define HILS_ERR_BAD_ARG (-1)
+#define HILS_ERR_UNSUPPORTED (-2)
+#define HILS_ERR_CUDA (-3)
+#define HILS_ERR_WORKSPACE (-4)
+
+/* Library identification and the text of the last error raised on the calling thread. */
+int hils_version(void);
+const char* hils_last_error(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Chunk pooling.  Replaces ChunkAttnPoolFunction.forward/backward and the kernels behind it
+ * (ops/chunk_attn_pool_tilelang.py:540-602, kernels :329-533) and the GQA-aware contract of
+ * chunk_attn_pool (models/FlashHiLS/hils_attention.py:66-135).
+ *   mu_q (B,N,h_q,D); k: token rows of chunk n start at k + b*k_batch_stride + n*S*h_kv*D
+ *   (so a (B,T,h_kv,D) cache can be pooled in place); h_q = G*h_kv.
+ *   lmk_k (B,N,h_q,D) in `dtype`, lmk_b (B,N,h_q) fp32.  compact != 0: lmk_k is written as 0.
+ * Backward recomputes the softmax; g_lmk_k / g_lmk_b may be NULL (treated as zero).
+ *   d_mu_q (B,N,h_q,D), d_k (B,N,S,h_kv,D) dense, both in `dtype` (summed over the GQA group).
+ * ------------------------------------------------------------------------------------- */
+int hils_pool_fwd(const void* mu_q, const void* k, void* lmk_k, float* lmk_b,
+                  int B, int N, int S, int h_q, int h_kv, int D, int64_t k_batch_stride,
+                  float sm_scale, int compact, int dtype, void* stream);
+int hils_pool_bwd(const void* mu_q, const void* k, const void* g_lmk_k, const float* g_lmk_b,
+                  void* d_mu_q, void* d_k,
+                  int B, int N, int S, int h_q, int h_kv, int D, int64_t k_batch_stride,
+                  float sm_scale, int compact, int dtype, void* stream);
+
+/* Mean pooling of each chunk (the `.mean(dim=2)` of models/FlashHiLS/hils_attention.py:445-446,
+ * 458-462) and its gradient.  out (B,N,h_kv,D); d_k (B,N,S,h_kv,D) dense. */
+int hils_meanpool_fwd(const void* k, void* out, int B, int N, int S, int h_kv, int D,
+                      int64_t k_batch_stride, int dtype, void* stream);
+int hils_meanpool_bwd(const void* g_out, void* d_k, int B, int N, int S, int h_kv, int D,
+                      int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Chunk selection.  Replaces SoftmaxTopKMaxPoolingFusedFn.forward (ops/topk_head_softmax.py:
+ * 977-1038: hils_lse_kernel :192, torch.logaddexp :1019, weighted_select_kernel :438,
+ * sort_topk_indices_kernel :870, recompute_topk_max_pooling_scores_kernel :669) in one launch.
+ *   q (B,L,h_kv,G,D); lmks (B,N,h_kv,D) or, per_qhead != 0, (B,N,h_kv*G,D); both in `dtype`.
+ *   lse_swa (B,L,h_kv*G) in lse_dtype; bias (B,N,h_kv,G) fp32 or NULL; gumbel (h_kv*G, N) fp32
+ *   or NULL; drop_mask (B,L,N) int32 or NULL.
+ *   indices (B,L,h_kv,topk) int32 ascending, -1 padded; scores (B,L,h_kv*G,topk) in `dtype`
+ *   (= fl(scale*q.k'), -inf at -1).
+ *   Optional fp32 diagnostics (NULL to skip): lse_total (B,L,h_kv,G); rank_keys (B,L,h_kv,N) =
+ *   the value the selector ranked, -inf for non-candidates.
+ * q_offset is a host scalar (the reference builds a 1-element tensor from a Python int, :1199).
+ * ------------------------------------------------------------------------------------- */
+int hils_topk_fwd(const void* q, const void* lmks, const void* lse_swa, const float* bias,
+                  const float* gumbel, const int32_t* drop_mask,
+                  int32_t* indices, void* scores, float* lse_total, float* rank_keys,
+                  int B, int L, int N, int h_kv, int G, int D, int topk,
+                  int block_size, int window_size, int is_causal, int q_offset, int per_qhead,
+                  float sm_scale, int dtype, int lse_dtype, void* stream);
+
+/* Gradient of the returned scores (SoftmaxTopKMaxPoolingFusedFn.backward, :1040-1092, which
+ * scatters into a dense (B,h_kv,G,L,N) tensor and runs two bmm).  Here: a K-sparse gather for
+ * dq and an fp32 scatter-add for the chunk keys.
+ *   d_scores (B,L,h_kv*G,topk) in `dtype`; d_q (B,L,h_kv,G,D) in `dtype`;
+ *   d_lmks_f32: fp32 accumulator with the shape of lmks, zeroed by this call;
+ *   d_lmks: same shape in `dtype` (written from the accumulator). */
+int hils_topk_bwd(const void* d_scores, const int32_t* indices, const void* q, const void* lmks,
+                  void* d_q, float* d_lmks_f32, void* d_lmks,
+                  int B, int L, int N, int h_kv, int G, int D, int topk, int per_qhead,
+                  float sm_scale, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Sparse chunk attention.  Replaces _hils_block_M_attention_inverse.forward/backward
+ * (ops/hils_fwd_bwd_head.py:771-913; kernels :198-496 and :506-766).
+ *   o_i = sum_k w[i,k] * softmax_{j in chunk ids[i,k]}(scale*q_i.K_j - slope*max(0,S-2-j)) V_j
+ *   q (B,L,h_q,D), k (B,T,h_kv,D), v (B,T,h_kv,Dv), weights (B,L,h_q,num_weights) (first K
+ *   columns used), indices (B,L,h_kv,K); ids < 0 end a row's list.  slope (h_q) fp32 or NULL.
+ * Backward: d_q, d_k, d_v, d_w in `dtype`; d_w has num_weights columns, those >= K are zero.
+ * workspace: hils_sparse_attn_bwd_workspace_bytes() bytes of scratch (fp32 accumulators).
+ * ------------------------------------------------------------------------------------- */
+int hils_sparse_attn_fwd(const void* q, const void* k, const void* v, const void* weights,
+                         const int32_t* indices, const float* slope, void* o,
+                         int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K,
+                         int num_weights, int chunk_size, float sm_scale, int mask_last_token,
+                         int dtype, void* workspace, size_t workspace_bytes, void* stream);
+size_t hils_sparse_attn_fwd_workspace_bytes(int B, int L, int T, int h_q, int h_kv, int D, int Dv,
+                                            int K, int chunk_size, int dtype);
+int hils_sparse_attn_bwd(const void* q, const void* k, const void* v, const void* weights,
+                         const int32_t* indices, const float* slope, const void* d_o,
+                         void* d_q, void* d_k, void* d_v, void* d_w,
+                         int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K,
+                         int num_weights, int chunk_size, float sm_scale, int mask_last_token,
+                         int dtype, void* workspace, size_t workspace_bytes, void* stream);
+size_t hils_sparse_attn_bwd_workspace_bytes(int B, int L, int T, int h_q, int h_kv, int D, int Dv,
+                                            int K, int chunk_size, int dtype);
+
+/* ---------------------------------------------------------------------------------------
+ * Exact per-chunk log Z.  Replaces _ExactChunkLogZ.forward/backward
+ * (ops/exact_chunk_log_z_tilelang.py:394-478; kernels :25-137, :148-262, :273-391).
+ *   q (B,L,h_q,D), k (B,L,h_kv,D); log_z (B,L,h_q,ceil(L/S)) fp32, -inf where chunk c is not
+ *   strictly left of the snapped window of row i (i < (c+1)*S + W - 1).
+ *   Backward (mask_lmk == 0 only): d_q, d_k in `dtype`.
+ * ------------------------------------------------------------------------------------- */
+int hils_chunk_logz_fwd(const void* q, const void* k, float* log_z,
+                        int B, int L, int h_q, int h_kv, int D, int chunk_size, int window_size,
+                        float sm_scale, int mask_lmk, int dtype, void* stream);
+int hils_chunk_logz_bwd(const void* q, const void* k, const float* log_z, const float* d_log_z,
+                        void* d_q, void* d_k,
+                        int B, int L, int h_q, int h_kv, int D, int chunk_size, int window_size,
+                        float sm_scale, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Sliding-window branch with chunk-snapped left edge.  Replaces _FlexAttnTL.forward/backward
+ * (ops/flex_attn_tilelang.py:609-719; kernels :26-267, :279-588).
+ *   q (B,Lq,h_q,D), k (B,Lk,h_kv,D), v (B,Lk,h_kv,Dv); o (B,Lq,h_q,Dv) in `dtype`;
+ *   lse (B,Lq,h_q) fp32, natural log; rows with no visible key give o = 0, lse = -inf.
+ *   Query i sits at absolute position kv_start + (Lk-Lq) + i.
+ *   Backward takes d_o and d_lse (fp32, may be NULL) and writes d_q, d_k, d_v in `dtype`.
+ * ------------------------------------------------------------------------------------- */
+int hils_swa_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                 int B, int Lq, int Lk, int h_q, int h_kv, int D, int Dv,
+                 int window_size, int chunk_size, int mask_lmk, int expand_to_chunk,
+                 float sm_scale, int kv_start, int dtype, void* stream);
+int hils_swa_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                 const void* d_o, const float* d_lse, void* d_q, void* d_k, void* d_v,
+                 int B, int L, int h_q, int h_kv, int D, int Dv,
+                 int window_size, int chunk_size, int mask_lmk, int expand_to_chunk,
+                 float sm_scale, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HILS_B200_H */

@@ -1,0 +1,342 @@
+"""Parity of the CUDA ops (called through the C ABI) with the CPU oracle and with the golden
+fixtures produced by the reference's own functions.  Needs a B200."""
+import math
+
+import pytest
+import torch
+
+from oracle import hils_oracle as orc
+from tests.util import check, cuda, golden, rms_ratio
+
+pytestmark = pytest.mark.gpu
+BF, F32 = torch.bfloat16, torch.float32
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import hils_attention_b200 as pkg
+    return pkg
+
+
+# ------------------------------------------------------------------ pooling
+@pytest.mark.parametrize("tag", ["a", "b"])
+@pytest.mark.parametrize("dtype", [BF, F32])
+def test_pool_golden(ops, tag, dtype):
+    g = golden(f"pool_{tag}.npz")
+    mu = cuda(g["mu_q"], dtype).requires_grad_(True)
+    kc = cuda(g["k_chunked"], dtype).requires_grad_(True)
+    lk, lb = ops.chunk_attn_pool(mu, kc)
+    assert lk.dtype == dtype and lb.dtype == F32
+    check(lk, g["lmk_k"], dtype, "lmk_k")
+    check(lb, g["lmk_b"], F32 if dtype == F32 else BF, "lmk_b")
+    (lk.float() * cuda(g["g_lmk_k"])).sum().add((lb * cuda(g["g_lmk_b"])).sum()).backward()
+    check(mu.grad, g["d_mu_q"], dtype, "d_mu_q", scale=3.0)
+    check(kc.grad, g["d_k"], dtype, "d_k", scale=3.0)
+
+
+@pytest.mark.parametrize("shape", [(1, 64, 2, 128, 64), (2, 128, 4, 128, 64), (4, 256, 2, 128, 64),
+                                   (1, 32, 2, 64, 64), (1, 16, 1, 128, 32)])
+def test_pool_reference_shapes(ops, shape):
+    """The forward cases of the reference's pool unit test, with its thresholds
+    (ratio 0.005 for k', 0.01 for b')."""
+    B, N, H, D, S = shape
+    g = torch.Generator().manual_seed(42)
+    mu = torch.randn(B, N, H, D, generator=g).to(BF)
+    kc = torch.randn(B, N, S, H, D, generator=g).to(BF)
+    lk_ref, lb_ref = orc.chunk_attn_pool(mu, kc)
+    lk, lb = ops.chunk_attn_pool_tilelang(mu.cuda(), kc.cuda())
+    assert rms_ratio(lk, lk_ref) < 0.005
+    assert rms_ratio(lb, lb_ref) < 0.01
+
+
+def test_pool_gqa_in_place_cache_view_and_compact(ops):
+    g = torch.Generator().manual_seed(3)
+    B, T, h_kv, G, D, S = 2, 200, 2, 4, 64, 64
+    N = T // S
+    k = torch.randn(B, T, h_kv, D, generator=g).to(BF)
+    mu = torch.randn(B, N, h_kv * G, D, generator=g).to(BF)
+    kc = k[:, :N * S].reshape(B, N, S, h_kv, D)
+    lk_ref, lb_ref = orc.chunk_attn_pool(mu, kc)
+    kd = k.cuda()
+    view = kd[:, :N * S].view(B, N, S, h_kv, D)            # batch-strided view of the cache
+    lk, lb = ops.chunk_attn_pool(mu.cuda(), view)
+    check(lk, lk_ref, BF, "gqa lmk_k")
+    check(lb, lb_ref, BF, "gqa lmk_b")
+    lk0, lb0 = ops.chunk_attn_pool_tilelang(mu.cuda(), view, compact_lmk_k=True)
+    assert float(lk0.float().abs().max()) == 0.0
+    assert torch.equal(lb0, lb)
+    mp = ops.chunk_mean_pool(view)
+    check(mp, orc.chunk_mean_pool(kc), BF, "mean pool")
+
+
+def test_pool_gqa_backward_and_mean_backward(ops):
+    g = torch.Generator().manual_seed(4)
+    B, N, h_kv, G, D, S = 1, 5, 2, 2, 32, 32
+    mu0 = torch.randn(B, N, h_kv * G, D, generator=g)
+    kc0 = torch.randn(B, N, S, h_kv, D, generator=g)
+    gk = torch.randn(B, N, h_kv * G, D, generator=g)
+    gb = torch.randn(B, N, h_kv * G, generator=g)
+    mu_r, kc_r = mu0.clone().requires_grad_(True), kc0.clone().requires_grad_(True)
+    lk_r, lb_r = orc.chunk_attn_pool(mu_r, kc_r)
+    ((lk_r * gk).sum() + (lb_r * gb).sum() + (orc.chunk_mean_pool(kc_r) * gk[:, :, ::G]).sum()).backward()
+    mu, kc = mu0.cuda().requires_grad_(True), kc0.cuda().requires_grad_(True)
+    lk, lb = ops.chunk_attn_pool(mu, kc)
+    ((lk * gk.cuda()).sum() + (lb * gb.cuda()).sum() + (ops.chunk_mean_pool(kc) * gk[:, :, ::G].cuda()).sum()).backward()
+    check(mu.grad, mu_r.grad, F32, "gqa d_mu", scale=3.0)
+    check(kc.grad, kc_r.grad, F32, "gqa d_k", scale=3.0)
+
+
+def test_pool_errors(ops):
+    with pytest.raises(ValueError):
+        ops.chunk_attn_pool(torch.zeros(1, 2, 3, 8).cuda(), torch.zeros(1, 2, 4, 2, 8).cuda())   # 3 % 2
+    with pytest.raises(ValueError):
+        ops.chunk_attn_pool(torch.zeros(1, 2, 8).cuda(), torch.zeros(1, 2, 4, 2, 8).cuda())
+
+
+# ------------------------------------------------------------------ selection
+def _select_args(g):
+    K, S, W, qo = [int(x) for x in g["args"]]
+    return K, S, W, qo
+
+
+@pytest.mark.parametrize("tag", ["shared", "bias_pq", "decode", "ragged"])
+@pytest.mark.parametrize("dtype", [BF, F32])
+def test_topk_golden(ops, tag, dtype):
+    g = golden(f"topk_{tag}.npz")
+    K, S, W, qo = _select_args(g)
+    B, L, h_kv, G, D = g["q"].shape
+    per_q = g["lmks"].shape[2] == h_kv * G and G > 1
+    aux = {}
+    idx, sc = ops.online_softmax_topk_head(
+        cuda(g["q"], dtype), cuda(g["lmks"], dtype), cuda(g["lse_swa"]), K, S, W, True, qo,
+        is_training=(qo == 0), bias=None if "bias" not in g else g["bias"].cuda(),
+        gumbel_noise=None if "gumbel" not in g else g["gumbel"].cuda(), G=(G if per_q else 1), _aux=aux)
+    assert idx.dtype == torch.int32 and idx.shape == (B, L, h_kv, K)
+    # the selector itself is bit-exact on the values it ranked
+    assert torch.equal(idx.cpu(), orc.stable_topk_from_keys(aux["rank_keys"].cpu(), K))
+    # and on these small cases it reproduces the reference's ids outright
+    assert torch.equal(idx.cpu(), g["indices"].to(torch.int32))
+    check(sc.view(B, L, h_kv, G, K), g["scores"], dtype, "scores")
+    _, _, oaux = orc.topk_select(g["q"], g["lmks"], g["lse_swa"], K, S, W, True, qo, bias=g.get("bias"),
+                                 gumbel_noise=g.get("gumbel"), return_aux=True)
+    check(aux["lse_total"], oaux["lse_total"], F32, "lse_total", scale=10.0)
+
+
+@pytest.mark.parametrize("cfg", [(2, 1000, 2, 8, 64, 16, 64, 64), (1, 1024, 4, 1, 128, 32, 64, 512),
+                                 (1, 700, 1, 2, 64, 64, 32, 96)])
+def test_topk_selector_exact_and_match_rate(ops, cfg):
+    """Larger seeded cases: ids bit-exact against the stable selector fed the kernel's own fp32
+    ranking values; ranking values within tolerance of the oracle; >= 99% of the ids equal to the
+    oracle's own choice (the reference's acceptance threshold, ops/topk_head_softmax.py:1472)."""
+    B, L, h_kv, G, D, K, S, W = cfg
+    N = L // S
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(B, L, h_kv, G, D, generator=g).to(BF)
+    lm = torch.randn(B, N, h_kv, D, generator=g).to(BF)
+    lse = torch.randn(B, L, h_kv * G, generator=g) + 2
+    bias = torch.randn(B, N, h_kv * G, generator=g)
+    aux = {}
+    idx, sc = ops.online_softmax_topk_head(q.cuda(), lm.cuda(), lse.cuda(), K, S, W, bias=bias.cuda(), _aux=aux)
+    keys = aux["rank_keys"].cpu()
+    assert torch.equal(idx.cpu(), orc.stable_topk_from_keys(keys, K))
+    ridx, rsc, raux = orc.topk_select(q, lm, lse, K, S, W, True, 0, bias=bias, return_aux=True)
+    check(keys, raux["keys"], F32, "rank keys", scale=20.0)
+    match = (idx.cpu() == ridx).float().mean().item()
+    assert match >= 0.99, match
+    same = (idx.cpu() == ridx).all(-1)
+    check(sc.view(B, L, h_kv, G, K)[same], rsc[same], BF, "scores")
+
+
+def test_topk_ties_prefer_lower_id_and_padding(ops):
+    """All chunk keys identical -> every candidate ties; the K lowest ids must win.  Rows with
+    fewer than K candidates are -1 padded and their scores are -inf."""
+    B, L, H, D, S, W, K = 1, 512, 1, 64, 64, 64, 4
+    N = L // S
+    q = torch.randn(B, L, H, D, generator=torch.Generator().manual_seed(5)).to(BF)
+    lm = torch.ones(B, N, H, D).to(BF)
+    lse = torch.zeros(B, L, H)
+    idx, sc = ops.online_softmax_topk_head(q.cuda(), lm.cuda(), lse.cuda(), K, S, W)
+    idx = idx.cpu()
+    for l in (0, 63, 127, 128, 200, 320, 511):
+        lim = max(0, (l - W + 1) // S)
+        want = list(range(min(lim, K))) + [-1] * (K - min(lim, K))
+        assert idx[0, l, 0].tolist() == want, (l, idx[0, l, 0].tolist())
+    assert torch.isinf(sc.cpu().float()[idx.repeat_interleave(1, 2) < 0]).all()
+
+
+def test_topk_drop_mask_and_backward(ops):
+    g = torch.Generator().manual_seed(6)
+    B, L, h_kv, G, D, K, S, W = 1, 384, 2, 2, 32, 4, 32, 64
+    N = L // S
+    q0 = torch.randn(B, L, h_kv * G, D, generator=g)
+    lm0 = torch.randn(B, N, h_kv, D, generator=g)
+    lse = torch.randn(B, L, h_kv * G, generator=g)
+    drop = (torch.rand(B, L, N, generator=g) < 0.3).to(torch.int32)
+    gs = torch.randn(B, L, h_kv * G, K, generator=g)
+    q, lm = q0.cuda().requires_grad_(True), lm0.cuda().requires_grad_(True)
+    idx, sc = ops.online_softmax_topk_head(q, lm, lse.cuda(), K, S, W, drop_mask=drop.cuda())
+    ridx, rsc = orc.topk_select(q0.view(B, L, h_kv, G, D), lm0, lse, K, S, W, True, 0, drop_mask=drop)
+    assert torch.equal(idx.cpu(), ridx)
+    dropped = torch.gather(drop.unsqueeze(2).expand(-1, -1, h_kv, -1), -1, ridx.clamp_min(0).long())
+    assert int((dropped * (ridx >= 0)).sum()) == 0
+    valid = (idx >= 0).repeat_interleave(G, dim=2)
+    (sc.float().masked_fill(~valid, 0.0) * gs.cuda()).sum().backward()
+    # oracle gradient: scores = scale * <q, lmk[id]>
+    qr, lr = q0.clone().requires_grad_(True), lm0.clone().requires_grad_(True)
+    sel = lr[0][ridx[0].clamp_min(0).long(), torch.arange(h_kv).view(1, h_kv, 1)]          # (L,h_kv,K,D)
+    s = torch.einsum("lhgd,lhkd->lhgk", qr[0].view(L, h_kv, G, D), sel) / math.sqrt(D)
+    (s.reshape(1, L, h_kv * G, K).masked_fill(~valid.cpu(), 0.0) * gs).sum().backward()
+    check(q.grad, qr.grad, F32, "dq", scale=5.0)
+    check(lm.grad, lr.grad, F32, "dlmk", scale=50.0)
+
+
+# ------------------------------------------------------------------ sparse attention
+@pytest.mark.parametrize("tag", ["a", "kvlong"])
+@pytest.mark.parametrize("dtype", [F32, BF])
+def test_sparse_golden(ops, tag, dtype):
+    g = golden(f"sparse_{tag}.npz")
+    S = int(g["args"][0])
+    q, k, v, w = [cuda(g[n], dtype).requires_grad_(True) for n in ("q", "k", "v", "w")]
+    idx = g["indices"].cuda()
+    if dtype == F32:
+        ref = {n: g[n] for n in ("o", "dq", "dk", "dv", "dw")}
+    else:                                   # oracle on the bf16-rounded inputs
+        qr, kr, vr, wr = [t.detach().float().cpu().requires_grad_(True) for t in (q, k, v, w)]
+        o_r = orc.sparse_attn(qr, kr, vr, wr, g["indices"], chunk_size=S)
+        o_r.backward(g["do"].to(BF).float())
+        ref = {"o": o_r, "dq": qr.grad, "dk": kr.grad, "dv": vr.grad, "dw": wr.grad}
+    o = ops.HiLS_block_M_head(q, k, v, w, idx, block_size=S, mask_last_token=True,
+                              dtype="float" if dtype == F32 else "bfloat16")
+    check(o, ref["o"], dtype, "o")
+    o.backward(cuda(g["do"], dtype))
+    sc = {"dq": 5.0, "dk": 10.0, "dv": 10.0, "dw": 5.0}
+    for n, t in (("dq", q), ("dk", k), ("dv", v), ("dw", w)):
+        check(t.grad, ref[n], dtype, n, scale=sc[n])
+        assert rms_ratio(t.grad, ref[n]) < (5e-3 if dtype == F32 else 2e-2), n
+
+
+def test_sparse_unsorted_ids_slope_and_eval_mode(ops):
+    g = torch.Generator().manual_seed(8)
+    B, L, H, HQ, D, K, S = 1, 128, 1, 2, 32, 4, 32
+    q = torch.randn(B, L, HQ, D, generator=g)
+    k = torch.randn(B, L, H, D, generator=g)
+    v = torch.randn(B, L, H, D, generator=g)
+    idx = torch.stack([torch.randperm(L // S, generator=g)[:K] for _ in range(L)]).view(B, L, H, K).to(torch.int32)
+    idx[:, ::3, :, -1] = -1
+    w = torch.rand(B, L, HQ, K + 1, generator=g)
+    slope = torch.tensor([0.05, 0.2])
+    ref = orc.sparse_attn(q, k, v, w, idx, chunk_size=S, mask_last_token=False, slope=slope)
+    o = ops.HiLS_block_M_head(q.cuda(), k.cuda(), v.cuda(), w.cuda(), idx.cuda(), block_size=S,
+                              mask_last_token=False, is_training=False, slope=slope.cuda(), dtype="float")
+    check(o, ref, F32, "o slope/unsorted")
+    qg = q.cuda().requires_grad_(True)
+    o2 = ops.HiLS_block_M_head(qg, k.cuda(), v.cuda(), w.cuda(), idx.cuda(), block_size=S, is_training=False)
+    with pytest.raises(RuntimeError):
+        o2.sum().backward()
+
+
+# ------------------------------------------------------------------ exact log Z
+@pytest.mark.parametrize("tag", ["a", "b"])
+@pytest.mark.parametrize("dtype", [F32, BF])
+def test_logz_golden_and_backward(ops, tag, dtype):
+    g = golden(f"logz_{tag}.npz")
+    S, W = [int(x) for x in g["args"]]
+    q = cuda(g["q"], dtype).requires_grad_(True)
+    k = cuda(g["k"], dtype).requires_grad_(True)
+    lz = ops.exact_chunk_log_z_tl(q, k, chunk_size=S, window_size=W)
+    qr, kr = q.detach().float().cpu().requires_grad_(True), k.detach().float().cpu().requires_grad_(True)
+    ref = orc.exact_chunk_log_z(qr, kr, chunk_size=S, window_size=W)
+    if dtype == F32:
+        check(lz, g["log_z"], F32, "log_z vs reference", scale=10.0)
+    check(lz, ref, F32 if dtype == F32 else BF, "log_z", scale=10.0 if dtype == F32 else 1.0)
+    gz = torch.randn(ref.shape, generator=torch.Generator().manual_seed(1))
+    fin = torch.isfinite(ref)
+    (ref.masked_fill(~fin, 0.0) * gz).sum().backward()
+    (lz.masked_fill(~fin.cuda(), 0.0) * gz.cuda()).sum().backward()
+    check(q.grad, qr.grad, dtype, "dq", scale=20.0)
+    check(k.grad, kr.grad, dtype, "dk", scale=20.0)
+
+
+def test_logz_mask_lmk_forward_only(ops):
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(1, 200, 4, 32, generator=g)
+    k = torch.randn(1, 200, 2, 32, generator=g)
+    qg = q.cuda().requires_grad_(True)
+    lz = ops.exact_chunk_log_z_tl(qg, k.cuda(), chunk_size=32, window_size=64, mask_lmk=True)
+    check(lz, orc.exact_chunk_log_z(q, k, chunk_size=32, window_size=64, mask_lmk=True), F32, "logz lmk", scale=10.0)
+    with pytest.raises(NotImplementedError):
+        lz[torch.isfinite(lz)].sum().backward()
+
+
+# ------------------------------------------------------------------ sliding-window branch
+SWA_CASES = [
+    # B, Lq, Lk, h_q, h_kv, D, W, S, mask_lmk, expand, kv_start
+    (1, 256, 256, 2, 1, 32, 64, 32, True, True, 0),
+    (2, 333, 333, 4, 2, 64, 128, 64, False, True, 0),
+    (1, 130, 130, 2, 2, 32, 48, 65, True, False, 0),
+    (1, 70, 70, 1, 1, 64, 512, 64, True, True, 0),
+    (1, 1, 300, 2, 1, 32, 64, 32, True, True, 0),       # decode
+    (1, 64, 192, 2, 2, 32, 64, 32, True, True, 0),      # chunk prefill
+    (1, 2, 100, 2, 1, 32, 64, 32, True, True, 156),     # truncated cache
+]
+
+
+@pytest.mark.parametrize("case", SWA_CASES)
+@pytest.mark.parametrize("dtype", [F32, BF])
+def test_swa_forward_backward(ops, case, dtype):
+    B, Lq, Lk, hq, hk, D, W, S, ml, ex, ks = case
+    g = torch.Generator().manual_seed(13)
+    q0 = torch.randn(B, Lq, hq, D, generator=g).to(dtype).float()
+    k0 = torch.randn(B, Lk, hk, D, generator=g).to(dtype).float()
+    v0 = torch.randn(B, Lk, hk, D, generator=g).to(dtype).float()
+    training = (Lq == Lk and ks == 0)
+    qr, kr, vr = [t.clone().requires_grad_(True) for t in (q0, k0, v0)]
+    o_r, lse_r = orc.swa(qr, kr, vr, W, S, mask_lmk=ml, expand_to_chunk=ex, kv_start=ks)
+    q, k, v = [cuda(t, dtype).requires_grad_(training) for t in (q0, k0, v0)]
+    o, lse = ops.flex_attn_tl(q, k, v, W, S, training=training, mask_lmk=ml, expand_to_chunk=ex, kv_start=ks)
+    assert o.dtype == dtype and lse.dtype == F32
+    check(o, o_r, dtype, "swa o")
+    check(lse, lse_r, dtype, "swa lse")
+    if not training:
+        return
+    do = torch.randn(o_r.shape, generator=g)
+    dl = torch.randn(lse_r.shape, generator=g)
+    fin = torch.isfinite(lse_r)
+    ((o_r * do).sum() + (lse_r.masked_fill(~fin, 0.0) * dl).sum()).backward()
+    ((o.float() * do.cuda()).sum() + (lse.masked_fill(~fin.cuda(), 0.0) * dl.cuda()).sum()).backward()
+    for n, t, r in (("dq", q, qr), ("dk", k, kr), ("dv", v, vr)):
+        check(t.grad, r.grad, dtype, "swa " + n, scale=10.0)
+
+
+def test_swa_errors(ops):
+    x = torch.zeros(1, 8, 1, 32).cuda()
+    with pytest.raises(ValueError):
+        ops.flex_attn_tl(x, x, x, 4, 4, training=True, kv_start=3)
+    o, _ = ops.flex_attn_tl(x.requires_grad_(True), x, x, 4, 4, training=False)
+    with pytest.raises(RuntimeError):
+        o.sum().backward()
+
+
+# ------------------------------------------------------------------ whole naive block-sparse attention
+@pytest.mark.parametrize("tag", ["mha", "gqa", "lmk"])
+def test_naive_bsa_identity_on_gpu(ops, tag):
+    """flex_attn_tl + exact_chunk_log_z_tl + stable top-k + softmax + HiLS_block_M_head + addcmul
+    reproduces the reference's dense naive-BSA output (fp32)."""
+    g = golden(f"bsa_{tag}.npz")
+    S, W, K, ml = [int(x) for x in g["args"]]
+    q, k, v = g["q"].cuda(), g["k"].cuda(), g["v"].cuda()
+    B, L, hq, D = q.shape
+    G = hq // k.shape[2]
+    swa_o, lse = ops.flex_attn_tl(q, k, v, W, S, training=True, mask_lmk=bool(ml), expand_to_chunk=True)
+    lz = ops.exact_chunk_log_z_tl(q, k, chunk_size=S, window_size=W, mask_lmk=bool(ml))
+    n_chunk = lz.shape[-1]
+    lse_h = torch.logsumexp(lz, -1).nan_to_num(nan=float("-inf"))
+    keys = (lz - torch.logaddexp(lse, lse_h).unsqueeze(-1)).view(B, L, hq // G, G, n_chunk).max(3).values
+    idx = orc.stable_topk_from_keys(keys.nan_to_num(nan=float("-inf")).cpu(), K).cuda()
+    idx_hq = idx.repeat_interleave(G, 2)
+    sel = torch.gather(lz, -1, idx_hq.clamp_min(0).long()).masked_fill(idx_hq < 0, float("-inf"))
+    w = torch.softmax(torch.cat([sel, lse.unsqueeze(-1)], -1), -1)
+    o_h = ops.HiLS_block_M_head(q, k, v, w.contiguous(), idx, block_size=S, mask_last_token=bool(ml),
+                                is_training=False, dtype="float")
+    o = torch.addcmul(o_h, swa_o, w[..., -1:])
+    check(o, g["o"], F32, "naive bsa", scale=2.0)
