@@ -38,6 +38,14 @@ SIGNATURES = {
     "hils_swa_bwd": (_I, [_P] * 10 + [_I] * 10 + [_F, _I, _P]),
 }
 
+# kernels each entry point launches (memsets excluded); used to report launch counts
+KERNELS_PER_CALL = {
+    "hils_pool_fwd": 1, "hils_pool_bwd": 1, "hils_meanpool_fwd": 1, "hils_meanpool_bwd": 1,
+    "hils_topk_fwd": 1, "hils_topk_bwd": 2, "hils_sparse_attn_fwd": 1, "hils_sparse_attn_bwd": 3,
+    "hils_chunk_logz_fwd": 1, "hils_chunk_logz_bwd": 2, "hils_swa_fwd": 1, "hils_swa_bwd": 2,
+}
+_launches = 0
+
 _lib: Optional[C.CDLL] = None
 
 
@@ -85,8 +93,10 @@ def stream() -> int:
 
 def call(name: str, *args):
     """Invoke a status-returning entry point and raise HilsError on failure."""
+    global _launches
     lib = load()
     rc = getattr(lib, name)(*args)
+    _launches += KERNELS_PER_CALL.get(name, 1)
     if rc != 0:
         msg = lib.hils_last_error().decode("utf-8", "replace")
         raise HilsError(f"{name} failed with status {rc}: {msg}")
@@ -94,3 +104,8 @@ def call(name: str, *args):
 
 def query(name: str, *args) -> int:
     return int(getattr(load(), name)(*args))
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far by this process."""
+    return _launches

@@ -1,0 +1,185 @@
+"""The attention chain of the reference's HiLS attention module, on the B200 ops.
+
+``HiLSAttentionCore.forward`` follows ``HiLSAttention.forward`` of the reference
+(models/FlashHiLS/hils_attention.py:490-633) from the point where q, k, v and the landmark query
+are projected, normalised and rotated (:503-508) up to the tensor handed to ``o_proj`` (:631):
+
+  cache update (:512-523) -> flex_attn_tl (:536-547) -> chunk keys (:556, _compute_landmark_keys
+  :342-464 incl. the incremental pooling of just-completed chunks during decode) -> chunk selection
+  (:568-580) -> prior-bias gather and inter-chunk softmax (:585-610) -> sparse chunk attention (:619)
+  -> combine with the sliding-window branch (:620-629).
+
+Projections, RMS norms and rotary embedding stay with the caller (stock transformer plumbing).
+``install_into_reference()`` registers this package's ops under the module names the reference
+imports (``ops.hils_fwd_bwd_head`` ...), so the reference's own module file binds them unchanged.
+"""
+from __future__ import annotations
+
+import sys
+import types
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import ops
+
+
+@dataclass
+class HiLSAttentionConfig:
+    """The subset of the reference's HiLSConfig that the attention chain reads
+    (models/FlashHiLS/hils_attention.py:226-278)."""
+    num_attention_heads: int
+    num_key_value_heads: int
+    hils_topk: int = 32
+    chunk_size: int = 64
+    hils_sliding_window: int = 512
+    enable_prior_query: bool = True
+    enable_chunk_pooling: bool = False
+    enable_softmax1: bool = False
+    num_hidden_layers: int = 1
+
+
+class HiLSAttentionCore(torch.nn.Module):
+    def __init__(self, config: HiLSAttentionConfig, layer_idx: int = 0):
+        super().__init__()
+        self.config = config
+        self.layer_idx = layer_idx
+        self.h_q = config.num_attention_heads
+        self.h_kv = config.num_key_value_heads
+        self.topk = config.hils_topk
+        self.chunk_size = config.chunk_size
+        self.hils_sliding_window = config.hils_sliding_window
+        self.enable_prior_query = config.enable_prior_query
+        self.enable_chunk_pooling = config.enable_chunk_pooling
+        self.enable_softmax1 = config.enable_softmax1
+        self.topk_func = ops.online_softmax_topk_head
+        self.hils_func = ops.HiLS_block_M_head
+
+    # -- chunk keys: models/FlashHiLS/hils_attention.py:342-464 ---------------------------------
+    def _compute_landmark_keys(self, k_src, lmk_q, L, full_seq_len, use_cache, past_key_values):
+        S = self.chunk_size
+        B = k_src.shape[0]
+        prior_b = None
+        full_chunks = full_seq_len // S
+
+        def chunked(lo_chunk, hi_chunk):
+            return k_src[:, lo_chunk * S:hi_chunk * S].unflatten(1, (hi_chunk - lo_chunk, S))
+
+        if not self.enable_prior_query:
+            if self.enable_chunk_pooling:
+                return ops.chunk_mean_pool(chunked(0, full_chunks)), None
+            return k_src[:, S - 1::S], None
+
+        is_continuation = use_cache and past_key_values is not None and L < full_seq_len
+        if is_continuation:
+            store = past_key_values._hils_prior_cache
+            cached = store.get(self.layer_idx)
+            prev_len = full_seq_len - L
+            prev_full = prev_len // S
+            new_chunks = full_chunks - prev_full
+            if new_chunks > 0:
+                boundary_local = [S * (prev_full + j) - 1 - prev_len for j in range(1, new_chunks + 1)]
+                new_mu = lmk_q[:, boundary_local]
+                new_k = chunked(prev_full, full_chunks)
+                new_lmk_k, new_b = ops.chunk_attn_pool(new_mu, new_k)
+                if self.enable_chunk_pooling:
+                    new_lmk_k = ops.chunk_mean_pool(new_k)
+                if cached is not None:
+                    lmk_k = torch.cat([cached["lmk_k"], new_lmk_k], dim=1)
+                    prior_b = torch.cat([cached["prior_b"], new_b], dim=1)
+                else:
+                    lmk_k, prior_b = new_lmk_k, new_b
+                store[self.layer_idx] = {"lmk_k": lmk_k, "prior_b": prior_b}
+            elif cached is not None:
+                lmk_k, prior_b = cached["lmk_k"], cached["prior_b"]
+            else:
+                lmk_k, prior_b = k_src[:, S - 1::S], None
+            return lmk_k, prior_b
+
+        mu_q = lmk_q[:, S - 1::S][:, :full_chunks]
+        if mu_q.shape[1] == 0:
+            if self.enable_chunk_pooling and full_chunks > 0:
+                return ops.chunk_mean_pool(chunked(0, full_chunks)), None
+            return k_src[:, S - 1::S], None
+        kc = chunked(0, full_chunks)
+        pooled, prior_b = ops.chunk_attn_pool(mu_q, kc)     # kv heads are shared inside the kernel
+        lmk_k = ops.chunk_mean_pool(kc) if self.enable_chunk_pooling else pooled
+        if use_cache and past_key_values is not None and prior_b is not None:
+            past_key_values._hils_prior_cache[self.layer_idx] = {"lmk_k": lmk_k, "prior_b": prior_b}
+        return lmk_k, prior_b
+
+    def forward(self, q, k, v, lmk_q, past_key_values=None, use_cache: bool = False,
+                return_aux: bool = False):
+        """q, lmk_q (B,L,h_q,D); k, v (B,L,h_kv,D) of the NEW tokens.  Returns (B,L,h_q,Dv), the
+        tensor the reference flattens and feeds to o_proj."""
+        B, L = q.shape[0], q.shape[1]
+        S, W = self.chunk_size, self.hils_sliding_window
+        caching = use_cache and past_key_values is not None
+        if caching:
+            k, v = past_key_values.update(k, v, self.layer_idx + self.config.num_hidden_layers, None)
+        swa_o, lse_sum = ops.flex_attn_tl(q, k, v, window_size=W, chunk_size=S,
+                                          training=(past_key_values is None), mask_lmk=True,
+                                          expand_to_chunk=True)
+        lse_sum = lse_sum.contiguous().to(q.dtype)
+        full_seq_len = k.shape[1]
+        aux = {"swa_o": swa_o, "lse_swa": lse_sum}
+        if full_seq_len >= S:
+            lmk_k, prior_b = self._compute_landmark_keys(k, lmk_q, L, full_seq_len, use_cache, past_key_values)
+            q_offset = full_seq_len - L if caching else 0
+            indices, scores = self.topk_func(
+                lmk_q, lmk_k, lse_sum, self.topk, block_size=S, window_size=W, is_training=self.training,
+                is_causal=True, q_offset=q_offset, G=lmk_k.shape[2] // self.h_kv, bias=prior_b)
+            if self.enable_prior_query and prior_b is not None:
+                K = indices.shape[-1]
+                g_kernel = prior_b.shape[2] // indices.shape[2]
+                idx_hq = indices.repeat_interleave(g_kernel, dim=2) if g_kernel != 1 else indices
+                src = prior_b.unsqueeze(-1).expand(-1, -1, -1, K)
+                gathered = torch.gather(src, dim=1, index=idx_hq.clamp_min(0).long())
+                scores = scores + gathered.to(scores.dtype)
+            if not self.enable_softmax1:
+                cat_scores = torch.cat([scores, lse_sum.unsqueeze(-1)], dim=-1)
+                swa_idx = -1
+            else:
+                cat_scores = torch.cat([scores, lse_sum.unsqueeze(-1),
+                                        torch.zeros(B, L, scores.shape[2], 1, device=q.device, dtype=scores.dtype)],
+                                       dim=-1)
+                swa_idx = -2
+            chunk_weights = F.softmax(cat_scores, dim=-1).to(q.dtype)
+            hils_o = self.hils_func(q, k, v, weights=chunk_weights, indices=indices, block_size=S,
+                                    mask_last_token=True, is_training=self.training)
+            o_lower = torch.addcmul(hils_o, swa_o, chunk_weights[:, :, :, swa_idx].unsqueeze(-1))
+            aux.update(indices=indices, scores=scores, weights=chunk_weights, lmk_k=lmk_k, prior_b=prior_b,
+                       hils_o=hils_o)
+        elif self.enable_softmax1:
+            o_lower = swa_o * torch.sigmoid(lse_sum).to(swa_o.dtype).unsqueeze(-1)
+        else:
+            o_lower = swa_o
+        return (o_lower, aux) if return_aux else o_lower
+
+
+def install_into_reference() -> None:
+    """Register this package's ops under the module paths the reference imports from, so that
+    ``from ops.hils_fwd_bwd_head import HiLS_block_M_head`` (models/FlashHiLS/hils_attention.py:9-10,
+    :264-265; models/NaiveBSA/naive_bsa_kernel.py:169-171) resolves here.  Call before importing the
+    reference's model code."""
+    table = {
+        "ops.hils_fwd_bwd_head": {"HiLS_block_M_head": ops.HiLS_block_M_head},
+        "ops.topk_head_softmax": {"online_softmax_topk_head": ops.online_softmax_topk_head},
+        "ops.chunk_attn_pool_tilelang": {"chunk_attn_pool_tilelang": ops.chunk_attn_pool_tilelang},
+        "ops.exact_chunk_log_z_tilelang": {"exact_chunk_log_z_tl": ops.exact_chunk_log_z_tl},
+        "ops.flex_attn_tilelang": {"flex_attn_tl": ops.flex_attn_tl,
+                                   "flex_attn_tl_two_phase": ops.flex_attn_tl_two_phase},
+    }
+    pkg = sys.modules.get("ops")
+    if pkg is None:
+        pkg = types.ModuleType("ops")
+        pkg.__path__ = []  # mark as package
+        sys.modules["ops"] = pkg
+    for name, attrs in table.items():
+        mod = types.ModuleType(name)
+        for k, fn in attrs.items():
+            setattr(mod, k, fn)
+        sys.modules[name] = mod
+        setattr(pkg, name.split(".", 1)[1], mod)

@@ -64,9 +64,9 @@ def main(ref_root):
     # ---- selection ---------------------------------------------------------------------
     cases = {
         # tag: B, L, N, h_kv, G, D, K, S, W, q_offset, bias, per_qhead, gumbel
-        "shared": (1, 640, 10, 2, 2, 64, 4, 64, 64, 0, False, False, False),
+        "shared": (1, 640, 10, 2, 2, 64, 4, 64, 64, 0, False, False, True),
         "bias_pq": (2, 512, 8, 1, 4, 32, 4, 64, 128, 0, True, True, False),
-        "decode": (1, 3, 16, 2, 1, 64, 8, 64, 64, 1021, True, False, True),
+        "decode": (1, 3, 16, 2, 1, 64, 8, 64, 64, 1021, True, False, False),
         "ragged": (1, 333, 5, 1, 2, 64, 8, 64, 64, 0, False, False, False),
     }
     for tag, (B, L, N, hk, G, D, K, S, W, qo, use_b, pq, gum) in cases.items():

@@ -1,0 +1,136 @@
+"""The whole attention chain (module level) against the oracle chain, prefill-vs-decode
+consistency through the KV store, and properties at the benchmark's full size.  Needs a B200."""
+import math
+
+import pytest
+import torch
+
+from oracle import hils_oracle as orc
+from tests.util import check
+
+pytestmark = pytest.mark.gpu
+BF, F32 = torch.bfloat16, torch.float32
+
+
+def _inputs(B, T, hq, hk, D, S, seed, dtype, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, T, hq, D, generator=g) * scale
+    k = torch.randn(B, T, hk, D, generator=g) * scale
+    off = torch.randn(B, T // S, 1, hk, D, generator=g) * 0.5 * scale
+    k[:, :(T // S) * S] += off.expand(-1, -1, S, -1, -1).reshape(B, (T // S) * S, hk, D)
+    v = torch.randn(B, T, hk, D, generator=g) * scale
+    return [t.to(dtype) for t in (q, k, v)]
+
+
+def _core(hq, hk, K, S, W, **kw):
+    from hils_attention_b200.attention import HiLSAttentionConfig, HiLSAttentionCore
+    return HiLSAttentionCore(HiLSAttentionConfig(hq, hk, K, S, W, **kw))
+
+
+@pytest.mark.parametrize("cfg", [
+    # B, T, hq, hk, D, S, K, W, dtype, pooling kw
+    (1, 2048, 4, 4, 64, 64, 8, 512, F32, dict(enable_prior_query=False, enable_chunk_pooling=True)),  # config 1, fewer heads
+    (2, 1024, 4, 4, 64, 64, 8, 256, BF, dict()),
+    (1, 1024, 8, 2, 64, 64, 4, 128, BF, dict()),                                                       # GQA, per-q-head keys
+    (1, 1024, 4, 2, 32, 32, 4, 64, BF, dict(enable_chunk_pooling=True, enable_softmax1=True)),
+])
+def test_chain_matches_oracle(cfg):
+    B, T, hq, hk, D, S, K, W, dtype, kw = cfg
+    q, k, v = _inputs(B, T, hq, hk, D, S, 21, dtype, scale=(1 / math.sqrt(D) if dtype == F32 else 1.0))
+    core = _core(hq, hk, K, S, W, **kw).train()
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o, aux = core(qd, kd, vd, qd, return_aux=True)
+    pooling = "mean" if kw.get("enable_chunk_pooling") else "attn"
+    ref, raux = orc.hils_attention_chain(q, k, v, q, chunk_size=S, window_size=W, topk=K, pooling=pooling,
+                                         use_prior_bias=kw.get("enable_prior_query", True),
+                                         softmax1=kw.get("enable_softmax1", False), return_aux=True)
+    same = (aux["indices"].cpu() == raux["indices"]).all(-1)                 # (B,T,hk)
+    assert same.float().mean().item() >= 0.99
+    rows = same.repeat_interleave(hq // hk, dim=2)
+    check(o[rows.cuda()], ref.float()[rows], dtype, "chain output", scale=2.0)
+    check(aux["lse_swa"], raux["lse_swa"], dtype, "lse_swa")
+    do = torch.randn(o.shape, generator=torch.Generator().manual_seed(5)).to(dtype)
+    o.backward(do.cuda())
+    for t in (qd, kd, vd):
+        assert t.grad is not None and torch.isfinite(t.grad.float()).all()
+
+
+def test_chain_gradients_match_oracle_fp32():
+    """fp32, selection frozen to the kernel's ids: gradients of the chain wrt q, k, v against
+    autograd through the oracle with the same ids."""
+    B, T, H, D, S, K, W = 1, 512, 2, 32, 32, 4, 64
+    q, k, v = _inputs(B, T, H, H, D, S, 33, F32, scale=0.5)
+    core = _core(H, H, K, S, W).train()
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o, aux = core(qd, kd, vd, qd, return_aux=True)
+    do = torch.randn(o.shape, generator=torch.Generator().manual_seed(6))
+    o.backward(do.cuda())
+    idx = aux["indices"].cpu()
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+    swa_o, lse = orc.swa(qr, kr, vr, W, S)
+    N = T // S
+    lmk_k, pb = orc.chunk_attn_pool(qr[:, S - 1::S][:, :N], kr[:, :N * S].reshape(B, N, S, H, D))
+    sel = lmk_k[torch.arange(B).view(B, 1, 1, 1), idx.clamp_min(0).long(), torch.arange(H).view(1, 1, H, 1)]
+    sc = torch.einsum("blhd,blhkd->blhk", qr, sel) / math.sqrt(D)
+    sc = sc.masked_fill(idx < 0, float("-inf"))
+    w = orc.inter_chunk_weights(sc, idx, lse, pb)
+    oh = orc.sparse_attn(qr, kr, vr, w, idx, chunk_size=S)
+    ref = oh + swa_o * w[..., -1:]
+    check(o, ref, F32, "o", scale=5.0)
+    ref.backward(do)
+    for n, a, b in (("dq", qd, qr), ("dk", kd, kr), ("dv", vd, vr)):
+        check(a.grad, b.grad, F32, n, scale=50.0)
+
+
+def test_prefill_then_decode_matches_full_forward():
+    """Feeding the sequence through the KV store (prefill 700 tokens, one 100-token chunk-prefill,
+    then single-token decode steps) reproduces the one-shot forward: same ids, same outputs."""
+    from hils_attention_b200.cache import HiLSCache
+    B, T, hq, hk, D, S, K, W = 1, 832, 4, 2, 64, 64, 4, 128
+    q, k, v = _inputs(B, T, hq, hk, D, S, 44, BF)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    core = _core(hq, hk, K, S, W).eval()
+    with torch.no_grad():
+        full, faux = core(qd, kd, vd, qd, return_aux=True)
+        cache = HiLSCache()
+        outs, ids = [], []
+        for lo, hi in [(0, 700), (700, 800)] + [(t, t + 1) for t in range(800, T)]:
+            o, aux = core(qd[:, lo:hi], kd[:, lo:hi], vd[:, lo:hi], qd[:, lo:hi], past_key_values=cache,
+                          use_cache=True, return_aux=True)
+            outs.append(o)
+            ids.append(aux["indices"])
+    got, gid = torch.cat(outs, 1), torch.cat(ids, 1)
+    same = (gid == faux["indices"]).all(-1)
+    assert same.float().mean().item() >= 0.99
+    rows = same.repeat_interleave(hq // hk, dim=2)
+    check(got[rows], full[rows], BF, "decode vs full")
+    assert cache.get_seq_length(1) == T
+
+
+@pytest.mark.parametrize("B", [1])
+def test_full_size_properties(B):
+    """Benchmark-sized sequence (T=8192, 16 heads, D=64, K=32): size-independent properties.
+    ids ascending, in the causal remote range, -1 only as trailing padding with the right count;
+    the sparse attention is linear in v and in the weights; weights sum to one."""
+    import hils_attention_b200 as hb
+    T, H, D, S, K, W = 8192, 16, 64, 64, 32, 512
+    q, k, v = _inputs(B, T, H, H, D, S, 2, BF)
+    core = _core(H, H, K, S, W).eval()
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    with torch.no_grad():
+        o, aux = core(qd, kd, vd, qd, return_aux=True)
+        idx, w = aux["indices"], aux["weights"].contiguous()
+        t = torch.arange(T, device="cuda")
+        lim = ((t - W + 1).div(S, rounding_mode="floor")).clamp(0, T // S).view(1, T, 1, 1)
+        assert bool(((idx < lim) & (idx >= -1)).all())
+        nvalid = (idx >= 0).sum(-1)
+        assert torch.equal(nvalid, torch.minimum(lim.squeeze(-1).expand_as(nvalid), torch.full_like(nvalid, K)))
+        srt = idx.masked_fill(idx < 0, 1 << 30)
+        assert bool((srt[..., 1:] > srt[..., :-1]).logical_or(srt[..., 1:] == (1 << 30)).all())
+        assert bool((w.float().sum(-1) - 1).abs().max() < 2e-2)
+        o1 = hb.HiLS_block_M_head(qd, kd, vd, w, idx, block_size=S, is_training=False)
+        o2 = hb.HiLS_block_M_head(qd, kd, (2 * vd.float()).to(BF), w, idx, block_size=S, is_training=False)
+        check(o2, 2 * o1.float(), BF, "linearity in v")
+        o3 = hb.HiLS_block_M_head(qd, kd, vd, (0.5 * w.float()).to(BF), idx, block_size=S, is_training=False)
+        check(o3, 0.5 * o1.float(), BF, "linearity in weights")
+        assert torch.isfinite(o.float()).all()
