@@ -22,6 +22,7 @@ _P, _I, _F, _I64, _SZ = C.c_void_p, C.c_int, C.c_float, C.c_int64, C.c_size_t
 SIGNATURES = {
     "hils_version": (_I, []),
     "hils_last_error": (C.c_char_p, []),
+    "hils_take_device_status": (_I, []),
     "hils_pool_fwd": (_I, [_P] * 4 + [_I] * 6 + [_I64, _F, _I, _I, _P]),
     "hils_pool_bwd": (_I, [_P] * 6 + [_I] * 6 + [_I64, _F, _I, _I, _P]),
     "hils_meanpool_fwd": (_I, [_P, _P] + [_I] * 5 + [_I64, _I, _P]),

@@ -3,6 +3,8 @@
 
 namespace hils {
 
+int sparse_fwd_tc_launch(const SparseParams& p, cudaStream_t st);  // sparse_attn_tc.cu
+
 static int check_sparse(int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights,
                         int chunk_size, int dtype) {
   HILS_REQUIRE(B > 0 && L >= 0 && T >= 0 && h_q > 0 && h_kv > 0 && D > 0 && Dv > 0, "sparse_attn: bad size");
@@ -55,10 +57,14 @@ extern "C" int hils_sparse_attn_fwd(const void* q, const void* k, const void* v,
   SparseParams p = make_params(q, k, v, weights, indices, slope, B, L, T, h_q, h_kv, D, Dv, K, num_weights,
                                chunk_size, sm_scale, mask_last_token);
   p.o = o;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == HILS_BF16) {  // tensor-core path for the shapes it covers
+    const int rc = sparse_fwd_tc_launch(p, st);
+    if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  }
   const int64_t rows = (int64_t)B * L * h_q;
   const size_t smem = 4 * (size_t)(D + chunk_size) * sizeof(float);
   HILS_REQUIRE(smem <= 200 * 1024, "sparse_attn_fwd: chunk_size %d too large", chunk_size);
-  cudaStream_t st = (cudaStream_t)stream;
   const unsigned blocks = (unsigned)((rows + 3) / 4);
   if (dtype == HILS_BF16) {
     cudaFuncSetAttribute(sparse_fwd_generic_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -40,6 +40,12 @@ extern "C" {
 int hils_version(void);
 const char* hils_last_error(void);
 
+/* Device-side error word: kernels whose bounded waits (mbarrier polls of the tensor-core paths)
+ * expire record a non-zero code here and return instead of spinning.  This call synchronises the
+ * device, returns the word (0 = no error, -1 = the synchronisation itself failed) and clears it.
+ * The reference has no counterpart (its kernels have no device-side waits). */
+int hils_take_device_status(void);
+
 /* ---------------------------------------------------------------------------------------
  * Chunk pooling.  Replaces ChunkAttnPoolFunction.forward/backward and the kernels behind it
  * (ops/chunk_attn_pool_tilelang.py:540-602, kernels :329-533) and the GQA-aware contract of

@@ -1,0 +1,72 @@
+"""Tensor-core (tcgen05) sparse chunk attention against the CPU oracle: bf16, chunk 64, head dims
+64 and 128, MHA and GQA, ragged lengths, unsorted and duplicated ids, kv longer than q."""
+import pytest
+import torch
+
+from oracle import hils_oracle as orc
+from tests.util import check
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _case(B, L, T, H, G, D, K, seed, sort=True, dup=False):
+    g = torch.Generator().manual_seed(seed)
+    S = 64
+    N = T // S
+    q = torch.randn(B, L, H * G, D, generator=g).to(BF)
+    k = torch.randn(B, T, H, D, generator=g).to(BF)
+    v = torch.randn(B, T, H, D, generator=g).to(BF)
+    idx = torch.full((B, L, H, K), -1, dtype=torch.int32)
+    for b in range(B):
+        for t in range(L):
+            lim = min((t + (T - L)) // S + 1, N)
+            for h in range(H):
+                n = min(K, lim, int(torch.randint(0, K + 1, (1,), generator=g)))
+                sel = torch.randperm(lim, generator=g)[:n]
+                if sort:
+                    sel = sel.sort()[0]
+                idx[b, t, h, :n] = sel.to(torch.int32)
+                if dup and n >= 2:
+                    idx[b, t, h, 1] = idx[b, t, h, 0]
+    w = torch.rand(B, L, H * G, K + 1, generator=g).to(BF)
+    return q, k, v, w, idx
+
+
+@pytest.mark.parametrize("cfg", [
+    # B, L, T, H, G, D, K, sort, dup
+    (1, 512, 512, 2, 1, 64, 8, True, False),
+    (2, 300, 300, 1, 2, 64, 4, True, False),       # ragged block, GQA
+    (1, 256, 640, 2, 8, 64, 4, True, False),       # kv longer than q, G=8
+    (1, 384, 384, 1, 1, 128, 8, True, False),      # head dim 128
+    (1, 200, 512, 2, 4, 128, 4, True, True),       # duplicates add their weights
+    (1, 256, 256, 1, 2, 64, 4, False, False),      # unsorted lists (naive block-sparse path)
+    (1, 1024, 1024, 1, 1, 64, 32, True, False),    # K=32 as in the benchmark
+])
+def test_tc_forward_matches_oracle(cfg):
+    import hils_attention_b200 as hb
+    from hils_attention_b200 import _lib
+    B, L, T, H, G, D, K, sort, dup = cfg
+    q, k, v, w, idx = _case(B, L, T, H, G, D, K, 77, sort, dup)
+    ref = orc.sparse_attn(q, k, v, w, idx, chunk_size=64, mask_last_token=True)
+    o = hb.HiLS_block_M_head(q.cuda(), k.cuda(), v.cuda(), w.cuda(), idx.cuda(), block_size=64, is_training=False)
+    assert _lib.load().hils_take_device_status() == 0
+    check(o, ref, BF, "tc forward", scale=2.0)
+
+
+def test_tc_forward_slope_and_no_last_mask():
+    import hils_attention_b200 as hb
+    q, k, v, w, idx = _case(1, 256, 256, 1, 2, 64, 4, 5)
+    slope = torch.tensor([0.02, 0.1])
+    ref = orc.sparse_attn(q, k, v, w, idx, chunk_size=64, mask_last_token=False, slope=slope)
+    o = hb.HiLS_block_M_head(q.cuda(), k.cuda(), v.cuda(), w.cuda(), idx.cuda(), block_size=64,
+                             mask_last_token=False, is_training=False, slope=slope.cuda())
+    check(o, ref, BF, "tc forward slope", scale=2.0)
+
+
+def test_tc_forward_is_deterministic():
+    import hils_attention_b200 as hb
+    q, k, v, w, idx = [t.cuda() for t in _case(1, 512, 512, 2, 1, 64, 8, 9)]
+    o1 = hb.HiLS_block_M_head(q, k, v, w, idx, block_size=64, is_training=False)
+    o2 = hb.HiLS_block_M_head(q, k, v, w, idx, block_size=64, is_training=False)
+    assert torch.equal(o1, o2)
