@@ -4,6 +4,8 @@
 namespace hils {
 
 int sparse_fwd_tc_launch(const SparseParams& p, cudaStream_t st);  // sparse_attn_tc.cu
+size_t sparse_bwd_tc_workspace(const SparseParams& p);
+int sparse_bwd_tc_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st);
 
 static int check_sparse(int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights,
                         int chunk_size, int dtype) {
@@ -23,6 +25,7 @@ static SparseParams make_params(const void* q, const void* k, const void* v, con
   SparseParams p;
   p.q = q; p.k = k; p.v = v; p.w = w; p.idx = idx; p.slope = slope;
   p.o = nullptr; p.d_o = nullptr; p.d_q = nullptr; p.d_w = nullptr; p.dk_acc = nullptr; p.dv_acc = nullptr;
+  p.d_k_out = nullptr; p.d_v_out = nullptr;
   p.B = B; p.L = L; p.T = T; p.h_q = h_q; p.h_kv = h_kv; p.D = D; p.Dv = Dv; p.K = K;
   p.num_weights = num_weights; p.S = S; p.mask_last = mask_last; p.scale = scale;
   return p;
@@ -40,7 +43,12 @@ extern "C" size_t hils_sparse_attn_fwd_workspace_bytes(int B, int L, int T, int 
 
 extern "C" size_t hils_sparse_attn_bwd_workspace_bytes(int B, int L, int T, int h_q, int h_kv, int D, int Dv,
                                                        int K, int chunk_size, int dtype) {
-  (void)L; (void)h_q; (void)K; (void)chunk_size; (void)dtype;
+  if (dtype == HILS_BF16 && h_q > 0 && h_kv > 0 && h_q % h_kv == 0) {
+    SparseParams p = make_params(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, B, L, T, h_q, h_kv, D, Dv, K, K,
+                                 chunk_size, 1.f, 1);
+    const size_t tc = sparse_bwd_tc_workspace(p);
+    if (tc > 0) return tc;
+  }
   return (size_t)B * T * h_kv * (size_t)(D + Dv) * sizeof(float);
 }
 
@@ -90,6 +98,22 @@ extern "C" int hils_sparse_attn_bwd(const void* q, const void* k, const void* v,
     return HILS_ERR_WORKSPACE;
   }
   cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == HILS_BF16 && L > 0) {  // tensor-core path for the shapes it covers
+    SparseParams p = make_params(q, k, v, weights, indices, slope, B, L, T, h_q, h_kv, D, Dv, K, num_weights,
+                                 chunk_size, sm_scale, mask_last_token);
+    if (sparse_bwd_tc_workspace(p) > 0) {
+      HILS_REQUIRE(q && k && v && weights && indices && d_o && d_q && d_k && d_v && d_w, "sparse_attn_bwd: null pointer");
+      p.d_o = d_o; p.d_q = d_q; p.d_w = d_w;
+      const int rc = sparse_bwd_tc_launch(p, d_k, d_v, workspace, st);
+      if (rc != HILS_ERR_UNSUPPORTED) return rc;
+      // misaligned pointers: the fp32-accumulator path below needs its larger workspace
+      const size_t need2 = (size_t)B * T * h_kv * (size_t)(D + Dv) * sizeof(float);
+      if (workspace_bytes < need2) {
+        set_error("sparse_attn_bwd: tensors must be 16-byte aligned for this shape");
+        return HILS_ERR_BAD_ARG;
+      }
+    }
+  }
   const int64_t nk = (int64_t)B * T * h_kv * D, nv = (int64_t)B * T * h_kv * Dv;
   float* dk_acc = static_cast<float*>(workspace);
   float* dv_acc = dk_acc + nk;

@@ -14,7 +14,7 @@ namespace hils {
 
 struct SparseParams {
   const void* q; const void* k; const void* v; const void* w; const int32_t* idx; const float* slope;
-  void* o; const void* d_o; void* d_q; void* d_w; float* dk_acc; float* dv_acc;
+  void* o; const void* d_o; void* d_q; void* d_w; float* dk_acc; float* dv_acc; void* d_k_out; void* d_v_out;
   int B, L, T, h_q, h_kv, D, Dv, K, num_weights, S, mask_last;
   float scale;
 };

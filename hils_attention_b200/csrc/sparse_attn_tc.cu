@@ -27,8 +27,20 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// The tensor-map encoder is a driver-API call and needs a context current on the calling host
+// thread; a thread that has made no runtime call yet (e.g. an autograd worker) has none until the
+// runtime binds the primary context, which this does once per thread.
+static void bind_context_once() {
+  static thread_local bool done = false;
+  if (!done) {
+    cudaFree(nullptr);
+    done = true;
+  }
+}
+
 int make_tmap_bf16_rows(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
                         uint32_t box_rows) {
+  bind_context_once();
   static EncodeTiledFn enc = nullptr;
   if (!enc) {
     cudaDriverEntryPointQueryResult q;
@@ -46,6 +58,31 @@ int make_tmap_bf16_rows(CUtensorMap* map, const void* base, uint64_t rows, uint6
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed with %d", (int)r);
+    return HILS_ERR_CUDA;
+  }
+  return HILS_OK;
+}
+
+int make_tmap_bf16_thd(CUtensorMap* map, const void* base, uint64_t tokens, uint64_t heads, uint64_t D,
+                       uint32_t box_heads, uint32_t box_tokens) {
+  bind_context_once();
+  static EncodeTiledFn enc = nullptr;
+  if (!enc) {
+    cudaDriverEntryPointQueryResult q;
+    void* fn = nullptr;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || !fn) return cuda_fail(e, "cuTensorMapEncodeTiled lookup");
+    enc = (EncodeTiledFn)fn;
+  }
+  cuuint64_t dims[3] = {D, heads, tokens};
+  cuuint64_t strides[2] = {D * 2, heads * D * 2};
+  cuuint32_t box[3] = {64, box_heads, box_tokens};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (3-D) failed with %d", (int)r);
     return HILS_ERR_CUDA;
   }
   return HILS_OK;
@@ -327,6 +364,649 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
   tc_fence_before();
   __syncthreads();
   if (warp == 4) tmem_dealloc(tmem, 256);
+}
+
+
+// =================================================================================================
+// Backward, two atomic-free passes over the same (128-row query block, chunk) pairs as the forward:
+//   pass "dq"  (query-major, one CTA per query block): dQ accumulates in TMEM over the block's union
+//              list; dW is written per (row, slot).  It also stores the block's union bitmap and its
+//              "all lists ascending" flag in the workspace for the second pass.
+//   pass "dkv" (chunk-major, one CTA per chunk): walks the query blocks whose bitmap holds the chunk;
+//              dK and dV of the chunk accumulate in TMEM (M = 64 accumulators) and are written once.
+// Per pair both passes recompute S = Q K^T and dP = dO V^T on the tensor cores; one thread per row
+// forms P, dw = sum_j P_j dP_j, dS = scale w P (dP - dw) (ops/hils_fwd_bwd_head.py:651-757).
+// =================================================================================================
+
+// S row in sv, dP row in dp  ->  dS row in sv, w*P row in dp; returns dw
+__device__ __forceinline__ float bwd_row(float* sv, float* dp, float wsum, float scale, float scale_log2, float slope,
+                                         int mask_last) {
+  if (slope != 0.f) {
+#pragma unroll
+    for (int j = 0; j < 62; ++j) sv[j] -= slope * (float)(62 - j);
+  }
+  if (mask_last) sv[63] = -CUDART_INF_F;
+  float m = sv[0];
+#pragma unroll
+  for (int j = 1; j < 64; ++j) m = fmaxf(m, sv[j]);
+  const float mb = m * scale_log2;
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 64; ++j) {
+    sv[j] = ex2(fmaf(sv[j], scale_log2, -mb));
+    sum += sv[j];
+  }
+  const float inv = 1.f / sum;
+  float dw = 0.f;
+#pragma unroll
+  for (int j = 0; j < 64; ++j) {
+    sv[j] *= inv;
+    dw = fmaf(sv[j], dp[j], dw);
+  }
+  const float sw = scale * wsum;
+#pragma unroll
+  for (int j = 0; j < 64; ++j) {
+    const float pj = sv[j];
+    sv[j] = sw * pj * (dp[j] - dw);
+    dp[j] = wsum * pj;
+  }
+  return dw;
+}
+
+__device__ __forceinline__ void store_row_bf16_sw128(uint8_t* tile, int r, const float* v) {
+#pragma unroll
+  for (int c8 = 0; c8 < 8; ++c8) {
+    __nv_bfloat162 hh[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) hh[e] = __floats2bfloat162_rn(v[c8 * 8 + 2 * e], v[c8 * 8 + 2 * e + 1]);
+    *reinterpret_cast<uint4*>(tile + sw128_off(r, c8)) = *reinterpret_cast<uint4*>(hh);
+  }
+}
+__device__ __forceinline__ void store_row_zero_sw128(uint8_t* tile, int r) {
+#pragma unroll
+  for (int c8 = 0; c8 < 8; ++c8) *reinterpret_cast<uint4*>(tile + sw128_off(r, c8)) = make_uint4(0u, 0u, 0u, 0u);
+}
+
+struct BwdWs {
+  uint32_t* bitmap;  // [B*h_kv][nblk][nwords]
+  int* flags;        // [B*h_kv][nblk]  1 = some row of the block has a non-ascending id list
+};
+
+template <int D>
+__global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseParams p, BwdWs ws,
+                                                                          const __grid_constant__ CUtensorMap tmK,
+                                                                          const __grid_constant__ CUtensorMap tmV) {
+  constexpr int DB = D / 64;
+  constexpr int QBYTES = DB * 16384;
+  constexpr int KVBYTES = DB * 8192;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* Qs = smem;
+  uint8_t* dOs = Qs + QBYTES;
+  uint8_t* Ks = dOs + QBYTES;            // 2 stages
+  uint8_t* Vs = Ks + 2 * KVBYTES;        // 2 stages
+  uint8_t* dSs = Vs + 2 * KVBYTES;       // 2 x [128 x 64] bf16
+  int* union_s = reinterpret_cast<int*>(dSs + 2 * 16384);
+  const int nchunk = p.T / 64;
+  const int nwords = (nchunk + 31) >> 5;
+  const int G = p.h_q / p.h_kv, QB = 128 / G;
+  const int umax = min(nchunk, QB * p.K);
+  uint32_t* bitmap_s = reinterpret_cast<uint32_t*>(union_s + umax);
+
+  __shared__ uint64_t kv_full[2], sdp_full[2], ds_full[2], dq_done[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int n_union_s, warp_tot_s[4];
+  __shared__ volatile int abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nblk = gridDim.x;
+  const int blk = nblk - 1 - blockIdx.x;
+  const int q0 = blk * QB, h = blockIdx.y, b = blockIdx.z;
+
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&sdp_full[s], 1);
+      mbar_init(&ds_full[s], 128);
+      mbar_init(&dq_done[s], 1);
+    }
+    mbar_init_fence();
+    abort_s = 0;
+  }
+  if (warp == 4) tmem_alloc(&tmem_base_s, 512);
+  for (int w = tid; w < nwords; w += kTcThreads) bitmap_s[w] = 0u;
+  __syncthreads();
+
+  const int r = tid;
+  const int ql = r / G, g = r % G, t = q0 + ql;
+  const bool is_row = tid < 128;
+  const bool valid = is_row && t < p.L;
+  const int hq = h * G + g;
+  const int64_t rowi = ((int64_t)b * p.L + (valid ? t : 0)) * p.h_q + hq;
+  const int32_t* ids = p.idx + (((int64_t)b * p.L + (valid ? t : 0)) * p.h_kv + h) * p.K;
+  const bf16* wrow = static_cast<const bf16*>(p.w) + rowi * p.num_weights;
+  bf16* dwrow = static_cast<bf16*>(p.d_w) + rowi * p.num_weights;
+  int nvalid = 0, my_unsorted = 0;
+  if (is_row) {
+    const bf16* qrow = static_cast<const bf16*>(p.q) + rowi * D;
+    const bf16* dorow = static_cast<const bf16*>(p.d_o) + rowi * D;
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+      uint4 x = make_uint4(0u, 0u, 0u, 0u), y = make_uint4(0u, 0u, 0u, 0u);
+      if (valid) {
+        x = *reinterpret_cast<const uint4*>(qrow + c * 8);
+        y = *reinterpret_cast<const uint4*>(dorow + c * 8);
+      }
+      *reinterpret_cast<uint4*>(Qs + (c >> 3) * 16384 + sw128_off(r, c & 7)) = x;
+      *reinterpret_cast<uint4*>(dOs + (c >> 3) * 16384 + sw128_off(r, c & 7)) = y;
+    }
+    if (valid) {
+      for (int k = 0; k < p.num_weights; ++k) dwrow[k] = __float2bfloat16_rn(0.f);
+      int prev = -1;
+      for (int k = 0; k < p.K; ++k) {
+        const int id = __ldg(ids + k);
+        if (id < 0) break;
+        ++nvalid;
+        if (id < prev) my_unsorted = 1;
+        prev = id;
+        if (g == 0 && id < nchunk) atomicOr(&bitmap_s[id >> 5], 1u << (id & 31));
+      }
+    }
+  }
+  const int unsorted = __syncthreads_or(my_unsorted);
+  {
+    const int64_t bh = (int64_t)b * p.h_kv + h;
+    for (int w = tid; w < nwords; w += kTcThreads) ws.bitmap[(bh * nblk + blk) * nwords + w] = bitmap_s[w];
+    if (tid == 0) ws.flags[bh * nblk + blk] = unsorted;
+    const int wpt = (nwords + 127) / 128;
+    int cnt = 0;
+    if (is_row)
+      for (int w = tid * wpt; w < min(nwords, (tid + 1) * wpt); ++w) cnt += __popc(bitmap_s[w]);
+    int inc = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int nn = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += nn;
+    }
+    if (is_row && lane == 31) warp_tot_s[warp] = inc;
+    __syncthreads();
+    if (is_row) {
+      int base = inc - cnt;
+      for (int w = 0; w < warp; ++w) base += warp_tot_s[w];
+      for (int w = tid * wpt; w < min(nwords, (tid + 1) * wpt); ++w) {
+        uint32_t bits = bitmap_s[w];
+        while (bits) {
+          const int bpos = __ffs(bits) - 1;
+          bits &= bits - 1;
+          if (base < umax) union_s[base] = w * 32 + bpos;
+          ++base;
+        }
+      }
+      if (tid == 127) n_union_s = min(base, umax);
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const int n = n_union_s;
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t tdQ = tmem + 256;
+
+  if (warp == 5) {
+    if (lane == 0) {
+      for (int i = 0; i < n; ++i) {
+        const int s = i & 1, u = i >> 1;
+        if (abort_s) break;
+        if (i >= 2 && !mbar_wait(&dq_done[s], (u - 1) & 1)) { abort_s = 1; atomicExch(&g_device_status, 201); break; }
+        const int c = union_s[i];
+        mbar_expect_tx(&kv_full[s], 2 * KVBYTES);
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+          tma_load_2d(Ks + s * KVBYTES + db * 8192, &tmK, &kv_full[s], h * D + db * 64, b * p.T + c * 64);
+          tma_load_2d(Vs + s * KVBYTES + db * 8192, &tmV, &kv_full[s], h * D + db * 64, b * p.T + c * 64);
+        }
+      }
+    }
+  } else if (warp == 4) {
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_s = idesc_bf16(128, 64, 0);
+      constexpr uint32_t idesc_dq = idesc_bf16(128, D, 1);
+      const uint32_t q_addr = smem_u32(Qs), do_addr = smem_u32(dOs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs),
+                     ds_addr = smem_u32(dSs);
+      auto issue_sdp = [&](int i) {
+        const int s = i & 1;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = s * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32;
+          mma_ss(tmem + s * 128, desc_sw128(q_addr + ao, 16, 1024), desc_sw128(k_addr + bo, 16, 1024), idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = s * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32;
+          mma_ss(tmem + s * 128 + 64, desc_sw128(do_addr + ao, 16, 1024), desc_sw128(v_addr + bo, 16, 1024), idesc_s, kk > 0);
+        }
+        mma_commit(&sdp_full[s]);
+      };
+      bool ok = mbar_wait(&kv_full[0], 0);
+      if (ok) { tc_fence_after(); issue_sdp(0); }
+      for (int i = 0; ok && i < n; ++i) {
+        const int s = i & 1, u = i >> 1;
+        if (abort_s) break;
+        if (i + 1 < n) {
+          ok = mbar_wait(&kv_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sdp(i + 1);
+        }
+        ok = mbar_wait(&ds_full[s], u & 1);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          mma_ss(tdQ, desc_sw128(ds_addr + s * 16384 + kk * 32, 16, 1024),
+                 desc_sw128(k_addr + s * KVBYTES + kk * 2048, 8192, 1024), idesc_dq, (i > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(&dq_done[s]);
+      }
+      if (!ok) { abort_s = 1; atomicExch(&g_device_status, 202); }
+    }
+  } else {
+    const float scale_log2 = p.scale * kLog2e;
+    const float slope = p.slope ? p.slope[hq] : 0.f;
+    int ptr = 0;
+    int cur = (nvalid > 0) ? __ldg(ids) : 0x7fffffff;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    bool ok = true;
+    for (int i = 0; i < n; ++i) {
+      const int s = i & 1, u = i >> 1;
+      const int c = union_s[i];
+      float wsum = 0.f;
+      bool owner = false;
+      int k_first = 0, k_last = 0;
+      if (!unsorted) {
+        k_first = ptr;
+        while (cur == c) {
+          owner = true;
+          wsum += to_f(wrow[ptr]);
+          ++ptr;
+          cur = (ptr < nvalid) ? __ldg(ids + ptr) : 0x7fffffff;
+        }
+        k_last = ptr;
+      } else {
+        for (int k = 0; k < nvalid; ++k)
+          if (__ldg(ids + k) == c) { owner = true; wsum += to_f(wrow[k]); }
+      }
+      ok = mbar_wait(&sdp_full[s], u & 1);
+      if (i >= 2) ok = mbar_wait(&dq_done[s], (u - 1) & 1) && ok;
+      ok = __all_sync(0xffffffffu, ok) && !abort_s;
+      if (!ok) break;
+      tc_fence_after();
+      float sv[64], dp[64];
+      tmem_ld32(tmem + lane_base + s * 128, sv);
+      tmem_ld32(tmem + lane_base + s * 128 + 32, sv + 32);
+      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);
+      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
+      tmem_ld_wait();
+      uint8_t* dsrow = dSs + s * 16384;
+      if (owner) {
+        const float dw = bwd_row(sv, dp, wsum, p.scale, scale_log2, slope, p.mask_last);
+        store_row_bf16_sw128(dsrow, r, sv);
+        const bf16 dwb = __float2bfloat16_rn(dw);
+        if (!unsorted) {
+          for (int k = k_first; k < k_last; ++k) dwrow[k] = dwb;
+        } else {
+          for (int k = 0; k < nvalid; ++k)
+            if (__ldg(ids + k) == c) dwrow[k] = dwb;
+        }
+      } else {
+        store_row_zero_sw128(dsrow, r);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&ds_full[s]);
+    }
+    if (ok && n > 0) {
+      ok = mbar_wait(&dq_done[(n - 1) & 1], ((n - 1) >> 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok && lane == 0) { abort_s = 1; atomicExch(&g_device_status, 203); }
+    } else if (!ok && lane == 0) {
+      abort_s = 1;
+      atomicExch(&g_device_status, 204);
+    }
+    bf16* orow = static_cast<bf16*>(p.d_q) + rowi * D;
+    if (ok) tc_fence_after();
+#pragma unroll
+    for (int cb = 0; cb < D / 32; ++cb) {
+      float ov[32];
+      if (ok && n > 0) {
+        tmem_ld32(tdQ + lane_base + cb * 32, ov);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) ov[j] = 0.f;
+      }
+      if (valid) {
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          __nv_bfloat162 hh[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) hh[e] = __floats2bfloat162_rn(ov[c8 * 8 + 2 * e], ov[c8 * 8 + 2 * e + 1]);
+          *reinterpret_cast<uint4*>(orow + cb * 32 + c8 * 8) = *reinterpret_cast<uint4*>(hh);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem, 512);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dkv_tc_kernel(SparseParams p, BwdWs ws, int nblk,
+                                                                           const __grid_constant__ CUtensorMap tmK,
+                                                                           const __grid_constant__ CUtensorMap tmV,
+                                                                           const __grid_constant__ CUtensorMap tmQ,
+                                                                           const __grid_constant__ CUtensorMap tmdO) {
+  constexpr int DB = D / 64;
+  constexpr int QBYTES = DB * 16384;
+  constexpr int KVBYTES = DB * 8192;
+  constexpr int NDS = (D == 64) ? 2 : 1;   // buffers for the dS / wP tiles
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* Qs = smem;                      // 2 stages
+  uint8_t* dOs = Qs + 2 * QBYTES;          // 2 stages
+  uint8_t* Ks = dOs + 2 * QBYTES;
+  uint8_t* Vs = Ks + KVBYTES;
+  uint8_t* dSs = Vs + KVBYTES;             // NDS x 16 KB
+  uint8_t* Pws = dSs + NDS * 16384;        // NDS x 16 KB
+  int* list_s = reinterpret_cast<int*>(Pws + NDS * 16384);
+
+  __shared__ uint64_t kv_full, qdo_full[2], sdp_full[2], dsp_full[2], dkv_done[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int m_s, warp_tot_s[4];
+  __shared__ volatile int abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int nchunk = p.T / 64, nwords = (nchunk + 31) >> 5;
+  const int G = p.h_q / p.h_kv, QB = 128 / G;
+  const int64_t bh = (int64_t)b * p.h_kv + h;
+
+  if (tid == 0) {
+    mbar_init(&kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&sdp_full[s], 1);
+      mbar_init(&dsp_full[s], 128);
+      mbar_init(&dkv_done[s], 1);
+    }
+    mbar_init_fence();
+    abort_s = 0;
+  }
+  if (warp == 4) tmem_alloc(&tmem_base_s, 512);
+  // ---- query blocks that selected this chunk, ascending ----------------------------------------
+  {
+    const int per = (nblk + 127) / 128;
+    int cnt = 0;
+    if (tid < 128)
+      for (int j = tid * per; j < min(nblk, (tid + 1) * per); ++j)
+        cnt += (ws.bitmap[(bh * nblk + j) * nwords + (c >> 5)] >> (c & 31)) & 1u;
+    int inc = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int nn = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += nn;
+    }
+    if (tid < 128 && lane == 31) warp_tot_s[warp] = inc;
+    __syncthreads();
+    if (tid < 128) {
+      int base = inc - cnt;
+      for (int w = 0; w < warp; ++w) base += warp_tot_s[w];
+      for (int j = tid * per; j < min(nblk, (tid + 1) * per); ++j)
+        if ((ws.bitmap[(bh * nblk + j) * nwords + (c >> 5)] >> (c & 31)) & 1u) list_s[base++] = j;
+      if (tid == 127) m_s = base;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const int m = m_s;
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t tdK = tmem + 256, tdV = tmem + 256 + D;
+
+  if (warp == 5) {
+    if (lane == 0 && m > 0) {
+      mbar_expect_tx(&kv_full, 2 * KVBYTES);
+#pragma unroll
+      for (int db = 0; db < DB; ++db) {
+        tma_load_2d(Ks + db * 8192, &tmK, &kv_full, h * D + db * 64, b * p.T + c * 64);
+        tma_load_2d(Vs + db * 8192, &tmV, &kv_full, h * D + db * 64, b * p.T + c * 64);
+      }
+      for (int j = 0; j < m; ++j) {
+        const int s = j & 1, u = j >> 1;
+        if (abort_s) break;
+        if (j >= 2 && !mbar_wait(&dkv_done[s], (u - 1) & 1)) { abort_s = 1; atomicExch(&g_device_status, 301); break; }
+        const int blk = list_s[j];
+        mbar_expect_tx(&qdo_full[s], 2 * QBYTES);
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+          tma_load_3d(Qs + s * QBYTES + db * 16384, &tmQ, &qdo_full[s], db * 64, h * G, b * p.L + blk * QB);
+          tma_load_3d(dOs + s * QBYTES + db * 16384, &tmdO, &qdo_full[s], db * 64, h * G, b * p.L + blk * QB);
+        }
+      }
+    }
+  } else if (warp == 4) {
+    if (lane == 0 && m > 0) {
+      constexpr uint32_t idesc_s = idesc_bf16(128, 64, 0);
+      constexpr uint32_t idesc_dkv = idesc_bf16(64, D, 1, 1);
+      const uint32_t q_addr = smem_u32(Qs), do_addr = smem_u32(dOs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs),
+                     ds_addr = smem_u32(dSs), pw_addr = smem_u32(Pws);
+      auto issue_sdp = [&](int j) {
+        const int s = j & 1;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t ao = s * QBYTES + (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
+          mma_ss(tmem + s * 128, desc_sw128(q_addr + ao, 16, 1024), desc_sw128(k_addr + bo, 16, 1024), idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t ao = s * QBYTES + (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
+          mma_ss(tmem + s * 128 + 64, desc_sw128(do_addr + ao, 16, 1024), desc_sw128(v_addr + bo, 16, 1024), idesc_s, kk > 0);
+        }
+        mma_commit(&sdp_full[s]);
+      };
+      bool ok = mbar_wait(&kv_full, 0) && mbar_wait(&qdo_full[0], 0);
+      if (ok) { tc_fence_after(); issue_sdp(0); }
+      for (int j = 0; ok && j < m; ++j) {
+        const int s = j & 1, u = j >> 1, sb = j % NDS;
+        if (abort_s) break;
+        if (j + 1 < m) {
+          ok = mbar_wait(&qdo_full[(j + 1) & 1], ((j + 1) >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sdp(j + 1);
+        }
+        ok = mbar_wait(&dsp_full[s], u & 1);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {   // 16 query rows per step
+          const uint64_t db_q = desc_sw128(q_addr + s * QBYTES + kk * 2048, 16384, 1024);
+          const uint64_t db_do = desc_sw128(do_addr + s * QBYTES + kk * 2048, 16384, 1024);
+          mma_ss(tdK, desc_sw128(ds_addr + sb * 16384 + kk * 2048, 16384, 1024), db_q, idesc_dkv, (j > 0 || kk > 0) ? 1u : 0u);
+          mma_ss(tdV, desc_sw128(pw_addr + sb * 16384 + kk * 2048, 16384, 1024), db_do, idesc_dkv, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(&dkv_done[s]);
+      }
+      if (!ok) { abort_s = 1; atomicExch(&g_device_status, 302); }
+    }
+  } else {
+    const int r = tid, ql = r / G, g = r % G, hq = h * G + g;
+    const float scale_log2 = p.scale * kLog2e;
+    const float slope = p.slope ? p.slope[hq] : 0.f;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    bool ok = true;
+    for (int j = 0; j < m; ++j) {
+      const int s = j & 1, u = j >> 1, sb = j % NDS;
+      const int blk = list_s[j];
+      const int t = blk * QB + ql;
+      const bool valid = t < p.L;
+      float wsum = 0.f;
+      bool owner = false;
+      if (valid) {
+        const int32_t* ids = p.idx + (((int64_t)b * p.L + t) * p.h_kv + h) * p.K;
+        const bf16* wrow = static_cast<const bf16*>(p.w) + (((int64_t)b * p.L + t) * p.h_q + hq) * p.num_weights;
+        if (!ws.flags[bh * nblk + blk]) {
+          // ascending list with negative padding at the end: first position holding an id >= c
+          int lo = 0, hi = p.K;
+          while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            const int id = __ldg(ids + mid);
+            if (id >= 0 && id < c) lo = mid + 1; else hi = mid;
+          }
+          while (lo < p.K && __ldg(ids + lo) == c) { owner = true; wsum += to_f(wrow[lo]); ++lo; }
+        } else {
+          for (int k = 0; k < p.K; ++k) {
+            const int id = __ldg(ids + k);
+            if (id < 0) break;
+            if (id == c) { owner = true; wsum += to_f(wrow[k]); }
+          }
+        }
+      }
+      ok = mbar_wait(&sdp_full[s], u & 1);
+      if (j >= NDS) ok = mbar_wait(&dkv_done[(j - NDS) & 1], ((j - NDS) >> 1) & 1) && ok;
+      ok = __all_sync(0xffffffffu, ok) && !abort_s;
+      if (!ok) break;
+      tc_fence_after();
+      float sv[64], dp[64];
+      tmem_ld32(tmem + lane_base + s * 128, sv);
+      tmem_ld32(tmem + lane_base + s * 128 + 32, sv + 32);
+      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);
+      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
+      tmem_ld_wait();
+      if (owner) {
+        bwd_row(sv, dp, wsum, p.scale, scale_log2, slope, p.mask_last);
+        store_row_bf16_sw128(dSs + sb * 16384, r, sv);
+        store_row_bf16_sw128(Pws + sb * 16384, r, dp);
+      } else {
+        store_row_zero_sw128(dSs + sb * 16384, r);
+        store_row_zero_sw128(Pws + sb * 16384, r);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&dsp_full[s]);
+    }
+    if (ok && m > 0) {
+      ok = mbar_wait(&dkv_done[(m - 1) & 1], ((m - 1) >> 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok && lane == 0) { abort_s = 1; atomicExch(&g_device_status, 303); }
+    } else if (!ok && lane == 0) {
+      abort_s = 1;
+      atomicExch(&g_device_status, 304);
+    }
+    // M = 64 accumulators: key row 16*warp + lane lives in TMEM lane 32*warp + lane, lanes 0..15 of each warp
+    const int krow = 16 * warp + lane;
+    const int64_t tok = (int64_t)b * p.T + (int64_t)c * 64 + krow;
+    bf16* dkrow = static_cast<bf16*>(p.d_k_out) + (tok * p.h_kv + h) * D;
+    bf16* dvrow = static_cast<bf16*>(p.d_v_out) + (tok * p.h_kv + h) * D;
+    if (ok) tc_fence_after();
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+#pragma unroll
+      for (int cb = 0; cb < D / 32; ++cb) {
+        float ov[32];
+        if (ok && m > 0) {
+          tmem_ld32((which ? tdV : tdK) + lane_base + cb * 32, ov);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) ov[jj] = 0.f;
+        }
+        if (lane < 16) {
+          bf16* dst = (which ? dvrow : dkrow) + cb * 32;
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) {
+            __nv_bfloat162 hh[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) hh[e] = __floats2bfloat162_rn(ov[c8 * 8 + 2 * e], ov[c8 * 8 + 2 * e + 1]);
+            *reinterpret_cast<uint4*>(dst + c8 * 8) = *reinterpret_cast<uint4*>(hh);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem, 512);
+}
+
+static bool tc_shape_ok(const SparseParams& p) {
+  const int D = p.D;
+  if (p.S != 64 || p.D != p.Dv || (D != 64 && D != 128)) return false;
+  const int G = p.h_q / p.h_kv;
+  if (G > 128 || (128 % G) != 0) return false;
+  if (p.T < 64 || p.K > 1024) return false;
+  if ((int64_t)p.B * p.T >= (1ll << 31) || (int64_t)p.B * p.L >= (1ll << 31)) return false;
+  return true;
+}
+
+static size_t tc_bwd_smem_dq(const SparseParams& p) {
+  const int D = p.D, G = p.h_q / p.h_kv, QB = 128 / G, nchunk = p.T / 64;
+  const int umax = min(nchunk, QB * p.K);
+  return 1024 + 2 * (size_t)(D / 64) * 16384 + 4 * (size_t)(D / 64) * 8192 + 2 * 16384 + (size_t)umax * 4 +
+         (size_t)((nchunk + 31) / 32) * 4 + 16;
+}
+static size_t tc_bwd_smem_dkv(const SparseParams& p, int nblk) {
+  const int D = p.D, NDS = (D == 64) ? 2 : 1;
+  return 1024 + 4 * (size_t)(D / 64) * 16384 + 2 * (size_t)(D / 64) * 8192 + 2 * (size_t)NDS * 16384 + (size_t)nblk * 4 + 16;
+}
+
+// workspace of the tensor-core backward (0 when the shape is outside this path)
+size_t sparse_bwd_tc_workspace(const SparseParams& p) {
+  if (!tc_shape_ok(p)) return 0;
+  const int G = p.h_q / p.h_kv, QB = 128 / G, nblk = ceil_div(p.L, QB), nchunk = p.T / 64;
+  if (tc_bwd_smem_dq(p) > 220 * 1024 || tc_bwd_smem_dkv(p, nblk) > 220 * 1024) return 0;
+  const size_t nw = (size_t)((nchunk + 31) / 32);
+  return ((size_t)p.B * p.h_kv * nblk * nw + (size_t)p.B * p.h_kv * nblk) * 4 + 256;
+}
+
+int sparse_bwd_tc_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st) {
+  if (sparse_bwd_tc_workspace(p) == 0) return HILS_ERR_UNSUPPORTED;
+  if (((uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.d_o | (uintptr_t)p.d_q | (uintptr_t)d_k |
+       (uintptr_t)d_v) & 15)
+    return HILS_ERR_UNSUPPORTED;
+  const int D = p.D, G = p.h_q / p.h_kv, QB = 128 / G, nblk = ceil_div(p.L, QB), nchunk = p.T / 64;
+  const size_t nw = (size_t)((nchunk + 31) / 32);
+  BwdWs ws;
+  ws.bitmap = static_cast<uint32_t*>(workspace);
+  ws.flags = reinterpret_cast<int*>(ws.bitmap + (size_t)p.B * p.h_kv * nblk * nw);
+  SparseParams pp = p;
+  pp.d_k_out = d_k;
+  pp.d_v_out = d_v;
+  CUtensorMap tmK, tmV, tmQ, tmdO;
+  if (int rc = make_tmap_bf16_rows(&tmK, p.k, (uint64_t)p.B * p.T, (uint64_t)p.h_kv * D, (uint64_t)p.h_kv * D, 64)) return rc;
+  if (int rc = make_tmap_bf16_rows(&tmV, p.v, (uint64_t)p.B * p.T, (uint64_t)p.h_kv * D, (uint64_t)p.h_kv * D, 64)) return rc;
+  if (int rc = make_tmap_bf16_thd(&tmQ, p.q, (uint64_t)p.B * p.L, p.h_q, D, G, QB)) return rc;
+  if (int rc = make_tmap_bf16_thd(&tmdO, p.d_o, (uint64_t)p.B * p.L, p.h_q, D, G, QB)) return rc;
+  if (p.T % 64 != 0) {  // tokens after the last full chunk belong to no chunk: their gradients are zero
+    cudaMemsetAsync(d_k, 0, (size_t)p.B * p.T * p.h_kv * D * 2, st);
+    cudaMemsetAsync(d_v, 0, (size_t)p.B * p.T * p.h_kv * D * 2, st);
+  }
+  const size_t smem_dq = tc_bwd_smem_dq(p), smem_dkv = tc_bwd_smem_dkv(p, nblk);
+  dim3 grid_q(nblk, p.h_kv, p.B), grid_c(nchunk, p.h_kv, p.B);
+  if (D == 64) {
+    cudaFuncSetAttribute(sparse_bwd_dq_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq);
+    cudaFuncSetAttribute(sparse_bwd_dkv_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dkv);
+    sparse_bwd_dq_tc_kernel<64><<<grid_q, kTcThreads, smem_dq, st>>>(pp, ws, tmK, tmV);
+    sparse_bwd_dkv_tc_kernel<64><<<grid_c, kTcThreads, smem_dkv, st>>>(pp, ws, nblk, tmK, tmV, tmQ, tmdO);
+  } else {
+    cudaFuncSetAttribute(sparse_bwd_dq_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq);
+    cudaFuncSetAttribute(sparse_bwd_dkv_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dkv);
+    sparse_bwd_dq_tc_kernel<128><<<grid_q, kTcThreads, smem_dq, st>>>(pp, ws, tmK, tmV);
+    sparse_bwd_dkv_tc_kernel<128><<<grid_c, kTcThreads, smem_dkv, st>>>(pp, ws, nblk, tmK, tmV, tmQ, tmdO);
+  }
+  HILS_LAUNCH_CHECK("sparse_attn_bwd (tensor-core path)");
+  return HILS_OK;
 }
 
 // Returns HILS_ERR_UNSUPPORTED (without setting an error text) when the shape is outside this path.

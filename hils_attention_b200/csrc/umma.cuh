@@ -52,6 +52,14 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       : "memory");
 }
 
+// 3-D TMA tile load (innermost coordinate first)
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
 // shared-memory matrix descriptor, 128-byte swizzle; start address must lie in a 1024-byte aligned tile
 //   K-major operand : rows of 128 B (64 bf16 of K), 8-row groups 1024 B apart -> lbo 16, sbo 1024
 //   MN-major operand: rows (one K index each) of 128 B (64 bf16 of N); sbo = 1024 (next 8 K rows),
@@ -66,10 +74,10 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr, uint32_t lbo_byte
   return d;
 }
 
-// instruction descriptor: bf16 x bf16 -> fp32, A K-major, B K-major (b_mn = 0) or MN-major (b_mn = 1)
-__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int b_mn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(N >> 3) << 17) |
-         ((uint32_t)(M >> 4) << 24);
+// instruction descriptor: bf16 x bf16 -> fp32; a_mn / b_mn = 0 for a K-major operand, 1 for MN-major
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int b_mn, int a_mn = 0) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; one thread issues
@@ -122,5 +130,9 @@ __device__ __forceinline__ float ex2(float x) {
 // host side: tensor map over a row-major bf16 matrix [rows][cols], tiles of 64 rows x 64 cols (128 B), 128-B swizzle
 int make_tmap_bf16_rows(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
                         uint32_t box_rows);
+// tensor map over a (tokens, heads, D) bf16 tensor; a tile is 64 columns x `box_heads` heads x `box_tokens` tokens,
+// laid out in shared memory as rows of 128 B ordered (token, head)
+int make_tmap_bf16_thd(CUtensorMap* map, const void* base, uint64_t tokens, uint64_t heads, uint64_t D,
+                       uint32_t box_heads, uint32_t box_tokens);
 
 }  // namespace hils
