@@ -36,7 +36,8 @@ SIGNATURES = {
     "hils_chunk_logz_fwd": (_I, [_P] * 3 + [_I] * 7 + [_F, _I, _I, _P]),
     "hils_chunk_logz_bwd": (_I, [_P] * 6 + [_I] * 7 + [_F, _I, _P]),
     "hils_swa_fwd": (_I, [_P] * 5 + [_I] * 11 + [_F, _I, _I, _P]),
-    "hils_swa_bwd": (_I, [_P] * 10 + [_I] * 10 + [_F, _I, _P]),
+    "hils_swa_bwd": (_I, [_P] * 10 + [_I] * 10 + [_F, _I, _P, _SZ, _P]),
+    "hils_swa_bwd_workspace_bytes": (_SZ, [_I] * 8),
 }
 
 # kernels each entry point launches (memsets excluded); used to report launch counts

@@ -21,5 +21,19 @@ int cuda_fail(cudaError_t e, const char* what) {
 
 }  // namespace hils
 
+namespace hils {
+int take_status_sparse_tc();
+int take_status_swa_tc();
+}  // namespace hils
+
 extern "C" int hils_version(void) { return 100; }
+
+// Device-side error words written by kernels whose bounded waits expired (0 = none).  Reading them
+// synchronises the device and clears them.
+extern "C" int hils_take_device_status(void) {
+  const int a = hils::take_status_sparse_tc();
+  const int b = hils::take_status_swa_tc();
+  if (a < 0 || b < 0) return -1;
+  return a != 0 ? a : b;
+}
 extern "C" const char* hils_last_error(void) { return hils::g_err; }

@@ -18,10 +18,11 @@
 // word, every role leaves its loop, TMEM is released and the kernel returns.
 #include "sparse_attn_generic.cuh"
 #include "umma.cuh"
+#include "tc_rows.cuh"
 
 namespace hils {
 
-__device__ int g_device_status = 0;
+static __device__ int g_device_status = 0;
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -411,20 +412,6 @@ __device__ __forceinline__ float bwd_row(float* sv, float* dp, float wsum, float
     dp[j] = wsum * pj;
   }
   return dw;
-}
-
-__device__ __forceinline__ void store_row_bf16_sw128(uint8_t* tile, int r, const float* v) {
-#pragma unroll
-  for (int c8 = 0; c8 < 8; ++c8) {
-    __nv_bfloat162 hh[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) hh[e] = __floats2bfloat162_rn(v[c8 * 8 + 2 * e], v[c8 * 8 + 2 * e + 1]);
-    *reinterpret_cast<uint4*>(tile + sw128_off(r, c8)) = *reinterpret_cast<uint4*>(hh);
-  }
-}
-__device__ __forceinline__ void store_row_zero_sw128(uint8_t* tile, int r) {
-#pragma unroll
-  for (int c8 = 0; c8 < 8; ++c8) *reinterpret_cast<uint4*>(tile + sw128_off(r, c8)) = make_uint4(0u, 0u, 0u, 0u);
 }
 
 struct BwdWs {
@@ -1040,12 +1027,13 @@ int sparse_fwd_tc_launch(const SparseParams& p, cudaStream_t st) {
 
 }  // namespace hils
 
-// Device-side error word written by kernels whose bounded waits expired (0 = none).  Reading it
-// synchronises the device and clears it.
-extern "C" int hils_take_device_status(void) {
+namespace hils {
+// device-side error word of this file's kernels (0 = none); synchronises and clears
+int take_status_sparse_tc() {
   int v = 0, zero = 0;
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-  if (cudaMemcpyFromSymbol(&v, hils::g_device_status, sizeof(int)) != cudaSuccess) return -1;
-  if (v != 0) cudaMemcpyToSymbol(hils::g_device_status, &zero, sizeof(int));
+  if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
   return v;
 }
+}  // namespace hils

@@ -260,6 +260,14 @@ __global__ void __launch_bounds__(128) swa_bwd_dkv_kernel(SwaParams p, int64_t r
   }
 }
 
+int swa_fwd_tc_launch(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Lq, int Lk, int h_q,
+                      int h_kv, int D, int Dv, int W, int S, int mask_lmk, int expand, float scale, int kv_start,
+                      cudaStream_t st);  // swa_tc.cu
+size_t swa_bwd_tc_workspace(int B, int L, int h_q, int h_kv, int D, int Dv, int S);
+int swa_bwd_tc_launch(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                      const float* d_lse, void* d_q, void* d_k, void* d_v, void* workspace, int B, int L, int h_q, int h_kv,
+                      int D, int Dv, int W, int S, int mask_lmk, int expand, float scale, cudaStream_t st);
+
 static int check_swa(int B, int Lq, int Lk, int h_q, int h_kv, int D, int Dv, int S, int dtype) {
   HILS_REQUIRE(B > 0 && Lq >= 0 && Lk >= 0 && h_q > 0 && h_kv > 0 && D > 0 && Dv > 0 && S > 0, "swa: bad size");
   HILS_REQUIRE(h_q % h_kv == 0, "swa: h_q (%d) must be a multiple of h_kv (%d)", h_q, h_kv);
@@ -281,6 +289,11 @@ extern "C" int hils_swa_fwd(const void* q, const void* k, const void* v, void* o
   HILS_REQUIRE(Lq <= Lk, "swa_fwd: Lq (%d) must not exceed Lk (%d)", Lq, Lk);
   if (Lq == 0) return HILS_OK;
   HILS_REQUIRE(q && k && v && o && lse, "swa_fwd: null pointer");
+  if (dtype == HILS_BF16) {  // tensor-core path for the shapes it covers
+    const int rc = swa_fwd_tc_launch(q, k, v, o, lse, B, Lq, Lk, h_q, h_kv, D, Dv, window_size, chunk_size, mask_lmk,
+                                     expand_to_chunk, sm_scale, kv_start, (cudaStream_t)stream);
+    if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  }
   SwaParams p;
   p.q = q; p.k = k; p.v = v; p.o = o; p.lse = lse; p.d_o = nullptr; p.d_lse = nullptr;
   p.d_q = nullptr; p.d_k = nullptr; p.d_v = nullptr;
@@ -296,13 +309,31 @@ extern "C" int hils_swa_fwd(const void* q, const void* k, const void* v, void* o
   return HILS_OK;
 }
 
+extern "C" size_t hils_swa_bwd_workspace_bytes(int B, int L, int h_q, int h_kv, int D, int Dv, int chunk_size, int dtype) {
+  if (dtype != HILS_BF16 || h_q <= 0 || h_kv <= 0 || h_q % h_kv != 0) return 0;
+  return swa_bwd_tc_workspace(B, L, h_q, h_kv, D, Dv, chunk_size);
+}
+
 extern "C" int hils_swa_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
                             const void* d_o, const float* d_lse, void* d_q, void* d_k, void* d_v, int B, int L,
                             int h_q, int h_kv, int D, int Dv, int window_size, int chunk_size, int mask_lmk,
-                            int expand_to_chunk, float sm_scale, int dtype, void* stream) {
+                            int expand_to_chunk, float sm_scale, int dtype, void* workspace, size_t workspace_bytes,
+                            void* stream) {
   if (int rc = check_swa(B, L, L, h_q, h_kv, D, Dv, chunk_size, dtype)) return rc;
   if (L == 0) return HILS_OK;
   HILS_REQUIRE(q && k && v && o && lse && d_o && d_q && d_k && d_v, "swa_bwd: null pointer");
+  if (dtype == HILS_BF16) {
+    const size_t need = swa_bwd_tc_workspace(B, L, h_q, h_kv, D, Dv, chunk_size);
+    if (need > 0) {
+      if (!workspace || workspace_bytes < need) {
+        set_error("swa_bwd: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+        return HILS_ERR_WORKSPACE;
+      }
+      const int rc = swa_bwd_tc_launch(q, k, v, o, lse, d_o, d_lse, d_q, d_k, d_v, workspace, B, L, h_q, h_kv, D, Dv,
+                                       window_size, chunk_size, mask_lmk, expand_to_chunk, sm_scale, (cudaStream_t)stream);
+      if (rc != HILS_ERR_UNSUPPORTED) return rc;
+    }
+  }
   SwaParams p;
   p.q = q; p.k = k; p.v = v; p.o = const_cast<void*>(o); p.lse = const_cast<float*>(lse); p.d_o = d_o;
   p.d_lse = d_lse; p.d_q = d_q; p.d_k = d_k; p.d_v = d_v;

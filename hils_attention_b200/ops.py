@@ -433,8 +433,10 @@ class _FlexAttn(torch.autograd.Function):
         do = do.contiguous().to(q.dtype)
         dlse = None if dlse is None else dlse.contiguous().float()
         d_q, d_k, d_v = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        ws_bytes = query("hils_swa_bwd_workspace_bytes", B, L, H, H_kv, D, Dv, S, dt)
+        ws = _workspace(ws_bytes, q.device)
         call("hils_swa_bwd", ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(do), ptr(dlse), ptr(d_q), ptr(d_k),
-             ptr(d_v), B, L, H, H_kv, D, Dv, W, S, mask_lmk, expand, scale, dt, stream())
+             ptr(d_v), B, L, H, H_kv, D, Dv, W, S, mask_lmk, expand, scale, dt, ptr(ws), ws_bytes, stream())
         return d_q, d_k, d_v, None, None, None, None, None, None, None
 
 

@@ -148,7 +148,8 @@ int hils_chunk_logz_bwd(const void* q, const void* k, const float* log_z, const 
  *   q (B,Lq,h_q,D), k (B,Lk,h_kv,D), v (B,Lk,h_kv,Dv); o (B,Lq,h_q,Dv) in `dtype`;
  *   lse (B,Lq,h_q) fp32, natural log; rows with no visible key give o = 0, lse = -inf.
  *   Query i sits at absolute position kv_start + (Lk-Lq) + i.
- *   Backward takes d_o and d_lse (fp32, may be NULL) and writes d_q, d_k, d_v in `dtype`.
+ *   Backward takes d_o and d_lse (fp32, may be NULL) and writes d_q, d_k, d_v in `dtype`;
+ *   workspace: hils_swa_bwd_workspace_bytes() bytes of scratch (per-row Delta, fp32).
  * ------------------------------------------------------------------------------------- */
 int hils_swa_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                  int B, int Lq, int Lk, int h_q, int h_kv, int D, int Dv,
@@ -158,7 +159,9 @@ int hils_swa_bwd(const void* q, const void* k, const void* v, const void* o, con
                  const void* d_o, const float* d_lse, void* d_q, void* d_k, void* d_v,
                  int B, int L, int h_q, int h_kv, int D, int Dv,
                  int window_size, int chunk_size, int mask_lmk, int expand_to_chunk,
-                 float sm_scale, int dtype, void* stream);
+                 float sm_scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+size_t hils_swa_bwd_workspace_bytes(int B, int L, int h_q, int h_kv, int D, int Dv, int chunk_size,
+                                    int dtype);
 
 #ifdef __cplusplus
 }

@@ -278,6 +278,14 @@ SWA_CASES = [
     (1, 1, 300, 2, 1, 32, 64, 32, True, True, 0),       # decode
     (1, 64, 192, 2, 2, 32, 64, 32, True, True, 0),      # chunk prefill
     (1, 2, 100, 2, 1, 32, 64, 32, True, True, 156),     # truncated cache
+    # head dims 64 / 128: the tensor-core path in bf16
+    (1, 1024, 1024, 2, 2, 64, 512, 64, True, True, 0),
+    (2, 777, 777, 8, 1, 64, 128, 64, True, True, 0),    # G = 8, ragged
+    (1, 640, 640, 2, 1, 128, 256, 64, True, True, 0),
+    (1, 300, 300, 2, 2, 128, 100, 65, True, False, 0),  # chunk 65, no snapping
+    (1, 1, 700, 4, 2, 64, 128, 64, True, True, 0),      # decode
+    (1, 100, 612, 2, 1, 128, 128, 64, False, True, 0),  # chunk prefill
+    (1, 2, 200, 2, 1, 64, 64, 32, True, True, 157),     # truncated cache
 ]
 
 
@@ -306,6 +314,8 @@ def test_swa_forward_backward(ops, case, dtype):
     ((o.float() * do.cuda()).sum() + (lse.masked_fill(~fin.cuda(), 0.0) * dl.cuda()).sum()).backward()
     for n, t, r in (("dq", q, qr), ("dk", k, kr), ("dv", v, vr)):
         check(t.grad, r.grad, dtype, "swa " + n, scale=10.0)
+    from hils_attention_b200 import _lib
+    assert _lib.load().hils_take_device_status() == 0
 
 
 def test_swa_errors(ops):
