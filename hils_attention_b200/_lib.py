@@ -29,6 +29,8 @@ SIGNATURES = {
     "hils_meanpool_bwd": (_I, [_P, _P] + [_I] * 6 + [_P]),
     "hils_topk_fwd": (_I, [_P] * 10 + [_I] * 12 + [_F, _I, _I, _P]),
     "hils_topk_bwd": (_I, [_P] * 7 + [_I] * 8 + [_F, _I, _P]),
+    "hils_topk_bwd_noalloc": (_I, [_P] * 6 + [_I] * 8 + [_F, _I, _P]),
+    "hils_topk_bwd_noalloc_max_elems": (_SZ, []),
     "hils_sparse_attn_fwd": (_I, [_P] * 7 + [_I] * 10 + [_F, _I, _I, _P, _SZ, _P]),
     "hils_sparse_attn_fwd_workspace_bytes": (_SZ, [_I] * 10),
     "hils_sparse_attn_bwd": (_I, [_P] * 11 + [_I] * 10 + [_F, _I, _I, _P, _SZ, _P]),
@@ -43,7 +45,7 @@ SIGNATURES = {
 # kernels each entry point launches (memsets excluded); used to report launch counts
 KERNELS_PER_CALL = {
     "hils_pool_fwd": 1, "hils_pool_bwd": 1, "hils_meanpool_fwd": 1, "hils_meanpool_bwd": 1,
-    "hils_topk_fwd": 1, "hils_topk_bwd": 2, "hils_sparse_attn_fwd": 1, "hils_sparse_attn_bwd": 3,
+    "hils_topk_fwd": 1, "hils_topk_bwd": 2, "hils_topk_bwd_noalloc": 2, "hils_sparse_attn_fwd": 1, "hils_sparse_attn_bwd": 3,
     "hils_chunk_logz_fwd": 1, "hils_chunk_logz_bwd": 2, "hils_swa_fwd": 1, "hils_swa_bwd": 2,
 }
 _launches = 0

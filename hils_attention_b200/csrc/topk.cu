@@ -428,3 +428,66 @@ extern "C" int hils_topk_bwd(const void* d_scores, const int32_t* indices, const
   }
   return HILS_OK;
 }
+
+
+// -------------------------------------------------------------------------------------------------
+// Selection backward for callers that must not allocate.
+//
+// Some hosts of this library cannot obtain device memory at call time: code running while a
+// caching allocator is frozen or nearly full, a serving process that pinned all of its memory at
+// start-up, or a plugin whose owner forbids cudaMalloc after initialisation.  hils_topk_bwd needs
+// an fp32 accumulator with the shape of the chunk keys; this variant keeps that accumulator in a
+// fixed array inside the library image, so the caller passes only inputs and outputs.
+//
+// The array is a file-scope __device__ variable.  In host code its name is only a handle, not a
+// device address, so the address is fetched once per device with cudaGetSymbolAddress (with that
+// device current) and that pointer is what the kernels receive.
+// -------------------------------------------------------------------------------------------------
+namespace hils {
+
+constexpr size_t kNoAllocFloats = (size_t)1 << 20;  // 4 MiB of fp32, held by every GPU that loads the library
+static __device__ __align__(256) float g_topk_bwd_scratch[kNoAllocFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_scratch_ptr[kMaxDevices] = {nullptr};
+
+// device address of the scratch array on the current device (looked up on the first call per device)
+static int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "topk_bwd_noalloc: cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_error("topk_bwd_noalloc: device ordinal %d outside [0, %d)", dev, kMaxDevices);
+    return HILS_ERR_UNSUPPORTED;
+  }
+  if (!g_scratch_ptr[dev]) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_topk_bwd_scratch);
+    if (e != cudaSuccess || !ptr) return cuda_fail(e, "topk_bwd_noalloc: cudaGetSymbolAddress");
+    g_scratch_ptr[dev] = ptr;
+  }
+  *out = g_scratch_ptr[dev];
+  return HILS_OK;
+}
+
+}  // namespace hils
+
+extern "C" size_t hils_topk_bwd_noalloc_max_elems(void) { return hils::kNoAllocFloats; }
+
+extern "C" int hils_topk_bwd_noalloc(const void* d_scores, const int32_t* indices, const void* q, const void* lmks,
+                                     void* d_q, void* d_lmks, int B, int L, int N, int h_kv, int G, int D, int topk,
+                                     int per_qhead, float sm_scale, int dtype, void* stream) {
+  HILS_REQUIRE(B > 0 && L >= 0 && N >= 0 && h_kv > 0 && G > 0 && D > 0 && topk > 0, "topk_bwd_noalloc: bad size");
+  const int HL = per_qhead ? h_kv * G : h_kv;
+  const unsigned long long need = (unsigned long long)B * N * HL * D;
+  if (need > hils::kNoAllocFloats) {
+    set_error("topk_bwd_noalloc: chunk-key gradient of %llu elements (B*N*heads*D) exceeds the built-in scratch of "
+              "%zu elements; use hils_topk_bwd with a caller-provided accumulator", need, hils::kNoAllocFloats);
+    return HILS_ERR_WORKSPACE;
+  }
+  float* scratch = nullptr;
+  if (int rc = hils::noalloc_scratch(&scratch)) return rc;
+  // hils_topk_bwd zeroes the accumulator itself (cudaMemsetAsync on the stream) before accumulating
+  return hils_topk_bwd(d_scores, indices, q, lmks, d_q, scratch, d_lmks, B, L, N, h_kv, G, D, topk, per_qhead,
+                       sm_scale, dtype, stream);
+}

@@ -102,6 +102,24 @@ int hils_topk_bwd(const void* d_scores, const int32_t* indices, const void* q, c
                   int B, int L, int N, int h_kv, int G, int D, int topk, int per_qhead,
                   float sm_scale, int dtype, void* stream);
 
+/* Selection backward for callers that cannot allocate device memory when they call (a frozen or
+ * exhausted caching allocator, a server that reserved all memory at start-up, a plugin barred
+ * from cudaMalloc after initialisation).  Same inputs, outputs and arithmetic as hils_topk_bwd,
+ * but the fp32 accumulator is a fixed 4 MiB array inside the library image (every GPU that loads
+ * the library holds it until exit), so nothing is allocated by the call or by the caller.
+ *   Limit: B*N*heads*D (elements of lmks) <= hils_topk_bwd_noalloc_max_elems() = 1,048,576;
+ *   larger problems are rejected with HILS_ERR_WORKSPACE.
+ *   The first call on each device looks up the array's device address; make that first call
+ *   outside any stream capture.
+ *   All calls share the one array: it is cleared at the start of every call, and two calls whose
+ *   work overlaps on the GPU (different streams) race on it - serialise them.
+ * This entry point has no counterpart in the reference. */
+int hils_topk_bwd_noalloc(const void* d_scores, const int32_t* indices, const void* q, const void* lmks,
+                          void* d_q, void* d_lmks,
+                          int B, int L, int N, int h_kv, int G, int D, int topk, int per_qhead,
+                          float sm_scale, int dtype, void* stream);
+size_t hils_topk_bwd_noalloc_max_elems(void);
+
 /* ---------------------------------------------------------------------------------------
  * Sparse chunk attention.  Replaces _hils_block_M_attention_inverse.forward/backward
  * (ops/hils_fwd_bwd_head.py:771-913; kernels :198-496 and :506-766).
