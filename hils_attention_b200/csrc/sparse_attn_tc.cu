@@ -92,6 +92,7 @@ int make_tmap_bf16_thd(CUtensorMap* map, const void* base, uint64_t tokens, uint
 using namespace umma;
 
 constexpr int kTcThreads = 192;
+constexpr int kBwdThreads = 320;  // 2 row warpgroups + MMA warp + TMA warp
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D>
@@ -420,7 +421,7 @@ struct BwdWs {
 };
 
 template <int D>
-__global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseParams p, BwdWs ws,
+__global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(SparseParams p, BwdWs ws,
                                                                           const __grid_constant__ CUtensorMap tmK,
                                                                           const __grid_constant__ CUtensorMap tmV) {
   constexpr int DB = D / 64;
@@ -440,7 +441,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
   const int umax = min(nchunk, QB * p.K);
   uint32_t* bitmap_s = reinterpret_cast<uint32_t*>(union_s + umax);
 
-  __shared__ uint64_t kv_full[2], sdp_full[2], ds_full[2], dq_done[2];
+  __shared__ uint64_t kv_full[2], sdp_full[2], ds_full[2], dq_done[2], all_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int n_union_s, warp_tot_s[4];
   __shared__ volatile int abort_s;
@@ -457,16 +458,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
       mbar_init(&ds_full[s], 128);
       mbar_init(&dq_done[s], 1);
     }
+    mbar_init(&all_done, 1);
     mbar_init_fence();
     abort_s = 0;
   }
-  if (warp == 4) tmem_alloc(&tmem_base_s, 512);
-  for (int w = tid; w < nwords; w += kTcThreads) bitmap_s[w] = 0u;
+  if (warp == 8) tmem_alloc(&tmem_base_s, 512);
+  for (int w = tid; w < nwords; w += kBwdThreads) bitmap_s[w] = 0u;
   __syncthreads();
 
-  const int r = tid;
+  // rows: two warpgroups (threads 0..127 and 128..255) each own all 128 rows and alternate over the
+  // union entries (warpgroup w takes entries w, w+2, ... and the buffers of stage w)
+  const int r = tid & 127, wg = tid >> 7;
   const int ql = r / G, g = r % G, t = q0 + ql;
-  const bool is_row = tid < 128;
+  const bool is_row = tid < 256, is_loader = tid < 128;
   const bool valid = is_row && t < p.L;
   const int hq = h * G + g;
   const int64_t rowi = ((int64_t)b * p.L + (valid ? t : 0)) * p.h_q + hq;
@@ -474,7 +478,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
   const bf16* wrow = static_cast<const bf16*>(p.w) + rowi * p.num_weights;
   bf16* dwrow = static_cast<bf16*>(p.d_w) + rowi * p.num_weights;
   int nvalid = 0, my_unsorted = 0;
-  if (is_row) {
+  if (is_loader) {
     const bf16* qrow = static_cast<const bf16*>(p.q) + rowi * D;
     const bf16* dorow = static_cast<const bf16*>(p.d_o) + rowi * D;
 #pragma unroll
@@ -487,27 +491,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
       *reinterpret_cast<uint4*>(Qs + (c >> 3) * 16384 + sw128_off(r, c & 7)) = x;
       *reinterpret_cast<uint4*>(dOs + (c >> 3) * 16384 + sw128_off(r, c & 7)) = y;
     }
-    if (valid) {
+    if (valid)
       for (int k = 0; k < p.num_weights; ++k) dwrow[k] = __float2bfloat16_rn(0.f);
-      int prev = -1;
-      for (int k = 0; k < p.K; ++k) {
-        const int id = __ldg(ids + k);
-        if (id < 0) break;
-        ++nvalid;
-        if (id < prev) my_unsorted = 1;
-        prev = id;
-        if (g == 0 && id < nchunk) atomicOr(&bitmap_s[id >> 5], 1u << (id & 31));
-      }
+  }
+  if (valid) {
+    int prev = -1;
+    for (int k = 0; k < p.K; ++k) {
+      const int id = __ldg(ids + k);
+      if (id < 0) break;
+      ++nvalid;
+      if (id < prev) my_unsorted = 1;
+      prev = id;
+      if (is_loader && g == 0 && id < nchunk) atomicOr(&bitmap_s[id >> 5], 1u << (id & 31));
     }
   }
   const int unsorted = __syncthreads_or(my_unsorted);
   {
     const int64_t bh = (int64_t)b * p.h_kv + h;
-    for (int w = tid; w < nwords; w += kTcThreads) ws.bitmap[(bh * nblk + blk) * nwords + w] = bitmap_s[w];
+    for (int w = tid; w < nwords; w += kBwdThreads) ws.bitmap[(bh * nblk + blk) * nwords + w] = bitmap_s[w];
     if (tid == 0) ws.flags[bh * nblk + blk] = unsorted;
     const int wpt = (nwords + 127) / 128;
     int cnt = 0;
-    if (is_row)
+    if (is_loader)
       for (int w = tid * wpt; w < min(nwords, (tid + 1) * wpt); ++w) cnt += __popc(bitmap_s[w]);
     int inc = cnt;
 #pragma unroll
@@ -515,9 +520,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
       int nn = __shfl_up_sync(0xffffffffu, inc, o);
       if (lane >= o) inc += nn;
     }
-    if (is_row && lane == 31) warp_tot_s[warp] = inc;
+    if (is_loader && lane == 31) warp_tot_s[warp] = inc;
     __syncthreads();
-    if (is_row) {
+    if (is_loader) {
       int base = inc - cnt;
       for (int w = 0; w < warp; ++w) base += warp_tot_s[w];
       for (int w = tid * wpt; w < min(nwords, (tid + 1) * wpt); ++w) {
@@ -540,7 +545,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
   const uint32_t tmem = tmem_base_s;
   const uint32_t tdQ = tmem + 256;
 
-  if (warp == 5) {
+  if (warp == 9) {
     if (lane == 0) {
       for (int i = 0; i < n; ++i) {
         const int s = i & 1, u = i >> 1;
@@ -555,7 +560,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     if (lane == 0 && n > 0) {
       constexpr uint32_t idesc_s = idesc_bf16(128, 64, 0);
       constexpr uint32_t idesc_dq = idesc_bf16(128, D, 1);
@@ -595,6 +600,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
                  desc_sw128(k_addr + s * KVBYTES + kk * 2048, 8192, 1024), idesc_dq, (i > 0 || kk > 0) ? 1u : 0u);
         mma_commit(&dq_done[s]);
       }
+      // both row warpgroups wait on this for the epilogue: a parity wait on a stage barrier could be
+      // satisfied by an older phase for the warpgroup that did not take the last entry
+      if (ok) mma_commit(&all_done);
       if (!ok) { abort_s = 1; atomicExch(&g_device_status, 202); }
     }
   } else {
@@ -602,15 +610,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
     const float slope = p.slope ? p.slope[hq] : 0.f;
     int ptr = 0;
     int cur = (nvalid > 0) ? __ldg(ids) : 0x7fffffff;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
-    for (int i = 0; i < n; ++i) {
+    for (int i = wg; i < n; i += 2) {
       const int s = i & 1, u = i >> 1;
       const int c = union_s[i];
       float wsum = 0.f;
       bool owner = false;
       int k_first = 0, k_last = 0;
       if (!unsorted) {
+        while (cur < c) {  // ids consumed by the other warpgroup's entries
+          ++ptr;
+          cur = (ptr < nvalid) ? __ldg(ids + ptr) : 0x7fffffff;
+        }
         k_first = ptr;
         while (cur == c) {
           owner = true;
@@ -653,7 +665,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
       mbar_arrive(&ds_full[s]);
     }
     if (ok && n > 0) {
-      ok = mbar_wait(&dq_done[(n - 1) & 1], ((n - 1) >> 1) & 1);
+      ok = mbar_wait(&all_done, 0);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok && lane == 0) { abort_s = 1; atomicExch(&g_device_status, 203); }
     } else if (!ok && lane == 0) {
@@ -663,7 +675,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
     bf16* orow = static_cast<bf16*>(p.d_q) + rowi * D;
     if (ok) tc_fence_after();
 #pragma unroll
-    for (int cb = 0; cb < D / 32; ++cb) {
+    for (int cb = wg; cb < D / 32; cb += 2) {  // each warpgroup writes half of the columns
       float ov[32];
       if (ok && n > 0) {
         tmem_ld32(tdQ + lane_base + cb * 32, ov);
@@ -685,11 +697,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dq_tc_kernel(SparseP
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, 512);
+  if (warp == 8) tmem_dealloc(tmem, 512);
 }
 
 template <int D>
-__global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dkv_tc_kernel(SparseParams p, BwdWs ws, int nblk,
+__global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(SparseParams p, BwdWs ws, int nblk,
                                                                            const __grid_constant__ CUtensorMap tmK,
                                                                            const __grid_constant__ CUtensorMap tmV,
                                                                            const __grid_constant__ CUtensorMap tmQ,
@@ -708,7 +720,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dkv_tc_kernel(Sparse
   uint8_t* Pws = dSs + NDS * 16384;        // NDS x 16 KB
   int* list_s = reinterpret_cast<int*>(Pws + NDS * 16384);
 
-  __shared__ uint64_t kv_full, qdo_full[2], sdp_full[2], dsp_full[2], dkv_done[2];
+  __shared__ uint64_t kv_full, qdo_full[2], sdp_full[2], dsp_full[2], dkv_done[2], all_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int m_s, warp_tot_s[4];
   __shared__ volatile int abort_s;
@@ -721,6 +733,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dkv_tc_kernel(Sparse
 
   if (tid == 0) {
     mbar_init(&kv_full, 1);
+    mbar_init(&all_done, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&qdo_full[s], 1);
       mbar_init(&sdp_full[s], 1);
@@ -730,7 +743,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dkv_tc_kernel(Sparse
     mbar_init_fence();
     abort_s = 0;
   }
-  if (warp == 4) tmem_alloc(&tmem_base_s, 512);
+  if (warp == 8) tmem_alloc(&tmem_base_s, 512);
   // ---- query blocks that selected this chunk, ascending ----------------------------------------
   {
     const int per = (nblk + 127) / 128;
@@ -761,7 +774,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dkv_tc_kernel(Sparse
   const uint32_t tmem = tmem_base_s;
   const uint32_t tdK = tmem + 256, tdV = tmem + 256 + D;
 
-  if (warp == 5) {
+  if (warp == 9) {
     if (lane == 0 && m > 0) {
       mbar_expect_tx(&kv_full, 2 * KVBYTES);
 #pragma unroll
@@ -782,7 +795,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dkv_tc_kernel(Sparse
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     if (lane == 0 && m > 0) {
       constexpr uint32_t idesc_s = idesc_bf16(128, 64, 0);
       constexpr uint32_t idesc_dkv = idesc_bf16(64, D, 1, 1);
@@ -825,15 +838,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dkv_tc_kernel(Sparse
         }
         mma_commit(&dkv_done[s]);
       }
+      if (ok) mma_commit(&all_done);  // epilogue barrier for both row warpgroups (see the dq kernel)
       if (!ok) { abort_s = 1; atomicExch(&g_device_status, 302); }
     }
   } else {
-    const int r = tid, ql = r / G, g = r % G, hq = h * G + g;
+    // two row warpgroups alternate over the query blocks (warpgroup w takes blocks w, w+2, ...)
+    const int r = tid & 127, wg = tid >> 7, ql = r / G, g = r % G, hq = h * G + g;
     const float scale_log2 = p.scale * kLog2e;
     const float slope = p.slope ? p.slope[hq] : 0.f;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
-    for (int j = 0; j < m; ++j) {
+    for (int j = wg; j < m; j += 2) {
       const int s = j & 1, u = j >> 1, sb = j % NDS;
       const int blk = list_s[j];
       const int t = blk * QB + ql;
@@ -884,7 +899,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dkv_tc_kernel(Sparse
       mbar_arrive(&dsp_full[s]);
     }
     if (ok && m > 0) {
-      ok = mbar_wait(&dkv_done[(m - 1) & 1], ((m - 1) >> 1) & 1);
+      ok = mbar_wait(&all_done, 0);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok && lane == 0) { abort_s = 1; atomicExch(&g_device_status, 303); }
     } else if (!ok && lane == 0) {
@@ -892,13 +907,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dkv_tc_kernel(Sparse
       atomicExch(&g_device_status, 304);
     }
     // M = 64 accumulators: key row 16*warp + lane lives in TMEM lane 32*warp + lane, lanes 0..15 of each warp
-    const int krow = 16 * warp + lane;
+    const int krow = 16 * (warp & 3) + lane;
     const int64_t tok = (int64_t)b * p.T + (int64_t)c * 64 + krow;
     bf16* dkrow = static_cast<bf16*>(p.d_k_out) + (tok * p.h_kv + h) * D;
     bf16* dvrow = static_cast<bf16*>(p.d_v_out) + (tok * p.h_kv + h) * D;
     if (ok) tc_fence_after();
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
+    {
+      const int which = wg;  // warpgroup 0 writes dK, warpgroup 1 writes dV
 #pragma unroll
       for (int cb = 0; cb < D / 32; ++cb) {
         float ov[32];
@@ -924,7 +939,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_bwd_dkv_tc_kernel(Sparse
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, 512);
+  if (warp == 8) tmem_dealloc(tmem, 512);
 }
 
 static bool tc_shape_ok(const SparseParams& p) {
@@ -984,13 +999,13 @@ int sparse_bwd_tc_launch(const SparseParams& p, void* d_k, void* d_v, void* work
   if (D == 64) {
     cudaFuncSetAttribute(sparse_bwd_dq_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq);
     cudaFuncSetAttribute(sparse_bwd_dkv_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dkv);
-    sparse_bwd_dq_tc_kernel<64><<<grid_q, kTcThreads, smem_dq, st>>>(pp, ws, tmK, tmV);
-    sparse_bwd_dkv_tc_kernel<64><<<grid_c, kTcThreads, smem_dkv, st>>>(pp, ws, nblk, tmK, tmV, tmQ, tmdO);
+    sparse_bwd_dq_tc_kernel<64><<<grid_q, kBwdThreads, smem_dq, st>>>(pp, ws, tmK, tmV);
+    sparse_bwd_dkv_tc_kernel<64><<<grid_c, kBwdThreads, smem_dkv, st>>>(pp, ws, nblk, tmK, tmV, tmQ, tmdO);
   } else {
     cudaFuncSetAttribute(sparse_bwd_dq_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq);
     cudaFuncSetAttribute(sparse_bwd_dkv_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dkv);
-    sparse_bwd_dq_tc_kernel<128><<<grid_q, kTcThreads, smem_dq, st>>>(pp, ws, tmK, tmV);
-    sparse_bwd_dkv_tc_kernel<128><<<grid_c, kTcThreads, smem_dkv, st>>>(pp, ws, nblk, tmK, tmV, tmQ, tmdO);
+    sparse_bwd_dq_tc_kernel<128><<<grid_q, kBwdThreads, smem_dq, st>>>(pp, ws, tmK, tmV);
+    sparse_bwd_dkv_tc_kernel<128><<<grid_c, kBwdThreads, smem_dkv, st>>>(pp, ws, nblk, tmK, tmV, tmQ, tmdO);
   }
   HILS_LAUNCH_CHECK("sparse_attn_bwd (tensor-core path)");
   return HILS_OK;

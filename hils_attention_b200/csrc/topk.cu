@@ -29,7 +29,8 @@ struct TopkParams {
   float scale;
 };
 
-constexpr int TN = 64;  // candidates per tile
+constexpr int TN = 128;  // candidates per tile
+constexpr int CPT = TN / 16;  // candidates per thread in the score product
 
 __device__ __forceinline__ uint32_t order_bits(float f) {
   uint32_t u = __float_as_uint(f + 0.0f);  // -0 -> +0
@@ -50,6 +51,67 @@ __device__ __forceinline__ int row_limit(const TopkParams& p, int l) {
   return max(0, min(lim, p.N));
 }
 
+typedef unsigned long long u64;
+
+__device__ __forceinline__ u64 shfl_xor64(u64 v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
+__device__ __forceinline__ u64 max64(u64 a, u64 b) { return a > b ? a : b; }
+__device__ __forceinline__ u64 min64(u64 a, u64 b) { return a > b ? b : a; }
+
+// Descending bitonic sort of 128 packed items held 4 per lane; item index = lane*4 + i.
+__device__ __forceinline__ void sort128_desc(u64 (&x)[4], int lane) {
+#pragma unroll
+  for (int k = 2; k <= 128; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      if (j >= 4) {
+        const int lj = j >> 2;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int idx = lane * 4 + i;
+          const u64 o = shfl_xor64(x[i], lj);
+          const bool keep_max = ((idx & k) == 0) == ((idx & j) == 0);
+          x[i] = keep_max ? max64(x[i], o) : min64(x[i], o);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if ((i & j) == 0) {
+            const int idx = lane * 4 + i;
+            const u64 a = x[i], c = x[i ^ j];
+            const bool first_max = ((idx & k) == 0);
+            x[i] = first_max ? max64(a, c) : min64(a, c);
+            x[i ^ j] = first_max ? min64(a, c) : max64(a, c);
+          }
+        }
+      }
+    }
+  }
+}
+
+// one item per lane, bitonic input (first descending then ascending or the reverse) -> descending
+__device__ __forceinline__ u64 merge32_desc(u64 v, int lane) {
+#pragma unroll
+  for (int j = 16; j > 0; j >>= 1) {
+    const u64 o = shfl_xor64(v, j);
+    v = ((lane & j) == 0) ? max64(v, o) : min64(v, o);
+  }
+  return v;
+}
+
+// ascending bitonic sort of one int per lane
+__device__ __forceinline__ int sort32_asc(int v, int lane) {
+#pragma unroll
+  for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      const int o = __shfl_xor_sync(0xffffffffu, v, j);
+      const bool keep_min = ((lane & k) == 0) == ((lane & j) == 0);
+      v = keep_min ? min(v, o) : max(v, o);
+    }
+  }
+  return v;
+}
+
 template <typename T, int KPL>
 __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
   extern __shared__ __align__(16) float smem[];
@@ -59,7 +121,8 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
   float* sc_s = kt_s + TN * RS;            // [M][TN]
   float* lse_s = sc_s + (size_t)M * TN;    // [M] running max, later lse_total
   float* sum_s = lse_s + M;                // [M] running sum
-  int* ids_s = reinterpret_cast<int*>(sum_s + M);  // [4][32*KPL]
+  float* bias_s = sum_s + M;               // [G][TN] bias + gumbel of the current tile
+  int* ids_s = reinterpret_cast<int*>(bias_s + G * TN);  // [4][32*KPL]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int l0 = blockIdx.x * RB, h = blockIdx.y, b = blockIdx.z;
   const T* q = static_cast<const T*>(p.q);
@@ -79,9 +142,21 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
   const int cta_limit = row_limit(p, last_row);  // limits are non-decreasing in l
   const int tx = tid & 15, ty = tid >> 4;
 
-  // scores of one 64-candidate tile into sc_s (selection logits v; -inf where not a candidate)
+  // selection logits v of one 128-candidate tile into sc_s (-inf where not a candidate)
   auto score_tile = [&](int c0) {
     const int ng = p.per_qhead ? G : 1;
+    __syncthreads();
+    if (p.bias || p.gumbel) {
+      for (int e = tid; e < G * TN; e += 128) {
+        const int gg = e / TN, c = c0 + (e - gg * TN);
+        float x = 0.f;
+        if (c < p.N) {
+          if (p.bias) x += p.bias[(((int64_t)b * p.N + c) * p.h_kv + h) * G + gg];
+          if (p.gumbel) x += p.gumbel[(int64_t)(h * G + gg) * p.N + c];
+        }
+        bias_s[e] = x;
+      }
+    }
     for (int g = 0; g < ng; ++g) {
       __syncthreads();
       for (int idx = tid * 4; idx < TN * D; idx += 128 * 4) {
@@ -97,14 +172,16 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
         const int i1 = i0 + 8;
         const int m0 = p.per_qhead ? i0 * G + g : i0;
         const int m1 = (i1 < nrow) ? (p.per_qhead ? i1 * G + g : i1) : m0;
-        float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+        float a0[CPT], a1[CPT];
+#pragma unroll
+        for (int jj = 0; jj < CPT; ++jj) { a0[jj] = 0.f; a1[jj] = 0.f; }
         const float* q0 = q_s + (size_t)m0 * D;
         const float* q1 = q_s + (size_t)m1 * D;
         for (int d = 0; d < D; d += 4) {
           float4 x0 = *reinterpret_cast<const float4*>(q0 + d);
           float4 x1 = *reinterpret_cast<const float4*>(q1 + d);
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
+          for (int jj = 0; jj < CPT; ++jj) {
             float4 kv = *reinterpret_cast<const float4*>(kt_s + (tx + 16 * jj) * RS + d);
             a0[jj] = fmaf(x0.x, kv.x, a0[jj]); a0[jj] = fmaf(x0.y, kv.y, a0[jj]);
             a0[jj] = fmaf(x0.z, kv.z, a0[jj]); a0[jj] = fmaf(x0.w, kv.w, a0[jj]);
@@ -119,13 +196,12 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
           const int l = l0 + m / G, gg = m % G;
           const int lim = row_limit(p, l);
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
+          for (int jj = 0; jj < CPT; ++jj) {
             const int c = c0 + tx + 16 * jj;
             float v = -CUDART_INF_F;
             if (c < lim) {
               v = (rr ? a1[jj] : a0[jj]) * p.scale;
-              if (p.bias) v += p.bias[(((int64_t)b * p.N + c) * p.h_kv + h) * G + gg];
-              if (p.gumbel) v += p.gumbel[(int64_t)(h * G + gg) * p.N + c];
+              if (p.bias || p.gumbel) v += bias_s[gg * TN + tx + 16 * jj];
             }
             sc_s[(size_t)m * TN + tx + 16 * jj] = v;
           }
@@ -141,12 +217,12 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
     for (int r = 0; r < RW; ++r) {
       for (int g = 0; g < G; ++g) {
         const int m = (warp * RW + r) * G + g;
-        float v0 = sc_s[(size_t)m * TN + lane], v1 = sc_s[(size_t)m * TN + lane + 32];
-        float tmax = warp_max(fmaxf(v0, v1));
+        const float4 v = *reinterpret_cast<const float4*>(sc_s + (size_t)m * TN + lane * 4);
+        float tmax = warp_max(fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
         float mo = lse_s[m];
         float mn = fmaxf(mo, tmax);
         if (mn > -CUDART_INF_F) {
-          float s = expf(v0 - mn) + expf(v1 - mn);
+          float s = expf(v.x - mn) + expf(v.y - mn) + expf(v.z - mn) + expf(v.w - mn);
           s = warp_sum(s);
           if (lane == 0) {
             sum_s[m] = sum_s[m] * ((mo > -CUDART_INF_F) ? expf(mo - mn) : 0.f) + s;
@@ -175,7 +251,10 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
   __syncthreads();
 
   // ---------------- pass 2: ranking keys and the running top-K -------------------------------
-  unsigned long long best[4][KPL];
+  // Items pack the order-preserving key bits above the inverted chunk id, so one unsigned compare
+  // means "greater key, then smaller id"; 0 marks "no candidate".  Item index inside a tile is
+  // lane*4 + i (a float4 of logits per lane).
+  u64 best[4][KPL];
 #pragma unroll
   for (int r = 0; r < 4; ++r)
 #pragma unroll
@@ -191,42 +270,68 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
       const int row = warp * RW + r;
       const int l = l0 + row;
       if (l >= p.L) continue;
+      float key[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+      for (int g = 0; g < G; ++g) {
+        const float4 v = *reinterpret_cast<const float4*>(sc_s + (size_t)(row * G + g) * TN + lane * 4);
+        const float lt = lse_s[row * G + g];
+        if (v.x > -CUDART_INF_F) key[0] = fmaxf(key[0], v.x - lt);
+        if (v.y > -CUDART_INF_F) key[1] = fmaxf(key[1], v.y - lt);
+        if (v.z > -CUDART_INF_F) key[2] = fmaxf(key[2], v.z - lt);
+        if (v.w > -CUDART_INF_F) key[3] = fmaxf(key[3], v.w - lt);
+      }
+      u64 item[4];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int c = c0 + lane + 32 * half;
-        float key = -CUDART_INF_F;
-        for (int g = 0; g < G; ++g) {
-          float v = sc_s[(size_t)(row * G + g) * TN + lane + 32 * half];
-          if (v > -CUDART_INF_F) key = fmaxf(key, v - lse_s[row * G + g]);
+      for (int i = 0; i < 4; ++i) {
+        const int c = c0 + lane * 4 + i;
+        if (p.drop_mask && c < p.N && p.drop_mask[((int64_t)b * p.L + l) * p.N + c] != 0) key[i] = -CUDART_INF_F;
+        if (p.rank_keys && c < p.N) p.rank_keys[(((int64_t)b * p.L + l) * p.h_kv + h) * p.N + c] = key[i];
+        const bool cand = key[i] > -CUDART_INF_F;  // false for NaN too
+        item[i] = cand ? (((u64)order_bits(key[i]) << 32) | (0xFFFFFFFFu - (uint32_t)c)) : 0ull;
+      }
+      if (KPL == 1) {
+        // sort the tile, keep its best 32, merge with the running (descending, one per lane) list
+        const u64 thr = __shfl_sync(0xffffffffu, best[r][0], thr_lane);
+        const bool any = item[0] > thr || item[1] > thr || item[2] > thr || item[3] > thr;
+        if (__any_sync(0xffffffffu, any)) {
+          sort128_desc(item, lane);
+          u64 top = 0ull;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const u64 t = __shfl_sync(0xffffffffu, item[i], lane >> 2);
+            if ((lane & 3) == i) top = t;
+          }
+          const u64 rev = __shfl_sync(0xffffffffu, top, 31 - lane);
+          best[r][0] = merge32_desc(max64(best[r][0], rev), lane);
         }
-        if (p.drop_mask && c < p.N && p.drop_mask[((int64_t)b * p.L + l) * p.N + c] != 0) key = -CUDART_INF_F;
-        if (p.rank_keys && c < p.N) p.rank_keys[(((int64_t)b * p.L + l) * p.h_kv + h) * p.N + c] = key;
-        const bool cand = key > -CUDART_INF_F;  // false for NaN too
-        unsigned long long item = cand ? (((unsigned long long)order_bits(key) << 32) | (0xFFFFFFFFu - (uint32_t)c)) : 0ull;
-        unsigned long long thr = 0ull;
+      } else {
+        // K > 32: insertion into a sorted list spread over the lanes, candidates filtered by a ballot
 #pragma unroll
-        for (int i = 0; i < KPL; ++i) {
-          unsigned long long t = __shfl_sync(0xffffffffu, best[r][i], thr_lane);
-          if (i == thr_i) thr = t;
-        }
-        unsigned mask = __ballot_sync(0xffffffffu, item > thr);
-        while (mask) {
-          const int src = __ffs(mask) - 1;
-          mask &= mask - 1;
-          const unsigned long long x = __shfl_sync(0xffffffffu, item, src);
-          if (x > thr) {
-            unsigned long long prev_last = __shfl_up_sync(0xffffffffu, best[r][KPL - 1], 1);
-            if (lane == 0) prev_last = ~0ull;
+        for (int i4 = 0; i4 < 4; ++i4) {
+          u64 thr = 0ull;
 #pragma unroll
-            for (int i = KPL - 1; i >= 0; --i) {
-              const unsigned long long prev = (i > 0) ? best[r][i - 1] : prev_last;
-              const unsigned long long cur = best[r][i];
-              best[r][i] = (cur > x) ? cur : ((prev > x) ? x : prev);
-            }
+          for (int i = 0; i < KPL; ++i) {
+            u64 t = __shfl_sync(0xffffffffu, best[r][i], thr_lane);
+            if (i == thr_i) thr = t;
+          }
+          unsigned mask = __ballot_sync(0xffffffffu, item[i4] > thr);
+          while (mask) {
+            const int src = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const u64 x = __shfl_sync(0xffffffffu, item[i4], src);
+            if (x > thr) {
+              u64 prev_last = __shfl_up_sync(0xffffffffu, best[r][KPL - 1], 1);
+              if (lane == 0) prev_last = ~0ull;
 #pragma unroll
-            for (int i = 0; i < KPL; ++i) {
-              unsigned long long t = __shfl_sync(0xffffffffu, best[r][i], thr_lane);
-              if (i == thr_i) thr = t;
+              for (int i = KPL - 1; i >= 0; --i) {
+                const u64 prev = (i > 0) ? best[r][i - 1] : prev_last;
+                const u64 cur = best[r][i];
+                best[r][i] = (cur > x) ? cur : ((prev > x) ? x : prev);
+              }
+#pragma unroll
+              for (int i = 0; i < KPL; ++i) {
+                u64 t = __shfl_sync(0xffffffffu, best[r][i], thr_lane);
+                if (i == thr_i) thr = t;
+              }
             }
           }
         }
@@ -243,49 +348,58 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
     const int row = warp * RW + r;
     const int l = l0 + row;
     if (l >= p.L) continue;  // warp-uniform
-    __syncwarp();
-#pragma unroll
-    for (int i = 0; i < KPL; ++i) {
-      const int pos = lane * KPL + i;
-      const unsigned long long it = best[r][i];
-      my_ids[pos] = (pos < K && it != 0ull) ? (int)(0xFFFFFFFFu - (uint32_t)(it & 0xFFFFFFFFull)) : 0x7fffffff;
-    }
-    __syncwarp();
     int32_t* out = p.indices + (((int64_t)b * p.L + l) * p.h_kv + h) * K;
-    int sorted[KPL];
+    __syncwarp();
+    if (KPL == 1) {
+      const u64 it = best[r][0];
+      int id = (lane < K && it != 0ull) ? (int)(0xFFFFFFFFu - (uint32_t)(it & 0xFFFFFFFFull)) : 0x7fffffff;
+      id = sort32_asc(id, lane);
+      if (id == 0x7fffffff) id = -1;
+      if (lane < K) out[lane] = id;
+      my_ids[lane] = id;
+    } else {
 #pragma unroll
-    for (int i = 0; i < KPL; ++i) {
-      const int pos = lane * KPL + i;
-      const int mine = my_ids[pos];
-      int rank = 0;
-      for (int j = 0; j < K; ++j) {
-        const int o = my_ids[j];
-        rank += (o < mine || (o == mine && j < pos)) ? 1 : 0;
+      for (int i = 0; i < KPL; ++i) {
+        const int pos = lane * KPL + i;
+        const u64 it = best[r][i];
+        my_ids[pos] = (pos < K && it != 0ull) ? (int)(0xFFFFFFFFu - (uint32_t)(it & 0xFFFFFFFFull)) : 0x7fffffff;
       }
-      sorted[i] = rank;
-    }
-    __syncwarp();
+      __syncwarp();
+      int sorted[KPL], mine[KPL];
 #pragma unroll
-    for (int i = 0; i < KPL; ++i) {
-      const int pos = lane * KPL + i;
-      const int mine = my_ids[pos];
-      if (pos < K) out[sorted[i]] = (mine == 0x7fffffff) ? -1 : mine;
+      for (int i = 0; i < KPL; ++i) {
+        const int pos = lane * KPL + i;
+        mine[i] = my_ids[pos];
+        int rank = 0;
+        for (int j = 0; j < K; ++j) {
+          const int o = my_ids[j];
+          rank += (o < mine[i] || (o == mine[i] && j < pos)) ? 1 : 0;
+        }
+        sorted[i] = rank;
+      }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < KPL; ++i) {
+        const int pos = lane * KPL + i;
+        if (pos < K) {
+          const int v = (mine[i] == 0x7fffffff) ? -1 : mine[i];
+          out[sorted[i]] = v;
+          my_ids[sorted[i]] = v;
+        }
+      }
     }
     __syncwarp();
-    // re-read the sorted ids (written by this warp) to form the scores
-    for (int kp = 0; kp < K; ++kp) {
-      const int id = out[kp];
+    // scores of the picked chunks: each lane forms the full dot product of its own chunk key
+    for (int kp = lane; kp < K; kp += 32) {
+      const int id = my_ids[kp];
       for (int g = 0; g < G; ++g) {
         float acc = 0.f;
         if (id >= 0) {
           const T* krow = lmks + (((int64_t)b * p.N + id) * HL + (p.per_qhead ? h * G + g : h)) * D;
-          const float* qr = q_s + (size_t)(row * G + g) * D;
-          for (int d = lane; d < D; d += 32) acc = fmaf(qr[d], to_f(krow[d]), acc);
-          acc = warp_sum(acc);
+          acc = dot_row(q_s + (size_t)(row * G + g) * D, krow, D);
         }
-        if (lane == 0)
-          scores[((((int64_t)b * p.L + l) * p.h_kv + h) * G + g) * K + kp] =
-              from_f<T>(id >= 0 ? acc * p.scale : -CUDART_INF_F);
+        scores[((((int64_t)b * p.L + l) * p.h_kv + h) * G + g) * K + kp] =
+            from_f<T>(id >= 0 ? acc * p.scale : -CUDART_INF_F);
       }
     }
   }
@@ -337,7 +451,8 @@ static int launch_topk(const TopkParams& p, cudaStream_t st) {
   int RW = 4;
   for (; RW >= 1; RW >>= 1) {
     int M = 4 * RW * p.G;
-    smem = ((size_t)M * p.D + (size_t)TN * (p.D + 4) + (size_t)M * TN + 2 * (size_t)M) * sizeof(float) +
+    smem = ((size_t)M * p.D + (size_t)TN * (p.D + 4) + (size_t)M * TN + 2 * (size_t)M + (size_t)p.G * TN) *
+               sizeof(float) +
            4 * 32 * KPL * sizeof(int);
     if (smem <= 200 * 1024) break;
   }
