@@ -91,12 +91,11 @@ int make_tmap_bf16_thd(CUtensorMap* map, const void* base, uint64_t tokens, uint
 
 using namespace umma;
 
-constexpr int kTcThreads = 192;
 constexpr int kBwdThreads = 320;  // 2 row warpgroups + MMA warp + TMA warp
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D>
-__global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tmK,
+__global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tmK,
                                                                    const __grid_constant__ CUtensorMap tmV) {
   constexpr int DB = D / 64;             // 64-wide column blocks of a [rows x D] tile
   constexpr int QBYTES = DB * 16384;     // Q tile 128 x D
@@ -114,7 +113,7 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
   const int umax = min(nchunk, QB * p.K);
   uint32_t* bitmap_s = reinterpret_cast<uint32_t*>(union_s + umax);
 
-  __shared__ uint64_t kv_full[2], s_full[2], p_full[2], pv_done[2];
+  __shared__ uint64_t kv_full[2], s_full[2], p_full[2], pv_done[2], all_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int n_union_s, warp_tot_s[4];
   __shared__ volatile int abort_s;
@@ -130,24 +129,26 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
       mbar_init(&p_full[s], 128);
       mbar_init(&pv_done[s], 1);
     }
+    mbar_init(&all_done, 1);
     mbar_init_fence();
     abort_s = 0;
   }
-  if (warp == 4) tmem_alloc(&tmem_base_s, 256);
-  for (int w = tid; w < nwords; w += kTcThreads) bitmap_s[w] = 0u;
+  if (warp == 8) tmem_alloc(&tmem_base_s, 256);
+  for (int w = tid; w < nwords; w += kBwdThreads) bitmap_s[w] = 0u;
   __syncthreads();
 
   // ---- per-row setup: Q row into shared memory, chunk ids into the bitmap -----------------------
-  const int r = tid;                       // row of the tile (softmax threads only)
+  // two row warpgroups (threads 0..127, 128..255) each own all 128 rows and alternate over the union
+  const int r = tid & 127, wg = tid >> 7;
   const int ql = r / G, g = r % G, t = q0 + ql;
-  const bool is_row = tid < 128;
+  const bool is_row = tid < 256, is_loader = tid < 128;
   const bool valid = is_row && t < p.L;
   const int hq = h * G + g;
   const int32_t* ids = p.idx + (((int64_t)b * p.L + (valid ? t : 0)) * p.h_kv + h) * p.K;
   const bf16* wrow = static_cast<const bf16*>(p.w) + (((int64_t)b * p.L + (valid ? t : 0)) * p.h_q + hq) * p.num_weights;
   int nvalid = 0;
   int my_unsorted = 0;
-  if (is_row) {
+  if (is_loader) {
     const bf16* qrow = static_cast<const bf16*>(p.q) + (((int64_t)b * p.L + (valid ? t : 0)) * p.h_q + hq) * D;
 #pragma unroll
     for (int c = 0; c < D / 8; ++c) {
@@ -155,16 +156,16 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
       if (valid) x = *reinterpret_cast<const uint4*>(qrow + c * 8);
       *reinterpret_cast<uint4*>(Qs + (c >> 3) * 16384 + sw128_off(r, c & 7)) = x;
     }
-    if (valid) {
-      int prev = -1;
-      for (int k = 0; k < p.K; ++k) {
-        const int id = __ldg(ids + k);
-        if (id < 0) break;
-        ++nvalid;
-        if (id < prev) my_unsorted = 1;
-        prev = id;
-        if (g == 0 && id < nchunk) atomicOr(&bitmap_s[id >> 5], 1u << (id & 31));
-      }
+  }
+  if (valid) {
+    int prev = -1;
+    for (int k = 0; k < p.K; ++k) {
+      const int id = __ldg(ids + k);
+      if (id < 0) break;
+      ++nvalid;
+      if (id < prev) my_unsorted = 1;
+      prev = id;
+      if (is_loader && g == 0 && id < nchunk) atomicOr(&bitmap_s[id >> 5], 1u << (id & 31));
     }
   }
   const int unsorted = __syncthreads_or(my_unsorted);
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
   {
     const int wpt = (nwords + 127) / 128;
     int cnt = 0;
-    if (is_row)
+    if (is_loader)
       for (int w = tid * wpt; w < min(nwords, (tid + 1) * wpt); ++w) cnt += __popc(bitmap_s[w]);
     int inc = cnt;
 #pragma unroll
@@ -181,9 +182,9 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
       int n = __shfl_up_sync(0xffffffffu, inc, o);
       if (lane >= o) inc += n;
     }
-    if (is_row && lane == 31) warp_tot_s[warp] = inc;
+    if (is_loader && lane == 31) warp_tot_s[warp] = inc;
     __syncthreads();
-    if (is_row) {
+    if (is_loader) {
       int base = inc - cnt;
       for (int w = 0; w < warp; ++w) base += warp_tot_s[w];
       for (int w = tid * wpt; w < min(nwords, (tid + 1) * wpt); ++w) {
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
   const uint32_t tmem = tmem_base_s;
   const uint32_t tS = tmem, tO = tmem + 128;
 
-  if (warp == 5) {
+  if (warp == 9) {
     // =============================== TMA producer ===============================================
     if (lane == 0) {
       for (int i = 0; i < n; ++i) {
@@ -222,7 +223,7 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     // =============================== MMA issuer =================================================
     if (lane == 0 && n > 0) {
       constexpr uint32_t idesc_qk = idesc_bf16(128, 64, 0);
@@ -263,6 +264,7 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
         }
         mma_commit(&pv_done[s]);
       }
+      if (ok) mma_commit(&all_done);  // epilogue barrier for both row warpgroups
       if (!ok) { abort_s = 1; atomicExch(&g_device_status, 102); }
     }
   } else {
@@ -271,14 +273,18 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
     const float slope = p.slope ? p.slope[hq] : 0.f;
     int ptr = 0;
     int cur = (nvalid > 0) ? __ldg(ids) : 0x7fffffff;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
-    for (int i = 0; i < n; ++i) {
+    for (int i = wg; i < n; i += 2) {
       const int s = i & 1, u = i >> 1;
       const int c = union_s[i];
       float wsum = 0.f;
       bool owner = false;
       if (!unsorted) {
+        while (cur < c) {  // ids belonging to the other warpgroup's entries
+          ++ptr;
+          cur = (ptr < nvalid) ? __ldg(ids + ptr) : 0x7fffffff;
+        }
         while (cur == c) {
           owner = true;
           wsum += to_f(wrow[ptr]);
@@ -333,7 +339,7 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
     }
     // ---- epilogue: O row -> bf16 -> global ---------------------------------------------------------
     if (ok && n > 0) {
-      ok = mbar_wait(&pv_done[(n - 1) & 1], ((n - 1) >> 1) & 1);
+      ok = mbar_wait(&all_done, 0);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok && lane == 0) { abort_s = 1; atomicExch(&g_device_status, 103); }
     } else if (!ok && lane == 0) {
@@ -343,7 +349,7 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
     bf16* orow = static_cast<bf16*>(p.o) + (((int64_t)b * p.L + (valid ? t : 0)) * p.h_q + hq) * D;
     if (ok) tc_fence_after();
 #pragma unroll
-    for (int cb = 0; cb < D / 32; ++cb) {
+    for (int cb = wg; cb < D / 32; cb += 2) {  // each warpgroup stores half of the columns
       float ov[32];
       if (ok && n > 0) {
         tmem_ld32(tO + lane_base + cb * 32, ov);
@@ -365,7 +371,7 @@ __global__ void __launch_bounds__(kTcThreads) sparse_fwd_tc_kernel(SparseParams 
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, 256);
+  if (warp == 8) tmem_dealloc(tmem, 256);
 }
 
 
@@ -1031,10 +1037,10 @@ int sparse_fwd_tc_launch(const SparseParams& p, cudaStream_t st) {
   dim3 grid(ceil_div(p.L, QB), p.h_kv, p.B);
   if (D == 64) {
     cudaFuncSetAttribute(sparse_fwd_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sparse_fwd_tc_kernel<64><<<grid, kTcThreads, smem, st>>>(p, tmK, tmV);
+    sparse_fwd_tc_kernel<64><<<grid, kBwdThreads, smem, st>>>(p, tmK, tmV);
   } else {
     cudaFuncSetAttribute(sparse_fwd_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sparse_fwd_tc_kernel<128><<<grid, kTcThreads, smem, st>>>(p, tmK, tmV);
+    sparse_fwd_tc_kernel<128><<<grid, kBwdThreads, smem, st>>>(p, tmK, tmV);
   }
   HILS_LAUNCH_CHECK("sparse_attn_fwd (tensor-core path)");
   return HILS_OK;

@@ -436,12 +436,17 @@ __global__ void __launch_bounds__(128) topk_bwd_kernel(
       float4 kv = load4(lmks + off);
       acc.x = fmaf(s, kv.x, acc.x); acc.y = fmaf(s, kv.y, acc.y);
       acc.z = fmaf(s, kv.z, acc.z); acc.w = fmaf(s, kv.w, acc.w);
-      atomicAdd(dl + off + 0, s * qv.x); atomicAdd(dl + off + 1, s * qv.y);
-      atomicAdd(dl + off + 2, s * qv.z); atomicAdd(dl + off + 3, s * qv.w);
+      if (dl) {
+        atomicAdd(dl + off + 0, s * qv.x); atomicAdd(dl + off + 1, s * qv.y);
+        atomicAdd(dl + off + 2, s * qv.z); atomicAdd(dl + off + 3, s * qv.w);
+      }
     }
     store4(dq + row * D + d0, acc);
   }
 }
+
+int topk_bwd_dk_tc_launch(const void* d_scores, const int32_t* indices, const void* q, void* d_lmks, int B, int L, int N,
+                          int h_kv, int G, int D, int topk, int per_qhead, float scale, cudaStream_t st);  // topk_tc.cu
 
 template <typename T, int KPL>
 static int launch_topk(const TopkParams& p, cudaStream_t st) {
@@ -515,6 +520,20 @@ extern "C" int hils_topk_bwd(const void* d_scores, const int32_t* indices, const
   cudaStream_t st = (cudaStream_t)stream;
   const int HL = per_qhead ? h_kv * G : h_kv;
   const int64_t nl = (int64_t)B * N * HL * D;
+  if (dtype == HILS_BF16 && nl > 0 && L > 0) {
+    // tensor-core path: chunk-key gradient without atomics or an fp32 accumulator, then the K-sparse gather for dq
+    HILS_REQUIRE(d_scores && indices && q && lmks && d_q && d_lmks, "topk_bwd: null pointer");
+    const int rc = topk_bwd_dk_tc_launch(d_scores, indices, q, d_lmks, B, L, N, h_kv, G, D, topk, per_qhead, sm_scale, st);
+    if (rc == HILS_OK) {
+      const int64_t rows = (int64_t)B * L * h_kv * G;
+      topk_bwd_kernel<bf16><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>((const bf16*)d_scores, indices, (const bf16*)q,
+                                                                       (const bf16*)lmks, (bf16*)d_q, nullptr, L, N, h_kv,
+                                                                       G, D, topk, per_qhead, sm_scale, rows);
+      HILS_LAUNCH_CHECK("topk_bwd dq");
+      return HILS_OK;
+    }
+    if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  }
   if (nl > 0) {
     HILS_REQUIRE(d_lmks_f32 && d_lmks, "topk_bwd: null chunk-key gradient buffers");
     cudaError_t e = cudaMemsetAsync(d_lmks_f32, 0, nl * sizeof(float), st);

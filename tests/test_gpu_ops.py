@@ -350,3 +350,40 @@ def test_naive_bsa_identity_on_gpu(ops, tag):
                                 is_training=False, dtype="float")
     o = torch.addcmul(o_h, swa_o, w[..., -1:])
     check(o, g["o"], F32, "naive bsa", scale=2.0)
+
+
+@pytest.mark.parametrize("cfg", [
+    # B, L, h_kv, G, D, K, per_qhead
+    (2, 500, 2, 1, 64, 8, False),
+    (1, 384, 2, 4, 64, 4, False),     # shared keys, GQA: gradients of the group add up
+    (1, 300, 1, 2, 128, 8, True),     # per-q-head keys
+    (1, 1024, 1, 1, 64, 32, False),
+])
+def test_topk_backward_bf16_tensor_core_path(ops, cfg):
+    """bf16 gradients of the returned scores (tensor-core chunk-key gradient, K-sparse gather for
+    dq) against autograd through scale * <q, k'[id]> on the same ids."""
+    B, L, h_kv, G, D, K, per_q = cfg
+    S, W = 64, 64
+    N = L // S
+    g = torch.Generator().manual_seed(17)
+    q0 = torch.randn(B, L, h_kv * G, D, generator=g).to(BF)
+    lm0 = torch.randn(B, N, h_kv * G if per_q else h_kv, D, generator=g).to(BF)
+    lse = torch.randn(B, L, h_kv * G, generator=g)
+    gs = torch.randn(B, L, h_kv * G, K, generator=g).to(BF)
+    q, lm = q0.cuda().requires_grad_(True), lm0.cuda().requires_grad_(True)
+    idx, sc = ops.online_softmax_topk_head(q, lm, lse.cuda(), K, S, W, G=(G if per_q else 1))
+    valid = (idx >= 0).repeat_interleave(G, dim=2)
+    (sc.float().masked_fill(~valid, 0.0) * gs.cuda().float()).sum().backward()
+    from hils_attention_b200 import _lib
+    assert _lib.load().hils_take_device_status() == 0
+    ridx = idx.cpu().long().clamp_min(0)
+    qr, lr = q0.float().requires_grad_(True), lm0.float().requires_grad_(True)
+    lmv = lr.view(B, N, h_kv, G if per_q else 1, D)
+    bi = torch.arange(B).view(B, 1, 1, 1)
+    hi = torch.arange(h_kv).view(1, 1, h_kv, 1)
+    sel = lmv[bi, ridx, hi]                                         # (B,L,h_kv,K,Gk,D)
+    qv = qr.view(B, L, h_kv, G, D)
+    s = torch.einsum("blhgd,blhkgd->blhgk", qv, sel.expand(-1, -1, -1, -1, G, -1)) / math.sqrt(D)
+    (s.reshape(B, L, h_kv * G, K).masked_fill(~valid.cpu(), 0.0) * gs.float()).sum().backward()
+    check(q.grad, qr.grad, BF, "dq", scale=float(qr.grad.abs().max()))
+    check(lm.grad, lr.grad, BF, "dlmk", scale=float(lr.grad.abs().max()))
