@@ -92,6 +92,7 @@ int make_tmap_bf16_thd(CUtensorMap* map, const void* base, uint64_t tokens, uint
 using namespace umma;
 
 constexpr int kBwdThreads = 320;  // 2 row warpgroups + MMA warp + TMA warp
+constexpr int kFwdStages = 3;     // K/V ring depth of the forward kernel
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D>
@@ -100,12 +101,13 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
   constexpr int DB = D / 64;             // 64-wide column blocks of a [rows x D] tile
   constexpr int QBYTES = DB * 16384;     // Q tile 128 x D
   constexpr int KVBYTES = DB * 8192;     // K or V tile 64 x D
+  constexpr int NST = kFwdStages;        // K/V ring depth (loads run ahead of the MMAs)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* Qs = smem;
-  uint8_t* Ks = Qs + QBYTES;             // 2 stages
-  uint8_t* Vs = Ks + 2 * KVBYTES;        // 2 stages
-  uint8_t* Ps = Vs + 2 * KVBYTES;        // 2 x [128 x 64] bf16
+  uint8_t* Ks = Qs + QBYTES;             // NST stages
+  uint8_t* Vs = Ks + NST * KVBYTES;      // NST stages
+  uint8_t* Ps = Vs + NST * KVBYTES;        // 2 x [128 x 64] bf16
   int* union_s = reinterpret_cast<int*>(Ps + 2 * 16384);
   const int nchunk = p.T / 64;
   const int nwords = (nchunk + 31) >> 5;
@@ -113,7 +115,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
   const int umax = min(nchunk, QB * p.K);
   uint32_t* bitmap_s = reinterpret_cast<uint32_t*>(union_s + umax);
 
-  __shared__ uint64_t kv_full[2], s_full[2], p_full[2], pv_done[2], all_done;
+  __shared__ uint64_t kv_full[4], kv_free[4], s_full[2], p_full[2], pv_done[2], all_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int n_union_s, warp_tot_s[4];
   __shared__ volatile int abort_s;
@@ -124,10 +126,13 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
 
   if (tid == 0) {
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], 128);
       mbar_init(&pv_done[s], 1);
+    }
+    for (int st = 0; st < NST; ++st) {
+      mbar_init(&kv_full[st], 1);
+      mbar_init(&kv_free[st], 1);
     }
     mbar_init(&all_done, 1);
     mbar_init_fence();
@@ -211,9 +216,9 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
     // =============================== TMA producer ===============================================
     if (lane == 0) {
       for (int i = 0; i < n; ++i) {
-        const int s = i & 1, u = i >> 1;
+        const int s = i % NST;
         if (abort_s) break;
-        if (i >= 2 && !mbar_wait(&pv_done[s], (u - 1) & 1)) { abort_s = 1; atomicExch(&g_device_status, 101); break; }
+        if (i >= NST && !mbar_wait(&kv_free[s], ((i / NST) - 1) & 1)) { abort_s = 1; atomicExch(&g_device_status, 101); break; }
         const int c = union_s[i];
         mbar_expect_tx(&kv_full[s], 2 * KVBYTES);
 #pragma unroll
@@ -234,7 +239,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint64_t da = desc_sw128(q_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
-          const uint64_t db = desc_sw128(k_addr + s * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024);
+          const uint64_t db = desc_sw128(k_addr + (i % NST) * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024);
           mma_ss(tS + s * 64, da, db, idesc_qk, kk > 0);
         }
         mma_commit(&s_full[s]);
@@ -248,7 +253,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
         const int s = i & 1, u = i >> 1;
         if (abort_s) break;
         if (i + 1 < n) {
-          ok = mbar_wait(&kv_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
+          ok = mbar_wait(&kv_full[(i + 1) % NST], ((i + 1) / NST) & 1);
           if (!ok) break;
           tc_fence_after();
           issue_qk(i + 1);
@@ -259,10 +264,11 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const uint64_t da = desc_sw128(p_addr + s * 16384 + kk * 32, 16, 1024);
-          const uint64_t db = desc_sw128(v_addr + s * KVBYTES + kk * 2048, 8192, 1024);
+          const uint64_t db = desc_sw128(v_addr + (i % NST) * KVBYTES + kk * 2048, 8192, 1024);
           mma_ss(tO, da, db, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
         }
         mma_commit(&pv_done[s]);
+        mma_commit(&kv_free[i % NST]);
       }
       if (ok) mma_commit(&all_done);  // epilogue barrier for both row warpgroups
       if (!ok) { abort_s = 1; atomicExch(&g_device_status, 102); }
@@ -272,7 +278,8 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
     const float scale_log2 = p.scale * kLog2e;
     const float slope = p.slope ? p.slope[hq] : 0.f;
     int ptr = 0;
-    int cur = (nvalid > 0) ? __ldg(ids) : 0x7fffffff;
+    int cur = (nvalid > 0) ? __ldg(ids) : 0x7fffffff;       // next unconsumed id and its weight are held
+    float cur_w = (nvalid > 0) ? to_f(wrow[0]) : 0.f;       // one step ahead, so their loads are not waited on
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
     for (int i = wg; i < n; i += 2) {
@@ -284,12 +291,14 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
         while (cur < c) {  // ids belonging to the other warpgroup's entries
           ++ptr;
           cur = (ptr < nvalid) ? __ldg(ids + ptr) : 0x7fffffff;
+          cur_w = (ptr < nvalid) ? to_f(wrow[ptr]) : 0.f;
         }
         while (cur == c) {
           owner = true;
-          wsum += to_f(wrow[ptr]);
+          wsum += cur_w;
           ++ptr;
           cur = (ptr < nvalid) ? __ldg(ids + ptr) : 0x7fffffff;
+          cur_w = (ptr < nvalid) ? to_f(wrow[ptr]) : 0.f;
         }
       } else {
         for (int k = 0; k < nvalid; ++k)
@@ -311,16 +320,18 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
           for (int j = 0; j < 62; ++j) sv[j] -= slope * (float)(62 - j);
         }
         if (p.mask_last) sv[63] = -CUDART_INF_F;
-        float m = sv[0];
+        float m4[4] = {sv[0], sv[1], sv[2], sv[3]};   // interleaved partial reductions (short chains)
 #pragma unroll
-        for (int j = 1; j < 64; ++j) m = fmaxf(m, sv[j]);
+        for (int j = 4; j < 64; ++j) m4[j & 3] = fmaxf(m4[j & 3], sv[j]);
+        const float m = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         const float mb = m * scale_log2;
-        float sum = 0.f;
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
           sv[j] = ex2(fmaf(sv[j], scale_log2, -mb));
-          sum += sv[j];
+          s4[j & 3] += sv[j];
         }
+        const float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
         const float f = wsum / sum;
 #pragma unroll
         for (int c8 = 0; c8 < 8; ++c8) {
@@ -394,23 +405,28 @@ __device__ __forceinline__ float bwd_row(float* sv, float* dp, float wsum, float
     for (int j = 0; j < 62; ++j) sv[j] -= slope * (float)(62 - j);
   }
   if (mask_last) sv[63] = -CUDART_INF_F;
-  float m = sv[0];
+  // reductions use four interleaved partial accumulators: a single dependent chain of 64 operations
+  // would leave the thread waiting on arithmetic latency most of the time
+  float m4[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-  for (int j = 1; j < 64; ++j) m = fmaxf(m, sv[j]);
+  for (int j = 4; j < 64; ++j) m4[j & 3] = fmaxf(m4[j & 3], sv[j]);
+  const float m = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
   const float mb = m * scale_log2;
-  float sum = 0.f;
+  float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int j = 0; j < 64; ++j) {
     sv[j] = ex2(fmaf(sv[j], scale_log2, -mb));
-    sum += sv[j];
+    s4[j & 3] += sv[j];
   }
+  const float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
   const float inv = 1.f / sum;
-  float dw = 0.f;
+  float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int j = 0; j < 64; ++j) {
     sv[j] *= inv;
-    dw = fmaf(sv[j], dp[j], dw);
+    d4[j & 3] = fmaf(sv[j], dp[j], d4[j & 3]);
   }
+  const float dw = (d4[0] + d4[1]) + (d4[2] + d4[3]);
   const float sw = scale * wsum;
 #pragma unroll
   for (int j = 0; j < 64; ++j) {
@@ -422,9 +438,12 @@ __device__ __forceinline__ float bwd_row(float* sv, float* dp, float wsum, float
 }
 
 struct BwdWs {
-  uint32_t* bitmap;  // [B*h_kv][nblk][nwords]
-  int* flags;        // [B*h_kv][nblk]  1 = some row of the block has a non-ascending id list
+  uint32_t* bitmap;  // [B*h_kv][nblk][nwords]  union bitmap of each query block
+  uint16_t* wtab;    // [B*h_kv][nblk][umax][128]  bf16 weight of (block, union entry, row); kNotOwner when the
+                     // row did not select that chunk.  Written by the dq pass, read by the dkv pass.
+  int umax;
 };
+constexpr uint16_t kNotOwner = 0x7FC1;  // a bf16 NaN pattern
 
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(SparseParams p, BwdWs ws,
@@ -433,13 +452,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
   constexpr int DB = D / 64;
   constexpr int QBYTES = DB * 16384;
   constexpr int KVBYTES = DB * 8192;
+  constexpr int NST = (D == 64) ? 4 : 3;  // K/V ring depth
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* Qs = smem;
   uint8_t* dOs = Qs + QBYTES;
-  uint8_t* Ks = dOs + QBYTES;            // 2 stages
-  uint8_t* Vs = Ks + 2 * KVBYTES;        // 2 stages
-  uint8_t* dSs = Vs + 2 * KVBYTES;       // 2 x [128 x 64] bf16
+  uint8_t* Ks = dOs + QBYTES;            // NST stages
+  uint8_t* Vs = Ks + NST * KVBYTES;      // NST stages
+  uint8_t* dSs = Vs + NST * KVBYTES;       // 2 x [128 x 64] bf16
   int* union_s = reinterpret_cast<int*>(dSs + 2 * 16384);
   const int nchunk = p.T / 64;
   const int nwords = (nchunk + 31) >> 5;
@@ -447,7 +467,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
   const int umax = min(nchunk, QB * p.K);
   uint32_t* bitmap_s = reinterpret_cast<uint32_t*>(union_s + umax);
 
-  __shared__ uint64_t kv_full[2], sdp_full[2], ds_full[2], dq_done[2], all_done;
+  __shared__ uint64_t kv_full[4], kv_free[4], sdp_full[2], ds_full[2], dq_done[2], all_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int n_union_s, warp_tot_s[4];
   __shared__ volatile int abort_s;
@@ -459,10 +479,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
 
   if (tid == 0) {
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1);
       mbar_init(&sdp_full[s], 1);
       mbar_init(&ds_full[s], 128);
       mbar_init(&dq_done[s], 1);
+    }
+    for (int st = 0; st < NST; ++st) {
+      mbar_init(&kv_full[st], 1);
+      mbar_init(&kv_free[st], 1);
     }
     mbar_init(&all_done, 1);
     mbar_init_fence();
@@ -515,7 +538,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
   {
     const int64_t bh = (int64_t)b * p.h_kv + h;
     for (int w = tid; w < nwords; w += kBwdThreads) ws.bitmap[(bh * nblk + blk) * nwords + w] = bitmap_s[w];
-    if (tid == 0) ws.flags[bh * nblk + blk] = unsorted;
     const int wpt = (nwords + 127) / 128;
     int cnt = 0;
     if (is_loader)
@@ -554,9 +576,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
   if (warp == 9) {
     if (lane == 0) {
       for (int i = 0; i < n; ++i) {
-        const int s = i & 1, u = i >> 1;
+        const int s = i % NST;
         if (abort_s) break;
-        if (i >= 2 && !mbar_wait(&dq_done[s], (u - 1) & 1)) { abort_s = 1; atomicExch(&g_device_status, 201); break; }
+        if (i >= NST && !mbar_wait(&kv_free[s], ((i / NST) - 1) & 1)) { abort_s = 1; atomicExch(&g_device_status, 201); break; }
         const int c = union_s[i];
         mbar_expect_tx(&kv_full[s], 2 * KVBYTES);
 #pragma unroll
@@ -576,12 +598,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
         const int s = i & 1;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = s * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32;
+          const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = (i % NST) * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32;
           mma_ss(tmem + s * 128, desc_sw128(q_addr + ao, 16, 1024), desc_sw128(k_addr + bo, 16, 1024), idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = s * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32;
+          const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = (i % NST) * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32;
           mma_ss(tmem + s * 128 + 64, desc_sw128(do_addr + ao, 16, 1024), desc_sw128(v_addr + bo, 16, 1024), idesc_s, kk > 0);
         }
         mma_commit(&sdp_full[s]);
@@ -592,7 +614,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
         const int s = i & 1, u = i >> 1;
         if (abort_s) break;
         if (i + 1 < n) {
-          ok = mbar_wait(&kv_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
+          ok = mbar_wait(&kv_full[(i + 1) % NST], ((i + 1) / NST) & 1);
           if (!ok) break;
           tc_fence_after();
           issue_sdp(i + 1);
@@ -603,8 +625,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           mma_ss(tdQ, desc_sw128(ds_addr + s * 16384 + kk * 32, 16, 1024),
-                 desc_sw128(k_addr + s * KVBYTES + kk * 2048, 8192, 1024), idesc_dq, (i > 0 || kk > 0) ? 1u : 0u);
+                 desc_sw128(k_addr + (i % NST) * KVBYTES + kk * 2048, 8192, 1024), idesc_dq, (i > 0 || kk > 0) ? 1u : 0u);
         mma_commit(&dq_done[s]);
+        mma_commit(&kv_free[i % NST]);
       }
       // both row warpgroups wait on this for the epilogue: a parity wait on a stage barrier could be
       // satisfied by an older phase for the warpgroup that did not take the last entry
@@ -615,7 +638,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
     const float scale_log2 = p.scale * kLog2e;
     const float slope = p.slope ? p.slope[hq] : 0.f;
     int ptr = 0;
-    int cur = (nvalid > 0) ? __ldg(ids) : 0x7fffffff;
+    int cur = (nvalid > 0) ? __ldg(ids) : 0x7fffffff;       // next unconsumed id and its weight are held
+    float cur_w = (nvalid > 0) ? to_f(wrow[0]) : 0.f;       // one step ahead, so their loads are not waited on
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
     for (int i = wg; i < n; i += 2) {
@@ -628,18 +652,25 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
         while (cur < c) {  // ids consumed by the other warpgroup's entries
           ++ptr;
           cur = (ptr < nvalid) ? __ldg(ids + ptr) : 0x7fffffff;
+          cur_w = (ptr < nvalid) ? to_f(wrow[ptr]) : 0.f;
         }
         k_first = ptr;
         while (cur == c) {
           owner = true;
-          wsum += to_f(wrow[ptr]);
+          wsum += cur_w;
           ++ptr;
           cur = (ptr < nvalid) ? __ldg(ids + ptr) : 0x7fffffff;
+          cur_w = (ptr < nvalid) ? to_f(wrow[ptr]) : 0.f;
         }
         k_last = ptr;
       } else {
         for (int k = 0; k < nvalid; ++k)
           if (__ldg(ids + k) == c) { owner = true; wsum += to_f(wrow[k]); }
+      }
+      {
+        const __nv_bfloat16 wb = __float2bfloat16_rn(wsum);
+        ws.wtab[((((int64_t)b * p.h_kv + h) * nblk + blk) * ws.umax + i) * 128 + r] =
+            owner ? *reinterpret_cast<const uint16_t*>(&wb) : kNotOwner;
       }
       ok = mbar_wait(&sdp_full[s], u & 1);
       if (i >= 2) ok = mbar_wait(&dq_done[s], (u - 1) & 1) && ok;
@@ -716,17 +747,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
   constexpr int QBYTES = DB * 16384;
   constexpr int KVBYTES = DB * 8192;
   constexpr int NDS = (D == 64) ? 2 : 1;   // buffers for the dS / wP tiles
+  constexpr int NQ = (D == 64) ? 3 : 2;    // Q / dO ring depth
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* Qs = smem;                      // 2 stages
-  uint8_t* dOs = Qs + 2 * QBYTES;          // 2 stages
-  uint8_t* Ks = dOs + 2 * QBYTES;
+  uint8_t* Qs = smem;                      // NQ stages
+  uint8_t* dOs = Qs + NQ * QBYTES;         // NQ stages
+  uint8_t* Ks = dOs + NQ * QBYTES;
   uint8_t* Vs = Ks + KVBYTES;
   uint8_t* dSs = Vs + KVBYTES;             // NDS x 16 KB
   uint8_t* Pws = dSs + NDS * 16384;        // NDS x 16 KB
-  int* list_s = reinterpret_cast<int*>(Pws + NDS * 16384);
+  int* list_s = reinterpret_cast<int*>(Pws + NDS * 16384);   // owning query blocks
+  int* pos_s = list_s + nblk;                                // position of this chunk in each block's union list
 
-  __shared__ uint64_t kv_full, qdo_full[2], sdp_full[2], dsp_full[2], dkv_done[2], all_done;
+  __shared__ uint64_t kv_full, qdo_full[4], qdo_free[4], sdp_full[2], dsp_full[2], dkv_done[2], all_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int m_s, warp_tot_s[4];
   __shared__ volatile int abort_s;
@@ -740,8 +773,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
   if (tid == 0) {
     mbar_init(&kv_full, 1);
     mbar_init(&all_done, 1);
+    for (int st = 0; st < NQ; ++st) {
+      mbar_init(&qdo_full[st], 1);
+      mbar_init(&qdo_free[st], 1);
+    }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&qdo_full[s], 1);
       mbar_init(&sdp_full[s], 1);
       mbar_init(&dsp_full[s], 128);
       mbar_init(&dkv_done[s], 1);
@@ -769,7 +805,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
       int base = inc - cnt;
       for (int w = 0; w < warp; ++w) base += warp_tot_s[w];
       for (int j = tid * per; j < min(nblk, (tid + 1) * per); ++j)
-        if ((ws.bitmap[(bh * nblk + j) * nwords + (c >> 5)] >> (c & 31)) & 1u) list_s[base++] = j;
+        if ((ws.bitmap[(bh * nblk + j) * nwords + (c >> 5)] >> (c & 31)) & 1u) {
+          const uint32_t* bm = ws.bitmap + (bh * nblk + j) * nwords;
+          int pos = __popc(bm[c >> 5] & ((1u << (c & 31)) - 1u));
+          for (int w = 0; w < (c >> 5); ++w) pos += __popc(bm[w]);
+          list_s[base] = j;
+          pos_s[base] = pos;
+          ++base;
+        }
       if (tid == 127) m_s = base;
     }
   }
@@ -789,9 +832,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
         tma_load_2d(Vs + db * 8192, &tmV, &kv_full, h * D + db * 64, b * p.T + c * 64);
       }
       for (int j = 0; j < m; ++j) {
-        const int s = j & 1, u = j >> 1;
+        const int s = j % NQ;
         if (abort_s) break;
-        if (j >= 2 && !mbar_wait(&dkv_done[s], (u - 1) & 1)) { abort_s = 1; atomicExch(&g_device_status, 301); break; }
+        if (j >= NQ && !mbar_wait(&qdo_free[s], ((j / NQ) - 1) & 1)) { abort_s = 1; atomicExch(&g_device_status, 301); break; }
         const int blk = list_s[j];
         mbar_expect_tx(&qdo_full[s], 2 * QBYTES);
 #pragma unroll
@@ -811,12 +854,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
         const int s = j & 1;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = s * QBYTES + (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
+          const uint32_t ao = (j % NQ) * QBYTES + (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
           mma_ss(tmem + s * 128, desc_sw128(q_addr + ao, 16, 1024), desc_sw128(k_addr + bo, 16, 1024), idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = s * QBYTES + (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
+          const uint32_t ao = (j % NQ) * QBYTES + (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
           mma_ss(tmem + s * 128 + 64, desc_sw128(do_addr + ao, 16, 1024), desc_sw128(v_addr + bo, 16, 1024), idesc_s, kk > 0);
         }
         mma_commit(&sdp_full[s]);
@@ -827,7 +870,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
         const int s = j & 1, u = j >> 1, sb = j % NDS;
         if (abort_s) break;
         if (j + 1 < m) {
-          ok = mbar_wait(&qdo_full[(j + 1) & 1], ((j + 1) >> 1) & 1);
+          ok = mbar_wait(&qdo_full[(j + 1) % NQ], ((j + 1) / NQ) & 1);
           if (!ok) break;
           tc_fence_after();
           issue_sdp(j + 1);
@@ -837,12 +880,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {   // 16 query rows per step
-          const uint64_t db_q = desc_sw128(q_addr + s * QBYTES + kk * 2048, 16384, 1024);
-          const uint64_t db_do = desc_sw128(do_addr + s * QBYTES + kk * 2048, 16384, 1024);
+          const uint64_t db_q = desc_sw128(q_addr + (j % NQ) * QBYTES + kk * 2048, 16384, 1024);
+          const uint64_t db_do = desc_sw128(do_addr + (j % NQ) * QBYTES + kk * 2048, 16384, 1024);
           mma_ss(tdK, desc_sw128(ds_addr + sb * 16384 + kk * 2048, 16384, 1024), db_q, idesc_dkv, (j > 0 || kk > 0) ? 1u : 0u);
           mma_ss(tdV, desc_sw128(pw_addr + sb * 16384 + kk * 2048, 16384, 1024), db_do, idesc_dkv, (j > 0 || kk > 0) ? 1u : 0u);
         }
         mma_commit(&dkv_done[s]);
+        mma_commit(&qdo_free[j % NQ]);
       }
       if (ok) mma_commit(&all_done);  // epilogue barrier for both row warpgroups (see the dq kernel)
       if (!ok) { abort_s = 1; atomicExch(&g_device_status, 302); }
@@ -854,33 +898,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
     const float slope = p.slope ? p.slope[hq] : 0.f;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
+    uint16_t wnext = kNotOwner;
+    if (wg < m) wnext = __ldg(ws.wtab + (((bh * nblk + list_s[wg]) * ws.umax + pos_s[wg]) * 128 + r));
     for (int j = wg; j < m; j += 2) {
       const int s = j & 1, u = j >> 1, sb = j % NDS;
-      const int blk = list_s[j];
-      const int t = blk * QB + ql;
-      const bool valid = t < p.L;
-      float wsum = 0.f;
-      bool owner = false;
-      if (valid) {
-        const int32_t* ids = p.idx + (((int64_t)b * p.L + t) * p.h_kv + h) * p.K;
-        const bf16* wrow = static_cast<const bf16*>(p.w) + (((int64_t)b * p.L + t) * p.h_q + hq) * p.num_weights;
-        if (!ws.flags[bh * nblk + blk]) {
-          // ascending list with negative padding at the end: first position holding an id >= c
-          int lo = 0, hi = p.K;
-          while (lo < hi) {
-            const int mid = (lo + hi) >> 1;
-            const int id = __ldg(ids + mid);
-            if (id >= 0 && id < c) lo = mid + 1; else hi = mid;
-          }
-          while (lo < p.K && __ldg(ids + lo) == c) { owner = true; wsum += to_f(wrow[lo]); ++lo; }
-        } else {
-          for (int k = 0; k < p.K; ++k) {
-            const int id = __ldg(ids + k);
-            if (id < 0) break;
-            if (id == c) { owner = true; wsum += to_f(wrow[k]); }
-          }
-        }
-      }
+      // weight of this row for the chunk, looked up in the table of the dq pass; the entry of this
+      // warpgroup's next block is requested now so that its latency is hidden
+      const uint16_t wraw = wnext;
+      if (j + 2 < m)
+        wnext = __ldg(ws.wtab + (((bh * nblk + list_s[j + 2]) * ws.umax + pos_s[j + 2]) * 128 + r));
+      const bool owner = wraw != kNotOwner;
+      const float wsum = owner ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&wraw)) : 0.f;
       ok = mbar_wait(&sdp_full[s], u & 1);
       if (j >= NDS) ok = mbar_wait(&dkv_done[(j - NDS) & 1], ((j - NDS) >> 1) & 1) && ok;
       ok = __all_sync(0xffffffffu, ok) && !abort_s;
@@ -961,12 +989,13 @@ static bool tc_shape_ok(const SparseParams& p) {
 static size_t tc_bwd_smem_dq(const SparseParams& p) {
   const int D = p.D, G = p.h_q / p.h_kv, QB = 128 / G, nchunk = p.T / 64;
   const int umax = min(nchunk, QB * p.K);
-  return 1024 + 2 * (size_t)(D / 64) * 16384 + 4 * (size_t)(D / 64) * 8192 + 2 * 16384 + (size_t)umax * 4 +
+  const int NST = (D == 64) ? 4 : 3;
+  return 1024 + 2 * (size_t)(D / 64) * 16384 + 2 * (size_t)NST * (D / 64) * 8192 + 2 * 16384 + (size_t)umax * 4 +
          (size_t)((nchunk + 31) / 32) * 4 + 16;
 }
 static size_t tc_bwd_smem_dkv(const SparseParams& p, int nblk) {
-  const int D = p.D, NDS = (D == 64) ? 2 : 1;
-  return 1024 + 4 * (size_t)(D / 64) * 16384 + 2 * (size_t)(D / 64) * 8192 + 2 * (size_t)NDS * 16384 + (size_t)nblk * 4 + 16;
+  const int D = p.D, NDS = (D == 64) ? 2 : 1, NQ = (D == 64) ? 3 : 2;
+  return 1024 + 2 * (size_t)NQ * (D / 64) * 16384 + 2 * (size_t)(D / 64) * 8192 + 2 * (size_t)NDS * 16384 + (size_t)nblk * 8 + 16;
 }
 
 // workspace of the tensor-core backward (0 when the shape is outside this path)
@@ -975,7 +1004,10 @@ size_t sparse_bwd_tc_workspace(const SparseParams& p) {
   const int G = p.h_q / p.h_kv, QB = 128 / G, nblk = ceil_div(p.L, QB), nchunk = p.T / 64;
   if (tc_bwd_smem_dq(p) > 220 * 1024 || tc_bwd_smem_dkv(p, nblk) > 220 * 1024) return 0;
   const size_t nw = (size_t)((nchunk + 31) / 32);
-  return ((size_t)p.B * p.h_kv * nblk * nw + (size_t)p.B * p.h_kv * nblk) * 4 + 256;
+  const size_t umax = (size_t)min(nchunk, QB * p.K);
+  const size_t tab = (size_t)p.B * p.h_kv * nblk * umax * 128 * sizeof(uint16_t);
+  if (tab > ((size_t)16 << 30)) return 0;   // ownership table beyond 16 GiB: shape left to the generic path
+  return (size_t)p.B * p.h_kv * nblk * nw * 4 + 256 + tab;
 }
 
 int sparse_bwd_tc_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st) {
@@ -987,7 +1019,9 @@ int sparse_bwd_tc_launch(const SparseParams& p, void* d_k, void* d_v, void* work
   const size_t nw = (size_t)((nchunk + 31) / 32);
   BwdWs ws;
   ws.bitmap = static_cast<uint32_t*>(workspace);
-  ws.flags = reinterpret_cast<int*>(ws.bitmap + (size_t)p.B * p.h_kv * nblk * nw);
+  ws.wtab = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(workspace) +
+                                        (((size_t)p.B * p.h_kv * nblk * nw * 4 + 255) & ~(size_t)255));
+  ws.umax = min(nchunk, QB * p.K);
   SparseParams pp = p;
   pp.d_k_out = d_k;
   pp.d_v_out = d_v;
@@ -1028,7 +1062,7 @@ int sparse_fwd_tc_launch(const SparseParams& p, cudaStream_t st) {
   if ((int64_t)p.B * p.T >= (1ll << 31)) return HILS_ERR_UNSUPPORTED;
   const int QB = 128 / G, nchunk = p.T / 64;
   const int umax = min(nchunk, QB * p.K);
-  const size_t smem = 1024 + (size_t)(D / 64) * 16384 + 4 * (size_t)(D / 64) * 8192 + 2 * 16384 + (size_t)umax * 4 +
+  const size_t smem = 1024 + (size_t)(D / 64) * 16384 + 2 * (size_t)kFwdStages * (D / 64) * 8192 + 2 * 16384 + (size_t)umax * 4 +
                       (size_t)((nchunk + 31) / 32) * 4 + 16;
   if (smem > 220 * 1024) return HILS_ERR_UNSUPPORTED;
   CUtensorMap tmK, tmV;
