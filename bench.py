@@ -39,6 +39,9 @@ WORKLOADS = {
     "c2": dict(B=8, T=8192, h_q=16, h_kv=16, D=64, S=64, K=32, W=512),
     "c2_small": dict(B=1, T=8192, h_q=16, h_kv=16, D=64, S=64, K=32, W=512),
     "c3": dict(B=1, T=65536, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
+    # decode: 32 sequences, one new token each, against a 131072-token KV store
+    "c4": dict(B=32, T=131072, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
+    "c4_small": dict(B=4, T=16384, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
 }
 CPU_SAMPLE = dict(B=1, T=2048, h_q=16, h_kv=16, D=64, S=64, K=8, W=512)   # the reference's CPU-runnable case
 
@@ -158,6 +161,115 @@ def run_reference(args):
     }))
 
 
+def run_decode(args):
+    """Decode against a cached HiLS KV store: one new token per sequence and step through the whole
+    chain (store append, sliding-window branch, selection over the pooled chunk keys, inter-chunk
+    softmax, sparse chunk attention, combine).  The batch is sharded over the ranks (no collective)."""
+    import torch.distributed as dist
+    from hils_attention_b200 import _lib
+    from hils_attention_b200.attention import HiLSAttentionConfig, HiLSAttentionCore
+    from hils_attention_b200.cache import HiLSCache
+    import hils_attention_b200 as hb
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    w = WORKLOADS[args.workload]
+    Bt, T, hq, hk, D, S, K, W = (w[x] for x in ("B", "T", "h_q", "h_kv", "D", "S", "K", "W"))
+    B = max(1, Bt // world)
+    dtype = torch.bfloat16
+    n_steps = args.warmup + args.steps + 4
+    cap = T + n_steps + 8
+    g = torch.Generator(device=dev).manual_seed(4 + rank)
+    kbuf = torch.empty((cap, B, hk, D), dtype=dtype, device=dev)
+    vbuf = torch.empty((cap, B, hk, D), dtype=dtype, device=dev)
+    for t0 in range(0, T, 4096):                                   # fill in slices: no second copy of the store
+        n = min(4096, T - t0)
+        off = torch.randn((n // S + 1, 1, B, hk, D), generator=g, device=dev) * 0.5
+        off = off.expand(-1, S, -1, -1, -1).reshape(-1, B, hk, D)[:n]
+        kbuf[t0:t0 + n] = (torch.randn((n, B, hk, D), generator=g, device=dev) + off).to(dtype)
+        vbuf[t0:t0 + n] = torch.randn((n, B, hk, D), generator=g, device=dev).to(dtype)
+    cache = HiLSCache()
+    layer = cache.layer(1)
+    layer.adopt(kbuf, vbuf, T)
+    N = T // S
+    with torch.no_grad():                                          # pooled chunk keys of the cached prefix
+        kf, _ = layer.folded()
+        mu = torch.randn((1, N, B * hq, D), generator=g, device=dev).to(dtype)
+        lmk_k, prior_b = hb.chunk_attn_pool(mu, kf[:, :N * S].unflatten(1, (N, S)))
+    cache._hils_prior_cache[0] = {"lmk_k": lmk_k, "prior_b": prior_b}
+    core = HiLSAttentionCore(HiLSAttentionConfig(hq, hk, K, S, W)).eval()
+    host = [torch.randn((B, 1, h, D), generator=torch.Generator().manual_seed(9 + i)).to(dtype).pin_memory()
+            for i, h in enumerate((hq, hk, hk))]
+    qn, kn, vn = (t.to(dev) for t in host)
+    out_host = torch.empty((B, 1, hq, D), dtype=dtype).pin_memory()
+
+    def step(q1, k1, v1):
+        with torch.no_grad():
+            return core(q1, k1, v1, q1, past_key_values=cache, use_cache=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(qn, kn, vn)
+    barrier()
+    c0 = _lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step(qn, kn, vn)
+        e1.record()
+        barrier()
+    launches = _lib.launch_count() - c0
+    ms = e0.elapsed_time(e1)
+    # end to end: the new token's q, k, v come from pinned host memory, the output row goes back
+    dq_, dk_, dv_ = (torch.empty_like(t) for t in (qn, kn, vn))
+    barrier()
+    e0.record()
+    for _ in range(4):
+        for d_, h_ in zip((dq_, dk_, dv_), host):
+            d_.copy_(h_, non_blocking=True)
+        out_host.copy_(step(dq_, dk_, dv_), non_blocking=True)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / 4
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+    us_step = 1e3 * ms / args.steps
+    pk = peaks()
+    # bytes a step must touch: pooled keys + bias, the K selected K/V chunks, the sliding window
+    alg = B * hk * (N * D * 2 + N * 4 * (hq // hk) + K * S * D * 2 * 2 + (W + S) * D * 2 * 2)
+    achieved = alg / (us_step * 1e-6) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": "hils_decode_us_per_step", "value": us_step, "unit": "us/step", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": us_step / 1e3, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, **w, "sequences_per_gpu": B,
+                       "parallelism": f"batch-sharded x{world}, no collective", "l2": "kv_store_larger_than_L2"},
+            "e2e": {"value": 1e3 * ms_e2e, "unit": "us/step",
+                    "h2d_bytes_per_step": sum(h.numel() * 2 for h in host), "d2h_bytes_per_step": out_host.numel() * 2},
+            "gpu_launches": launches, "clocks": clk.summary(),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / pk["hbm_gbs"], "traffic": None, "kernel": "decode step (all kernels)",
+                         "algorithmic_bytes_per_step": alg, "peak_source": pk["source"]},
+            "cpu_baseline": None,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -170,6 +282,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload.startswith("c4"):
+        return run_decode(args)
 
     import torch.distributed as dist
     import hils_attention_b200 as hb

@@ -117,7 +117,18 @@ class HiLSAttentionCore(torch.nn.Module):
         B, L = q.shape[0], q.shape[1]
         S, W = self.chunk_size, self.hils_sliding_window
         caching = use_cache and past_key_values is not None
-        if caching:
+        h_kv = self.h_kv
+        folded = False
+        if caching and hasattr(past_key_values, "layer"):
+            # token-major store of this package: the batch is folded into the head dimension, so the
+            # cached K/V are consumed in place as (1, T, B*h_kv, D) and only the new tokens are copied
+            layer = past_key_values.layer(self.layer_idx + self.config.num_hidden_layers)
+            layer.update(k, v)
+            k, v = layer.folded()
+            q = q.transpose(0, 1).reshape(1, L, B * self.h_q, q.shape[-1])
+            lmk_q = lmk_q.transpose(0, 1).reshape(1, L, B * lmk_q.shape[2], lmk_q.shape[-1])
+            h_kv, folded, B_orig, B = B * self.h_kv, True, B, 1
+        elif caching:
             k, v = past_key_values.update(k, v, self.layer_idx + self.config.num_hidden_layers, None)
         swa_o, lse_sum = ops.flex_attn_tl(q, k, v, window_size=W, chunk_size=S,
                                           training=(past_key_values is None), mask_lmk=True,
@@ -130,7 +141,7 @@ class HiLSAttentionCore(torch.nn.Module):
             q_offset = full_seq_len - L if caching else 0
             indices, scores = self.topk_func(
                 lmk_q, lmk_k, lse_sum, self.topk, block_size=S, window_size=W, is_training=self.training,
-                is_causal=True, q_offset=q_offset, G=lmk_k.shape[2] // self.h_kv, bias=prior_b)
+                is_causal=True, q_offset=q_offset, G=lmk_k.shape[2] // h_kv, bias=prior_b)
             if self.enable_prior_query and prior_b is not None:
                 K = indices.shape[-1]
                 g_kernel = prior_b.shape[2] // indices.shape[2]
@@ -156,6 +167,12 @@ class HiLSAttentionCore(torch.nn.Module):
             o_lower = swa_o * torch.sigmoid(lse_sum).to(swa_o.dtype).unsqueeze(-1)
         else:
             o_lower = swa_o
+        if folded:  # back to (B, L, heads, ...)
+            def unfold(t):
+                return t.reshape(L, B_orig, t.shape[2] // B_orig, *t.shape[3:]).transpose(0, 1)
+            o_lower = unfold(o_lower)
+            aux = {n: (unfold(t) if n in ("indices", "scores", "weights", "lse_swa", "swa_o", "hils_o") else t)
+                   for n, t in aux.items()}
         return (o_lower, aux) if return_aux else o_lower
 
 

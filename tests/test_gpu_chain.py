@@ -82,11 +82,12 @@ def test_chain_gradients_match_oracle_fp32():
         check(a.grad, b.grad, F32, n, scale=50.0)
 
 
-def test_prefill_then_decode_matches_full_forward():
+@pytest.mark.parametrize("B", [1, 3])
+def test_prefill_then_decode_matches_full_forward(B):
     """Feeding the sequence through the KV store (prefill 700 tokens, one 100-token chunk-prefill,
     then single-token decode steps) reproduces the one-shot forward: same ids, same outputs."""
     from hils_attention_b200.cache import HiLSCache
-    B, T, hq, hk, D, S, K, W = 1, 832, 4, 2, 64, 64, 4, 128
+    T, hq, hk, D, S, K, W = 832, 4, 2, 64, 64, 4, 128
     q, k, v = _inputs(B, T, hq, hk, D, S, 44, BF)
     qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
     core = _core(hq, hk, K, S, W).eval()
