@@ -1,0 +1,302 @@
+// Decode-shaped attention kernels: a handful of query rows per sequence against a long KV store.
+// With one query row a 128-row tensor-core tile would be 99 % padding and the step is bound by
+// streaming K/V out of HBM, so these kernels are CUDA-core streamers: one CTA per (kv-head, batch,
+// query row) reads each K/V row once with 16-byte loads (16 lanes per row) and serves all G query
+// heads of the group from it.  Same contracts as the sparse chunk attention
+// (ops/hils_fwd_bwd_head.py:404-485) and the sliding-window branch (ops/flex_attn_tilelang.py:115-253).
+#include "common.cuh"
+
+namespace hils {
+
+constexpr int kDecWarps = 8;
+constexpr int kDecMaxG = 8;
+
+struct DecodeParams {
+  const void* q; const void* k; const void* v; const void* w; const int32_t* idx; const float* slope;
+  void* o; float* lse;
+  int B, L, T, h_q, h_kv, D, K, num_weights, S, mask_last;       // sparse
+  int W, mask_lmk, expand, kv_start;                              // sliding window
+  float scale;
+};
+
+// scores of `n` consecutive key rows (row stride rs elements) against the G query rows in q_s:
+// out[g * ostride + j] = <q_g, K_j>.  Half-warp per key row, four rows in flight per half-warp.
+template <typename T, int PER>
+__device__ __forceinline__ void score_rows(const float* q_s, const T* kbase, int64_t rs, int n, int G, int D, float* out,
+                                           int ostride, int lane) {
+  const int half = lane >> 4, sub = lane & 15;
+  for (int j0 = 0; j0 < n; j0 += 8) {
+    float kv[4][PER];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u * 2 + half;
+      if (j < n) {
+#pragma unroll
+        for (int e = 0; e < PER; e += 4) {
+          const float4 x = load4(kbase + (int64_t)j * rs + sub * PER + e);
+          kv[u][e] = x.x; kv[u][e + 1] = x.y; kv[u][e + 2] = x.z; kv[u][e + 3] = x.w;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) kv[u][e] = 0.f;
+      }
+    }
+    for (int g = 0; g < G; ++g) {
+      float qv[PER];
+#pragma unroll
+      for (int e = 0; e < PER; ++e) qv[e] = q_s[g * D + sub * PER + e];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < PER; ++e) acc = fmaf(qv[e], kv[u][e], acc);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        const int j = j0 + u * 2 + half;
+        if (sub == 0 && j < n) out[g * ostride + j] = acc;
+      }
+    }
+  }
+}
+
+// acc[g][.] += sum_j p[g * pstride + j] * V_j ; lane owns PER consecutive output columns
+template <typename T, int PER>
+__device__ __forceinline__ void pv_rows(const float* p_s, int pstride, const T* vbase, int64_t rs, int n, int G,
+                                        float (&acc)[kDecMaxG][PER], int lane) {
+  for (int j0 = 0; j0 < n; j0 += 8) {          // eight value rows in flight per lane
+    float vv[8][PER];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int j = min(j0 + u, n - 1);
+      if constexpr (PER >= 4) {
+#pragma unroll
+        for (int e = 0; e < PER; e += 4) {
+          const float4 x = load4(vbase + (int64_t)j * rs + lane * PER + e);
+          vv[u][e] = x.x; vv[u][e + 1] = x.y; vv[u][e + 2] = x.z; vv[u][e + 3] = x.w;
+        }
+      } else {
+        const float2 x = load2(vbase + (int64_t)j * rs + lane * PER);
+        vv[u][0] = x.x; vv[u][1] = x.y;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (j0 + u < n) {
+#pragma unroll
+        for (int g = 0; g < kDecMaxG; ++g) {
+          if (g < G) {
+            const float pj = p_s[g * pstride + j0 + u];
+#pragma unroll
+            for (int e = 0; e < PER; ++e) acc[g][e] = fmaf(pj, vv[u][e], acc[g][e]);
+          }
+        }
+      }
+    }
+  }
+}
+
+// ---- sparse chunk attention, decode shape: D = 32 * PER columns, keys per chunk S <= 64 -------------
+template <typename T, int PER>
+__global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_kernel(DecodeParams p) {
+  constexpr int D = 32 * PER, KPER = D / 16;
+  extern __shared__ __align__(16) float smem[];
+  const int G = p.h_q / p.h_kv;
+  float* q_s = smem;                                  // [G][D]
+  float* p_s = q_s + G * D;                           // [warps][G][64]
+  float* o_s = p_s + kDecWarps * G * 64;              // [warps][G][D]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.x, b = blockIdx.y, l = blockIdx.z;
+  const int64_t row0 = (((int64_t)b * p.L + l) * p.h_q + h * G);
+  const T* q = static_cast<const T*>(p.q) + row0 * D;
+  for (int i = tid; i < G * D; i += kDecWarps * 32) q_s[i] = to_f(q[i]);
+  __syncthreads();
+  const int32_t* ids = p.idx + (((int64_t)b * p.L + l) * p.h_kv + h) * p.K;
+  const T* wts = static_cast<const T*>(p.w) + row0 * p.num_weights;
+  const int nchunk = p.T / p.S;
+  int nvalid = 0;
+  while (nvalid < p.K && ids[nvalid] >= 0) ++nvalid;
+  float acc[kDecMaxG][PER];
+#pragma unroll
+  for (int g = 0; g < kDecMaxG; ++g)
+#pragma unroll
+    for (int e = 0; e < PER; ++e) acc[g][e] = 0.f;
+  float* pw = p_s + warp * G * 64;
+  const int64_t rs = (int64_t)p.h_kv * D;
+  for (int kk = warp; kk < nvalid; kk += kDecWarps) {
+    const int c = ids[kk];
+    if (c >= nchunk) continue;
+    const int64_t tok0 = (int64_t)b * p.T + (int64_t)c * p.S;
+    const T* kb = static_cast<const T*>(p.k) + (tok0 * p.h_kv + h) * D;
+    const T* vb = static_cast<const T*>(p.v) + (tok0 * p.h_kv + h) * D;
+    __syncwarp();
+    score_rows<T, KPER>(q_s, kb, rs, p.S, G, D, pw, 64, lane);
+    __syncwarp();
+    for (int g = 0; g < G; ++g) {
+      const float slope = p.slope ? p.slope[h * G + g] : 0.f;
+      float s0 = -CUDART_INF_F, s1 = -CUDART_INF_F;
+      const int j0 = lane, j1 = lane + 32;
+      if (j0 < p.S && !(p.mask_last && j0 == p.S - 1)) s0 = (pw[g * 64 + j0] - slope * (float)max(0, p.S - 2 - j0)) * p.scale;
+      if (j1 < p.S && !(p.mask_last && j1 == p.S - 1)) s1 = (pw[g * 64 + j1] - slope * (float)max(0, p.S - 2 - j1)) * p.scale;
+      const float m = warp_max(fmaxf(s0, s1));
+      float e0 = 0.f, e1 = 0.f;
+      if (m > -CUDART_INF_F) { e0 = expf(s0 - m); e1 = expf(s1 - m); }
+      const float sum = warp_sum(e0 + e1);
+      const float f = (sum > 0.f) ? to_f(wts[g * p.num_weights + kk]) / sum : 0.f;
+      if (j0 < 64) pw[g * 64 + j0] = e0 * f;
+      if (j1 < 64) pw[g * 64 + j1] = e1 * f;
+    }
+    __syncwarp();
+    pv_rows<T, PER>(pw, 64, vb, rs, p.S, G, acc, lane);
+  }
+  float* ow = o_s + warp * G * D;
+#pragma unroll
+  for (int g = 0; g < kDecMaxG; ++g)
+    if (g < G)
+#pragma unroll
+      for (int e = 0; e < PER; ++e) ow[g * D + lane * PER + e] = acc[g][e];
+  __syncthreads();
+  T* o = static_cast<T*>(p.o) + row0 * D;
+  for (int i = tid; i < G * D; i += kDecWarps * 32) {
+    float s = 0.f;
+    for (int w = 0; w < kDecWarps; ++w) s += o_s[w * G * D + i];
+    o[i] = from_f<T>(s);
+  }
+}
+
+// ---- sliding-window branch, decode shape ------------------------------------------------------------
+template <typename T, int PER>
+__global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams p) {
+  constexpr int D = 32 * PER, KPER = D / 16;
+  extern __shared__ __align__(16) float smem[];
+  const int G = p.h_q / p.h_kv;
+  float* q_s = smem;                                  // [G][D]
+  float* p_s = q_s + G * D;                           // [warps][G][64]
+  float* o_s = p_s + kDecWarps * G * 64;              // [warps][G][D]
+  float* ml_s = o_s + kDecWarps * G * D;              // [warps][G][2]  running max, sum
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.x, b = blockIdx.y, i = blockIdx.z;
+  const int64_t row0 = (((int64_t)b * p.L + i) * p.h_q + h * G);
+  const T* q = static_cast<const T*>(p.q) + row0 * D;
+  for (int x = tid; x < G * D; x += kDecWarps * 32) q_s[x] = to_f(q[x]);
+  __syncthreads();
+  const int t = p.kv_start + (p.T - p.L) + i;
+  int start = t - p.W + 1;
+  if (p.expand) start = floor_div(start, p.S) * p.S;
+  const int lo = max(0, start - p.kv_start), hi = min(p.T - 1, t - p.kv_start);
+  float acc[kDecMaxG][PER], m[kDecMaxG], lsum[kDecMaxG];
+#pragma unroll
+  for (int g = 0; g < kDecMaxG; ++g) {
+    m[g] = -CUDART_INF_F; lsum[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) acc[g][e] = 0.f;
+  }
+  float* pw = p_s + warp * G * 64;
+  const int64_t rs = (int64_t)p.h_kv * D;
+  const T* kb0 = static_cast<const T*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
+  const T* vb0 = static_cast<const T*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
+  for (int j0 = lo + warp * 64; j0 <= hi; j0 += kDecWarps * 64) {   // 64 keys per warp step
+    const int n = min(64, hi - j0 + 1);
+    __syncwarp();
+    score_rows<T, KPER>(q_s, kb0 + (int64_t)j0 * rs, rs, n, G, D, pw, 64, lane);
+    __syncwarp();
+#pragma unroll
+    for (int g = 0; g < kDecMaxG; ++g) {
+      if (g < G) {
+        const int ja = lane, jb = lane + 32;
+        float s0 = -CUDART_INF_F, s1 = -CUDART_INF_F;
+        if (ja < n && !(p.mask_lmk && ((p.kv_start + j0 + ja + 1) % p.S == 0))) s0 = pw[g * 64 + ja] * p.scale;
+        if (jb < n && !(p.mask_lmk && ((p.kv_start + j0 + jb + 1) % p.S == 0))) s1 = pw[g * 64 + jb] * p.scale;
+        const float mn = fmaxf(m[g], warp_max(fmaxf(s0, s1)));
+        float e0 = 0.f, e1 = 0.f, corr = 1.f;
+        if (mn > -CUDART_INF_F) {
+          corr = (m[g] > -CUDART_INF_F) ? expf(m[g] - mn) : 0.f;
+          e0 = expf(s0 - mn); e1 = expf(s1 - mn);
+        }
+        lsum[g] = lsum[g] * corr + warp_sum(e0 + e1);
+        m[g] = mn;
+#pragma unroll
+        for (int e = 0; e < PER; ++e) acc[g][e] *= corr;
+        pw[g * 64 + ja] = e0;
+        pw[g * 64 + jb] = e1;
+      }
+    }
+    __syncwarp();
+    pv_rows<T, PER>(pw, 64, vb0 + (int64_t)j0 * rs, rs, n, G, acc, lane);
+  }
+  float* ow = o_s + warp * G * D;
+#pragma unroll
+  for (int g = 0; g < kDecMaxG; ++g)
+    if (g < G) {
+#pragma unroll
+      for (int e = 0; e < PER; ++e) ow[g * D + lane * PER + e] = acc[g][e];
+      if (lane == 0) { ml_s[(warp * G + g) * 2] = m[g]; ml_s[(warp * G + g) * 2 + 1] = lsum[g]; }
+    }
+  __syncthreads();
+  T* o = static_cast<T*>(p.o) + row0 * D;
+  for (int x = tid; x < G * D; x += kDecWarps * 32) {
+    const int g = x / D;
+    float mm = -CUDART_INF_F;
+    for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, ml_s[(w * G + g) * 2]);
+    float tot = 0.f, s = 0.f;
+    if (mm > -CUDART_INF_F)
+      for (int w = 0; w < kDecWarps; ++w) {
+        const float mw = ml_s[(w * G + g) * 2];
+        const float c = (mw > -CUDART_INF_F) ? expf(mw - mm) : 0.f;
+        tot += ml_s[(w * G + g) * 2 + 1] * c;
+        s += o_s[w * G * D + x] * c;
+      }
+    o[x] = from_f<T>(tot > 0.f ? s / tot : 0.f);
+    if (x % D == 0) p.lse[row0 + g] = (tot > 0.f) ? mm + logf(tot) : -CUDART_INF_F;
+  }
+}
+
+template <typename T>
+static int launch_decode(const DecodeParams& p, bool swa, cudaStream_t st) {
+  const int G = p.h_q / p.h_kv;
+  const size_t smem = ((size_t)G * p.D + (size_t)kDecWarps * G * 64 + (size_t)kDecWarps * G * p.D +
+                       (size_t)kDecWarps * G * 2) * sizeof(float);
+  dim3 grid(p.h_kv, p.B, p.L);
+#define HILS_DEC_LAUNCH(KERNEL, PER)                                                              \
+  do {                                                                                            \
+    cudaFuncSetAttribute(KERNEL<T, PER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    KERNEL<T, PER><<<grid, kDecWarps * 32, smem, st>>>(p);                                        \
+  } while (0)
+  if (swa) {
+    if (p.D == 128) HILS_DEC_LAUNCH(swa_decode_kernel, 4); else HILS_DEC_LAUNCH(swa_decode_kernel, 2);
+  } else {
+    if (p.D == 128) HILS_DEC_LAUNCH(sparse_decode_kernel, 4); else HILS_DEC_LAUNCH(sparse_decode_kernel, 2);
+  }
+#undef HILS_DEC_LAUNCH
+  HILS_LAUNCH_CHECK(swa ? "swa_fwd (decode)" : "sparse_attn_fwd (decode)");
+  return HILS_OK;
+}
+
+static bool decode_shape_ok(int B, int L, int h_q, int h_kv, int D, int Dv) {
+  const int G = h_q / h_kv;
+  return L >= 1 && L <= 4 && D == Dv && (D == 64 || D == 128) && G <= kDecMaxG && B <= 65535 && h_kv <= (1 << 30);
+}
+
+// HILS_ERR_UNSUPPORTED when the shape is not a decode shape
+int sparse_decode_launch(const void* q, const void* k, const void* v, const void* w, const int32_t* idx, const float* slope,
+                         void* o, int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights, int S,
+                         float scale, int mask_last, int dtype, cudaStream_t st) {
+  if (!decode_shape_ok(B, L, h_q, h_kv, D, Dv) || S > 64) return HILS_ERR_UNSUPPORTED;
+  DecodeParams p = {};
+  p.q = q; p.k = k; p.v = v; p.w = w; p.idx = idx; p.slope = slope; p.o = o;
+  p.B = B; p.L = L; p.T = T; p.h_q = h_q; p.h_kv = h_kv; p.D = D; p.K = K; p.num_weights = num_weights; p.S = S;
+  p.mask_last = mask_last; p.scale = scale;
+  return dtype == HILS_BF16 ? launch_decode<bf16>(p, false, st) : launch_decode<float>(p, false, st);
+}
+
+int swa_decode_launch(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Lq, int Lk, int h_q,
+                      int h_kv, int D, int Dv, int W, int S, int mask_lmk, int expand, float scale, int kv_start, int dtype,
+                      cudaStream_t st) {
+  if (!decode_shape_ok(B, Lq, h_q, h_kv, D, Dv)) return HILS_ERR_UNSUPPORTED;
+  DecodeParams p = {};
+  p.q = q; p.k = k; p.v = v; p.o = o; p.lse = lse;
+  p.B = B; p.L = Lq; p.T = Lk; p.h_q = h_q; p.h_kv = h_kv; p.D = D; p.S = S; p.W = W; p.mask_lmk = mask_lmk;
+  p.expand = expand; p.kv_start = kv_start; p.scale = scale;
+  return dtype == HILS_BF16 ? launch_decode<bf16>(p, true, st) : launch_decode<float>(p, true, st);
+}
+
+}  // namespace hils

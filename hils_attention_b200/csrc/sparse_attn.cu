@@ -5,6 +5,9 @@ namespace hils {
 
 int sparse_fwd_tc_launch(const SparseParams& p, cudaStream_t st);  // sparse_attn_tc.cu
 size_t sparse_bwd_tc_workspace(const SparseParams& p);
+int sparse_decode_launch(const void* q, const void* k, const void* v, const void* w, const int32_t* idx, const float* slope,
+                         void* o, int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights, int S,
+                         float scale, int mask_last, int dtype, cudaStream_t st);  // decode_attn.cu
 int sparse_bwd_tc_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st);
 
 static int check_sparse(int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights,
@@ -68,6 +71,11 @@ extern "C" int hils_sparse_attn_fwd(const void* q, const void* k, const void* v,
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == HILS_BF16) {  // tensor-core path for the shapes it covers
     const int rc = sparse_fwd_tc_launch(p, st);
+    if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  }
+  {  // a few query rows against a long store (fp32, or bf16 outside the tensor-core shapes): streaming kernel
+    const int rc = sparse_decode_launch(q, k, v, weights, indices, slope, o, B, L, T, h_q, h_kv, D, Dv, K, num_weights,
+                                        chunk_size, sm_scale, mask_last_token, dtype, st);
     if (rc != HILS_ERR_UNSUPPORTED) return rc;
   }
   const int64_t rows = (int64_t)B * L * h_q;

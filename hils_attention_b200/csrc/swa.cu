@@ -263,6 +263,9 @@ __global__ void __launch_bounds__(128) swa_bwd_dkv_kernel(SwaParams p, int64_t r
 int swa_fwd_tc_launch(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Lq, int Lk, int h_q,
                       int h_kv, int D, int Dv, int W, int S, int mask_lmk, int expand, float scale, int kv_start,
                       cudaStream_t st);  // swa_tc.cu
+int swa_decode_launch(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Lq, int Lk, int h_q,
+                      int h_kv, int D, int Dv, int W, int S, int mask_lmk, int expand, float scale, int kv_start, int dtype,
+                      cudaStream_t st);  // decode_attn.cu
 size_t swa_bwd_tc_workspace(int B, int L, int h_q, int h_kv, int D, int Dv, int S);
 int swa_bwd_tc_launch(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
                       const float* d_lse, void* d_q, void* d_k, void* d_v, void* workspace, int B, int L, int h_q, int h_kv,
@@ -289,6 +292,11 @@ extern "C" int hils_swa_fwd(const void* q, const void* k, const void* v, void* o
   HILS_REQUIRE(Lq <= Lk, "swa_fwd: Lq (%d) must not exceed Lk (%d)", Lq, Lk);
   if (Lq == 0) return HILS_OK;
   HILS_REQUIRE(q && k && v && o && lse, "swa_fwd: null pointer");
+  if (Lq < Lk) {  // a few query rows against a long store: the streaming decode kernel
+    const int rc = swa_decode_launch(q, k, v, o, lse, B, Lq, Lk, h_q, h_kv, D, Dv, window_size, chunk_size, mask_lmk,
+                                     expand_to_chunk, sm_scale, kv_start, dtype, (cudaStream_t)stream);
+    if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  }
   if (dtype == HILS_BF16) {  // tensor-core path for the shapes it covers
     const int rc = swa_fwd_tc_launch(q, k, v, o, lse, B, Lq, Lk, h_q, h_kv, D, Dv, window_size, chunk_size, mask_lmk,
                                      expand_to_chunk, sm_scale, kv_start, (cudaStream_t)stream);

@@ -405,6 +405,167 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
   }
 }
 
+// ---- selection for decode: few query rows against many chunk keys ----------------------------------
+// One CTA per (kv-head, batch, query row).  The chunk keys of that head are streamed once (16 lanes per
+// key row, 16-byte loads), logits go to shared memory, then log-sum-exp, ranking keys and the same
+// sort/merge selection as above, with the candidate tiles spread over the CTA's 8 warps.
+template <typename T>
+__global__ void __launch_bounds__(256) topk_decode_kernel(TopkParams p) {
+  extern __shared__ __align__(16) float smem[];
+  const int G = p.G, D = p.D, N = p.N, K = p.topk;
+  const int Npad = (N + 127) & ~127;
+  float* q_s = smem;                         // [G][D]
+  float* v_s = q_s + G * D;                  // [G][Npad] selection logits
+  float* key_s = v_s + (size_t)G * Npad;     // [Npad]
+  float* red_s = key_s + Npad;               // [16] + [G] lse_total
+  u64* list_s = reinterpret_cast<u64*>(red_s + 16 + ((G + 1) & ~1));  // [8][32]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.x, b = blockIdx.y, l = blockIdx.z;
+  const T* q = static_cast<const T*>(p.q) + ((((int64_t)b * p.L + l) * p.h_kv + h) * G) * D;
+  const T* lmks = static_cast<const T*>(p.lmks);
+  const int HL = p.per_qhead ? p.h_kv * G : p.h_kv;
+  const int lim = row_limit(p, l);
+  for (int i = tid; i < G * D; i += 256) q_s[i] = to_f(q[i]);
+  __syncthreads();
+  // ---- logits: half-warp per chunk key -------------------------------------------------------
+  const int hw = tid >> 4, sub = tid & 15, per = D / 16;
+  const int ng = p.per_qhead ? G : 1;
+  for (int cb = 0; cb < Npad; cb += 64) {                 // four key rows in flight per half-warp
+    for (int g0 = 0; g0 < ng; ++g0) {
+      float kv[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = cb + u * 16 + hw;
+        if (c < lim) {
+          const T* krow = lmks + (((int64_t)b * N + c) * HL + (p.per_qhead ? h * G + g0 : h)) * D + sub * per;
+          for (int e = 0; e < per; e += 4) {
+            const float4 x = load4(krow + e);
+            kv[u][e] = x.x; kv[u][e + 1] = x.y; kv[u][e + 2] = x.z; kv[u][e + 3] = x.w;
+          }
+        }
+      }
+      const int gl = p.per_qhead ? g0 : 0, gh = p.per_qhead ? g0 + 1 : G;
+      for (int g = gl; g < gh; ++g) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = cb + u * 16 + hw;
+          const bool live = c < lim;
+          float acc = 0.f;
+          if (live)
+            for (int e = 0; e < per; ++e) acc = fmaf(q_s[g * D + sub * per + e], kv[u][e], acc);
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+          if (sub == 0 && c < Npad) {
+            float v = -CUDART_INF_F;
+            if (live) {
+              v = acc * p.scale;
+              if (p.bias) v += p.bias[(((int64_t)b * N + c) * p.h_kv + h) * G + g];
+              if (p.gumbel) v += p.gumbel[(int64_t)(h * G + g) * N + c];
+            }
+            v_s[(size_t)g * Npad + c] = v;
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // ---- log-sum-exp per group member, lse_total --------------------------------------------------
+  for (int g = 0; g < G; ++g) {
+    float m = -CUDART_INF_F;
+    for (int c = tid; c < lim; c += 256) m = fmaxf(m, v_s[(size_t)g * Npad + c]);
+    m = warp_max(m);
+    if (lane == 0) red_s[warp] = m;
+    __syncthreads();
+    m = red_s[0];
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, red_s[w]);
+    float sum = 0.f;
+    if (m > -CUDART_INF_F)
+      for (int c = tid; c < lim; c += 256) sum += expf(v_s[(size_t)g * Npad + c] - m);
+    sum = warp_sum(sum);
+    if (lane == 0) red_s[8 + warp] = sum;
+    __syncthreads();
+    if (tid == 0) {
+      float tot = 0.f;
+      for (int w = 0; w < 8; ++w) tot += red_s[8 + w];
+      const float lh = (tot > 0.f) ? m + logf(tot) : -CUDART_INF_F;
+      const int64_t o = (((int64_t)b * p.L + l) * p.h_kv + h) * G + g;
+      const float ls = (p.lse_dtype == HILS_BF16) ? to_f(static_cast<const bf16*>(p.lse_swa)[o])
+                                                  : static_cast<const float*>(p.lse_swa)[o];
+      const float lt = log_add_exp(ls, lh);
+      red_s[16 + g] = lt;
+      if (p.lse_total) p.lse_total[o] = lt;
+    }
+    __syncthreads();
+  }
+  // ---- ranking keys --------------------------------------------------------------------------------
+  for (int c = tid; c < Npad; c += 256) {
+    float key = -CUDART_INF_F;
+    if (c < lim) {
+      for (int g = 0; g < G; ++g) {
+        const float v = v_s[(size_t)g * Npad + c];
+        if (v > -CUDART_INF_F) key = fmaxf(key, v - red_s[16 + g]);
+      }
+      if (p.drop_mask && p.drop_mask[((int64_t)b * p.L + l) * N + c] != 0) key = -CUDART_INF_F;
+    }
+    key_s[c] = key;
+    if (p.rank_keys && c < N) p.rank_keys[(((int64_t)b * p.L + l) * p.h_kv + h) * N + c] = key;
+  }
+  __syncthreads();
+  // ---- selection: each warp sorts its tiles of 128 and keeps a descending top-32 -------------------
+  u64 best = 0ull;
+  const int ntile = (lim + 127) >> 7;
+  for (int t = warp; t < ntile; t += 8) {
+    const int c0 = t * 128;
+    const float4 kk = *reinterpret_cast<const float4*>(key_s + c0 + lane * 4);
+    const float key[4] = {kk.x, kk.y, kk.z, kk.w};
+    u64 item[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      item[i] = (key[i] > -CUDART_INF_F)
+                    ? (((u64)order_bits(key[i]) << 32) | (0xFFFFFFFFu - (uint32_t)(c0 + lane * 4 + i))) : 0ull;
+    sort128_desc(item, lane);
+    u64 top = 0ull;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const u64 x = __shfl_sync(0xffffffffu, item[i], lane >> 2);
+      if ((lane & 3) == i) top = x;
+    }
+    const u64 rev = __shfl_sync(0xffffffffu, top, 31 - lane);
+    best = merge32_desc(max64(best, rev), lane);
+  }
+  list_s[warp * 32 + lane] = best;
+  __syncthreads();
+  if (warp == 0) {
+    for (int w = 1; w < 8; ++w) best = merge32_desc(max64(best, list_s[w * 32 + 31 - lane]), lane);
+    int id = (lane < K && best != 0ull) ? (int)(0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull)) : 0x7fffffff;
+    id = sort32_asc(id, lane);
+    if (id == 0x7fffffff) id = -1;
+    if (lane < K) {
+      p.indices[(((int64_t)b * p.L + l) * p.h_kv + h) * K + lane] = id;
+      T* scores = static_cast<T*>(p.scores);
+      for (int g = 0; g < G; ++g) {
+        float acc = 0.f;
+        if (id >= 0) acc = dot_row(q_s + g * D, lmks + (((int64_t)b * N + id) * HL + (p.per_qhead ? h * G + g : h)) * D, D);
+        scores[((((int64_t)b * p.L + l) * p.h_kv + h) * G + g) * K + lane] =
+            from_f<T>(id >= 0 ? acc * p.scale : -CUDART_INF_F);
+      }
+    }
+  }
+}
+
+template <typename T>
+static int launch_topk_decode(const TopkParams& p, cudaStream_t st) {
+  const int Npad = (p.N + 127) & ~127;
+  const size_t smem = ((size_t)p.G * p.D + (size_t)p.G * Npad + Npad + 16 + ((p.G + 1) & ~1)) * sizeof(float) +
+                      8 * 32 * sizeof(u64) + 16;
+  if (smem > 200 * 1024) return HILS_ERR_UNSUPPORTED;
+  cudaFuncSetAttribute(topk_decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid(p.h_kv, p.B, p.L);
+  topk_decode_kernel<T><<<grid, 256, smem, st>>>(p);
+  HILS_LAUNCH_CHECK("topk_fwd (decode)");
+  return HILS_OK;
+}
+
 // ---- backward of the returned scores ---------------------------------------------------------
 // dq[i,g] = scale * sum_k ds[i,g,k] k'_{id_k};  dk'_c += scale * ds[i,g,k] q[i,g]  (fp32 atomics)
 template <typename T>
@@ -500,6 +661,11 @@ extern "C" int hils_topk_fwd(const void* q, const void* lmks, const void* lse_sw
   p.window_size = window_size; p.is_causal = is_causal; p.q_offset = q_offset; p.per_qhead = per_qhead;
   p.lse_dtype = lse_dtype; p.RW = 4; p.scale = sm_scale;
   cudaStream_t st = (cudaStream_t)stream;
+  // few query rows against many chunk keys (decode, short chunk-prefill): stream the keys once per row
+  if (L <= 4 && N >= 512 && topk <= 32 && D % 16 == 0 && D / 16 <= 8 && (D / 16) % 4 == 0 && L <= 65535) {
+    const int rc = (dtype == HILS_BF16) ? launch_topk_decode<bf16>(p, st) : launch_topk_decode<float>(p, st);
+    if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  }
   const int kpl = (topk + 31) / 32;
   if (dtype == HILS_BF16) {
     if (kpl == 1) return launch_topk<bf16, 1>(p, st);

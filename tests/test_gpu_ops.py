@@ -387,3 +387,51 @@ def test_topk_backward_bf16_tensor_core_path(ops, cfg):
     (s.reshape(B, L, h_kv * G, K).masked_fill(~valid.cpu(), 0.0) * gs.float()).sum().backward()
     check(q.grad, qr.grad, BF, "dq", scale=float(qr.grad.abs().max()))
     check(lm.grad, lr.grad, BF, "dlmk", scale=float(lr.grad.abs().max()))
+
+
+@pytest.mark.parametrize("cfg", [
+    # B, L, N, h_kv, G, D, K, per_qhead, dtype
+    (2, 1, 600, 2, 1, 128, 32, False, BF),
+    (1, 3, 1000, 2, 4, 64, 16, False, BF),
+    (1, 2, 520, 1, 2, 64, 8, True, F32),
+])
+def test_topk_decode_kernel(ops, cfg):
+    """Few query rows against many chunk keys (the decode-specialised selection kernel): ids bit-exact
+    on the kernel's own ranking values, ranking values and scores within tolerance of the oracle."""
+    B, L, N, h_kv, G, D, K, per_q, dtype = cfg
+    S, W = 64, 512
+    q_offset = N * S + W + 5 - L                      # every chunk is a remote candidate for the last row
+    g = torch.Generator().manual_seed(23)
+    q = torch.randn(B, L, h_kv, G, D, generator=g).to(dtype)
+    lm = torch.randn(B, N, h_kv * G if per_q else h_kv, D, generator=g).to(dtype)
+    lse = torch.randn(B, L, h_kv * G, generator=g) + 2
+    bias = torch.randn(B, N, h_kv * G, generator=g)
+    aux = {}
+    idx, sc = ops.online_softmax_topk_head(q.cuda(), lm.cuda(), lse.cuda(), K, S, W, q_offset=q_offset,
+                                           is_training=False, bias=bias.cuda(), G=(G if per_q else 1), _aux=aux)
+    keys = aux["rank_keys"].cpu()
+    assert torch.equal(idx.cpu(), orc.stable_topk_from_keys(keys, K))
+    ridx, rsc, raux = orc.topk_select(q.float(), lm.float(), lse, K, S, W, True, q_offset, bias=bias, return_aux=True)
+    check(keys, raux["keys"], F32, "rank keys", scale=50.0)
+    check(aux["lse_total"], raux["lse_total"], F32, "lse_total", scale=50.0)
+    assert (idx.cpu() == ridx).float().mean().item() >= 0.97
+    same = (idx.cpu() == ridx).all(-1)
+    check(sc.view(B, L, h_kv, G, K)[same], rsc[same], dtype, "scores", scale=(1.0 if dtype == BF else 50.0))
+
+
+@pytest.mark.parametrize("cfg", [(2, 1, 640, 2, 2, 64, 8), (1, 3, 512, 1, 4, 128, 4)])
+def test_sparse_decode_kernel_fp32(ops, cfg):
+    """The streaming decode form of the sparse chunk attention (few query rows, long store), fp32."""
+    B, L, T, H, G, D, K = cfg
+    g = torch.Generator().manual_seed(31)
+    S, N = 64, T // 64
+    q = torch.randn(B, L, H * G, D, generator=g)
+    k = torch.randn(B, T, H, D, generator=g)
+    v = torch.randn(B, T, H, D, generator=g)
+    idx = torch.stack([torch.randperm(N, generator=g)[:K].sort()[0] for _ in range(B * L * H)]).view(B, L, H, K).to(torch.int32)
+    idx[:, :, 0, -2:] = -1
+    w = torch.rand(B, L, H * G, K + 1, generator=g)
+    ref = orc.sparse_attn(q, k, v, w, idx, chunk_size=S, mask_last_token=True)
+    o = ops.HiLS_block_M_head(q.cuda(), k.cuda(), v.cuda(), w.cuda(), idx.cuda(), block_size=S, is_training=False,
+                              dtype="float")
+    check(o, ref, F32, "sparse decode", scale=5.0)
