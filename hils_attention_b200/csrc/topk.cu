@@ -405,11 +405,134 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
   }
 }
 
+// Logits of all chunk keys of one (batch, kv-head) for up to 16 query rows, bf16, on the warp-level
+// tensor-core path (mma.sync m16n8k16): the keys stream through a 3-stage cp.async ring of 64-key
+// tiles in shared memory; warp w owns keys 8w..8w+7 of every tile; the 16 x D query block stays in
+// registers as A fragments.  Decode scoring is a 1..16-row problem, far below a tcgen05 tile.
+constexpr int kDecTile = 64, kDecStages = 5;
+
+template <int NK>   // NK = D / 16
+__device__ __forceinline__ void decode_logits_bf16(const TopkParams& p, const bf16* q, const bf16* lmks, int b, int h,
+                                                   int lim, int G, int Npad, int HL, float* q_s, bf16* qb_s,
+                                                   bf16* tile_s, float* v_s, int tid) {
+  constexpr int D = NK * 16, RS = D + 8;                   // padded row (elements): conflict-free ldmatrix
+  constexpr int CPR = D / 8;                               // 16-byte pieces per key row
+  constexpr int NCP = kDecTile * CPR / 256;                // pieces per thread and tile
+  constexpr int RSTEP = 256 / CPR;                         // key rows between a thread's pieces
+  constexpr uint32_t kStageBytes = kDecTile * RS * 2;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int ng = p.per_qhead ? G : 1;
+  const int ntile = (lim + kDecTile - 1) / kDecTile;
+  const int row0 = tid / CPR, col0 = (tid % CPR) * 8;
+  const uint32_t tile_base = (uint32_t)__cvta_generic_to_shared(tile_s);
+  const uint32_t dst0 = tile_base + (uint32_t)(row0 * RS + col0) * 2u;
+  const int64_t key_stride = (int64_t)HL * D, step = key_stride * RSTEP, tile_step = key_stride * kDecTile;
+  const uint32_t b_off = (uint32_t)((warp * 8 + (lane & 7)) * RS + ((lane >> 3) & 1) * 8) * 2u;
+  for (int g0 = 0; g0 < ng; ++g0) {
+    const bf16* src = lmks + ((int64_t)b * p.N * HL + (p.per_qhead ? h * G + g0 : h)) * D + row0 * key_stride + col0;
+    int t_issue = 0, st_issue = 0;
+    auto issue = [&]() {
+      if (t_issue < ntile) {
+        const uint32_t dst = dst0 + (uint32_t)st_issue * kStageBytes;
+        const int row = t_issue * kDecTile + row0;
+#pragma unroll
+        for (int i = 0; i < NCP; ++i)
+          if (row + i * RSTEP < p.N)                      // rows past the last key stay stale: never candidates
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(i * RSTEP * RS * 2)),
+                         "l"(src + i * step) : "memory");
+        src += tile_step;
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      ++t_issue;
+      if (++st_issue == kDecStages) st_issue = 0;
+    };
+    for (int t = 0; t < kDecStages - 1; ++t) issue();
+    if (g0 == 0) {
+      // the query rows (fp32 copy for the returned scores, padded bf16 copy with a zero row for the
+      // A fragments) and the additive terms of the logits are staged while the first tiles are in flight
+      for (int i = tid; i < 17 * RS; i += 256) {
+        const int r = i / RS, d = i - r * RS;
+        const bool live = r < G && d < D;
+        const bf16 x = live ? q[r * D + d] : __float2bfloat16_rn(0.f);
+        qb_s[i] = x;
+        if (live) q_s[r * D + d] = __bfloat162float(x);
+      }
+      for (int g = 0; g < G; ++g)
+        for (int c = tid; c < Npad; c += 256) {
+          float add = 0.f;
+          if (c < lim) {
+            if (p.bias) add = p.bias[(((int64_t)b * p.N + c) * p.h_kv + h) * G + g];
+            if (p.gumbel) add += p.gumbel[(int64_t)(h * G + g) * p.N + c];
+          }
+          v_s[(size_t)g * Npad + c] = (c < ntile * kDecTile) ? add : -CUDART_INF_F;
+        }
+      __syncthreads();
+    }
+    // A fragments: rows = group members (shared keys) or the single member g0 (per-q-head keys)
+    uint32_t afrag[NK][4];
+    {
+      const int arow = (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
+      const int grow = p.per_qhead ? (arow == 0 ? g0 : 16) : arow;      // row 16 is the zero row
+      const uint32_t a32 = (uint32_t)__cvta_generic_to_shared(qb_s + grow * RS + acol);
+#pragma unroll
+      for (int kk = 0; kk < NK; ++kk)
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(afrag[kk][0]), "=r"(afrag[kk][1]), "=r"(afrag[kk][2]), "=r"(afrag[kk][3])
+                     : "r"(a32 + kk * 32));
+    }
+    // this thread's accumulator rows lane/4 and lane/4+8, columns 2*(lane%4)+{0,1} of the warp's 8 keys
+    const int r0 = lane >> 2;
+    const bool ok0 = p.per_qhead ? (r0 == 0) : (r0 < G), ok1 = !p.per_qhead && (r0 + 8 < G);
+    const int ccol = warp * 8 + (lane & 3) * 2;
+    float* cell0 = v_s + (size_t)(p.per_qhead ? g0 : r0) * Npad + ccol;
+    float* cell1 = v_s + (size_t)(p.per_qhead ? g0 : r0 + 8) * Npad + ccol;
+    int st_use = 0;
+    for (int t = 0; t < ntile; ++t) {
+      asm volatile("cp.async.wait_group %0;" ::"n"(kDecStages - 2) : "memory");
+      __syncthreads();
+      issue();
+      const uint32_t b32 = tile_base + (uint32_t)st_use * kStageBytes + b_off;
+      if (++st_use == kDecStages) st_use = 0;
+      float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};     // two chains over the k-steps
+#pragma unroll
+      for (int kk = 0; kk < NK; ++kk) {
+        uint32_t b0, b1;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(b32 + kk * 32));
+        if (kk & 1)
+          asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                       : "+f"(cb[0]), "+f"(cb[1]), "+f"(cb[2]), "+f"(cb[3])
+                       : "r"(afrag[kk][0]), "r"(afrag[kk][1]), "r"(afrag[kk][2]), "r"(afrag[kk][3]), "r"(b0), "r"(b1));
+        else
+          asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                       : "+f"(ca[0]), "+f"(ca[1]), "+f"(ca[2]), "+f"(ca[3])
+                       : "r"(afrag[kk][0]), "r"(afrag[kk][1]), "r"(afrag[kk][2]), "r"(afrag[kk][3]), "r"(b0), "r"(b1));
+      }
+      const int c = t * kDecTile + ccol;
+      if (ok0) {
+        float2* cell = reinterpret_cast<float2*>(cell0 + t * kDecTile);
+        float2 a = *cell;
+        a.x = (c < lim) ? __fmul_rn(ca[0] + cb[0], p.scale) + a.x : -CUDART_INF_F;
+        a.y = (c + 1 < lim) ? __fmul_rn(ca[1] + cb[1], p.scale) + a.y : -CUDART_INF_F;
+        *cell = a;
+      }
+      if (ok1) {
+        float2* cell = reinterpret_cast<float2*>(cell1 + t * kDecTile);
+        float2 a = *cell;
+        a.x = (c < lim) ? __fmul_rn(ca[2] + cb[2], p.scale) + a.x : -CUDART_INF_F;
+        a.y = (c + 1 < lim) ? __fmul_rn(ca[3] + cb[3], p.scale) + a.y : -CUDART_INF_F;
+        *cell = a;
+      }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+  }
+}
+
 // ---- selection for decode: few query rows against many chunk keys ----------------------------------
 // One CTA per (kv-head, batch, query row).  The chunk keys of that head are streamed once (16 lanes per
 // key row, 16-byte loads), logits go to shared memory, then log-sum-exp, ranking keys and the same
 // sort/merge selection as above, with the candidate tiles spread over the CTA's 8 warps.
-template <typename T>
+template <typename T, int NK>
 __global__ void __launch_bounds__(256) topk_decode_kernel(TopkParams p) {
   extern __shared__ __align__(16) float smem[];
   const int G = p.G, D = p.D, N = p.N, K = p.topk;
@@ -417,17 +540,32 @@ __global__ void __launch_bounds__(256) topk_decode_kernel(TopkParams p) {
   float* q_s = smem;                         // [G][D]
   float* v_s = q_s + G * D;                  // [G][Npad] selection logits
   float* key_s = v_s + (size_t)G * Npad;     // [Npad]
-  float* red_s = key_s + Npad;               // [16] + [G] lse_total
-  u64* list_s = reinterpret_cast<u64*>(red_s + 16 + ((G + 1) & ~1));  // [8][32]
+  float* red_s = key_s + Npad;               // [G][16] partial (max, sum) + [G] lse_total
+  u64* list_s = reinterpret_cast<u64*>(red_s + 16 * G + ((G + 1) & ~1));  // 2 KB of selection scratch
+  bf16* qb_s = reinterpret_cast<bf16*>(                               // bf16 path: [17][D+8] queries (+ zero row)
+      (reinterpret_cast<uintptr_t>(list_s + 8 * 32) + 15) & ~uintptr_t(15));
+  bf16* tile_s = qb_s + 17 * (D + 8);                                 // bf16 path: key tiles, kDecStages x [64][D+8]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int h = blockIdx.x, b = blockIdx.y, l = blockIdx.z;
   const T* q = static_cast<const T*>(p.q) + ((((int64_t)b * p.L + l) * p.h_kv + h) * G) * D;
   const T* lmks = static_cast<const T*>(p.lmks);
   const int HL = p.per_qhead ? p.h_kv * G : p.h_kv;
   const int lim = row_limit(p, l);
+  float ls_mine = 0.f;                        // thread g < G: lse of the sliding-window branch of member g
+  if (tid < G) {
+    const int64_t o = (((int64_t)b * p.L + l) * p.h_kv + h) * G + tid;
+    ls_mine = (p.lse_dtype == HILS_BF16) ? to_f(static_cast<const bf16*>(p.lse_swa)[o])
+                                         : static_cast<const float*>(p.lse_swa)[o];
+  }
+  // ---- logits ------------------------------------------------------------------------------------
+  constexpr bool kIsBf16 = sizeof(T) == 2;
+  if constexpr (kIsBf16) {
+    decode_logits_bf16<NK>(p, reinterpret_cast<const bf16*>(q), reinterpret_cast<const bf16*>(lmks), b, h, lim, G, Npad,
+                           HL, q_s, qb_s, tile_s, v_s, tid);
+  } else {
   for (int i = tid; i < G * D; i += 256) q_s[i] = to_f(q[i]);
   __syncthreads();
-  // ---- logits: half-warp per chunk key -------------------------------------------------------
+  // exact fp32 form: half-warp per chunk key
   const int hw = tid >> 4, sub = tid & 15, per = D / 16;
   const int ng = p.per_qhead ? G : 1;
   for (int cb = 0; cb < Npad; cb += 64) {                 // four key rows in flight per half-warp
@@ -468,100 +606,181 @@ __global__ void __launch_bounds__(256) topk_decode_kernel(TopkParams p) {
       }
     }
   }
-  __syncthreads();
-  // ---- log-sum-exp per group member, lse_total --------------------------------------------------
-  for (int g = 0; g < G; ++g) {
-    float m = -CUDART_INF_F;
-    for (int c = tid; c < lim; c += 256) m = fmaxf(m, v_s[(size_t)g * Npad + c]);
-    m = warp_max(m);
-    if (lane == 0) red_s[warp] = m;
-    __syncthreads();
-    m = red_s[0];
-    for (int w = 1; w < 8; ++w) m = fmaxf(m, red_s[w]);
-    float sum = 0.f;
-    if (m > -CUDART_INF_F)
-      for (int c = tid; c < lim; c += 256) sum += expf(v_s[(size_t)g * Npad + c] - m);
-    sum = warp_sum(sum);
-    if (lane == 0) red_s[8 + warp] = sum;
-    __syncthreads();
-    if (tid == 0) {
-      float tot = 0.f;
-      for (int w = 0; w < 8; ++w) tot += red_s[8 + w];
-      const float lh = (tot > 0.f) ? m + logf(tot) : -CUDART_INF_F;
-      const int64_t o = (((int64_t)b * p.L + l) * p.h_kv + h) * G + g;
-      const float ls = (p.lse_dtype == HILS_BF16) ? to_f(static_cast<const bf16*>(p.lse_swa)[o])
-                                                  : static_cast<const float*>(p.lse_swa)[o];
-      const float lt = log_add_exp(ls, lh);
-      red_s[16 + g] = lt;
-      if (p.lse_total) p.lse_total[o] = lt;
-    }
-    __syncthreads();
   }
-  // ---- ranking keys --------------------------------------------------------------------------------
+  __syncthreads();
+  // ---- log-sum-exp per group member (one online pass), lse_total ------------------------------------
+  for (int g = 0; g < G; ++g) {
+    float m = -CUDART_INF_F, sum = 0.f;
+    for (int c = tid; c < lim; c += 256) {
+      const float v = v_s[(size_t)g * Npad + c];
+      if (v > -CUDART_INF_F) {
+        const float nm = fmaxf(m, v);
+        sum = sum * __expf(m - nm) + __expf(v - nm);
+        m = nm;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, sum, o);
+      const float nm = fmaxf(m, om);
+      sum = (nm > -CUDART_INF_F) ? sum * __expf(m - nm) + os * __expf(om - nm) : 0.f;
+      m = nm;
+    }
+    if (lane == 0) { red_s[g * 16 + warp] = m; red_s[g * 16 + 8 + warp] = sum; }
+  }
+  __syncthreads();
+  if (tid < G) {
+    const float* r = red_s + tid * 16;
+    float m = r[0];
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, r[w]);
+    float tot = 0.f;
+    if (m > -CUDART_INF_F)
+      for (int w = 0; w < 8; ++w) tot += r[8 + w] * expf(r[w] - m);
+    const float lh = (tot > 0.f) ? m + logf(tot) : -CUDART_INF_F;
+    const float lt = log_add_exp(ls_mine, lh);
+    red_s[16 * G + tid] = lt;
+    if (p.lse_total) p.lse_total[(((int64_t)b * p.L + l) * p.h_kv + h) * G + tid] = lt;
+  }
+  __syncthreads();
+  // ---- ranking keys, kept as order-preserving bits (0 = not a candidate) -------------------------
+  uint32_t* bits_s = reinterpret_cast<uint32_t*>(key_s);
+  uint32_t* hist = reinterpret_cast<uint32_t*>(list_s);   // [256]
+  uint32_t* wsum = hist + 256;                            // [8]
+  uint32_t* ctl = wsum + 8;                               // [4]: prefix, remaining rank, done
+  int* sel_ids = reinterpret_cast<int*>(ctl + 4);         // [32]
   for (int c = tid; c < Npad; c += 256) {
     float key = -CUDART_INF_F;
     if (c < lim) {
       for (int g = 0; g < G; ++g) {
         const float v = v_s[(size_t)g * Npad + c];
-        if (v > -CUDART_INF_F) key = fmaxf(key, v - red_s[16 + g]);
+        if (v > -CUDART_INF_F) key = fmaxf(key, v - red_s[16 * G + g]);
       }
       if (p.drop_mask && p.drop_mask[((int64_t)b * p.L + l) * N + c] != 0) key = -CUDART_INF_F;
     }
-    key_s[c] = key;
+    bits_s[c] = (key > -CUDART_INF_F) ? order_bits(key) : 0u;   // false for NaN too
     if (p.rank_keys && c < N) p.rank_keys[(((int64_t)b * p.L + l) * p.h_kv + h) * N + c] = key;
   }
-  __syncthreads();
-  // ---- selection: each warp sorts its tiles of 128 and keeps a descending top-32 -------------------
-  u64 best = 0ull;
-  const int ntile = (lim + 127) >> 7;
-  for (int t = warp; t < ntile; t += 8) {
-    const int c0 = t * 128;
-    const float4 kk = *reinterpret_cast<const float4*>(key_s + c0 + lane * 4);
-    const float key[4] = {kk.x, kk.y, kk.z, kk.w};
-    u64 item[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      item[i] = (key[i] > -CUDART_INF_F)
-                    ? (((u64)order_bits(key[i]) << 32) | (0xFFFFFFFFu - (uint32_t)(c0 + lane * 4 + i))) : 0ull;
-    sort128_desc(item, lane);
-    u64 top = 0ull;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const u64 x = __shfl_sync(0xffffffffu, item[i], lane >> 2);
-      if ((lane & 3) == i) top = x;
-    }
-    const u64 rev = __shfl_sync(0xffffffffu, top, 31 - lane);
-    best = merge32_desc(max64(best, rev), lane);
-  }
-  list_s[warp * 32 + lane] = best;
-  __syncthreads();
-  if (warp == 0) {
-    for (int w = 1; w < 8; ++w) best = merge32_desc(max64(best, list_s[w * 32 + 31 - lane]), lane);
-    int id = (lane < K && best != 0ull) ? (int)(0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull)) : 0x7fffffff;
-    id = sort32_asc(id, lane);
-    if (id == 0x7fffffff) id = -1;
-    if (lane < K) {
-      p.indices[(((int64_t)b * p.L + l) * p.h_kv + h) * K + lane] = id;
-      T* scores = static_cast<T*>(p.scores);
-      for (int g = 0; g < G; ++g) {
-        float acc = 0.f;
-        if (id >= 0) acc = dot_row(q_s + g * D, lmks + (((int64_t)b * N + id) * HL + (p.per_qhead ? h * G + g : h)) * D, D);
-        scores[((((int64_t)b * p.L + l) * p.h_kv + h) * G + g) * K + lane] =
-            from_f<T>(id >= 0 ? acc * p.scale : -CUDART_INF_F);
+  if (tid < 32) sel_ids[tid] = -1;
+  // ---- the K-th largest key by radix select (8 bits per pass, most significant first) ---------------
+  // thr = bits of the K-th largest candidate, take = how many candidates equal to thr are selected
+  // (those with the lowest chunk ids); fewer than K candidates: thr = 0 and every candidate is taken.
+  uint32_t thr = 0u, mask = 0u;
+  int take = K;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    hist[tid] = 0u;
+    __syncthreads();
+    for (int c = tid; c < Npad; c += 256) {
+      const uint32_t u = bits_s[c];                       // whole warps run this loop together
+      const bool act = u != 0u && (u & mask) == thr;
+      const uint32_t digit = (u >> shift) & 255u;
+      const uint32_t among = __ballot_sync(0xffffffffu, act);
+      if (act) {                                          // one atomic per distinct digit in the warp
+        const uint32_t peers = __match_any_sync(among, digit);
+        if (lane == __ffs(peers) - 1) atomicAdd(&hist[digit], (uint32_t)__popc(peers));
       }
+    }
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t cnt[8], tot = 0u;                          // lane 0 holds the 8 highest digits
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { cnt[j] = hist[255 - (lane * 8 + j)]; tot += cnt[j]; }
+      uint32_t inc = tot;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t x = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += x;
+      }
+      const uint32_t exc = inc - tot;
+      const bool here = exc < (uint32_t)take && (uint32_t)take <= inc;
+      if (here) {
+        uint32_t run = exc;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (run < (uint32_t)take && (uint32_t)take <= run + cnt[j]) {
+            ctl[0] = thr | ((uint32_t)(255 - (lane * 8 + j)) << shift);
+            ctl[1] = (uint32_t)take - run;
+            ctl[2] = 0u;
+          }
+          run += cnt[j];
+        }
+      }
+      if (!__any_sync(0xffffffffu, here) && lane == 0) { ctl[0] = 0u; ctl[1] = 0u; ctl[2] = 1u; }
+    }
+    __syncthreads();
+    thr = ctl[0]; take = (int)ctl[1];
+    mask |= 0xFFu << shift;
+    if (ctl[2]) break;
+  }
+  // ---- compaction in chunk-id order: ids come out ascending ---------------------------------------------
+  {
+    const int per = (Npad + 255) >> 8, c0 = tid * per, c1 = min(c0 + per, Npad);
+    uint32_t n_gt = 0u, n_eq = 0u;
+    for (int c = c0; c < c1; ++c) {
+      const uint32_t u = bits_s[c];
+      n_gt += (u > thr) ? 1u : 0u;
+      n_eq += (u == thr && thr != 0u) ? 1u : 0u;
+    }
+    const uint32_t mine = (n_gt << 16) | n_eq;
+    uint32_t inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t x = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += x;
+    }
+    if (lane == 31) wsum[warp] = inc;
+    __syncthreads();
+    uint32_t before = inc - mine;
+    for (int w = 0; w < warp; ++w) before += wsum[w];
+    uint32_t eq_rank = before & 0xFFFFu;
+    int pos = (int)(before >> 16) + (int)min(eq_rank, (uint32_t)take);
+    for (int c = c0; c < c1; ++c) {
+      const uint32_t u = bits_s[c];
+      bool sel = u > thr;
+      if (u == thr && thr != 0u) { sel = eq_rank < (uint32_t)take; ++eq_rank; }
+      if (sel && pos < 32) sel_ids[pos++] = c;
+    }
+  }
+  __syncthreads();
+  // ---- ids and the raw scores of the selected chunks: eight lanes per chunk, four chunks per warp ------
+  for (int k0 = warp * 4; k0 < K; k0 += 32) {
+    const int k = k0 + (lane >> 3), sub = lane & 7;
+    const int id = (k < K) ? sel_ids[k] : -1;
+    if (sub == 0 && k < K) p.indices[(((int64_t)b * p.L + l) * p.h_kv + h) * K + k] = id;
+    T* scores = static_cast<T*>(p.scores);
+    for (int g = 0; g < G; ++g) {
+      float acc = 0.f;
+      if (id >= 0) {
+        const T* krow = lmks + (((int64_t)b * N + id) * HL + (p.per_qhead ? h * G + g : h)) * D;
+        for (int e = sub * 4; e < D; e += 32) {
+          const float4 x = load4(krow + e);
+          const float* qq = q_s + g * D + e;
+          acc = fmaf(qq[0], x.x, acc); acc = fmaf(qq[1], x.y, acc);
+          acc = fmaf(qq[2], x.z, acc); acc = fmaf(qq[3], x.w, acc);
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      if (sub == 0 && k < K)
+        scores[((((int64_t)b * p.L + l) * p.h_kv + h) * G + g) * K + k] =
+            from_f<T>(id >= 0 ? acc * p.scale : -CUDART_INF_F);
     }
   }
 }
 
-template <typename T>
+template <typename T, int NK>
 static int launch_topk_decode(const TopkParams& p, cudaStream_t st) {
   const int Npad = (p.N + 127) & ~127;
-  const size_t smem = ((size_t)p.G * p.D + (size_t)p.G * Npad + Npad + 16 + ((p.G + 1) & ~1)) * sizeof(float) +
-                      8 * 32 * sizeof(u64) + 16;
+  size_t smem = ((size_t)p.G * p.D + (size_t)p.G * Npad + Npad + 16 * p.G + ((p.G + 1) & ~1)) * sizeof(float) +
+                8 * 32 * sizeof(u64) + 16;
+  if (sizeof(T) == 2) {
+    if (p.G > 16) return HILS_ERR_UNSUPPORTED;            // one 16-row A tile holds the group
+    smem += (size_t)(17 + kDecStages * kDecTile) * (p.D + 8) * sizeof(bf16) + 16;
+  }
   if (smem > 200 * 1024) return HILS_ERR_UNSUPPORTED;
-  cudaFuncSetAttribute(topk_decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaFuncSetAttribute(topk_decode_kernel<T, NK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(p.h_kv, p.B, p.L);
-  topk_decode_kernel<T><<<grid, 256, smem, st>>>(p);
+  topk_decode_kernel<T, NK><<<grid, 256, smem, st>>>(p);
   HILS_LAUNCH_CHECK("topk_fwd (decode)");
   return HILS_OK;
 }
@@ -662,8 +881,10 @@ extern "C" int hils_topk_fwd(const void* q, const void* lmks, const void* lse_sw
   p.lse_dtype = lse_dtype; p.RW = 4; p.scale = sm_scale;
   cudaStream_t st = (cudaStream_t)stream;
   // few query rows against many chunk keys (decode, short chunk-prefill): stream the keys once per row
-  if (L <= 4 && N >= 512 && topk <= 32 && D % 16 == 0 && D / 16 <= 8 && (D / 16) % 4 == 0 && L <= 65535) {
-    const int rc = (dtype == HILS_BF16) ? launch_topk_decode<bf16>(p, st) : launch_topk_decode<float>(p, st);
+  if (L <= 4 && N >= 512 && topk <= 32 && (D == 64 || D == 128) && L <= 65535) {
+    const int rc = (dtype != HILS_BF16) ? launch_topk_decode<float, 0>(p, st)
+                   : (D == 128)         ? launch_topk_decode<bf16, 8>(p, st)
+                                        : launch_topk_decode<bf16, 4>(p, st);
     if (rc != HILS_ERR_UNSUPPORTED) return rc;
   }
   const int kpl = (topk + 31) / 32;
