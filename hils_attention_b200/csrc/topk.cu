@@ -405,6 +405,325 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
   }
 }
 
+// ---- selection for training / prefill shapes, bf16: scores on the warp-level tensor cores -------------
+// One CTA = RB consecutive tokens x G group members of one (batch, kv-head): M = RB*G score rows, held
+// member-major (row = g*RB + token).  The scaled scores of every candidate chunk of the CTA stay in
+// shared memory (fp32), so the keys are read once and nothing is recomputed: log-sum-exp per row, then
+// per token a warp builds the ranking keys, finds the K-th largest by bisection over the key bits
+// (warp-wide population counts), and compacts the selected ids in ascending order.
+constexpr int kSelTile = 128;     // candidates per key tile; warp w owns candidates 32w..32w+31 of a tile
+
+struct SelLayout {
+  int RB, M, Npad, RSV, NS;
+  size_t q_off, k_off, v_off, add_off, lt_off, lim_off, bits_off, total;
+};
+
+static SelLayout sel_layout(int G, int D, int N, int cta_tiles_max) {
+  SelLayout s;
+  s.RB = (G == 1) ? 64 : (G == 2) ? 32 : 16;
+  s.M = s.RB * G;
+  s.Npad = (N + kSelTile - 1) / kSelTile * kSelTile;
+  s.RSV = s.Npad + 8;                                      // row stride of the score rows (floats)
+  s.NS = cta_tiles_max > 1 ? 2 : 1;
+  size_t o = 0;
+  s.q_off = o;    o += (size_t)s.M * (D + 8) * 2;
+  s.k_off = o;    o += (size_t)s.NS * kSelTile * (D + 8) * 2;
+  s.v_off = o;    o += (size_t)s.M * s.RSV * 4;
+  s.add_off = o;  o += (size_t)G * s.Npad * 4;
+  s.lt_off = o;   o += (size_t)s.M * 4;
+  s.lim_off = o;  o += (size_t)s.RB * 4;
+  s.bits_off = o; o += (size_t)4 * s.Npad * 4;
+  s.total = o;
+  return s;
+}
+
+template <int NK>   // NK = D / 16
+__global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayout sl) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int D = NK * 16, RS = D + 8, CPR = D / 8;
+  const int G = p.G, RB = sl.RB, M = sl.M, Npad = sl.Npad, RSV = sl.RSV, K = p.topk;
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw + sl.q_off);        // [M][RS]
+  bf16* k_s = reinterpret_cast<bf16*>(smem_raw + sl.k_off);        // [NS][128][RS]
+  float* v_s = reinterpret_cast<float*>(smem_raw + sl.v_off);      // [M][RSV] scaled scores, -inf = no candidate
+  float* add_s = reinterpret_cast<float*>(smem_raw + sl.add_off);  // [G][Npad] bias + gumbel
+  float* lt_s = reinterpret_cast<float*>(smem_raw + sl.lt_off);    // [M] lse of the window branch, then lse_total
+  int* lim_s = reinterpret_cast<int*>(smem_raw + sl.lim_off);      // [RB] candidates of each token
+  uint32_t* bits_s = reinterpret_cast<uint32_t*>(smem_raw + sl.bits_off);  // [4 warps][Npad]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int l0 = blockIdx.x * RB, h = blockIdx.y, b = blockIdx.z;
+  const bf16* q = static_cast<const bf16*>(p.q);
+  const bf16* lmks = static_cast<const bf16*>(p.lmks);
+  const int HL = p.per_qhead ? p.h_kv * G : p.h_kv;
+  const bool has_add = p.bias || p.gumbel;
+  const int cta_limit = row_limit(p, min(l0 + RB, p.L) - 1);       // limits are non-decreasing in l
+  const int ntile = (cta_limit + kSelTile - 1) / kSelTile;
+  const int n_pass = p.per_qhead ? G : 1;
+  const int total = n_pass * ntile;
+
+  auto load_keys = [&](int it, int stage) {
+    const int pass = it / ntile, c0 = (it - pass * ntile) * kSelTile;
+    const bf16* src = lmks + ((int64_t)b * p.N * HL + (p.per_qhead ? h * G + pass : h)) * D;
+    bf16* dst = k_s + (size_t)stage * kSelTile * RS;
+    for (int i = tid; i < kSelTile * CPR; i += 128) {
+      const int row = i / CPR, col = (i - row * CPR) * 8;
+      if (c0 + row < p.N)                                  // rows past the last key stay stale: never candidates
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst + row * RS + col)),
+                     "l"(src + (int64_t)(c0 + row) * HL * D + col) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (total > 0) load_keys(0, 0);
+  // queries (member-major rows), per-token limits, lse of the window branch, additive terms
+  for (int i = tid; i < M * CPR; i += 128) {
+    const int row = i / CPR, col = (i - row * CPR) * 8;
+    const int g = row / RB, l = l0 + (row - g * RB);
+    uint4 x = make_uint4(0u, 0u, 0u, 0u);
+    if (l < p.L) x = *reinterpret_cast<const uint4*>(q + ((((int64_t)b * p.L + l) * p.h_kv + h) * G + g) * D + col);
+    *reinterpret_cast<uint4*>(q_s + row * RS + col) = x;
+  }
+  for (int t = tid; t < RB; t += 128) lim_s[t] = row_limit(p, l0 + t);
+  for (int row = tid; row < M; row += 128) {
+    const int g = row / RB, l = l0 + (row - g * RB);
+    float ls = 0.f;
+    if (l < p.L) {
+      const int64_t o = (((int64_t)b * p.L + l) * p.h_kv + h) * G + g;
+      ls = (p.lse_dtype == HILS_BF16) ? to_f(static_cast<const bf16*>(p.lse_swa)[o])
+                                      : static_cast<const float*>(p.lse_swa)[o];
+    }
+    lt_s[row] = ls;
+  }
+  if (has_add)
+    for (int g = 0; g < G; ++g)
+      for (int c = tid; c < ntile * kSelTile; c += 128) {
+        float x = 0.f;
+        if (c < p.N) {
+          if (p.bias) x += p.bias[(((int64_t)b * p.N + c) * p.h_kv + h) * G + g];
+          if (p.gumbel) x += p.gumbel[(int64_t)(h * G + g) * p.N + c];
+        }
+        add_s[g * Npad + c] = x;
+      }
+
+  // ---------------- scores: A = query rows, B = key tile, fp32 accumulators -> v_s --------------------------
+  const int mb_pass = p.per_qhead ? RB / 16 : M / 16;      // 16-row blocks multiplied with one key tile
+  const uint32_t q32 = (uint32_t)__cvta_generic_to_shared(q_s);
+  const uint32_t k32 = (uint32_t)__cvta_generic_to_shared(k_s);
+  const uint32_t a_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * RS + (lane >> 4) * 8) * 2u;
+  const uint32_t b_off = (uint32_t)((warp * 32 + (lane & 7) + ((lane >> 4) & 1) * 8) * RS + ((lane >> 3) & 1) * 8) * 2u;
+  for (int it = 0; it < total; ++it) {
+    const int stage = (sl.NS == 2) ? (it & 1) : 0;
+    if (sl.NS == 2 && it + 1 < total) {
+      load_keys(it + 1, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const int pass = it / ntile, c0 = (it - pass * ntile) * kSelTile;
+    const int cw = c0 + warp * 32;
+    if (cw < cta_limit) {
+      const uint32_t kb = k32 + (uint32_t)stage * (kSelTile * RS * 2) + b_off;
+      for (int mb0 = 0; mb0 < mb_pass; mb0 += 4) {
+        const int row_base = (p.per_qhead ? pass * RB : 0) + mb0 * 16;
+        const int nmb = min(4, mb_pass - mb0);
+        float acc[4][4][4];
+#pragma unroll
+        for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+          for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[mi][ni][e] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < NK; ++kk) {
+          uint32_t bfr[4][2];
+#pragma unroll
+          for (int np = 0; np < 2; ++np)                   // two 8-candidate blocks per ldmatrix.x4
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(bfr[2 * np][0]), "=r"(bfr[2 * np][1]), "=r"(bfr[2 * np + 1][0]), "=r"(bfr[2 * np + 1][1])
+                         : "r"(kb + (uint32_t)(np * 16 * RS * 2 + kk * 32)));
+#pragma unroll
+          for (int mi = 0; mi < 4; ++mi) {
+            if (mi < nmb) {
+              uint32_t a[4];
+              asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                           : "r"(q32 + (uint32_t)((row_base + mi * 16) * RS * 2 + kk * 32) + a_off));
+#pragma unroll
+              for (int ni = 0; ni < 4; ++ni)
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(acc[mi][ni][0]), "+f"(acc[mi][ni][1]), "+f"(acc[mi][ni][2]), "+f"(acc[mi][ni][3])
+                             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(bfr[ni][0]), "r"(bfr[ni][1]));
+            }
+          }
+        }
+        // accumulator rows lane/4 and lane/4+8 of each block, columns 2*(lane%4)+{0,1} of each 8-candidate block
+#pragma unroll
+        for (int mi = 0; mi < 4; ++mi) {
+          if (mi < nmb) {
+#pragma unroll
+            for (int hr = 0; hr < 2; ++hr) {
+              const int row = row_base + mi * 16 + (lane >> 2) + hr * 8;
+              const int lim = lim_s[row & (RB - 1)];
+              float* vrow = v_s + (size_t)row * RSV + cw + (lane & 3) * 2;
+#pragma unroll
+              for (int ni = 0; ni < 4; ++ni) {
+                const int c = cw + ni * 8 + (lane & 3) * 2;
+                float2 o;
+                o.x = (c < lim) ? __fmul_rn(acc[mi][ni][2 * hr], p.scale) : -CUDART_INF_F;
+                o.y = (c + 1 < lim) ? __fmul_rn(acc[mi][ni][2 * hr + 1], p.scale) : -CUDART_INF_F;
+                *reinterpret_cast<float2*>(vrow + ni * 8) = o;
+              }
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (sl.NS == 1 && it + 1 < total) load_keys(it + 1, 0);
+  }
+  if (total == 0) __syncthreads();
+
+  // ---------------- log-sum-exp of the selection logits per row, lse_total ---------------------------------
+  for (int row = warp; row < M; row += 4) {
+    const int g = row / RB, tok = row - g * RB, l = l0 + tok;
+    if (l >= p.L) continue;                                 // warp-uniform
+    const int lim = lim_s[tok];
+    const float* vrow = v_s + (size_t)row * RSV;
+    const float* arow = add_s + g * Npad;
+    float m = -CUDART_INF_F;
+    for (int c = lane; c < lim; c += 32) m = fmaxf(m, has_add ? vrow[c] + arow[c] : vrow[c]);
+    m = warp_max(m);
+    float sum = 0.f;
+    if (m > -CUDART_INF_F)
+      for (int c = lane; c < lim; c += 32) sum += expf((has_add ? vrow[c] + arow[c] : vrow[c]) - m);
+    sum = warp_sum(sum);
+    if (lane == 0) {
+      const float lh = (sum > 0.f) ? m + logf(sum) : -CUDART_INF_F;
+      const float lt = log_add_exp(lt_s[row], lh);
+      lt_s[row] = lt;
+      if (p.lse_total) p.lse_total[(((int64_t)b * p.L + l) * p.h_kv + h) * G + g] = lt;
+    }
+  }
+  __syncthreads();
+
+  // ---------------- per token: ranking keys, K-th largest by bisection, ordered compaction ------------------
+  uint32_t* bits = bits_s + warp * Npad;
+  bf16* scores = static_cast<bf16*>(p.scores);
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  for (int tok = warp; tok < RB; tok += 4) {
+    const int l = l0 + tok;
+    if (l >= p.L) continue;                                 // warp-uniform
+    const int lim = lim_s[tok];
+    const int lim32 = (lim + 31) & ~31;
+    const int key_end = p.rank_keys ? ((p.N + 31) & ~31) : lim32;
+    int n_cand = 0;
+    __syncwarp();
+    for (int c = lane; c < key_end; c += 32) {
+      float key = -CUDART_INF_F;
+      if (c < lim) {
+        for (int g = 0; g < G; ++g) {
+          float v = v_s[(size_t)(g * RB + tok) * RSV + c];
+          if (has_add) v += add_s[g * Npad + c];
+          if (v > -CUDART_INF_F) key = fmaxf(key, v - lt_s[g * RB + tok]);
+        }
+        if (p.drop_mask && p.drop_mask[((int64_t)b * p.L + l) * p.N + c] != 0) key = -CUDART_INF_F;
+      }
+      if (p.rank_keys && c < p.N) p.rank_keys[(((int64_t)b * p.L + l) * p.h_kv + h) * p.N + c] = key;
+      const uint32_t u = (key > -CUDART_INF_F) ? order_bits(key) : 0u;   // false for NaN too
+      if (c < lim32) bits[c] = u;
+      n_cand += (u != 0u) ? 1 : 0;
+    }
+    n_cand = __reduce_add_sync(0xffffffffu, n_cand);
+    __syncwarp();
+    // thr / take: chunks with bits > thr are selected, plus the `take` lowest-id chunks with bits == thr
+    uint32_t thr = 0u;
+    int take = 0;
+    if (n_cand > K) {
+      if (lim32 <= 128) {                                   // the whole row in registers
+        uint32_t u[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) u[i] = (lane + 32 * i < lim32) ? bits[lane + 32 * i] : 0u;
+        bool exact = false;
+        for (int bit = 31; bit >= 0; --bit) {
+          const uint32_t trial = thr | (1u << bit);
+          int cnt = (u[0] >= trial) + (u[1] >= trial) + (u[2] >= trial) + (u[3] >= trial);
+          cnt = __reduce_add_sync(0xffffffffu, cnt);
+          if (cnt >= K) {
+            thr = trial;
+            if (cnt == K) { exact = true; break; }
+          }
+        }
+        if (exact) {
+          thr -= 1u;                                        // bits > thr  <=>  bits >= trial: exactly K chunks
+        } else {
+          int gt = (u[0] > thr) + (u[1] > thr) + (u[2] > thr) + (u[3] > thr);
+          take = K - __reduce_add_sync(0xffffffffu, gt);
+        }
+      } else {
+        bool exact = false;
+        for (int bit = 31; bit >= 0; --bit) {
+          const uint32_t trial = thr | (1u << bit);
+          int cnt = 0;
+          for (int c = lane; c < lim32; c += 32) cnt += (bits[c] >= trial) ? 1 : 0;
+          cnt = __reduce_add_sync(0xffffffffu, cnt);
+          if (cnt >= K) {
+            thr = trial;
+            if (cnt == K) { exact = true; break; }
+          }
+        }
+        if (exact) {
+          thr -= 1u;
+        } else {
+          int gt = 0;
+          for (int c = lane; c < lim32; c += 32) gt += (bits[c] > thr) ? 1 : 0;
+          take = K - __reduce_add_sync(0xffffffffu, gt);
+        }
+      }
+    }
+    // compaction in chunk-id order
+    int32_t* out_ids = p.indices + (((int64_t)b * p.L + l) * p.h_kv + h) * K;
+    bf16* out_sc = scores + ((((int64_t)b * p.L + l) * p.h_kv + h) * G) * K;
+    int n_out = 0, eq_seen = 0;
+    for (int c0 = 0; c0 < lim32; c0 += 32) {
+      const int c = c0 + lane;
+      const uint32_t u = bits[c];
+      const bool is_eq = take > 0 && u == thr;
+      const uint32_t m_eq = __ballot_sync(0xffffffffu, is_eq);
+      const bool sel = (u > thr) || (is_eq && eq_seen + __popc(m_eq & lt_mask) < take);
+      const uint32_t m_sel = __ballot_sync(0xffffffffu, sel);
+      if (sel) {
+        const int pos = n_out + __popc(m_sel & lt_mask);
+        if (pos < K) {
+          out_ids[pos] = c;
+          for (int g = 0; g < G; ++g)
+            out_sc[g * K + pos] = __float2bfloat16_rn(v_s[(size_t)(g * RB + tok) * RSV + c]);
+        }
+      }
+      n_out += __popc(m_sel);
+      eq_seen += __popc(m_eq);
+    }
+    for (int pos = n_out + lane; pos < K; pos += 32) {
+      out_ids[pos] = -1;
+      for (int g = 0; g < G; ++g) out_sc[g * K + pos] = __float2bfloat16_rn(-CUDART_INF_F);
+    }
+  }
+}
+
+template <int NK>
+static int launch_topk_mma(const TopkParams& p, cudaStream_t st) {
+  // largest number of key tiles any CTA walks (the last tokens see the most chunks)
+  TopkParams hp = p;
+  const int max_lim = p.is_causal ? std::max(0, std::min(p.N, (p.window_size > 0)
+                          ? (p.q_offset + p.L - 1 - p.window_size + 1) / p.block_size
+                          : (p.q_offset + p.L - 1) / p.block_size)) : p.N;
+  const SelLayout sl = sel_layout(p.G, p.D, p.N, (max_lim + kSelTile - 1) / kSelTile);
+  if (sl.M > 256 || sl.total > 200 * 1024) return HILS_ERR_UNSUPPORTED;
+  cudaFuncSetAttribute(topk_fwd_mma_kernel<NK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sl.total);
+  dim3 grid((p.L + sl.RB - 1) / sl.RB, p.h_kv, p.B);
+  topk_fwd_mma_kernel<NK><<<grid, 128, sl.total, st>>>(hp, sl);
+  HILS_LAUNCH_CHECK("topk_fwd (tensor-core scores)");
+  return HILS_OK;
+}
+
 // Logits of all chunk keys of one (batch, kv-head) for up to 16 query rows, bf16, on the warp-level
 // tensor-core path (mma.sync m16n8k16): the keys stream through a 3-stage cp.async ring of 64-key
 // tiles in shared memory; warp w owns keys 8w..8w+7 of every tile; the 16 x D query block stays in
@@ -885,6 +1204,11 @@ extern "C" int hils_topk_fwd(const void* q, const void* lmks, const void* lse_sw
     const int rc = (dtype != HILS_BF16) ? launch_topk_decode<float, 0>(p, st)
                    : (D == 128)         ? launch_topk_decode<bf16, 8>(p, st)
                                         : launch_topk_decode<bf16, 4>(p, st);
+    if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  }
+  // bf16: scores on the tensor cores, the CTA's scores resident in shared memory
+  if (dtype == HILS_BF16 && (D == 64 || D == 128) && G <= 16 && topk <= N && L <= 65535 * 16) {
+    const int rc = (D == 128) ? launch_topk_mma<8>(p, st) : launch_topk_mma<4>(p, st);
     if (rc != HILS_ERR_UNSUPPORTED) return rc;
   }
   const int kpl = (topk + 31) / 32;

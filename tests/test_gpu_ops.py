@@ -147,6 +147,46 @@ def test_topk_selector_exact_and_match_rate(ops, cfg):
     check(sc.view(B, L, h_kv, G, K)[same], rsc[same], BF, "scores")
 
 
+@pytest.mark.parametrize("cfg", [
+    # B, L, h_kv, G, D, K, S, W, per_qhead, drop, gumbel
+    (1, 4096, 2, 1, 64, 32, 16, 32, False, False, False),      # N = 256: two key tiles, double-buffered
+    (1, 3000, 1, 4, 128, 8, 8, 24, True, True, False),         # per-q-head keys, N = 375, ragged tail, drop mask
+    (2, 1536, 2, 2, 64, 48, 16, 64, False, True, True),        # K > 32, gumbel noise
+    (1, 640, 1, 16, 64, 4, 32, 64, False, False, False),       # 256 score rows per CTA
+])
+def test_topk_tensor_core_scores_path(ops, cfg):
+    """bf16 training/prefill selection (scores on the tensor cores, scores resident in shared memory):
+    ids bit-exact against the stable selector fed the kernel's own ranking values, ranking values and
+    lse_total within tolerance of the oracle, >= 99% of the ids equal to the oracle's."""
+    B, L, h_kv, G, D, K, S, W, per_q, use_drop, use_gumbel = cfg
+    N = L // S
+    g = torch.Generator().manual_seed(23)
+    q = torch.randn(B, L, h_kv, G, D, generator=g).to(BF)
+    lm = torch.randn(B, N, h_kv * G if per_q else h_kv, D, generator=g).to(BF)
+    lse = torch.randn(B, L, h_kv * G, generator=g) + 2
+    bias = torch.randn(B, N, h_kv * G, generator=g)
+    drop = (torch.rand(B, L, N, generator=g) < 0.2).to(torch.int32) if use_drop else None
+    gum = torch.randn(1, 1, h_kv * G, N, generator=g) * 0.1 if use_gumbel else None
+    aux = {}
+    idx, sc = ops.online_softmax_topk_head(
+        q.cuda(), lm.cuda(), lse.cuda(), K, S, W, bias=bias.cuda(), G=(G if per_q else 1),
+        drop_mask=None if drop is None else drop.cuda(), gumbel_noise=None if gum is None else gum.cuda(), _aux=aux)
+    keys = aux["rank_keys"].cpu()
+    assert torch.equal(idx.cpu(), orc.stable_topk_from_keys(keys, K))
+    ridx, rsc, raux = orc.topk_select(q, lm, lse, K, S, W, True, 0, bias=bias, drop_mask=drop, gumbel_noise=gum,
+                                      return_aux=True)
+    check(keys, raux["keys"], F32, "rank keys", scale=20.0)
+    check(aux["lse_total"], raux["lse_total"], F32, "lse_total", scale=20.0)
+    assert (idx.cpu() == ridx).float().mean().item() >= 0.99
+    same = (idx.cpu() == ridx).all(-1)
+    check(sc.view(B, L, h_kv, G, K)[same], rsc[same], BF, "scores")
+    # without the auxiliary outputs the kernel walks only the candidates: same ids
+    idx2, _ = ops.online_softmax_topk_head(
+        q.cuda(), lm.cuda(), lse.cuda(), K, S, W, bias=bias.cuda(), G=(G if per_q else 1),
+        drop_mask=None if drop is None else drop.cuda(), gumbel_noise=None if gum is None else gum.cuda())
+    assert torch.equal(idx2, idx)
+
+
 def test_topk_ties_prefer_lower_id_and_padding(ops):
     """All chunk keys identical -> every candidate ties; the K lowest ids must win.  Rows with
     fewer than K candidates are -1 padded and their scores are -inf."""
