@@ -40,6 +40,10 @@ SIGNATURES = {
     "hils_swa_fwd": (_I, [_P] * 5 + [_I] * 11 + [_F, _I, _I, _P]),
     "hils_swa_bwd": (_I, [_P] * 10 + [_I] * 10 + [_F, _I, _P, _SZ, _P]),
     "hils_swa_bwd_workspace_bytes": (_SZ, [_I] * 8),
+    "hils_chunk_weights_fwd": (_I, [_P] * 5 + [_I] * 8 + [_P]),
+    "hils_chunk_weights_bwd": (_I, [_P] * 6 + [_I] * 8 + [_P]),
+    "hils_combine_fwd": (_I, [_P] * 4 + [_I] * 7 + [_P]),
+    "hils_combine_bwd": (_I, [_P] * 5 + [_I] * 7 + [_P]),
 }
 
 # kernels each entry point launches (memsets excluded); used to report launch counts
@@ -47,6 +51,7 @@ KERNELS_PER_CALL = {
     "hils_pool_fwd": 1, "hils_pool_bwd": 1, "hils_meanpool_fwd": 1, "hils_meanpool_bwd": 1,
     "hils_topk_fwd": 1, "hils_topk_bwd": 2, "hils_topk_bwd_noalloc": 2, "hils_sparse_attn_fwd": 1, "hils_sparse_attn_bwd": 3,
     "hils_chunk_logz_fwd": 1, "hils_chunk_logz_bwd": 2, "hils_swa_fwd": 1, "hils_swa_bwd": 2,
+    "hils_chunk_weights_fwd": 1, "hils_chunk_weights_bwd": 1, "hils_combine_fwd": 1, "hils_combine_bwd": 1,
 }
 _launches = 0
 

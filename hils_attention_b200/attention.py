@@ -142,25 +142,19 @@ class HiLSAttentionCore(torch.nn.Module):
             indices, scores = self.topk_func(
                 lmk_q, lmk_k, lse_sum, self.topk, block_size=S, window_size=W, is_training=self.training,
                 is_causal=True, q_offset=q_offset, G=lmk_k.shape[2] // h_kv, bias=prior_b)
-            if self.enable_prior_query and prior_b is not None:
-                K = indices.shape[-1]
-                g_kernel = prior_b.shape[2] // indices.shape[2]
-                idx_hq = indices.repeat_interleave(g_kernel, dim=2) if g_kernel != 1 else indices
-                src = prior_b.unsqueeze(-1).expand(-1, -1, -1, K)
-                gathered = torch.gather(src, dim=1, index=idx_hq.clamp_min(0).long())
-                scores = scores + gathered.to(scores.dtype)
-            if not self.enable_softmax1:
-                cat_scores = torch.cat([scores, lse_sum.unsqueeze(-1)], dim=-1)
-                swa_idx = -1
+            # prior-bias gather, concatenation with the window branch's lse and softmax: one kernel
+            chunk_weights = ops.inter_chunk_softmax(
+                scores, indices, lse_sum, prior_b if self.enable_prior_query else None, self.enable_softmax1)
+            swa_idx = -2 if self.enable_softmax1 else -1
+            if self.hils_func is ops.HiLS_block_M_head:
+                # sparse chunk attention and o = o_hils + w_swa * o_swa as one op
+                o_lower = ops.sparse_attn_combine(q, k, v, chunk_weights, indices, swa_o, swa_idx, block_size=S,
+                                                  mask_last_token=True, is_training=self.training)
+                hils_o = None
             else:
-                cat_scores = torch.cat([scores, lse_sum.unsqueeze(-1),
-                                        torch.zeros(B, L, scores.shape[2], 1, device=q.device, dtype=scores.dtype)],
-                                       dim=-1)
-                swa_idx = -2
-            chunk_weights = F.softmax(cat_scores, dim=-1).to(q.dtype)
-            hils_o = self.hils_func(q, k, v, weights=chunk_weights, indices=indices, block_size=S,
-                                    mask_last_token=True, is_training=self.training)
-            o_lower = torch.addcmul(hils_o, swa_o, chunk_weights[:, :, :, swa_idx].unsqueeze(-1))
+                hils_o = self.hils_func(q, k, v, weights=chunk_weights, indices=indices, block_size=S,
+                                        mask_last_token=True, is_training=self.training)
+                o_lower = torch.addcmul(hils_o, swa_o, chunk_weights[:, :, :, swa_idx].unsqueeze(-1))
             aux.update(indices=indices, scores=scores, weights=chunk_weights, lmk_k=lmk_k, prior_b=prior_b,
                        hils_o=hils_o)
         elif self.enable_softmax1:
@@ -171,7 +165,7 @@ class HiLSAttentionCore(torch.nn.Module):
             def unfold(t):
                 return t.reshape(L, B_orig, t.shape[2] // B_orig, *t.shape[3:]).transpose(0, 1)
             o_lower = unfold(o_lower)
-            aux = {n: (unfold(t) if n in ("indices", "scores", "weights", "lse_swa", "swa_o", "hils_o") else t)
+            aux = {n: (unfold(t) if n in ("indices", "scores", "weights", "lse_swa", "swa_o", "hils_o") and t is not None else t)
                    for n, t in aux.items()}
         return (o_lower, aux) if return_aux else o_lower
 

@@ -1,0 +1,341 @@
+// Inter-chunk softmax and the combination of the two attention branches, forward and backward.
+//
+// In the reference these steps are a dozen small PyTorch ops inside the attention module
+// (models/FlashHiLS/hils_attention.py:585-610 gather of the prior bias, concatenation with the
+// sliding-window log-sum-exp and softmax; :620-629 o = o_hils + w_swa * o_swa).  Here each direction
+// is one kernel per step: a warp owns one (batch, token, query head) row, so every tensor is read and
+// written once.  Roundings follow the reference's sequence of dtype casts: bias rounded to the score
+// dtype, the sum rounded to the score dtype, softmax in fp32 rounded once, gradients of the softmax
+// rounded to the score dtype before they fan out.
+#include "common.cuh"
+
+namespace hils {
+
+constexpr int kMaxCols = 96;        // K + 2 columns at most; 3 per lane
+constexpr int kRowsPerCta = 8;      // one warp per row
+
+constexpr int kBatch = 4;           // rows a warp has in flight
+
+template <typename T>
+__global__ void __launch_bounds__(32 * kRowsPerCta)
+chunk_weights_fwd_kernel(const T* __restrict__ scores, const int32_t* __restrict__ indices,
+                         const float* __restrict__ bias, const T* __restrict__ lse_swa, T* __restrict__ weights,
+                         uint32_t rows, int L, int N, int h_q, int h_idx, int K, int softmax1) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t r0 = (blockIdx.x * kRowsPerCta + (threadIdx.x >> 5)) * kBatch;
+  if (r0 >= rows) return;
+  const int g = h_q / h_idx;
+  const int ncol = K + 1 + (softmax1 ? 1 : 0);
+  float x[kBatch][3];
+  int id[kBatch][3];
+  // all loads of the batch first, then the arithmetic
+#pragma unroll
+  for (int j = 0; j < kBatch; ++j) {
+    const uint32_t r = min(r0 + j, rows - 1);
+    const uint32_t bl = r / (uint32_t)h_q, hq = r - bl * (uint32_t)h_q;
+    const int32_t* idx = indices + ((int64_t)bl * h_idx + hq / g) * K;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int c = lane + 32 * i;
+      float v = -CUDART_INF_F;
+      id[j][i] = 0;
+      if (c < K) {
+        v = to_f(scores[(int64_t)r * K + c]);
+        if (bias) id[j][i] = max(idx[c], 0);
+      } else if (c == K) {
+        v = to_f(lse_swa[r]);
+      } else if (c < ncol) {
+        v = 0.f;
+      }
+      x[j][i] = v;
+    }
+  }
+  if (bias) {
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const uint32_t r = min(r0 + j, rows - 1);
+      const uint32_t bl = r / (uint32_t)h_q, hq = r - bl * (uint32_t)h_q;
+      const int64_t b = bl / (uint32_t)L;
+#pragma unroll
+      for (int i = 0; i < 3; ++i)
+        if (lane + 32 * i < K)
+          x[j][i] = to_f(from_f<T>(x[j][i] + to_f(from_f<T>(bias[(b * N + id[j][i]) * h_q + hq]))));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kBatch; ++j) {
+    if (r0 + j >= rows) break;                            // warp-uniform
+    const float m = warp_max(fmaxf(fmaxf(x[j][0], x[j][1]), x[j][2]));
+    float e[3], sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      e[i] = (lane + 32 * i < ncol && m > -CUDART_INF_F) ? expf(x[j][i] - m) : 0.f;
+      sum += e[i];
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;                           // all -inf: 0/0 = NaN, as the reference's softmax
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int c = lane + 32 * i;
+      if (c < ncol) weights[(int64_t)(r0 + j) * ncol + c] = from_f<T>(e[i] * inv);
+    }
+  }
+}
+
+// d_x = w * (d_w - sum(w * d_w)), rounded to T; columns [0,K) -> d_scores and (scattered) d_bias,
+// column K -> d_lse.  A CTA owns kTokPerCta tokens of one (batch, query head): the bias gradient is
+// accumulated per chunk id in shared memory and leaves the CTA as one atomic per touched chunk.
+constexpr int kTokPerCta = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(32 * kRowsPerCta)
+chunk_weights_bwd_kernel(const T* __restrict__ weights, const T* __restrict__ d_weights,
+                         const int32_t* __restrict__ indices, T* __restrict__ d_scores, T* __restrict__ d_lse,
+                         float* __restrict__ d_bias, int L, int N, int h_q, int h_idx, int K, int softmax1,
+                         int bias_in_smem) {
+  extern __shared__ float acc_s[];                          // [N] when bias_in_smem
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int hq = blockIdx.y;
+  const int64_t b = blockIdx.z;
+  const int l0 = blockIdx.x * kTokPerCta, l1 = min(l0 + kTokPerCta, L);
+  const int g = h_q / h_idx;
+  const int ncol = K + 1 + (softmax1 ? 1 : 0);
+  if (bias_in_smem) {
+    for (int c = threadIdx.x; c < N; c += 32 * kRowsPerCta) acc_s[c] = 0.f;
+    __syncthreads();
+  }
+  for (int lb = l0 + warp * kBatch; lb < l1; lb += kRowsPerCta * kBatch) {
+    float w[kBatch][3], dw[kBatch][3];
+    int id[kBatch][3];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {                     // all loads of the batch first
+      const int l = min(lb + j, l1 - 1);
+      const int64_t bl = b * L + l, r = bl * h_q + hq;
+      const int32_t* idx = indices + (bl * h_idx + hq / g) * K;
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int c = lane + 32 * i;
+        w[j][i] = (c < ncol) ? to_f(weights[r * ncol + c]) : 0.f;
+        dw[j][i] = (c < ncol) ? to_f(d_weights[r * ncol + c]) : 0.f;
+        id[j][i] = (d_bias && c < K) ? idx[c] : -1;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (lb + j >= l1) break;                              // warp-uniform
+      const int64_t r = (b * L + lb + j) * h_q + hq;
+      float dot = fmaf(w[j][0], dw[j][0], fmaf(w[j][1], dw[j][1], w[j][2] * dw[j][2]));
+      dot = warp_sum(dot);
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int c = lane + 32 * i;
+        if (c >= ncol) continue;
+        const T dx = from_f<T>(w[j][i] * (dw[j][i] - dot));
+        if (c < K) {
+          d_scores[r * K + c] = dx;
+          if (id[j][i] >= 0) {
+            if (bias_in_smem) atomicAdd(acc_s + id[j][i], to_f(dx));
+            else atomicAdd(d_bias + (b * N + id[j][i]) * h_q + hq, to_f(dx));
+          }
+        } else if (c == K) {
+          d_lse[r] = dx;
+        }
+      }
+    }
+  }
+  if (bias_in_smem) {
+    __syncthreads();
+    for (int c = threadIdx.x; c < N; c += 32 * kRowsPerCta) {
+      const float x = acc_s[c];
+      if (x != 0.f) atomicAdd(d_bias + (b * N + c) * h_q + hq, x);
+    }
+  }
+}
+
+// Both combine kernels give a row to a group of 2^lg lanes (4 elements per lane and step) and keep
+// kBatch rows per group in flight.
+// o = o_hils + o_swa * w[:, swa_col]
+template <typename T>
+__global__ void __launch_bounds__(256)
+combine_fwd_kernel(const T* o_h, const T* __restrict__ o_swa, const T* __restrict__ weights,
+                   T* o,   // o may alias o_h (in place)
+                   uint32_t rows, int D, int ncol, int swa_col, int lg) {
+  const uint32_t gid = blockIdx.x * 256u + threadIdx.x;
+  const uint32_t r0 = (gid >> lg) * kBatch;
+  const int d0 = (int)(gid & ((1u << lg) - 1u)) * 4, dstep = 4 << lg;
+  if (r0 >= rows) return;
+  for (int d = d0; d < D; d += dstep) {
+    float4 a[kBatch], x[kBatch];
+    float w[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int64_t r = min(r0 + j, rows - 1);
+      a[j] = load4(o_h + r * D + d);
+      x[j] = load4(o_swa + r * D + d);
+      w[j] = to_f(weights[r * ncol + swa_col]);
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j)
+      if (r0 + j < rows)
+        store4(o + (int64_t)(r0 + j) * D + d, make_float4(fmaf(x[j].x, w[j], a[j].x), fmaf(x[j].y, w[j], a[j].y),
+                                                          fmaf(x[j].z, w[j], a[j].z), fmaf(x[j].w, w[j], a[j].w)));
+  }
+}
+
+// d_o_swa = d_o * w_swa;  d_w[:, swa_col] = sum_d d_o * o_swa
+template <typename T>
+__global__ void __launch_bounds__(256)
+combine_bwd_kernel(const T* __restrict__ d_o, const T* __restrict__ o_swa, const T* __restrict__ weights,
+                   T* __restrict__ d_o_swa, T* __restrict__ d_weights, uint32_t rows, int D, int ncol, int swa_col,
+                   int lg) {
+  const uint32_t gid = blockIdx.x * 256u + threadIdx.x;
+  const uint32_t r0 = (gid >> lg) * kBatch;
+  const int d0 = (int)(gid & ((1u << lg) - 1u)) * 4, dstep = 4 << lg;
+  float dot[kBatch];
+#pragma unroll
+  for (int j = 0; j < kBatch; ++j) dot[j] = 0.f;
+  if (r0 < rows) {
+    for (int d = d0; d < D; d += dstep) {
+      float4 g[kBatch], x[kBatch];
+      float w[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const int64_t r = min(r0 + j, rows - 1);
+        g[j] = load4(d_o + r * D + d);
+        x[j] = load4(o_swa + r * D + d);
+        w[j] = to_f(weights[r * ncol + swa_col]);
+      }
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        dot[j] = fmaf(g[j].x, x[j].x, fmaf(g[j].y, x[j].y, fmaf(g[j].z, x[j].z, fmaf(g[j].w, x[j].w, dot[j]))));
+        if (r0 + j < rows)
+          store4(d_o_swa + (int64_t)(r0 + j) * D + d,
+                 make_float4(g[j].x * w[j], g[j].y * w[j], g[j].z * w[j], g[j].w * w[j]));
+      }
+    }
+  }
+  // groups are aligned inside the warp: reduce over the 2^lg lanes of a group
+#pragma unroll
+  for (int j = 0; j < kBatch; ++j) {
+    for (int o = 1; o < (1 << lg); o <<= 1) dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
+    if (d0 == 0 && r0 + j < rows) d_weights[(int64_t)(r0 + j) * ncol + swa_col] = from_f<T>(dot[j]);
+  }
+}
+
+}  // namespace hils
+
+using namespace hils;
+
+extern "C" int hils_chunk_weights_fwd(const void* scores, const int32_t* indices, const float* bias,
+                                      const void* lse_swa, void* weights, int B, int L, int N, int h_q, int h_idx,
+                                      int K, int softmax1, int dtype, void* stream) {
+  HILS_REQUIRE(dtype == HILS_BF16 || dtype == HILS_F32, "chunk_weights_fwd: dtype must be bf16 or fp32");
+  HILS_REQUIRE(K >= 1 && K + 2 <= kMaxCols, "chunk_weights_fwd: topk must be in [1, 94]");
+  HILS_REQUIRE(h_idx >= 1 && h_q % h_idx == 0, "chunk_weights_fwd: h_q must be a multiple of the index heads");
+  const int64_t rows = (int64_t)B * L * h_q;
+  if (rows == 0) return HILS_OK;
+  HILS_REQUIRE(scores && indices && lse_swa && weights, "chunk_weights_fwd: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  HILS_REQUIRE(rows < (int64_t)1 << 31, "chunk_weights_fwd: more than 2^31 rows");
+  const unsigned grid = (unsigned)((rows + kRowsPerCta * kBatch - 1) / (kRowsPerCta * kBatch));
+  if (dtype == HILS_BF16)
+    chunk_weights_fwd_kernel<bf16><<<grid, 32 * kRowsPerCta, 0, st>>>(
+        (const bf16*)scores, indices, bias, (const bf16*)lse_swa, (bf16*)weights, (uint32_t)rows, L, N, h_q, h_idx, K,
+        softmax1);
+  else
+    chunk_weights_fwd_kernel<float><<<grid, 32 * kRowsPerCta, 0, st>>>(
+        (const float*)scores, indices, bias, (const float*)lse_swa, (float*)weights, (uint32_t)rows, L, N, h_q, h_idx,
+        K, softmax1);
+  HILS_LAUNCH_CHECK("chunk_weights_fwd");
+  return HILS_OK;
+}
+
+extern "C" int hils_chunk_weights_bwd(const void* weights, const void* d_weights, const int32_t* indices,
+                                      void* d_scores, void* d_lse, float* d_bias, int B, int L, int N, int h_q,
+                                      int h_idx, int K, int softmax1, int dtype, void* stream) {
+  HILS_REQUIRE(dtype == HILS_BF16 || dtype == HILS_F32, "chunk_weights_bwd: dtype must be bf16 or fp32");
+  HILS_REQUIRE(K >= 1 && K + 2 <= kMaxCols, "chunk_weights_bwd: topk must be in [1, 94]");
+  HILS_REQUIRE(h_idx >= 1 && h_q % h_idx == 0, "chunk_weights_bwd: h_q must be a multiple of the index heads");
+  const int64_t rows = (int64_t)B * L * h_q;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (d_bias) {
+    const cudaError_t e = cudaMemsetAsync(d_bias, 0, sizeof(float) * (size_t)B * N * h_q, st);
+    if (e != cudaSuccess) return cuda_fail(e, "chunk_weights_bwd (memset)");
+  }
+  if (rows == 0) return HILS_OK;
+  HILS_REQUIRE(weights && d_weights && indices && d_scores && d_lse, "chunk_weights_bwd: null pointer");
+  HILS_REQUIRE(h_q <= 65535 && B <= 65535, "chunk_weights_bwd: more than 65535 heads or sequences");
+  const int in_smem = d_bias && (size_t)N * 4 <= 96 * 1024;
+  const size_t smem = in_smem ? (size_t)N * 4 : 0;
+  dim3 grid((L + kTokPerCta - 1) / kTokPerCta, h_q, B);
+  if (dtype == HILS_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(chunk_weights_bwd_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    chunk_weights_bwd_kernel<bf16><<<grid, 32 * kRowsPerCta, smem, st>>>(
+        (const bf16*)weights, (const bf16*)d_weights, indices, (bf16*)d_scores, (bf16*)d_lse, d_bias, L, N, h_q, h_idx,
+        K, softmax1, in_smem);
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(chunk_weights_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    chunk_weights_bwd_kernel<float><<<grid, 32 * kRowsPerCta, smem, st>>>(
+        (const float*)weights, (const float*)d_weights, indices, (float*)d_scores, (float*)d_lse, d_bias, L, N, h_q,
+        h_idx, K, softmax1, in_smem);
+  }
+  HILS_LAUNCH_CHECK("chunk_weights_bwd");
+  return HILS_OK;
+}
+
+static int lanes_log2(int D) {            // lanes per row: the smallest power of two >= D/4, at most 32
+  int lg = 0;
+  while ((4 << lg) < D && lg < 5) ++lg;
+  return lg;
+}
+
+extern "C" int hils_combine_fwd(const void* o_hils, const void* o_swa, const void* weights, void* o, int B, int L,
+                                int h_q, int D, int num_weights, int swa_col, int dtype, void* stream) {
+  HILS_REQUIRE(dtype == HILS_BF16 || dtype == HILS_F32, "combine_fwd: dtype must be bf16 or fp32");
+  HILS_REQUIRE(D % 4 == 0, "combine_fwd: D must be a multiple of 4");
+  HILS_REQUIRE(swa_col >= 0 && swa_col < num_weights, "combine_fwd: swa_col out of range");
+  const int64_t rows = (int64_t)B * L * h_q;
+  if (rows == 0) return HILS_OK;
+  HILS_REQUIRE(rows < (int64_t)1 << 31, "combine_fwd: more than 2^31 rows");
+  HILS_REQUIRE(o_hils && o_swa && weights && o, "combine_fwd: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int lg = lanes_log2(D);
+  const int64_t threads = ((rows + kBatch - 1) / kBatch) << lg;
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  if (dtype == HILS_BF16)
+    combine_fwd_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)o_hils, (const bf16*)o_swa, (const bf16*)weights,
+                                                   (bf16*)o, (uint32_t)rows, D, num_weights, swa_col, lg);
+  else
+    combine_fwd_kernel<float><<<grid, 256, 0, st>>>((const float*)o_hils, (const float*)o_swa, (const float*)weights,
+                                                    (float*)o, (uint32_t)rows, D, num_weights, swa_col, lg);
+  HILS_LAUNCH_CHECK("combine_fwd");
+  return HILS_OK;
+}
+
+extern "C" int hils_combine_bwd(const void* d_o, const void* o_swa, const void* weights, void* d_o_swa,
+                                void* d_weights, int B, int L, int h_q, int D, int num_weights, int swa_col,
+                                int dtype, void* stream) {
+  HILS_REQUIRE(dtype == HILS_BF16 || dtype == HILS_F32, "combine_bwd: dtype must be bf16 or fp32");
+  HILS_REQUIRE(D % 4 == 0, "combine_bwd: D must be a multiple of 4");
+  HILS_REQUIRE(swa_col >= 0 && swa_col < num_weights, "combine_bwd: swa_col out of range");
+  const int64_t rows = (int64_t)B * L * h_q;
+  if (rows == 0) return HILS_OK;
+  HILS_REQUIRE(rows < (int64_t)1 << 31, "combine_bwd: more than 2^31 rows");
+  HILS_REQUIRE(d_o && o_swa && weights && d_o_swa && d_weights, "combine_bwd: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int lg = lanes_log2(D);
+  const int64_t threads = ((rows + kBatch - 1) / kBatch) << lg;
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  if (dtype == HILS_BF16)
+    combine_bwd_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)d_o, (const bf16*)o_swa, (const bf16*)weights,
+                                                   (bf16*)d_o_swa, (bf16*)d_weights, (uint32_t)rows, D, num_weights,
+                                                   swa_col, lg);
+  else
+    combine_bwd_kernel<float><<<grid, 256, 0, st>>>((const float*)d_o, (const float*)o_swa, (const float*)weights,
+                                                    (float*)d_o_swa, (float*)d_weights, (uint32_t)rows, D, num_weights,
+                                                    swa_col, lg);
+  HILS_LAUNCH_CHECK("combine_bwd");
+  return HILS_OK;
+}

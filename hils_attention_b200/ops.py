@@ -282,7 +282,8 @@ def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
 
 class _SparseChunkAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, weights, indices, block_size, sm_scale, mask_last_token, is_training, slope):
+    def forward(ctx, q, k, v, weights, indices, block_size, sm_scale, mask_last_token, is_training, slope,
+                swa_o=None, swa_col=-1):
         assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
         assert weights.is_contiguous() and indices.is_contiguous()
         B, L, HQ, D = q.shape
@@ -307,11 +308,17 @@ class _SparseChunkAttention(torch.autograd.Function):
         ws = _workspace(ws_bytes, q.device)
         call("hils_sparse_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(w), ptr(idx), ptr(slope_dev), ptr(o), *dims, nw,
              int(block_size), float(sm_scale), int(bool(mask_last_token)), dt, ptr(ws), ws_bytes, stream())
+        swa_col = int(swa_col) % nw if swa_o is not None else -1
+        if swa_o is not None:
+            # o <- o + w[..., swa_col] * swa_o (models/FlashHiLS/hils_attention.py:620-629), in place
+            assert swa_o.shape == o.shape and swa_o.dtype == o.dtype and swa_o.is_contiguous()
+            call("hils_combine_fwd", ptr(o), ptr(swa_o), ptr(w), ptr(o), B, L, HQ, Dv, nw, swa_col, dt, stream())
         ctx.is_training = bool(is_training)
         if is_training:
-            ctx.save_for_backward(q, k, v, w, idx, slope_dev if slope_dev is not None else q.new_empty(0))
+            ctx.save_for_backward(q, k, v, w, idx, slope_dev if slope_dev is not None else q.new_empty(0),
+                                  swa_o if swa_o is not None else q.new_empty(0))
             ctx.meta = (dims, nw, int(block_size), float(sm_scale), int(bool(mask_last_token)), dt,
-                        slope_dev is not None, weights.dtype)
+                        slope_dev is not None, weights.dtype, swa_col)
         return o
 
     @staticmethod
@@ -320,8 +327,8 @@ class _SparseChunkAttention(torch.autograd.Function):
             raise RuntimeError(
                 "HiLS_block_M_head: the forward ran with is_training=False, which keeps nothing for "
                 "the backward pass; call it with is_training=True to differentiate.")
-        q, k, v, w, idx, slope_dev = ctx.saved_tensors
-        dims, nw, S, scale, mask_last, dt, has_slope, w_dtype = ctx.meta
+        q, k, v, w, idx, slope_dev, swa_o = ctx.saved_tensors
+        dims, nw, S, scale, mask_last, dt, has_slope, w_dtype, swa_col = ctx.meta
         B, L, T, HQ, H, D, Dv, K = dims
         do = do.contiguous().to(q.dtype)
         d_q = torch.empty_like(q)
@@ -333,7 +340,12 @@ class _SparseChunkAttention(torch.autograd.Function):
         call("hils_sparse_attn_bwd", ptr(q), ptr(k), ptr(v), ptr(w), ptr(idx), ptr(slope_dev) if has_slope else None,
              ptr(do), ptr(d_q), ptr(d_k), ptr(d_v), ptr(d_w), *dims, nw, S, scale, mask_last, dt, ptr(ws),
              ws_bytes, stream())
-        return d_q, d_k, d_v, d_w.to(w_dtype), None, None, None, None, None, None
+        d_swa_o = None
+        if swa_col >= 0:
+            d_swa_o = torch.empty_like(swa_o)
+            call("hils_combine_bwd", ptr(do), ptr(swa_o), ptr(w), ptr(d_swa_o), ptr(d_w), B, L, HQ, Dv, nw, swa_col,
+                 dt, stream())
+        return d_q, d_k, d_v, d_w.to(w_dtype), None, None, None, None, None, None, d_swa_o, None
 
 
 def HiLS_block_M_head(q, k, v, weights, indices, block_size=64, sm_scale=None, block_M=None,
@@ -352,12 +364,74 @@ def HiLS_block_M_head(q, k, v, weights, indices, block_size=64, sm_scale=None, b
     assert D == Dk, f"Q head_dim ({D}) must equal K head_dim ({Dk})"
     assert HQ % H == 0, f"HQ={HQ} must be divisible by H={H}"
     return _SparseChunkAttention.apply(q, k, v, weights, indices, block_size, sm_scale, mask_last_token,
-                                       is_training, slope)
+                                       is_training, slope, None, -1)
 
 
 # ------------------------------------------------------------------------------------------
 # exact per-chunk log Z
 # ------------------------------------------------------------------------------------------
+
+def sparse_attn_combine(q, k, v, weights, indices, swa_o, swa_col=-1, block_size=64, sm_scale=None,
+                        mask_last_token=True, is_training=True, slope=None):
+    """Sparse chunk attention followed by the combination with the sliding-window branch,
+    ``HiLS_block_M_head(...) + weights[..., swa_col, None] * swa_o`` (models/FlashHiLS/hils_attention.py:619-629),
+    as one differentiable op: the weight column of the window branch gets its gradient in the same
+    tensor the sparse backward fills, and no intermediate is materialised."""
+    return _SparseChunkAttention.apply(q.contiguous(), k.contiguous(), v.contiguous(), weights.contiguous(),
+                                       indices.contiguous(), int(block_size), sm_scale, mask_last_token,
+                                       is_training, slope, swa_o.contiguous(), int(swa_col))
+
+
+class _ChunkWeights(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, scores, indices, lse_swa, prior_b, softmax1):
+        B, L, HQ, K = scores.shape
+        h_idx = indices.shape[2]
+        assert indices.shape == (B, L, h_idx, K) and HQ % h_idx == 0
+        assert lse_swa.shape == (B, L, HQ), f"lse_swa shape {tuple(lse_swa.shape)} != ({B}, {L}, {HQ})"
+        dt = dtype_code(scores)
+        sc = scores.contiguous()
+        idx = (indices if indices.dtype == torch.int32 else indices.to(torch.int32)).contiguous()
+        lse = lse_swa.to(scores.dtype).contiguous()
+        N = 0
+        pb = None
+        if prior_b is not None:
+            N = prior_b.shape[1]
+            assert prior_b.shape == (B, N, HQ), f"prior_b shape {tuple(prior_b.shape)} != ({B}, {N}, {HQ})"
+            pb = prior_b.to(torch.float32).contiguous()
+        ncol = K + 1 + (1 if softmax1 else 0)
+        w = torch.empty((B, L, HQ, ncol), dtype=scores.dtype, device=scores.device)
+        call("hils_chunk_weights_fwd", ptr(sc), ptr(idx), ptr(pb), ptr(lse), ptr(w), B, L, N, HQ, h_idx, K,
+             int(bool(softmax1)), dt, stream())
+        ctx.save_for_backward(w, idx)
+        ctx.meta = (B, L, N, HQ, h_idx, K, int(bool(softmax1)), dt, prior_b is not None,
+                    None if prior_b is None else prior_b.dtype, lse_swa.dtype)
+        return w
+
+    @staticmethod
+    def backward(ctx, dw):
+        w, idx = ctx.saved_tensors
+        B, L, N, HQ, h_idx, K, softmax1, dt, has_pb, pb_dtype, lse_dtype = ctx.meta
+        want_db = has_pb and ctx.needs_input_grad[3]
+        dw = dw.contiguous().to(w.dtype)
+        d_sc = torch.empty((B, L, HQ, K), dtype=w.dtype, device=w.device)
+        d_lse = torch.empty((B, L, HQ), dtype=w.dtype, device=w.device)
+        d_pb = torch.empty((B, N, HQ), dtype=torch.float32, device=w.device) if want_db else None
+        call("hils_chunk_weights_bwd", ptr(w), ptr(dw), ptr(idx), ptr(d_sc), ptr(d_lse), ptr(d_pb), B, L, N, HQ,
+             h_idx, K, softmax1, dt, stream())
+        return d_sc, None, d_lse.to(lse_dtype), (None if d_pb is None else d_pb.to(pb_dtype)), None
+
+
+def inter_chunk_softmax(scores, indices, lse_swa, prior_b=None, softmax1=False):
+    """Weights of the selected chunks and of the sliding-window branch
+    (models/FlashHiLS/hils_attention.py:585-610): softmax over [scores + prior_b[ids], lse_swa(, 0)].
+
+    scores (B,L,h_q,K) and lse_swa (B,L,h_q) in the activation dtype, indices (B,L,h_kv,K) int32 with
+    -1 for empty slots, prior_b (B,N,h_q) fp32 or None.  Returns (B,L,h_q,K+1[+1]) in scores' dtype;
+    differentiable with respect to scores, lse_swa and prior_b."""
+    return _ChunkWeights.apply(scores, indices, lse_swa, prior_b, bool(softmax1))
+
+
 class _ExactChunkLogZ(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, chunk_size, window_size, sm_scale, mask_lmk):

@@ -181,6 +181,37 @@ int hils_swa_bwd(const void* q, const void* k, const void* v, const void* o, con
 size_t hils_swa_bwd_workspace_bytes(int B, int L, int h_q, int h_kv, int D, int Dv, int chunk_size,
                                     int dtype);
 
+/* ---------------------------------------------------------------------------------------
+ * Inter-chunk softmax.  Replaces the PyTorch ops of HiLSAttention.forward that turn the selection
+ * scores into chunk weights (models/FlashHiLS/hils_attention.py:585-610): gather of the prior bias
+ * at the selected ids, add, concatenation with the sliding-window log-sum-exp (and a zero column
+ * when softmax1 != 0), softmax over K+1(+1) columns.
+ *   scores (B,L,h_q,K) and lse_swa (B,L,h_q) in `dtype`; indices (B,L,h_idx,K) int32, h_q a multiple
+ *   of h_idx, -1 = empty slot; bias (B,N,h_q) fp32 or NULL; weights (B,L,h_q,K+1+softmax1) in `dtype`.
+ *   Backward: d_scores (B,L,h_q,K) and d_lse (B,L,h_q) in `dtype`; d_bias (B,N,h_q) fp32 or NULL, zeroed
+ *   here and accumulated with atomics.  K <= 94.
+ * ------------------------------------------------------------------------------------- */
+int hils_chunk_weights_fwd(const void* scores, const int32_t* indices, const float* bias,
+                           const void* lse_swa, void* weights,
+                           int B, int L, int N, int h_q, int h_idx, int K, int softmax1, int dtype,
+                           void* stream);
+int hils_chunk_weights_bwd(const void* weights, const void* d_weights, const int32_t* indices,
+                           void* d_scores, void* d_lse, float* d_bias,
+                           int B, int L, int N, int h_q, int h_idx, int K, int softmax1, int dtype,
+                           void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Combination of the two branches, o = o_hils + weights[..., swa_col] * o_swa.  Replaces the
+ * torch.addcmul of HiLSAttention.forward (models/FlashHiLS/hils_attention.py:620-629).
+ *   o_hils, o_swa, o, d_o, d_o_swa (B,L,h_q,D) and weights, d_weights (B,L,h_q,num_weights) in `dtype`.
+ *   Backward writes d_o_swa and the single column d_weights[..., swa_col]; the gradient of o_hils is d_o.
+ * ------------------------------------------------------------------------------------- */
+int hils_combine_fwd(const void* o_hils, const void* o_swa, const void* weights, void* o,
+                     int B, int L, int h_q, int D, int num_weights, int swa_col, int dtype, void* stream);
+int hils_combine_bwd(const void* d_o, const void* o_swa, const void* weights, void* d_o_swa,
+                     void* d_weights,
+                     int B, int L, int h_q, int D, int num_weights, int swa_col, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -475,3 +475,68 @@ def test_sparse_decode_kernel_fp32(ops, cfg):
     o = ops.HiLS_block_M_head(q.cuda(), k.cuda(), v.cuda(), w.cuda(), idx.cuda(), block_size=S, is_training=False,
                               dtype="float")
     check(o, ref, F32, "sparse decode", scale=5.0)
+
+
+# ------------------------------------------------------------------ inter-chunk softmax, branch combination
+@pytest.mark.parametrize("cfg", [
+    # B, L, N, h_q, h_idx, K, softmax1, dtype
+    (2, 70, 9, 4, 2, 8, False, BF),
+    (1, 33, 40, 6, 6, 32, True, BF),
+    (1, 20, 80, 2, 1, 64, False, F32),
+    (1, 17, 5, 4, 4, 3, True, F32),
+])
+def test_inter_chunk_softmax(ops, cfg):
+    B, L, N, HQ, HI, K, sm1, dtype = cfg
+    g = torch.Generator().manual_seed(31)
+    sc0 = torch.randn(B, L, HQ, K, generator=g).to(dtype)
+    idx = torch.stack([torch.stack([torch.stack([torch.randperm(N, generator=g)[:min(K, N)].sort().values
+                                                 if K <= N else torch.arange(K) % N
+                                                 for _ in range(HI)]) for _ in range(L)]) for _ in range(B)]).int()
+    pad = torch.rand(B, L, HI, generator=g) < 0.3                  # rows with empty slots at the end
+    n_pad = torch.randint(1, K, (B, L, HI), generator=g)
+    slot = torch.arange(K).view(1, 1, 1, K)
+    empty = pad.unsqueeze(-1) & (slot >= (K - n_pad).unsqueeze(-1))
+    idx = idx.masked_fill(empty, -1)
+    sc0 = sc0.masked_fill(empty.repeat_interleave(HQ // HI, dim=2), float("-inf"))
+    lse0 = torch.randn(B, L, HQ, generator=g).to(dtype)
+    pb0 = torch.randn(B, N, HQ, generator=g)
+    dw = torch.randn(B, L, HQ, K + 1 + int(sm1), generator=g).to(dtype)
+    sc, lse, pb = sc0.cuda().requires_grad_(True), lse0.cuda().requires_grad_(True), pb0.cuda().requires_grad_(True)
+    w = ops.inter_chunk_softmax(sc, idx.cuda(), lse, pb, sm1)
+    assert w.dtype == dtype and w.shape == (B, L, HQ, K + 1 + int(sm1))
+    w.backward(dw.cuda())
+    scr, lser, pbr = sc0.clone().requires_grad_(True), lse0.clone().requires_grad_(True), pb0.clone().requires_grad_(True)
+    wr = orc.inter_chunk_weights(scr, idx, lser, pbr, softmax1=sm1)
+    wr.backward(dw)
+    check(w, wr, dtype, "weights")
+    check(sc.grad, scr.grad, dtype, "d_scores")
+    check(lse.grad, lser.grad, dtype, "d_lse")
+    check(pb.grad, pbr.grad, dtype, "d_prior_b", scale=4.0)
+    # without a prior bias
+    w2 = ops.inter_chunk_softmax(sc0.cuda(), idx.cuda(), lse0.cuda(), None, sm1)
+    check(w2, orc.inter_chunk_weights(sc0, idx, lse0, None, softmax1=sm1), dtype, "weights (no bias)")
+
+
+@pytest.mark.parametrize("dtype", [BF, F32])
+def test_sparse_attn_combine_matches_separate_ops(ops, dtype):
+    """The fused op equals HiLS_block_M_head followed by addcmul, forward and backward."""
+    g = torch.Generator().manual_seed(32)
+    B, L, HQ, H, D, S, K = 1, 256, 4, 2, 64, 32, 4
+    N = L // S
+    q0, k0, v0, so0 = [torch.randn(B, L, h, D, generator=g).to(dtype) for h in (HQ, H, H, HQ)]
+    w0 = torch.softmax(torch.randn(B, L, HQ, K + 2, generator=g), -1).to(dtype)
+    idx = torch.stack([torch.stack([torch.stack([torch.randperm(N, generator=g)[:K].sort().values
+                                                 for _ in range(H)]) for _ in range(L)]) for _ in range(B)]).int().cuda()
+    do = torch.randn(B, L, HQ, D, generator=g).to(dtype).cuda()
+    outs = []
+    for fused in (True, False):
+        q, k, v, w, so = [t.cuda().requires_grad_(True) for t in (q0, k0, v0, w0, so0)]
+        if fused:
+            o = ops.sparse_attn_combine(q, k, v, w, idx, so, -2, block_size=S)
+        else:
+            oh = ops.HiLS_block_M_head(q, k, v, w, idx, block_size=S)
+            o = torch.addcmul(oh, so, w[..., -2].unsqueeze(-1))
+        o.backward(do)
+        outs.append([o.detach()] + [t.grad for t in (q, k, v, w, so)])
+    for a, b, n in zip(outs[0], outs[1], ("o", "dq", "dk", "dv", "dw", "d_swa_o")):
+        check(a, b, dtype, n, scale=2.0 if n == "dw" else 1.0)
