@@ -1144,8 +1144,9 @@ __global__ void __launch_bounds__(128) topk_bwd_kernel(
   }
 }
 
-int topk_bwd_dk_tc_launch(const void* d_scores, const int32_t* indices, const void* q, void* d_lmks, int B, int L, int N,
-                          int h_kv, int G, int D, int topk, int per_qhead, float scale, cudaStream_t st);  // topk_tc.cu
+int topk_bwd_mma_launch(const void* d_scores, const int32_t* indices, const void* q, const void* lmks, void* d_q,
+                        float* dl, int B, int L, int N, int h_kv, int G, int D, int topk, int per_qhead, float scale,
+                        cudaStream_t st);  // topk_bwd_mma.cu
 
 template <typename T, int KPL>
 static int launch_topk(const TopkParams& p, cudaStream_t st) {
@@ -1231,16 +1232,16 @@ extern "C" int hils_topk_bwd(const void* d_scores, const int32_t* indices, const
   cudaStream_t st = (cudaStream_t)stream;
   const int HL = per_qhead ? h_kv * G : h_kv;
   const int64_t nl = (int64_t)B * N * HL * D;
-  if (dtype == HILS_BF16 && nl > 0 && L > 0) {
-    // tensor-core path: chunk-key gradient without atomics or an fp32 accumulator, then the K-sparse gather for dq
+  if (dtype == HILS_BF16 && nl > 0 && L > 0 && (D == 64 || D == 128) && d_lmks_f32) {
+    // dense 64 x 128 tiles of the score gradient in shared memory, both products on the tensor cores
     HILS_REQUIRE(d_scores && indices && q && lmks && d_q && d_lmks, "topk_bwd: null pointer");
-    const int rc = topk_bwd_dk_tc_launch(d_scores, indices, q, d_lmks, B, L, N, h_kv, G, D, topk, per_qhead, sm_scale, st);
+    cudaError_t e = cudaMemsetAsync(d_lmks_f32, 0, nl * sizeof(float), st);
+    if (e != cudaSuccess) return cuda_fail(e, "topk_bwd memset");
+    const int rc = topk_bwd_mma_launch(d_scores, indices, q, lmks, d_q, d_lmks_f32, B, L, N, h_kv, G, D, topk, per_qhead,
+                                       sm_scale, st);
     if (rc == HILS_OK) {
-      const int64_t rows = (int64_t)B * L * h_kv * G;
-      topk_bwd_kernel<bf16><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>((const bf16*)d_scores, indices, (const bf16*)q,
-                                                                       (const bf16*)lmks, (bf16*)d_q, nullptr, L, N, h_kv,
-                                                                       G, D, topk, per_qhead, sm_scale, rows);
-      HILS_LAUNCH_CHECK("topk_bwd dq");
+      launch_cast_from_f32<bf16>(d_lmks_f32, (bf16*)d_lmks, nl, st);
+      HILS_LAUNCH_CHECK("topk_bwd cast");
       return HILS_OK;
     }
     if (rc != HILS_ERR_UNSUPPORTED) return rc;

@@ -1,0 +1,241 @@
+// Backward of the selection scores, bf16, on the warp-level tensor cores.
+//
+// scores[i,g,k] = scale * q[i,g] . k'[id(i,k)]  (ops/topk_head_softmax.py:1040-1092 scatters the score
+// gradient into a dense (rows x N) matrix and runs two batched matrix products).  Here the dense matrix
+// exists only as a 64 x 128 tile in shared memory: a CTA walks blocks of 64 (token, member) rows of one
+// (batch, key head), scatters their K score gradients into the tile and multiplies
+//     dq  [64 x D]  = tile     [64 x 128] . k' [128 x D]
+//     dk' [128 x D] += tile^T  [128 x 64] . q  [64 x D]
+// with mma.sync m16n8k16.  With a single 128-candidate tile (N <= 128) the dk' accumulators stay in
+// registers over all row blocks of the CTA and leave as one fp32 vector atomic per element pair.
+#include "common.cuh"
+
+namespace hils {
+
+struct TopkBwdMmaParams {
+  const bf16* ds; const int32_t* ids; const bf16* q; const bf16* lmks;
+  bf16* dq; float* dl;
+  int L, N, h_kv, G, K, per_qhead;
+  float scale;
+};
+
+constexpr int kBwdRows = 64;       // rows per block
+constexpr int kBwdBlocks = 8;      // row blocks per CTA
+constexpr int kBwdTile = 128;      // candidates per tile
+constexpr int kDsStride = kBwdTile + 8;
+
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int NK>   // NK = D / 16
+__global__ void __launch_bounds__(256) topk_bwd_mma_kernel(TopkBwdMmaParams p) {
+  constexpr int D = NK * 16, RS = D + 8, NB = D / 8, CPR = D / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* ds_s = reinterpret_cast<bf16*>(smem_raw);                // [64][136] score gradients, dense over one tile
+  bf16* k_s = ds_s + kBwdRows * kDsStride;                       // [128][RS] chunk keys of the tile
+  bf16* q_s = k_s + kBwdTile * RS;                               // [64][RS] query rows of the block
+  __shared__ int max_id_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int members = p.per_qhead ? 1 : p.G;                     // rows per token in this CTA
+  const int hl = blockIdx.y;                                     // key head
+  const int h = p.per_qhead ? hl / p.G : hl, g_fixed = p.per_qhead ? hl % p.G : 0;
+  const int HL = p.per_qhead ? p.h_kv * p.G : p.h_kv;
+  const int64_t b = blockIdx.z;
+  const int n_rows = p.L * members;                              // rows of this (batch, key head)
+  const int cta_row0 = blockIdx.x * kBwdRows * kBwdBlocks;
+  const int ntile_all = (p.N + kBwdTile - 1) / kBwdTile;
+  const bool keep_dk = ntile_all == 1;                           // dk' accumulators live across the row blocks
+  const uint32_t ds32 = (uint32_t)__cvta_generic_to_shared(ds_s);
+  const uint32_t k32 = (uint32_t)__cvta_generic_to_shared(k_s);
+  const uint32_t q32 = (uint32_t)__cvta_generic_to_shared(q_s);
+
+  auto row_ptrs = [&](int r, int64_t& row_index, int64_t& tok_head) {   // r: row inside this (b, head)
+    const int l = r / members, gi = p.per_qhead ? g_fixed : r - l * members;
+    tok_head = (b * p.L + l) * p.h_kv + h;
+    row_index = tok_head * p.G + gi;
+  };
+  auto load_keys = [&](int c0) {
+    for (int i = tid; i < kBwdTile * CPR; i += 256) {
+      const int row = i / CPR, col = (i - row * CPR) * 8;
+      uint4 x = make_uint4(0u, 0u, 0u, 0u);
+      if (c0 + row < p.N) x = *reinterpret_cast<const uint4*>(p.lmks + ((b * p.N + c0 + row) * HL + hl) * D + col);
+      *reinterpret_cast<uint4*>(k_s + row * RS + col) = x;
+    }
+  };
+  float dk[NB][4];                                               // warp w: candidates 16w..16w+15 of the tile
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dk[nb][e] = 0.f;
+  auto flush_dk = [&](int c0) {
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      const int c = c0 + warp * 16 + (lane >> 2) + hr * 8;
+      if (c < p.N) {
+        float* dst = p.dl + ((b * p.N + c) * HL + hl) * D + (lane & 3) * 2;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          const float2 v = make_float2(dk[nb][2 * hr] * p.scale, dk[nb][2 * hr + 1] * p.scale);
+          if (v.x != 0.f || v.y != 0.f) atomicAdd(reinterpret_cast<float2*>(dst + nb * 8), v);
+        }
+      }
+    }
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dk[nb][e] = 0.f;
+  };
+  if (keep_dk) load_keys(0);
+
+  for (int blk = 0; blk < kBwdBlocks; ++blk) {
+    const int r0 = cta_row0 + blk * kBwdRows;
+    if (r0 >= n_rows) break;
+    __syncthreads();                                             // previous block's tiles are consumed
+    if (tid == 0) max_id_s = -1;
+    for (int i = tid; i < kBwdRows * CPR; i += 256) {
+      const int row = i / CPR, col = (i - row * CPR) * 8;
+      uint4 x = make_uint4(0u, 0u, 0u, 0u);
+      if (r0 + row < n_rows) {
+        int64_t ri, th;
+        row_ptrs(r0 + row, ri, th);
+        x = *reinterpret_cast<const uint4*>(p.q + ri * D + col);
+      }
+      *reinterpret_cast<uint4*>(q_s + row * RS + col) = x;
+    }
+    __syncthreads();
+    {  // largest selected id of the block -> number of candidate tiles to visit
+      const int row = tid >> 2;
+      int mx = -1;
+      if (r0 + row < n_rows) {
+        int64_t ri, th;
+        row_ptrs(r0 + row, ri, th);
+        for (int k = tid & 3; k < p.K; k += 4) mx = max(mx, p.ids[th * p.K + k]);
+      }
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      if ((tid & 3) == 0 && mx >= 0) atomicMax(&max_id_s, mx);
+    }
+    __syncthreads();
+    const int max_id = max_id_s;
+    const int ntile = max_id < 0 ? 0 : min(ntile_all, max_id / kBwdTile + 1);
+    float dq[NB / 2][4];                                         // warp w: rows 16(w&3).., d-half (w>>2)
+#pragma unroll
+    for (int nb = 0; nb < NB / 2; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dq[nb][e] = 0.f;
+    for (int t = 0; t < ntile; ++t) {
+      const int c0 = t * kBwdTile;
+      if (t > 0 || !keep_dk) {
+        __syncthreads();                                         // the previous tile is consumed
+        if (!keep_dk) load_keys(c0);
+      }
+      for (int i = tid; i < kBwdRows * kDsStride / 8; i += 256) reinterpret_cast<uint4*>(ds_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+      __syncthreads();
+      {  // scatter: four threads per row
+        const int row = tid >> 2;
+        if (r0 + row < n_rows) {
+          int64_t ri, th;
+          row_ptrs(r0 + row, ri, th);
+          for (int k = tid & 3; k < p.K; k += 4) {
+            const int id = p.ids[th * p.K + k];
+            if (id >= c0 && id < c0 + kBwdTile && id < p.N) ds_s[row * kDsStride + id - c0] = p.ds[ri * p.K + k];
+          }
+        }
+      }
+      __syncthreads();
+      // dq += tile . k'
+      {
+        const int mrow = (warp & 3) * 16, nhalf = (warp >> 2) * (D / 2);
+        const uint32_t a_addr = ds32 + (uint32_t)((mrow + (lane & 7) + ((lane >> 3) & 1) * 8) * kDsStride + (lane >> 4) * 8) * 2u;
+        const uint32_t b_addr = k32 + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * RS + nhalf + ((lane >> 4) & 1) * 8) * 2u;
+#pragma unroll
+        for (int kk = 0; kk < kBwdTile / 16; ++kk) {
+          uint32_t a[4];
+          ldsm4(a, a_addr + kk * 32);
+#pragma unroll
+          for (int np = 0; np < NB / 4; ++np) {
+            uint32_t bb[4];
+            ldsm4_t(bb, b_addr + (uint32_t)(kk * 16 * RS + np * 16) * 2u);
+            mma16816(dq[2 * np], a, bb[0], bb[1]);
+            mma16816(dq[2 * np + 1], a, bb[2], bb[3]);
+          }
+        }
+      }
+      // dk' += tile^T . q
+      {
+        const int mcol = warp * 16;                              // candidates of this warp
+        const uint32_t a_addr = ds32 + (uint32_t)(((lane & 7) + ((lane >> 4) & 1) * 8) * kDsStride + mcol + ((lane >> 3) & 1) * 8) * 2u;
+        const uint32_t b_addr = q32 + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * RS + ((lane >> 4) & 1) * 8) * 2u;
+#pragma unroll
+        for (int kk = 0; kk < kBwdRows / 16; ++kk) {
+          uint32_t a[4];
+          ldsm4_t(a, a_addr + (uint32_t)(kk * 16 * kDsStride) * 2u);
+#pragma unroll
+          for (int np = 0; np < NB / 2; ++np) {
+            uint32_t bb[4];
+            ldsm4_t(bb, b_addr + (uint32_t)(kk * 16 * RS + np * 16) * 2u);
+            mma16816(dk[2 * np], a, bb[0], bb[1]);
+            mma16816(dk[2 * np + 1], a, bb[2], bb[3]);
+          }
+        }
+      }
+      if (!keep_dk) flush_dk(c0);
+    }
+    // dq rows of the block
+    {
+      const int mrow = (warp & 3) * 16, nhalf = (warp >> 2) * (D / 2);
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr) {
+        const int r = r0 + mrow + (lane >> 2) + hr * 8;
+        if (r < n_rows) {
+          int64_t ri, th;
+          row_ptrs(r, ri, th);
+          bf16* dst = p.dq + ri * D + nhalf + (lane & 3) * 2;
+#pragma unroll
+          for (int nb = 0; nb < NB / 2; ++nb)
+            *reinterpret_cast<__nv_bfloat162*>(dst + nb * 8) =
+                __floats2bfloat162_rn(dq[nb][2 * hr] * p.scale, dq[nb][2 * hr + 1] * p.scale);
+        }
+      }
+    }
+  }
+  if (keep_dk) flush_dk(0);
+}
+
+// d_q in bf16; dl: fp32 accumulator of the chunk-key gradient, zeroed by the caller.
+int topk_bwd_mma_launch(const void* d_scores, const int32_t* indices, const void* q, const void* lmks, void* d_q,
+                        float* dl, int B, int L, int N, int h_kv, int G, int D, int topk, int per_qhead, float scale,
+                        cudaStream_t st) {
+  if (D != 64 && D != 128) return HILS_ERR_UNSUPPORTED;
+  const int HL = per_qhead ? h_kv * G : h_kv;
+  if (HL > 65535 || B > 65535) return HILS_ERR_UNSUPPORTED;
+  TopkBwdMmaParams p;
+  p.ds = (const bf16*)d_scores; p.ids = indices; p.q = (const bf16*)q; p.lmks = (const bf16*)lmks;
+  p.dq = (bf16*)d_q; p.dl = dl;
+  p.L = L; p.N = N; p.h_kv = h_kv; p.G = G; p.K = topk; p.per_qhead = per_qhead; p.scale = scale;
+  const int n_rows = L * (per_qhead ? 1 : G);
+  dim3 grid((n_rows + kBwdRows * kBwdBlocks - 1) / (kBwdRows * kBwdBlocks), HL, B);
+  const size_t smem = (size_t)(kBwdRows * kDsStride + (kBwdTile + kBwdRows) * (D + 8)) * sizeof(bf16);
+  if (D == 64) {
+    cudaFuncSetAttribute(topk_bwd_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    topk_bwd_mma_kernel<4><<<grid, 256, smem, st>>>(p);
+  } else {
+    cudaFuncSetAttribute(topk_bwd_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    topk_bwd_mma_kernel<8><<<grid, 256, smem, st>>>(p);
+  }
+  HILS_LAUNCH_CHECK("topk_bwd (tensor-core)");
+  return HILS_OK;
+}
+
+}  // namespace hils

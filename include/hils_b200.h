@@ -92,8 +92,9 @@ int hils_topk_fwd(const void* q, const void* lmks, const void* lse_swa, const fl
                   float sm_scale, int dtype, int lse_dtype, void* stream);
 
 /* Gradient of the returned scores (SoftmaxTopKMaxPoolingFusedFn.backward, :1040-1092, which
- * scatters into a dense (B,h_kv,G,L,N) tensor and runs two bmm).  Here: a K-sparse gather for
- * dq and an fp32 scatter-add for the chunk keys.
+ * scatters into a dense (B,h_kv,G,L,N) tensor and runs two bmm).  Here, bf16 with D = 64 or 128: the
+ * dense matrix exists only as 64 x 128 tiles in shared memory and both products run on the tensor
+ * cores; otherwise a K-sparse gather for dq and an fp32 scatter-add for the chunk keys.
  *   d_scores (B,L,h_kv*G,topk) in `dtype`; d_q (B,L,h_kv,G,D) in `dtype`;
  *   d_lmks_f32: fp32 accumulator with the shape of lmks, zeroed by this call;
  *   d_lmks: same shape in `dtype` (written from the accumulator). */
