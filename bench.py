@@ -11,7 +11,8 @@ combine, and the backward of all of it.  With N > 1 every rank runs the same sha
 batch (the path shards by batch/head with no collective): weak scaling, value = total tokens/s.
 
 Prints ONE JSON line.  `value` is timed with inputs resident in HBM; `e2e` times the same step
-through the public API with pinned HOST buffers (q, k, v, dO copied in; o, dq, dk, dv copied out).
+through the public API with pinned HOST buffers (q, k, v, dO copied in; o, dq, dk, dv copied out
+every step, copies of neighbouring steps overlapped with compute by hils_attention_b200.host_pipeline).
 `roofline` is for the dominant kernel, timed alone with CUDA events on the launch stream.
 `--impl reference` times the CPU restatement of the reference's PyTorch path (oracle/) on the host
 cores on a bounded sample of the same workload.
@@ -338,23 +339,22 @@ def main():
     value = world * B * T / (ms_step / 1e3)
 
     # ---- end to end through the public API with pinned host buffers ----------------------------
-    out_host = [torch.empty_like(h) for h in (host[0], host[0], host[1], host[2])]
-    dbuf = [torch.empty_like(t) for t in (q, k, v, do)]
-
-    def e2e_step():
-        for d, h in zip(dbuf, host):
-            d.copy_(h, non_blocking=True)
-        outs = step(*dbuf)
-        for h, o in zip(out_host, outs):
-            h.copy_(o, non_blocking=True)
-
-    e2e_step()
+    # every step copies q, k, v, dO in and o, dq, dk, dv out; the package's HostPipeline runs the copies
+    # of neighbouring steps on their own streams so that they overlap this step's kernels
+    from hils_attention_b200.host_pipeline import HostPipeline
+    out_host = [torch.empty_like(h).pin_memory() for h in (host[0], host[0], host[1], host[2])]
+    pipe = HostPipeline(step, host, dev, depth=2)
+    for _ in range(2):
+        pipe.submit(host, out_host)
+    pipe.drain()
     barrier()
-    n_e2e = max(2, min(args.steps, 5))
+    n_e2e = max(4, min(args.steps, 8))
     e0.record()
     for _ in range(n_e2e):
-        e2e_step()
+        pipe.submit(host, out_host)
+    pipe.join_stream()
     e1.record()
+    pipe.drain()
     barrier()
     ms_e2e = e0.elapsed_time(e1)
     if world > 1:

@@ -135,3 +135,34 @@ def test_full_size_properties(B):
         o3 = hb.HiLS_block_M_head(qd, kd, vd, (0.5 * w.float()).to(BF), idx, block_size=S, is_training=False)
         check(o3, 0.5 * o1.float(), BF, "linearity in weights")
         assert torch.isfinite(o.float()).all()
+
+
+@pytest.mark.gpu
+def test_host_pipeline_matches_direct_steps():
+    """Steps fed from pinned host memory through HostPipeline give the results of the same steps run
+    directly, for every queued batch (copies of neighbouring steps overlap the kernels)."""
+    from hils_attention_b200.attention import HiLSAttentionConfig, HiLSAttentionCore
+    from hils_attention_b200.host_pipeline import HostPipeline
+    dev = torch.device("cuda", 0)
+    B, T, H, D, S, K, W = 1, 1024, 4, 64, 64, 4, 128
+    core = HiLSAttentionCore(HiLSAttentionConfig(H, H, K, S, W)).train()
+
+    def step(q, k, v, do):
+        q, k, v = (t.detach().requires_grad_(True) for t in (q, k, v))
+        o = core(q, k, v, q)
+        o.backward(do)
+        return o.detach(), q.grad, k.grad, v.grad
+
+    g = torch.Generator().manual_seed(77)
+    batches = [[torch.randn(B, T, H, D, generator=g).to(torch.bfloat16).pin_memory() for _ in range(4)]
+               for _ in range(5)]
+    outs = [[torch.empty_like(b[0]).pin_memory() for _ in range(4)] for b in batches]
+    pipe = HostPipeline(step, batches[0], dev, depth=2)
+    for b, o in zip(batches, outs):
+        pipe.submit(b, o)
+    pipe.drain()
+    for b, o in zip(batches, outs):
+        ref = step(*[t.to(dev) for t in b])
+        for got, want in zip(o, ref):   # fp32 atomics in the key-gradient accumulation: last-bit differences only
+            w = want.float().cpu()
+            assert (got.float() - w).abs().max() <= 2e-2 * w.abs().max()
