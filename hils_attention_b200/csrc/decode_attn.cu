@@ -250,12 +250,320 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams
   }
 }
 
+// =================================================================================================
+// bf16 fast path.  Scores come from mma.sync.m16n8k16 whose B fragments are loaded straight from the
+// key rows in global memory: the dot product does not care about the order of the D elements, so the
+// k index of every k-step pair is permuted such that a thread's two B registers are four CONSECUTIVE
+// bf16 of one key row.  Lane (key = lane/4, j = lane%4) reads 16 bytes = elements 32s+8j .. 32s+8j+7 of
+// its key: elements 0,1 / 2,3 feed k-step 2s, elements 4,5 / 6,7 feed k-step 2s+1; the A fragments (the
+// query rows) are built with the same permutation.  No shared-memory staging, no barrier, and every
+// 64-byte segment a warp instruction touches is fully used.  P.V runs on the CUDA cores with 16-byte
+// loads: D/8 lanes cover one value row, 32/(D/8) rows per instruction, eight loads in flight per lane.
+// =================================================================================================
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int NK>
+__device__ __forceinline__ void make_q_frags(const float* q_s, int G, int lane, uint32_t (&af)[NK][4]) {
+  constexpr int D = NK * 16;
+  const int r0 = lane >> 2, r1 = r0 + 8, j = lane & 3;
+#pragma unroll
+  for (int kk = 0; kk < NK; ++kk) {
+    const int d = 32 * (kk >> 1) + 8 * j + 4 * (kk & 1);
+    const float* a = q_s + r0 * D + d;
+    const float* b = q_s + r1 * D + d;
+    af[kk][0] = (r0 < G) ? pack_bf16(a[0], a[1]) : 0u;
+    af[kk][1] = (r1 < G) ? pack_bf16(b[0], b[1]) : 0u;
+    af[kk][2] = (r0 < G) ? pack_bf16(a[2], a[3]) : 0u;
+    af[kk][3] = (r1 < G) ? pack_bf16(b[2], b[3]) : 0u;
+  }
+}
+
+// out[g * ostride + j] = <q_g, K_j> for j < n <= 64
+template <int NK>
+__device__ __forceinline__ void score_rows_mma(const uint32_t (&af)[NK][4], const bf16* kbase, int64_t rs, int n, int G,
+                                               float* out, int ostride, int lane) {
+  const int kr = lane >> 2, j = lane & 3;
+#pragma unroll
+  for (int nb0 = 0; nb0 < 8; nb0 += 4) {               // four 8-key blocks in flight
+    if (nb0 * 8 >= n) break;
+    uint4 kv[4][NK / 2];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int key = min((nb0 + u) * 8 + kr, n - 1);
+      const bf16* row = kbase + (int64_t)key * rs + 8 * j;
+#pragma unroll
+      for (int sidx = 0; sidx < NK / 2; ++sidx) kv[u][sidx] = *reinterpret_cast<const uint4*>(row + 32 * sidx);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int sidx = 0; sidx < NK / 2; ++sidx) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(af[2 * sidx][0]), "r"(af[2 * sidx][1]), "r"(af[2 * sidx][2]), "r"(af[2 * sidx][3]),
+                       "r"(kv[u][sidx].x), "r"(kv[u][sidx].y));
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(af[2 * sidx + 1][0]), "r"(af[2 * sidx + 1][1]), "r"(af[2 * sidx + 1][2]), "r"(af[2 * sidx + 1][3]),
+                       "r"(kv[u][sidx].z), "r"(kv[u][sidx].w));
+      }
+      const int key0 = (nb0 + u) * 8 + 2 * j;
+      if (kr < G) {
+        if (key0 < n) out[kr * ostride + key0] = c[0];
+        if (key0 + 1 < n) out[kr * ostride + key0 + 1] = c[1];
+      }
+      if (kr + 8 < G) {
+        if (key0 < n) out[(kr + 8) * ostride + key0] = c[2];
+        if (key0 + 1 < n) out[(kr + 8) * ostride + key0 + 1] = c[3];
+      }
+    }
+  }
+}
+
+// acc[g][0..7] += sum_j p[g * pstride + j] * V_j[sub*8 .. sub*8+7] over the rows this lane's group visits
+template <int NK, int GM>
+__device__ __forceinline__ void pv_rows16(const float* p_s, int pstride, const bf16* vbase, int64_t rs, int n, int G,
+                                          float (&acc)[GM][8], int lane) {
+  constexpr int LPR = 2 * NK, RPI = 32 / LPR;          // lanes per row, rows per load instruction
+  const int sub = lane % LPR, rg = lane / LPR;
+  for (int j0 = 0; j0 < n; j0 += RPI * 8) {
+    uint4 vv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int jr = min(j0 + u * RPI + rg, n - 1);
+      vv[u] = *reinterpret_cast<const uint4*>(vbase + (int64_t)jr * rs + sub * 8);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int jr = j0 + u * RPI + rg;
+      if (jr < n) {
+        const uint32_t w4[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          f[2 * e] = __uint_as_float(w4[e] << 16);
+          f[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
+        }
+#pragma unroll
+        for (int g = 0; g < GM; ++g) {
+          if (g < G) {
+            const float pj = p_s[g * pstride + jr];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pj, f[e], acc[g][e]);
+          }
+        }
+      }
+    }
+  }
+}
+
+// sum over the row groups of a warp; afterwards lanes < D/8 hold the totals of columns lane*8 .. lane*8+7
+template <int NK, int GM>
+__device__ __forceinline__ void pv_reduce(float (&acc)[GM][8]) {
+  constexpr int LPR = 2 * NK;
+#pragma unroll
+  for (int off = LPR; off < 32; off <<= 1)
+#pragma unroll
+    for (int g = 0; g < GM; ++g)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], off);
+}
+
+template <int NK, int GM>
+__global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_bf16_kernel(DecodeParams p) {
+  constexpr int D = NK * 16, LPR = 2 * NK;
+  extern __shared__ __align__(16) float smem[];
+  const int G = p.h_q / p.h_kv;
+  float* q_s = smem;                                  // [G][D]
+  float* p_s = q_s + G * D;                           // [warps][G][64]
+  float* o_s = p_s + kDecWarps * G * 64;              // [warps][G][D]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.x, b = blockIdx.y, l = blockIdx.z;
+  const int64_t row0 = (((int64_t)b * p.L + l) * p.h_q + h * G);
+  const bf16* q = static_cast<const bf16*>(p.q) + row0 * D;
+  for (int i = tid; i < G * D; i += kDecWarps * 32) q_s[i] = to_f(q[i]);
+  __syncthreads();
+  uint32_t af[NK][4];
+  make_q_frags<NK>(q_s, G, lane, af);
+  const int32_t* ids = p.idx + (((int64_t)b * p.L + l) * p.h_kv + h) * p.K;
+  const bf16* wts = static_cast<const bf16*>(p.w) + row0 * p.num_weights;
+  const int nchunk = p.T / p.S;
+  int nvalid = 0;
+  while (nvalid < p.K && ids[nvalid] >= 0) ++nvalid;
+  float acc[GM][8];
+#pragma unroll
+  for (int g = 0; g < GM; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+  float* pw = p_s + warp * G * 64;
+  const int64_t rs = (int64_t)p.h_kv * D;
+  for (int kk = warp; kk < nvalid; kk += kDecWarps) {
+    const int c = ids[kk];
+    if (c >= nchunk) continue;
+    const int64_t tok0 = (int64_t)b * p.T + (int64_t)c * p.S;
+    const bf16* kb = static_cast<const bf16*>(p.k) + (tok0 * p.h_kv + h) * D;
+    const bf16* vb = static_cast<const bf16*>(p.v) + (tok0 * p.h_kv + h) * D;
+    __syncwarp();
+    score_rows_mma<NK>(af, kb, rs, p.S, G, pw, 64, lane);
+    __syncwarp();
+    for (int g = 0; g < G; ++g) {
+      const float slope = p.slope ? p.slope[h * G + g] : 0.f;
+      float s0 = -CUDART_INF_F, s1 = -CUDART_INF_F;
+      const int j0 = lane, j1 = lane + 32;
+      if (j0 < p.S && !(p.mask_last && j0 == p.S - 1)) s0 = (pw[g * 64 + j0] - slope * (float)max(0, p.S - 2 - j0)) * p.scale;
+      if (j1 < p.S && !(p.mask_last && j1 == p.S - 1)) s1 = (pw[g * 64 + j1] - slope * (float)max(0, p.S - 2 - j1)) * p.scale;
+      const float m = warp_max(fmaxf(s0, s1));
+      float e0 = 0.f, e1 = 0.f;
+      if (m > -CUDART_INF_F) { e0 = expf(s0 - m); e1 = expf(s1 - m); }
+      const float sum = warp_sum(e0 + e1);
+      const float f = (sum > 0.f) ? to_f(wts[g * p.num_weights + kk]) / sum : 0.f;
+      pw[g * 64 + j0] = e0 * f;
+      pw[g * 64 + j1] = e1 * f;
+    }
+    __syncwarp();
+    pv_rows16<NK, GM>(pw, 64, vb, rs, p.S, G, acc, lane);
+  }
+  pv_reduce<NK, GM>(acc);
+  float* ow = o_s + warp * G * D;
+  if (lane < LPR)
+#pragma unroll
+    for (int g = 0; g < GM; ++g)
+      if (g < G)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ow[g * D + lane * 8 + e] = acc[g][e];
+  __syncthreads();
+  bf16* o = static_cast<bf16*>(p.o) + row0 * D;
+  for (int i = tid; i < G * D; i += kDecWarps * 32) {
+    float sacc = 0.f;
+    for (int w = 0; w < kDecWarps; ++w) sacc += o_s[w * G * D + i];
+    o[i] = __float2bfloat16_rn(sacc);
+  }
+}
+
+constexpr int kSwaDecTile = 32;      // keys per warp step
+
+template <int NK, int GM>
+__global__ void __launch_bounds__(kDecWarps * 32) swa_decode_bf16_kernel(DecodeParams p) {
+  constexpr int D = NK * 16, LPR = 2 * NK;
+  extern __shared__ __align__(16) float smem[];
+  const int G = p.h_q / p.h_kv;
+  float* q_s = smem;                                  // [G][D]
+  float* p_s = q_s + G * D;                           // [warps][G][64]
+  float* o_s = p_s + kDecWarps * G * 64;              // [warps][G][D]
+  float* ml_s = o_s + kDecWarps * G * D;              // [warps][G][2]  running max, sum
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.x, b = blockIdx.y, i = blockIdx.z;
+  const int64_t row0 = (((int64_t)b * p.L + i) * p.h_q + h * G);
+  const bf16* q = static_cast<const bf16*>(p.q) + row0 * D;
+  for (int x = tid; x < G * D; x += kDecWarps * 32) q_s[x] = to_f(q[x]);
+  __syncthreads();
+  uint32_t af[NK][4];
+  make_q_frags<NK>(q_s, G, lane, af);
+  const int t = p.kv_start + (p.T - p.L) + i;
+  int start = t - p.W + 1;
+  if (p.expand) start = floor_div(start, p.S) * p.S;
+  const int lo = max(0, start - p.kv_start), hi = min(p.T - 1, t - p.kv_start);
+  float acc[GM][8], m[GM], lsum[GM];
+#pragma unroll
+  for (int g = 0; g < GM; ++g) {
+    m[g] = -CUDART_INF_F; lsum[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+  }
+  float* pw = p_s + warp * G * 64;
+  const int64_t rs = (int64_t)p.h_kv * D;
+  const bf16* kb0 = static_cast<const bf16*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
+  const bf16* vb0 = static_cast<const bf16*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
+  for (int j0 = lo + warp * kSwaDecTile; j0 <= hi; j0 += kDecWarps * kSwaDecTile) {
+    const int n = min(kSwaDecTile, hi - j0 + 1);
+    __syncwarp();
+    score_rows_mma<NK>(af, kb0 + (int64_t)j0 * rs, rs, n, G, pw, 64, lane);
+    __syncwarp();
+#pragma unroll
+    for (int g = 0; g < GM; ++g) {
+      if (g < G) {
+        float s0 = -CUDART_INF_F;
+        if (lane < n && !(p.mask_lmk && ((p.kv_start + j0 + lane + 1) % p.S == 0))) s0 = pw[g * 64 + lane] * p.scale;
+        const float mn = fmaxf(m[g], warp_max(s0));
+        float e0 = 0.f, corr = 1.f;
+        if (mn > -CUDART_INF_F) {
+          corr = (m[g] > -CUDART_INF_F) ? expf(m[g] - mn) : 0.f;
+          e0 = expf(s0 - mn);
+        }
+        lsum[g] = lsum[g] * corr + warp_sum(e0);
+        m[g] = mn;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] *= corr;
+        pw[g * 64 + lane] = e0;
+      }
+    }
+    __syncwarp();
+    pv_rows16<NK, GM>(pw, 64, vb0 + (int64_t)j0 * rs, rs, n, G, acc, lane);
+  }
+  pv_reduce<NK, GM>(acc);
+  float* ow = o_s + warp * G * D;
+#pragma unroll
+  for (int g = 0; g < GM; ++g)
+    if (g < G) {
+      if (lane < LPR)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ow[g * D + lane * 8 + e] = acc[g][e];
+      if (lane == 0) { ml_s[(warp * G + g) * 2] = m[g]; ml_s[(warp * G + g) * 2 + 1] = lsum[g]; }
+    }
+  __syncthreads();
+  bf16* o = static_cast<bf16*>(p.o) + row0 * D;
+  for (int x = tid; x < G * D; x += kDecWarps * 32) {
+    const int g = x / D;
+    float mm = -CUDART_INF_F;
+    for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, ml_s[(w * G + g) * 2]);
+    float tot = 0.f, sacc = 0.f;
+    if (mm > -CUDART_INF_F)
+      for (int w = 0; w < kDecWarps; ++w) {
+        const float mw = ml_s[(w * G + g) * 2];
+        const float c = (mw > -CUDART_INF_F) ? expf(mw - mm) : 0.f;
+        tot += ml_s[(w * G + g) * 2 + 1] * c;
+        sacc += o_s[w * G * D + x] * c;
+      }
+    o[x] = __float2bfloat16_rn(tot > 0.f ? sacc / tot : 0.f);
+    if (x % D == 0) p.lse[row0 + g] = (tot > 0.f) ? mm + logf(tot) : -CUDART_INF_F;
+  }
+}
+
+template <int NK, int GM>
+static void launch_decode_bf16_g(const DecodeParams& p, bool swa, dim3 grid, size_t smem, cudaStream_t st) {
+  if (swa) {
+    cudaFuncSetAttribute(swa_decode_bf16_kernel<NK, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    swa_decode_bf16_kernel<NK, GM><<<grid, kDecWarps * 32, smem, st>>>(p);
+  } else {
+    cudaFuncSetAttribute(sparse_decode_bf16_kernel<NK, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sparse_decode_bf16_kernel<NK, GM><<<grid, kDecWarps * 32, smem, st>>>(p);
+  }
+}
+
+template <int NK>
+static void launch_decode_bf16(const DecodeParams& p, bool swa, dim3 grid, size_t smem, cudaStream_t st) {
+  const int G = p.h_q / p.h_kv;
+  if (G == 1) launch_decode_bf16_g<NK, 1>(p, swa, grid, smem, st);
+  else if (G == 2) launch_decode_bf16_g<NK, 2>(p, swa, grid, smem, st);
+  else if (G <= 4) launch_decode_bf16_g<NK, 4>(p, swa, grid, smem, st);
+  else launch_decode_bf16_g<NK, 8>(p, swa, grid, smem, st);
+}
+
 template <typename T>
 static int launch_decode(const DecodeParams& p, bool swa, cudaStream_t st) {
   const int G = p.h_q / p.h_kv;
   const size_t smem = ((size_t)G * p.D + (size_t)kDecWarps * G * 64 + (size_t)kDecWarps * G * p.D +
                        (size_t)kDecWarps * G * 2) * sizeof(float);
   dim3 grid(p.h_kv, p.B, p.L);
+  if (sizeof(T) == 2) {
+    if (p.D == 128) launch_decode_bf16<8>(p, swa, grid, smem, st); else launch_decode_bf16<4>(p, swa, grid, smem, st);
+    HILS_LAUNCH_CHECK(swa ? "swa_fwd (decode)" : "sparse_attn_fwd (decode)");
+    return HILS_OK;
+  }
 #define HILS_DEC_LAUNCH(KERNEL, PER)                                                              \
   do {                                                                                            \
     cudaFuncSetAttribute(KERNEL<T, PER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
@@ -281,6 +589,7 @@ int sparse_decode_launch(const void* q, const void* k, const void* v, const void
                          void* o, int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights, int S,
                          float scale, int mask_last, int dtype, cudaStream_t st) {
   if (!decode_shape_ok(B, L, h_q, h_kv, D, Dv) || S > 64) return HILS_ERR_UNSUPPORTED;
+  if (dtype == HILS_BF16 && (((uintptr_t)k | (uintptr_t)v) & 15)) return HILS_ERR_UNSUPPORTED;   // 16-byte row loads
   DecodeParams p = {};
   p.q = q; p.k = k; p.v = v; p.w = w; p.idx = idx; p.slope = slope; p.o = o;
   p.B = B; p.L = L; p.T = T; p.h_q = h_q; p.h_kv = h_kv; p.D = D; p.K = K; p.num_weights = num_weights; p.S = S;
@@ -292,6 +601,7 @@ int swa_decode_launch(const void* q, const void* k, const void* v, void* o, floa
                       int h_kv, int D, int Dv, int W, int S, int mask_lmk, int expand, float scale, int kv_start, int dtype,
                       cudaStream_t st) {
   if (!decode_shape_ok(B, Lq, h_q, h_kv, D, Dv)) return HILS_ERR_UNSUPPORTED;
+  if (dtype == HILS_BF16 && (((uintptr_t)k | (uintptr_t)v) & 15)) return HILS_ERR_UNSUPPORTED;   // 16-byte row loads
   DecodeParams p = {};
   p.q = q; p.k = k; p.v = v; p.o = o; p.lse = lse;
   p.B = B; p.L = Lq; p.T = Lk; p.h_q = h_q; p.h_kv = h_kv; p.D = D; p.S = S; p.W = W; p.mask_lmk = mask_lmk;

@@ -69,13 +69,13 @@ extern "C" int hils_sparse_attn_fwd(const void* q, const void* k, const void* v,
                                chunk_size, sm_scale, mask_last_token);
   p.o = o;
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == HILS_BF16) {  // tensor-core path for the shapes it covers
-    const int rc = sparse_fwd_tc_launch(p, st);
-    if (rc != HILS_ERR_UNSUPPORTED) return rc;
-  }
-  {  // a few query rows against a long store (fp32, or bf16 outside the tensor-core shapes): streaming kernel
+  if (L <= 4) {  // a few query rows against a long store: streaming kernel, keys and values read once
     const int rc = sparse_decode_launch(q, k, v, weights, indices, slope, o, B, L, T, h_q, h_kv, D, Dv, K, num_weights,
                                         chunk_size, sm_scale, mask_last_token, dtype, st);
+    if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  }
+  if (dtype == HILS_BF16) {  // tensor-core path for the shapes it covers
+    const int rc = sparse_fwd_tc_launch(p, st);
     if (rc != HILS_ERR_UNSUPPORTED) return rc;
   }
   const int64_t rows = (int64_t)B * L * h_q;
