@@ -27,7 +27,8 @@ SIGNATURES = {
     "hils_pool_bwd": (_I, [_P] * 6 + [_I] * 6 + [_I64, _F, _I, _I, _P]),
     "hils_meanpool_fwd": (_I, [_P, _P] + [_I] * 5 + [_I64, _I, _P]),
     "hils_meanpool_bwd": (_I, [_P, _P] + [_I] * 6 + [_P]),
-    "hils_topk_fwd": (_I, [_P] * 10 + [_I] * 12 + [_F, _I, _I, _P]),
+    "hils_topk_fwd": (_I, [_P] * 10 + [_I] * 12 + [_F, _I, _I, _P, _SZ, _P]),
+    "hils_topk_fwd_workspace_bytes": (_SZ, [_I] * 7),
     "hils_topk_bwd": (_I, [_P] * 7 + [_I] * 8 + [_F, _I, _P]),
     "hils_topk_bwd_noalloc": (_I, [_P] * 6 + [_I] * 8 + [_F, _I, _P]),
     "hils_topk_bwd_noalloc_max_elems": (_SZ, []),

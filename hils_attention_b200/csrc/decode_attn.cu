@@ -5,6 +5,7 @@
 // heads of the group from it.  Same contracts as the sparse chunk attention
 // (ops/hils_fwd_bwd_head.py:404-485) and the sliding-window branch (ops/flex_attn_tilelang.py:115-253).
 #include "common.cuh"
+#include "mma_rows.cuh"
 
 namespace hils {
 
@@ -251,74 +252,28 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams
 }
 
 // =================================================================================================
-// bf16 fast path.  Scores come from mma.sync.m16n8k16 whose B fragments are loaded straight from the
-// key rows in global memory: the dot product does not care about the order of the D elements, so the
-// k index of every k-step pair is permuted such that a thread's two B registers are four CONSECUTIVE
-// bf16 of one key row.  Lane (key = lane/4, j = lane%4) reads 16 bytes = elements 32s+8j .. 32s+8j+7 of
-// its key: elements 0,1 / 2,3 feed k-step 2s, elements 4,5 / 6,7 feed k-step 2s+1; the A fragments (the
-// query rows) are built with the same permutation.  No shared-memory staging, no barrier, and every
-// 64-byte segment a warp instruction touches is fully used.  P.V runs on the CUDA cores with 16-byte
-// loads: D/8 lanes cover one value row, 32/(D/8) rows per instruction, eight loads in flight per lane.
+// bf16 fast path.  Scores come from mma.sync with B fragments loaded straight from the key rows in
+// global memory (mma_rows.cuh): no shared-memory staging, no barrier.  P.V runs on the CUDA cores with
+// 16-byte loads: D/8 lanes cover one value row, 32/(D/8) rows per instruction, eight loads in flight.
 // =================================================================================================
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-
-template <int NK>
-__device__ __forceinline__ void make_q_frags(const float* q_s, int G, int lane, uint32_t (&af)[NK][4]) {
-  constexpr int D = NK * 16;
-  const int r0 = lane >> 2, r1 = r0 + 8, j = lane & 3;
-#pragma unroll
-  for (int kk = 0; kk < NK; ++kk) {
-    const int d = 32 * (kk >> 1) + 8 * j + 4 * (kk & 1);
-    const float* a = q_s + r0 * D + d;
-    const float* b = q_s + r1 * D + d;
-    af[kk][0] = (r0 < G) ? pack_bf16(a[0], a[1]) : 0u;
-    af[kk][1] = (r1 < G) ? pack_bf16(b[0], b[1]) : 0u;
-    af[kk][2] = (r0 < G) ? pack_bf16(a[2], a[3]) : 0u;
-    af[kk][3] = (r1 < G) ? pack_bf16(b[2], b[3]) : 0u;
-  }
-}
-
 // out[g * ostride + j] = <q_g, K_j> for j < n <= 64
 template <int NK>
 __device__ __forceinline__ void score_rows_mma(const uint32_t (&af)[NK][4], const bf16* kbase, int64_t rs, int n, int G,
                                                float* out, int ostride, int lane) {
   const int kr = lane >> 2, j = lane & 3;
-#pragma unroll
-  for (int nb0 = 0; nb0 < 8; nb0 += 4) {               // four 8-key blocks in flight
-    if (nb0 * 8 >= n) break;
-    uint4 kv[4][NK / 2];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int key = min((nb0 + u) * 8 + kr, n - 1);
-      const bf16* row = kbase + (int64_t)key * rs + 8 * j;
-#pragma unroll
-      for (int sidx = 0; sidx < NK / 2; ++sidx) kv[u][sidx] = *reinterpret_cast<const uint4*>(row + 32 * sidx);
-    }
+  for (int k0 = 0; k0 < n; k0 += 32) {
+    float c[4][4];
+    dot32_mma<NK>(af, kbase + (int64_t)k0 * rs, rs, n - k0, lane, c);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int sidx = 0; sidx < NK / 2; ++sidx) {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(af[2 * sidx][0]), "r"(af[2 * sidx][1]), "r"(af[2 * sidx][2]), "r"(af[2 * sidx][3]),
-                       "r"(kv[u][sidx].x), "r"(kv[u][sidx].y));
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(af[2 * sidx + 1][0]), "r"(af[2 * sidx + 1][1]), "r"(af[2 * sidx + 1][2]), "r"(af[2 * sidx + 1][3]),
-                       "r"(kv[u][sidx].z), "r"(kv[u][sidx].w));
-      }
-      const int key0 = (nb0 + u) * 8 + 2 * j;
+      const int key0 = k0 + u * 8 + 2 * j;
       if (kr < G) {
-        if (key0 < n) out[kr * ostride + key0] = c[0];
-        if (key0 + 1 < n) out[kr * ostride + key0 + 1] = c[1];
+        if (key0 < n) out[kr * ostride + key0] = c[u][0];
+        if (key0 + 1 < n) out[kr * ostride + key0 + 1] = c[u][1];
       }
       if (kr + 8 < G) {
-        if (key0 < n) out[(kr + 8) * ostride + key0] = c[2];
-        if (key0 + 1 < n) out[(kr + 8) * ostride + key0 + 1] = c[3];
+        if (key0 < n) out[(kr + 8) * ostride + key0] = c[u][2];
+        if (key0 + 1 < n) out[(kr + 8) * ostride + key0 + 1] = c[u][3];
       }
     }
   }
@@ -388,7 +343,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_bf16_kernel(Deco
   for (int i = tid; i < G * D; i += kDecWarps * 32) q_s[i] = to_f(q[i]);
   __syncthreads();
   uint32_t af[NK][4];
-  make_q_frags<NK>(q_s, G, lane, af);
+  make_q_frags<NK>(q_s, lane, af, [G](int r) { return r < G ? r : -1; });
   const int32_t* ids = p.idx + (((int64_t)b * p.L + l) * p.h_kv + h) * p.K;
   const bf16* wts = static_cast<const bf16*>(p.w) + row0 * p.num_weights;
   const int nchunk = p.T / p.S;
@@ -462,7 +417,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_bf16_kernel(DecodeP
   for (int x = tid; x < G * D; x += kDecWarps * 32) q_s[x] = to_f(q[x]);
   __syncthreads();
   uint32_t af[NK][4];
-  make_q_frags<NK>(q_s, G, lane, af);
+  make_q_frags<NK>(q_s, lane, af, [G](int r) { return r < G ? r : -1; });
   const int t = p.kv_start + (p.T - p.L) + i;
   int start = t - p.W + 1;
   if (p.expand) start = floor_div(start, p.S) * p.S;

@@ -18,6 +18,7 @@
 // key bits above, inverted id below, so one unsigned compare implements "greater key, then smaller
 // id").  New candidates are filtered by a warp ballot against the current K-th item.
 #include "common.cuh"
+#include "mma_rows.cuh"
 
 namespace hils {
 
@@ -27,6 +28,7 @@ struct TopkParams {
   int B, L, N, h_kv, G, D, topk, block_size, window_size, is_causal, q_offset, per_qhead, lse_dtype;
   int RW;
   float scale;
+  float* dots;   // decode, bf16: raw q.k' of every candidate, written by the streaming kernel (or null)
 };
 
 constexpr int TN = 128;  // candidates per tile
@@ -43,7 +45,7 @@ __device__ __forceinline__ float log_add_exp(float a, float b) {
   return mx + log1pf(expf(mn - mx));
 }
 
-__device__ __forceinline__ int row_limit(const TopkParams& p, int l) {
+__host__ __device__ __forceinline__ int row_limit(const TopkParams& p, int l) {
   if (l >= p.L) return 0;
   if (!p.is_causal) return p.N;
   int t = p.q_offset + l;
@@ -724,126 +726,198 @@ static int launch_topk_mma(const TopkParams& p, cudaStream_t st) {
   return HILS_OK;
 }
 
-// Logits of all chunk keys of one (batch, kv-head) for up to 16 query rows, bf16, on the warp-level
-// tensor-core path (mma.sync m16n8k16): the keys stream through a 3-stage cp.async ring of 64-key
-// tiles in shared memory; warp w owns keys 8w..8w+7 of every tile; the 16 x D query block stays in
-// registers as A fragments.  Decode scoring is a 1..16-row problem, far below a tcgen05 tile.
-constexpr int kDecTile = 64, kDecStages = 5;
+// Raw dot products q.k' of the decode selection, bf16: a pure streaming kernel.  One persistent CTA per SM
+// walks work items = (batch, query row, kv-head[, group member], range of kDotKeys keys); the 64-key tiles of
+// consecutive items flow through ONE cp.async ring that fills almost all of the SM's shared memory, so about
+// 190 KB of loads are in flight per SM at any time - what it takes to cover HBM latency at full bandwidth (a
+// register-resident or two-CTA design holds a third of that and stalls at ~3.7 TB/s).  Warp w computes keys
+// 16w..16w+15 of a tile with mma.sync m16n8k16; the item's query rows travel in the stage of its first tile.
+constexpr int kDotKeys = 1024, kDotTile = 128;   // warp w computes keys 16w..16w+15 of a tile
 
-template <int NK>   // NK = D / 16
-__device__ __forceinline__ void decode_logits_bf16(const TopkParams& p, const bf16* q, const bf16* lmks, int b, int h,
-                                                   int lim, int G, int Npad, int HL, float* q_s, bf16* qb_s,
-                                                   bf16* tile_s, float* v_s, int tid) {
-  constexpr int D = NK * 16, RS = D + 8;                   // padded row (elements): conflict-free ldmatrix
-  constexpr int CPR = D / 8;                               // 16-byte pieces per key row
-  constexpr int NCP = kDecTile * CPR / 256;                // pieces per thread and tile
-  constexpr int RSTEP = 256 / CPR;                         // key rows between a thread's pieces
-  constexpr uint32_t kStageBytes = kDecTile * RS * 2;
-  const int lane = tid & 31, warp = tid >> 5;
-  const int ng = p.per_qhead ? G : 1;
-  const int ntile = (lim + kDecTile - 1) / kDecTile;
-  const int row0 = tid / CPR, col0 = (tid % CPR) * 8;
-  const uint32_t tile_base = (uint32_t)__cvta_generic_to_shared(tile_s);
-  const uint32_t dst0 = tile_base + (uint32_t)(row0 * RS + col0) * 2u;
-  const int64_t key_stride = (int64_t)HL * D, step = key_stride * RSTEP, tile_step = key_stride * kDecTile;
-  const uint32_t b_off = (uint32_t)((warp * 8 + (lane & 7)) * RS + ((lane >> 3) & 1) * 8) * 2u;
-  for (int g0 = 0; g0 < ng; ++g0) {
-    const bf16* src = lmks + ((int64_t)b * p.N * HL + (p.per_qhead ? h * G + g0 : h)) * D + row0 * key_stride + col0;
-    int t_issue = 0, st_issue = 0;
-    auto issue = [&]() {
-      if (t_issue < ntile) {
-        const uint32_t dst = dst0 + (uint32_t)st_issue * kStageBytes;
-        const int row = t_issue * kDecTile + row0;
-#pragma unroll
-        for (int i = 0; i < NCP; ++i)
-          if (row + i * RSTEP < p.N)                      // rows past the last key stay stale: never candidates
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(i * RSTEP * RS * 2)),
-                         "l"(src + i * step) : "memory");
-        src += tile_step;
+struct DotCursor {
+  int item, tile, ntile, key_lo, key_hi;
+  const bf16* keys;      // key row key_lo of the item's key head, advanced tile by tile
+  const bf16* q;         // the item's query rows
+  float* out;            // dots of the item's first fragment row, advanced tile by tile
+};
+
+template <int NK, int STAGES>
+__global__ void __launch_bounds__(256, 1) topk_decode_dots_kernel(TopkParams p, int Npad, int n_items, int ranges) {
+  constexpr int stages = STAGES;
+  constexpr int D = NK * 16, RS = D + 8, CPR = D / 8;
+  constexpr int kStageRows = kDotTile + 16;              // key rows + query rows
+  constexpr uint32_t kStageBytes = kStageRows * RS * 2;
+  extern __shared__ __align__(16) unsigned char ring[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = p.G, ng = p.per_qhead ? G : 1;
+  const int HL = p.per_qhead ? p.h_kv * G : p.h_kv;
+  const int64_t rs = (int64_t)HL * D;
+  const uint32_t ring32 = (uint32_t)__cvta_generic_to_shared(ring);
+
+  auto load_item = [&](DotCursor& c) {                   // skips items without candidates
+    for (; c.item < n_items; c.item += gridDim.x) {
+      const int r = c.item % ranges, x = c.item / ranges;
+      const int g0 = x % ng, row = x / ng;                 // row = (b*L + l)*h_kv + h
+      const int h = row % p.h_kv, bl = row / p.h_kv, l = bl % p.L;
+      const int64_t b = bl / p.L;
+      const int lim = row_limit(p, l);
+      c.key_lo = r * kDotKeys;
+      c.key_hi = min(lim, c.key_lo + kDotKeys);
+      c.tile = 0;
+      c.ntile = (c.key_hi - c.key_lo + kDotTile - 1) / kDotTile;
+      if (c.ntile > 0) {
+        c.keys = static_cast<const bf16*>(p.lmks) + ((b * p.N + c.key_lo) * HL + (p.per_qhead ? h * G + g0 : h)) * D;
+        c.q = static_cast<const bf16*>(p.q) + ((int64_t)row * G + (p.per_qhead ? g0 : 0)) * D;
+        c.out = p.dots + ((int64_t)row * G + (p.per_qhead ? g0 : 0)) * Npad + c.key_lo;
+        return;
       }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      ++t_issue;
-      if (++st_issue == kDecStages) st_issue = 0;
-    };
-    for (int t = 0; t < kDecStages - 1; ++t) issue();
-    if (g0 == 0) {
-      // the query rows (fp32 copy for the returned scores, padded bf16 copy with a zero row for the
-      // A fragments) and the additive terms of the logits are staged while the first tiles are in flight
-      for (int i = tid; i < 17 * RS; i += 256) {
-        const int r = i / RS, d = i - r * RS;
-        const bool live = r < G && d < D;
-        const bf16 x = live ? q[r * D + d] : __float2bfloat16_rn(0.f);
-        qb_s[i] = x;
-        if (live) q_s[r * D + d] = __bfloat162float(x);
-      }
-      for (int g = 0; g < G; ++g)
-        for (int c = tid; c < Npad; c += 256) {
-          float add = 0.f;
-          if (c < lim) {
-            if (p.bias) add = p.bias[(((int64_t)b * p.N + c) * p.h_kv + h) * G + g];
-            if (p.gumbel) add += p.gumbel[(int64_t)(h * G + g) * p.N + c];
-          }
-          v_s[(size_t)g * Npad + c] = (c < ntile * kDecTile) ? add : -CUDART_INF_F;
-        }
-      __syncthreads();
     }
-    // A fragments: rows = group members (shared keys) or the single member g0 (per-q-head keys)
-    uint32_t afrag[NK][4];
-    {
-      const int arow = (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
-      const int grow = p.per_qhead ? (arow == 0 ? g0 : 16) : arow;      // row 16 is the zero row
-      const uint32_t a32 = (uint32_t)__cvta_generic_to_shared(qb_s + grow * RS + acol);
+  };
+  auto advance = [&](DotCursor& c) {
+    if (++c.tile == c.ntile) {
+      c.item += gridDim.x;
+      load_item(c);
+    } else {
+      c.keys += (int64_t)kDotTile * rs;
+      c.out += kDotTile;
+      c.key_lo += kDotTile;                                // key_lo is now the first key of the current tile
+    }
+  };
+  const int cp_row = tid / CPR, cp_col = (tid % CPR) * 8;   // this thread's 16-byte pieces: rows cp_row + i*(256/CPR)
+  constexpr int RSTEP = 256 / CPR, NCP = kDotTile / RSTEP;
+  const uint32_t cp_dst = (uint32_t)(cp_row * RS + cp_col) * 2u;
+  const int64_t cp_src = (int64_t)cp_row * rs + cp_col, cp_step = (int64_t)RSTEP * rs;
+  auto issue = [&](DotCursor& c, int stage) {
+    if (c.item < n_items) {
+      const uint32_t dst = ring32 + (uint32_t)stage * kStageBytes + cp_dst;
+      const bf16* src = c.keys + cp_src;
+      const int key0 = c.key_lo + cp_row;
+#pragma unroll
+      for (int i = 0; i < NCP; ++i)
+        if (key0 + i * RSTEP < c.key_hi)                  // rows past the range stay stale: never stored
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(i * RSTEP * RS * 2)),
+                       "l"(src + i * cp_step) : "memory");
+      if (c.tile == 0) {                                  // the item's query rows ride in this stage
+        const int nq = p.per_qhead ? 1 : G;
+        if (tid < nq * CPR)                               // thread's piece: query row cp_row, columns cp_col..
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring32 + (uint32_t)stage * kStageBytes +
+                       (uint32_t)(kDotTile * RS * 2) + cp_dst), "l"(c.q + cp_row * D + cp_col) : "memory");
+      }
+      advance(c);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // query rows beyond the group are zero in every stage
+  for (int i = tid; i < stages * 16 * RS; i += 256) {
+    const int st = i / (16 * RS), o = i - st * 16 * RS;
+    reinterpret_cast<bf16*>(ring + (size_t)st * kStageBytes)[kDotTile * RS + o] = __float2bfloat16_rn(0.f);
+  }
+  __syncthreads();
+  DotCursor prod, cons;
+  prod.item = cons.item = blockIdx.x;
+  load_item(prod);
+  cons = prod;
+  int st_issue = 0, st_use = 0;
+  for (int i = 0; i < stages - 1; ++i) {
+    issue(prod, st_issue);
+    if (++st_issue == stages) st_issue = 0;
+  }
+  uint32_t af[NK][4];
+  const uint32_t a_off = (uint32_t)((kDotTile + (lane & 7) + ((lane >> 3) & 1) * 8) * RS + (lane >> 4) * 8) * 2u;
+  const uint32_t b_off = (uint32_t)((warp * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * RS + ((lane >> 3) & 1) * 8) * 2u;
+  const int kr = lane >> 2, j = lane & 3;
+  while (cons.item < n_items) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    __syncthreads();
+    issue(prod, st_issue);
+    if (++st_issue == stages) st_issue = 0;
+    const uint32_t sbase = ring32 + (uint32_t)st_use * kStageBytes;
+    if (cons.tile == 0) {
 #pragma unroll
       for (int kk = 0; kk < NK; ++kk)
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(afrag[kk][0]), "=r"(afrag[kk][1]), "=r"(afrag[kk][2]), "=r"(afrag[kk][3])
-                     : "r"(a32 + kk * 32));
+                     : "=r"(af[kk][0]), "=r"(af[kk][1]), "=r"(af[kk][2]), "=r"(af[kk][3]) : "r"(sbase + a_off + kk * 32));
     }
-    // this thread's accumulator rows lane/4 and lane/4+8, columns 2*(lane%4)+{0,1} of the warp's 8 keys
-    const int r0 = lane >> 2;
-    const bool ok0 = p.per_qhead ? (r0 == 0) : (r0 < G), ok1 = !p.per_qhead && (r0 + 8 < G);
-    const int ccol = warp * 8 + (lane & 3) * 2;
-    float* cell0 = v_s + (size_t)(p.per_qhead ? g0 : r0) * Npad + ccol;
-    float* cell1 = v_s + (size_t)(p.per_qhead ? g0 : r0 + 8) * Npad + ccol;
-    int st_use = 0;
-    for (int t = 0; t < ntile; ++t) {
-      asm volatile("cp.async.wait_group %0;" ::"n"(kDecStages - 2) : "memory");
-      __syncthreads();
-      issue();
-      const uint32_t b32 = tile_base + (uint32_t)st_use * kStageBytes + b_off;
-      if (++st_use == kDecStages) st_use = 0;
-      float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};     // two chains over the k-steps
+    float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};   // keys 16w..16w+7 and 16w+8..16w+15
 #pragma unroll
-      for (int kk = 0; kk < NK; ++kk) {
-        uint32_t b0, b1;
-        asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(b32 + kk * 32));
-        if (kk & 1)
-          asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                       : "+f"(cb[0]), "+f"(cb[1]), "+f"(cb[2]), "+f"(cb[3])
-                       : "r"(afrag[kk][0]), "r"(afrag[kk][1]), "r"(afrag[kk][2]), "r"(afrag[kk][3]), "r"(b0), "r"(b1));
-        else
-          asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                       : "+f"(ca[0]), "+f"(ca[1]), "+f"(ca[2]), "+f"(ca[3])
-                       : "r"(afrag[kk][0]), "r"(afrag[kk][1]), "r"(afrag[kk][2]), "r"(afrag[kk][3]), "r"(b0), "r"(b1));
-      }
-      const int c = t * kDecTile + ccol;
-      if (ok0) {
-        float2* cell = reinterpret_cast<float2*>(cell0 + t * kDecTile);
-        float2 a = *cell;
-        a.x = (c < lim) ? __fmul_rn(ca[0] + cb[0], p.scale) + a.x : -CUDART_INF_F;
-        a.y = (c + 1 < lim) ? __fmul_rn(ca[1] + cb[1], p.scale) + a.y : -CUDART_INF_F;
-        *cell = a;
-      }
-      if (ok1) {
-        float2* cell = reinterpret_cast<float2*>(cell1 + t * kDecTile);
-        float2 a = *cell;
-        a.x = (c < lim) ? __fmul_rn(ca[2] + cb[2], p.scale) + a.x : -CUDART_INF_F;
-        a.y = (c + 1 < lim) ? __fmul_rn(ca[3] + cb[3], p.scale) + a.y : -CUDART_INF_F;
-        *cell = a;
+    for (int kk = 0; kk < NK; ++kk) {
+      uint32_t b0, b1, b2, b3;
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(sbase + b_off + kk * 32));
+      asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                   : "+f"(ca[0]), "+f"(ca[1]), "+f"(ca[2]), "+f"(ca[3])
+                   : "r"(af[kk][0]), "r"(af[kk][1]), "r"(af[kk][2]), "r"(af[kk][3]), "r"(b0), "r"(b1));
+      asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                   : "+f"(cb[0]), "+f"(cb[1]), "+f"(cb[2]), "+f"(cb[3])
+                   : "r"(af[kk][0]), "r"(af[kk][1]), "r"(af[kk][2]), "r"(af[kk][3]), "r"(b2), "r"(b3));
+    }
+    {
+      const int koff = warp * 16 + 2 * j;                 // even: 8-byte aligned pair
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr) {
+        const int row = kr + 8 * hr;
+        const bool ok = p.per_qhead ? (row == 0) : (row < G);
+        if (ok) {
+          float* o = cons.out + (int64_t)row * Npad + koff;
+          if (cons.key_lo + koff < cons.key_hi) *reinterpret_cast<float2*>(o) = make_float2(ca[2 * hr], ca[2 * hr + 1]);
+          if (cons.key_lo + koff + 8 < cons.key_hi)
+            *reinterpret_cast<float2*>(o + 8) = make_float2(cb[2 * hr], cb[2 * hr + 1]);
+        }
       }
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
+    advance(cons);
+    if (++st_use == stages) st_use = 0;
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// Logits of all chunk keys of one (batch, kv-head) for up to 16 query rows, bf16: mma.sync with the B
+// fragments loaded straight from the key rows (mma_rows.cuh), warp w taking every 8th group of 32 keys.
+// Nothing is staged in shared memory, so the CTA is small and many are resident per SM.
+template <int NK>   // NK = D / 16
+__device__ __forceinline__ void decode_logits_bf16(const TopkParams& p, const bf16* q, const bf16* lmks, int b, int h,
+                                                   int lim, int G, int Npad, int HL, float* q_s, float* v_s, int tid) {
+  constexpr int D = NK * 16;
+  const int lane = tid & 31, warp = tid >> 5;
+  // query rows as fp32 (also used for the returned scores) and the additive terms of the logits
+  for (int i = tid; i < G * D; i += 256) q_s[i] = __bfloat162float(q[i]);
+  for (int g = 0; g < G; ++g)
+    for (int c = tid; c < Npad; c += 256) {
+      float add = -CUDART_INF_F;
+      if (c < lim) {
+        add = 0.f;
+        if (p.bias) add = p.bias[(((int64_t)b * p.N + c) * p.h_kv + h) * G + g];
+        if (p.gumbel) add += p.gumbel[(int64_t)(h * G + g) * p.N + c];
+      }
+      v_s[(size_t)g * Npad + c] = add;
+    }
+  __syncthreads();
+  const int ng = p.per_qhead ? G : 1;
+  const int64_t rs = (int64_t)HL * D;
+  const int kr = lane >> 2, j = lane & 3;
+  for (int g0 = 0; g0 < ng; ++g0) {
+    uint32_t af[NK][4];
+    if (p.per_qhead) make_q_frags<NK>(q_s, lane, af, [g0](int r) { return r == 0 ? g0 : -1; });
+    else make_q_frags<NK>(q_s, lane, af, [G](int r) { return r < G ? r : -1; });
+    const bf16* base = lmks + ((int64_t)b * p.N * HL + (p.per_qhead ? h * G + g0 : h)) * D;
+    for (int k0 = warp * 32; k0 < lim; k0 += 8 * 32) {
+      float c[4][4];
+      dot32_mma<NK>(af, base + (int64_t)k0 * rs, rs, lim - k0, lane, c);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int key = k0 + u * 8 + 2 * j;
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+          const int row = kr + 8 * hr;
+          const bool ok = p.per_qhead ? (row == 0) : (row < G);
+          if (ok) {
+            float* cell = v_s + (size_t)(p.per_qhead ? g0 : row) * Npad + key;
+            if (key < lim) cell[0] = __fmul_rn(c[u][2 * hr], p.scale) + cell[0];
+            if (key + 1 < lim) cell[1] = __fmul_rn(c[u][2 * hr + 1], p.scale) + cell[1];
+          }
+        }
+      }
+    }
   }
 }
 
@@ -851,8 +925,8 @@ __device__ __forceinline__ void decode_logits_bf16(const TopkParams& p, const bf
 // One CTA per (kv-head, batch, query row).  The chunk keys of that head are streamed once (16 lanes per
 // key row, 16-byte loads), logits go to shared memory, then log-sum-exp, ranking keys and the same
 // sort/merge selection as above, with the candidate tiles spread over the CTA's 8 warps.
-template <typename T, int NK>
-__global__ void __launch_bounds__(256) topk_decode_kernel(TopkParams p) {
+template <typename T, int NK, bool kDots>   // kDots: the logits come from topk_decode_dots_kernel's output
+__global__ void __launch_bounds__(256, kDots ? 4 : 1) topk_decode_kernel(TopkParams p) {
   extern __shared__ __align__(16) float smem[];
   const int G = p.G, D = p.D, N = p.N, K = p.topk;
   const int Npad = (N + 127) & ~127;
@@ -861,9 +935,6 @@ __global__ void __launch_bounds__(256) topk_decode_kernel(TopkParams p) {
   float* key_s = v_s + (size_t)G * Npad;     // [Npad]
   float* red_s = key_s + Npad;               // [G][16] partial (max, sum) + [G] lse_total
   u64* list_s = reinterpret_cast<u64*>(red_s + 16 * G + ((G + 1) & ~1));  // 2 KB of selection scratch
-  bf16* qb_s = reinterpret_cast<bf16*>(                               // bf16 path: [17][D+8] queries (+ zero row)
-      (reinterpret_cast<uintptr_t>(list_s + 8 * 32) + 15) & ~uintptr_t(15));
-  bf16* tile_s = qb_s + 17 * (D + 8);                                 // bf16 path: key tiles, kDecStages x [64][D+8]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int h = blockIdx.x, b = blockIdx.y, l = blockIdx.z;
   const T* q = static_cast<const T*>(p.q) + ((((int64_t)b * p.L + l) * p.h_kv + h) * G) * D;
@@ -878,9 +949,23 @@ __global__ void __launch_bounds__(256) topk_decode_kernel(TopkParams p) {
   }
   // ---- logits ------------------------------------------------------------------------------------
   constexpr bool kIsBf16 = sizeof(T) == 2;
-  if constexpr (kIsBf16) {
+  if constexpr (kDots) {
+    // the dots were streamed by topk_decode_dots_kernel: logits = fl(dot * scale) + bias (+ gumbel)
+    for (int i = tid; i < G * D; i += 256) q_s[i] = to_f(q[i]);
+    const float* dots = p.dots + ((((int64_t)b * p.L + l) * p.h_kv + h) * G) * (int64_t)Npad;
+    for (int g = 0; g < G; ++g)
+      for (int c = tid; c < Npad; c += 256) {
+        float v = -CUDART_INF_F;
+        if (c < lim) {
+          v = __fmul_rn(dots[(int64_t)g * Npad + c], p.scale);
+          if (p.bias) v += p.bias[(((int64_t)b * N + c) * p.h_kv + h) * G + g];
+          if (p.gumbel) v += p.gumbel[(int64_t)(h * G + g) * N + c];
+        }
+        v_s[(size_t)g * Npad + c] = v;
+      }
+  } else if constexpr (kIsBf16) {
     decode_logits_bf16<NK>(p, reinterpret_cast<const bf16*>(q), reinterpret_cast<const bf16*>(lmks), b, h, lim, G, Npad,
-                           HL, q_s, qb_s, tile_s, v_s, tid);
+                           HL, q_s, v_s, tid);
   } else {
   for (int i = tid; i < G * D; i += 256) q_s[i] = to_f(q[i]);
   __syncthreads();
@@ -1094,12 +1179,36 @@ static int launch_topk_decode(const TopkParams& p, cudaStream_t st) {
                 8 * 32 * sizeof(u64) + 16;
   if (sizeof(T) == 2) {
     if (p.G > 16) return HILS_ERR_UNSUPPORTED;            // one 16-row A tile holds the group
-    smem += (size_t)(17 + kDecStages * kDecTile) * (p.D + 8) * sizeof(bf16) + 16;
   }
   if (smem > 200 * 1024) return HILS_ERR_UNSUPPORTED;
-  cudaFuncSetAttribute(topk_decode_kernel<T, NK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if constexpr (sizeof(T) == 2) {
+    if (p.dots) {      // stream the keys once at memory speed, then select from the small fp32 dots array
+      const int max_lim = row_limit(p, p.L - 1);
+      if (max_lim > 0) {
+        constexpr int kStages = (NK == 8) ? 5 : 10;        // ~200 KB of ring per SM
+        const size_t ring = (size_t)kStages * (kDotTile + 16) * (NK * 16 + 8) * sizeof(bf16);
+        const int ranges = (max_lim + kDotKeys - 1) / kDotKeys;
+        const int n_items = p.B * p.L * p.h_kv * (p.per_qhead ? p.G : 1) * ranges;
+        static int n_sm = 0;
+        if (n_sm == 0) {
+          int dev = 0;
+          cudaGetDevice(&dev);
+          cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        }
+        cudaFuncSetAttribute(topk_decode_dots_kernel<NK, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+        topk_decode_dots_kernel<NK, kStages><<<std::min(n_items, n_sm), 256, ring, st>>>(p, Npad, n_items, ranges);
+        HILS_LAUNCH_CHECK("topk_fwd (decode, key stream)");
+      }
+    }
+  }
   dim3 grid(p.h_kv, p.B, p.L);
-  topk_decode_kernel<T, NK><<<grid, 256, smem, st>>>(p);
+  if (sizeof(T) == 2 && p.dots) {
+    cudaFuncSetAttribute(topk_decode_kernel<T, NK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    topk_decode_kernel<T, NK, true><<<grid, 256, smem, st>>>(p);
+  } else {
+    cudaFuncSetAttribute(topk_decode_kernel<T, NK, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    topk_decode_kernel<T, NK, false><<<grid, 256, smem, st>>>(p);
+  }
   HILS_LAUNCH_CHECK("topk_fwd (decode)");
   return HILS_OK;
 }
@@ -1178,11 +1287,19 @@ static int launch_topk(const TopkParams& p, cudaStream_t st) {
 
 using namespace hils;
 
+extern "C" size_t hils_topk_fwd_workspace_bytes(int B, int L, int N, int h_kv, int G, int D, int dtype) {
+  // only the bf16 decode shape uses scratch: the raw dot products of every candidate, fp32
+  if (dtype != HILS_BF16 || L > 4 || N < 512 || !(D == 64 || D == 128) || G > 16) return 0;
+  const size_t Npad = ((size_t)N + 127) & ~(size_t)127;
+  return (size_t)B * L * h_kv * G * Npad * sizeof(float);
+}
+
 extern "C" int hils_topk_fwd(const void* q, const void* lmks, const void* lse_swa, const float* bias,
                              const float* gumbel, const int32_t* drop_mask, int32_t* indices, void* scores,
                              float* lse_total, float* rank_keys, int B, int L, int N, int h_kv, int G, int D,
                              int topk, int block_size, int window_size, int is_causal, int q_offset,
-                             int per_qhead, float sm_scale, int dtype, int lse_dtype, void* stream) {
+                             int per_qhead, float sm_scale, int dtype, int lse_dtype, void* workspace,
+                             size_t workspace_bytes, void* stream) {
   HILS_REQUIRE(B > 0 && L >= 0 && N >= 0 && h_kv > 0 && G > 0 && D > 0, "topk_fwd: non-positive size");
   HILS_REQUIRE(topk > 0 && topk <= 128, "topk_fwd: topk (%d) must be in [1,128]", topk);
   HILS_REQUIRE(block_size > 0, "topk_fwd: block_size must be positive");
@@ -1198,10 +1315,13 @@ extern "C" int hils_topk_fwd(const void* q, const void* lmks, const void* lse_sw
   p.indices = indices; p.scores = scores; p.lse_total = lse_total; p.rank_keys = rank_keys;
   p.B = B; p.L = L; p.N = N; p.h_kv = h_kv; p.G = G; p.D = D; p.topk = topk; p.block_size = block_size;
   p.window_size = window_size; p.is_causal = is_causal; p.q_offset = q_offset; p.per_qhead = per_qhead;
-  p.lse_dtype = lse_dtype; p.RW = 4; p.scale = sm_scale;
+  p.lse_dtype = lse_dtype; p.RW = 4; p.scale = sm_scale; p.dots = nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   // few query rows against many chunk keys (decode, short chunk-prefill): stream the keys once per row
   if (L <= 4 && N >= 512 && topk <= 32 && (D == 64 || D == 128) && L <= 65535) {
+    const size_t need = hils_topk_fwd_workspace_bytes(B, L, N, h_kv, G, D, dtype);
+    if (workspace && need > 0 && workspace_bytes >= need && (int64_t)B * h_kv <= 65535)
+      p.dots = static_cast<float*>(workspace);
     const int rc = (dtype != HILS_BF16) ? launch_topk_decode<float, 0>(p, st)
                    : (D == 128)         ? launch_topk_decode<bf16, 8>(p, st)
                                         : launch_topk_decode<bf16, 4>(p, st);

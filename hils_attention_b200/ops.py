@@ -160,10 +160,12 @@ class _TopkSelect(torch.autograd.Function):
             rank_keys = torch.empty((B, L, h_kv, N), dtype=torch.float32, device=dev)
             aux["lse_total"], aux["rank_keys"] = lse_total, rank_keys
         scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
+        ws_bytes = query("hils_topk_fwd_workspace_bytes", B, L, N, h_kv, G, D, dt)
+        ws = _workspace(ws_bytes, dev)
         call("hils_topk_fwd", ptr(q_in), ptr(k_in), ptr(lse), ptr(bias), ptr(gumbel), ptr(drop_mask),
              ptr(indices), ptr(scores), ptr(lse_total), ptr(rank_keys), B, L, N, h_kv, G, D, int(topk),
              int(block_size), int(window_size), int(bool(is_causal)), int(q_offset), int(per_qhead), scale,
-             dt, dtype_code(lse), stream())
+             dt, dtype_code(lse), ptr(ws), ws_bytes, stream())
         ctx.save_for_backward(q_in, k_in, indices)
         ctx.meta = (B, L, N, h_kv, G, D, int(topk), int(per_qhead), scale, dt, q.dtype, lmks.dtype)
         ctx.mark_non_differentiable(indices)

@@ -89,7 +89,13 @@ int hils_topk_fwd(const void* q, const void* lmks, const void* lse_swa, const fl
                   int32_t* indices, void* scores, float* lse_total, float* rank_keys,
                   int B, int L, int N, int h_kv, int G, int D, int topk,
                   int block_size, int window_size, int is_causal, int q_offset, int per_qhead,
-                  float sm_scale, int dtype, int lse_dtype, void* stream);
+                  float sm_scale, int dtype, int lse_dtype,
+                  void* workspace, size_t workspace_bytes, void* stream);
+/* Scratch of hils_topk_fwd: non-zero only for the bf16 decode shape (L <= 4 query rows, N >= 512), where
+ * one kernel streams the chunk keys at memory speed into an fp32 array of raw dot products and a second
+ * one selects from it.  workspace may be NULL (or too small): the selection kernel then reads the keys
+ * itself. */
+size_t hils_topk_fwd_workspace_bytes(int B, int L, int N, int h_kv, int G, int D, int dtype);
 
 /* Gradient of the returned scores (SoftmaxTopKMaxPoolingFusedFn.backward, :1040-1092, which
  * scatters into a dense (B,h_kv,G,L,N) tensor and runs two bmm).  Here, bf16 with D = 64 or 128: the
