@@ -110,6 +110,33 @@ class HiLSAttentionCore(torch.nn.Module):
             past_key_values._hils_prior_cache[self.layer_idx] = {"lmk_k": lmk_k, "prior_b": prior_b}
         return lmk_k, prior_b
 
+    def _fused_decode_step(self, q, k, v, lmk_q, layer, past_key_values):
+        """One new token per sequence against the store: the whole step as one library call.  Returns
+        None when the step needs the op-by-op path (training, no pooled keys yet, or the new token
+        completes a chunk, whose pooled key must be formed first)."""
+        S = self.chunk_size
+        cached = past_key_values._hils_prior_cache.get(self.layer_idx)
+        needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, lmk_q))
+        if (self.training or needs_grad or not self.enable_prior_query or cached is None
+                or not layer.is_initialized or self.hils_func is not ops.HiLS_block_M_head
+                or self.topk_func is not ops.online_softmax_topk_head or q.dtype not in (torch.bfloat16, torch.float32)):
+            return None
+        length = layer.get_seq_length()
+        if (length + 1) % S == 0 or length + 1 < S or cached.get("prior_b") is None:
+            return None
+        B, _, h_q, D = q.shape
+        layer._reserve(k, v, length + 1)
+        kbuf, vbuf = layer._kbuf, layer._vbuf
+        lmk_k, prior_b = cached["lmk_k"], cached["prior_b"]
+        o, self._step_ws = ops.decode_step(
+            q.reshape(B * h_q, D), lmk_q.reshape(B * h_q, D), k.reshape(-1, D), v.reshape(-1, D),
+            kbuf.view(kbuf.shape[0], -1, D), vbuf.view(vbuf.shape[0], -1, D), length,
+            lmk_k.reshape(lmk_k.shape[1], -1, D), prior_b.reshape(prior_b.shape[1], -1), self.topk, S,
+            self.hils_sliding_window, self.enable_softmax1, workspace=getattr(self, "_step_ws", None))
+        layer._len = length + 1
+        layer._publish()
+        return o.view(B, 1, h_q, D)
+
     def forward(self, q, k, v, lmk_q, past_key_values=None, use_cache: bool = False,
                 return_aux: bool = False):
         """q, lmk_q (B,L,h_q,D); k, v (B,L,h_kv,D) of the NEW tokens.  Returns (B,L,h_q,Dv), the
@@ -123,6 +150,9 @@ class HiLSAttentionCore(torch.nn.Module):
             # token-major store of this package: the batch is folded into the head dimension, so the
             # cached K/V are consumed in place as (1, T, B*h_kv, D) and only the new tokens are copied
             layer = past_key_values.layer(self.layer_idx + self.config.num_hidden_layers)
+            fused = self._fused_decode_step(q, k, v, lmk_q, layer, past_key_values) if (L == 1 and not return_aux) else None
+            if fused is not None:
+                return fused
             layer.update(k, v)
             k, v = layer.folded()
             q = q.transpose(0, 1).reshape(1, L, B * self.h_q, q.shape[-1])

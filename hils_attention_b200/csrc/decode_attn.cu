@@ -261,7 +261,9 @@ template <int NK>
 __device__ __forceinline__ void score_rows_mma(const uint32_t (&af)[NK][4], const bf16* kbase, int64_t rs, int n, int G,
                                                float* out, int ostride, int lane) {
   const int kr = lane >> 2, j = lane & 3;
-  for (int k0 = 0; k0 < n; k0 += 32) {
+#pragma unroll
+  for (int k0 = 0; k0 < 64; k0 += 32) {       // unrolled: the loads of the second group may start before the first's math
+    if (k0 >= n) break;
     float c[4][4];
     dot32_mma<NK>(af, kbase + (int64_t)k0 * rs, rs, n - k0, lane, c);
 #pragma unroll
@@ -329,7 +331,7 @@ __device__ __forceinline__ void pv_reduce(float (&acc)[GM][8]) {
 }
 
 template <int NK, int GM>
-__global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_bf16_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(kDecWarps * 32, 2) sparse_decode_bf16_kernel(DecodeParams p) {
   constexpr int D = NK * 16, LPR = 2 * NK;
   extern __shared__ __align__(16) float smem[];
   const int G = p.h_q / p.h_kv;
@@ -347,8 +349,12 @@ __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_bf16_kernel(Deco
   const int32_t* ids = p.idx + (((int64_t)b * p.L + l) * p.h_kv + h) * p.K;
   const bf16* wts = static_cast<const bf16*>(p.w) + row0 * p.num_weights;
   const int nchunk = p.T / p.S;
-  int nvalid = 0;
-  while (nvalid < p.K && ids[nvalid] >= 0) ++nvalid;
+  int nvalid = p.K;                                   // ids are valid up to the first negative one
+  for (int k0 = 0; k0 < p.K; k0 += 32) {
+    const int id = (k0 + lane < p.K) ? ids[k0 + lane] : -1;
+    const uint32_t neg = __ballot_sync(0xffffffffu, id < 0);
+    if (neg) { nvalid = min(p.K, k0 + __ffs(neg) - 1); break; }
+  }
   float acc[GM][8];
 #pragma unroll
   for (int g = 0; g < GM; ++g)
@@ -402,7 +408,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_bf16_kernel(Deco
 constexpr int kSwaDecTile = 32;      // keys per warp step
 
 template <int NK, int GM>
-__global__ void __launch_bounds__(kDecWarps * 32) swa_decode_bf16_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(DecodeParams p) {
   constexpr int D = NK * 16, LPR = 2 * NK;
   extern __shared__ __align__(16) float smem[];
   const int G = p.h_q / p.h_kv;

@@ -1,0 +1,120 @@
+// One decode step of the HiLS attention chain as a single host call.
+//
+// The reference runs this step as a sequence of Python-level ops (models/FlashHiLS/hils_attention.py:512-633
+// with one new token per sequence: cache append, sliding-window branch, chunk selection, prior-bias gather and
+// inter-chunk softmax, sparse chunk attention, combine).  At decode sizes the kernels take a few hundred
+// microseconds in total, comparable to the host time of issuing them one by one through an interpreter;
+// this entry point issues all of them back to back on one stream.  The batch is folded into the head
+// dimension (every stage is independent per (sequence, head)): `heads_*` below are batch * heads.
+#include "common.cuh"
+
+namespace hils {
+
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ src, T* __restrict__ dst, int n) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < n) dst[i] = from_f<T>(src[i]);
+}
+
+static size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct StepLayout {
+  size_t swa_o, lse32, lse_act, scores, weights, indices, topk_ws, total;
+};
+
+static StepLayout step_layout(int heads_q, int heads_kv, int D, int K, int N, int softmax1, int dtype, int h_t, int g_t) {
+  const size_t es = dtype == HILS_BF16 ? 2 : 4;
+  StepLayout s;
+  size_t o = 0;
+  s.swa_o = o;   o += up256((size_t)heads_q * D * es);
+  s.lse32 = o;   o += up256((size_t)heads_q * 4);
+  s.lse_act = o; o += up256((size_t)heads_q * es);
+  s.scores = o;  o += up256((size_t)heads_q * K * es);
+  s.weights = o; o += up256((size_t)heads_q * (K + 1 + (softmax1 ? 1 : 0)) * es);
+  s.indices = o; o += up256((size_t)heads_kv * K * 4);
+  s.topk_ws = o; o += up256(hils_topk_fwd_workspace_bytes(1, 1, N, h_t, g_t, D, dtype));
+  s.total = o;
+  return s;
+}
+
+// selection runs with shared keys (one key head per kv head) or per-q-head keys
+static bool topk_shape(int heads_q, int heads_kv, int heads_lmk, int* h_t, int* g_t, int* per_qhead) {
+  if (heads_lmk == heads_kv) { *h_t = heads_kv; *g_t = heads_q / heads_kv; *per_qhead = 0; return true; }
+  if (heads_lmk == heads_q) { *h_t = heads_kv; *g_t = heads_q / heads_kv; *per_qhead = 1; return true; }
+  return false;
+}
+
+}  // namespace hils
+
+using namespace hils;
+
+extern "C" size_t hils_decode_step_workspace_bytes(int heads_q, int heads_kv, int heads_lmk, int D, int K, int N,
+                                                   int softmax1, int dtype) {
+  int h_t, g_t, pq;
+  if (heads_kv <= 0 || heads_q % heads_kv != 0 || !topk_shape(heads_q, heads_kv, heads_lmk, &h_t, &g_t, &pq)) return 0;
+  return step_layout(heads_q, heads_kv, D, K, N, softmax1, dtype, h_t, g_t).total;
+}
+
+extern "C" int hils_decode_step(const void* q, const void* lmk_q, const void* k_new, const void* v_new, void* k_store, void* v_store,
+                                int len, const void* lmk_k, const float* prior_b, int N, void* o, int32_t* indices_out,
+                                int heads_q, int heads_kv, int heads_lmk, int D, int K, int chunk_size, int window_size,
+                                int softmax1, float sm_scale, int dtype, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  HILS_REQUIRE(dtype == HILS_BF16 || dtype == HILS_F32, "decode_step: dtype must be bf16 or fp32");
+  HILS_REQUIRE(heads_q > 0 && heads_kv > 0 && heads_q % heads_kv == 0, "decode_step: heads_q must be a multiple of heads_kv");
+  HILS_REQUIRE(len >= 0 && N >= 0 && K > 0 && D > 0 && chunk_size > 0, "decode_step: bad size");
+  int h_t, g_t, per_qhead;
+  HILS_REQUIRE(topk_shape(heads_q, heads_kv, heads_lmk, &h_t, &g_t, &per_qhead),
+               "decode_step: the chunk keys must have heads_kv or heads_q heads");
+  if (len + 1 < chunk_size || N == 0) {
+    set_error("decode_step: no complete chunk yet; run the step op by op");
+    return HILS_ERR_UNSUPPORTED;
+  }
+  HILS_REQUIRE(q && lmk_q && k_new && v_new && k_store && v_store && lmk_k && o, "decode_step: null pointer");
+  const StepLayout lay = step_layout(heads_q, heads_kv, D, K, N, softmax1, dtype, h_t, g_t);
+  if (!workspace || workspace_bytes < lay.total) {
+    set_error("decode_step: workspace of %zu bytes needed, %zu given", lay.total, workspace_bytes);
+    return HILS_ERR_WORKSPACE;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t es = dtype == HILS_BF16 ? 2 : 4;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  void* swa_o = ws + lay.swa_o;
+  float* lse32 = reinterpret_cast<float*>(ws + lay.lse32);
+  void* lse_act = ws + lay.lse_act;
+  void* scores = ws + lay.scores;
+  void* weights = ws + lay.weights;
+  int32_t* indices = indices_out ? indices_out : reinterpret_cast<int32_t*>(ws + lay.indices);
+  // 1. append the new token to the token-major store
+  const size_t row_bytes = (size_t)heads_kv * D * es;
+  cudaError_t e = cudaMemcpyAsync(static_cast<unsigned char*>(k_store) + (size_t)len * row_bytes, k_new, row_bytes,
+                                  cudaMemcpyDeviceToDevice, st);
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(static_cast<unsigned char*>(v_store) + (size_t)len * row_bytes, v_new, row_bytes,
+                        cudaMemcpyDeviceToDevice, st);
+  if (e != cudaSuccess) return cuda_fail(e, "decode_step (store append)");
+  const int T = len + 1;
+  // 2. sliding-window branch over the store, landmark columns masked, left edge snapped to the chunk
+  if (int rc = hils_swa_fwd(q, k_store, v_store, swa_o, lse32, 1, 1, T, heads_q, heads_kv, D, D, window_size, chunk_size, 1,
+                            1, sm_scale, 0, dtype, stream))
+    return rc;
+  // 3. the chain carries the log-sum-exp in the activation dtype
+  if (dtype == HILS_BF16) cast_rows_kernel<bf16><<<(heads_q + 255) / 256, 256, 0, st>>>(lse32, (bf16*)lse_act, heads_q);
+  else cast_rows_kernel<float><<<(heads_q + 255) / 256, 256, 0, st>>>(lse32, (float*)lse_act, heads_q);
+  HILS_LAUNCH_CHECK("decode_step (lse cast)");
+  // 4. chunk selection at absolute position `len`
+  if (int rc = hils_topk_fwd(lmk_q, lmk_k, lse_act, prior_b, nullptr, nullptr, indices, scores, nullptr, nullptr, 1, 1, N, h_t, g_t,
+                             D, K, chunk_size, window_size, 1, len, per_qhead, sm_scale, dtype, dtype, ws + lay.topk_ws,
+                             lay.total - lay.topk_ws, stream))
+    return rc;
+  // 5. prior-bias gather + softmax over [chunks, window(, 0)]
+  const int nw = K + 1 + (softmax1 ? 1 : 0);
+  if (int rc = hils_chunk_weights_fwd(scores, indices, prior_b, lse_act, weights, 1, 1, N, heads_q, heads_kv, K, softmax1,
+                                      dtype, stream))
+    return rc;
+  // 6. sparse chunk attention over the store, then o += w_swa * o_swa
+  if (int rc = hils_sparse_attn_fwd(q, k_store, v_store, weights, indices, nullptr, o, 1, 1, T, heads_q, heads_kv, D, D, K, nw,
+                                    chunk_size, sm_scale, 1, dtype, nullptr, 0, stream))
+    return rc;
+  return hils_combine_fwd(o, swa_o, weights, o, 1, 1, heads_q, D, nw, K, dtype, stream);
+}

@@ -434,6 +434,38 @@ def inter_chunk_softmax(scores, indices, lse_swa, prior_b=None, softmax1=False):
     return _ChunkWeights.apply(scores, indices, lse_swa, prior_b, bool(softmax1))
 
 
+def decode_step(q, lmk_q, k_new, v_new, k_store, v_store, length: int, lmk_k, prior_b, topk: int, chunk_size: int = 64,
+                window_size: int = 512, softmax1: bool = False, sm_scale: Optional[float] = None,
+                workspace: Optional[torch.Tensor] = None, return_indices: bool = False):
+    """One decode step of the whole chain in a single library call
+    (models/FlashHiLS/hils_attention.py:512-633 with one new token per sequence; inference only).
+
+    Batch folded into heads: q and lmk_q (the selection's query) (heads_q, D); k_new, v_new (heads_kv, D); k_store, v_store
+    (capacity, heads_kv, D) token-major holding `length` tokens - the new token is written to row
+    `length`; lmk_k (N, heads_lmk, D) pooled chunk keys, prior_b (N, heads_q) fp32 or None.
+    Returns o (heads_q, D) [, indices (heads_kv, topk)].  `workspace` (uint8) is reused when large enough."""
+    heads_q, D = q.shape
+    heads_kv = k_new.shape[0]
+    N, heads_lmk = lmk_k.shape[0], lmk_k.shape[1]
+    assert k_store.shape[1:] == (heads_kv, D) and v_store.shape[1:] == (heads_kv, D)
+    assert k_store.shape[0] > length, "the store has no free row"
+    assert q.is_contiguous() and lmk_q.is_contiguous() and k_new.is_contiguous() and v_new.is_contiguous()
+    assert lmk_q.shape == q.shape and k_store.is_contiguous() and v_store.is_contiguous() and lmk_k.is_contiguous()
+    dt = dtype_code(q)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    pb = None if prior_b is None else prior_b.to(torch.float32).contiguous()
+    need = query("hils_decode_step_workspace_bytes", heads_q, heads_kv, heads_lmk, D, int(topk), N, int(bool(softmax1)), dt)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=q.device)
+    o = torch.empty_like(q)
+    idx = torch.empty((heads_kv, topk), dtype=torch.int32, device=q.device) if return_indices else None
+    call("hils_decode_step", ptr(q), ptr(lmk_q), ptr(k_new), ptr(v_new), ptr(k_store), ptr(v_store), int(length), ptr(lmk_k), ptr(pb),
+         N, ptr(o), ptr(idx), heads_q, heads_kv, heads_lmk, D, int(topk), int(chunk_size), int(window_size),
+         int(bool(softmax1)), float(sm_scale), dt, ptr(workspace), workspace.numel(), stream())
+    return (o, idx, workspace) if return_indices else (o, workspace)
+
+
 class _ExactChunkLogZ(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, chunk_size, window_size, sm_scale, mask_lmk):

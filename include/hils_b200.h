@@ -219,6 +219,27 @@ int hils_combine_bwd(const void* d_o, const void* o_swa, const void* weights, vo
                      void* d_weights,
                      int B, int L, int h_q, int D, int num_weights, int swa_col, int dtype, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * One decode step of the whole chain as a single call (one new token per sequence).  Replaces the
+ * op-by-op decode branch of HiLSAttention.forward (models/FlashHiLS/hils_attention.py:512-633):
+ * cache append, sliding-window branch, chunk selection at position `len`, prior-bias gather and
+ * inter-chunk softmax, sparse chunk attention, combine.  The batch is folded into the head dimension
+ * (heads_* = batch * heads), which the token-major store makes free:
+ *   q and lmk_q, the query of the selection, (heads_q, D); k_new, v_new (heads_kv, D); k_store, v_store (capacity, heads_kv, D) holding `len`
+ *   tokens, the new token is written to row `len` (capacity > len); lmk_k (N, heads_lmk, D) pooled
+ *   chunk keys with heads_lmk = heads_kv or heads_q; prior_b (N, heads_q) fp32 or NULL;
+ *   o (heads_q, D); indices_out (heads_kv, K) int32 or NULL.
+ * Returns HILS_ERR_UNSUPPORTED while the store holds no complete chunk (run the step op by op).
+ * ------------------------------------------------------------------------------------- */
+int hils_decode_step(const void* q, const void* lmk_q, const void* k_new, const void* v_new,
+                     void* k_store, void* v_store,
+                     int len, const void* lmk_k, const float* prior_b, int N, void* o, int32_t* indices_out,
+                     int heads_q, int heads_kv, int heads_lmk, int D, int K, int chunk_size, int window_size,
+                     int softmax1, float sm_scale, int dtype,
+                     void* workspace, size_t workspace_bytes, void* stream);
+size_t hils_decode_step_workspace_bytes(int heads_q, int heads_kv, int heads_lmk, int D, int K, int N,
+                                        int softmax1, int dtype);
+
 #ifdef __cplusplus
 }
 #endif

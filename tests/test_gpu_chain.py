@@ -108,6 +108,33 @@ def test_prefill_then_decode_matches_full_forward(B):
     assert cache.get_seq_length(1) == T
 
 
+@pytest.mark.parametrize("cfg", [(2, 4, 2, 64, BF), (3, 4, 4, 128, BF), (1, 2, 2, 64, F32)])
+def test_fused_decode_step_matches_op_by_op(cfg):
+    """Single-token steps through the one-call decode step (hils_decode_step) give the outputs of the
+    same steps run op by op, including across a chunk boundary (where the fused path steps aside) and
+    with a selection query different from the attention query."""
+    from hils_attention_b200.cache import HiLSCache
+    B, hq, hk, D, dtype = cfg
+    T0, n_dec, S, K, W = 640, 70, 64, 4, 128
+    q, k, v = _inputs(B, T0 + n_dec, hq, hk, D, S, 45, dtype)
+    lq = torch.randn(q.shape, generator=torch.Generator().manual_seed(46)).to(dtype)
+    qd, kd, vd, ld = q.cuda(), k.cuda(), v.cuda(), lq.cuda()
+    core = _core(hq, hk, K, S, W).eval()
+    outs = {}
+    with torch.no_grad():
+        for fused in (True, False):
+            cache = HiLSCache()
+            core(qd[:, :T0], kd[:, :T0], vd[:, :T0], ld[:, :T0], past_key_values=cache, use_cache=True)
+            res = []
+            for t in range(T0, T0 + n_dec):
+                r = core(qd[:, t:t + 1], kd[:, t:t + 1], vd[:, t:t + 1], ld[:, t:t + 1], past_key_values=cache,
+                         use_cache=True, return_aux=not fused)          # return_aux forces the op-by-op path
+                res.append(r if fused else r[0])
+            outs[fused] = torch.cat(res, 1)
+            assert cache.get_seq_length(1) == T0 + n_dec
+    check(outs[True], outs[False], dtype, "fused vs op-by-op decode")
+
+
 @pytest.mark.parametrize("B", [1])
 def test_full_size_properties(B):
     """Benchmark-sized sequence (T=8192, 16 heads, D=64, K=32): size-independent properties.
