@@ -397,8 +397,13 @@ def main():
     dom = "sparse_attn_bwd" if t_bwd > t_fwd else "sparse_attn_fwd"
     f_dom, t_dom = (f_bwd, t_bwd) if t_bwd > t_fwd else (f_fwd, t_fwd)
     achieved = f_dom / (t_dom / 1e3) / 1e12
+    # DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
+    # profiles/sparse_and_selection_kernels_c2.md (dram__bytes_read.sum + dram__bytes_write.sum; the backward
+    # is the dq pass plus the dkv pass); captured at c2 only
+    traffic = {"sparse_attn_bwd": (724 + 301 + 622 + 246) * 1e6, "sparse_attn_fwd": (586 + 123) * 1e6}[dom] \
+        if args.workload == "c2" else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-                "frac": achieved / pk["tflops"], "traffic": None, "kernel": dom,
+                "frac": achieved / pk["tflops"], "traffic": traffic, "kernel": dom,
                 "kernel_ms": t_dom, "peak_source": pk["source"],
                 "sparse_attn_fwd_ms": t_fwd, "sparse_attn_bwd_ms": t_bwd,
                 "algorithmic_flops_fwd": f_fwd, "algorithmic_flops_bwd": f_bwd}
