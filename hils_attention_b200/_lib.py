@@ -47,6 +47,8 @@ SIGNATURES = {
     "hils_combine_bwd": (_I, [_P] * 5 + [_I] * 7 + [_P]),
     "hils_decode_step": (_I, [_P] * 6 + [_I] + [_P] * 2 + [_I] + [_P] * 2 + [_I] * 8 + [_F, _I, _P, _SZ, _P]),
     "hils_decode_step_workspace_bytes": (_SZ, [_I] * 8),
+    "hils_norm_rope_fwd": (_I, [_P] * 6 + [_I] * 5 + [_F, _I, _I, _P]),
+    "hils_norm_rope_bwd": (_I, [_P] * 8 + [_I] * 7 + [_P]),
 }
 
 # kernels each entry point launches (memsets excluded); used to report launch counts
@@ -55,6 +57,7 @@ KERNELS_PER_CALL = {
     "hils_topk_fwd": 1, "hils_topk_bwd": 2, "hils_topk_bwd_noalloc": 2, "hils_sparse_attn_fwd": 1, "hils_sparse_attn_bwd": 3,
     "hils_chunk_logz_fwd": 1, "hils_chunk_logz_bwd": 2, "hils_swa_fwd": 1, "hils_swa_bwd": 2,
     "hils_chunk_weights_fwd": 1, "hils_chunk_weights_bwd": 1, "hils_combine_fwd": 1, "hils_combine_bwd": 1,
+    "hils_norm_rope_fwd": 1, "hils_norm_rope_bwd": 1,
     "hils_decode_step": 7,   # window, cast, key stream, selection, weights, sparse, combine (the 2 copies not counted)
 }
 _launches = 0

@@ -212,6 +212,8 @@ def install_into_reference() -> None:
         "ops.exact_chunk_log_z_tilelang": {"exact_chunk_log_z_tl": ops.exact_chunk_log_z_tl},
         "ops.flex_attn_tilelang": {"flex_attn_tl": ops.flex_attn_tl,
                                    "flex_attn_tl_two_phase": ops.flex_attn_tl_two_phase},
+        "ops.rope_tilelang_fp32": {"single_tensor_rope_autograd": ops.single_tensor_rope_autograd,
+                                   "rope_rotary_pos_emb": ops.rope_rotary_pos_emb},
     }
     pkg = sys.modules.get("ops")
     if pkg is None:

@@ -466,6 +466,75 @@ def decode_step(q, lmk_q, k_new, v_new, k_store, v_store, length: int, lmk_k, pr
     return (o, idx, workspace) if return_indices else (o, workspace)
 
 
+# ------------------------------------------------------------------------------------------
+# per-head RMSNorm + rotary embedding
+# ------------------------------------------------------------------------------------------
+class _NormRope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, cos, sin, eps):
+        B, L, H, D = x.shape
+        xc = x.contiguous()
+        w = None if weight is None else weight.to(x.dtype).contiguous()
+        cs_batched, cs_code = 0, dtype_code(xc)
+        c = s_ = None
+        if cos is not None:
+            assert sin is not None and cos.shape == sin.shape and cos.dtype == sin.dtype
+            c, s_ = cos, sin
+            if c.dim() == 3 and c.shape[0] == 1:
+                c, s_ = c[0], s_[0]
+            if c.dim() == 3:
+                assert c.shape == (B, L, D), f"cos shape {tuple(cos.shape)} != ({B}, {L}, {D})"
+                cs_batched = 1
+            else:
+                assert c.shape == (L, D), f"cos shape {tuple(cos.shape)} != ({L}, {D})"
+            if c.dtype not in (torch.float32, torch.bfloat16):
+                c, s_ = c.float(), s_.float()
+            c, s_ = c.contiguous(), s_.contiguous()
+            cs_code = dtype_code(c)
+        out = torch.empty_like(xc)
+        rstd = torch.empty((B, L, H), dtype=torch.float32, device=x.device) if w is not None else None
+        call("hils_norm_rope_fwd", ptr(xc), ptr(w), ptr(c), ptr(s_), ptr(out), ptr(rstd), B, L, H, D, cs_batched,
+             float(eps), dtype_code(xc), cs_code, stream())
+        ctx.save_for_backward(xc, *(t for t in (w, c, s_, rstd) if t is not None))
+        ctx.meta = (B, L, H, D, cs_batched, cs_code, w is not None, c is not None,
+                    None if weight is None else weight.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        B, L, H, D, cs_batched, cs_code, has_w, has_cs, w_dtype = ctx.meta
+        saved = list(ctx.saved_tensors)
+        xc = saved.pop(0)
+        w = saved.pop(0) if has_w else None
+        c = saved.pop(0) if has_cs else None
+        s_ = saved.pop(0) if has_cs else None
+        rstd = saved.pop(0) if has_w else None
+        g = d_out.contiguous().to(xc.dtype)
+        d_x = torch.empty_like(xc)
+        d_w = torch.empty((D,), dtype=torch.float32, device=xc.device) if has_w else None
+        call("hils_norm_rope_bwd", ptr(xc), ptr(w), ptr(c), ptr(s_), ptr(rstd), ptr(g), ptr(d_x), ptr(d_w), B, L, H, D,
+             cs_batched, dtype_code(xc), cs_code, stream())
+        return d_x, (None if d_w is None else d_w.to(w_dtype)), None, None, None
+
+
+def rmsnorm_rope(x, weight=None, cos=None, sin=None, eps: float = 1e-6):
+    """Per-head RMSNorm (models/FlashHiLS/modeling_olmo_hils.py:105-111) followed by the rotary embedding
+    (ops/rope_tilelang_fp32.py:96-181) in one pass.  x (B,L,H,D); weight (D,) or None; cos, sin (L,D),
+    (1,L,D) or (B,L,D), bf16 or fp32, or None.  Differentiable with respect to x and weight."""
+    return _NormRope.apply(x, weight, cos, sin, float(eps))
+
+
+def single_tensor_rope_autograd(x, x_cos, x_sin):
+    """Rotary embedding of one tensor (ops/rope_tilelang_fp32.py:173-182): x (B,L,H,D); x_cos, x_sin
+    (B,L,D) / (1,L,D) / (L,D), bf16 or fp32; returns x's dtype."""
+    return _NormRope.apply(x, None, x_cos, x_sin, 0.0)
+
+
+def rope_rotary_pos_emb(q, k, cos, sin):
+    """Rotary embedding of q and k (ops/rope_tilelang_fp32.py:84-88): returns (q_out, k_out)."""
+    return _NormRope.apply(q, None, cos, sin, 0.0), _NormRope.apply(k, None, cos, sin, 0.0)
+
+
 class _ExactChunkLogZ(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, chunk_size, window_size, sm_scale, mask_lmk):

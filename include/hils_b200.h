@@ -240,6 +240,23 @@ int hils_decode_step(const void* q, const void* lmk_q, const void* k_new, const 
 size_t hils_decode_step_workspace_bytes(int heads_q, int heads_kv, int heads_lmk, int D, int K, int N,
                                         int softmax1, int dtype);
 
+/* ---------------------------------------------------------------------------------------
+ * Per-head RMSNorm followed by the rotary embedding in one pass (upstream of the attention path).
+ * Replaces rms_norm (models/FlashHiLS/modeling_olmo_hils.py:105-111, per-head q_norm / k_norm /
+ * lmk_q_norm of hils_attention.py:250-253, :296-321) chained with single_tensor_rope_autograd
+ * (ops/rope_tilelang_fp32.py:96-181; fp32 x*cos + rotate_half(x)*sin, rounded once).
+ *   x, out, d_out, d_x (B,L,H,D) in `dtype`; weight (D) in `dtype` or NULL (no norm);
+ *   cos, sin (L,D) shared over the batch (cos_batched = 0) or (B,L,D) (cos_batched = 1), in
+ *   `cs_dtype`, or both NULL (no rotation); rstd (B,L,H) fp32 written by the forward when weight is
+ *   given and read by the backward; d_weight (D) fp32, zeroed here and accumulated with atomics.
+ * ------------------------------------------------------------------------------------- */
+int hils_norm_rope_fwd(const void* x, const void* weight, const void* cos, const void* sin, void* out,
+                       float* rstd, int B, int L, int H, int D, int cos_batched, float eps,
+                       int dtype, int cs_dtype, void* stream);
+int hils_norm_rope_bwd(const void* x, const void* weight, const void* cos, const void* sin,
+                       const float* rstd, const void* d_out, void* d_x, float* d_weight,
+                       int B, int L, int H, int D, int cos_batched, int dtype, int cs_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -15,6 +15,9 @@ were produced by running the reference's own PyTorch functions
   sparse attn     ops/hils_fwd_bwd_head.py:21-93            (hils_torch_ref)
   exact log Z     models/NaiveBSA/naive_bsa_kernel.py:39-118 (exact_chunk_log_z)
   whole naive-BSA models/NaiveBSA/naive_bsa_ref.py:50-187   (naive_bsa_attention)
+  norm + rotary   models/FlashHiLS/modeling_olmo_hils.py:105-111 (rms_norm, executed from its source
+                  text) and ops/rope_tilelang_fp32.py:185-189, :244-247 (rotate_half_torch and the
+                  torch formula of that file's own correctness test)
   SWA mask        ops/flex_attn_tilelang.py:1366-1376       (mask_mod of the torch reference;
                   that reference itself needs a CUDA device, so the SWA restatement is pinned
                   through the naive-BSA identity and through naive_bsa_ref's local branch)
@@ -170,6 +173,34 @@ def inter_chunk_weights(scores: torch.Tensor, indices: torch.Tensor, lse_swa: to
     if softmax1:
         cols.append(torch.zeros(B, L, h_q, 1, dtype=s.dtype))
     return F.softmax(torch.cat(cols, dim=-1), dim=-1).to(dt)
+
+
+# --------------------------------------------------------------------------
+# per-head RMSNorm followed by rotary embedding (upstream of the path)
+#   rms_norm: models/FlashHiLS/modeling_olmo_hils.py:105-111 (fp32 statistics, the normalised
+#   tensor rounded to the input dtype, then multiplied by the weight in that dtype)
+#   rotary:   ops/rope_tilelang_fp32.py:120-134 = x*cos + rotate_half(x)*sin in fp32, rounded once
+# --------------------------------------------------------------------------
+def rmsnorm_rope(x: torch.Tensor, weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                 cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x (B,L,H,D); weight (D,) or None (no norm); cos, sin (L,D), (1,L,D) or (B,L,D) or None (no
+    rotation).  Output in x's dtype."""
+    dt = x.dtype
+    y = x
+    if weight is not None:
+        xf = x.float()
+        var = xf.pow(2).mean(-1, keepdim=True)
+        y = weight.to(dt) * (xf * torch.rsqrt(var + eps)).to(dt)
+    if cos is not None:
+        c, s_ = cos.float(), sin.float()
+        if c.dim() == 2:
+            c, s_ = c.unsqueeze(0), s_.unsqueeze(0)
+        c, s_ = c.unsqueeze(2), s_.unsqueeze(2)                      # (Bc, L, 1, D)
+        yf = y.float()
+        half = yf.shape[-1] // 2
+        rot = torch.cat((-yf[..., half:], yf[..., :half]), dim=-1)
+        y = (yf * c + rot * s_).to(dt)
+    return y
 
 
 # --------------------------------------------------------------------------

@@ -10,6 +10,9 @@ Reference functions executed:
   ops/hils_fwd_bwd_head.py          hils_torch_ref
   models/NaiveBSA/naive_bsa_kernel.py  exact_chunk_log_z      (loaded by file path)
   models/NaiveBSA/naive_bsa_ref.py     naive_bsa_attention    (loaded by file path)
+  models/FlashHiLS/modeling_olmo_hils.py  rms_norm            (its source text is compiled on its own:
+                                                               the module imports packages absent here)
+  ops/rope_tilelang_fp32.py         rotate_half_torch, with the torch formula of that file's test
 Each fixture stores the inputs (fp32 arrays; bf16 cases hold bf16-representable values),
 the call's scalar arguments and the reference outputs / autograd gradients.
 """
@@ -138,7 +141,53 @@ def main(ref_root):
         np.savez_compressed(os.path.join(HERE, f"bsa_{tag}.npz"), q=_np(q), k=_np(k), v=_np(v), o=_np(o),
                             lse_swa=_np(aux["log_Z_swa"]), log_z=_np(aux["log_Z_chunk"]),
                             args=np.array([S, W, K, int(ml)], dtype=np.int64))
+    norm_rope_fixtures(ref_root)
     print("golden fixtures written to", HERE)
+
+
+def _function_from_source(path, name):
+    """Compile ONE top-level function of a reference file from its source text (for modules whose
+    imports are not installed here) and return it."""
+    import ast
+    src = open(path).read()
+    node = next(n for n in ast.parse(src).body if isinstance(n, ast.FunctionDef) and n.name == name)
+    ns = {"torch": torch}
+    exec(compile(ast.Module(body=[node], type_ignores=[]), path, "exec"), ns)
+    return ns[name]
+
+
+def norm_rope_fixtures(ref_root):
+    """Per-head RMSNorm (the reference's rms_norm) followed by the rotary embedding (the reference's
+    rotate_half_torch in the formula of its own test), forward and autograd gradients."""
+    sys.path.insert(0, ref_root)
+    from ops.rope_tilelang_fp32 import rotate_half_torch
+    rms_norm = _function_from_source(os.path.join(ref_root, "models/FlashHiLS/modeling_olmo_hils.py"), "rms_norm")
+    for tag, (B, L, H, D, shared, cs_fp32, dt) in {"a": (2, 40, 3, 64, True, False, torch.bfloat16),
+                                                   "b": (1, 33, 2, 128, False, True, torch.bfloat16),
+                                                   "c": (1, 20, 2, 64, True, True, torch.float32)}.items():
+        g = torch.Generator().manual_seed(600 + ord(tag))
+        x = torch.randn(B, L, H, D, generator=g).to(dt)
+        w = (1.0 + 0.2 * torch.randn(D, generator=g)).to(dt)
+        freqs = torch.randn(1 if shared else B, L, D // 2, generator=g)
+        emb = torch.cat((freqs, freqs), dim=-1)
+        cs_dt = torch.float32 if cs_fp32 else torch.bfloat16
+        cos, sin = emb.cos().to(cs_dt), emb.sin().to(cs_dt)
+        do = torch.randn(B, L, H, D, generator=g).to(dt)
+        # fp32 leaves for the gradients, values representable in dt
+        xl, wl = x.float().requires_grad_(True), w.float().requires_grad_(True)
+        y = rms_norm(xl.to(dt), wl.to(dt), 1e-6)                                   # (B,L,H,D) in dt
+        yr = y.transpose(1, 2).float()                                             # (B,H,L,D)
+        out = ((yr * cos.float().unsqueeze(1)) + (rotate_half_torch(yr) * sin.float().unsqueeze(1))) \
+            .transpose(1, 2).contiguous().to(dt)
+        out_norm_only = y.detach().clone()
+        rope_only = ((x.transpose(1, 2).float() * cos.float().unsqueeze(1))
+                     + (rotate_half_torch(x.transpose(1, 2).float()) * sin.float().unsqueeze(1))) \
+            .transpose(1, 2).contiguous().to(dt)
+        out.backward(do)
+        np.savez_compressed(os.path.join(HERE, f"normrope_{tag}.npz"), x=_np(x), w=_np(w), cos=_np(cos), sin=_np(sin),
+                            do=_np(do), out=_np(out), out_norm_only=_np(out_norm_only), out_rope_only=_np(rope_only),
+                            dx=_np(xl.grad), dw=_np(wl.grad),
+                            args=np.array([int(dt == torch.bfloat16), int(cs_fp32)], dtype=np.int64))
 
 
 if __name__ == "__main__":

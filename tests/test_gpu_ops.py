@@ -540,3 +540,30 @@ def test_sparse_attn_combine_matches_separate_ops(ops, dtype):
         outs.append([o.detach()] + [t.grad for t in (q, k, v, w, so)])
     for a, b, n in zip(outs[0], outs[1], ("o", "dq", "dk", "dv", "dw", "d_swa_o")):
         check(a, b, dtype, n, scale=2.0 if n == "dw" else 1.0)
+
+
+# ------------------------------------------------------------------ per-head RMSNorm + rotary embedding
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_norm_rope_golden(ops, tag):
+    g = golden(f"normrope_{tag}.npz")
+    dt = BF if int(g["args"][0]) else F32
+    cs_dt = F32 if int(g["args"][1]) else BF
+    x = cuda(g["x"], dt).requires_grad_(True)
+    w = cuda(g["w"], dt).requires_grad_(True)
+    cos, sin = cuda(g["cos"], cs_dt), cuda(g["sin"], cs_dt)
+    out = ops.rmsnorm_rope(x, w, cos, sin, eps=1e-6)
+    assert out.dtype == dt
+    check(out, g["out"], dt, "norm+rope")
+    out.backward(cuda(g["do"], dt))
+    check(x.grad, g["dx"], dt, "dx", scale=3.0)
+    check(w.grad, g["dw"], dt, "dw", scale=30.0)
+    check(ops.rmsnorm_rope(x.detach(), w.detach()), g["out_norm_only"], dt, "norm only")
+    check(ops.single_tensor_rope_autograd(x.detach(), cos, sin), g["out_rope_only"], dt, "rope only")
+    qo, ko = ops.rope_rotary_pos_emb(x.detach(), x.detach()[:, :, :1].contiguous(), cos, sin)
+    check(qo, g["out_rope_only"], dt, "rope q")
+    check(ko, g["out_rope_only"][:, :, :1], dt, "rope k")
+    # rotation is orthogonal: the backward of the rotation alone is its inverse
+    xr = x.detach().clone().requires_grad_(True)
+    ops.single_tensor_rope_autograd(xr, cos.float(), sin.float()).backward(
+        ops.single_tensor_rope_autograd(x.detach(), cos.float(), sin.float()))
+    check(xr.grad, x.detach(), dt, "rope^T rope = id", scale=2.0)

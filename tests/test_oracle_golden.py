@@ -103,3 +103,18 @@ def test_chain_runs_and_weights_sum_to_one():
     idx = aux["indices"]
     lim = orc.remote_chunk_limit(torch.arange(L), 64, S).view(1, L, 1, 1)
     assert bool(((idx < lim) | (idx < 0)).all())
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_norm_rope_matches_reference(tag):
+    """Oracle restatement of per-head RMSNorm + rotary embedding against fixtures produced by the
+    reference's rms_norm and rotate_half_torch."""
+    d = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", f"normrope_{tag}.npz"))
+    g = {k: torch.from_numpy(d[k]) for k in d.files}
+    dt = torch.bfloat16 if int(g["args"][0]) else torch.float32
+    cs_dt = torch.float32 if int(g["args"][1]) else torch.bfloat16
+    x, w = g["x"].to(dt), g["w"].to(dt)
+    cos, sin = g["cos"].to(cs_dt), g["sin"].to(cs_dt)
+    assert torch.equal(orc.rmsnorm_rope(x, w, 1e-6, cos, sin).float(), g["out"])
+    assert torch.equal(orc.rmsnorm_rope(x, w, 1e-6).float(), g["out_norm_only"])
+    assert torch.equal(orc.rmsnorm_rope(x, None, 1e-6, cos, sin).float(), g["out_rope_only"])
