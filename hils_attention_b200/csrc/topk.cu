@@ -420,23 +420,41 @@ struct SelLayout {
   size_t q_off, k_off, v_off, add_off, lt_off, lim_off, bits_off, total;
 };
 
-static SelLayout sel_layout(int G, int D, int N, int cta_tiles_max) {
+static SelLayout sel_layout_for(int G, int D, int N, int RB, int NS) {
   SelLayout s;
-  s.RB = (G == 1) ? 64 : (G == 2) ? 32 : 16;
-  s.M = s.RB * G;
+  s.RB = RB;
+  s.M = RB * G;
   s.Npad = (N + kSelTile - 1) / kSelTile * kSelTile;
   s.RSV = s.Npad + 8;                                      // row stride of the score rows (floats)
-  s.NS = cta_tiles_max > 1 ? 2 : 1;
+  s.NS = NS;
   size_t o = 0;
   s.q_off = o;    o += (size_t)s.M * (D + 8) * 2;
-  s.k_off = o;    o += (size_t)s.NS * kSelTile * (D + 8) * 2;
+  // the key tiles are dead once the scores are formed: the per-warp key-bit rows of the selection reuse them
+  s.k_off = o;    s.bits_off = o;
+  o += std::max((size_t)NS * kSelTile * (D + 8) * 2, (size_t)4 * s.Npad * (4 + 2));   // bits (u32) + ids (u16) per warp
   s.v_off = o;    o += (size_t)s.M * s.RSV * 4;
   s.add_off = o;  o += (size_t)G * s.Npad * 4;
   s.lt_off = o;   o += (size_t)s.M * 4;
-  s.lim_off = o;  o += (size_t)s.RB * 4;
-  s.bits_off = o; o += (size_t)4 * s.Npad * 4;
+  s.lim_off = o;  o += (size_t)RB * 4;
   s.total = o;
   return s;
+}
+
+// Rows per CTA: as many tokens as keep three (else two, else one) CTAs resident per SM with the scores of
+// all candidates in shared memory.  total == 0: no layout fits.
+static SelLayout sel_layout(int G, int D, int N, int cta_tiles_max, int per_qhead) {
+  const int rb_max = (G == 1) ? 64 : (G == 2) ? 32 : 16;
+  const size_t classes[3] = {75 * 1024, 113 * 1024, 200 * 1024};
+  for (int c = 0; c < 3; ++c)
+    for (int RB = rb_max; RB >= 1; RB >>= 1) {
+      if ((RB * G) % 16 != 0 || RB * G > 256 || (per_qhead && RB % 16 != 0)) continue;
+      for (int NS = (cta_tiles_max > 1 ? 2 : 1); NS >= 1; --NS) {
+        const SelLayout s = sel_layout_for(G, D, N, RB, NS);
+        if (s.total <= classes[c]) return s;
+      }
+    }
+  SelLayout none = {};
+  return none;
 }
 
 template <int NK>   // NK = D / 16
@@ -609,6 +627,7 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
 
   // ---------------- per token: ranking keys, K-th largest by bisection, ordered compaction ------------------
   uint32_t* bits = bits_s + warp * Npad;
+  uint16_t* cand_id = reinterpret_cast<uint16_t*>(bits_s + 4 * Npad) + warp * Npad;   // long rows: ids of the survivors
   bf16* scores = static_cast<bf16*>(p.scores);
   const uint32_t lt_mask = (1u << lane) - 1u;
   for (int tok = warp; tok < RB; tok += 4) {
@@ -618,6 +637,7 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
     const int lim32 = (lim + 31) & ~31;
     const int key_end = p.rank_keys ? ((p.N + 31) & ~31) : lim32;
     int n_cand = 0;
+    uint32_t lane_max = 0u;
     __syncwarp();
     for (int c = lane; c < key_end; c += 32) {
       float key = -CUDART_INF_F;
@@ -633,19 +653,28 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
       const uint32_t u = (key > -CUDART_INF_F) ? order_bits(key) : 0u;   // false for NaN too
       if (c < lim32) bits[c] = u;
       n_cand += (u != 0u) ? 1 : 0;
+      lane_max = max(lane_max, u);
     }
     n_cand = __reduce_add_sync(0xffffffffu, n_cand);
     __syncwarp();
     // thr / take: chunks with bits > thr are selected, plus the `take` lowest-id chunks with bits == thr
     uint32_t thr = 0u;
-    int take = 0;
+    int take = 0, scan_end = lim32;
+    bool compacted = false;
     if (n_cand > K) {
+      // The K-th largest lies between the smallest per-lane maximum (32 distinct elements are at least that
+      // large; used for K <= 32) and the row maximum: the bits above their highest differing bit are known.
+      const uint32_t row_max = __reduce_max_sync(0xffffffffu, lane_max);
+      const uint32_t floor_u = (K <= 32) ? __reduce_min_sync(0xffffffffu, lane_max) : 0u;
+      const uint32_t diff = row_max ^ floor_u;
+      const int top = diff ? 31 - __clz(diff) : -1;
+      thr = (top >= 0) ? (top == 31 ? 0u : (row_max & ~((2u << top) - 1u))) : row_max;
       if (lim32 <= 128) {                                   // the whole row in registers
         uint32_t u[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) u[i] = (lane + 32 * i < lim32) ? bits[lane + 32 * i] : 0u;
         bool exact = false;
-        for (int bit = 31; bit >= 0; --bit) {
+        for (int bit = top; bit >= 0; --bit) {
           const uint32_t trial = thr | (1u << bit);
           int cnt = (u[0] >= trial) + (u[1] >= trial) + (u[2] >= trial) + (u[3] >= trial);
           cnt = __reduce_add_sync(0xffffffffu, cnt);
@@ -661,11 +690,32 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
           take = K - __reduce_add_sync(0xffffffffu, gt);
         }
       } else {
+        // long row: keep only the survivors (bits >= floor_u), compacted in id order together with their
+        // ids, then bisect and select over the short survivor list
+        if (floor_u > 0u && Npad <= 65536) {
+          int n_s = 0;
+          for (int c0 = 0; c0 < lim32; c0 += 32) {
+            const uint32_t u = bits[c0 + lane];
+            const bool keep = u >= floor_u;
+            const uint32_t m = __ballot_sync(0xffffffffu, keep);
+            if (keep) {
+              const int pos = n_s + __popc(m & lt_mask);     // pos <= c0 + lane: in place is safe
+              bits[pos] = u;
+              cand_id[pos] = (uint16_t)(c0 + lane);
+            }
+            n_s += __popc(m);
+          }
+          const int n_s32 = (n_s + 31) & ~31;
+          if (n_s + lane < n_s32) bits[n_s + lane] = 0u;      // pad the last group
+          __syncwarp();
+          compacted = true;
+          scan_end = n_s32;
+        }
         bool exact = false;
-        for (int bit = 31; bit >= 0; --bit) {
+        for (int bit = top; bit >= 0; --bit) {
           const uint32_t trial = thr | (1u << bit);
           int cnt = 0;
-          for (int c = lane; c < lim32; c += 32) cnt += (bits[c] >= trial) ? 1 : 0;
+          for (int c = lane; c < scan_end; c += 32) cnt += (bits[c] >= trial) ? 1 : 0;
           cnt = __reduce_add_sync(0xffffffffu, cnt);
           if (cnt >= K) {
             thr = trial;
@@ -676,7 +726,7 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
           thr -= 1u;
         } else {
           int gt = 0;
-          for (int c = lane; c < lim32; c += 32) gt += (bits[c] > thr) ? 1 : 0;
+          for (int c = lane; c < scan_end; c += 32) gt += (bits[c] > thr) ? 1 : 0;
           take = K - __reduce_add_sync(0xffffffffu, gt);
         }
       }
@@ -685,9 +735,9 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
     int32_t* out_ids = p.indices + (((int64_t)b * p.L + l) * p.h_kv + h) * K;
     bf16* out_sc = scores + ((((int64_t)b * p.L + l) * p.h_kv + h) * G) * K;
     int n_out = 0, eq_seen = 0;
-    for (int c0 = 0; c0 < lim32; c0 += 32) {
-      const int c = c0 + lane;
-      const uint32_t u = bits[c];
+    for (int c0 = 0; c0 < scan_end; c0 += 32) {
+      const uint32_t u = bits[c0 + lane];
+      const int c = compacted ? (int)cand_id[c0 + lane] : c0 + lane;
       const bool is_eq = take > 0 && u == thr;
       const uint32_t m_eq = __ballot_sync(0xffffffffu, is_eq);
       const bool sel = (u > thr) || (is_eq && eq_seen + __popc(m_eq & lt_mask) < take);
@@ -717,8 +767,8 @@ static int launch_topk_mma(const TopkParams& p, cudaStream_t st) {
   const int max_lim = p.is_causal ? std::max(0, std::min(p.N, (p.window_size > 0)
                           ? (p.q_offset + p.L - 1 - p.window_size + 1) / p.block_size
                           : (p.q_offset + p.L - 1) / p.block_size)) : p.N;
-  const SelLayout sl = sel_layout(p.G, p.D, p.N, (max_lim + kSelTile - 1) / kSelTile);
-  if (sl.M > 256 || sl.total > 200 * 1024) return HILS_ERR_UNSUPPORTED;
+  const SelLayout sl = sel_layout(p.G, p.D, p.N, (max_lim + kSelTile - 1) / kSelTile, p.per_qhead);
+  if (sl.total == 0) return HILS_ERR_UNSUPPORTED;
   cudaFuncSetAttribute(topk_fwd_mma_kernel<NK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sl.total);
   dim3 grid((p.L + sl.RB - 1) / sl.RB, p.h_kv, p.B);
   topk_fwd_mma_kernel<NK><<<grid, 128, sl.total, st>>>(hp, sl);

@@ -153,6 +153,8 @@ def test_topk_selector_exact_and_match_rate(ops, cfg):
     (1, 3000, 1, 4, 128, 8, 8, 24, True, True, False),         # per-q-head keys, N = 375, ragged tail, drop mask
     (2, 1536, 2, 2, 64, 48, 16, 64, False, True, True),        # K > 32, gumbel noise
     (1, 640, 1, 16, 64, 4, 32, 64, False, False, False),       # 256 score rows per CTA
+    (1, 8192, 1, 1, 128, 32, 8, 16, False, False, False),      # N = 1024: 16 tokens per CTA, key-bit rows reuse the key tiles
+    (1, 4096, 2, 2, 64, 16, 4, 8, True, True, False),          # N = 1024, per-q-head keys, drop mask
 ])
 def test_topk_tensor_core_scores_path(ops, cfg):
     """bf16 training/prefill selection (scores on the tensor cores, scores resident in shared memory):
