@@ -397,9 +397,10 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
 // forms P, dw = sum_j P_j dP_j, dS = scale w P (dP - dw) (ops/hils_fwd_bwd_head.py:651-757).
 // =================================================================================================
 
-// S row in sv, dP row in dp  ->  dS row in sv, w*P row in dp; returns dw
-__device__ __forceinline__ float bwd_row(float* sv, float* dp, float wsum, float scale, float scale_log2, float slope,
-                                         int mask_last) {
+// Backward row arithmetic in two phases, so that the dP row can still be in flight from TMEM while the
+// first phase works on the S row.
+// Phase A: S row in sv  ->  e_j = exp(scale (S_j - max)) in sv; returns sum_j e_j.
+__device__ __forceinline__ float bwd_row_exp(float* sv, float scale_log2, float slope, int mask_last) {
   if (slope != 0.f) {
 #pragma unroll
     for (int j = 0; j < 62; ++j) sv[j] -= slope * (float)(62 - j);
@@ -418,21 +419,24 @@ __device__ __forceinline__ float bwd_row(float* sv, float* dp, float wsum, float
     sv[j] = ex2(fmaf(sv[j], scale_log2, -mb));
     s4[j & 3] += sv[j];
   }
-  const float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+  return (s4[0] + s4[1]) + (s4[2] + s4[3]);
+}
+// Phase B: e row in sv, dP row in dp  ->  dS row in sv (= scale w P (dP - dw)) and, when kWantWP, the
+// w*P row in dp; returns dw = sum_j P_j dP_j.  P_j = e_j / sum is never formed: the factors fold into
+// one multiplier per product.
+template <bool kWantWP>
+__device__ __forceinline__ float bwd_row_grad(float* sv, float* dp, float sum, float wsum, float scale) {
   const float inv = 1.f / sum;
   float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-  for (int j = 0; j < 64; ++j) {
-    sv[j] *= inv;
-    d4[j & 3] = fmaf(sv[j], dp[j], d4[j & 3]);
-  }
-  const float dw = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-  const float sw = scale * wsum;
+  for (int j = 0; j < 64; ++j) d4[j & 3] = fmaf(sv[j], dp[j], d4[j & 3]);
+  const float dw = ((d4[0] + d4[1]) + (d4[2] + d4[3])) * inv;
+  const float c = scale * wsum * inv, cdw = -c * dw, wp = wsum * inv;
 #pragma unroll
   for (int j = 0; j < 64; ++j) {
-    const float pj = sv[j];
-    sv[j] = sw * pj * (dp[j] - dw);
-    dp[j] = wsum * pj;
+    const float e = sv[j];
+    sv[j] = e * fmaf(c, dp[j], cdw);
+    if (kWantWP) dp[j] = wp * e;
   }
   return dw;
 }
@@ -680,12 +684,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
       float sv[64], dp[64];
       tmem_ld32(tmem + lane_base + s * 128, sv);
       tmem_ld32(tmem + lane_base + s * 128 + 32, sv + 32);
-      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);
-      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
       tmem_ld_wait();
+      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);        // in flight while the S row is exponentiated
+      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
+      float esum = 1.f;
+      if (owner) esum = bwd_row_exp(sv, scale_log2, slope, p.mask_last);
+      tmem_ld_wait64(dp);
       uint8_t* dsrow = dSs + s * 16384;
       if (owner) {
-        const float dw = bwd_row(sv, dp, wsum, p.scale, scale_log2, slope, p.mask_last);
+        const float dw = bwd_row_grad<false>(sv, dp, esum, wsum, p.scale);
         store_row_bf16_sw128(dsrow, r, sv);
         const bf16 dwb = __float2bfloat16_rn(dw);
         if (!unsorted) {
@@ -917,11 +924,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
       float sv[64], dp[64];
       tmem_ld32(tmem + lane_base + s * 128, sv);
       tmem_ld32(tmem + lane_base + s * 128 + 32, sv + 32);
-      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);
-      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
       tmem_ld_wait();
+      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);        // in flight while the S row is exponentiated
+      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
+      float esum = 1.f;
+      if (owner) esum = bwd_row_exp(sv, scale_log2, slope, p.mask_last);
+      tmem_ld_wait64(dp);
       if (owner) {
-        bwd_row(sv, dp, wsum, p.scale, scale_log2, slope, p.mask_last);
+        bwd_row_grad<true>(sv, dp, esum, wsum, p.scale);
         store_row_bf16_sw128(dSs + sb * 16384, r, sv);
         store_row_bf16_sw128(Pws + sb * 16384, r, dp);
       } else {

@@ -229,14 +229,22 @@ __global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, con
   if (warp == 4) tmem_dealloc(tmem, 256);
 }
 
-// dS row from S row (sv) and dP row (dp): P = exp2(scale*S - lse) masked; sv <- dS, dp <- P
-__device__ __forceinline__ void swa_bwd_row(float* sv, float* dp, float sl2, float lse_l2, float delta, float scale, int a,
-                                            int e, unsigned long long lm) {
+// Backward row arithmetic in two phases, so that the dP row can still be in flight from TMEM while the
+// first phase works on the S row.  Phase A: sv <- P = exp2(scale*S - lse), masked.
+__device__ __forceinline__ void swa_bwd_row_p(float* sv, float sl2, float lse_l2, int a, int e, unsigned long long lm) {
 #pragma unroll
   for (int jj = 0; jj < 64; ++jj) {
     const bool vis = jj >= a && jj <= e && !((lm >> jj) & 1ull);
-    const float pj = vis ? ex2(fmaf(sv[jj], sl2, -lse_l2)) : 0.f;
-    sv[jj] = pj * (dp[jj] - delta) * scale;
+    sv[jj] = vis ? ex2(fmaf(sv[jj], sl2, -lse_l2)) : 0.f;
+  }
+}
+// Phase B: sv <- dS = scale * P * (dP - delta), dp <- P
+__device__ __forceinline__ void swa_bwd_row_ds(float* sv, float* dp, float delta, float scale) {
+  const float nds = -delta * scale;
+#pragma unroll
+  for (int jj = 0; jj < 64; ++jj) {
+    const float pj = sv[jj];
+    sv[jj] = pj * fmaf(dp[jj], scale, nds);
     dp[jj] = pj;
   }
 }
@@ -388,10 +396,12 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dq_tc_kernel(SwaTcParams 
       float sv[64], dp[64];
       tmem_ld32(tmem + lane_base + s * 128, sv);
       tmem_ld32(tmem + lane_base + s * 128 + 32, sv + 32);
-      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);
-      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
       tmem_ld_wait();
-      swa_bwd_row(sv, dp, sl2, lse_l2, delta, p.scale, lo - j0, hi - j0, lmk_bits(p, j0));
+      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);        // in flight while P is formed
+      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
+      swa_bwd_row_p(sv, sl2, lse_l2, lo - j0, hi - j0, lmk_bits(p, j0));
+      tmem_ld_wait64(dp);
+      swa_bwd_row_ds(sv, dp, delta, p.scale);
       store_row_bf16_sw128(dSs + s * 16384, r, sv);
       fence_async_smem();
       tc_fence_before();
@@ -570,10 +580,12 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams
       float sv[64], dp[64];
       tmem_ld32(tmem + lane_base + s * 128, sv);
       tmem_ld32(tmem + lane_base + s * 128 + 32, sv + 32);
-      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);
-      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
       tmem_ld_wait();
-      swa_bwd_row(sv, dp, sl2, lse_l2, delta, p.scale, lo - j_first, hi - j_first, lm);
+      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);        // in flight while P is formed
+      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
+      swa_bwd_row_p(sv, sl2, lse_l2, lo - j_first, hi - j_first, lm);
+      tmem_ld_wait64(dp);
+      swa_bwd_row_ds(sv, dp, delta, p.scale);
       store_row_bf16_sw128(dSs + sb * 16384, r, sv);
       store_row_bf16_sw128(Pws + sb * 16384, r, dp);
       fence_async_smem();
