@@ -15,69 +15,93 @@ constexpr int kMaxCols = 96;        // K + 2 columns at most; 3 per lane
 constexpr int kRowsPerCta = 8;      // one warp per row
 
 constexpr int kBatch = 4;           // rows a warp has in flight
+constexpr int kFwdRowsPerCta = 512; // rows one CTA walks: amortises staging the bias table of its batch
 
+// The prior bias of one batch (N x h_q fp32) is staged once per CTA in shared memory, transposed to
+// [h_q][N+1] so that the K gathers of a row (ascending chunk ids, one head) fall into different banks;
+// gathering it from global memory costs one 32-byte sector per element.
 template <typename T>
 __global__ void __launch_bounds__(32 * kRowsPerCta)
 chunk_weights_fwd_kernel(const T* __restrict__ scores, const int32_t* __restrict__ indices,
                          const float* __restrict__ bias, const T* __restrict__ lse_swa, T* __restrict__ weights,
-                         uint32_t rows, int L, int N, int h_q, int h_idx, int K, int softmax1) {
-  const int lane = threadIdx.x & 31;
-  const uint32_t r0 = (blockIdx.x * kRowsPerCta + (threadIdx.x >> 5)) * kBatch;
-  if (r0 >= rows) return;
+                         uint32_t rows, int L, int N, int h_q, int h_idx, int K, int softmax1, int bias_in_smem,
+                         int rows_per_cta) {
+  extern __shared__ float bias_s[];                         // [h_q][N + 1] when bias_in_smem
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t cta_row0 = blockIdx.x * (uint32_t)rows_per_cta;
+  const uint32_t cta_row1 = min(rows, cta_row0 + (uint32_t)rows_per_cta);
+  const uint32_t rows_per_batch = (uint32_t)L * (uint32_t)h_q;
+  const uint32_t b0 = cta_row0 / rows_per_batch;
+  if (bias && bias_in_smem) {
+    const float* src = bias + (int64_t)b0 * N * h_q;
+    for (int i = threadIdx.x; i < N * h_q; i += 32 * kRowsPerCta) {
+      const int c = i / h_q, hq = i - c * h_q;
+      bias_s[hq * (N + 1) + c] = src[i];
+    }
+    __syncthreads();
+  }
   const int g = h_q / h_idx;
   const int ncol = K + 1 + (softmax1 ? 1 : 0);
-  float x[kBatch][3];
-  int id[kBatch][3];
-  // all loads of the batch first, then the arithmetic
-#pragma unroll
-  for (int j = 0; j < kBatch; ++j) {
-    const uint32_t r = min(r0 + j, rows - 1);
-    const uint32_t bl = r / (uint32_t)h_q, hq = r - bl * (uint32_t)h_q;
-    const int32_t* idx = indices + ((int64_t)bl * h_idx + hq / g) * K;
-#pragma unroll
-    for (int i = 0; i < 3; ++i) {
-      const int c = lane + 32 * i;
-      float v = -CUDART_INF_F;
-      id[j][i] = 0;
-      if (c < K) {
-        v = to_f(scores[(int64_t)r * K + c]);
-        if (bias) id[j][i] = max(idx[c], 0);
-      } else if (c == K) {
-        v = to_f(lse_swa[r]);
-      } else if (c < ncol) {
-        v = 0.f;
-      }
-      x[j][i] = v;
-    }
-  }
-  if (bias) {
+  const int ni = (ncol + 31) >> 5;                          // 32-column groups in use (1..3)
+  for (uint32_t r0 = cta_row0 + warp * kBatch; r0 < cta_row1; r0 += kRowsPerCta * kBatch) {
+    float x[kBatch][3];
+    int id[kBatch][3];
+    uint32_t hq_of[kBatch], b_of[kBatch];
+    // all loads of the batch first, then the arithmetic
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
       const uint32_t r = min(r0 + j, rows - 1);
       const uint32_t bl = r / (uint32_t)h_q, hq = r - bl * (uint32_t)h_q;
-      const int64_t b = bl / (uint32_t)L;
+      hq_of[j] = hq;
+      b_of[j] = bl / (uint32_t)L;
+      const int32_t* idx = indices + ((int64_t)bl * h_idx + hq / g) * K;
 #pragma unroll
-      for (int i = 0; i < 3; ++i)
-        if (lane + 32 * i < K)
-          x[j][i] = to_f(from_f<T>(x[j][i] + to_f(from_f<T>(bias[(b * N + id[j][i]) * h_q + hq]))));
+      for (int i = 0; i < 3; ++i) {
+        x[j][i] = -CUDART_INF_F;
+        id[j][i] = 0;
+        if (i < ni) {
+          const int c = lane + 32 * i;
+          if (c < K) {
+            x[j][i] = to_f(scores[(int64_t)r * K + c]);
+            if (bias) id[j][i] = max(idx[c], 0);
+          } else if (c == K) {
+            x[j][i] = to_f(lse_swa[r]);
+          } else if (c < ncol) {
+            x[j][i] = 0.f;
+          }
+        }
+      }
     }
-  }
+    if (bias) {
 #pragma unroll
-  for (int j = 0; j < kBatch; ++j) {
-    if (r0 + j >= rows) break;                            // warp-uniform
-    const float m = warp_max(fmaxf(fmaxf(x[j][0], x[j][1]), x[j][2]));
-    float e[3], sum = 0.f;
+      for (int j = 0; j < kBatch; ++j) {
+        const bool staged = bias_in_smem && b_of[j] == b0;      // a CTA may straddle two batches
 #pragma unroll
-    for (int i = 0; i < 3; ++i) {
-      e[i] = (lane + 32 * i < ncol && m > -CUDART_INF_F) ? expf(x[j][i] - m) : 0.f;
-      sum += e[i];
+        for (int i = 0; i < 3; ++i)
+          if (i < ni && lane + 32 * i < K) {
+            const float bv = staged ? bias_s[hq_of[j] * (N + 1) + id[j][i]]
+                                    : bias[((int64_t)b_of[j] * N + id[j][i]) * h_q + hq_of[j]];
+            x[j][i] = to_f(from_f<T>(x[j][i] + to_f(from_f<T>(bv))));
+          }
+      }
     }
-    sum = warp_sum(sum);
-    const float inv = 1.f / sum;                           // all -inf: 0/0 = NaN, as the reference's softmax
 #pragma unroll
-    for (int i = 0; i < 3; ++i) {
-      const int c = lane + 32 * i;
-      if (c < ncol) weights[(int64_t)(r0 + j) * ncol + c] = from_f<T>(e[i] * inv);
+    for (int j = 0; j < kBatch; ++j) {
+      if (r0 + j >= cta_row1) break;                        // warp-uniform
+      const float m = warp_max(fmaxf(fmaxf(x[j][0], x[j][1]), x[j][2]));
+      float e[3], sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        e[i] = (i < ni && lane + 32 * i < ncol && m > -CUDART_INF_F) ? __expf(x[j][i] - m) : 0.f;
+        sum += e[i];
+      }
+      sum = warp_sum(sum);
+      const float inv = 1.f / sum;                           // all -inf: 0/0 = NaN, as the reference's softmax
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int c = lane + 32 * i;
+        if (i < ni && c < ncol) weights[(int64_t)(r0 + j) * ncol + c] = from_f<T>(e[i] * inv);
+      }
     }
   }
 }
@@ -237,15 +261,24 @@ extern "C" int hils_chunk_weights_fwd(const void* scores, const int32_t* indices
   HILS_REQUIRE(scores && indices && lse_swa && weights, "chunk_weights_fwd: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   HILS_REQUIRE(rows < (int64_t)1 << 31, "chunk_weights_fwd: more than 2^31 rows");
-  const unsigned grid = (unsigned)((rows + kRowsPerCta * kBatch - 1) / (kRowsPerCta * kBatch));
-  if (dtype == HILS_BF16)
-    chunk_weights_fwd_kernel<bf16><<<grid, 32 * kRowsPerCta, 0, st>>>(
+  const size_t table = (size_t)h_q * (N + 1) * sizeof(float);
+  const int in_smem = bias && table <= 96 * 1024 && rows >= 4 * (int64_t)kFwdRowsPerCta;
+  const int rpc = in_smem ? kFwdRowsPerCta : kRowsPerCta * kBatch;
+  const unsigned grid = (unsigned)((rows + rpc - 1) / rpc);
+  const size_t smem = in_smem ? table : 0;
+  if (dtype == HILS_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(chunk_weights_fwd_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    chunk_weights_fwd_kernel<bf16><<<grid, 32 * kRowsPerCta, smem, st>>>(
         (const bf16*)scores, indices, bias, (const bf16*)lse_swa, (bf16*)weights, (uint32_t)rows, L, N, h_q, h_idx, K,
-        softmax1);
-  else
-    chunk_weights_fwd_kernel<float><<<grid, 32 * kRowsPerCta, 0, st>>>(
-        (const float*)scores, indices, bias, (const float*)lse_swa, (float*)weights, (uint32_t)rows, L, N, h_q, h_idx,
-        K, softmax1);
+        softmax1, in_smem, rpc);
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(chunk_weights_fwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    chunk_weights_fwd_kernel<float><<<grid, 32 * kRowsPerCta, smem, st>>>(
+        (const float*)scores, indices, bias, (const float*)lse_swa, (float*)weights, (uint32_t)rows, L, N, h_q, h_idx, K,
+        softmax1, in_smem, rpc);
+  }
   HILS_LAUNCH_CHECK("chunk_weights_fwd");
   return HILS_OK;
 }
