@@ -32,3 +32,39 @@ def test_ops_refuse_cpu_tensors():
     x = torch.zeros(1, 4, 1, 8)
     with pytest.raises(RuntimeError):
         hb.flex_attn_tl(x, x, x, 2, 2)
+
+
+def _prototypes():
+    """name -> (return type, [parameter types]) parsed from the header."""
+    text = open(os.path.join(ROOT, "include", "hils_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    out = {}
+    for m in re.finditer(r"\b(int|size_t|const char\*)\s+(hils_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", text, flags=re.S):
+        ret, name, params = m.group(1), m.group(2), m.group(3).strip()
+        plist = [] if params in ("", "void") else [" ".join(x.split()) for x in params.split(",")]
+        out[name] = (ret, plist)
+    return out
+
+
+def _kind(ctype_decl):
+    """C parameter declaration -> the ctypes class the binding table must use."""
+    d = ctype_decl
+    if "*" in d:
+        return ctypes.c_void_p
+    base = d.rsplit(" ", 1)[0].replace("const ", "").strip()
+    return {"int": ctypes.c_int, "float": ctypes.c_float, "size_t": ctypes.c_size_t, "int64_t": ctypes.c_int64}[base]
+
+
+def test_binding_table_matches_header_prototypes():
+    """Every ctypes signature has the header's arity, parameter kinds and return type: a wrong count
+    or a float passed where the C side reads an int would corrupt the call silently."""
+    from hils_attention_b200 import _lib
+    protos = _prototypes()
+    assert set(protos) == set(_lib.SIGNATURES)
+    for name, (ret, params) in protos.items():
+        restype, argtypes = _lib.SIGNATURES[name]
+        want_ret = {"int": ctypes.c_int, "size_t": ctypes.c_size_t, "const char*": ctypes.c_char_p}[ret]
+        assert restype is want_ret, f"{name}: return type {restype} vs header {ret}"
+        assert len(argtypes) == len(params), f"{name}: {len(argtypes)} bound arguments vs {len(params)} in the header"
+        for i, (a, d) in enumerate(zip(argtypes, params)):
+            assert a is _kind(d), f"{name}: argument {i} ({d}) bound as {a}"
