@@ -65,4 +65,78 @@ __device__ __forceinline__ void dot32_mma(const uint32_t (&af)[NK][4], const bf1
   }
 }
 
+// out[g * ostride + j] = <q_g, K_j> for j < n <= 64
+template <int NK>
+__device__ __forceinline__ void score_rows_mma(const uint32_t (&af)[NK][4], const bf16* kbase, int64_t rs, int n, int G,
+                                               float* out, int ostride, int lane) {
+  const int kr = lane >> 2, j = lane & 3;
+#pragma unroll
+  for (int k0 = 0; k0 < 64; k0 += 32) {       // unrolled: the loads of the second group may start before the first's math
+    if (k0 >= n) break;
+    float c[4][4];
+    dot32_mma<NK>(af, kbase + (int64_t)k0 * rs, rs, n - k0, lane, c);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int key0 = k0 + u * 8 + 2 * j;
+      if (kr < G) {
+        if (key0 < n) out[kr * ostride + key0] = c[u][0];
+        if (key0 + 1 < n) out[kr * ostride + key0 + 1] = c[u][1];
+      }
+      if (kr + 8 < G) {
+        if (key0 < n) out[(kr + 8) * ostride + key0] = c[u][2];
+        if (key0 + 1 < n) out[(kr + 8) * ostride + key0 + 1] = c[u][3];
+      }
+    }
+  }
+}
+
+// acc[g][0..7] += sum_j p[g * pstride + j] * V_j[sub*8 .. sub*8+7] over the rows this lane's group visits
+template <int NK, int GM>
+__device__ __forceinline__ void pv_rows16(const float* p_s, int pstride, const bf16* vbase, int64_t rs, int n, int G,
+                                          float (&acc)[GM][8], int lane) {
+  constexpr int LPR = 2 * NK, RPI = 32 / LPR;          // lanes per row, rows per load instruction
+  const int sub = lane % LPR, rg = lane / LPR;
+  for (int j0 = 0; j0 < n; j0 += RPI * 8) {
+    uint4 vv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int jr = min(j0 + u * RPI + rg, n - 1);
+      vv[u] = *reinterpret_cast<const uint4*>(vbase + (int64_t)jr * rs + sub * 8);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int jr = j0 + u * RPI + rg;
+      if (jr < n) {
+        const uint32_t w4[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          f[2 * e] = __uint_as_float(w4[e] << 16);
+          f[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
+        }
+#pragma unroll
+        for (int g = 0; g < GM; ++g) {
+          if (g < G) {
+            const float pj = p_s[g * pstride + jr];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pj, f[e], acc[g][e]);
+          }
+        }
+      }
+    }
+  }
+}
+
+// sum over the row groups of a warp; afterwards lanes < D/8 hold the totals of columns lane*8 .. lane*8+7
+template <int NK, int GM>
+__device__ __forceinline__ void pv_reduce(float (&acc)[GM][8]) {
+  constexpr int LPR = 2 * NK;
+#pragma unroll
+  for (int off = LPR; off < 32; off <<= 1)
+#pragma unroll
+    for (int g = 0; g < GM; ++g)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], off);
+}
+
 }  // namespace hils

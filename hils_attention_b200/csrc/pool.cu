@@ -8,6 +8,7 @@
 //   dP_j = <g_k', K_j>; delta = sum p_j dP_j; dl_j = p_j[(dP_j - delta) - g_b'(ln p_j + b')]
 //   dmu = scale sum_j dl_j K_j;  dK_j = scale dl_j mu + p_j g_k'
 #include "common.cuh"
+#include "mma_rows.cuh"
 
 namespace hils {
 
@@ -197,6 +198,177 @@ __global__ void meanpool_bwd_kernel(const T* __restrict__ g_out, T* __restrict__
   store4(d_k + bns * HD + c * 4, make_float4(g.x * inv, g.y * inv, g.z * inv, g.w * inv));
 }
 
+// =================================================================================================
+// bf16 fast path (S <= 64, D = 64 or 128, G <= 8): one WARP per (chunk, kv-head).  Scores come from
+// mma.sync with the B fragments loaded straight from the chunk's key rows (mma_rows.cuh), the weighted
+// key sums run on the CUDA cores with 16-byte row loads.  Nothing is staged in shared memory beyond the
+// 64 logits of the chunk, no block-wide barrier is needed, and a CTA of eight warps keeps eight 8-16 KB
+// tiles in flight - the generic kernel above holds one tile per CTA and synchronises ~8 times per head.
+// =================================================================================================
+constexpr int kPoolWarps = 8;
+
+// logits in pw[g*64 + j] (raw dots) -> probabilities in place; returns the entropy b' (all lanes)
+__device__ __forceinline__ float pool_softmax_row(float* pw, int S, float scale, int lane, float* m_out, float* logsum_out) {
+  const int j0 = lane, j1 = lane + 32;
+  const float l0 = (j0 < S - 1) ? pw[j0] * scale : -CUDART_INF_F;
+  const float l1 = (j1 < S - 1) ? pw[j1] * scale : -CUDART_INF_F;
+  const float m = warp_max(fmaxf(l0, l1));
+  float e0 = 0.f, e1 = 0.f;
+  if (m > -CUDART_INF_F) { e0 = __expf(l0 - m); e1 = __expf(l1 - m); }
+  const float sum = warp_sum(e0 + e1);
+  const float log_sum = (sum > 0.f) ? __logf(sum) : 0.f;
+  const float p0 = (sum > 0.f) ? e0 / sum : 0.f, p1 = (sum > 0.f) ? e1 / sum : 0.f;
+  float ent = 0.f;
+  if (p0 > 0.f) ent -= p0 * ((l0 - m) - log_sum);
+  if (p1 > 0.f) ent -= p1 * ((l1 - m) - log_sum);
+  ent = warp_sum(ent);
+  pw[j0] = p0;
+  pw[j1] = p1;
+  *m_out = m;
+  *logsum_out = log_sum;
+  return ent;
+}
+
+template <int NK, int GM>
+__global__ void __launch_bounds__(32 * kPoolWarps) pool_fwd_bf16_kernel(
+    const bf16* __restrict__ mu_q, const bf16* __restrict__ k, bf16* __restrict__ lmk_k, float* __restrict__ lmk_b,
+    int N, int S, int h_q, int h_kv, int64_t k_batch_stride, float scale, int compact) {
+  constexpr int D = NK * 16, LPR = 2 * NK;
+  extern __shared__ __align__(16) float smem[];
+  const int G = h_q / h_kv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* q_s = smem + warp * (G * D + G * 64);           // [G][D] landmark queries
+  float* pw = q_s + G * D;                               // [G][64] logits -> probabilities
+  const int n = blockIdx.x * kPoolWarps + warp, h = blockIdx.y, b = blockIdx.z;
+  if (n >= N) return;
+  const int64_t orow0 = ((int64_t)b * N + n) * h_q + h * G;
+  for (int i = lane; i < G * D; i += 32) q_s[i] = to_f(mu_q[orow0 * D + i]);
+  __syncwarp();
+  uint32_t af[NK][4];
+  make_q_frags<NK>(q_s, lane, af, [G](int r) { return r < G ? r : -1; });
+  const bf16* kbase = k + (int64_t)b * k_batch_stride + ((int64_t)n * S * h_kv + h) * D;
+  const int64_t rs = (int64_t)h_kv * D;
+  score_rows_mma<NK>(af, kbase, rs, S, G, pw, 64, lane);
+  __syncwarp();
+  for (int g = 0; g < G; ++g) {
+    float m, ls;
+    const float ent = pool_softmax_row(pw + g * 64, S, scale, lane, &m, &ls);
+    if (lane == 0) lmk_b[orow0 + g] = ent;
+  }
+  __syncwarp();
+  float acc[GM][8];
+#pragma unroll
+  for (int g = 0; g < GM; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+  if (!compact) {
+    pv_rows16<NK, GM>(pw, 64, kbase, rs, S, G, acc, lane);
+    pv_reduce<NK, GM>(acc);
+  }
+  if (lane < LPR)
+#pragma unroll
+    for (int g = 0; g < GM; ++g)
+      if (g < G) {
+        uint4 o;
+        o.x = pack_bf16(acc[g][0], acc[g][1]); o.y = pack_bf16(acc[g][2], acc[g][3]);
+        o.z = pack_bf16(acc[g][4], acc[g][5]); o.w = pack_bf16(acc[g][6], acc[g][7]);
+        *reinterpret_cast<uint4*>(lmk_k + (orow0 + g) * D + lane * 8) = o;
+      }
+}
+
+// backward: fragment rows 0..G-1 = landmark queries, rows G..2G-1 = g_k' (so one pass over the tile gives
+// both the logits and dP); then dmu = scale * sum_j dl_j K_j (row loads) and the dK tile, written once.
+template <int NK, int GM>
+__global__ void __launch_bounds__(32 * kPoolWarps) pool_bwd_bf16_kernel(
+    const bf16* __restrict__ mu_q, const bf16* __restrict__ k, const bf16* __restrict__ g_lmk_k,
+    const float* __restrict__ g_lmk_b, bf16* __restrict__ d_mu_q, bf16* __restrict__ d_k, int N, int S, int h_q,
+    int h_kv, int64_t k_batch_stride, float scale, int compact) {
+  constexpr int D = NK * 16, LPR = 2 * NK, RPI = 32 / LPR;
+  extern __shared__ __align__(16) float smem[];
+  const int G = h_q / h_kv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* q_s = smem + warp * (2 * G * D + 2 * G * 64);   // [2G][D]: mu rows, then g_k' rows
+  float* pw = q_s + 2 * G * D;                           // [2G][64]: logits -> p, dP -> dl
+  const int n = blockIdx.x * kPoolWarps + warp, h = blockIdx.y, b = blockIdx.z;
+  if (n >= N) return;
+  const int64_t orow0 = ((int64_t)b * N + n) * h_q + h * G;
+  const bool has_gk = g_lmk_k != nullptr && !compact;
+  for (int i = lane; i < G * D; i += 32) {
+    q_s[i] = to_f(mu_q[orow0 * D + i]);
+    q_s[G * D + i] = has_gk ? to_f(g_lmk_k[orow0 * D + i]) : 0.f;
+  }
+  __syncwarp();
+  uint32_t af[NK][4];
+  make_q_frags<NK>(q_s, lane, af, [G](int r) { return r < 2 * G ? r : -1; });
+  const bf16* kbase = k + (int64_t)b * k_batch_stride + ((int64_t)n * S * h_kv + h) * D;
+  bf16* dkbase = d_k + (int64_t)b * k_batch_stride + ((int64_t)n * S * h_kv + h) * D;
+  const int64_t rs = (int64_t)h_kv * D;
+  score_rows_mma<NK>(af, kbase, rs, S, 2 * G, pw, 64, lane);
+  __syncwarp();
+  for (int g = 0; g < G; ++g) {
+    float* pg = pw + g * 64;
+    float* dg = pw + (G + g) * 64;
+    const int j0 = lane, j1 = lane + 32;
+    const float l0 = (j0 < S - 1) ? pg[j0] * scale : -CUDART_INF_F;
+    const float l1 = (j1 < S - 1) ? pg[j1] * scale : -CUDART_INF_F;
+    float m, log_sum;
+    const float ent = pool_softmax_row(pg, S, scale, lane, &m, &log_sum);
+    const float p0 = pg[j0], p1 = pg[j1];
+    const float dp0 = (j0 < S) ? dg[j0] : 0.f, dp1 = (j1 < S) ? dg[j1] : 0.f;
+    const float delta = warp_sum(p0 * dp0 + p1 * dp1);
+    const float gb = g_lmk_b ? g_lmk_b[orow0 + g] : 0.f;
+    // ln p_j = (l_j - m) - log_sum
+    dg[j0] = (p0 > 0.f) ? p0 * ((dp0 - delta) - gb * (((l0 - m) - log_sum) + ent)) : 0.f;
+    dg[j1] = (p1 > 0.f) ? p1 * ((dp1 - delta) - gb * (((l1 - m) - log_sum) + ent)) : 0.f;
+  }
+  __syncwarp();
+  // dmu_g = scale * sum_j dl_{g,j} K_j
+  {
+    float acc[GM][8];
+#pragma unroll
+    for (int g = 0; g < GM; ++g)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+    pv_rows16<NK, GM>(pw + G * 64, 64, kbase, rs, S, G, acc, lane);
+    pv_reduce<NK, GM>(acc);
+    if (lane < LPR)
+#pragma unroll
+      for (int g = 0; g < GM; ++g)
+        if (g < G) {
+          uint4 o;
+          o.x = pack_bf16(acc[g][0] * scale, acc[g][1] * scale); o.y = pack_bf16(acc[g][2] * scale, acc[g][3] * scale);
+          o.z = pack_bf16(acc[g][4] * scale, acc[g][5] * scale); o.w = pack_bf16(acc[g][6] * scale, acc[g][7] * scale);
+          *reinterpret_cast<uint4*>(d_mu_q + (orow0 + g) * D + lane * 8) = o;
+        }
+  }
+  // dK_j = sum_g (scale * dl_{g,j} mu_g + p_{g,j} g_k'_g): D/8 lanes per key row, 32/(D/8) rows per step
+  const int sub = lane % LPR, rg = lane / LPR;
+  for (int j0 = 0; j0 < S; j0 += RPI) {
+    const int j = j0 + rg;
+    if (j < S) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = 0.f;
+      for (int g = 0; g < G; ++g) {
+        const float a = scale * pw[(G + g) * 64 + j], pj = pw[g * 64 + j];
+        const float* mu = q_s + g * D + sub * 8;
+        const float* gk = q_s + (G + g) * D + sub * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = fmaf(a, mu[e], fmaf(pj, gk[e], o[e]));
+      }
+      uint4 w4;
+      w4.x = pack_bf16(o[0], o[1]); w4.y = pack_bf16(o[2], o[3]); w4.z = pack_bf16(o[4], o[5]); w4.w = pack_bf16(o[6], o[7]);
+      *reinterpret_cast<uint4*>(dkbase + (int64_t)j * rs + sub * 8) = w4;
+    }
+  }
+}
+
+static bool pool_bf16_ok(const void* mu_q, const void* k, int S, int h_q, int h_kv, int D, int64_t k_batch_stride) {
+  const int G = h_q / h_kv;
+  return S >= 2 && S <= 64 && (D == 64 || D == 128) && G <= 8 && (k_batch_stride % 8) == 0 &&
+         ((((uintptr_t)mu_q) | ((uintptr_t)k)) & 15) == 0;
+}
+
 static int check_pool_args(int B, int N, int S, int h_q, int h_kv, int D, int dtype) {
   HILS_REQUIRE(B > 0 && N >= 0 && S > 0 && h_q > 0 && h_kv > 0 && D > 0, "pool: non-positive size");
   HILS_REQUIRE(h_q % h_kv == 0, "pool: h_q (%d) must be a multiple of h_kv (%d)", h_q, h_kv);
@@ -215,10 +387,26 @@ extern "C" int hils_pool_fwd(const void* mu_q, const void* k, void* lmk_k, float
   if (int rc = check_pool_args(B, N, S, h_q, h_kv, D, dtype)) return rc;
   if (N == 0) return HILS_OK;
   HILS_REQUIRE(mu_q && k && lmk_k && lmk_b, "pool_fwd: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == HILS_BF16 && pool_bf16_ok(mu_q, k, S, h_q, h_kv, D, k_batch_stride) && (((uintptr_t)lmk_k) & 15) == 0) {
+    const int G = h_q / h_kv;
+    const size_t sm = (size_t)kPoolWarps * (G * D + G * 64) * sizeof(float);
+    dim3 grid((N + kPoolWarps - 1) / kPoolWarps, h_kv, B);
+#define HILS_POOL_FWD(NK, GM)                                                                                     \
+    do {                                                                                                          \
+      cudaFuncSetAttribute(pool_fwd_bf16_kernel<NK, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);   \
+      pool_fwd_bf16_kernel<NK, GM><<<grid, 32 * kPoolWarps, sm, st>>>((const bf16*)mu_q, (const bf16*)k, (bf16*)lmk_k, \
+                                                                      lmk_b, N, S, h_q, h_kv, k_batch_stride, sm_scale, compact); \
+    } while (0)
+    if (D == 64) { if (G == 1) HILS_POOL_FWD(4, 1); else if (G == 2) HILS_POOL_FWD(4, 2); else if (G <= 4) HILS_POOL_FWD(4, 4); else HILS_POOL_FWD(4, 8); }
+    else { if (G == 1) HILS_POOL_FWD(8, 1); else if (G == 2) HILS_POOL_FWD(8, 2); else if (G <= 4) HILS_POOL_FWD(8, 4); else HILS_POOL_FWD(8, 8); }
+#undef HILS_POOL_FWD
+    HILS_LAUNCH_CHECK("pool_fwd");
+    return HILS_OK;
+  }
   size_t smem = (size_t)(S * D + D + S) * sizeof(float);
   HILS_REQUIRE(smem <= 200 * 1024, "pool_fwd: chunk tile S*D=%d too large for shared memory", S * D);
   dim3 grid(N, h_kv, B);
-  cudaStream_t st = (cudaStream_t)stream;
   if (dtype == HILS_BF16) {
     cudaFuncSetAttribute(pool_fwd_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     pool_fwd_kernel<bf16><<<grid, 128, smem, st>>>((const bf16*)mu_q, (const bf16*)k, (bf16*)lmk_k, lmk_b, N, S,
@@ -238,10 +426,28 @@ extern "C" int hils_pool_bwd(const void* mu_q, const void* k, const void* g_lmk_
   if (int rc = check_pool_args(B, N, S, h_q, h_kv, D, dtype)) return rc;
   if (N == 0) return HILS_OK;
   HILS_REQUIRE(mu_q && k && d_mu_q && d_k, "pool_bwd: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == HILS_BF16 && pool_bf16_ok(mu_q, k, S, h_q, h_kv, D, k_batch_stride) &&
+      ((((uintptr_t)d_mu_q) | ((uintptr_t)d_k) | ((uintptr_t)g_lmk_k)) & 15) == 0) {
+    const int G = h_q / h_kv;
+    const size_t sm = (size_t)kPoolWarps * (2 * G * D + 2 * G * 64) * sizeof(float);
+    dim3 grid((N + kPoolWarps - 1) / kPoolWarps, h_kv, B);
+#define HILS_POOL_BWD(NK, GM)                                                                                     \
+    do {                                                                                                          \
+      cudaFuncSetAttribute(pool_bwd_bf16_kernel<NK, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);   \
+      pool_bwd_bf16_kernel<NK, GM><<<grid, 32 * kPoolWarps, sm, st>>>((const bf16*)mu_q, (const bf16*)k, (const bf16*)g_lmk_k, \
+                                                                      g_lmk_b, (bf16*)d_mu_q, (bf16*)d_k, N, S, h_q, h_kv,     \
+                                                                      k_batch_stride, sm_scale, compact);                      \
+    } while (0)
+    if (D == 64) { if (G == 1) HILS_POOL_BWD(4, 1); else if (G == 2) HILS_POOL_BWD(4, 2); else if (G <= 4) HILS_POOL_BWD(4, 4); else HILS_POOL_BWD(4, 8); }
+    else { if (G == 1) HILS_POOL_BWD(8, 1); else if (G == 2) HILS_POOL_BWD(8, 2); else if (G <= 4) HILS_POOL_BWD(8, 4); else HILS_POOL_BWD(8, 8); }
+#undef HILS_POOL_BWD
+    HILS_LAUNCH_CHECK("pool_bwd");
+    return HILS_OK;
+  }
   size_t smem = (size_t)(2 * S * D + 2 * D + 2 * S) * sizeof(float);
   HILS_REQUIRE(smem <= 200 * 1024, "pool_bwd: chunk tile S*D=%d too large for shared memory", S * D);
   dim3 grid(N, h_kv, B);
-  cudaStream_t st = (cudaStream_t)stream;
   if (dtype == HILS_BF16) {
     cudaFuncSetAttribute(pool_bwd_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     pool_bwd_kernel<bf16><<<grid, 128, smem, st>>>((const bf16*)mu_q, (const bf16*)k, (const bf16*)g_lmk_k,
