@@ -106,6 +106,99 @@ chunk_weights_fwd_kernel(const T* __restrict__ scores, const int32_t* __restrict
   }
 }
 
+// Same computation for K <= 32, K % 4 == 0 (the common top-k sizes): eight lanes per row, four columns per
+// lane with vector loads, so one warp instruction serves four rows; reductions take three shuffles.
+template <typename T>
+__global__ void __launch_bounds__(32 * kRowsPerCta)
+chunk_weights_fwd8_kernel(const T* __restrict__ scores, const int32_t* __restrict__ indices,
+                          const float* __restrict__ bias, const T* __restrict__ lse_swa, T* __restrict__ weights,
+                          uint32_t rows, int L, int N, int h_q, int h_idx, int K, int softmax1, int bias_in_smem,
+                          int rows_per_cta) {
+  extern __shared__ float bias_s[];                         // [h_q][N + 1] when bias_in_smem
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 7, rq = lane >> 3;
+  const uint32_t cta_row0 = blockIdx.x * (uint32_t)rows_per_cta;
+  const uint32_t cta_row1 = min(rows, cta_row0 + (uint32_t)rows_per_cta);
+  const uint32_t rows_per_batch = (uint32_t)L * (uint32_t)h_q;
+  const uint32_t b0 = cta_row0 / rows_per_batch;
+  if (bias && bias_in_smem) {
+    const float* src = bias + (int64_t)b0 * N * h_q;
+    for (int i = threadIdx.x; i < N * h_q; i += 32 * kRowsPerCta) {
+      const int c = i / h_q, hq = i - c * h_q;
+      bias_s[hq * (N + 1) + c] = src[i];
+    }
+    __syncthreads();
+  }
+  const int g = h_q / h_idx;
+  const int ncol = K + 1 + (softmax1 ? 1 : 0);
+  const bool has_cols = 4 * sub < K;
+  for (uint32_t r0 = cta_row0 + warp * 8; r0 < cta_row1; r0 += kRowsPerCta * 8) {   // two row groups in flight
+    float4 sc[2];
+    int4 id[2];
+    float ls[2];
+    uint32_t hq_of[2], b_of[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t r = min(r0 + 4 * j + rq, rows - 1);
+      const uint32_t bl = r / (uint32_t)h_q, hq = r - bl * (uint32_t)h_q;
+      hq_of[j] = hq;
+      b_of[j] = bl / (uint32_t)L;
+      sc[j] = make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+      id[j] = make_int4(0, 0, 0, 0);
+      if (has_cols) {
+        sc[j] = load4(scores + (int64_t)r * K + 4 * sub);
+        if (bias) id[j] = *reinterpret_cast<const int4*>(indices + ((int64_t)bl * h_idx + hq / g) * K + 4 * sub);
+      }
+      ls[j] = to_f(lse_swa[r]);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t r = r0 + 4 * j + rq;
+      float x[4] = {sc[j].x, sc[j].y, sc[j].z, sc[j].w};
+      if (bias && has_cols) {
+        const int ids[4] = {max(id[j].x, 0), max(id[j].y, 0), max(id[j].z, 0), max(id[j].w, 0)};
+        const bool staged = bias_in_smem && b_of[j] == b0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float bv = staged ? bias_s[hq_of[j] * (N + 1) + ids[e]]
+                                  : bias[((int64_t)b_of[j] * N + ids[e]) * h_q + hq_of[j]];
+          x[e] = to_f(from_f<T>(x[e] + to_f(from_f<T>(bv))));
+        }
+      }
+      float m = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+      m = fmaxf(m, ls[j]);
+      if (softmax1) m = fmaxf(m, 0.f);
+      float e4[4], sum = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        e4[e] = (m > -CUDART_INF_F) ? __expf(x[e] - m) : 0.f;
+        sum += e4[e];
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      const float e_l = (m > -CUDART_INF_F) ? __expf(ls[j] - m) : 0.f;
+      const float e_z = (softmax1 && m > -CUDART_INF_F) ? __expf(-m) : 0.f;
+      sum += e_l + e_z;
+      const float inv = 1.f / sum;                           // all -inf: 0/0 = NaN, as the reference's softmax
+      if (r < cta_row1) {
+        T* wrow = weights + (int64_t)r * ncol;
+        if (has_cols) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) wrow[4 * sub + e] = from_f<T>(e4[e] * inv);
+        }
+        if (sub == 0) {
+          wrow[K] = from_f<T>(e_l * inv);
+          if (softmax1) wrow[K + 1] = from_f<T>(e_z * inv);
+        }
+      }
+    }
+  }
+}
+
 // d_x = w * (d_w - sum(w * d_w)), rounded to T; columns [0,K) -> d_scores and (scattered) d_bias,
 // column K -> d_lse.  A CTA owns kTokPerCta tokens of one (batch, query head): the bias gradient is
 // accumulated per chunk id in shared memory and leaves the CTA as one atomic per touched chunk.
@@ -164,6 +257,85 @@ chunk_weights_bwd_kernel(const T* __restrict__ weights, const T* __restrict__ d_
         } else if (c == K) {
           d_lse[r] = dx;
         }
+      }
+    }
+  }
+  if (bias_in_smem) {
+    __syncthreads();
+    for (int c = threadIdx.x; c < N; c += 32 * kRowsPerCta) {
+      const float x = acc_s[c];
+      if (x != 0.f) atomicAdd(d_bias + (b * N + c) * h_q + hq, x);
+    }
+  }
+}
+
+// Backward for K <= 32, K % 4 == 0: eight lanes per row, four columns per lane (see the forward variant).
+template <typename T>
+__global__ void __launch_bounds__(32 * kRowsPerCta)
+chunk_weights_bwd8_kernel(const T* __restrict__ weights, const T* __restrict__ d_weights,
+                          const int32_t* __restrict__ indices, T* __restrict__ d_scores, T* __restrict__ d_lse,
+                          float* __restrict__ d_bias, int L, int N, int h_q, int h_idx, int K, int softmax1,
+                          int bias_in_smem) {
+  extern __shared__ float acc_s[];                          // [N] when bias_in_smem
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 7, rq = lane >> 3;
+  const int hq = blockIdx.y;
+  const int64_t b = blockIdx.z;
+  const int l0 = blockIdx.x * kTokPerCta, l1 = min(l0 + kTokPerCta, L);
+  const int g = h_q / h_idx;
+  const int ncol = K + 1 + (softmax1 ? 1 : 0);
+  const bool has_cols = 4 * sub < K;
+  if (bias_in_smem) {
+    for (int c = threadIdx.x; c < N; c += 32 * kRowsPerCta) acc_s[c] = 0.f;
+    __syncthreads();
+  }
+  for (int lb = l0 + warp * 8; lb < l1; lb += kRowsPerCta * 8) {       // two groups of four tokens in flight
+    float w[2][4], dw[2][4], wx[2][2], dwx[2][2];
+    int4 id[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {                            // all loads first
+      const int l = min(lb + 4 * j + rq, l1 - 1);
+      const int64_t bl = b * L + l, r = bl * h_q + hq;
+      const T* wr = weights + r * ncol;
+      const T* dr = d_weights + r * ncol;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        w[j][e] = has_cols ? to_f(wr[4 * sub + e]) : 0.f;
+        dw[j][e] = has_cols ? to_f(dr[4 * sub + e]) : 0.f;
+      }
+      // the window column (and the zero column) are handled by the first lane of the group
+      wx[j][0] = (sub == 0) ? to_f(wr[K]) : 0.f;
+      dwx[j][0] = (sub == 0) ? to_f(dr[K]) : 0.f;
+      wx[j][1] = (sub == 0 && softmax1) ? to_f(wr[K + 1]) : 0.f;
+      dwx[j][1] = (sub == 0 && softmax1) ? to_f(dr[K + 1]) : 0.f;
+      id[j] = make_int4(-1, -1, -1, -1);
+      if (d_bias && has_cols) id[j] = *reinterpret_cast<const int4*>(indices + (bl * h_idx + hq / g) * K + 4 * sub);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int l = lb + 4 * j + rq;
+      float dot = fmaf(wx[j][0], dwx[j][0], wx[j][1] * dwx[j][1]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dot = fmaf(w[j][e], dw[j][e], dot);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+      if (l < l1) {
+        const int64_t r = (b * L + l) * h_q + hq;
+        if (has_cols) {
+          const int ids[4] = {id[j].x, id[j].y, id[j].z, id[j].w};
+          float dx[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            dx[e] = to_f(from_f<T>(w[j][e] * (dw[j][e] - dot)));
+            if (ids[e] >= 0) {
+              if (bias_in_smem) atomicAdd(acc_s + ids[e], dx[e]);
+              else atomicAdd(d_bias + (b * N + ids[e]) * h_q + hq, dx[e]);
+            }
+          }
+          store4(d_scores + r * K + 4 * sub, make_float4(dx[0], dx[1], dx[2], dx[3]));
+        }
+        if (sub == 0) d_lse[r] = from_f<T>(wx[j][0] * (dwx[j][0] - dot));
       }
     }
   }
@@ -266,6 +438,26 @@ extern "C" int hils_chunk_weights_fwd(const void* scores, const int32_t* indices
   const int rpc = in_smem ? kFwdRowsPerCta : kRowsPerCta * kBatch;
   const unsigned grid = (unsigned)((rows + rpc - 1) / rpc);
   const size_t smem = in_smem ? table : 0;
+  if (K <= 32 && K % 4 == 0 && ((((uintptr_t)scores) | ((uintptr_t)indices)) & 15) == 0) {
+    // eight lanes per row
+    const int rpc8 = in_smem ? kFwdRowsPerCta : kRowsPerCta * 8;
+    const unsigned grid8 = (unsigned)((rows + rpc8 - 1) / rpc8);
+    if (dtype == HILS_BF16) {
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(chunk_weights_fwd8_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      chunk_weights_fwd8_kernel<bf16><<<grid8, 32 * kRowsPerCta, smem, st>>>(
+          (const bf16*)scores, indices, bias, (const bf16*)lse_swa, (bf16*)weights, (uint32_t)rows, L, N, h_q, h_idx, K,
+          softmax1, in_smem, rpc8);
+    } else {
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(chunk_weights_fwd8_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      chunk_weights_fwd8_kernel<float><<<grid8, 32 * kRowsPerCta, smem, st>>>(
+          (const float*)scores, indices, bias, (const float*)lse_swa, (float*)weights, (uint32_t)rows, L, N, h_q, h_idx, K,
+          softmax1, in_smem, rpc8);
+    }
+    HILS_LAUNCH_CHECK("chunk_weights_fwd");
+    return HILS_OK;
+  }
   if (dtype == HILS_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(chunk_weights_fwd_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -301,6 +493,23 @@ extern "C" int hils_chunk_weights_bwd(const void* weights, const void* d_weights
   const int in_smem = d_bias && (size_t)N * 4 <= 96 * 1024;
   const size_t smem = in_smem ? (size_t)N * 4 : 0;
   dim3 grid((L + kTokPerCta - 1) / kTokPerCta, h_q, B);
+  if (K <= 32 && K % 4 == 0 && ((((uintptr_t)d_scores) | ((uintptr_t)indices)) & 15) == 0) {
+    if (dtype == HILS_BF16) {
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(chunk_weights_bwd8_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      chunk_weights_bwd8_kernel<bf16><<<grid, 32 * kRowsPerCta, smem, st>>>(
+          (const bf16*)weights, (const bf16*)d_weights, indices, (bf16*)d_scores, (bf16*)d_lse, d_bias, L, N, h_q, h_idx,
+          K, softmax1, in_smem);
+    } else {
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(chunk_weights_bwd8_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      chunk_weights_bwd8_kernel<float><<<grid, 32 * kRowsPerCta, smem, st>>>(
+          (const float*)weights, (const float*)d_weights, indices, (float*)d_scores, (float*)d_lse, d_bias, L, N, h_q,
+          h_idx, K, softmax1, in_smem);
+    }
+    HILS_LAUNCH_CHECK("chunk_weights_bwd");
+    return HILS_OK;
+  }
   if (dtype == HILS_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(chunk_weights_bwd_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
