@@ -397,9 +397,9 @@ def main():
     dom = "sparse_attn_bwd" if t_bwd > t_fwd else "sparse_attn_fwd"
     f_dom, t_dom = (f_bwd, t_bwd) if t_bwd > t_fwd else (f_fwd, t_fwd)
     achieved = f_dom / (t_dom / 1e3) / 1e12
-    # DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
-    # profiles/sparse_and_selection_kernels_c2.md (dram__bytes_read.sum + dram__bytes_write.sum; the backward
-    # is the dq pass plus the dkv pass); captured at c2 only
+    # DRAM bytes per launch of the dominant kernel, from an ncu capture of this workload whose summary is kept
+    # under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum; the backward is the dq pass plus the dkv
+    # pass); captured at c2 only
     traffic = {"sparse_attn_bwd": (724 + 301 + 622 + 246) * 1e6, "sparse_attn_fwd": (586 + 123) * 1e6}[dom] \
         if args.workload == "c2" else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
