@@ -413,10 +413,11 @@ __global__ void __launch_bounds__(128) topk_fwd_kernel(TopkParams p) {
 // shared memory (fp32), so the keys are read once and nothing is recomputed: log-sum-exp per row, then
 // per token a warp builds the ranking keys, finds the K-th largest by bisection over the key bits
 // (warp-wide population counts), and compacts the selected ids in ascending order.
-constexpr int kSelTile = 128;     // candidates per key tile; warp w owns candidates 32w..32w+31 of a tile
+constexpr int kSelTile = 128;     // candidates per key tile
+constexpr int kSelWarps = 8;      // warp w owns candidates 16w..16w+15 of a tile, and every 8th row / token
 
 struct SelLayout {
-  int RB, M, Npad, RSV, NS;
+  int RB, M, Npad, RSV, NS, SW;   // SW: warps that run the per-token selection (each needs a key-bit row)
   size_t q_off, k_off, v_off, add_off, lt_off, lim_off, bits_off, total;
 };
 
@@ -431,7 +432,9 @@ static SelLayout sel_layout_for(int G, int D, int N, int RB, int NS) {
   s.q_off = o;    o += (size_t)s.M * (D + 8) * 2;
   // the key tiles are dead once the scores are formed: the per-warp key-bit rows of the selection reuse them
   s.k_off = o;    s.bits_off = o;
-  o += std::max((size_t)NS * kSelTile * (D + 8) * 2, (size_t)4 * s.Npad * (4 + 2));   // bits (u32) + ids (u16) per warp
+  const size_t k_bytes = (size_t)NS * kSelTile * (D + 8) * 2;
+  s.SW = ((size_t)kSelWarps * s.Npad * (4 + 2) <= k_bytes) ? kSelWarps : 4;   // bits (u32) + ids (u16) per selecting warp
+  o += std::max(k_bytes, (size_t)s.SW * s.Npad * (4 + 2));
   s.v_off = o;    o += (size_t)s.M * s.RSV * 4;
   s.add_off = o;  o += (size_t)G * s.Npad * 4;
   s.lt_off = o;   o += (size_t)s.M * 4;
@@ -458,7 +461,10 @@ static SelLayout sel_layout(int G, int D, int N, int cta_tiles_max, int per_qhea
 }
 
 template <int NK>   // NK = D / 16
-__global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayout sl) {
+__global__ void __launch_bounds__(kSelWarps * 32) topk_fwd_mma_kernel(TopkParams p, SelLayout sl) {
+  constexpr int NT = kSelWarps * 32;             // threads
+  constexpr int CW = kSelTile / kSelWarps;       // candidates of a key tile per warp
+  constexpr int NBW = CW / 8;                    // 8-candidate blocks per warp
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int D = NK * 16, RS = D + 8, CPR = D / 8;
   const int G = p.G, RB = sl.RB, M = sl.M, Npad = sl.Npad, RSV = sl.RSV, K = p.topk;
@@ -468,7 +474,7 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
   float* add_s = reinterpret_cast<float*>(smem_raw + sl.add_off);  // [G][Npad] bias + gumbel
   float* lt_s = reinterpret_cast<float*>(smem_raw + sl.lt_off);    // [M] lse of the window branch, then lse_total
   int* lim_s = reinterpret_cast<int*>(smem_raw + sl.lim_off);      // [RB] candidates of each token
-  uint32_t* bits_s = reinterpret_cast<uint32_t*>(smem_raw + sl.bits_off);  // [4 warps][Npad]
+  uint32_t* bits_s = reinterpret_cast<uint32_t*>(smem_raw + sl.bits_off);  // [warps][Npad]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int l0 = blockIdx.x * RB, h = blockIdx.y, b = blockIdx.z;
   const bf16* q = static_cast<const bf16*>(p.q);
@@ -484,7 +490,7 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
     const int pass = it / ntile, c0 = (it - pass * ntile) * kSelTile;
     const bf16* src = lmks + ((int64_t)b * p.N * HL + (p.per_qhead ? h * G + pass : h)) * D;
     bf16* dst = k_s + (size_t)stage * kSelTile * RS;
-    for (int i = tid; i < kSelTile * CPR; i += 128) {
+    for (int i = tid; i < kSelTile * CPR; i += NT) {
       const int row = i / CPR, col = (i - row * CPR) * 8;
       if (c0 + row < p.N)                                  // rows past the last key stay stale: never candidates
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst + row * RS + col)),
@@ -494,15 +500,15 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
   };
   if (total > 0) load_keys(0, 0);
   // queries (member-major rows), per-token limits, lse of the window branch, additive terms
-  for (int i = tid; i < M * CPR; i += 128) {
+  for (int i = tid; i < M * CPR; i += NT) {
     const int row = i / CPR, col = (i - row * CPR) * 8;
     const int g = row / RB, l = l0 + (row - g * RB);
     uint4 x = make_uint4(0u, 0u, 0u, 0u);
     if (l < p.L) x = *reinterpret_cast<const uint4*>(q + ((((int64_t)b * p.L + l) * p.h_kv + h) * G + g) * D + col);
     *reinterpret_cast<uint4*>(q_s + row * RS + col) = x;
   }
-  for (int t = tid; t < RB; t += 128) lim_s[t] = row_limit(p, l0 + t);
-  for (int row = tid; row < M; row += 128) {
+  for (int t = tid; t < RB; t += NT) lim_s[t] = row_limit(p, l0 + t);
+  for (int row = tid; row < M; row += NT) {
     const int g = row / RB, l = l0 + (row - g * RB);
     float ls = 0.f;
     if (l < p.L) {
@@ -514,7 +520,7 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
   }
   if (has_add)
     for (int g = 0; g < G; ++g)
-      for (int c = tid; c < ntile * kSelTile; c += 128) {
+      for (int c = tid; c < ntile * kSelTile; c += NT) {
         float x = 0.f;
         if (c < p.N) {
           if (p.bias) x += p.bias[(((int64_t)b * p.N + c) * p.h_kv + h) * G + g];
@@ -528,7 +534,7 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
   const uint32_t q32 = (uint32_t)__cvta_generic_to_shared(q_s);
   const uint32_t k32 = (uint32_t)__cvta_generic_to_shared(k_s);
   const uint32_t a_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * RS + (lane >> 4) * 8) * 2u;
-  const uint32_t b_off = (uint32_t)((warp * 32 + (lane & 7) + ((lane >> 4) & 1) * 8) * RS + ((lane >> 3) & 1) * 8) * 2u;
+  const uint32_t b_off = (uint32_t)((warp * CW + (lane & 7) + ((lane >> 4) & 1) * 8) * RS + ((lane >> 3) & 1) * 8) * 2u;
   for (int it = 0; it < total; ++it) {
     const int stage = (sl.NS == 2) ? (it & 1) : 0;
     if (sl.NS == 2 && it + 1 < total) {
@@ -539,24 +545,24 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
     }
     __syncthreads();
     const int pass = it / ntile, c0 = (it - pass * ntile) * kSelTile;
-    const int cw = c0 + warp * 32;
+    const int cw = c0 + warp * CW;
     if (cw < cta_limit) {
       const uint32_t kb = k32 + (uint32_t)stage * (kSelTile * RS * 2) + b_off;
       for (int mb0 = 0; mb0 < mb_pass; mb0 += 4) {
         const int row_base = (p.per_qhead ? pass * RB : 0) + mb0 * 16;
         const int nmb = min(4, mb_pass - mb0);
-        float acc[4][4][4];
+        float acc[4][NBW][4];
 #pragma unroll
         for (int mi = 0; mi < 4; ++mi)
 #pragma unroll
-          for (int ni = 0; ni < 4; ++ni)
+          for (int ni = 0; ni < NBW; ++ni)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[mi][ni][e] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < NK; ++kk) {
-          uint32_t bfr[4][2];
+          uint32_t bfr[NBW][2];
 #pragma unroll
-          for (int np = 0; np < 2; ++np)                   // two 8-candidate blocks per ldmatrix.x4
+          for (int np = 0; np < NBW / 2; ++np)             // two 8-candidate blocks per ldmatrix.x4
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                          : "=r"(bfr[2 * np][0]), "=r"(bfr[2 * np][1]), "=r"(bfr[2 * np + 1][0]), "=r"(bfr[2 * np + 1][1])
                          : "r"(kb + (uint32_t)(np * 16 * RS * 2 + kk * 32)));
@@ -568,7 +574,7 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
                            : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
                            : "r"(q32 + (uint32_t)((row_base + mi * 16) * RS * 2 + kk * 32) + a_off));
 #pragma unroll
-              for (int ni = 0; ni < 4; ++ni)
+              for (int ni = 0; ni < NBW; ++ni)
                 asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                              : "+f"(acc[mi][ni][0]), "+f"(acc[mi][ni][1]), "+f"(acc[mi][ni][2]), "+f"(acc[mi][ni][3])
                              : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(bfr[ni][0]), "r"(bfr[ni][1]));
@@ -585,7 +591,7 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
               const int lim = lim_s[row & (RB - 1)];
               float* vrow = v_s + (size_t)row * RSV + cw + (lane & 3) * 2;
 #pragma unroll
-              for (int ni = 0; ni < 4; ++ni) {
+              for (int ni = 0; ni < NBW; ++ni) {
                 const int c = cw + ni * 8 + (lane & 3) * 2;
                 float2 o;
                 o.x = (c < lim) ? __fmul_rn(acc[mi][ni][2 * hr], p.scale) : -CUDART_INF_F;
@@ -603,7 +609,7 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
   if (total == 0) __syncthreads();
 
   // ---------------- log-sum-exp of the selection logits per row, lse_total ---------------------------------
-  for (int row = warp; row < M; row += 4) {
+  for (int row = warp; row < M; row += kSelWarps) {
     const int g = row / RB, tok = row - g * RB, l = l0 + tok;
     if (l >= p.L) continue;                                 // warp-uniform
     const int lim = lim_s[tok];
@@ -627,10 +633,11 @@ __global__ void __launch_bounds__(128) topk_fwd_mma_kernel(TopkParams p, SelLayo
 
   // ---------------- per token: ranking keys, K-th largest by bisection, ordered compaction ------------------
   uint32_t* bits = bits_s + warp * Npad;
-  uint16_t* cand_id = reinterpret_cast<uint16_t*>(bits_s + 4 * Npad) + warp * Npad;   // long rows: ids of the survivors
+  uint16_t* cand_id = reinterpret_cast<uint16_t*>(bits_s + sl.SW * Npad) + warp * Npad;   // long rows: ids of the survivors
   bf16* scores = static_cast<bf16*>(p.scores);
   const uint32_t lt_mask = (1u << lane) - 1u;
-  for (int tok = warp; tok < RB; tok += 4) {
+  for (int tok = warp; tok < RB; tok += sl.SW) {
+    if (warp >= sl.SW) break;
     const int l = l0 + tok;
     if (l >= p.L) continue;                                 // warp-uniform
     const int lim = lim_s[tok];
@@ -771,7 +778,7 @@ static int launch_topk_mma(const TopkParams& p, cudaStream_t st) {
   if (sl.total == 0) return HILS_ERR_UNSUPPORTED;
   cudaFuncSetAttribute(topk_fwd_mma_kernel<NK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sl.total);
   dim3 grid((p.L + sl.RB - 1) / sl.RB, p.h_kv, p.B);
-  topk_fwd_mma_kernel<NK><<<grid, 128, sl.total, st>>>(hp, sl);
+  topk_fwd_mma_kernel<NK><<<grid, kSelWarps * 32, sl.total, st>>>(hp, sl);
   HILS_LAUNCH_CHECK("topk_fwd (tensor-core scores)");
   return HILS_OK;
 }
