@@ -39,6 +39,8 @@ WORKLOADS = {
     # name: B, T, h_q, h_kv, D, S, K, W
     "c2": dict(B=8, T=8192, h_q=16, h_kv=16, D=64, S=64, K=32, W=512),
     "c2_small": dict(B=1, T=8192, h_q=16, h_kv=16, D=64, S=64, K=32, W=512),
+    # same tokens with the head grouping of the reference's 345M model (2 kv heads, groups of 8 query heads)
+    "c2_gqa": dict(B=8, T=8192, h_q=16, h_kv=2, D=64, S=64, K=32, W=512),
     "c3": dict(B=1, T=65536, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
     # decode: 32 sequences, one new token each, against a 131072-token KV store
     "c4": dict(B=32, T=131072, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
