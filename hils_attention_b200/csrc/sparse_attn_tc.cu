@@ -233,42 +233,48 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
     if (lane == 0 && n > 0) {
       constexpr uint32_t idesc_qk = idesc_bf16(128, 64, 0);
       constexpr uint32_t idesc_pv = idesc_bf16(128, D, 1);
-      const uint32_t q_addr = smem_u32(Qs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs), p_addr = smem_u32(Ps);
-      auto issue_qk = [&](int i) {
-        const int s = i & 1;
+      // descriptor words built once; inside the loops an operand is addressed by adding to the low word
+      const DescWords q_d = desc_words_sw128(smem_u32(Qs), 16, 1024), k_d = desc_words_sw128(smem_u32(Ks), 16, 1024),
+                      p_d = desc_words_sw128(smem_u32(Ps), 16, 1024), v_d = desc_words_sw128(smem_u32(Vs), 8192, 1024);
+      auto issue_qk = [&](int st, int s) {   // st: K/V ring stage of the entry, s: its S buffer
+        const uint32_t kb = k_d.lo + st * (KVBYTES >> 4);
+        mma_ss_w<false>(tS + s * 64, q_d.lo, q_d.hi, kb, k_d.hi, idesc_qk);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t da = desc_sw128(q_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
-          const uint64_t db = desc_sw128(k_addr + (i % NST) * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024);
-          mma_ss(tS + s * 64, da, db, idesc_qk, kk > 0);
-        }
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(tS + s * 64, q_d.lo + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), q_d.hi,
+                         kb + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), k_d.hi, idesc_qk);
         mma_commit(&s_full[s]);
       };
       bool ok = mbar_wait(&kv_full[0], 0);
       if (ok) {
         tc_fence_after();
-        issue_qk(0);
+        issue_qk(0, 0);
       }
+      int st = 0;                 // ring stage of entry i
+      int st1 = 0, ph1 = 0;       // ring stage and phase of entry i + 1
       for (int i = 0; ok && i < n; ++i) {
         const int s = i & 1, u = i >> 1;
         if (abort_s) break;
+        if (++st1 == NST) { st1 = 0; ph1 ^= 1; }
         if (i + 1 < n) {
-          ok = mbar_wait(&kv_full[(i + 1) % NST], ((i + 1) / NST) & 1);
+          ok = mbar_wait(&kv_full[st1], ph1);
           if (!ok) break;
           tc_fence_after();
-          issue_qk(i + 1);
+          issue_qk(st1, s ^ 1);
         }
         ok = mbar_wait(&p_full[s], u & 1);
         if (!ok) break;
         tc_fence_after();
+        {
+          const uint32_t a0 = p_d.lo + s * (16384 >> 4), b0 = v_d.lo + st * (KVBYTES >> 4);
+          mma_ss_wr(tO, a0, p_d.hi, b0, v_d.hi, idesc_pv, i > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t da = desc_sw128(p_addr + s * 16384 + kk * 32, 16, 1024);
-          const uint64_t db = desc_sw128(v_addr + (i % NST) * KVBYTES + kk * 2048, 8192, 1024);
-          mma_ss(tO, da, db, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 1; kk < 4; ++kk)
+            mma_ss_w<true>(tO, a0 + ((kk * 32) >> 4), p_d.hi, b0 + ((kk * 2048) >> 4), v_d.hi, idesc_pv);
         }
         mma_commit(&pv_done[s]);
-        mma_commit(&kv_free[i % NST]);
+        mma_commit(&kv_free[st]);
+        st = st1;
       }
       if (ok) mma_commit(&all_done);  // epilogue barrier for both row warpgroups
       if (!ok) { abort_s = 1; atomicExch(&g_device_status, 102); }
@@ -448,6 +454,7 @@ struct BwdWs {
   int umax;
 };
 constexpr uint16_t kNotOwner = 0x7FC1;  // a bf16 NaN pattern
+constexpr int kMaxMaskWords = 32;       // ownership bit masks are kept for unions of up to 1024 chunks
 
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(SparseParams p, BwdWs ws,
@@ -456,7 +463,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
   constexpr int DB = D / 64;
   constexpr int QBYTES = DB * 16384;
   constexpr int KVBYTES = DB * 8192;
-  constexpr int NST = (D == 64) ? 4 : 3;  // K/V ring depth
+  // S/dP accumulator buffers in TMEM and K/V ring depth.  With three accumulator buffers the products of
+  // entry i+2 are issued as soon as entry i-1 has been consumed, one full entry ahead of the warpgroup
+  // that will read them, so that warpgroup never waits on the tensor pipe; the ring then has to hold the
+  // entries i-1 .. i+2 plus the loads in flight.  D = 128 has shared memory for three stages only and
+  // keeps two buffers (products issued one entry ahead).
+  constexpr int NSB = (D == 64) ? 3 : 2;
+  constexpr int NST = (D == 64) ? 6 : 3;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* Qs = smem;
@@ -470,8 +483,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
   const int G = p.h_q / p.h_kv, QB = 128 / G;
   const int umax = min(nchunk, QB * p.K);
   uint32_t* bitmap_s = reinterpret_cast<uint32_t*>(union_s + umax);
+  // ownership of the union entries: word w of row r (at own_s[w * 128 + r]) has bit e set when the row selected
+  // entry 32 w + e; pref_s[w] = number of union entries below chunk 32 w.  Present when the shape leaves room.
+  const int nmw = (umax + 31) >> 5;
+  const bool have_mask = nmw <= kMaxMaskWords;
+  int* pref_s = reinterpret_cast<int*>(bitmap_s + nwords);
+  uint32_t* own_s = reinterpret_cast<uint32_t*>(pref_s + nwords);
 
-  __shared__ uint64_t kv_full[4], kv_free[4], sdp_full[2], ds_full[2], dq_done[2], all_done;
+  __shared__ uint64_t kv_full[6], kv_free[6], sdp_full[3], ds_full[2], dq_done[2], all_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int n_union_s, warp_tot_s[4];
   __shared__ volatile int abort_s;
@@ -483,10 +502,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
 
   if (tid == 0) {
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&sdp_full[s], 1);
       mbar_init(&ds_full[s], 128);
       mbar_init(&dq_done[s], 1);
     }
+    for (int s = 0; s < NSB; ++s) mbar_init(&sdp_full[s], 1);
     for (int st = 0; st < NST; ++st) {
       mbar_init(&kv_full[st], 1);
       mbar_init(&kv_free[st], 1);
@@ -533,7 +552,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
       const int id = __ldg(ids + k);
       if (id < 0) break;
       ++nvalid;
-      if (id < prev) my_unsorted = 1;
+      if (id <= prev) my_unsorted = 1;   // descending or repeated ids: the general path below
       prev = id;
       if (is_loader && g == 0 && id < nchunk) atomicOr(&bitmap_s[id >> 5], 1u << (id & 31));
     }
@@ -559,6 +578,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
       for (int w = 0; w < warp; ++w) base += warp_tot_s[w];
       for (int w = tid * wpt; w < min(nwords, (tid + 1) * wpt); ++w) {
         uint32_t bits = bitmap_s[w];
+        pref_s[w] = base;
         while (bits) {
           const int bpos = __ffs(bits) - 1;
           bits &= bits - 1;
@@ -569,13 +589,27 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
       if (tid == 127) n_union_s = min(base, umax);
     }
   }
+  const bool fast_own = have_mask && !unsorted;
+  if (fast_own) {
+    __syncthreads();   // pref_s complete
+    if (is_loader) {
+      for (int w = 0; w < nmw; ++w) own_s[w * 128 + r] = 0u;
+      for (int k = 0; k < nvalid; ++k) {
+        const int id = __ldg(ids + k);
+        if (id < nchunk) {
+          const int pos = pref_s[id >> 5] + __popc(bitmap_s[id >> 5] & ((1u << (id & 31)) - 1u));
+          own_s[(pos >> 5) * 128 + r] |= 1u << (pos & 31);
+        }
+      }
+    }
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const int n = n_union_s;
   const uint32_t tmem = tmem_base_s;
-  const uint32_t tdQ = tmem + 256;
+  const uint32_t tdQ = tmem + NSB * 128;
 
   if (warp == 9) {
     if (lane == 0) {
@@ -596,42 +630,59 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
     if (lane == 0 && n > 0) {
       constexpr uint32_t idesc_s = idesc_bf16(128, 64, 0);
       constexpr uint32_t idesc_dq = idesc_bf16(128, D, 1);
-      const uint32_t q_addr = smem_u32(Qs), do_addr = smem_u32(dOs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs),
-                     ds_addr = smem_u32(dSs);
-      auto issue_sdp = [&](int i) {
-        const int s = i & 1;
+      // descriptor words built once; inside the loops an operand is addressed by adding to the low word
+      const DescWords q_d = desc_words_sw128(smem_u32(Qs), 16, 1024), do_d = desc_words_sw128(smem_u32(dOs), 16, 1024),
+                      k_d = desc_words_sw128(smem_u32(Ks), 16, 1024), v_d = desc_words_sw128(smem_u32(Vs), 16, 1024),
+                      ds_d = desc_words_sw128(smem_u32(dSs), 16, 1024), kmn_d = desc_words_sw128(smem_u32(Ks), 8192, 1024);
+      auto issue_sdp = [&](int st, int sb) {   // st: K/V ring stage of the entry, sb: its S/dP buffer
+        const uint32_t kb = k_d.lo + st * (KVBYTES >> 4), vb = v_d.lo + st * (KVBYTES >> 4);
+        const uint32_t ts = tmem + sb * 128;
+        mma_ss_w<false>(ts, q_d.lo, q_d.hi, kb, k_d.hi, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = (i % NST) * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32;
-          mma_ss(tmem + s * 128, desc_sw128(q_addr + ao, 16, 1024), desc_sw128(k_addr + bo, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(ts, q_d.lo + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), q_d.hi,
+                         kb + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), k_d.hi, idesc_s);
+        mma_ss_w<false>(ts + 64, do_d.lo, do_d.hi, vb, v_d.hi, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = (i % NST) * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32;
-          mma_ss(tmem + s * 128 + 64, desc_sw128(do_addr + ao, 16, 1024), desc_sw128(v_addr + bo, 16, 1024), idesc_s, kk > 0);
-        }
-        mma_commit(&sdp_full[s]);
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(ts + 64, do_d.lo + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), do_d.hi,
+                         vb + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), v_d.hi, idesc_s);
+        mma_commit(&sdp_full[sb]);
       };
-      bool ok = mbar_wait(&kv_full[0], 0);
-      if (ok) { tc_fence_after(); issue_sdp(0); }
+      // entries 0 .. NSB-2 are issued before the loop; iteration i then issues entry e = i + NSB - 1, whose
+      // buffer was last read for entry i - 1 (consumed: its dS arrival was waited for in iteration i - 1)
+      bool ok = true;
+      int ste = 0, phe = 0, sbe = 0;   // ring stage, ring phase and accumulator buffer of the next entry to issue
+      auto issue_next = [&]() {
+        ok = mbar_wait(&kv_full[ste], phe);
+        if (!ok) return;
+        tc_fence_after();
+        issue_sdp(ste, sbe);
+        if (++ste == NST) { ste = 0; phe ^= 1; }
+        if (++sbe == NSB) sbe = 0;
+      };
+      for (int e = 0; ok && e < NSB - 1 && e < n; ++e) issue_next();
+      int st = 0;                      // ring stage of entry i
       for (int i = 0; ok && i < n; ++i) {
         const int s = i & 1, u = i >> 1;
         if (abort_s) break;
-        if (i + 1 < n) {
-          ok = mbar_wait(&kv_full[(i + 1) % NST], ((i + 1) / NST) & 1);
+        if (i + NSB - 1 < n) {
+          issue_next();
           if (!ok) break;
-          tc_fence_after();
-          issue_sdp(i + 1);
         }
         ok = mbar_wait(&ds_full[s], u & 1);
         if (!ok) break;
         tc_fence_after();
+        {
+          const uint32_t a0 = ds_d.lo + s * (16384 >> 4), b0 = kmn_d.lo + st * (KVBYTES >> 4);
+          mma_ss_wr(tdQ, a0, ds_d.hi, b0, kmn_d.hi, idesc_dq, i > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          mma_ss(tdQ, desc_sw128(ds_addr + s * 16384 + kk * 32, 16, 1024),
-                 desc_sw128(k_addr + (i % NST) * KVBYTES + kk * 2048, 8192, 1024), idesc_dq, (i > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 1; kk < 4; ++kk)
+            mma_ss_w<true>(tdQ, a0 + ((kk * 32) >> 4), ds_d.hi, b0 + ((kk * 2048) >> 4), kmn_d.hi, idesc_dq);
+        }
         mma_commit(&dq_done[s]);
-        mma_commit(&kv_free[i % NST]);
+        mma_commit(&kv_free[st]);
+        if (++st == NST) st = 0;
       }
       // both row warpgroups wait on this for the epilogue: a parity wait on a stage barrier could be
       // satisfied by an older phase for the warpgroup that did not take the last entry
@@ -646,13 +697,27 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
     float cur_w = (nvalid > 0) ? to_f(wrow[0]) : 0.f;       // one step ahead, so their loads are not waited on
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
+    int sb = wg, sph = 0;   // accumulator buffer of entry i (i % NSB) and the phase of its barrier ((i / NSB) & 1)
+    int own_w = 0, own_below = 0;                       // current ownership word and the row's slots in the words below it
+    uint32_t own_bits = fast_own ? own_s[r] : 0u;
     for (int i = wg; i < n; i += 2) {
       const int s = i & 1, u = i >> 1;
       const int c = union_s[i];
       float wsum = 0.f;
       bool owner = false;
       int k_first = 0, k_last = 0;
-      if (!unsorted) {
+      if (fast_own) {
+        // ids strictly ascending: the slot of entry i is the number of the row's entries below it
+        while (own_w < (i >> 5)) {
+          own_below += __popc(own_bits);
+          ++own_w;
+          own_bits = own_s[own_w * 128 + r];
+        }
+        owner = (own_bits >> (i & 31)) & 1u;
+        k_first = own_below + __popc(own_bits & ((1u << (i & 31)) - 1u));
+        k_last = k_first + (owner ? 1 : 0);
+        if (owner) wsum = to_f(wrow[k_first]);
+      } else if (!unsorted) {
         while (cur < c) {  // ids consumed by the other warpgroup's entries
           ++ptr;
           cur = (ptr < nvalid) ? __ldg(ids + ptr) : 0x7fffffff;
@@ -671,25 +736,33 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dq_tc_kernel(Sparse
         for (int k = 0; k < nvalid; ++k)
           if (__ldg(ids + k) == c) { owner = true; wsum += to_f(wrow[k]); }
       }
+      ok = mbar_wait(&sdp_full[sb], sph);
+      ok = __all_sync(0xffffffffu, ok) && !abort_s;
+      if (!ok) break;
+      tc_fence_after();
+      float sv[64], dp[64];
+      const uint32_t tsd = tmem + lane_base + sb * 128;
+      tmem_ld32(tsd, sv);
+      tmem_ld32(tsd + 32, sv + 32);
+      tmem_ld_wait();
+      tmem_ld32(tsd + 64, dp);        // in flight while the S row is exponentiated
+      tmem_ld32(tsd + 96, dp + 32);
+      float esum = 1.f;
+      if (owner) esum = bwd_row_exp(sv, scale_log2, slope, p.mask_last);
+      tmem_ld_wait64(dp);
+      sb += 2;
+      if (sb >= NSB) { sb -= NSB; sph ^= 1; }
       {
         const __nv_bfloat16 wb = __float2bfloat16_rn(wsum);
         ws.wtab[((((int64_t)b * p.h_kv + h) * nblk + blk) * ws.umax + i) * 128 + r] =
             owner ? *reinterpret_cast<const uint16_t*>(&wb) : kNotOwner;
       }
-      ok = mbar_wait(&sdp_full[s], u & 1);
-      if (i >= 2) ok = mbar_wait(&dq_done[s], (u - 1) & 1) && ok;
-      ok = __all_sync(0xffffffffu, ok) && !abort_s;
-      if (!ok) break;
-      tc_fence_after();
-      float sv[64], dp[64];
-      tmem_ld32(tmem + lane_base + s * 128, sv);
-      tmem_ld32(tmem + lane_base + s * 128 + 32, sv + 32);
-      tmem_ld_wait();
-      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);        // in flight while the S row is exponentiated
-      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
-      float esum = 1.f;
-      if (owner) esum = bwd_row_exp(sv, scale_log2, slope, p.mask_last);
-      tmem_ld_wait64(dp);
+      // the dS buffer was last read by the dQ product of entry i - 2
+      if (i >= 2) {
+        ok = mbar_wait(&dq_done[s], (u - 1) & 1);
+        ok = __all_sync(0xffffffffu, ok) && !abort_s;
+        if (!ok) break;
+      }
       uint8_t* dsrow = dSs + s * 16384;
       if (owner) {
         const float dw = bwd_row_grad<false>(sv, dp, esum, wsum, p.scale);
@@ -855,45 +928,58 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
     if (lane == 0 && m > 0) {
       constexpr uint32_t idesc_s = idesc_bf16(128, 64, 0);
       constexpr uint32_t idesc_dkv = idesc_bf16(64, D, 1, 1);
-      const uint32_t q_addr = smem_u32(Qs), do_addr = smem_u32(dOs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs),
-                     ds_addr = smem_u32(dSs), pw_addr = smem_u32(Pws);
-      auto issue_sdp = [&](int j) {
-        const int s = j & 1;
+      // descriptor words built once (see the dq kernel); the Q / dO tiles are read K-major for S and dP and
+      // MN-major (16 query rows per step) for dK and dV
+      const DescWords q_d = desc_words_sw128(smem_u32(Qs), 16, 1024), do_d = desc_words_sw128(smem_u32(dOs), 16, 1024),
+                      k_d = desc_words_sw128(smem_u32(Ks), 16, 1024), v_d = desc_words_sw128(smem_u32(Vs), 16, 1024),
+                      qmn_d = desc_words_sw128(smem_u32(Qs), 16384, 1024), domn_d = desc_words_sw128(smem_u32(dOs), 16384, 1024),
+                      ds_d = desc_words_sw128(smem_u32(dSs), 16384, 1024), pw_d = desc_words_sw128(smem_u32(Pws), 16384, 1024);
+      auto issue_sdp = [&](int sq, int s) {   // sq: Q/dO ring stage of the block, s: its S/dP buffer
+        const uint32_t qb = q_d.lo + sq * (QBYTES >> 4), dob = do_d.lo + sq * (QBYTES >> 4);
+        const uint32_t ts = tmem + s * 128;
+        mma_ss_w<false>(ts, qb, q_d.hi, k_d.lo, k_d.hi, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = (j % NQ) * QBYTES + (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
-          mma_ss(tmem + s * 128, desc_sw128(q_addr + ao, 16, 1024), desc_sw128(k_addr + bo, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(ts, qb + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), q_d.hi,
+                         k_d.lo + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), k_d.hi, idesc_s);
+        mma_ss_w<false>(ts + 64, dob, do_d.hi, v_d.lo, v_d.hi, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = (j % NQ) * QBYTES + (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
-          mma_ss(tmem + s * 128 + 64, desc_sw128(do_addr + ao, 16, 1024), desc_sw128(v_addr + bo, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(ts + 64, dob + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), do_d.hi,
+                         v_d.lo + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), v_d.hi, idesc_s);
         mma_commit(&sdp_full[s]);
       };
       bool ok = mbar_wait(&kv_full, 0) && mbar_wait(&qdo_full[0], 0);
-      if (ok) { tc_fence_after(); issue_sdp(0); }
+      if (ok) { tc_fence_after(); issue_sdp(0, 0); }
+      int sq = 0;                 // ring stage of block j
+      int sq1 = 0, ph1 = 0;       // ring stage and phase of block j + 1
       for (int j = 0; ok && j < m; ++j) {
-        const int s = j & 1, u = j >> 1, sb = j % NDS;
+        const int s = j & 1, u = j >> 1, sb = (NDS == 2) ? s : 0;
         if (abort_s) break;
+        if (++sq1 == NQ) { sq1 = 0; ph1 ^= 1; }
         if (j + 1 < m) {
-          ok = mbar_wait(&qdo_full[(j + 1) % NQ], ((j + 1) / NQ) & 1);
+          ok = mbar_wait(&qdo_full[sq1], ph1);
           if (!ok) break;
           tc_fence_after();
-          issue_sdp(j + 1);
+          issue_sdp(sq1, s ^ 1);
         }
         ok = mbar_wait(&dsp_full[s], u & 1);
         if (!ok) break;
         tc_fence_after();
+        {
+          const uint32_t dsb = ds_d.lo + sb * (16384 >> 4), pwb = pw_d.lo + sb * (16384 >> 4);
+          const uint32_t qb = qmn_d.lo + sq * (QBYTES >> 4), dob = domn_d.lo + sq * (QBYTES >> 4);
+          mma_ss_wr(tdK, dsb, ds_d.hi, qb, qmn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
+          mma_ss_wr(tdV, pwb, pw_d.hi, dob, domn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {   // 16 query rows per step
-          const uint64_t db_q = desc_sw128(q_addr + (j % NQ) * QBYTES + kk * 2048, 16384, 1024);
-          const uint64_t db_do = desc_sw128(do_addr + (j % NQ) * QBYTES + kk * 2048, 16384, 1024);
-          mma_ss(tdK, desc_sw128(ds_addr + sb * 16384 + kk * 2048, 16384, 1024), db_q, idesc_dkv, (j > 0 || kk > 0) ? 1u : 0u);
-          mma_ss(tdV, desc_sw128(pw_addr + sb * 16384 + kk * 2048, 16384, 1024), db_do, idesc_dkv, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 1; kk < 8; ++kk) {   // 16 query rows per step
+            mma_ss_w<true>(tdK, dsb + ((kk * 2048) >> 4), ds_d.hi, qb + ((kk * 2048) >> 4), qmn_d.hi, idesc_dkv);
+            mma_ss_w<true>(tdV, pwb + ((kk * 2048) >> 4), pw_d.hi, dob + ((kk * 2048) >> 4), domn_d.hi, idesc_dkv);
+          }
         }
         mma_commit(&dkv_done[s]);
-        mma_commit(&qdo_free[j % NQ]);
+        mma_commit(&qdo_free[sq]);
+        sq = sq1;
       }
       if (ok) mma_commit(&all_done);  // epilogue barrier for both row warpgroups (see the dq kernel)
       if (!ok) { abort_s = 1; atomicExch(&g_device_status, 302); }
@@ -999,9 +1085,10 @@ static bool tc_shape_ok(const SparseParams& p) {
 static size_t tc_bwd_smem_dq(const SparseParams& p) {
   const int D = p.D, G = p.h_q / p.h_kv, QB = 128 / G, nchunk = p.T / 64;
   const int umax = min(nchunk, QB * p.K);
-  const int NST = (D == 64) ? 4 : 3;
+  const int NST = (D == 64) ? 6 : 3;
+  const size_t nmw = (size_t)(umax + 31) / 32;
   return 1024 + 2 * (size_t)(D / 64) * 16384 + 2 * (size_t)NST * (D / 64) * 8192 + 2 * 16384 + (size_t)umax * 4 +
-         (size_t)((nchunk + 31) / 32) * 4 + 16;
+         (size_t)((nchunk + 31) / 32) * 8 + (nmw <= (size_t)kMaxMaskWords ? nmw * 512 : 0) + 16;
 }
 static size_t tc_bwd_smem_dkv(const SparseParams& p, int nblk) {
   const int D = p.D, NDS = (D == 64) ? 2 : 1, NQ = (D == 64) ? 3 : 2;

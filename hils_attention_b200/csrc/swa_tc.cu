@@ -123,13 +123,17 @@ __global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, con
     if (lane == 0 && n > 0) {
       constexpr uint32_t idesc_qk = idesc_bf16(128, 64, 0);
       constexpr uint32_t idesc_pv = idesc_bf16(128, D, 1);
-      const uint32_t q_addr = smem_u32(Qs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs), p_addr = smem_u32(Ps);
+      // descriptor words built once; inside the loops an operand is addressed by adding to the low word
+      const DescWords q_d = desc_words_sw128(smem_u32(Qs), 16, 1024), k_d = desc_words_sw128(smem_u32(Ks), 16, 1024),
+                      p_d = desc_words_sw128(smem_u32(Ps), 16, 1024), v_d = desc_words_sw128(smem_u32(Vs), 8192, 1024);
       auto issue_qk = [&](int it) {
         const int s = it & 1;
+        const uint32_t kb = k_d.lo + s * (KVBYTES >> 4);
+        mma_ss_w<false>(tS + s * 64, q_d.lo, q_d.hi, kb, k_d.hi, idesc_qk);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss(tS + s * 64, desc_sw128(q_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
-                 desc_sw128(k_addr + s * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024), idesc_qk, kk > 0);
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(tS + s * 64, q_d.lo + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), q_d.hi,
+                         kb + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), k_d.hi, idesc_qk);
         mma_commit(&s_full[s]);
       };
       bool ok = mbar_wait(&kv_full[0], 0);
@@ -147,10 +151,11 @@ __global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, con
         if (!ok) break;
         tc_fence_after();
         if (it >= nt) {
+          const uint32_t a0 = p_d.lo + s * (16384 >> 4), b0 = v_d.lo + s * (KVBYTES >> 4);
+          mma_ss_wr(tO, a0, p_d.hi, b0, v_d.hi, idesc_pv, it > nt ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            mma_ss(tO, desc_sw128(p_addr + s * 16384 + kk * 32, 16, 1024),
-                   desc_sw128(v_addr + s * KVBYTES + kk * 2048, 8192, 1024), idesc_pv, (it > nt || kk > 0) ? 1u : 0u);
+          for (int kk = 1; kk < 4; ++kk)
+            mma_ss_w<true>(tO, a0 + ((kk * 32) >> 4), p_d.hi, b0 + ((kk * 2048) >> 4), v_d.hi, idesc_pv);
         }
         mma_commit(&pv_done[s]);
       }
@@ -341,20 +346,24 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dq_tc_kernel(SwaTcParams 
     if (lane == 0 && n > 0) {
       constexpr uint32_t idesc_s = idesc_bf16(128, 64, 0);
       constexpr uint32_t idesc_dq = idesc_bf16(128, D, 1);
-      const uint32_t q_addr = smem_u32(Qs), do_addr = smem_u32(dOs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs),
-                     ds_addr = smem_u32(dSs);
+      // descriptor words built once; inside the loops an operand is addressed by adding to the low word
+      const DescWords q_d = desc_words_sw128(smem_u32(Qs), 16, 1024), do_d = desc_words_sw128(smem_u32(dOs), 16, 1024),
+                      k_d = desc_words_sw128(smem_u32(Ks), 16, 1024), v_d = desc_words_sw128(smem_u32(Vs), 16, 1024),
+                      ds_d = desc_words_sw128(smem_u32(dSs), 16, 1024), kmn_d = desc_words_sw128(smem_u32(Ks), 8192, 1024);
       auto issue_sdp = [&](int it) {
         const int s = it & 1;
+        const uint32_t kb = k_d.lo + s * (KVBYTES >> 4), vb = v_d.lo + s * (KVBYTES >> 4);
+        const uint32_t ts = tmem + s * 128;
+        mma_ss_w<false>(ts, q_d.lo, q_d.hi, kb, k_d.hi, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = s * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32;
-          mma_ss(tmem + s * 128, desc_sw128(q_addr + ao, 16, 1024), desc_sw128(k_addr + bo, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(ts, q_d.lo + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), q_d.hi,
+                         kb + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), k_d.hi, idesc_s);
+        mma_ss_w<false>(ts + 64, do_d.lo, do_d.hi, vb, v_d.hi, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = s * KVBYTES + (kk >> 2) * 8192 + (kk & 3) * 32;
-          mma_ss(tmem + s * 128 + 64, desc_sw128(do_addr + ao, 16, 1024), desc_sw128(v_addr + bo, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(ts + 64, do_d.lo + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), do_d.hi,
+                         vb + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), v_d.hi, idesc_s);
         mma_commit(&sdp_full[s]);
       };
       bool ok = mbar_wait(&kv_full[0], 0);
@@ -371,10 +380,13 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dq_tc_kernel(SwaTcParams 
         ok = mbar_wait(&ds_full[s], u & 1);
         if (!ok) break;
         tc_fence_after();
+        {
+          const uint32_t a0 = ds_d.lo + s * (16384 >> 4), b0 = kmn_d.lo + s * (KVBYTES >> 4);
+          mma_ss_wr(tdQ, a0, ds_d.hi, b0, kmn_d.hi, idesc_dq, it > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          mma_ss(tdQ, desc_sw128(ds_addr + s * 16384 + kk * 32, 16, 1024),
-                 desc_sw128(k_addr + s * KVBYTES + kk * 2048, 8192, 1024), idesc_dq, (it > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 1; kk < 4; ++kk)
+            mma_ss_w<true>(tdQ, a0 + ((kk * 32) >> 4), ds_d.hi, b0 + ((kk * 2048) >> 4), kmn_d.hi, idesc_dq);
+        }
         mma_commit(&dq_done[s]);
       }
       if (!ok) { abort_s = 1; atomicExch(&g_device_status, 412); }
@@ -511,20 +523,25 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams
     if (lane == 0 && m > 0) {
       constexpr uint32_t idesc_s = idesc_bf16(128, 64, 0);
       constexpr uint32_t idesc_dkv = idesc_bf16(64, D, 1, 1);
-      const uint32_t q_addr = smem_u32(Qs), do_addr = smem_u32(dOs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs),
-                     ds_addr = smem_u32(dSs), pw_addr = smem_u32(Pws);
+      // descriptor words built once; the Q / dO tiles are read K-major for S and dP and MN-major for dK and dV
+      const DescWords q_d = desc_words_sw128(smem_u32(Qs), 16, 1024), do_d = desc_words_sw128(smem_u32(dOs), 16, 1024),
+                      k_d = desc_words_sw128(smem_u32(Ks), 16, 1024), v_d = desc_words_sw128(smem_u32(Vs), 16, 1024),
+                      qmn_d = desc_words_sw128(smem_u32(Qs), 16384, 1024), domn_d = desc_words_sw128(smem_u32(dOs), 16384, 1024),
+                      ds_d = desc_words_sw128(smem_u32(dSs), 16384, 1024), pw_d = desc_words_sw128(smem_u32(Pws), 16384, 1024);
       auto issue_sdp = [&](int j) {
         const int s = j & 1;
+        const uint32_t qb = q_d.lo + s * (QBYTES >> 4), dob = do_d.lo + s * (QBYTES >> 4);
+        const uint32_t ts = tmem + s * 128;
+        mma_ss_w<false>(ts, qb, q_d.hi, k_d.lo, k_d.hi, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = s * QBYTES + (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
-          mma_ss(tmem + s * 128, desc_sw128(q_addr + ao, 16, 1024), desc_sw128(k_addr + bo, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(ts, qb + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), q_d.hi,
+                         k_d.lo + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), k_d.hi, idesc_s);
+        mma_ss_w<false>(ts + 64, dob, do_d.hi, v_d.lo, v_d.hi, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t ao = s * QBYTES + (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
-          mma_ss(tmem + s * 128 + 64, desc_sw128(do_addr + ao, 16, 1024), desc_sw128(v_addr + bo, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(ts + 64, dob + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), do_d.hi,
+                         v_d.lo + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), v_d.hi, idesc_s);
         mma_commit(&sdp_full[s]);
       };
       bool ok = mbar_wait(&kv_full, 0) && mbar_wait(&qdo_full[0], 0);
@@ -541,12 +558,16 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams
         ok = mbar_wait(&dsp_full[s], u & 1);
         if (!ok) break;
         tc_fence_after();
+        {
+          const uint32_t dsb = ds_d.lo + sb * (16384 >> 4), pwb = pw_d.lo + sb * (16384 >> 4);
+          const uint32_t qb = qmn_d.lo + s * (QBYTES >> 4), dob = domn_d.lo + s * (QBYTES >> 4);
+          mma_ss_wr(tdK, dsb, ds_d.hi, qb, qmn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
+          mma_ss_wr(tdV, pwb, pw_d.hi, dob, domn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          mma_ss(tdK, desc_sw128(ds_addr + sb * 16384 + kk * 2048, 16384, 1024),
-                 desc_sw128(q_addr + s * QBYTES + kk * 2048, 16384, 1024), idesc_dkv, (j > 0 || kk > 0) ? 1u : 0u);
-          mma_ss(tdV, desc_sw128(pw_addr + sb * 16384 + kk * 2048, 16384, 1024),
-                 desc_sw128(do_addr + s * QBYTES + kk * 2048, 16384, 1024), idesc_dkv, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 1; kk < 8; ++kk) {
+            mma_ss_w<true>(tdK, dsb + ((kk * 2048) >> 4), ds_d.hi, qb + ((kk * 2048) >> 4), qmn_d.hi, idesc_dkv);
+            mma_ss_w<true>(tdV, pwb + ((kk * 2048) >> 4), pw_d.hi, dob + ((kk * 2048) >> 4), domn_d.hi, idesc_dkv);
+          }
         }
         mma_commit(&dkv_done[s]);
       }

@@ -87,6 +87,39 @@ __device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t da, uint64_t db
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same MMA with the two shared-memory descriptors passed as (low, high) words.  The issuing thread shares
+// its scheduler with busy row warps, so what it executes between two MMAs decides how densely the tensor
+// pipe is fed: descriptors are built once outside the loops and advanced by adding bytes >> 4 to the low
+// word (the address field; the operand stays below 256 KB, so the add never carries out of it).
+struct DescWords { uint32_t lo, hi; };
+__device__ __forceinline__ DescWords desc_words_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  const uint64_t d = desc_sw128(saddr, lbo_bytes, sbo_bytes);
+  return DescWords{(uint32_t)d, (uint32_t)(d >> 32)};
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_ss_w(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
+  if (kAccumulate)
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\nsetp.ne.b32 p, 1, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
+        : "memory");
+  else
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\nsetp.ne.b32 p, 0, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
+        : "memory");
+}
+// accumulate flag known only at run time (the first product into an accumulator)
+__device__ __forceinline__ void mma_ss_wr(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\nsetp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // arrive on `bar` when all MMAs issued so far by this thread have completed
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
