@@ -256,11 +256,16 @@ __device__ __forceinline__ void swa_bwd_row_ds(float* sv, float* dp, float delta
 
 // ================================================================================================
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1) swa_bwd_dq_tc_kernel(SwaTcParams p, const __grid_constant__ CUtensorMap tmK,
+__global__ void __launch_bounds__(kThreads, (D == 64) ? 2 : 1) swa_bwd_dq_tc_kernel(SwaTcParams p, const __grid_constant__ CUtensorMap tmK,
                                                                     const __grid_constant__ CUtensorMap tmV) {
   constexpr int DB = D / 64;
   constexpr int QBYTES = DB * 16384;
   constexpr int KVBYTES = DB * 8192;
+  // A block's window is only ~10 key tiles, so a CTA's prologue, pipeline fill and epilogue weigh as much
+  // as its loop.  At D = 64 two CTAs share an SM and hide them for each other: one S/dP accumulator per
+  // CTA (256 TMEM columns), products issued after the previous tile's dS.  D = 128 needs the whole shared
+  // memory for one CTA and double-buffers the accumulator instead.
+  constexpr int NSB = (D == 64) ? 1 : 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* Qs = smem;
@@ -288,7 +293,7 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dq_tc_kernel(SwaTcParams 
     mbar_init_fence();
     abort_s = 0;
   }
-  if (warp == 4) tmem_alloc(&tmem_base_s, 512);
+  if (warp == 4) tmem_alloc(&tmem_base_s, NSB == 1 ? 256 : 512);
 
   const int r = tid, ql = r / G, g = r % G, i = q0 + ql;
   const bool is_row = tid < 128;
@@ -326,7 +331,7 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dq_tc_kernel(SwaTcParams 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t tdQ = tmem + 256;
+  const uint32_t tdQ = tmem + NSB * 128;
 
   if (warp == 5) {
     if (lane == 0) {
@@ -353,7 +358,7 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dq_tc_kernel(SwaTcParams 
       auto issue_sdp = [&](int it) {
         const int s = it & 1;
         const uint32_t kb = k_d.lo + s * (KVBYTES >> 4), vb = v_d.lo + s * (KVBYTES >> 4);
-        const uint32_t ts = tmem + s * 128;
+        const uint32_t ts = tmem + (NSB == 2 ? s : 0) * 128;
         mma_ss_w<false>(ts, q_d.lo, q_d.hi, kb, k_d.hi, idesc_s);
 #pragma unroll
         for (int kk = 1; kk < D / 16; ++kk)
@@ -364,14 +369,14 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dq_tc_kernel(SwaTcParams 
         for (int kk = 1; kk < D / 16; ++kk)
           mma_ss_w<true>(ts + 64, do_d.lo + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), do_d.hi,
                          vb + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), v_d.hi, idesc_s);
-        mma_commit(&sdp_full[s]);
+        mma_commit(&sdp_full[NSB == 2 ? s : 0]);
       };
       bool ok = mbar_wait(&kv_full[0], 0);
       if (ok) { tc_fence_after(); issue_sdp(0); }
       for (int it = 0; ok && it < n; ++it) {
         const int s = it & 1, u = it >> 1;
         if (abort_s) break;
-        if (it + 1 < n) {
+        if (NSB == 2 && it + 1 < n) {
           ok = mbar_wait(&kv_full[(it + 1) & 1], ((it + 1) >> 1) & 1);
           if (!ok) break;
           tc_fence_after();
@@ -388,6 +393,12 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dq_tc_kernel(SwaTcParams 
             mma_ss_w<true>(tdQ, a0 + ((kk * 32) >> 4), ds_d.hi, b0 + ((kk * 2048) >> 4), kmn_d.hi, idesc_dq);
         }
         mma_commit(&dq_done[s]);
+        if (NSB == 1 && it + 1 < n) {   // the single accumulator was consumed before the dS arrival above
+          ok = mbar_wait(&kv_full[(it + 1) & 1], ((it + 1) >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sdp(it + 1);
+        }
       }
       if (!ok) { abort_s = 1; atomicExch(&g_device_status, 412); }
     }
@@ -400,17 +411,18 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dq_tc_kernel(SwaTcParams 
     for (int it = 0; it < n; ++it) {
       const int s = it & 1, u = it >> 1;
       const int j0 = (jt0 + it) * 64;
-      ok = mbar_wait(&sdp_full[s], u & 1);
+      ok = (NSB == 2) ? mbar_wait(&sdp_full[s], u & 1) : mbar_wait(&sdp_full[0], it & 1);
       if (it >= 2) ok = mbar_wait(&dq_done[s], (u - 1) & 1) && ok;
       ok = __all_sync(0xffffffffu, ok) && !abort_s;
       if (!ok) break;
       tc_fence_after();
       float sv[64], dp[64];
-      tmem_ld32(tmem + lane_base + s * 128, sv);
-      tmem_ld32(tmem + lane_base + s * 128 + 32, sv + 32);
+      const uint32_t tsd = tmem + lane_base + (NSB == 2 ? s : 0) * 128;
+      tmem_ld32(tsd, sv);
+      tmem_ld32(tsd + 32, sv + 32);
       tmem_ld_wait();
-      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);        // in flight while P is formed
-      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
+      tmem_ld32(tsd + 64, dp);        // in flight while P is formed
+      tmem_ld32(tsd + 96, dp + 32);
       swa_bwd_row_p(sv, sl2, lse_l2, lo - j0, hi - j0, lmk_bits(p, j0));
       tmem_ld_wait64(dp);
       swa_bwd_row_ds(sv, dp, delta, p.scale);
@@ -443,20 +455,23 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dq_tc_kernel(SwaTcParams 
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, 512);
+  if (warp == 4) tmem_dealloc(tmem, NSB == 1 ? 256 : 512);
 }
 
 // ================================================================================================
 // key-major pass (training layout: Lq == Lk, kv_start == 0, so query i sits at position i)
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams p, const __grid_constant__ CUtensorMap tmK,
+__global__ void __launch_bounds__(kThreads, (D == 64) ? 2 : 1) swa_bwd_dkv_tc_kernel(SwaTcParams p, const __grid_constant__ CUtensorMap tmK,
                                                                      const __grid_constant__ CUtensorMap tmV,
                                                                      const __grid_constant__ CUtensorMap tmQ,
                                                                      const __grid_constant__ CUtensorMap tmdO) {
   constexpr int DB = D / 64;
   constexpr int QBYTES = DB * 16384;
   constexpr int KVBYTES = DB * 8192;
-  constexpr int NDS = (D == 64) ? 2 : 1;
+  // Only ~6 query blocks see a key tile, so at D = 64 two CTAs share an SM (see the query-major pass): one
+  // S/dP accumulator (256 TMEM columns) and one dS / P buffer per CTA.
+  constexpr int NDS = 1;
+  constexpr int NSB = (D == 64) ? 1 : 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* Qs = smem;
@@ -465,6 +480,16 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams
   uint8_t* Vs = Ks + KVBYTES;
   uint8_t* dSs = Vs + KVBYTES;
   uint8_t* Pws = dSs + NDS * 16384;
+  {
+    // the launch sizes the dynamic region for the static variables in front of it (see the host side):
+    // refuse to run rather than write past it if the layout is ever different
+    uint32_t dyn_bytes;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    if ((size_t)(Pws + NDS * 16384 - smem_raw) > dyn_bytes) {
+      if (threadIdx.x == 0) atomicExch(&g_device_status, 425);
+      return;
+    }
+  }
 
   __shared__ uint64_t kv_full, qdo_full[2], sdp_full[2], dsp_full[2], dkv_done[2];
   __shared__ uint32_t tmem_base_s;
@@ -486,7 +511,7 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams
     mbar_init_fence();
     abort_s = 0;
   }
-  if (warp == 4) tmem_alloc(&tmem_base_s, 512);
+  if (warp == 4) tmem_alloc(&tmem_base_s, NSB == 1 ? 256 : 512);
   // queries that can see a key of this tile: i in [j_first, i_hi(j_last)]
   const int j_first = jt * 64, j_last = min(j_first + 63, L - 1);
   int i_hi = p.expand ? (j_last / p.S + 1) * p.S + p.W - 2 : j_last + p.W - 1;
@@ -497,7 +522,7 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t tdK = tmem + 256, tdV = tmem + 256 + D;
+  const uint32_t tdK = tmem + NSB * 128, tdV = tmem + NSB * 128 + D;
 
   if (warp == 5) {
     if (lane == 0 && m > 0) {
@@ -531,7 +556,7 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams
       auto issue_sdp = [&](int j) {
         const int s = j & 1;
         const uint32_t qb = q_d.lo + s * (QBYTES >> 4), dob = do_d.lo + s * (QBYTES >> 4);
-        const uint32_t ts = tmem + s * 128;
+        const uint32_t ts = tmem + (NSB == 2 ? s : 0) * 128;
         mma_ss_w<false>(ts, qb, q_d.hi, k_d.lo, k_d.hi, idesc_s);
 #pragma unroll
         for (int kk = 1; kk < D / 16; ++kk)
@@ -542,14 +567,14 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams
         for (int kk = 1; kk < D / 16; ++kk)
           mma_ss_w<true>(ts + 64, dob + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), do_d.hi,
                          v_d.lo + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), v_d.hi, idesc_s);
-        mma_commit(&sdp_full[s]);
+        mma_commit(&sdp_full[NSB == 2 ? s : 0]);
       };
       bool ok = mbar_wait(&kv_full, 0) && mbar_wait(&qdo_full[0], 0);
       if (ok) { tc_fence_after(); issue_sdp(0); }
       for (int j = 0; ok && j < m; ++j) {
         const int s = j & 1, u = j >> 1, sb = j % NDS;
         if (abort_s) break;
-        if (j + 1 < m) {
+        if (NSB == 2 && j + 1 < m) {
           ok = mbar_wait(&qdo_full[(j + 1) & 1], ((j + 1) >> 1) & 1);
           if (!ok) break;
           tc_fence_after();
@@ -570,6 +595,12 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams
           }
         }
         mma_commit(&dkv_done[s]);
+        if (NSB == 1 && j + 1 < m) {   // the single accumulator was consumed before the dS arrival above
+          ok = mbar_wait(&qdo_full[(j + 1) & 1], ((j + 1) >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sdp(j + 1);
+        }
       }
       if (!ok) { abort_s = 1; atomicExch(&g_device_status, 422); }
     }
@@ -593,17 +624,18 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams
           delta = p.delta[rowi];
         }
       }
-      ok = mbar_wait(&sdp_full[s], u & 1);
+      ok = (NSB == 2) ? mbar_wait(&sdp_full[s], u & 1) : mbar_wait(&sdp_full[0], j & 1);
       if (j >= NDS) ok = mbar_wait(&dkv_done[(j - NDS) & 1], ((j - NDS) >> 1) & 1) && ok;
       ok = __all_sync(0xffffffffu, ok) && !abort_s;
       if (!ok) break;
       tc_fence_after();
       float sv[64], dp[64];
-      tmem_ld32(tmem + lane_base + s * 128, sv);
-      tmem_ld32(tmem + lane_base + s * 128 + 32, sv + 32);
+      const uint32_t tsd = tmem + lane_base + (NSB == 2 ? s : 0) * 128;
+      tmem_ld32(tsd, sv);
+      tmem_ld32(tsd + 32, sv + 32);
       tmem_ld_wait();
-      tmem_ld32(tmem + lane_base + s * 128 + 64, dp);        // in flight while P is formed
-      tmem_ld32(tmem + lane_base + s * 128 + 96, dp + 32);
+      tmem_ld32(tsd + 64, dp);        // in flight while P is formed
+      tmem_ld32(tsd + 96, dp + 32);
       swa_bwd_row_p(sv, sl2, lse_l2, lo - j_first, hi - j_first, lm);
       tmem_ld_wait64(dp);
       swa_bwd_row_ds(sv, dp, delta, p.scale);
@@ -643,7 +675,7 @@ __global__ void __launch_bounds__(kThreads, 1) swa_bwd_dkv_tc_kernel(SwaTcParams
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, 512);
+  if (warp == 4) tmem_dealloc(tmem, NSB == 1 ? 256 : 512);
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -712,9 +744,13 @@ int swa_bwd_tc_launch(const void* q, const void* k, const void* v, const void* o
   if (int rc = make_tmap_bf16_rows(&tmV, v, (uint64_t)B * L, (uint64_t)h_kv * D, (uint64_t)h_kv * D, 64)) return rc;
   if (int rc = make_tmap_bf16_thd(&tmQ, q, (uint64_t)B * L, h_q, D, G, QB)) return rc;
   if (int rc = make_tmap_bf16_thd(&tmdO, d_o, (uint64_t)B * L, h_q, D, G, QB)) return rc;
-  const int NDS = (D == 64) ? 2 : 1;
+  const int NDS = 1;
   const size_t smem_dq = 1024 + 2 * (size_t)(D / 64) * 16384 + 4 * (size_t)(D / 64) * 8192 + 2 * 16384;
-  const size_t smem_dkv = 1024 + 4 * (size_t)(D / 64) * 16384 + 2 * (size_t)(D / 64) * 8192 + 2 * (size_t)NDS * 16384;
+  // D = 64: two CTAs per SM need (228 KB / 2 - 1 KB reserved) = 115,712 bytes each, static variables (80 bytes) included.
+  // The tiles take 114,688; the static variables sit in front of the dynamic
+  // region, so 944 bytes of slack reach the next 1 KB boundary (the kernel checks that they do).
+  const size_t smem_dkv = (D == 64 ? 944 : 1024) + 4 * (size_t)(D / 64) * 16384 + 2 * (size_t)(D / 64) * 8192 +
+                          2 * (size_t)NDS * 16384;
   dim3 grid_q(ceil_div(L, QB), h_kv, B), grid_k(ceil_div(L, 64), h_kv, B);
   if (D == 64) {
     cudaFuncSetAttribute(swa_bwd_dq_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq);

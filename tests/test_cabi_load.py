@@ -68,3 +68,11 @@ def test_binding_table_matches_header_prototypes():
         assert len(argtypes) == len(params), f"{name}: {len(argtypes)} bound arguments vs {len(params)} in the header"
         for i, (a, d) in enumerate(zip(argtypes, params)):
             assert a is _kind(d), f"{name}: argument {i} ({d}) bound as {a}"
+
+
+def test_integration_notes_name_every_entry_point():
+    """INTEGRATION.md lists each declared entry point (a base name covers its _fwd/_bwd/_workspace_bytes forms)."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    for n in _declared_symbols():
+        base = re.sub(r"_(fwd|bwd)?_?workspace_bytes$", "", n)
+        assert n in text or base in text, f"{n} is not described in INTEGRATION.md"
