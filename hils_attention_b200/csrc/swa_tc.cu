@@ -50,11 +50,15 @@ __device__ __forceinline__ unsigned long long lmk_bits(const SwaTcParams& p, int
 
 // ================================================================================================
 template <int D>
-__global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, const __grid_constant__ CUtensorMap tmK,
+__global__ void __launch_bounds__(kThreads, (D == 64) ? 3 : 1) swa_fwd_tc_kernel(SwaTcParams p, const __grid_constant__ CUtensorMap tmK,
                                                               const __grid_constant__ CUtensorMap tmV) {
   constexpr int DB = D / 64;
   constexpr int QBYTES = DB * 16384;
   constexpr int KVBYTES = DB * 8192;
+  // A block's window is ~10 key tiles swept twice, so CTA prologue, pipeline fill and epilogue weigh as much
+  // as the loop: at D = 64 three CTAs share an SM (one S accumulator, one P tile, 128 TMEM columns and
+  // 65 KB of shared memory each) and hide them for one another; D = 128 double-buffers S and P instead.
+  constexpr int NSB = (D == 64) ? 1 : 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* Qs = smem;
@@ -81,7 +85,7 @@ __global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, con
     mbar_init_fence();
     abort_s = 0;
   }
-  if (warp == 4) tmem_alloc(&tmem_base_s, 256);
+  if (warp == 4) tmem_alloc(&tmem_base_s, NSB == 1 ? 128 : 256);
 
   const int r = tid, ql = r / G, g = r % G, i = q0 + ql;
   const bool is_row = tid < 128;
@@ -101,7 +105,7 @@ __global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t tS = tmem, tO = tmem + 128;
+  const uint32_t tS = tmem, tO = tmem + NSB * 64;
 
   if (warp == 5) {
     if (lane == 0) {
@@ -129,10 +133,11 @@ __global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, con
       auto issue_qk = [&](int it) {
         const int s = it & 1;
         const uint32_t kb = k_d.lo + s * (KVBYTES >> 4);
-        mma_ss_w<false>(tS + s * 64, q_d.lo, q_d.hi, kb, k_d.hi, idesc_qk);
+        const uint32_t ts = tS + (NSB == 2 ? s : 0) * 64;
+        mma_ss_w<false>(ts, q_d.lo, q_d.hi, kb, k_d.hi, idesc_qk);
 #pragma unroll
         for (int kk = 1; kk < D / 16; ++kk)
-          mma_ss_w<true>(tS + s * 64, q_d.lo + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), q_d.hi,
+          mma_ss_w<true>(ts, q_d.lo + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), q_d.hi,
                          kb + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), k_d.hi, idesc_qk);
         mma_commit(&s_full[s]);
       };
@@ -141,7 +146,7 @@ __global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, con
       for (int it = 0; ok && it < n; ++it) {
         const int s = it & 1, u = it >> 1;
         if (abort_s) break;
-        if (it + 1 < n) {
+        if (NSB == 2 && it + 1 < n) {
           ok = mbar_wait(&kv_full[(it + 1) & 1], ((it + 1) >> 1) & 1);
           if (!ok) break;
           tc_fence_after();
@@ -151,13 +156,19 @@ __global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, con
         if (!ok) break;
         tc_fence_after();
         if (it >= nt) {
-          const uint32_t a0 = p_d.lo + s * (16384 >> 4), b0 = v_d.lo + s * (KVBYTES >> 4);
+          const uint32_t a0 = p_d.lo + (NSB == 2 ? s : 0) * (16384 >> 4), b0 = v_d.lo + s * (KVBYTES >> 4);
           mma_ss_wr(tO, a0, p_d.hi, b0, v_d.hi, idesc_pv, it > nt ? 1u : 0u);
 #pragma unroll
           for (int kk = 1; kk < 4; ++kk)
             mma_ss_w<true>(tO, a0 + ((kk * 32) >> 4), p_d.hi, b0 + ((kk * 2048) >> 4), v_d.hi, idesc_pv);
         }
         mma_commit(&pv_done[s]);
+        if (NSB == 1 && it + 1 < n) {   // S was consumed before the arrival on p_full waited for above
+          ok = mbar_wait(&kv_full[(it + 1) & 1], ((it + 1) >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_qk(it + 1);
+        }
       }
       if (!ok) { abort_s = 1; atomicExch(&g_device_status, 402); }
     }
@@ -178,8 +189,8 @@ __global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, con
       if (!ok) break;
       tc_fence_after();
       float sv[64];
-      tmem_ld32(tS + lane_base + s * 64, sv);
-      tmem_ld32(tS + lane_base + s * 64 + 32, sv + 32);
+      tmem_ld32(tS + lane_base + (NSB == 2 ? s : 0) * 64, sv);
+      tmem_ld32(tS + lane_base + (NSB == 2 ? s : 0) * 64 + 32, sv + 32);
       tmem_ld_wait();
       const int a = lo - j0, e = hi - j0;
       const unsigned long long lm = lmk_bits(p, j0);
@@ -197,7 +208,7 @@ __global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, con
           part += sv[jj];
         }
         l += part;
-        store_row_bf16_sw128(Ps + s * 16384, r, sv);
+        store_row_bf16_sw128(Ps + (NSB == 2 ? s : 0) * 16384, r, sv);
       }
       fence_async_smem();
       tc_fence_before();
@@ -231,7 +242,7 @@ __global__ void __launch_bounds__(kThreads) swa_fwd_tc_kernel(SwaTcParams p, con
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, 256);
+  if (warp == 4) tmem_dealloc(tmem, NSB == 1 ? 128 : 256);
 }
 
 // Backward row arithmetic in two phases, so that the dP row can still be in flight from TMEM while the
@@ -709,7 +720,7 @@ int swa_fwd_tc_launch(const void* q, const void* k, const void* v, void* o, floa
   if (int rc = make_tmap_bf16_rows(&tmK, k, (uint64_t)B * Lk, (uint64_t)h_kv * D, (uint64_t)h_kv * D, 64)) return rc;
   if (int rc = make_tmap_bf16_rows(&tmV, v, (uint64_t)B * Lk, (uint64_t)h_kv * D, (uint64_t)h_kv * D, 64)) return rc;
   const int QB = 128 / (h_q / h_kv);
-  const size_t smem = 1024 + (size_t)(D / 64) * 16384 + 4 * (size_t)(D / 64) * 8192 + 2 * 16384;
+  const size_t smem = 1024 + (size_t)(D / 64) * 16384 + 4 * (size_t)(D / 64) * 8192 + (D == 64 ? 1 : 2) * 16384;
   dim3 grid(ceil_div(Lq, QB), h_kv, B);
   if (D == 64) {
     cudaFuncSetAttribute(swa_fwd_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
