@@ -928,6 +928,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
     if (lane == 0 && m > 0) {
       constexpr uint32_t idesc_s = idesc_bf16(128, 64, 0);
       constexpr uint32_t idesc_dkv = idesc_bf16(64, D, 1, 1);
+      // D = 64: dK and dV of a block come from ONE product of M = 128, N = 128: A = [dS^T ; (wP)^T] (the
+      // two tiles are 64-row blocks of an MN-major operand, NDS * 16 KB apart), B = [Q | dO] (64-column
+      // blocks NQ * 16 KB apart); the diagonal blocks of the 128 x 128 accumulator are dK (rows 0..63,
+      // columns 0..63) and dV (rows 64..127, columns 64..127), the off-diagonal ones are not read.  Half
+      // the MMA instructions for the same operand bytes: an instruction of this size is bound by its
+      // shared-memory reads either way.
+      constexpr bool kStacked = (D == 64);
+      constexpr uint32_t idesc_st = idesc_bf16(128, 128, 1, 1);
+      const DescWords ast_d = desc_words_sw128(smem_u32(dSs), NDS * 16384, 1024),
+                      bst_d = desc_words_sw128(smem_u32(Qs), NQ * QBYTES, 1024);
       // descriptor words built once (see the dq kernel); the Q / dO tiles are read K-major for S and dP and
       // MN-major (16 query rows per step) for dK and dV
       const DescWords q_d = desc_words_sw128(smem_u32(Qs), 16, 1024), do_d = desc_words_sw128(smem_u32(dOs), 16, 1024),
@@ -969,12 +979,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
         {
           const uint32_t dsb = ds_d.lo + sb * (16384 >> 4), pwb = pw_d.lo + sb * (16384 >> 4);
           const uint32_t qb = qmn_d.lo + sq * (QBYTES >> 4), dob = domn_d.lo + sq * (QBYTES >> 4);
-          mma_ss_wr(tdK, dsb, ds_d.hi, qb, qmn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
-          mma_ss_wr(tdV, pwb, pw_d.hi, dob, domn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
+          if (kStacked) {
+            const uint32_t a0 = ast_d.lo + sb * (16384 >> 4), b0 = bst_d.lo + sq * (QBYTES >> 4);
+            mma_ss_wr(tdK, a0, ast_d.hi, b0, bst_d.hi, idesc_st, j > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 1; kk < 8; ++kk) {   // 16 query rows per step
-            mma_ss_w<true>(tdK, dsb + ((kk * 2048) >> 4), ds_d.hi, qb + ((kk * 2048) >> 4), qmn_d.hi, idesc_dkv);
-            mma_ss_w<true>(tdV, pwb + ((kk * 2048) >> 4), pw_d.hi, dob + ((kk * 2048) >> 4), domn_d.hi, idesc_dkv);
+            for (int kk = 1; kk < 8; ++kk)   // 16 query rows per step
+              mma_ss_w<true>(tdK, a0 + ((kk * 2048) >> 4), ast_d.hi, b0 + ((kk * 2048) >> 4), bst_d.hi, idesc_st);
+          } else {
+            mma_ss_wr(tdK, dsb, ds_d.hi, qb, qmn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
+            mma_ss_wr(tdV, pwb, pw_d.hi, dob, domn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
+#pragma unroll
+            for (int kk = 1; kk < 8; ++kk) {   // 16 query rows per step
+              mma_ss_w<true>(tdK, dsb + ((kk * 2048) >> 4), ds_d.hi, qb + ((kk * 2048) >> 4), qmn_d.hi, idesc_dkv);
+              mma_ss_w<true>(tdV, pwb + ((kk * 2048) >> 4), pw_d.hi, dob + ((kk * 2048) >> 4), domn_d.hi, idesc_dkv);
+            }
           }
         }
         mma_commit(&dkv_done[s]);
@@ -1042,7 +1060,30 @@ __global__ void __launch_bounds__(kBwdThreads, 1) sparse_bwd_dkv_tc_kernel(Spars
     bf16* dkrow = static_cast<bf16*>(p.d_k_out) + (tok * p.h_kv + h) * D;
     bf16* dvrow = static_cast<bf16*>(p.d_v_out) + (tok * p.h_kv + h) * D;
     if (ok) tc_fence_after();
-    {
+    if (D == 64) {
+      // stacked accumulator (M = 128): TMEM lane = row; rows 0..63 hold dK in columns 0..63, rows 64..127 hold
+      // dV in columns 64..127.  Warps 0, 1 of a warpgroup write dK rows, warps 2, 3 dV rows; warpgroup w
+      // takes the 32-column half w.
+      const int wq = warp & 3;
+      const bool is_v = wq >= 2;
+      const int64_t tokr = (int64_t)b * p.T + (int64_t)c * 64 + 32 * (wq & 1) + lane;
+      float ov[32];
+      if (ok && m > 0) {
+        tmem_ld32(tdK + lane_base + (is_v ? 64 : 0) + wg * 32, ov);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) ov[jj] = 0.f;
+      }
+      bf16* dst = static_cast<bf16*>(is_v ? p.d_v_out : p.d_k_out) + (tokr * p.h_kv + h) * D + wg * 32;
+#pragma unroll
+      for (int c8 = 0; c8 < 4; ++c8) {
+        __nv_bfloat162 hh[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) hh[e] = __floats2bfloat162_rn(ov[c8 * 8 + 2 * e], ov[c8 * 8 + 2 * e + 1]);
+        *reinterpret_cast<uint4*>(dst + c8 * 8) = *reinterpret_cast<uint4*>(hh);
+      }
+    } else {
       const int which = wg;  // warpgroup 0 writes dK, warpgroup 1 writes dV
 #pragma unroll
       for (int cb = 0; cb < D / 32; ++cb) {
