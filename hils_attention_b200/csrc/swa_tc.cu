@@ -559,6 +559,14 @@ __global__ void __launch_bounds__(kThreads, (D == 64) ? 2 : 1) swa_bwd_dkv_tc_ke
     if (lane == 0 && m > 0) {
       constexpr uint32_t idesc_s = idesc_bf16(128, 64, 0);
       constexpr uint32_t idesc_dkv = idesc_bf16(64, D, 1, 1);
+      // D = 64: dK and dV of a block come from one product of M = 128, N = 128: A = [dS^T ; P^T] (64-row
+      // blocks of an MN-major operand, one tile apart), B = [Q | dO] (64-column blocks two stages apart);
+      // dK is the block (rows 0..63, columns 0..63) of the accumulator, dV the block (rows 64..127,
+      // columns 64..127).  Half the MMA instructions for the same operand bytes.
+      constexpr bool kStacked = (D == 64);
+      constexpr uint32_t idesc_st = idesc_bf16(128, 128, 1, 1);
+      const DescWords ast_d = desc_words_sw128(smem_u32(dSs), NDS * 16384, 1024),
+                      bst_d = desc_words_sw128(smem_u32(Qs), 2 * QBYTES, 1024);
       // descriptor words built once; the Q / dO tiles are read K-major for S and dP and MN-major for dK and dV
       const DescWords q_d = desc_words_sw128(smem_u32(Qs), 16, 1024), do_d = desc_words_sw128(smem_u32(dOs), 16, 1024),
                       k_d = desc_words_sw128(smem_u32(Ks), 16, 1024), v_d = desc_words_sw128(smem_u32(Vs), 16, 1024),
@@ -597,12 +605,20 @@ __global__ void __launch_bounds__(kThreads, (D == 64) ? 2 : 1) swa_bwd_dkv_tc_ke
         {
           const uint32_t dsb = ds_d.lo + sb * (16384 >> 4), pwb = pw_d.lo + sb * (16384 >> 4);
           const uint32_t qb = qmn_d.lo + s * (QBYTES >> 4), dob = domn_d.lo + s * (QBYTES >> 4);
-          mma_ss_wr(tdK, dsb, ds_d.hi, qb, qmn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
-          mma_ss_wr(tdV, pwb, pw_d.hi, dob, domn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
+          if (kStacked) {
+            const uint32_t a0 = ast_d.lo + sb * (16384 >> 4), b0 = bst_d.lo + s * (QBYTES >> 4);
+            mma_ss_wr(tdK, a0, ast_d.hi, b0, bst_d.hi, idesc_st, j > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 1; kk < 8; ++kk) {
-            mma_ss_w<true>(tdK, dsb + ((kk * 2048) >> 4), ds_d.hi, qb + ((kk * 2048) >> 4), qmn_d.hi, idesc_dkv);
-            mma_ss_w<true>(tdV, pwb + ((kk * 2048) >> 4), pw_d.hi, dob + ((kk * 2048) >> 4), domn_d.hi, idesc_dkv);
+            for (int kk = 1; kk < 8; ++kk)
+              mma_ss_w<true>(tdK, a0 + ((kk * 2048) >> 4), ast_d.hi, b0 + ((kk * 2048) >> 4), bst_d.hi, idesc_st);
+          } else {
+            mma_ss_wr(tdK, dsb, ds_d.hi, qb, qmn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
+            mma_ss_wr(tdV, pwb, pw_d.hi, dob, domn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
+#pragma unroll
+            for (int kk = 1; kk < 8; ++kk) {
+              mma_ss_w<true>(tdK, dsb + ((kk * 2048) >> 4), ds_d.hi, qb + ((kk * 2048) >> 4), qmn_d.hi, idesc_dkv);
+              mma_ss_w<true>(tdV, pwb + ((kk * 2048) >> 4), pw_d.hi, dob + ((kk * 2048) >> 4), domn_d.hi, idesc_dkv);
+            }
           }
         }
         mma_commit(&dkv_done[s]);
@@ -668,6 +684,24 @@ __global__ void __launch_bounds__(kThreads, (D == 64) ? 2 : 1) swa_bwd_dkv_tc_ke
     const int tokj = j_first + krow;
     const int64_t tok = (int64_t)b * L + tokj;
     if (ok) tc_fence_after();
+    if (D == 64) {
+      // stacked accumulator (M = 128): TMEM lane = row; warps 0, 1 hold the dK rows (columns 0..63), warps
+      // 2, 3 the dV rows (columns 64..127)
+      const bool is_v = warp >= 2;
+      const int tokr = j_first + 32 * (warp & 1) + lane;
+#pragma unroll
+      for (int cb = 0; cb < 2; ++cb) {
+        float ov[32];
+        if (ok && m > 0) {
+          tmem_ld32(tdK + lane_base + (is_v ? 64 : 0) + cb * 32, ov);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) ov[jj] = 0.f;
+        }
+        if (tokr < L) store32_bf16((is_v ? p.d_v : p.d_k) + (((int64_t)b * L + tokr) * p.h_kv + h) * D + cb * 32, ov);
+      }
+    } else
 #pragma unroll
     for (int which = 0; which < 2; ++which) {
 #pragma unroll
