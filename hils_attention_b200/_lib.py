@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes as C
 import os
+import threading
 from typing import Optional
 
 import torch
@@ -61,6 +62,8 @@ KERNELS_PER_CALL = {
     "hils_decode_step": 7,   # window, cast, key stream, selection, weights, sparse, combine (the 2 copies not counted)
 }
 _launches = 0
+# HILS_B200_CHECK_STATUS=1: read the device status word after every call (synchronises; for debugging)
+_CHECK_STATUS = os.environ.get("HILS_B200_CHECK_STATUS", "0") not in ("", "0")
 
 _lib: Optional[C.CDLL] = None
 
@@ -95,27 +98,69 @@ def dtype_code(t: torch.Tensor) -> int:
     raise TypeError(f"hils_b200 kernels take bfloat16 or float32 tensors, got {t.dtype}")
 
 
+# Devices of the tensors whose pointers were taken for the call being assembled (per host thread: the
+# autograd engine runs backward functions on its own threads).  ptr() records, stream() and call() check.
+_tls = threading.local()
+
+
+def _pending() -> list:
+    devs = getattr(_tls, "devs", None)
+    if devs is None:
+        devs = _tls.devs = []
+    return devs
+
+
+def _call_device() -> Optional[torch.device]:
+    """The one device all tensors of the pending call live on; raises if they disagree."""
+    devs = _pending()
+    if not devs:
+        return None
+    first = devs[0]
+    for d in devs[1:]:
+        if d != first:
+            devs.clear()
+            raise RuntimeError(f"hils_b200: tensors of one call live on different devices ({first} and {d}); "
+                               "nothing was launched")
+    return first
+
+
 def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     if t is None:
         return None
     if not t.is_cuda:
+        _pending().clear()
         raise RuntimeError("hils_b200 kernels need CUDA tensors (no CPU fallback exists)")
+    _pending().append(t.device)
     return t.data_ptr()
 
 
 def stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Current torch stream of the device the pending call's tensors live on (the kernels follow their
+    tensors, like the reference's ops, not the process-wide current device)."""
+    dev = _call_device()
+    return torch.cuda.current_stream(dev).cuda_stream
 
 
 def call(name: str, *args):
-    """Invoke a status-returning entry point and raise HilsError on failure."""
+    """Invoke a status-returning entry point and raise HilsError on failure.  The call runs with the
+    tensors' device current (tensor maps, symbol addresses and launches bind to the current context)."""
     global _launches
     lib = load()
-    rc = getattr(lib, name)(*args)
+    dev = _call_device()
+    _pending().clear()
+    if dev is not None and torch.cuda.current_device() != dev.index:
+        with torch.cuda.device(dev):
+            rc = getattr(lib, name)(*args)
+    else:
+        rc = getattr(lib, name)(*args)
     _launches += KERNELS_PER_CALL.get(name, 1)
     if rc != 0:
         msg = lib.hils_last_error().decode("utf-8", "replace")
         raise HilsError(f"{name} failed with status {rc}: {msg}")
+    if _CHECK_STATUS:
+        st = int(lib.hils_take_device_status())
+        if st != 0:
+            raise HilsError(f"{name}: a bounded device-side wait expired (status {st}); the output is incomplete")
 
 
 def query(name: str, *args) -> int:

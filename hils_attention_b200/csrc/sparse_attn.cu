@@ -114,12 +114,10 @@ extern "C" int hils_sparse_attn_bwd(const void* q, const void* k, const void* v,
       p.d_o = d_o; p.d_q = d_q; p.d_w = d_w;
       const int rc = sparse_bwd_tc_launch(p, d_k, d_v, workspace, st);
       if (rc != HILS_ERR_UNSUPPORTED) return rc;
-      // misaligned pointers: the fp32-accumulator path below needs its larger workspace
-      const size_t need2 = (size_t)B * T * h_kv * (size_t)(D + Dv) * sizeof(float);
-      if (workspace_bytes < need2) {
-        set_error("sparse_attn_bwd: tensors must be 16-byte aligned for this shape");
-        return HILS_ERR_BAD_ARG;
-      }
+      // the tensor-core path covers this shape but the pointers are not 16-byte aligned: no other kernel is
+      // sized for the tensor-core workspace, so the call is refused rather than rerouted
+      set_error("sparse_attn_bwd: tensors must be 16-byte aligned for this shape");
+      return HILS_ERR_BAD_ARG;
     }
   }
   const int64_t nk = (int64_t)B * T * h_kv * D, nv = (int64_t)B * T * h_kv * Dv;

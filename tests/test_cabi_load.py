@@ -70,9 +70,30 @@ def test_binding_table_matches_header_prototypes():
             assert a is _kind(d), f"{name}: argument {i} ({d}) bound as {a}"
 
 
-def test_integration_notes_name_every_entry_point():
-    """INTEGRATION.md lists each declared entry point (a base name covers its _fwd/_bwd/_workspace_bytes forms)."""
-    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
-    for n in _declared_symbols():
-        base = re.sub(r"_(fwd|bwd)?_?workspace_bytes$", "", n)
-        assert n in text or base in text, f"{n} is not described in INTEGRATION.md"
+class _FakeCudaTensor:
+    """Stands in for a CUDA tensor on a box without a GPU: only what _lib.ptr() reads."""
+    is_cuda = True
+
+    def __init__(self, index):
+        import torch
+        self.device = torch.device("cuda", index)
+
+    def data_ptr(self):
+        return 4096
+
+
+def test_tensors_on_different_devices_are_refused_before_any_launch():
+    """A call assembled from tensors of two devices raises on the host; nothing reaches the library."""
+    import pytest
+    from hils_attention_b200 import _lib
+    _lib._pending().clear()
+    _lib.ptr(_FakeCudaTensor(0))
+    _lib.ptr(_FakeCudaTensor(1))
+    with pytest.raises(RuntimeError, match="different devices"):
+        _lib.stream()
+    assert _lib._pending() == []
+    # one device: the call's device is that device, whatever the process-wide current device is
+    _lib.ptr(_FakeCudaTensor(1))
+    _lib.ptr(_FakeCudaTensor(1))
+    assert _lib._call_device().index == 1
+    _lib._pending().clear()
