@@ -107,9 +107,11 @@ def topk_select(q: torch.Tensor, lmks: torch.Tensor, lse_swa: torch.Tensor, topk
                 block_size: int, window_size: int, is_causal: bool = True, q_offset: int = 0,
                 drop_mask: Optional[torch.Tensor] = None, sm_scale: Optional[float] = None,
                 bias: Optional[torch.Tensor] = None, gumbel_noise: Optional[torch.Tensor] = None,
-                return_aux: bool = False):
+                return_aux: bool = False, forced_indices: Optional[torch.Tensor] = None):
     """q (B,L,h_kv,G,D); lmks (B,N,h_kv,D) shared or (B,N,h_kv*G,D) per q-head;
     lse_swa (B,L,h_q) or (B,L,h_kv,G); bias (B,N,h_q) or (B,N,h_kv,G) fp32.
+    forced_indices (B,L,h_kv,K): skip the ranking and return the scores of these ids (used to
+    compare gradients on identical selections).
 
     Returns indices (B,L,h_kv,K) int32 and scores (B,L,h_kv,G,K) = scale*q.k' (fp32,
     -inf at -1).  With return_aux also the selection logits, lse_total and ranking keys.
@@ -143,7 +145,7 @@ def topk_select(q: torch.Tensor, lmks: torch.Tensor, lse_swa: torch.Tensor, topk
     keys = torch.where(torch.isnan(keys), torch.full_like(keys, NEG_INF), keys)
     if drop_mask is not None:
         keys = keys.masked_fill(drop_mask.bool().unsqueeze(2), NEG_INF)
-    indices = stable_topk_from_keys(keys, topk)
+    indices = stable_topk_from_keys(keys, topk) if forced_indices is None else forced_indices.to(torch.int32)
     safe = indices.clamp_min(0).long().unsqueeze(3).expand(-1, -1, -1, G, -1)
     scores = torch.gather(scaled, -1, safe)
     scores = scores.masked_fill((indices < 0).unsqueeze(3).expand_as(scores), NEG_INF)
@@ -324,7 +326,7 @@ def swa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window_size: int, chu
 def hils_attention_chain(q, k, v, lmk_q, *, chunk_size: int, window_size: int, topk: int,
                          pooling: str = "attn", use_prior_bias: bool = True, softmax1: bool = False,
                          q_offset: Optional[int] = None, act_dtype: Optional[torch.dtype] = None,
-                         return_aux: bool = False):
+                         return_aux: bool = False, forced_indices: Optional[torch.Tensor] = None):
     """SWA -> chunk keys -> selection -> inter-chunk softmax -> sparse attention -> combine.
 
     q, lmk_q (B,L,h_q,D); k, v (B,T,h_kv,D) with T >= L (T > L = cached prefix).
@@ -359,7 +361,7 @@ def hils_attention_chain(q, k, v, lmk_q, *, chunk_size: int, window_size: int, t
     g_lmk = lmk_k.shape[2] // h_kv
     G = h_q // h_kv
     idx, sc = topk_select(lmk_q.reshape(B, L, h_kv, G, D), lmk_k, lse_act, topk, S, window_size,
-                          True, q_offset, bias=prior_b)
+                          True, q_offset, bias=prior_b, forced_indices=forced_indices)
     scores = sc.reshape(B, L, h_q, -1).to(dt)
     w = inter_chunk_weights(scores, idx, lse_act, prior_b, softmax1, dt)
     o_hils = sparse_attn(q, k, v, w, idx, chunk_size=S, mask_last_token=True).to(dt)
@@ -403,3 +405,126 @@ def naive_bsa_chain(q, k, v, *, chunk_size: int, window_size: int, topk: int,
     o_hils = sparse_attn(q, k, v, w[..., :topk].contiguous(), idx, chunk_size=S, sm_scale=sm_scale,
                          mask_last_token=mask_last_token)
     return o_hils + swa_o * w[..., -1:]
+
+
+# --------------------------------------------------------------------------
+# the same chain for a SAMPLE of query rows (cost O(rows * (W + N + K*S)) per head)
+# --------------------------------------------------------------------------
+def pooled_keys_for_heads(k: torch.Tensor, lmk_q: torch.Tensor, kv_heads, G: int, chunk_size: int,
+                          chunk_batch: int = 256):
+    """chunk_attn_pool over all full chunks for the listed kv heads only, in batches of chunks.
+    k (B,T,h_kv,D), lmk_q (B,T,h_q,D) (its rows at each chunk's last token are the prior queries).
+    Returns lmk_k (B,N,len(kv_heads)*G,D) in k's dtype and prior_b (B,N,len(kv_heads)*G) fp32."""
+    S = chunk_size
+    B, T, _, D = k.shape
+    N = T // S
+    hk = torch.as_tensor(list(kv_heads))
+    hq = (hk.view(-1, 1) * G + torch.arange(G).view(1, -1)).reshape(-1)
+    outs_k, outs_b = [], []
+    for c0 in range(0, N, chunk_batch):
+        c1 = min(N, c0 + chunk_batch)
+        kc = k[:, c0 * S:c1 * S][:, :, hk].reshape(B, c1 - c0, S, len(hk), D)
+        mu = lmk_q[:, S - 1::S][:, c0:c1][:, :, hq]
+        a, b = chunk_attn_pool(mu, kc.repeat_interleave(G, dim=3) if G > 1 else kc)
+        outs_k.append(a)
+        outs_b.append(b)
+    return torch.cat(outs_k, 1), torch.cat(outs_b, 1)
+
+
+def hils_attention_rows(q, k, v, lmk_q, b_idx, t_idx, kv_heads, *, chunk_size: int, window_size: int,
+                        topk: int, lmk_k: Optional[torch.Tensor] = None, prior_b: Optional[torch.Tensor] = None,
+                        softmax1: bool = False, q_offset: int = 0, act_dtype: Optional[torch.dtype] = None,
+                        forced_indices: Optional[torch.Tensor] = None):
+    """The chain of `hils_attention_chain` evaluated only for the query rows (b_idx[r], t_idx[r]) and the
+    kv heads `kv_heads` (all query heads of those groups).  q, lmk_q (B,L,h_q,D); k, v (B,T,h_kv,D), query
+    row t sits at absolute position q_offset + t.  lmk_k (B,N,len(kv_heads)*G,D) / prior_b may be passed
+    (decode against a store with cached pooled keys); otherwise they are attention-pooled from k with the
+    prior queries lmk_q[:, S-1::S] (needs T == L).  forced_indices (R,len(kv_heads),K) skips the ranking.
+    Differentiable with respect to q and lmk_q (rows' own gradient) with the pooled keys held constant.
+
+    Returns dict: o (R,Hs*G,Dv) in the activation dtype, indices (R,Hs,K) int32, scores, weights,
+    lse_swa (R,Hs*G) fp32, swa_o, o_hils.
+    """
+    S, W = chunk_size, window_size
+    B, L, h_q, D = q.shape
+    T, h_kv = k.shape[1], k.shape[2]
+    G = h_q // h_kv
+    dt = act_dtype or q.dtype
+    hk = torch.as_tensor(list(kv_heads))
+    Hs = len(hk)
+    hq = (hk.view(-1, 1) * G + torch.arange(G).view(1, -1)).reshape(-1)          # query heads, group-major
+    b_idx, t_idx = torch.as_tensor(b_idx).long(), torch.as_tensor(t_idx).long()
+    R = b_idx.numel()
+    scale = 1.0 / math.sqrt(D)
+    N = T // S
+    if lmk_k is None:
+        lmk_k, pb = pooled_keys_for_heads(k, lmk_q, kv_heads, G, S)
+        prior_b = pb if prior_b is None else prior_b
+    qr = q[b_idx, t_idx][:, hq].float()                                            # (R, Hs*G, D)
+    lr = lmk_q[b_idx, t_idx][:, hq].float()
+    tabs = t_idx + q_offset
+    # ---- sliding-window branch: keys [start, t], landmark columns dropped ---------------------
+    start = (torch.div(tabs - W + 1, S, rounding_mode="floor") * S).clamp_min(0)
+    span = W + S
+    j = start.view(R, 1) + torch.arange(span).view(1, span)                        # (R, span) absolute key ids
+    keep = (j <= tabs.view(R, 1)) & ((j + 1) % S != 0)
+    jc = j.clamp_max(T - 1)
+    kw = k[b_idx.view(R, 1), jc][:, :, hk].float()                                 # (R, span, Hs, D)
+    vw = v[b_idx.view(R, 1), jc][:, :, hk].float()
+    s = torch.einsum("rhgd,rjhd->rhgj", qr.view(R, Hs, G, D), kw) * scale
+    s = s.masked_fill(~keep.view(R, 1, 1, span), NEG_INF)
+    lse = torch.logsumexp(s, dim=-1)                                               # (R, Hs, G)
+    p = torch.exp(s - lse.unsqueeze(-1))
+    swa_o = torch.einsum("rhgj,rjhd->rhgd", p, vw).reshape(R, Hs * G, -1).to(dt)
+    lse = lse.reshape(R, Hs * G)
+    lse_act = lse.to(dt)
+    # ---- selection over all chunk keys ------------------------------------------------------------
+    g_lmk = lmk_k.shape[2] // Hs
+    lk = lmk_k[b_idx].float()                                                      # (R, N, Hs*g_lmk, D)
+    if g_lmk == G and G > 1:
+        raw = torch.einsum("rhgd,rnhgd->rhgn", lr.view(R, Hs, G, D), lk.view(R, N, Hs, G, D))
+    else:
+        raw = torch.einsum("rhgd,rnhd->rhgn", lr.view(R, Hs, G, D), lk.view(R, N, Hs, D))
+    scaled = raw * scale
+    lim = remote_chunk_limit(tabs, W, S)
+    logits = scaled.masked_fill((torch.arange(N).view(1, N) >= lim.view(R, 1)).view(R, 1, 1, N), NEG_INF)
+    if prior_b is not None:
+        logits = logits + prior_b[b_idx].float().view(R, N, Hs, G).permute(0, 2, 3, 1)
+    lse_hils = torch.logsumexp(logits, dim=-1)
+    lse_total = torch.logaddexp(lse_act.float().view(R, Hs, G), lse_hils)
+    keys = (logits - lse_total.unsqueeze(-1)).max(dim=2).values                    # (R, Hs, N)
+    keys = torch.where(torch.isnan(keys), torch.full_like(keys, NEG_INF), keys)
+    idx = stable_topk_from_keys(keys, topk) if forced_indices is None else forced_indices.to(torch.int32)
+    safe = idx.clamp_min(0).long().unsqueeze(2).expand(-1, -1, G, -1)
+    sc = torch.gather(scaled, -1, safe).masked_fill((idx < 0).unsqueeze(2).expand(-1, -1, G, -1), NEG_INF)
+    scores = sc.reshape(R, Hs * G, -1).to(dt)
+    # ---- inter-chunk softmax ----------------------------------------------------------------------
+    z = scores
+    if prior_b is not None:
+        pbr = prior_b[b_idx].float().view(R, N, Hs * G).permute(0, 2, 1)           # (R, Hs*G, N)
+        z = z + torch.gather(pbr, -1, idx.repeat_interleave(G, dim=1).clamp_min(0).long()).to(z.dtype)
+    cols = [z, lse_act.unsqueeze(-1)]
+    if softmax1:
+        cols.append(torch.zeros(R, Hs * G, 1, dtype=z.dtype))
+    w = F.softmax(torch.cat(cols, dim=-1), dim=-1).to(dt)
+    # ---- sparse chunk attention: one softmax per selected chunk, last key of the chunk masked -------
+    Kk = idx.shape[-1]
+    o_h = torch.zeros(R, Hs, G, v.shape[-1], dtype=torch.float32)
+    ar = torch.arange(S)
+    for kk in range(Kk):
+        c = idx[:, :, kk].long()                                                   # (R, Hs)
+        valid = c >= 0
+        rows_k = (c.clamp_min(0) * S).unsqueeze(-1) + ar.view(1, 1, S)             # (R, Hs, S) token ids
+        kc = k[b_idx.view(R, 1, 1), rows_k, hk.view(1, Hs, 1)].float()             # (R, Hs, S, D)
+        vc = v[b_idx.view(R, 1, 1), rows_k, hk.view(1, Hs, 1)].float()
+        sk = torch.einsum("rhgd,rhsd->rhgs", qr.view(R, Hs, G, D), kc) * scale
+        sk = torch.cat([sk[..., :-1], torch.full_like(sk[..., -1:], NEG_INF)], dim=-1)
+        pk = torch.softmax(sk, dim=-1)
+        ok = torch.einsum("rhgs,rhsd->rhgd", pk, vc)
+        wk = w[..., kk].float().view(R, Hs, G) * valid.unsqueeze(-1).float()
+        o_h = o_h + ok * wk.unsqueeze(-1)
+    o_hils = o_h.reshape(R, Hs * G, -1).to(dt)
+    w_swa = w[..., -2 if softmax1 else -1]
+    o = torch.addcmul(o_hils, swa_o, w_swa.unsqueeze(-1))
+    return {"o": o, "indices": idx, "scores": scores, "weights": w, "lse_swa": lse, "swa_o": swa_o,
+            "o_hils": o_hils, "keys": keys, "lse_total": lse_total, "query_heads": hq}
