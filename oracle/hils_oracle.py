@@ -232,7 +232,9 @@ def sparse_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, weights: torc
     o = torch.zeros(B, L, H, G, Dv, dtype=torch.float32)
     bidx = torch.arange(B).view(B, 1, 1)
     hidx = torch.arange(H).view(1, 1, H)
-    for kk in range(K):
+    dist = ((S - 2) - torch.arange(S, dtype=torch.float32)).clamp(min=0)
+
+    def slot(kk, qf, kc, vc, wf):
         ids = indices[..., kk].long()                          # (B,L,H)
         valid = ids >= 0
         safe = ids.clamp_min(0)
@@ -240,7 +242,6 @@ def sparse_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, weights: torc
         vsel = vc[bidx, safe, :, hidx]
         s = torch.einsum("blhgd,blhsd->blhgs", qf, ksel)
         if slope is not None:
-            dist = ((S - 2) - torch.arange(S, dtype=torch.float32)).clamp(min=0)
             s = s - slope.float().view(1, 1, H, G, 1) * dist.view(1, 1, 1, 1, S)
         s = s * float(sm_scale)
         if mask_last_token:
@@ -248,7 +249,18 @@ def sparse_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, weights: torc
         p = torch.softmax(s, dim=-1)
         ok = torch.einsum("blhgs,blhsd->blhgd", p, vsel)
         wk = wf[..., kk] * valid.unsqueeze(-1).float()
-        o = o + ok * wk.unsqueeze(-1)
+        return ok * wk.unsqueeze(-1)
+
+    # with gradients on, a slot's gathered K/V tiles (B*L*H*S*D each) would be kept for all K slots; beyond
+    # ~2 GB the slots are recomputed in the backward pass instead
+    recompute = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, weights)) and \
+        2 * B * L * H * S * max(D, Dv) * 4 * K > (2 << 30)
+    for kk in range(K):
+        if recompute:
+            from torch.utils.checkpoint import checkpoint
+            o = o + checkpoint(slot, kk, qf, kc, vc, wf, use_reentrant=False)
+        else:
+            o = o + slot(kk, qf, kc, vc, wf)
     return o.reshape(B, L, HQ, Dv)
 
 

@@ -30,8 +30,8 @@ def test_pool_golden(ops, tag, dtype):
     check(lk, g["lmk_k"], dtype, "lmk_k")
     check(lb, g["lmk_b"], F32 if dtype == F32 else BF, "lmk_b")
     (lk.float() * cuda(g["g_lmk_k"])).sum().add((lb * cuda(g["g_lmk_b"])).sum()).backward()
-    check(mu.grad, g["d_mu_q"], dtype, "d_mu_q", scale=3.0)
-    check(kc.grad, g["d_k"], dtype, "d_k", scale=3.0)
+    check(mu.grad, g["d_mu_q"], dtype, "d_mu_q")
+    check(kc.grad, g["d_k"], dtype, "d_k")
 
 
 @pytest.mark.parametrize("shape", [(1, 64, 2, 128, 64), (2, 128, 4, 128, 64), (4, 256, 2, 128, 64),
@@ -82,8 +82,8 @@ def test_pool_gqa_backward_and_mean_backward(ops):
     mu, kc = mu0.cuda().requires_grad_(True), kc0.cuda().requires_grad_(True)
     lk, lb = ops.chunk_attn_pool(mu, kc)
     ((lk * gk.cuda()).sum() + (lb * gb.cuda()).sum() + (ops.chunk_mean_pool(kc) * gk[:, :, ::G].cuda()).sum()).backward()
-    check(mu.grad, mu_r.grad, F32, "gqa d_mu", scale=3.0)
-    check(kc.grad, kc_r.grad, F32, "gqa d_k", scale=3.0)
+    check(mu.grad, mu_r.grad, F32, "gqa d_mu")
+    check(kc.grad, kc_r.grad, F32, "gqa d_k")
 
 
 def test_pool_errors(ops):
@@ -119,7 +119,7 @@ def test_topk_golden(ops, tag, dtype):
     check(sc.view(B, L, h_kv, G, K), g["scores"], dtype, "scores")
     _, _, oaux = orc.topk_select(g["q"], g["lmks"], g["lse_swa"], K, S, W, True, qo, bias=g.get("bias"),
                                  gumbel_noise=g.get("gumbel"), return_aux=True)
-    check(aux["lse_total"], oaux["lse_total"], F32, "lse_total", scale=10.0)
+    check(aux["lse_total"], oaux["lse_total"], F32, "lse_total")
 
 
 @pytest.mark.parametrize("cfg", [(2, 1000, 2, 8, 64, 16, 64, 64), (1, 1024, 4, 1, 128, 32, 64, 512),
@@ -140,7 +140,7 @@ def test_topk_selector_exact_and_match_rate(ops, cfg):
     keys = aux["rank_keys"].cpu()
     assert torch.equal(idx.cpu(), orc.stable_topk_from_keys(keys, K))
     ridx, rsc, raux = orc.topk_select(q, lm, lse, K, S, W, True, 0, bias=bias, return_aux=True)
-    check(keys, raux["keys"], F32, "rank keys", scale=20.0)
+    check(keys, raux["keys"], F32, "rank keys")
     match = (idx.cpu() == ridx).float().mean().item()
     assert match >= 0.99, match
     same = (idx.cpu() == ridx).all(-1)
@@ -177,8 +177,8 @@ def test_topk_tensor_core_scores_path(ops, cfg):
     assert torch.equal(idx.cpu(), orc.stable_topk_from_keys(keys, K))
     ridx, rsc, raux = orc.topk_select(q, lm, lse, K, S, W, True, 0, bias=bias, drop_mask=drop, gumbel_noise=gum,
                                       return_aux=True)
-    check(keys, raux["keys"], F32, "rank keys", scale=20.0)
-    check(aux["lse_total"], raux["lse_total"], F32, "lse_total", scale=20.0)
+    check(keys, raux["keys"], F32, "rank keys")
+    check(aux["lse_total"], raux["lse_total"], F32, "lse_total")
     assert (idx.cpu() == ridx).float().mean().item() >= 0.99
     same = (idx.cpu() == ridx).all(-1)
     check(sc.view(B, L, h_kv, G, K)[same], rsc[same], BF, "scores")
@@ -228,8 +228,8 @@ def test_topk_drop_mask_and_backward(ops):
     sel = lr[0][ridx[0].clamp_min(0).long(), torch.arange(h_kv).view(1, h_kv, 1)]          # (L,h_kv,K,D)
     s = torch.einsum("lhgd,lhkd->lhgk", qr[0].view(L, h_kv, G, D), sel) / math.sqrt(D)
     (s.reshape(1, L, h_kv * G, K).masked_fill(~valid.cpu(), 0.0) * gs).sum().backward()
-    check(q.grad, qr.grad, F32, "dq", scale=5.0)
-    check(lm.grad, lr.grad, F32, "dlmk", scale=50.0)
+    check(q.grad, qr.grad, F32, "dq")
+    check(lm.grad, lr.grad, F32, "dlmk")
 
 
 # ------------------------------------------------------------------ sparse attention
@@ -251,9 +251,8 @@ def test_sparse_golden(ops, tag, dtype):
                               dtype="float" if dtype == F32 else "bfloat16")
     check(o, ref["o"], dtype, "o")
     o.backward(cuda(g["do"], dtype))
-    sc = {"dq": 5.0, "dk": 10.0, "dv": 10.0, "dw": 5.0}
     for n, t in (("dq", q), ("dk", k), ("dv", v), ("dw", w)):
-        check(t.grad, ref[n], dtype, n, scale=sc[n])
+        check(t.grad, ref[n], dtype, n)
         assert rms_ratio(t.grad, ref[n]) < (5e-3 if dtype == F32 else 2e-2), n
 
 
@@ -289,14 +288,14 @@ def test_logz_golden_and_backward(ops, tag, dtype):
     qr, kr = q.detach().float().cpu().requires_grad_(True), k.detach().float().cpu().requires_grad_(True)
     ref = orc.exact_chunk_log_z(qr, kr, chunk_size=S, window_size=W)
     if dtype == F32:
-        check(lz, g["log_z"], F32, "log_z vs reference", scale=10.0)
-    check(lz, ref, F32 if dtype == F32 else BF, "log_z", scale=10.0 if dtype == F32 else 1.0)
+        check(lz, g["log_z"], F32, "log_z vs reference")
+    check(lz, ref, F32 if dtype == F32 else BF, "log_z")
     gz = torch.randn(ref.shape, generator=torch.Generator().manual_seed(1))
     fin = torch.isfinite(ref)
     (ref.masked_fill(~fin, 0.0) * gz).sum().backward()
     (lz.masked_fill(~fin.cuda(), 0.0) * gz.cuda()).sum().backward()
-    check(q.grad, qr.grad, dtype, "dq", scale=20.0)
-    check(k.grad, kr.grad, dtype, "dk", scale=20.0)
+    check(q.grad, qr.grad, dtype, "dq")
+    check(k.grad, kr.grad, dtype, "dk")
 
 
 def test_logz_mask_lmk_forward_only(ops):
@@ -305,7 +304,7 @@ def test_logz_mask_lmk_forward_only(ops):
     k = torch.randn(1, 200, 2, 32, generator=g)
     qg = q.cuda().requires_grad_(True)
     lz = ops.exact_chunk_log_z_tl(qg, k.cuda(), chunk_size=32, window_size=64, mask_lmk=True)
-    check(lz, orc.exact_chunk_log_z(q, k, chunk_size=32, window_size=64, mask_lmk=True), F32, "logz lmk", scale=10.0)
+    check(lz, orc.exact_chunk_log_z(q, k, chunk_size=32, window_size=64, mask_lmk=True), F32, "logz lmk")
     with pytest.raises(NotImplementedError):
         lz[torch.isfinite(lz)].sum().backward()
 
@@ -355,7 +354,7 @@ def test_swa_forward_backward(ops, case, dtype):
     ((o_r * do).sum() + (lse_r.masked_fill(~fin, 0.0) * dl).sum()).backward()
     ((o.float() * do.cuda()).sum() + (lse.masked_fill(~fin.cuda(), 0.0) * dl.cuda()).sum()).backward()
     for n, t, r in (("dq", q, qr), ("dk", k, kr), ("dv", v, vr)):
-        check(t.grad, r.grad, dtype, "swa " + n, scale=10.0)
+        check(t.grad, r.grad, dtype, "swa " + n)
     from hils_attention_b200 import _lib
     assert _lib.load().hils_take_device_status() == 0
 
@@ -391,7 +390,7 @@ def test_naive_bsa_identity_on_gpu(ops, tag):
     o_h = ops.HiLS_block_M_head(q, k, v, w.contiguous(), idx, block_size=S, mask_last_token=bool(ml),
                                 is_training=False, dtype="float")
     o = torch.addcmul(o_h, swa_o, w[..., -1:])
-    check(o, g["o"], F32, "naive bsa", scale=2.0)
+    check(o, g["o"], F32, "naive bsa")
 
 
 @pytest.mark.parametrize("cfg", [
@@ -427,8 +426,8 @@ def test_topk_backward_bf16_tensor_core_path(ops, cfg):
     qv = qr.view(B, L, h_kv, G, D)
     s = torch.einsum("blhgd,blhkgd->blhgk", qv, sel.expand(-1, -1, -1, -1, G, -1)) / math.sqrt(D)
     (s.reshape(B, L, h_kv * G, K).masked_fill(~valid.cpu(), 0.0) * gs.float()).sum().backward()
-    check(q.grad, qr.grad, BF, "dq", scale=float(qr.grad.abs().max()))
-    check(lm.grad, lr.grad, BF, "dlmk", scale=float(lr.grad.abs().max()))
+    check(q.grad, qr.grad, BF, "dq")
+    check(lm.grad, lr.grad, BF, "dlmk")
 
 
 @pytest.mark.parametrize("cfg", [
@@ -454,11 +453,11 @@ def test_topk_decode_kernel(ops, cfg):
     keys = aux["rank_keys"].cpu()
     assert torch.equal(idx.cpu(), orc.stable_topk_from_keys(keys, K))
     ridx, rsc, raux = orc.topk_select(q.float(), lm.float(), lse, K, S, W, True, q_offset, bias=bias, return_aux=True)
-    check(keys, raux["keys"], F32, "rank keys", scale=50.0)
-    check(aux["lse_total"], raux["lse_total"], F32, "lse_total", scale=50.0)
-    assert (idx.cpu() == ridx).float().mean().item() >= 0.97
+    check(keys, raux["keys"], F32, "rank keys")
+    check(aux["lse_total"], raux["lse_total"], F32, "lse_total")
+    assert (idx.cpu() == ridx).float().mean().item() >= 0.99
     same = (idx.cpu() == ridx).all(-1)
-    check(sc.view(B, L, h_kv, G, K)[same], rsc[same], dtype, "scores", scale=(1.0 if dtype == BF else 50.0))
+    check(sc.view(B, L, h_kv, G, K)[same], rsc[same], dtype, "scores")
 
 
 @pytest.mark.parametrize("cfg", [(2, 1, 640, 2, 2, 64, 8), (1, 3, 512, 1, 4, 128, 4)])
@@ -476,7 +475,7 @@ def test_sparse_decode_kernel_fp32(ops, cfg):
     ref = orc.sparse_attn(q, k, v, w, idx, chunk_size=S, mask_last_token=True)
     o = ops.HiLS_block_M_head(q.cuda(), k.cuda(), v.cuda(), w.cuda(), idx.cuda(), block_size=S, is_training=False,
                               dtype="float")
-    check(o, ref, F32, "sparse decode", scale=5.0)
+    check(o, ref, F32, "sparse decode")
 
 
 # ------------------------------------------------------------------ inter-chunk softmax, branch combination
@@ -513,7 +512,7 @@ def test_inter_chunk_softmax(ops, cfg):
     check(w, wr, dtype, "weights")
     check(sc.grad, scr.grad, dtype, "d_scores")
     check(lse.grad, lser.grad, dtype, "d_lse")
-    check(pb.grad, pbr.grad, dtype, "d_prior_b", scale=4.0)
+    check(pb.grad, pbr.grad, dtype, "d_prior_b")
     # without a prior bias
     w2 = ops.inter_chunk_softmax(sc0.cuda(), idx.cuda(), lse0.cuda(), None, sm1)
     check(w2, orc.inter_chunk_weights(sc0, idx, lse0, None, softmax1=sm1), dtype, "weights (no bias)")
@@ -541,7 +540,7 @@ def test_sparse_attn_combine_matches_separate_ops(ops, dtype):
         o.backward(do)
         outs.append([o.detach()] + [t.grad for t in (q, k, v, w, so)])
     for a, b, n in zip(outs[0], outs[1], ("o", "dq", "dk", "dv", "dw", "d_swa_o")):
-        check(a, b, dtype, n, scale=2.0 if n == "dw" else 1.0)
+        check(a, b, dtype, n)
 
 
 # ------------------------------------------------------------------ per-head RMSNorm + rotary embedding
@@ -557,8 +556,8 @@ def test_norm_rope_golden(ops, tag):
     assert out.dtype == dt
     check(out, g["out"], dt, "norm+rope")
     out.backward(cuda(g["do"], dt))
-    check(x.grad, g["dx"], dt, "dx", scale=3.0)
-    check(w.grad, g["dw"], dt, "dw", scale=30.0)
+    check(x.grad, g["dx"], dt, "dx")
+    check(w.grad, g["dw"], dt, "dw")
     check(ops.rmsnorm_rope(x.detach(), w.detach()), g["out_norm_only"], dt, "norm only")
     check(ops.single_tensor_rope_autograd(x.detach(), cos, sin), g["out_rope_only"], dt, "rope only")
     qo, ko = ops.rope_rotary_pos_emb(x.detach(), x.detach()[:, :, :1].contiguous(), cos, sin)
@@ -568,4 +567,4 @@ def test_norm_rope_golden(ops, tag):
     xr = x.detach().clone().requires_grad_(True)
     ops.single_tensor_rope_autograd(xr, cos.float(), sin.float()).backward(
         ops.single_tensor_rope_autograd(x.detach(), cos.float(), sin.float()))
-    check(xr.grad, x.detach(), dt, "rope^T rope = id", scale=2.0)
+    check(xr.grad, x.detach(), dt, "rope^T rope = id")

@@ -51,7 +51,7 @@ def test_tc_forward_matches_oracle(cfg):
     ref = orc.sparse_attn(q, k, v, w, idx, chunk_size=64, mask_last_token=True)
     o = hb.HiLS_block_M_head(q.cuda(), k.cuda(), v.cuda(), w.cuda(), idx.cuda(), block_size=64, is_training=False)
     assert _lib.load().hils_take_device_status() == 0
-    check(o, ref, BF, "tc forward", scale=2.0)
+    check(o, ref, BF, "tc forward")
 
 
 def test_tc_forward_slope_and_no_last_mask():
@@ -61,7 +61,7 @@ def test_tc_forward_slope_and_no_last_mask():
     ref = orc.sparse_attn(q, k, v, w, idx, chunk_size=64, mask_last_token=False, slope=slope)
     o = hb.HiLS_block_M_head(q.cuda(), k.cuda(), v.cuda(), w.cuda(), idx.cuda(), block_size=64,
                              mask_last_token=False, is_training=False, slope=slope.cuda())
-    check(o, ref, BF, "tc forward slope", scale=2.0)
+    check(o, ref, BF, "tc forward slope")
 
 
 def test_tc_forward_is_deterministic():
@@ -94,11 +94,10 @@ def test_tc_backward_matches_oracle(cfg):
     o = hb.HiLS_block_M_head(qd, kd, vd, wd, idx.cuda(), block_size=64)
     o.backward(do.cuda())
     assert _lib.load().hils_take_device_status() == 0
-    check(o, ref, BF, "o", scale=2.0)
+    check(o, ref, BF, "o")
     # gradients sum up to K*64 bf16-rounded products per element: compare at the size of the tensor
     for name, a, r in (("dq", qd, qr), ("dk", kd, kr), ("dv", vd, vr), ("dw", wd, wr)):
-        mag = float(r.grad.abs().max())
-        check(a.grad, r.grad, BF, name, scale=max(1.0, mag))
+        check(a.grad, r.grad, BF, name)
         err = (a.grad.float().cpu() - r.grad).square().mean().sqrt() / r.grad.square().mean().sqrt().clamp_min(1e-20)
         assert float(err) < 2e-2, (name, float(err))
     assert float(wd.grad[..., K:].float().abs().max()) == 0.0

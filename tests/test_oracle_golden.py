@@ -118,3 +118,33 @@ def test_norm_rope_matches_reference(tag):
     assert torch.equal(orc.rmsnorm_rope(x, w, 1e-6, cos, sin).float(), g["out"])
     assert torch.equal(orc.rmsnorm_rope(x, w, 1e-6).float(), g["out_norm_only"])
     assert torch.equal(orc.rmsnorm_rope(x, None, 1e-6, cos, sin).float(), g["out_rope_only"])
+
+
+@pytest.mark.parametrize("cfg", [(2, 512, 4, 4, 32, 32, 64, 4), (1, 640, 8, 2, 32, 64, 128, 4)])
+def test_sampled_rows_oracle_equals_full_chain(cfg):
+    """hils_attention_rows (the chain for a sample of query rows, used at the benchmark shapes) reproduces
+    the full oracle chain on those rows: ids exactly, outputs and weights to fp32 rounding."""
+    from oracle import hils_oracle as orc
+    B, L, hq, hk, D, S, W, K = cfg
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(B, L, hq, D, generator=g)
+    k, v = (torch.randn(B, L, hk, D, generator=g) for _ in range(2))
+    ref, aux = orc.hils_attention_chain(q, k, v, q, chunk_size=S, window_size=W, topk=K, return_aux=True)
+    b = torch.randint(0, B, (48,), generator=g)
+    t = torch.randint(0, L, (48,), generator=g)
+    heads = list(range(hk)) if hk < 4 else [1, 3]
+    out = orc.hils_attention_rows(q, k, v, q, b, t, heads, chunk_size=S, window_size=W, topk=K)
+    hq_sel = out["query_heads"]
+    assert torch.equal(out["indices"], aux["indices"][b, t][:, heads])
+    assert (out["o"] - ref[b, t][:, hq_sel]).abs().max() < 2e-6
+    assert (out["weights"] - aux["weights"][b, t][:, hq_sel]).abs().max() < 2e-6
+    # forced ids reproduce the same result and carry a gradient to the sampled rows only
+    qf = q.clone().requires_grad_(True)
+    out2 = orc.hils_attention_rows(qf, k, v, q, b, t, heads, chunk_size=S, window_size=W, topk=K,
+                                   forced_indices=out["indices"])
+    assert (out2["o"] - out["o"]).abs().max() < 2e-6
+    out2["o"].sum().backward()
+    touched = qf.grad.abs().sum((2, 3)) > 0
+    mask = torch.zeros(B, L, dtype=torch.bool)
+    mask[b, t] = True
+    assert torch.equal(touched & ~mask, torch.zeros_like(mask))

@@ -43,7 +43,7 @@ def test_noalloc_matches_allocating_entry_point_twice(dtype):
              B, L, N, h_kv, G, D, K, 0, scale, dt, stream())
         torch.cuda.synchronize()
         assert torch.equal(dq, dq_ref)                       # dq has no accumulation order
-        check(dl, dl_ref, dtype, f"d_lmks (call {rep})", scale=float(dl_ref.float().abs().max()))
+        check(dl, dl_ref, dtype, f"d_lmks (call {rep})")
     assert _lib.load().hils_topk_bwd_noalloc_max_elems() == 1 << 20
 
 
