@@ -9,7 +9,10 @@ import torch
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 # tolerances of the parity contract: bf16 max-abs 2e-2 / max-rel 1e-2, fp32 1e-4
-TOL = {torch.bfloat16: (2e-2, 1e-2), torch.float32: (1e-4, 1e-4)}
+CONTRACT = {torch.bfloat16: (2e-2, 1e-2), torch.float32: (1e-4, 1e-4)}
+# what the tests enforce: half the contract in bf16 and a tenth of it in fp32 (the worst error observed over the
+# whole suite is 0.46 of the bf16 bound below and 0.12 of the fp32 one)
+TOL = {torch.bfloat16: (1e-2, 5e-3), torch.float32: (1e-5, 1e-5)}
 
 
 def golden(name):
@@ -37,7 +40,7 @@ def check(x, ref, dtype, what="", scale=None):
 
         |x - ref| <= atol * s + rtol * |ref|   elementwise,   s = max(1, max|ref|) over the tensor
 
-    with (atol, rtol) = (2e-2, 1e-2) for bf16 and (1e-4, 1e-4) for fp32.  Outputs of the path are O(1), where
+    with (atol, rtol) = TOL[dtype], tighter than the contract's (2e-2, 1e-2) for bf16 and 1e-4 for fp32.  Outputs of the path are O(1), where
     this is the contract's max-abs / max-rel bound as it stands; gradients are sums over thousands of products
     and can be much larger than 1, where the absolute part is taken relative to the tensor's largest entry.
     `scale`, where a test passes it, multiplies s and is stated with its reason at the call.
