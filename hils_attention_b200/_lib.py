@@ -55,7 +55,7 @@ SIGNATURES = {
 # kernels each entry point launches (memsets excluded); used to report launch counts
 KERNELS_PER_CALL = {
     "hils_pool_fwd": 1, "hils_pool_bwd": 1, "hils_meanpool_fwd": 1, "hils_meanpool_bwd": 1,
-    "hils_topk_fwd": 1, "hils_topk_bwd": 2, "hils_topk_bwd_noalloc": 2, "hils_sparse_attn_fwd": 1, "hils_sparse_attn_bwd": 3,
+    "hils_topk_fwd": 1, "hils_topk_bwd": 2, "hils_topk_bwd_noalloc": 2, "hils_sparse_attn_fwd": 6, "hils_sparse_attn_bwd": 6,
     "hils_chunk_logz_fwd": 1, "hils_chunk_logz_bwd": 2, "hils_swa_fwd": 1, "hils_swa_bwd": 2,
     "hils_chunk_weights_fwd": 1, "hils_chunk_weights_bwd": 1, "hils_combine_fwd": 1, "hils_combine_bwd": 1,
     "hils_norm_rope_fwd": 1, "hils_norm_rope_bwd": 1,

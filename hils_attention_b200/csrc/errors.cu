@@ -24,6 +24,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 namespace hils {
 int take_status_sparse_tc();
 int take_status_swa_tc();
+int take_status_sparse_cm();
 }  // namespace hils
 
 extern "C" int hils_version(void) { return 100; }
@@ -33,7 +34,8 @@ extern "C" int hils_version(void) { return 100; }
 extern "C" int hils_take_device_status(void) {
   const int a = hils::take_status_sparse_tc();
   const int b = hils::take_status_swa_tc();
-  if (a < 0 || b < 0) return -1;
-  return a != 0 ? a : b;
+  const int c = hils::take_status_sparse_cm();
+  if (a < 0 || b < 0 || c < 0) return -1;
+  return a != 0 ? a : (b != 0 ? b : c);
 }
 extern "C" const char* hils_last_error(void) { return hils::g_err; }

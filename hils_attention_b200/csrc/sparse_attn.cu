@@ -4,11 +4,15 @@
 namespace hils {
 
 int sparse_fwd_tc_launch(const SparseParams& p, cudaStream_t st);  // sparse_attn_tc.cu
+size_t sparse_fwd_cm_workspace(const SparseParams& p);             // sparse_attn_cm.cu
+int sparse_fwd_cm_launch(const SparseParams& p, void* workspace, cudaStream_t st);
 size_t sparse_bwd_tc_workspace(const SparseParams& p);
 int sparse_decode_launch(const void* q, const void* k, const void* v, const void* w, const int32_t* idx, const float* slope,
                          void* o, int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights, int S,
                          float scale, int mask_last, int dtype, cudaStream_t st);  // decode_attn.cu
 int sparse_bwd_tc_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st);
+size_t sparse_bwd_cm_workspace(const SparseParams& p);             // sparse_attn_cm.cu
+int sparse_bwd_cm_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st);
 
 static int check_sparse(int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights,
                         int chunk_size, int dtype) {
@@ -40,7 +44,11 @@ using namespace hils;
 
 extern "C" size_t hils_sparse_attn_fwd_workspace_bytes(int B, int L, int T, int h_q, int h_kv, int D, int Dv,
                                                        int K, int chunk_size, int dtype) {
-  (void)B; (void)L; (void)T; (void)h_q; (void)h_kv; (void)D; (void)Dv; (void)K; (void)chunk_size; (void)dtype;
+  if (dtype == HILS_BF16 && h_q > 0 && h_kv > 0 && h_q % h_kv == 0 && L > 4) {
+    SparseParams p = make_params(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, B, L, T, h_q, h_kv, D, Dv, K, K,
+                                 chunk_size, 1.f, 1);
+    return sparse_fwd_cm_workspace(p);   // inverse index + fp32 output accumulator of the chunk-major kernel
+  }
   return 0;
 }
 
@@ -49,6 +57,8 @@ extern "C" size_t hils_sparse_attn_bwd_workspace_bytes(int B, int L, int T, int 
   if (dtype == HILS_BF16 && h_q > 0 && h_kv > 0 && h_q % h_kv == 0) {
     SparseParams p = make_params(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, B, L, T, h_q, h_kv, D, Dv, K, K,
                                  chunk_size, 1.f, 1);
+    const size_t cm = sparse_bwd_cm_workspace(p);
+    if (cm > 0) return cm;
     const size_t tc = sparse_bwd_tc_workspace(p);
     if (tc > 0) return tc;
   }
@@ -60,7 +70,6 @@ extern "C" int hils_sparse_attn_fwd(const void* q, const void* k, const void* v,
                                     int h_q, int h_kv, int D, int Dv, int K, int num_weights, int chunk_size,
                                     float sm_scale, int mask_last_token, int dtype, void* workspace,
                                     size_t workspace_bytes, void* stream) {
-  (void)workspace; (void)workspace_bytes;
   if (int rc = check_sparse(B, L, T, h_q, h_kv, D, Dv, K, num_weights, chunk_size, dtype)) return rc;
   if (L == 0) return HILS_OK;
   HILS_REQUIRE(q && weights && indices && o, "sparse_attn_fwd: null pointer");
@@ -74,7 +83,16 @@ extern "C" int hils_sparse_attn_fwd(const void* q, const void* k, const void* v,
                                         chunk_size, sm_scale, mask_last_token, dtype, st);
     if (rc != HILS_ERR_UNSUPPORTED) return rc;
   }
-  if (dtype == HILS_BF16) {  // tensor-core path for the shapes it covers
+  if (dtype == HILS_BF16) {  // tensor-core paths for the shapes they cover
+    const size_t need = L > 4 ? sparse_fwd_cm_workspace(p) : 0;
+    if (need > 0) {
+      if (!workspace || workspace_bytes < need) {
+        set_error("sparse_attn_fwd: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+        return HILS_ERR_WORKSPACE;
+      }
+      const int rc = sparse_fwd_cm_launch(p, workspace, st);
+      if (rc != HILS_ERR_UNSUPPORTED) return rc;
+    }
     const int rc = sparse_fwd_tc_launch(p, st);
     if (rc != HILS_ERR_UNSUPPORTED) return rc;
   }
@@ -109,10 +127,11 @@ extern "C" int hils_sparse_attn_bwd(const void* q, const void* k, const void* v,
   if (dtype == HILS_BF16 && L > 0) {  // tensor-core path for the shapes it covers
     SparseParams p = make_params(q, k, v, weights, indices, slope, B, L, T, h_q, h_kv, D, Dv, K, num_weights,
                                  chunk_size, sm_scale, mask_last_token);
-    if (sparse_bwd_tc_workspace(p) > 0) {
+    const bool cm = sparse_bwd_cm_workspace(p) > 0;
+    if (cm || sparse_bwd_tc_workspace(p) > 0) {
       HILS_REQUIRE(q && k && v && weights && indices && d_o && d_q && d_k && d_v && d_w, "sparse_attn_bwd: null pointer");
       p.d_o = d_o; p.d_q = d_q; p.d_w = d_w;
-      const int rc = sparse_bwd_tc_launch(p, d_k, d_v, workspace, st);
+      const int rc = cm ? sparse_bwd_cm_launch(p, d_k, d_v, workspace, st) : sparse_bwd_tc_launch(p, d_k, d_v, workspace, st);
       if (rc != HILS_ERR_UNSUPPORTED) return rc;
       // the tensor-core path covers this shape but the pointers are not 16-byte aligned: no other kernel is
       // sized for the tensor-core workspace, so the call is refused rather than rerouted

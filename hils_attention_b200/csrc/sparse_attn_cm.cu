@@ -1,0 +1,959 @@
+// Sparse chunk attention, chunk-major over gathered owner rows (tcgen05 + TMEM + TMA), bf16.
+//
+// Every selected chunk has its own softmax (ops/hils_fwd_bwd_head.py:404-485), so the (token, slot) pairs of
+// one chunk can be processed together wherever their tokens sit in the sequence.  An inverse index lists, per
+// (batch, kv head, chunk), the pairs that selected the chunk.  One CTA owns one chunk: its K and V tiles
+// [64 x D] are loaded once by TMA, and the chunk's owner rows are walked in tiles of 128 rows
+// (128/G pairs x the G query heads of the group):
+//   producer warps : gather the 128 query rows of the tile with 16-byte cp.async into a swizzled A tile
+//   MMA warp       : S = Q K^T (tcgen05.mma, accumulator in TMEM), later O = P V
+//   row warpgroups : one thread per row: P = w * softmax(scale S) -> shared memory (A operand of P V);
+//                    then the O tile is read from TMEM and added to the fp32 output accumulator of each
+//                    row's token with red.global.add (no two rows of a tile share a token)
+// Every MMA row is a real (token, slot) pair: nothing is masked, whatever the overlap between neighbouring
+// tokens' selections.  The price is the scatter: the partial outputs of a token's K slots meet in an fp32
+// accumulator in global memory (L2-resident per head), which a last pass rounds to bf16.
+// All mbarrier waits are bounded; on expiry a status word is set, every role leaves its loop and the CTA
+// releases its TMEM and returns.
+#include "sparse_attn_generic.cuh"
+#include "umma.cuh"
+#include "tc_rows.cuh"
+
+namespace hils {
+
+using namespace umma;
+
+static __device__ int g_cm_status = 0;
+
+// Bounded wait of this file's kernels: 2^20 polls (tens of milliseconds; a healthy wait lasts microseconds).
+// After the first expiry anywhere on the device the status word is set and every CTA that starts later returns
+// at once, so a fault costs one wait, not one per CTA.
+__device__ __forceinline__ bool cm_wait(uint64_t* b, uint32_t parity) {
+  const uint32_t addr = umma::smem_u32(b);
+  for (int it = 0; it < (1 << 20); ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+// keeps the first failure: code = 1000 * (wait site) + tile
+__device__ __forceinline__ void cm_fail(int code) { atomicCAS(&g_cm_status, 0, code); }
+// one poll: has the phase with this parity completed?
+__device__ __forceinline__ bool cm_try(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(umma::smem_u32(b)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool cm_failed_before() { return *reinterpret_cast<volatile int*>(&g_cm_status) != 0; }
+
+constexpr int kEntShift = 10;                 // entry = token << 10 | slot
+constexpr int kEntSlotMask = (1 << kEntShift) - 1;
+
+// =================================================================================================
+// inverse index: pairs (token, slot) grouped by (batch, kv head, chunk)
+// =================================================================================================
+// Order inside a chunk's list: token tiles ascending; inside a tile tokens ascending, slots ascending.
+// It is fixed by the index alone (no atomics decide it), so everything summed in list order is deterministic.
+struct InvIndex {
+  const int32_t* list;    // [B*h_kv][L*K]
+  const uint32_t* coff;   // [B*h_kv][nchunk + 1] start of each chunk's list inside the (b, h) segment
+};
+
+struct InvLayout {
+  size_t cnt_off, tot_off, coff_off, list_off, total;
+  int TT, ntile;
+};
+
+static InvLayout inv_layout(int B, int L, int h_kv, int K, int nchunk) {
+  InvLayout l;
+  int tt = (nchunk + K - 1) / K;              // keeps the per-tile histograms no larger than the list
+  l.TT = max(128, (tt + 31) / 32 * 32);
+  l.ntile = (L + l.TT - 1) / l.TT;
+  const size_t bh = (size_t)B * h_kv;
+  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  l.cnt_off = 0;
+  l.tot_off = up(l.cnt_off + bh * l.ntile * nchunk * 4);
+  l.coff_off = up(l.tot_off + bh * nchunk * 4);
+  l.list_off = up(l.coff_off + bh * (nchunk + 1) * 4);
+  l.total = up(l.list_off + bh * (size_t)L * K * 4);
+  return l;
+}
+
+// ids of one token's slots k0 + lane; a row's list ends at its first negative id
+template <bool kFill>
+__device__ __forceinline__ bool inv_step(int id, bool in_k, int t, int k, int nchunk, uint32_t* hist, int32_t* list, int lane) {
+  const unsigned neg = __ballot_sync(0xffffffffu, !in_k || id < 0);
+  const bool live = neg == 0u || lane < (__ffs(neg) - 1);
+  const bool take = live && id < nchunk;
+  if (!kFill) {
+    if (take) atomicAdd(&hist[id], 1u);
+  } else {
+    // equal ids inside one token (repeated slots) take consecutive positions in slot order
+    const unsigned peers = __match_any_sync(0xffffffffu, take ? id : -1 - lane);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    uint32_t pos = 0;
+    if (take) pos = hist[id] + rank;
+    __syncwarp();
+    if (take) {
+      list[pos] = (t << kEntShift) | k;
+      if (rank == __popc(peers) - 1) hist[id] = pos + 1;
+    }
+    __syncwarp();
+  }
+  return neg != 0u;
+}
+
+// one warp per (token tile, kv head, batch).  kFill = false: histogram of the tile's chunk ids.
+// kFill = true: the same walk with the histogram started at each chunk's write position.
+template <bool kFill>
+__global__ void __launch_bounds__(32) inv_walk_kernel(const int32_t* __restrict__ idx, uint32_t* __restrict__ cnt,
+                                                      const uint32_t* __restrict__ coff, int32_t* __restrict__ list, int L,
+                                                      int h_kv, int K, int nchunk, int TT, int ntile) {
+  extern __shared__ uint32_t hist[];
+  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z, lane = threadIdx.x;
+  const size_t bh = (size_t)b * h_kv + h;
+  uint32_t* my_cnt = cnt + (bh * ntile + tile) * nchunk;
+  for (int c = lane; c < nchunk; c += 32) hist[c] = kFill ? coff[bh * (nchunk + 1) + c] + my_cnt[c] : 0u;
+  __syncwarp();
+  int32_t* my_list = list + bh * (size_t)L * K;
+  const int t0 = tile * TT, t1 = min(L, t0 + TT);
+  const int32_t* base = idx + (((size_t)b * L) * h_kv + h) * K;
+  const size_t tstride = (size_t)h_kv * K;
+  if (K <= 32) {
+    for (int t = t0; t < t1; t += 4) {   // four tokens' ids in flight
+      int v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = (t + u < t1 && lane < K) ? __ldg(base + (size_t)(t + u) * tstride + lane) : -1;
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (t + u < t1) inv_step<kFill>(v[u], lane < K, t + u, lane, nchunk, hist, my_list, lane);
+    }
+  } else {
+    for (int t = t0; t < t1; ++t)
+      for (int k0 = 0; k0 < K; k0 += 32) {
+        const int k = k0 + lane;
+        const int id = k < K ? __ldg(base + (size_t)t * tstride + k) : -1;
+        if (inv_step<kFill>(id, k < K, t, k, nchunk, hist, my_list, lane)) break;
+      }
+  }
+  if (!kFill) {
+    __syncwarp();
+    for (int c = lane; c < nchunk; c += 32) my_cnt[c] = hist[c];
+  }
+}
+
+// per (b, h, chunk): exclusive prefix of the tile histograms over the tiles (in place) and the chunk's total
+__global__ void __launch_bounds__(256) inv_scan_kernel(uint32_t* __restrict__ cnt, uint32_t* __restrict__ tot, int nchunk, int ntile) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  const size_t bh = blockIdx.y;
+  if (c >= nchunk) return;
+  uint32_t* p = cnt + bh * ntile * nchunk + c;
+  uint32_t run = 0;
+#pragma unroll 8
+  for (int t = 0; t < ntile; ++t) {
+    const uint32_t v = p[(size_t)t * nchunk];
+    p[(size_t)t * nchunk] = run;
+    run += v;
+  }
+  tot[bh * nchunk + c] = run;
+}
+
+// per (b, h): exclusive prefix of the chunk totals
+__global__ void __launch_bounds__(256) inv_offsets_kernel(const uint32_t* __restrict__ tot, uint32_t* __restrict__ coff, int nchunk) {
+  __shared__ uint32_t wsum[8];
+  __shared__ uint32_t carry_s;
+  const size_t bh = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) carry_s = 0;
+  __syncthreads();
+  for (int c0 = 0; c0 < nchunk; c0 += 256) {
+    const int c = c0 + tid;
+    const uint32_t v = c < nchunk ? tot[bh * nchunk + c] : 0u;
+    uint32_t inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t n = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += n;
+    }
+    if (lane == 31) wsum[warp] = inc;
+    __syncthreads();
+    uint32_t pre = carry_s;
+    for (int w = 0; w < warp; ++w) pre += wsum[w];
+    if (c < nchunk) coff[bh * (nchunk + 1) + c] = pre + inc - v;
+    __syncthreads();
+    if (tid == 255) carry_s = pre + inc;
+    __syncthreads();
+  }
+  if (tid == 0) coff[bh * (nchunk + 1) + nchunk] = carry_s;
+}
+
+static int build_inverse_index(const SparseParams& p, void* workspace, InvIndex* ix, cudaStream_t st) {
+  const int nchunk = p.T / 64;
+  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.K, nchunk);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint32_t* cnt = reinterpret_cast<uint32_t*>(ws + l.cnt_off);
+  uint32_t* tot = reinterpret_cast<uint32_t*>(ws + l.tot_off);
+  uint32_t* coff = reinterpret_cast<uint32_t*>(ws + l.coff_off);
+  int32_t* list = reinterpret_cast<int32_t*>(ws + l.list_off);
+  const size_t smem = (size_t)nchunk * 4;
+  if (smem > 48 * 1024) {
+    cudaFuncSetAttribute(inv_walk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(inv_walk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
+  dim3 gw(l.ntile, p.h_kv, p.B);
+  inv_walk_kernel<false><<<gw, 32, smem, st>>>(p.idx, cnt, nullptr, nullptr, p.L, p.h_kv, p.K, nchunk, l.TT, l.ntile);
+  inv_scan_kernel<<<dim3((nchunk + 255) / 256, p.B * p.h_kv), 256, 0, st>>>(cnt, tot, nchunk, l.ntile);
+  inv_offsets_kernel<<<p.B * p.h_kv, 256, 0, st>>>(tot, coff, nchunk);
+  inv_walk_kernel<true><<<gw, 32, smem, st>>>(p.idx, cnt, coff, list, p.L, p.h_kv, p.K, nchunk, l.TT, l.ntile);
+  HILS_LAUNCH_CHECK("sparse_attn inverse index");
+  ix->list = list;
+  ix->coff = coff;
+  return HILS_OK;
+}
+
+// =================================================================================================
+// forward
+// =================================================================================================
+// 2 row warpgroups + MMA/TMA warp + 2 producer warps: 11 warps, at most 3 per scheduler, which leaves the row
+// threads 168 registers (a 13-warp CTA would cap every thread at 128)
+constexpr int kCmProducers = 64;
+constexpr int kCmThreads = 288 + kCmProducers;
+
+template <int D>
+__global__ void __launch_bounds__(kCmThreads, 1) sparse_fwd_cm_kernel(SparseParams p, InvIndex ix, float* __restrict__ o_acc,
+                                                                      const __grid_constant__ CUtensorMap tmK,
+                                                                      const __grid_constant__ CUtensorMap tmV) {
+  constexpr int DB = D / 64;
+  constexpr int QBYTES = DB * 16384;     // gathered Q tile, 128 x D
+  constexpr int KVBYTES = DB * 8192;     // K or V tile, 64 x D
+  constexpr int NQ = 2;                  // Q tile ring
+  constexpr int PIECES = D / 8;          // 16-byte pieces per row
+  constexpr int RPP = kCmProducers / PIECES;   // rows per producer pass
+  constexpr int NPASS = 128 / RPP;
+  constexpr int TM_COLS = (D == 64) ? 256 : 512;   // S: 2 x 64 columns, O: 2 x D columns
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* Ks = smem;
+  uint8_t* Vs = Ks + KVBYTES;
+  uint8_t* Qs = Vs + KVBYTES;            // NQ stages
+  uint8_t* Ps = Qs + NQ * QBYTES;        // 2 x [128 x 64] bf16
+
+  __shared__ uint64_t kv_full, q_full[NQ], q_free[NQ], s_full[2], p_full[2], o_full[2], o_free[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int tgt_s[2][2][128];       // [warpgroup][tile parity][row]: output row of each tile row, -1 = none
+  __shared__ volatile int abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nchunk = p.T / 64;
+  const int c = blockIdx.x;              // early chunks carry the longest lists and start first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const size_t bh = (size_t)b * p.h_kv + h;
+  const uint32_t beg = ix.coff[bh * (nchunk + 1) + c], end = ix.coff[bh * (nchunk + 1) + c + 1];
+  const int n_ent = (int)(end - beg);
+  if (n_ent == 0 || cm_failed_before()) return;   // nobody selected this chunk, or an earlier CTA's wait expired
+  const int G = p.h_q / p.h_kv, QB = 128 / G;
+  const int ntile = (n_ent + QB - 1) / QB;
+  const int32_t* lst = ix.list + bh * (size_t)p.L * p.K + beg;
+
+  if (tid == 0) {
+    mbar_init(&kv_full, 1);
+    for (int s = 0; s < NQ; ++s) {
+      mbar_init(&q_full[s], kCmProducers);
+      mbar_init(&q_free[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 128);
+      mbar_init(&o_full[s], 1);
+      mbar_init(&o_free[s], 128);
+    }
+    mbar_init_fence();
+    abort_s = 0;
+  }
+  if (warp == 8) tmem_alloc(&tmem_base_s, TM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t tS = tmem, tO = tmem + 128;
+
+  if (warp >= 9) {
+    // =============================== gather producers ===========================================
+    const int pt = tid - 9 * 32;                       // 0..kCmProducers-1
+    const int piece = pt % PIECES, row0 = pt / PIECES;
+    const uint32_t qs_base = smem_u32(Qs);
+    const bf16* qbase = static_cast<const bf16*>(p.q) + ((size_t)b * p.L * p.h_q + (size_t)h * G) * D + piece * 8;
+    bool ok = true;
+    for (int j = 0; j < ntile; ++j) {
+      const int s = j % NQ;
+      if (j >= NQ) {
+        ok = cm_wait(&q_free[s], ((j / NQ) - 1) & 1) && !abort_s;
+        if (!ok) break;
+      }
+      int ent[NPASS];
+#pragma unroll
+      for (int i = 0; i < NPASS; ++i) {
+        const int e = j * QB + (i * RPP + row0) / G;
+        ent[i] = e < n_ent ? __ldg(lst + e) : -1;
+      }
+#pragma unroll
+      for (int i = 0; i < NPASS; ++i) {
+        const int row = i * RPP + row0;
+        const bool live = ent[i] >= 0;
+        const int t = live ? (ent[i] >> kEntShift) : 0;
+        const bf16* src = qbase + ((size_t)t * p.h_q + (row % G)) * D;
+        cp_async16(qs_base + s * QBYTES + (piece >> 3) * 16384 + sw128_off(row, piece & 7), src, live ? 16u : 0u);
+      }
+      cp_async_commit();
+      if (j >= 1) {
+        cp_async_wait<1>();
+        fence_async_smem();
+        mbar_arrive(&q_full[(j - 1) % NQ]);
+      }
+    }
+    cp_async_wait<0>();
+    if (ok) {
+      fence_async_smem();
+      mbar_arrive(&q_full[(ntile - 1) % NQ]);
+    } else if (lane == 0) {
+      abort_s = 1;
+      atomicExch(&g_cm_status, 401);
+    }
+  } else if (warp == 8) {
+    // =============================== TMA (once) + MMA issuer ====================================
+    if (lane == 0) {
+      mbar_expect_tx(&kv_full, 2 * KVBYTES);
+#pragma unroll
+      for (int db = 0; db < DB; ++db) {
+        tma_load_2d(Ks + db * 8192, &tmK, &kv_full, h * D + db * 64, b * p.T + c * 64);
+        tma_load_2d(Vs + db * 8192, &tmV, &kv_full, h * D + db * 64, b * p.T + c * 64);
+      }
+      constexpr uint32_t idesc_qk = idesc_bf16(128, 64, 0);
+      constexpr uint32_t idesc_pv = idesc_bf16(128, D, 1);
+      const DescWords q_d = desc_words_sw128(smem_u32(Qs), 16, 1024), k_d = desc_words_sw128(smem_u32(Ks), 16, 1024),
+                      p_d = desc_words_sw128(smem_u32(Ps), 16, 1024), v_d = desc_words_sw128(smem_u32(Vs), 8192, 1024);
+      auto issue_qk = [&](int sq, int sb) {   // sq: Q ring stage, sb: S buffer
+        const uint32_t qb = q_d.lo + sq * (QBYTES >> 4);
+        mma_ss_w<false>(tS + sb * 64, qb, q_d.hi, k_d.lo, k_d.hi, idesc_qk);
+#pragma unroll
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(tS + sb * 64, qb + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), q_d.hi,
+                         k_d.lo + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), k_d.hi, idesc_qk);
+        mma_commit(&q_free[sq]);
+        mma_commit(&s_full[sb]);
+      };
+      bool ok = cm_wait(&kv_full, 0) && cm_wait(&q_full[0], 0);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0, 0);
+      }
+      for (int j = 0; ok && j < ntile; ++j) {
+        const int sb = j & 1, u = j >> 1;
+        if (abort_s) { ok = false; break; }
+        if (j + 1 < ntile) {
+          const int s1 = (j + 1) % NQ;
+          ok = cm_wait(&q_full[s1], ((j + 1) / NQ) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_qk(s1, sb ^ 1);      // its S buffer was consumed by tile j - 1 (p_full waited for below, last iteration)
+        }
+        ok = cm_wait(&p_full[sb], u & 1);
+        if (ok && u >= 1) ok = cm_wait(&o_free[sb], (u - 1) & 1);   // the O buffer's previous tile has been read out
+        if (!ok) break;
+        tc_fence_after();
+        {
+          const uint32_t a0 = p_d.lo + sb * (16384 >> 4);
+          mma_ss_w<false>(tO + sb * D, a0, p_d.hi, v_d.lo, v_d.hi, idesc_pv);
+#pragma unroll
+          for (int kk = 1; kk < 4; ++kk)
+            mma_ss_w<true>(tO + sb * D, a0 + ((kk * 32) >> 4), p_d.hi, v_d.lo + ((kk * 2048) >> 4), v_d.hi, idesc_pv);
+        }
+        mma_commit(&o_full[sb]);
+      }
+      if (!ok) { abort_s = 1; atomicExch(&g_cm_status, 402); }
+    }
+  } else {
+    // =============================== row warpgroups ==============================================
+    const int r = tid & 127, wg = tid >> 7;                 // warpgroup wg takes tiles wg, wg + 2, ... and buffers wg
+    const int g = r % G, hq = h * G + g;
+    const float scale_log2 = p.scale * kLog2e;
+    const float slope = p.slope ? p.slope[hq] : 0.f;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const bf16* wbase = static_cast<const bf16*>(p.w);
+    uint8_t* prow = Ps + wg * 16384;
+    bool ok = true;
+    for (int j = wg, u = 0; j < ntile; j += 2, ++u) {
+      const int e = j * QB + r / G;
+      const bool live = e < n_ent;
+      const int ent = live ? __ldg(lst + e) : 0;
+      const int t = ent >> kEntShift, k = ent & kEntSlotMask;
+      const int64_t rowi = ((int64_t)b * p.L + t) * p.h_q + hq;
+      const float wv = live ? to_f(wbase[rowi * p.num_weights + k]) : 0.f;
+      ok = cm_wait(&s_full[wg], u & 1);
+      ok = __all_sync(0xffffffffu, ok) && !abort_s;
+      if (!ok) break;
+      tc_fence_after();
+      float sv[64];
+      tmem_ld32(tS + lane_base + wg * 64, sv);
+      tmem_ld32(tS + lane_base + wg * 64 + 32, sv + 32);
+      tmem_ld_wait();
+      if (live) {
+        if (slope != 0.f) {
+#pragma unroll
+          for (int jj = 0; jj < 62; ++jj) sv[jj] -= slope * (float)(62 - jj);
+        }
+        if (p.mask_last) sv[63] = -CUDART_INF_F;
+        float m4[4] = {sv[0], sv[1], sv[2], sv[3]};
+#pragma unroll
+        for (int jj = 4; jj < 64; ++jj) m4[jj & 3] = fmaxf(m4[jj & 3], sv[jj]);
+        const float mb = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale_log2;
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int jj = 0; jj < 64; ++jj) {
+          sv[jj] = ex2(fmaf(sv[jj], scale_log2, -mb));
+          s4[jj & 3] += sv[jj];
+        }
+        const float f = wv / ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+#pragma unroll
+        for (int jj = 0; jj < 64; ++jj) sv[jj] *= f;
+        store_row_bf16_sw128(prow, r, sv);
+      } else {
+        store_row_zero_sw128(prow, r);
+      }
+      tgt_s[wg][u & 1][r] = live ? (int)rowi : -1;
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&p_full[wg]);
+      // all 128 arrivals on p_full also mean that tgt_s of this tile is complete (a bounded wait, unlike bar.sync)
+      ok = cm_wait(&p_full[wg], u & 1) && cm_wait(&o_full[wg], u & 1);
+      ok = __all_sync(0xffffffffu, ok) && !abort_s;
+      if (!ok) break;
+      tc_fence_after();
+      // O tile -> fp32 accumulator rows: 4 neighbouring lanes add 32 consecutive bytes of one row
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int ra = (warp & 3) * 32 + half * 16 + (lane >> 2);
+        const int ta = tgt_s[wg][u & 1][ra], tb = tgt_s[wg][u & 1][ra + 8];
+        float* pa = o_acc + (int64_t)(ta < 0 ? 0 : ta) * D + 2 * (lane & 3);
+        float* pb = o_acc + (int64_t)(tb < 0 ? 0 : tb) * D + 2 * (lane & 3);
+#pragma unroll
+        for (int cb = 0; cb < D / 64; ++cb) {
+          float ov[32];
+          tmem_ld_16x256b_x8(tO + lane_base + ((uint32_t)(half * 16) << 16) + wg * D + cb * 64, ov);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (ta >= 0) red_add_v2(pa + cb * 64 + 8 * i, ov[4 * i], ov[4 * i + 1]);
+            if (tb >= 0) red_add_v2(pb + cb * 64 + 8 * i, ov[4 * i + 2], ov[4 * i + 3]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&o_free[wg]);
+      // tgt_s[wg][u & 1] is rewritten two tiles later, after every thread has passed the p_full wait of the next
+      // tile, i.e. after every thread has finished this read-out
+    }
+    if (!ok && lane == 0) { abort_s = 1; atomicExch(&g_cm_status, 403); }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem, TM_COLS);
+}
+
+// fp32 accumulator -> bf16 output, 8 elements per thread
+__global__ void __launch_bounds__(256) cm_round_kernel(const float* __restrict__ acc, bf16* __restrict__ out, int64_t n8) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n8) return;
+  const float4 a = *reinterpret_cast<const float4*>(acc + i * 8), c = *reinterpret_cast<const float4*>(acc + i * 8 + 4);
+  __nv_bfloat162 hh[4] = {__floats2bfloat162_rn(a.x, a.y), __floats2bfloat162_rn(a.z, a.w), __floats2bfloat162_rn(c.x, c.y),
+                          __floats2bfloat162_rn(c.z, c.w)};
+  *reinterpret_cast<uint4*>(out + i * 8) = *reinterpret_cast<uint4*>(hh);
+}
+
+static bool cm_shape_ok(const SparseParams& p) {
+  const int D = p.D;
+  if (p.S != 64 || p.D != p.Dv || (D != 64 && D != 128)) return false;
+  const int G = p.h_q / p.h_kv;
+  if (G > 128 || (128 % G) != 0) return false;
+  if (p.T < 64 || p.K > (1 << kEntShift) || p.L >= (1 << (31 - kEntShift))) return false;
+  if ((int64_t)p.B * p.T >= (1ll << 31) || (int64_t)p.B * p.L * p.h_q >= (1ll << 31)) return false;
+  if ((size_t)(p.T / 64) * 4 > 200 * 1024) return false;    // chunk histogram of the index build lives in shared memory
+  if ((int64_t)p.L * p.K >= (1ll << 32)) return false;
+  return true;
+}
+
+static size_t cm_fwd_smem(int D) { return 1024 + 2 * (size_t)(D / 64) * 8192 + 2 * (size_t)(D / 64) * 16384 + 2 * 16384; }
+
+// workspace of the chunk-major forward: inverse index + fp32 output accumulator (0: shape outside this path)
+size_t sparse_fwd_cm_workspace(const SparseParams& p) {
+  if (!cm_shape_ok(p)) return 0;
+  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.K, p.T / 64);
+  return l.total + (size_t)p.B * p.L * p.h_q * p.D * sizeof(float);
+}
+
+// Returns HILS_ERR_UNSUPPORTED (without setting an error text) when the shape is outside this path.
+int sparse_fwd_cm_launch(const SparseParams& p, void* workspace, cudaStream_t st) {
+  if (!cm_shape_ok(p) || !workspace) return HILS_ERR_UNSUPPORTED;
+  if (((uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o | (uintptr_t)workspace) & 15) return HILS_ERR_UNSUPPORTED;
+  const int D = p.D, nchunk = p.T / 64;
+  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.K, nchunk);
+  InvIndex ix;
+  if (int rc = build_inverse_index(p, workspace, &ix, st)) return rc;
+  float* o_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + l.total);
+  const size_t n_out = (size_t)p.B * p.L * p.h_q * D;
+  cudaError_t e = cudaMemsetAsync(o_acc, 0, n_out * sizeof(float), st);
+  if (e != cudaSuccess) return cuda_fail(e, "sparse_attn_fwd accumulator clear");
+  CUtensorMap tmK, tmV;
+  if (int rc = make_tmap_bf16_rows(&tmK, p.k, (uint64_t)p.B * p.T, (uint64_t)p.h_kv * D, (uint64_t)p.h_kv * D, 64)) return rc;
+  if (int rc = make_tmap_bf16_rows(&tmV, p.v, (uint64_t)p.B * p.T, (uint64_t)p.h_kv * D, (uint64_t)p.h_kv * D, 64)) return rc;
+  const size_t smem = cm_fwd_smem(D);
+  dim3 grid(nchunk, p.h_kv, p.B);
+  if (D == 64) {
+    cudaFuncSetAttribute(sparse_fwd_cm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sparse_fwd_cm_kernel<64><<<grid, kCmThreads, smem, st>>>(p, ix, o_acc, tmK, tmV);
+  } else {
+    cudaFuncSetAttribute(sparse_fwd_cm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sparse_fwd_cm_kernel<128><<<grid, kCmThreads, smem, st>>>(p, ix, o_acc, tmK, tmV);
+  }
+  cm_round_kernel<<<(unsigned)((n_out / 8 + 255) / 256), 256, 0, st>>>(o_acc, static_cast<bf16*>(p.o), (int64_t)(n_out / 8));
+  HILS_LAUNCH_CHECK("sparse_attn_fwd (chunk-major path)");
+  return HILS_OK;
+}
+
+// =================================================================================================
+// backward: one kernel, chunk-major like the forward
+// =================================================================================================
+// Per tile of 128 owner rows of the chunk (Q and dO rows gathered by the producer warps):
+//   MMA  : S = Q K^T and dP = dO V^T                                   (TMEM, 2 x 64 columns)
+//   rows : P from S, dw = sum_j P_j dP_j (stored per (token, q head, slot)), dS = scale w P (dP - dw) and w P
+//          as bf16 tiles in shared memory                                (ops/hils_fwd_bwd_head.py:651-757)
+//   MMA  : dQ tile = dS K (TMEM, read out and added to the fp32 dQ accumulator of each row's token);
+//          dK += dS^T Q and dV += (wP)^T dO accumulate in TMEM over ALL tiles of the chunk and are written
+//          once at the end: no atomics on dK / dV, and their sums run in list order (deterministic).
+// D = 64 keeps two S/dP accumulators, two dQ tiles and two dS / wP tiles and forms dK and dV in one stacked
+// M = 128, N = 128 product per 16 rows (A = [dS^T ; (wP)^T], B = [Q | dO]; the diagonal blocks of the accumulator
+// are dK and dV).  D = 128 has TMEM and shared memory for one of each.
+template <int D>
+__global__ void __launch_bounds__(kCmThreads, 1) sparse_bwd_cm_kernel(SparseParams p, InvIndex ix, float* __restrict__ dq_acc,
+                                                                      const __grid_constant__ CUtensorMap tmK,
+                                                                      const __grid_constant__ CUtensorMap tmV) {
+  constexpr int DB = D / 64;
+  constexpr int QBYTES = DB * 16384;
+  constexpr int KVBYTES = DB * 8192;
+  constexpr int NSB = (D == 64) ? 2 : 1;   // S/dP accumulators in TMEM
+  constexpr int NDQ = (D == 64) ? 2 : 1;   // dQ tiles in TMEM
+  constexpr int NDS = (D == 64) ? 2 : 1;   // dS / wP tiles in shared memory
+  constexpr int NQ = (D == 64) ? 3 : 2;    // Q / dO ring; NSB % NQ != 0, so the ring stage of tile j + NSB never waits on tile j
+  constexpr int PIECES = D / 8;
+  constexpr int RPP = kCmProducers / PIECES;
+  constexpr int NPASS = 128 / RPP;
+  constexpr bool kStacked = (D == 64);
+  // TMEM columns: S/dP [0, NSB*128), dQ [NSB*128, +NDQ*D), dK (and dV) after them
+  constexpr uint32_t C_DQ = NSB * 128, C_DK = C_DQ + NDQ * D, C_DV = C_DK + D;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* Qs = smem;                      // NQ stages
+  uint8_t* dOs = Qs + NQ * QBYTES;         // NQ stages
+  uint8_t* Ks = dOs + NQ * QBYTES;
+  uint8_t* Vs = Ks + KVBYTES;
+  uint8_t* dSs = Vs + KVBYTES;             // NDS x 16 KB
+  uint8_t* Pws = dSs + NDS * 16384;        // NDS x 16 KB
+
+  __shared__ uint64_t kv_full, qdo_full[3], qdo_free[3], sd_full[2], ds_full[2], ds_free[2], dq_full[2], dq_free[2], all_done;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int tgt_s[2][2][128];
+  __shared__ volatile int abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nchunk = p.T / 64;
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const size_t bh = (size_t)b * p.h_kv + h;
+  const uint32_t beg = ix.coff[bh * (nchunk + 1) + c], end = ix.coff[bh * (nchunk + 1) + c + 1];
+  const int n_ent = (int)(end - beg);
+  const int G = p.h_q / p.h_kv, QB = 128 / G;
+  if (n_ent == 0) {
+    // nobody selected this chunk: its key and value gradients are zero
+    bf16* dk = static_cast<bf16*>(p.d_k_out) + (((size_t)b * p.T + (size_t)c * 64) * p.h_kv + h) * D;
+    bf16* dv = static_cast<bf16*>(p.d_v_out) + (((size_t)b * p.T + (size_t)c * 64) * p.h_kv + h) * D;
+    for (int i = tid; i < 64 * PIECES; i += kCmThreads) {
+      const size_t off = (size_t)(i / PIECES) * p.h_kv * D + (i % PIECES) * 8;
+      *reinterpret_cast<uint4*>(dk + off) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(dv + off) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    return;
+  }
+  if (cm_failed_before()) return;
+  const int ntile = (n_ent + QB - 1) / QB;
+  const int32_t* lst = ix.list + bh * (size_t)p.L * p.K + beg;
+
+  if (tid == 0) {
+    mbar_init(&kv_full, 1);
+    mbar_init(&all_done, 1);
+    for (int s = 0; s < NQ; ++s) {
+      mbar_init(&qdo_full[s], kCmProducers);
+      mbar_init(&qdo_free[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sd_full[s], 1);
+      mbar_init(&ds_full[s], 128);
+      mbar_init(&ds_free[s], 1);
+      mbar_init(&dq_full[s], 1);
+      mbar_init(&dq_free[s], 128);
+    }
+    mbar_init_fence();
+    abort_s = 0;
+  }
+  if (warp == 8) tmem_alloc(&tmem_base_s, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t tdK = tmem + C_DK, tdV = tmem + C_DV;
+
+  if (warp >= 9) {
+    // =============================== gather producers ===========================================
+    const int pt = tid - 9 * 32;
+    const int piece = pt % PIECES, row0 = pt / PIECES;
+    const uint32_t qs_base = smem_u32(Qs), dos_base = smem_u32(dOs);
+    const size_t head_off = ((size_t)b * p.L * p.h_q + (size_t)h * G) * D + piece * 8;
+    const bf16* qbase = static_cast<const bf16*>(p.q) + head_off;
+    const bf16* dobase = static_cast<const bf16*>(p.d_o) + head_off;
+    bool ok = true, pending = false;
+    for (int j = 0; j < ntile; ++j) {
+      const int s = j % NQ;
+      if (j >= NQ) {
+        // The stage is released by the products of tile j - NQ, which the MMA warp issues only after it has seen
+        // tile j - 1 arrive: a tile that is still in flight here must be published before this thread may block.
+        if (pending && !cm_try(&qdo_free[s], ((j / NQ) - 1) & 1)) {
+          cp_async_wait<0>();
+          fence_async_smem();
+          mbar_arrive(&qdo_full[(j - 1) % NQ]);
+          pending = false;
+        }
+        ok = cm_wait(&qdo_free[s], ((j / NQ) - 1) & 1) && !abort_s;
+        if (!ok) { cm_fail(5010000 + j); break; }
+      }
+      int ent[NPASS];
+#pragma unroll
+      for (int i = 0; i < NPASS; ++i) {
+        const int e = j * QB + (i * RPP + row0) / G;
+        ent[i] = e < n_ent ? __ldg(lst + e) : -1;
+      }
+#pragma unroll
+      for (int i = 0; i < NPASS; ++i) {
+        const int row = i * RPP + row0;
+        const bool live = ent[i] >= 0;
+        const int t = live ? (ent[i] >> kEntShift) : 0;
+        const size_t off = ((size_t)t * p.h_q + (row % G)) * D;
+        const uint32_t dst = s * QBYTES + (piece >> 3) * 16384 + sw128_off(row, piece & 7);
+        cp_async16(qs_base + dst, qbase + off, live ? 16u : 0u);
+        cp_async16(dos_base + dst, dobase + off, live ? 16u : 0u);
+      }
+      cp_async_commit();
+      if (pending) {                      // tile j - 1 has landed once at most this tile's group is outstanding
+        cp_async_wait<1>();
+        fence_async_smem();
+        mbar_arrive(&qdo_full[(j - 1) % NQ]);
+      }
+      pending = true;
+    }
+    cp_async_wait<0>();
+    if (ok) {
+      fence_async_smem();
+      mbar_arrive(&qdo_full[(ntile - 1) % NQ]);
+    } else if (lane == 0) {
+      abort_s = 1;
+      cm_fail(5019999);
+    }
+  } else if (warp == 8) {
+    // =============================== TMA (once) + MMA issuer ====================================
+    if (lane == 0) {
+      mbar_expect_tx(&kv_full, 2 * KVBYTES);
+#pragma unroll
+      for (int db = 0; db < DB; ++db) {
+        tma_load_2d(Ks + db * 8192, &tmK, &kv_full, h * D + db * 64, b * p.T + c * 64);
+        tma_load_2d(Vs + db * 8192, &tmV, &kv_full, h * D + db * 64, b * p.T + c * 64);
+      }
+      constexpr uint32_t idesc_s = idesc_bf16(128, 64, 0);
+      constexpr uint32_t idesc_dq = idesc_bf16(128, D, 1);
+      constexpr uint32_t idesc_dkv = idesc_bf16(64, D, 1, 1);
+      constexpr uint32_t idesc_st = idesc_bf16(128, 128, 1, 1);
+      const DescWords q_d = desc_words_sw128(smem_u32(Qs), 16, 1024), do_d = desc_words_sw128(smem_u32(dOs), 16, 1024),
+                      k_d = desc_words_sw128(smem_u32(Ks), 16, 1024), v_d = desc_words_sw128(smem_u32(Vs), 16, 1024),
+                      kmn_d = desc_words_sw128(smem_u32(Ks), 8192, 1024), dsk_d = desc_words_sw128(smem_u32(dSs), 16, 1024),
+                      qmn_d = desc_words_sw128(smem_u32(Qs), 16384, 1024), domn_d = desc_words_sw128(smem_u32(dOs), 16384, 1024),
+                      ds_d = desc_words_sw128(smem_u32(dSs), 16384, 1024), pw_d = desc_words_sw128(smem_u32(Pws), 16384, 1024),
+                      ast_d = desc_words_sw128(smem_u32(dSs), NDS * 16384, 1024),
+                      bst_d = desc_words_sw128(smem_u32(Qs), NQ * QBYTES, 1024);
+      bool ok = cm_wait(&kv_full, 0);
+      auto issue_sdp = [&](int e) {   // S and dP of tile e
+        const int sq = e % NQ, sb = e % NSB;
+        ok = cm_wait(&qdo_full[sq], (e / NQ) & 1);
+        if (!ok) { cm_fail(5021000 + e); return; }
+        tc_fence_after();
+        const uint32_t qb = q_d.lo + sq * (QBYTES >> 4), dob = do_d.lo + sq * (QBYTES >> 4);
+        const uint32_t ts = tmem + sb * 128;
+        mma_ss_w<false>(ts, qb, q_d.hi, k_d.lo, k_d.hi, idesc_s);
+#pragma unroll
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(ts, qb + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), q_d.hi,
+                         k_d.lo + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), k_d.hi, idesc_s);
+        mma_ss_w<false>(ts + 64, dob, do_d.hi, v_d.lo, v_d.hi, idesc_s);
+#pragma unroll
+        for (int kk = 1; kk < D / 16; ++kk)
+          mma_ss_w<true>(ts + 64, dob + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), do_d.hi,
+                         v_d.lo + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), v_d.hi, idesc_s);
+        mma_commit(&sd_full[e & 1]);
+      };
+      // Barriers are indexed by the tile's parity (= the warpgroup that owns the tile) even where both warpgroups
+      // share one buffer: a warpgroup then meets the phases of its barriers in order.  (A parity wait on a barrier
+      // whose earlier phase is still open would pass at once.)
+      for (int e = 0; ok && e < NSB && e < ntile; ++e) issue_sdp(e);
+      for (int j = 0; ok && j < ntile; ++j) {
+        const int sq = j % NQ, db = j % NDS, qb = j % NDQ;
+        if (abort_s) { ok = false; break; }
+        ok = cm_wait(&ds_full[j & 1], (j >> 1) & 1);   // rows of tile j have read S/dP and written dS, wP
+        if (!ok) { cm_fail(5022000 + j); break; }
+        if (j + NSB < ntile) {                            // the accumulator of tile j is free again
+          issue_sdp(j + NSB);
+          if (!ok) break;
+        }
+        if (j >= NDQ) {                                   // the dQ tile's previous user (tile j - NDQ) has been read out
+          ok = cm_wait(&dq_free[(j - NDQ) & 1], ((j - NDQ) >> 1) & 1);
+          if (!ok) { cm_fail(5023000 + j); break; }
+        }
+        tc_fence_after();
+        {
+          const uint32_t a0 = dsk_d.lo + db * (16384 >> 4);
+          const uint32_t tq = tmem + C_DQ + qb * D;
+          mma_ss_w<false>(tq, a0, dsk_d.hi, kmn_d.lo, kmn_d.hi, idesc_dq);
+#pragma unroll
+          for (int kk = 1; kk < 4; ++kk)
+            mma_ss_w<true>(tq, a0 + ((kk * 32) >> 4), dsk_d.hi, kmn_d.lo + ((kk * 2048) >> 4), kmn_d.hi, idesc_dq);
+          mma_commit(&dq_full[j & 1]);
+        }
+        if (kStacked) {
+          const uint32_t a0 = ast_d.lo + db * (16384 >> 4), b0 = bst_d.lo + sq * (QBYTES >> 4);
+          mma_ss_wr(tdK, a0, ast_d.hi, b0, bst_d.hi, idesc_st, j > 0 ? 1u : 0u);
+#pragma unroll
+          for (int kk = 1; kk < 8; ++kk)   // 16 rows per step
+            mma_ss_w<true>(tdK, a0 + ((kk * 2048) >> 4), ast_d.hi, b0 + ((kk * 2048) >> 4), bst_d.hi, idesc_st);
+        } else {
+          const uint32_t dsb = ds_d.lo + db * (16384 >> 4), pwb = pw_d.lo + db * (16384 >> 4);
+          const uint32_t qmb = qmn_d.lo + sq * (QBYTES >> 4), domb = domn_d.lo + sq * (QBYTES >> 4);
+          mma_ss_wr(tdK, dsb, ds_d.hi, qmb, qmn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
+          mma_ss_wr(tdV, pwb, pw_d.hi, domb, domn_d.hi, idesc_dkv, j > 0 ? 1u : 0u);
+#pragma unroll
+          for (int kk = 1; kk < 8; ++kk) {
+            mma_ss_w<true>(tdK, dsb + ((kk * 2048) >> 4), ds_d.hi, qmb + ((kk * 2048) >> 4), qmn_d.hi, idesc_dkv);
+            mma_ss_w<true>(tdV, pwb + ((kk * 2048) >> 4), pw_d.hi, domb + ((kk * 2048) >> 4), domn_d.hi, idesc_dkv);
+          }
+        }
+        mma_commit(&ds_free[j & 1]);
+        mma_commit(&qdo_free[sq]);
+      }
+      if (ok) mma_commit(&all_done);
+      if (!ok) { abort_s = 1; cm_fail(5029999); }
+    }
+  } else {
+    // =============================== row warpgroups ==============================================
+    const int r = tid & 127, wg = tid >> 7;                 // warpgroup wg takes tiles wg, wg + 2, ...
+    const int g = r % G, hq = h * G + g;
+    const float scale_log2 = p.scale * kLog2e;
+    const float slope = p.slope ? p.slope[hq] : 0.f;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const bf16* wbase = static_cast<const bf16*>(p.w);
+    bf16* dwbase = static_cast<bf16*>(p.d_w);
+    bool ok = true;
+    for (int j = wg, u = 0; j < ntile; j += 2, ++u) {
+      const int sb = j % NSB, db = j % NDS, qb = j % NDQ;
+      const int e = j * QB + r / G;
+      const bool live = e < n_ent;
+      const int ent = live ? __ldg(lst + e) : 0;
+      const int t = ent >> kEntShift, k = ent & kEntSlotMask;
+      const int64_t rowi = ((int64_t)b * p.L + t) * p.h_q + hq;
+      const float wv = live ? to_f(wbase[rowi * p.num_weights + k]) : 0.f;
+      ok = cm_wait(&sd_full[wg], u & 1);
+      if (!ok) cm_fail(5031000 + j);
+      ok = __all_sync(0xffffffffu, ok) && !abort_s;
+      if (!ok) break;
+      tc_fence_after();
+      float sv[64], dp[64];
+      const uint32_t tsd = tmem + lane_base + sb * 128;
+      tmem_ld32(tsd, sv);
+      tmem_ld32(tsd + 32, sv + 32);
+      tmem_ld_wait();
+      tmem_ld32(tsd + 64, dp);          // in flight while the S row is exponentiated
+      tmem_ld32(tsd + 96, dp + 32);
+      float esum = 1.f;
+      if (live) esum = bwd_row_exp(sv, scale_log2, slope, p.mask_last);
+      tmem_ld_wait64(dp);
+      float dw = 0.f;
+      if (live) dw = bwd_row_grad<true>(sv, dp, esum, wv, p.scale);
+      if (j >= NDS) {                   // the dS / wP tile was last read by the products of tile j - NDS
+        ok = cm_wait(&ds_free[(j - NDS) & 1], ((j - NDS) >> 1) & 1);
+        if (!ok) cm_fail(5032000 + j);
+        ok = __all_sync(0xffffffffu, ok) && !abort_s;
+        if (!ok) break;
+      }
+      if (live) {
+        store_row_bf16_sw128(dSs + db * 16384, r, sv);
+        store_row_bf16_sw128(Pws + db * 16384, r, dp);
+        dwbase[rowi * p.num_weights + k] = __float2bfloat16_rn(dw);
+      } else {
+        store_row_zero_sw128(dSs + db * 16384, r);
+        store_row_zero_sw128(Pws + db * 16384, r);
+      }
+      tgt_s[wg][u & 1][r] = live ? (int)rowi : -1;
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&ds_full[wg]);
+      // all 128 arrivals also mean that tgt_s of this tile is complete
+      ok = cm_wait(&ds_full[wg], u & 1);
+      if (!ok) cm_fail(5033000 + j);
+      if (ok) {
+        ok = cm_wait(&dq_full[wg], u & 1);
+        if (!ok) cm_fail(5034000 + j);
+      }
+      ok = __all_sync(0xffffffffu, ok) && !abort_s;
+      if (!ok) break;
+      tc_fence_after();
+      // dQ tile -> fp32 accumulator rows: 4 neighbouring lanes add 32 consecutive bytes of one row
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int ra = (warp & 3) * 32 + half * 16 + (lane >> 2);
+        const int ta = tgt_s[wg][u & 1][ra], tb = tgt_s[wg][u & 1][ra + 8];
+        float* pa = dq_acc + (int64_t)(ta < 0 ? 0 : ta) * D + 2 * (lane & 3);
+        float* pb = dq_acc + (int64_t)(tb < 0 ? 0 : tb) * D + 2 * (lane & 3);
+#pragma unroll
+        for (int cb = 0; cb < D / 64; ++cb) {
+          float ov[32];
+          tmem_ld_16x256b_x8(tmem + lane_base + ((uint32_t)(half * 16) << 16) + C_DQ + qb * D + cb * 64, ov);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (ta >= 0) red_add_v2(pa + cb * 64 + 8 * i, ov[4 * i], ov[4 * i + 1]);
+            if (tb >= 0) red_add_v2(pb + cb * 64 + 8 * i, ov[4 * i + 2], ov[4 * i + 3]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&dq_free[wg]);
+    }
+    // ---- dK, dV of the chunk: TMEM -> bf16 -> global, once -------------------------------------
+    if (ok) {
+      ok = cm_wait(&all_done, 0);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (!ok && lane == 0) { abort_s = 1; cm_fail(5039999); }
+    if (ok) tc_fence_after();
+    if (kStacked) {
+      // stacked accumulator (M = 128): TMEM lane = row; rows 0..63 hold dK in columns 0..63, rows 64..127 hold dV in
+      // columns 64..127.  Warps 0, 1 of a warpgroup write dK rows, warps 2, 3 dV rows; warpgroup w takes the 32-column
+      // half w.
+      const int wq = warp & 3;
+      const bool is_v = wq >= 2;
+      const int64_t tokr = (int64_t)b * p.T + (int64_t)c * 64 + 32 * (wq & 1) + lane;
+      float ov[32];
+      if (ok) {
+        tmem_ld32(tdK + lane_base + (is_v ? 64 : 0) + wg * 32, ov);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) ov[jj] = 0.f;
+      }
+      store32_bf16(static_cast<bf16*>(is_v ? p.d_v_out : p.d_k_out) + (tokr * p.h_kv + h) * D + wg * 32, ov);
+    } else {
+      // M = 64 accumulators: key row 16 * warp + lane lives in TMEM lane 32 * warp + lane, lanes 0..15 of each warp;
+      // warpgroup 0 writes dK, warpgroup 1 writes dV
+      const int krow = 16 * (warp & 3) + lane;
+      const int64_t tok = (int64_t)b * p.T + (int64_t)c * 64 + krow;
+      bf16* dst = static_cast<bf16*>(wg ? p.d_v_out : p.d_k_out) + (tok * p.h_kv + h) * D;
+#pragma unroll
+      for (int cb = 0; cb < D / 32; ++cb) {
+        float ov[32];
+        if (ok) {
+          tmem_ld32((wg ? tdV : tdK) + lane_base + cb * 32, ov);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) ov[jj] = 0.f;
+        }
+        if (lane < 16) store32_bf16(dst + cb * 32, ov);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem, 512);
+}
+
+static size_t cm_bwd_smem(int D) {
+  const int NQ = (D == 64) ? 3 : 2, NDS = (D == 64) ? 2 : 1;
+  return 1024 + 2 * (size_t)NQ * (D / 64) * 16384 + 2 * (size_t)(D / 64) * 8192 + 2 * (size_t)NDS * 16384;
+}
+
+// workspace of the chunk-major backward: inverse index + fp32 dQ accumulator (0: shape outside this path)
+size_t sparse_bwd_cm_workspace(const SparseParams& p) {
+  if (!cm_shape_ok(p)) return 0;
+  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.K, p.T / 64);
+  return l.total + (size_t)p.B * p.L * p.h_q * p.D * sizeof(float);
+}
+
+int sparse_bwd_cm_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st) {
+  if (!cm_shape_ok(p) || !workspace) return HILS_ERR_UNSUPPORTED;
+  if (((uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.d_o | (uintptr_t)p.d_q | (uintptr_t)d_k | (uintptr_t)d_v |
+       (uintptr_t)workspace) & 15)
+    return HILS_ERR_UNSUPPORTED;
+  const int D = p.D, nchunk = p.T / 64;
+  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.K, nchunk);
+  InvIndex ix;
+  if (int rc = build_inverse_index(p, workspace, &ix, st)) return rc;
+  float* dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + l.total);
+  const size_t n_q = (size_t)p.B * p.L * p.h_q * D;
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, n_q * sizeof(float), st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(p.d_w, 0, (size_t)p.B * p.L * p.h_q * p.num_weights * 2, st);
+  if (e == cudaSuccess && p.T % 64 != 0) {   // tokens after the last full chunk belong to no chunk
+    e = cudaMemsetAsync(d_k, 0, (size_t)p.B * p.T * p.h_kv * D * 2, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(d_v, 0, (size_t)p.B * p.T * p.h_kv * D * 2, st);
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "sparse_attn_bwd accumulator clear");
+  SparseParams pp = p;
+  pp.d_k_out = d_k;
+  pp.d_v_out = d_v;
+  CUtensorMap tmK, tmV;
+  if (int rc = make_tmap_bf16_rows(&tmK, p.k, (uint64_t)p.B * p.T, (uint64_t)p.h_kv * D, (uint64_t)p.h_kv * D, 64)) return rc;
+  if (int rc = make_tmap_bf16_rows(&tmV, p.v, (uint64_t)p.B * p.T, (uint64_t)p.h_kv * D, (uint64_t)p.h_kv * D, 64)) return rc;
+  const size_t smem = cm_bwd_smem(D);
+  dim3 grid(nchunk, p.h_kv, p.B);
+  if (D == 64) {
+    cudaFuncSetAttribute(sparse_bwd_cm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sparse_bwd_cm_kernel<64><<<grid, kCmThreads, smem, st>>>(pp, ix, dq_acc, tmK, tmV);
+  } else {
+    cudaFuncSetAttribute(sparse_bwd_cm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sparse_bwd_cm_kernel<128><<<grid, kCmThreads, smem, st>>>(pp, ix, dq_acc, tmK, tmV);
+  }
+  cm_round_kernel<<<(unsigned)((n_q / 8 + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<bf16*>(p.d_q), (int64_t)(n_q / 8));
+  HILS_LAUNCH_CHECK("sparse_attn_bwd (chunk-major path)");
+  return HILS_OK;
+}
+
+// device-side error word of this file's kernels (0 = none); synchronises and clears
+int take_status_sparse_cm() {
+  int v = 0, zero = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(&v, g_cm_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_cm_status, &zero, sizeof(int));
+  return v;
+}
+
+}  // namespace hils

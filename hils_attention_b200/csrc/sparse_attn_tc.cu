@@ -93,7 +93,6 @@ using namespace umma;
 
 constexpr int kBwdThreads = 320;  // 2 row warpgroups + MMA warp + TMA warp
 constexpr int kFwdStages = 3;     // K/V ring depth of the forward kernel
-constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tmK,
@@ -402,50 +401,6 @@ __global__ void __launch_bounds__(kBwdThreads, 2) sparse_fwd_tc_kernel(SparsePar
 // Per pair both passes recompute S = Q K^T and dP = dO V^T on the tensor cores; one thread per row
 // forms P, dw = sum_j P_j dP_j, dS = scale w P (dP - dw) (ops/hils_fwd_bwd_head.py:651-757).
 // =================================================================================================
-
-// Backward row arithmetic in two phases, so that the dP row can still be in flight from TMEM while the
-// first phase works on the S row.
-// Phase A: S row in sv  ->  e_j = exp(scale (S_j - max)) in sv; returns sum_j e_j.
-__device__ __forceinline__ float bwd_row_exp(float* sv, float scale_log2, float slope, int mask_last) {
-  if (slope != 0.f) {
-#pragma unroll
-    for (int j = 0; j < 62; ++j) sv[j] -= slope * (float)(62 - j);
-  }
-  if (mask_last) sv[63] = -CUDART_INF_F;
-  // reductions use four interleaved partial accumulators: a single dependent chain of 64 operations
-  // would leave the thread waiting on arithmetic latency most of the time
-  float m4[4] = {sv[0], sv[1], sv[2], sv[3]};
-#pragma unroll
-  for (int j = 4; j < 64; ++j) m4[j & 3] = fmaxf(m4[j & 3], sv[j]);
-  const float m = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-  const float mb = m * scale_log2;
-  float s4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-  for (int j = 0; j < 64; ++j) {
-    sv[j] = ex2(fmaf(sv[j], scale_log2, -mb));
-    s4[j & 3] += sv[j];
-  }
-  return (s4[0] + s4[1]) + (s4[2] + s4[3]);
-}
-// Phase B: e row in sv, dP row in dp  ->  dS row in sv (= scale w P (dP - dw)) and, when kWantWP, the
-// w*P row in dp; returns dw = sum_j P_j dP_j.  P_j = e_j / sum is never formed: the factors fold into
-// one multiplier per product.
-template <bool kWantWP>
-__device__ __forceinline__ float bwd_row_grad(float* sv, float* dp, float sum, float wsum, float scale) {
-  const float inv = 1.f / sum;
-  float d4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-  for (int j = 0; j < 64; ++j) d4[j & 3] = fmaf(sv[j], dp[j], d4[j & 3]);
-  const float dw = ((d4[0] + d4[1]) + (d4[2] + d4[3])) * inv;
-  const float c = scale * wsum * inv, cdw = -c * dw, wp = wsum * inv;
-#pragma unroll
-  for (int j = 0; j < 64; ++j) {
-    const float e = sv[j];
-    sv[j] = e * fmaf(c, dp[j], cdw);
-    if (kWantWP) dp[j] = wp * e;
-  }
-  return dw;
-}
 
 struct BwdWs {
   uint32_t* bitmap;  // [B*h_kv][nblk][nwords]  union bitmap of each query block

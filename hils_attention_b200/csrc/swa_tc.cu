@@ -28,7 +28,6 @@ struct SwaTcParams {
 };
 
 constexpr int kThreads = 192;
-constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 // raw key range [lo, hi] visible from query row i (empty when lo > hi)

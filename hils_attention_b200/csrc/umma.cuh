@@ -166,6 +166,41 @@ __device__ __forceinline__ void tmem_ld_wait64(float* v) {
                : "memory");
 }
 
+
+// ---- asynchronous 16-byte copies global -> shared (gathers of single rows) ------------------------
+// src_bytes = 16 copies, src_bytes = 0 writes 16 zero bytes (the source is not read)
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory"); }
+
+// barrier among `nthreads` threads of the CTA (a warpgroup), ids 1..15
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// fp32 accumulate into global memory without a return value, two consecutive floats (8-byte aligned)
+__device__ __forceinline__ void red_add_v2(float* p, float a, float b) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(a), "f"(b) : "memory");
+}
+
+// 16 TMEM lanes x 64 fp32 columns in the accumulator-fragment layout: with q = lane / 4 and c = 2 * (lane % 4),
+// v[4i], v[4i+1] are columns 8i + c, 8i + c + 1 of lane (base + q) and v[4i+2], v[4i+3] the same columns of
+// lane (base + q + 8).  Four neighbouring threads hold 32 consecutive bytes of a row.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
 // byte offset of (row, 16-byte chunk) inside a [rows x 128 B] tile stored with the 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128_off(int row, int chunk16) { return row * 128 + ((chunk16 ^ (row & 7)) << 4); }
 
