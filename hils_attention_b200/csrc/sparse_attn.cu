@@ -6,11 +6,9 @@ namespace hils {
 int sparse_fwd_tc_launch(const SparseParams& p, cudaStream_t st);  // sparse_attn_tc.cu
 size_t sparse_fwd_cm_workspace(const SparseParams& p);             // sparse_attn_cm.cu
 int sparse_fwd_cm_launch(const SparseParams& p, void* workspace, cudaStream_t st);
-size_t sparse_bwd_tc_workspace(const SparseParams& p);
 int sparse_decode_launch(const void* q, const void* k, const void* v, const void* w, const int32_t* idx, const float* slope,
                          void* o, int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights, int S,
                          float scale, int mask_last, int dtype, cudaStream_t st);  // decode_attn.cu
-int sparse_bwd_tc_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st);
 size_t sparse_bwd_cm_workspace(const SparseParams& p);             // sparse_attn_cm.cu
 int sparse_bwd_cm_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st);
 
@@ -47,6 +45,7 @@ extern "C" size_t hils_sparse_attn_fwd_workspace_bytes(int B, int L, int T, int 
   if (dtype == HILS_BF16 && h_q > 0 && h_kv > 0 && h_q % h_kv == 0 && L > 4) {
     SparseParams p = make_params(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, B, L, T, h_q, h_kv, D, Dv, K, K,
                                  chunk_size, 1.f, 1);
+    if ((int64_t)(T / (chunk_size > 0 ? chunk_size : 1)) <= 4 * (int64_t)K) return 0;   // dense selections: the query-block-major kernel
     return sparse_fwd_cm_workspace(p);   // inverse index + fp32 output accumulator of the chunk-major kernel
   }
   return 0;
@@ -59,8 +58,6 @@ extern "C" size_t hils_sparse_attn_bwd_workspace_bytes(int B, int L, int T, int 
                                  chunk_size, 1.f, 1);
     const size_t cm = sparse_bwd_cm_workspace(p);
     if (cm > 0) return cm;
-    const size_t tc = sparse_bwd_tc_workspace(p);
-    if (tc > 0) return tc;
   }
   return (size_t)B * T * h_kv * (size_t)(D + Dv) * sizeof(float);
 }
@@ -84,6 +81,15 @@ extern "C" int hils_sparse_attn_fwd(const void* q, const void* k, const void* v,
     if (rc != HILS_ERR_UNSUPPORTED) return rc;
   }
   if (dtype == HILS_BF16) {  // tensor-core paths for the shapes they cover
+    // Two forward kernels.  Query-block-major (a block of 128 rows walks the union of its tokens' chunks, rows that did
+    // not select a chunk are masked): no gather, no scatter, but its work grows with the union, so it is the choice
+    // only where a token selects a large share of its candidates (few chunks per selected slot).  Chunk-major over
+    // gathered owner rows: every MMA row is a real pair, whatever the overlap; it pays a gather and a scatter.
+    const bool dense = (int64_t)(T / chunk_size) <= 4 * (int64_t)K;
+    if (dense) {
+      const int rc = sparse_fwd_tc_launch(p, st);
+      if (rc != HILS_ERR_UNSUPPORTED) return rc;
+    }
     const size_t need = L > 4 ? sparse_fwd_cm_workspace(p) : 0;
     if (need > 0) {
       if (!workspace || workspace_bytes < need) {
@@ -127,11 +133,10 @@ extern "C" int hils_sparse_attn_bwd(const void* q, const void* k, const void* v,
   if (dtype == HILS_BF16 && L > 0) {  // tensor-core path for the shapes it covers
     SparseParams p = make_params(q, k, v, weights, indices, slope, B, L, T, h_q, h_kv, D, Dv, K, num_weights,
                                  chunk_size, sm_scale, mask_last_token);
-    const bool cm = sparse_bwd_cm_workspace(p) > 0;
-    if (cm || sparse_bwd_tc_workspace(p) > 0) {
+    if (sparse_bwd_cm_workspace(p) > 0) {
       HILS_REQUIRE(q && k && v && weights && indices && d_o && d_q && d_k && d_v && d_w, "sparse_attn_bwd: null pointer");
       p.d_o = d_o; p.d_q = d_q; p.d_w = d_w;
-      const int rc = cm ? sparse_bwd_cm_launch(p, d_k, d_v, workspace, st) : sparse_bwd_tc_launch(p, d_k, d_v, workspace, st);
+      const int rc = sparse_bwd_cm_launch(p, d_k, d_v, workspace, st);
       if (rc != HILS_ERR_UNSUPPORTED) return rc;
       // the tensor-core path covers this shape but the pointers are not 16-byte aligned: no other kernel is
       // sized for the tensor-core workspace, so the call is refused rather than rerouted

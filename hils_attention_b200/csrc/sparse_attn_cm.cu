@@ -41,6 +41,71 @@ __device__ __forceinline__ bool cm_wait(uint64_t* b, uint32_t parity) {
   }
   return false;
 }
+// contiguous bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion counted in bytes on `bar`
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(umma::smem_u32(dst)), "l"(src), "r"(bytes), "r"(umma::smem_u32(bar))
+               : "memory");
+}
+// TMA gather of four rows of a 2-D tensor (box = 64 columns x 1 row, 128-byte swizzle): the rows land as four
+// consecutive 128-byte rows at `dst`, swizzled by their shared-memory address like a tiled load of the same place.
+__device__ __forceinline__ void tma_gather4(void* dst, const CUtensorMap* map, uint64_t* bar, int col, int r0, int r1, int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(umma::smem_u32(dst)), "l"(map), "r"(umma::smem_u32(bar)), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+      : "memory");
+}
+// ---- scatter of accumulator tiles -------------------------------------------------------------------------------
+// A tile's rows belong to different tokens, so its fp32 result is ADDED to global accumulator rows.  What bounds these
+// adds is the number of requests the L2 atomic units see, not their bytes: 16-byte adds in which neighbouring lanes
+// cover whole rows run about three times faster than 8-byte adds issued straight from the accumulator-fragment
+// layout, and one reduce per row through the bulk-copy unit is slower again because that unit also carries the row
+// gathers.  A single warp cannot issue the adds fast enough either.  Hence every row warp scatters its own 32 rows:
+// each lane copies SLW columns of its row from TMEM into the warp's staging rows in shared memory, then the warp reads
+// them back row by row (SLW/4 lanes per row) and issues red.global.add.v4.f32.  No barrier beyond __syncwarp.
+__device__ __forceinline__ void red_add_v4(float* p, float4 v) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+template <int SLW>
+struct StgGeom {
+  static constexpr int kStride = SLW * 4 + 16;      // bytes per staged row (+16 keeps the 16-byte accesses conflict-free)
+  static constexpr int kWarpBytes = 32 * kStride;   // staging rows of one warp
+};
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {   // 16 fp32 columns of this thread's TMEM lane
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                 "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr));
+}
+// One warp: columns col0 .. col0 + SLW - 1 of its 32 TMEM lanes (`taddr` = this lane's address of column col0) are
+// added to the accumulator rows `rowt` of the lanes (-1: no row).  `stg` = the warp's staging rows.
+template <int SLW>
+__device__ __forceinline__ void scatter_slice(uint8_t* stg, uint32_t taddr, int rowt, float* acc, int D, int col0, int lane) {
+  constexpr int LPR = SLW / 4, RPI = 32 / LPR;      // lanes per row, rows per instruction
+  float ov[SLW];
+  if (SLW == 16) {
+    tmem_ld16(taddr, ov);
+  } else {
+#pragma unroll
+    for (int cb = 0; cb < SLW / 32; ++cb) umma::tmem_ld32(taddr + cb * 32, ov + cb * 32);
+  }
+  umma::tmem_ld_wait();
+  __syncwarp();                                      // the previous slice has been read back by every lane
+  uint8_t* mine = stg + lane * StgGeom<SLW>::kStride;
+#pragma unroll
+  for (int i = 0; i < SLW / 4; ++i)
+    *reinterpret_cast<float4*>(mine + i * 16) = make_float4(ov[4 * i], ov[4 * i + 1], ov[4 * i + 2], ov[4 * i + 3]);
+  __syncwarp();
+  const int sub = lane / LPR, piece = lane % LPR;
+#pragma unroll
+  for (int it = 0; it < 32 / RPI; ++it) {
+    const int row = it * RPI + sub;
+    const int t = __shfl_sync(0xffffffffu, rowt, row);
+    const float4 v = *reinterpret_cast<const float4*>(stg + row * StgGeom<SLW>::kStride + piece * 16);
+    if (t >= 0) red_add_v4(acc + (int64_t)t * D + col0 + piece * 4, v);
+  }
+}
 // keeps the first failure: code = 1000 * (wait site) + tile
 __device__ __forceinline__ void cm_fail(int code) { atomicCAS(&g_cm_status, 0, code); }
 // one poll: has the phase with this parity completed?
@@ -59,38 +124,58 @@ constexpr int kEntShift = 10;                 // entry = token << 10 | slot
 constexpr int kEntSlotMask = (1 << kEntShift) - 1;
 
 // =================================================================================================
-// inverse index: pairs (token, slot) grouped by (batch, kv head, chunk)
+// inverse index: pairs (token, slot) grouped by (batch, kv head, chunk), with their weights
 // =================================================================================================
 // Order inside a chunk's list: token tiles ascending; inside a tile tokens ascending, slots ascending.
 // It is fixed by the index alone (no atomics decide it), so everything summed in list order is deterministic.
+// The pairs' weights (one per query head of the group) are copied into a list of the same order, so the
+// attention kernels stream entries and weights from contiguous memory instead of chasing token -> weight.
+constexpr int kListAlign = 8;    // chunk lists start at multiples of 8 entries (16-byte aligned bulk copies)
+constexpr int kTB = 4;           // tiles per metadata block
+constexpr int kMS = 4;           // metadata slots in shared memory
+
 struct InvIndex {
-  const int32_t* list;    // [B*h_kv][L*K]
+  const int32_t* list;    // [B*h_kv][cap]      entries (token << 10 | slot)
+  const bf16* wlist;      // [B*h_kv][cap * G]  weights of the entries' G rows
   const uint32_t* coff;   // [B*h_kv][nchunk + 1] start of each chunk's list inside the (b, h) segment
+  const uint32_t* tot;    // [B*h_kv][nchunk]   entries of each chunk
+  size_t cap;             // entries per (b, h) segment
 };
 
 struct InvLayout {
-  size_t cnt_off, tot_off, coff_off, list_off, total;
+  size_t cnt_off, tot_off, coff_off, list_off, wlist_off, total, cap;
   int TT, ntile;
 };
 
-static InvLayout inv_layout(int B, int L, int h_kv, int K, int nchunk) {
+static InvLayout inv_layout(int B, int L, int h_kv, int G, int K, int nchunk) {
   InvLayout l;
   int tt = (nchunk + K - 1) / K;              // keeps the per-tile histograms no larger than the list
   l.TT = max(128, (tt + 31) / 32 * 32);
   l.ntile = (L + l.TT - 1) / l.TT;
   const size_t bh = (size_t)B * h_kv;
   auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  l.cap = ((size_t)L * K + (size_t)kListAlign * nchunk + 63) & ~(size_t)63;
   l.cnt_off = 0;
   l.tot_off = up(l.cnt_off + bh * l.ntile * nchunk * 4);
   l.coff_off = up(l.tot_off + bh * nchunk * 4);
   l.list_off = up(l.coff_off + bh * (nchunk + 1) * 4);
-  l.total = up(l.list_off + bh * (size_t)L * K * 4);
+  l.wlist_off = up(l.list_off + bh * l.cap * 4 + 256);            // + slack: block copies round their size up to 16 bytes
+  l.total = up(l.wlist_off + bh * l.cap * G * 2 + 256);
   return l;
 }
 
-// ids of one token's slots k0 + lane; a row's list ends at its first negative id
+struct InvFill {
+  int32_t* list;
+  bf16* wlist;
+  const bf16* w;        // (B, L, h_q, num_weights)
+  int G, num_weights;
+};
+
+// ids of one token's slots k0 + lane; a row's list ends at its first negative id.  wrow: weights of (token, first
+// query head of the group); w0: its entry for slot k, loaded ahead by the caller.
 template <bool kFill>
-__device__ __forceinline__ bool inv_step(int id, bool in_k, int t, int k, int nchunk, uint32_t* hist, int32_t* list, int lane) {
+__device__ __forceinline__ bool inv_step(int id, bool in_k, int t, int k, int nchunk, uint32_t* hist, const InvFill& f,
+                                         const bf16* wrow, bf16 w0, int lane) {
   const unsigned neg = __ballot_sync(0xffffffffu, !in_k || id < 0);
   const bool live = neg == 0u || lane < (__ffs(neg) - 1);
   const bool take = live && id < nchunk;
@@ -104,7 +189,10 @@ __device__ __forceinline__ bool inv_step(int id, bool in_k, int t, int k, int nc
     if (take) pos = hist[id] + rank;
     __syncwarp();
     if (take) {
-      list[pos] = (t << kEntShift) | k;
+      f.list[pos] = (t << kEntShift) | k;
+      bf16* wl = f.wlist + (size_t)pos * f.G;
+      wl[0] = w0;
+      for (int g = 1; g < f.G; ++g) wl[g] = wrow[(size_t)g * f.num_weights + k];
       if (rank == __popc(peers) - 1) hist[id] = pos + 1;
     }
     __syncwarp();
@@ -116,7 +204,7 @@ __device__ __forceinline__ bool inv_step(int id, bool in_k, int t, int k, int nc
 // kFill = true: the same walk with the histogram started at each chunk's write position.
 template <bool kFill>
 __global__ void __launch_bounds__(32) inv_walk_kernel(const int32_t* __restrict__ idx, uint32_t* __restrict__ cnt,
-                                                      const uint32_t* __restrict__ coff, int32_t* __restrict__ list, int L,
+                                                      const uint32_t* __restrict__ coff, InvFill f, size_t cap, int L,
                                                       int h_kv, int K, int nchunk, int TT, int ntile) {
   extern __shared__ uint32_t hist[];
   const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z, lane = threadIdx.x;
@@ -124,25 +212,40 @@ __global__ void __launch_bounds__(32) inv_walk_kernel(const int32_t* __restrict_
   uint32_t* my_cnt = cnt + (bh * ntile + tile) * nchunk;
   for (int c = lane; c < nchunk; c += 32) hist[c] = kFill ? coff[bh * (nchunk + 1) + c] + my_cnt[c] : 0u;
   __syncwarp();
-  int32_t* my_list = list + bh * (size_t)L * K;
+  if (kFill) {
+    f.list += bh * cap;
+    f.wlist += bh * cap * f.G;
+  }
   const int t0 = tile * TT, t1 = min(L, t0 + TT);
   const int32_t* base = idx + (((size_t)b * L) * h_kv + h) * K;
   const size_t tstride = (size_t)h_kv * K;
+  const int h_q = h_kv * f.G;
+  const bf16* wbase = kFill ? f.w + (((size_t)b * L) * h_q + (size_t)h * f.G) * f.num_weights : nullptr;
+  const size_t wstride = (size_t)h_q * f.num_weights;
+  const bf16 zero = __float2bfloat16_rn(0.f);
   if (K <= 32) {
-    for (int t = t0; t < t1; t += 4) {   // four tokens' ids in flight
+    for (int t = t0; t < t1; t += 4) {   // four tokens' ids (and weights) in flight
       int v[4];
+      bf16 wv[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = (t + u < t1 && lane < K) ? __ldg(base + (size_t)(t + u) * tstride + lane) : -1;
+      for (int u = 0; u < 4; ++u) {
+        const bool in = t + u < t1 && lane < K;
+        v[u] = in ? __ldg(base + (size_t)(t + u) * tstride + lane) : -1;
+        wv[u] = (kFill && in) ? wbase[(size_t)(t + u) * wstride + lane] : zero;
+      }
 #pragma unroll
       for (int u = 0; u < 4; ++u)
-        if (t + u < t1) inv_step<kFill>(v[u], lane < K, t + u, lane, nchunk, hist, my_list, lane);
+        if (t + u < t1)
+          inv_step<kFill>(v[u], lane < K, t + u, lane, nchunk, hist, f, kFill ? wbase + (size_t)(t + u) * wstride : nullptr, wv[u], lane);
     }
   } else {
     for (int t = t0; t < t1; ++t)
       for (int k0 = 0; k0 < K; k0 += 32) {
         const int k = k0 + lane;
         const int id = k < K ? __ldg(base + (size_t)t * tstride + k) : -1;
-        if (inv_step<kFill>(id, k < K, t, k, nchunk, hist, my_list, lane)) break;
+        const bf16* wrow = kFill ? wbase + (size_t)t * wstride : nullptr;
+        const bf16 w0 = (kFill && k < K) ? wrow[k] : zero;
+        if (inv_step<kFill>(id, k < K, t, k, nchunk, hist, f, wrow, w0, lane)) break;
       }
   }
   if (!kFill) {
@@ -167,7 +270,7 @@ __global__ void __launch_bounds__(256) inv_scan_kernel(uint32_t* __restrict__ cn
   tot[bh * nchunk + c] = run;
 }
 
-// per (b, h): exclusive prefix of the chunk totals
+// per (b, h): exclusive prefix of the chunk totals, each rounded up to the list alignment
 __global__ void __launch_bounds__(256) inv_offsets_kernel(const uint32_t* __restrict__ tot, uint32_t* __restrict__ coff, int nchunk) {
   __shared__ uint32_t wsum[8];
   __shared__ uint32_t carry_s;
@@ -177,7 +280,7 @@ __global__ void __launch_bounds__(256) inv_offsets_kernel(const uint32_t* __rest
   __syncthreads();
   for (int c0 = 0; c0 < nchunk; c0 += 256) {
     const int c = c0 + tid;
-    const uint32_t v = c < nchunk ? tot[bh * nchunk + c] : 0u;
+    const uint32_t v = c < nchunk ? ((tot[bh * nchunk + c] + kListAlign - 1) / kListAlign) * kListAlign : 0u;
     uint32_t inc = v;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -197,48 +300,53 @@ __global__ void __launch_bounds__(256) inv_offsets_kernel(const uint32_t* __rest
 }
 
 static int build_inverse_index(const SparseParams& p, void* workspace, InvIndex* ix, cudaStream_t st) {
-  const int nchunk = p.T / 64;
-  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.K, nchunk);
+  const int nchunk = p.T / 64, G = p.h_q / p.h_kv;
+  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, G, p.K, nchunk);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   uint32_t* cnt = reinterpret_cast<uint32_t*>(ws + l.cnt_off);
   uint32_t* tot = reinterpret_cast<uint32_t*>(ws + l.tot_off);
   uint32_t* coff = reinterpret_cast<uint32_t*>(ws + l.coff_off);
-  int32_t* list = reinterpret_cast<int32_t*>(ws + l.list_off);
+  InvFill f;
+  f.list = reinterpret_cast<int32_t*>(ws + l.list_off);
+  f.wlist = reinterpret_cast<bf16*>(ws + l.wlist_off);
+  f.w = static_cast<const bf16*>(p.w);
+  f.G = G;
+  f.num_weights = p.num_weights;
   const size_t smem = (size_t)nchunk * 4;
   if (smem > 48 * 1024) {
     cudaFuncSetAttribute(inv_walk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(inv_walk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   }
   dim3 gw(l.ntile, p.h_kv, p.B);
-  inv_walk_kernel<false><<<gw, 32, smem, st>>>(p.idx, cnt, nullptr, nullptr, p.L, p.h_kv, p.K, nchunk, l.TT, l.ntile);
+  inv_walk_kernel<false><<<gw, 32, smem, st>>>(p.idx, cnt, nullptr, f, l.cap, p.L, p.h_kv, p.K, nchunk, l.TT, l.ntile);
   inv_scan_kernel<<<dim3((nchunk + 255) / 256, p.B * p.h_kv), 256, 0, st>>>(cnt, tot, nchunk, l.ntile);
   inv_offsets_kernel<<<p.B * p.h_kv, 256, 0, st>>>(tot, coff, nchunk);
-  inv_walk_kernel<true><<<gw, 32, smem, st>>>(p.idx, cnt, coff, list, p.L, p.h_kv, p.K, nchunk, l.TT, l.ntile);
+  inv_walk_kernel<true><<<gw, 32, smem, st>>>(p.idx, cnt, coff, f, l.cap, p.L, p.h_kv, p.K, nchunk, l.TT, l.ntile);
   HILS_LAUNCH_CHECK("sparse_attn inverse index");
-  ix->list = list;
+  ix->list = f.list;
+  ix->wlist = f.wlist;
   ix->coff = coff;
+  ix->tot = tot;
+  ix->cap = l.cap;
   return HILS_OK;
 }
 
 // =================================================================================================
 // forward
 // =================================================================================================
-// 2 row warpgroups + MMA/TMA warp + 2 producer warps: 11 warps, at most 3 per scheduler, which leaves the row
-// threads 168 registers (a 13-warp CTA would cap every thread at 128)
-constexpr int kCmProducers = 64;
-constexpr int kCmThreads = 288 + kCmProducers;
+// 2 row warpgroups + MMA/TMA warp + gather warp: 10 warps, at most 3 per scheduler, which leaves the row threads 168
+// registers (a 13-warp CTA would cap every thread at 128)
+constexpr int kCmThreads = 320;
 
 template <int D>
 __global__ void __launch_bounds__(kCmThreads, 1) sparse_fwd_cm_kernel(SparseParams p, InvIndex ix, float* __restrict__ o_acc,
                                                                       const __grid_constant__ CUtensorMap tmK,
-                                                                      const __grid_constant__ CUtensorMap tmV) {
+                                                                      const __grid_constant__ CUtensorMap tmV,
+                                                                      const __grid_constant__ CUtensorMap tmQ) {
   constexpr int DB = D / 64;
   constexpr int QBYTES = DB * 16384;     // gathered Q tile, 128 x D
   constexpr int KVBYTES = DB * 8192;     // K or V tile, 64 x D
-  constexpr int NQ = 2;                  // Q tile ring
-  constexpr int PIECES = D / 8;          // 16-byte pieces per row
-  constexpr int RPP = kCmProducers / PIECES;   // rows per producer pass
-  constexpr int NPASS = 128 / RPP;
+  constexpr int NQ = (D == 64) ? 4 : 2;  // Q tile ring (gathers of several tiles in flight)
   constexpr int TM_COLS = (D == 64) ? 256 : 512;   // S: 2 x 64 columns, O: 2 x D columns
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -246,10 +354,14 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_fwd_cm_kernel(SparsePara
   uint8_t* Vs = Ks + KVBYTES;
   uint8_t* Qs = Vs + KVBYTES;            // NQ stages
   uint8_t* Ps = Qs + NQ * QBYTES;        // 2 x [128 x 64] bf16
+  uint8_t* Stg = Ps + 2 * 16384;         // staging rows of the 8 row warps (32 rows x 64 fp32 columns each)
 
-  __shared__ uint64_t kv_full, q_full[NQ], q_free[NQ], s_full[2], p_full[2], o_full[2], o_free[2];
+  __shared__ uint64_t kv_full, q_full[4], q_free[4], s_full[2], p_full[2], o_full[2], o_free[2];
   __shared__ uint32_t tmem_base_s;
-  __shared__ int tgt_s[2][2][128];       // [warpgroup][tile parity][row]: output row of each tile row, -1 = none
+  // metadata of the chunk's owner rows, streamed in blocks of kTB tiles by bulk copies: list entries and weights
+  __shared__ __align__(16) int ent_ring[kMS][kTB * 128];
+  __shared__ __align__(16) bf16 w_ring[kMS][kTB * 128];
+  __shared__ uint64_t meta_full[kMS];
   __shared__ volatile int abort_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -257,17 +369,21 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_fwd_cm_kernel(SparsePara
   const int c = blockIdx.x;              // early chunks carry the longest lists and start first
   const int h = blockIdx.y, b = blockIdx.z;
   const size_t bh = (size_t)b * p.h_kv + h;
-  const uint32_t beg = ix.coff[bh * (nchunk + 1) + c], end = ix.coff[bh * (nchunk + 1) + c + 1];
-  const int n_ent = (int)(end - beg);
+  const uint32_t beg = ix.coff[bh * (nchunk + 1) + c];
+  const int n_ent = (int)ix.tot[bh * nchunk + c];
   if (n_ent == 0 || cm_failed_before()) return;   // nobody selected this chunk, or an earlier CTA's wait expired
-  const int G = p.h_q / p.h_kv, QB = 128 / G;
+  // G divides 128, so it is a power of two: rows map to (pair, group member) by shift and mask (a division by a
+  // run-time G in the gather loop cost more than the copies themselves)
+  const int G = p.h_q / p.h_kv, gs = 31 - __clz(G), QB = 128 >> gs;
   const int ntile = (n_ent + QB - 1) / QB;
-  const int32_t* lst = ix.list + bh * (size_t)p.L * p.K + beg;
+  const int32_t* lst = ix.list + bh * ix.cap + beg;
+  const bf16* wl = ix.wlist + (bh * ix.cap + beg) * G;
 
   if (tid == 0) {
     mbar_init(&kv_full, 1);
+    for (int s = 0; s < kMS; ++s) mbar_init(&meta_full[s], 1);
     for (int s = 0; s < NQ; ++s) {
-      mbar_init(&q_full[s], kCmProducers);
+      mbar_init(&q_full[s], 1);
       mbar_init(&q_free[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -286,48 +402,57 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_fwd_cm_kernel(SparsePara
   const uint32_t tmem = tmem_base_s;
   const uint32_t tS = tmem, tO = tmem + 128;
 
-  if (warp >= 9) {
-    // =============================== gather producers ===========================================
-    const int pt = tid - 9 * 32;                       // 0..kCmProducers-1
-    const int piece = pt % PIECES, row0 = pt / PIECES;
-    const uint32_t qs_base = smem_u32(Qs);
-    const bf16* qbase = static_cast<const bf16*>(p.q) + ((size_t)b * p.L * p.h_q + (size_t)h * G) * D + piece * 8;
+  if (warp == 9) {
+    // =============================== gather producer (one warp) =================================
+    // The rows of a tile are fetched by TMA gather instructions, four rows each: lane l issues the gathers of rows
+    // 4 l .. 4 l + 3 (one per 64-column block).  The TMA unit keeps the requests of several tiles in flight; this
+    // warp only reads the tile's list entries and waits for a free ring stage.
+    // Metadata block m = tiles kTB m .. kTB m + kTB - 1, slot m % kMS, fetched by bulk copies.  Block m + 1 is requested
+    // when block m starts: its slot was last used by block m - 3, i.e. by tiles up to kTB (m - 2) - 1.  The ring wait of
+    // tile kTB m has passed by then, which puts the row threads past tile kTB m - NQ - 2 at least, so with NQ <= 4 no
+    // thread still reads that slot or waits on its barrier (a waiter two phases behind would never wake).
+    const int TBQ = kTB * QB, nblk = (ntile + kTB - 1) / kTB;
+    auto request_meta = [&](int m) {
+      const int e0 = m * TBQ, ne = min(n_ent - e0, TBQ);
+      const uint32_t eb = (uint32_t)(ne * 4 + 15) & ~15u, wb = (uint32_t)(ne * G * 2 + 15) & ~15u;
+      mbar_expect_tx(&meta_full[m % kMS], eb + wb);
+      bulk_load(ent_ring[m % kMS], lst + e0, eb, &meta_full[m % kMS]);
+      bulk_load(w_ring[m % kMS], wl + (size_t)e0 * G, wb, &meta_full[m % kMS]);
+    };
+    if (lane == 0) {
+      request_meta(0);
+      if (nblk > 1) request_meta(1);
+    }
+    const int row_base = (b * p.L) * p.h_q + h * G;      // tensor row of (token 0, first query head of the group)
     bool ok = true;
     for (int j = 0; j < ntile; ++j) {
       const int s = j % NQ;
       if (j >= NQ) {
         ok = cm_wait(&q_free[s], ((j / NQ) - 1) & 1) && !abort_s;
-        if (!ok) break;
+        if (!ok) { cm_fail(4010000 + j); break; }
       }
-      int ent[NPASS];
+      const int m = j / kTB;
+      if (j % kTB == 0) {
+        if (m >= 1 && m + 1 < nblk && lane == 0) request_meta(m + 1);
+        ok = cm_wait(&meta_full[m % kMS], (m / kMS) & 1);
+        if (!ok) { cm_fail(4011000 + j); break; }
+      }
+      const int* ents = ent_ring[m % kMS] + (j % kTB) * QB;
+      int rr[4];
 #pragma unroll
-      for (int i = 0; i < NPASS; ++i) {
-        const int e = j * QB + (i * RPP + row0) / G;
-        ent[i] = e < n_ent ? __ldg(lst + e) : -1;
+      for (int i = 0; i < 4; ++i) {
+        const int row = 4 * lane + i;
+        const bool live = j * QB + (row >> gs) < n_ent;      // rows past the end of the list fetch row 0; their P is zero
+        rr[i] = live ? row_base + (ents[row >> gs] >> kEntShift) * p.h_q + (row & (G - 1)) : row_base;
       }
+      if (lane == 0) mbar_expect_tx(&q_full[s], QBYTES);
+      __syncwarp();
 #pragma unroll
-      for (int i = 0; i < NPASS; ++i) {
-        const int row = i * RPP + row0;
-        const bool live = ent[i] >= 0;
-        const int t = live ? (ent[i] >> kEntShift) : 0;
-        const bf16* src = qbase + ((size_t)t * p.h_q + (row % G)) * D;
-        cp_async16(qs_base + s * QBYTES + (piece >> 3) * 16384 + sw128_off(row, piece & 7), src, live ? 16u : 0u);
-      }
-      cp_async_commit();
-      if (j >= 1) {
-        cp_async_wait<1>();
-        fence_async_smem();
-        mbar_arrive(&q_full[(j - 1) % NQ]);
+      for (int db = 0; db < DB; ++db) {
+        tma_gather4(Qs + s * QBYTES + db * 16384 + lane * 512, &tmQ, &q_full[s], db * 64, rr[0], rr[1], rr[2], rr[3]);
       }
     }
-    cp_async_wait<0>();
-    if (ok) {
-      fence_async_smem();
-      mbar_arrive(&q_full[(ntile - 1) % NQ]);
-    } else if (lane == 0) {
-      abort_s = 1;
-      atomicExch(&g_cm_status, 401);
-    }
+    if (!ok && lane == 0) abort_s = 1;
   } else if (warp == 8) {
     // =============================== TMA (once) + MMA issuer ====================================
     if (lane == 0) {
@@ -362,12 +487,13 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_fwd_cm_kernel(SparsePara
         if (j + 1 < ntile) {
           const int s1 = (j + 1) % NQ;
           ok = cm_wait(&q_full[s1], ((j + 1) / NQ) & 1);
-          if (!ok) break;
+          if (!ok) { cm_fail(4021000 + j); break; }
           tc_fence_after();
           issue_qk(s1, sb ^ 1);      // its S buffer was consumed by tile j - 1 (p_full waited for below, last iteration)
         }
         ok = cm_wait(&p_full[sb], u & 1);
-        if (ok && u >= 1) ok = cm_wait(&o_free[sb], (u - 1) & 1);   // the O buffer's previous tile has been read out
+        if (!ok) cm_fail(4022000 + j);
+        if (ok && u >= 1) { ok = cm_wait(&o_free[sb], (u - 1) & 1); if (!ok) cm_fail(4023000 + j); }  // the O buffer's previous tile has been read out
         if (!ok) break;
         tc_fence_after();
         {
@@ -379,29 +505,31 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_fwd_cm_kernel(SparsePara
         }
         mma_commit(&o_full[sb]);
       }
-      if (!ok) { abort_s = 1; atomicExch(&g_cm_status, 402); }
+      if (!ok) { abort_s = 1; cm_fail(4020000); }
     }
   } else {
     // =============================== row warpgroups ==============================================
     const int r = tid & 127, wg = tid >> 7;                 // warpgroup wg takes tiles wg, wg + 2, ... and buffers wg
-    const int g = r % G, hq = h * G + g;
+    const int g = r & (G - 1), hq = h * G + g, rp = r >> gs;
     const float scale_log2 = p.scale * kLog2e;
     const float slope = p.slope ? p.slope[hq] : 0.f;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const bf16* wbase = static_cast<const bf16*>(p.w);
     uint8_t* prow = Ps + wg * 16384;
     bool ok = true;
     for (int j = wg, u = 0; j < ntile; j += 2, ++u) {
-      const int e = j * QB + r / G;
-      const bool live = e < n_ent;
-      const int ent = live ? __ldg(lst + e) : 0;
-      const int t = ent >> kEntShift, k = ent & kEntSlotMask;
-      const int64_t rowi = ((int64_t)b * p.L + t) * p.h_q + hq;
-      const float wv = live ? to_f(wbase[rowi * p.num_weights + k]) : 0.f;
       ok = cm_wait(&s_full[wg], u & 1);
+      if (!ok) cm_fail(4031000 + j);
       ok = __all_sync(0xffffffffu, ok) && !abort_s;
       if (!ok) break;
       tc_fence_after();
+      const int m = j / kTB;
+      ok = cm_wait(&meta_full[m % kMS], (m / kMS) & 1);
+      ok = __all_sync(0xffffffffu, ok) && !abort_s;
+      if (!ok) break;
+      const bool live = j * QB + rp < n_ent;
+      const int ent = live ? ent_ring[m % kMS][(j % kTB) * QB + rp] : 0;
+      const float wv = live ? to_f(w_ring[m % kMS][(j % kTB) * 128 + r]) : 0.f;
+      const int rowt = live ? (int)(((int64_t)b * p.L + (ent >> kEntShift)) * p.h_q + hq) : -1;
       float sv[64];
       tmem_ld32(tS + lane_base + wg * 64, sv);
       tmem_ld32(tS + lane_base + wg * 64 + 32, sv + 32);
@@ -429,40 +557,22 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_fwd_cm_kernel(SparsePara
       } else {
         store_row_zero_sw128(prow, r);
       }
-      tgt_s[wg][u & 1][r] = live ? (int)rowi : -1;
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(&p_full[wg]);
-      // all 128 arrivals on p_full also mean that tgt_s of this tile is complete (a bounded wait, unlike bar.sync)
-      ok = cm_wait(&p_full[wg], u & 1) && cm_wait(&o_full[wg], u & 1);
+      ok = cm_wait(&o_full[wg], u & 1);
+      if (!ok) cm_fail(4032000 + j);
       ok = __all_sync(0xffffffffu, ok) && !abort_s;
       if (!ok) break;
       tc_fence_after();
-      // O tile -> fp32 accumulator rows: 4 neighbouring lanes add 32 consecutive bytes of one row
+      // O tile -> fp32 accumulator rows of the tokens, 64 columns at a time
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int ra = (warp & 3) * 32 + half * 16 + (lane >> 2);
-        const int ta = tgt_s[wg][u & 1][ra], tb = tgt_s[wg][u & 1][ra + 8];
-        float* pa = o_acc + (int64_t)(ta < 0 ? 0 : ta) * D + 2 * (lane & 3);
-        float* pb = o_acc + (int64_t)(tb < 0 ? 0 : tb) * D + 2 * (lane & 3);
-#pragma unroll
-        for (int cb = 0; cb < D / 64; ++cb) {
-          float ov[32];
-          tmem_ld_16x256b_x8(tO + lane_base + ((uint32_t)(half * 16) << 16) + wg * D + cb * 64, ov);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (ta >= 0) red_add_v2(pa + cb * 64 + 8 * i, ov[4 * i], ov[4 * i + 1]);
-            if (tb >= 0) red_add_v2(pb + cb * 64 + 8 * i, ov[4 * i + 2], ov[4 * i + 3]);
-          }
-        }
-      }
+      for (int sl = 0; sl < D / 64; ++sl)
+        scatter_slice<64>(Stg + warp * StgGeom<64>::kWarpBytes, tO + lane_base + wg * D + sl * 64, rowt, o_acc, D, sl * 64, lane);
       tc_fence_before();
       mbar_arrive(&o_free[wg]);
-      // tgt_s[wg][u & 1] is rewritten two tiles later, after every thread has passed the p_full wait of the next
-      // tile, i.e. after every thread has finished this read-out
     }
-    if (!ok && lane == 0) { abort_s = 1; atomicExch(&g_cm_status, 403); }
+    if (!ok && lane == 0) { abort_s = 1; cm_fail(4030000); }
   }
   tc_fence_before();
   __syncthreads();
@@ -491,12 +601,15 @@ static bool cm_shape_ok(const SparseParams& p) {
   return true;
 }
 
-static size_t cm_fwd_smem(int D) { return 1024 + 2 * (size_t)(D / 64) * 8192 + 2 * (size_t)(D / 64) * 16384 + 2 * 16384; }
+static size_t cm_fwd_smem(int D) {
+  const int NQ = (D == 64) ? 4 : 2;
+  return 1024 + 2 * (size_t)(D / 64) * 8192 + (size_t)NQ * (D / 64) * 16384 + 2 * 16384 + 8 * (size_t)StgGeom<64>::kWarpBytes;
+}
 
 // workspace of the chunk-major forward: inverse index + fp32 output accumulator (0: shape outside this path)
 size_t sparse_fwd_cm_workspace(const SparseParams& p) {
   if (!cm_shape_ok(p)) return 0;
-  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.K, p.T / 64);
+  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.h_q / p.h_kv, p.K, p.T / 64);
   return l.total + (size_t)p.B * p.L * p.h_q * p.D * sizeof(float);
 }
 
@@ -505,7 +618,7 @@ int sparse_fwd_cm_launch(const SparseParams& p, void* workspace, cudaStream_t st
   if (!cm_shape_ok(p) || !workspace) return HILS_ERR_UNSUPPORTED;
   if (((uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o | (uintptr_t)workspace) & 15) return HILS_ERR_UNSUPPORTED;
   const int D = p.D, nchunk = p.T / 64;
-  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.K, nchunk);
+  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.h_q / p.h_kv, p.K, nchunk);
   InvIndex ix;
   if (int rc = build_inverse_index(p, workspace, &ix, st)) return rc;
   float* o_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + l.total);
@@ -515,14 +628,16 @@ int sparse_fwd_cm_launch(const SparseParams& p, void* workspace, cudaStream_t st
   CUtensorMap tmK, tmV;
   if (int rc = make_tmap_bf16_rows(&tmK, p.k, (uint64_t)p.B * p.T, (uint64_t)p.h_kv * D, (uint64_t)p.h_kv * D, 64)) return rc;
   if (int rc = make_tmap_bf16_rows(&tmV, p.v, (uint64_t)p.B * p.T, (uint64_t)p.h_kv * D, (uint64_t)p.h_kv * D, 64)) return rc;
+  CUtensorMap tmQ;   // rows = (batch, token, query head), one row per box: the source of the row gathers
+  if (int rc = make_tmap_bf16_rows(&tmQ, p.q, (uint64_t)p.B * p.L * p.h_q, D, D, 1)) return rc;
   const size_t smem = cm_fwd_smem(D);
   dim3 grid(nchunk, p.h_kv, p.B);
   if (D == 64) {
     cudaFuncSetAttribute(sparse_fwd_cm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sparse_fwd_cm_kernel<64><<<grid, kCmThreads, smem, st>>>(p, ix, o_acc, tmK, tmV);
+    sparse_fwd_cm_kernel<64><<<grid, kCmThreads, smem, st>>>(p, ix, o_acc, tmK, tmV, tmQ);
   } else {
     cudaFuncSetAttribute(sparse_fwd_cm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sparse_fwd_cm_kernel<128><<<grid, kCmThreads, smem, st>>>(p, ix, o_acc, tmK, tmV);
+    sparse_fwd_cm_kernel<128><<<grid, kCmThreads, smem, st>>>(p, ix, o_acc, tmK, tmV, tmQ);
   }
   cm_round_kernel<<<(unsigned)((n_out / 8 + 255) / 256), 256, 0, st>>>(o_acc, static_cast<bf16*>(p.o), (int64_t)(n_out / 8));
   HILS_LAUNCH_CHECK("sparse_attn_fwd (chunk-major path)");
@@ -545,17 +660,19 @@ int sparse_fwd_cm_launch(const SparseParams& p, void* workspace, cudaStream_t st
 template <int D>
 __global__ void __launch_bounds__(kCmThreads, 1) sparse_bwd_cm_kernel(SparseParams p, InvIndex ix, float* __restrict__ dq_acc,
                                                                       const __grid_constant__ CUtensorMap tmK,
-                                                                      const __grid_constant__ CUtensorMap tmV) {
+                                                                      const __grid_constant__ CUtensorMap tmV,
+                                                                      const __grid_constant__ CUtensorMap tmQ,
+                                                                      const __grid_constant__ CUtensorMap tmdO) {
   constexpr int DB = D / 64;
   constexpr int QBYTES = DB * 16384;
   constexpr int KVBYTES = DB * 8192;
   constexpr int NSB = (D == 64) ? 2 : 1;   // S/dP accumulators in TMEM
   constexpr int NDQ = (D == 64) ? 2 : 1;   // dQ tiles in TMEM
   constexpr int NDS = (D == 64) ? 2 : 1;   // dS / wP tiles in shared memory
-  constexpr int NQ = (D == 64) ? 3 : 2;    // Q / dO ring; NSB % NQ != 0, so the ring stage of tile j + NSB never waits on tile j
-  constexpr int PIECES = D / 8;
-  constexpr int RPP = kCmProducers / PIECES;
-  constexpr int NPASS = 128 / RPP;
+  constexpr int NQ = (D == 64) ? 3 : 2;    // Q / dO ring (> NSB: tile j + NSB can be gathered while tile j is in use)
+  constexpr int SLW = (D == 64) ? 32 : 16; // columns of a staged dQ slice (what shared memory is left for)
+  constexpr int NS = D / SLW;
+  constexpr int PIECES = D / 8;            // 16-byte pieces per row
   constexpr bool kStacked = (D == 64);
   // TMEM columns: S/dP [0, NSB*128), dQ [NSB*128, +NDQ*D), dK (and dV) after them
   constexpr uint32_t C_DQ = NSB * 128, C_DK = C_DQ + NDQ * D, C_DV = C_DK + D;
@@ -567,19 +684,25 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_bwd_cm_kernel(SparsePara
   uint8_t* Vs = Ks + KVBYTES;
   uint8_t* dSs = Vs + KVBYTES;             // NDS x 16 KB
   uint8_t* Pws = dSs + NDS * 16384;        // NDS x 16 KB
+  uint8_t* StgB = Pws + NDS * 16384;       // staging rows of the 8 row warps (32 rows x SLW fp32 columns each)
 
-  __shared__ uint64_t kv_full, qdo_full[3], qdo_free[3], sd_full[2], ds_full[2], ds_free[2], dq_full[2], dq_free[2], all_done;
+  __shared__ uint64_t kv_full, qdo_full[4], qdo_free[4], sd_full[2], ds_full[2], ds_free[2], dq_full[2], dq_free[2], all_done;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int tgt_s[2][2][128];
+  // metadata of the chunk's owner rows, streamed in blocks of kTB tiles by bulk copies: list entries and weights
+  __shared__ __align__(16) int ent_ring[kMS][kTB * 128];
+  __shared__ __align__(16) bf16 w_ring[kMS][kTB * 128];
+  __shared__ uint64_t meta_full[kMS];
   __shared__ volatile int abort_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nchunk = p.T / 64;
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const size_t bh = (size_t)b * p.h_kv + h;
-  const uint32_t beg = ix.coff[bh * (nchunk + 1) + c], end = ix.coff[bh * (nchunk + 1) + c + 1];
-  const int n_ent = (int)(end - beg);
-  const int G = p.h_q / p.h_kv, QB = 128 / G;
+  const uint32_t beg = ix.coff[bh * (nchunk + 1) + c];
+  const int n_ent = (int)ix.tot[bh * nchunk + c];
+  // G divides 128, so it is a power of two: rows map to (pair, group member) by shift and mask (a division by a
+  // run-time G in the gather loop cost more than the copies themselves)
+  const int G = p.h_q / p.h_kv, gs = 31 - __clz(G), QB = 128 >> gs;
   if (n_ent == 0) {
     // nobody selected this chunk: its key and value gradients are zero
     bf16* dk = static_cast<bf16*>(p.d_k_out) + (((size_t)b * p.T + (size_t)c * 64) * p.h_kv + h) * D;
@@ -593,13 +716,15 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_bwd_cm_kernel(SparsePara
   }
   if (cm_failed_before()) return;
   const int ntile = (n_ent + QB - 1) / QB;
-  const int32_t* lst = ix.list + bh * (size_t)p.L * p.K + beg;
+  const int32_t* lst = ix.list + bh * ix.cap + beg;
+  const bf16* wl = ix.wlist + (bh * ix.cap + beg) * G;
 
   if (tid == 0) {
     mbar_init(&kv_full, 1);
+    for (int s = 0; s < kMS; ++s) mbar_init(&meta_full[s], 1);
     mbar_init(&all_done, 1);
     for (int s = 0; s < NQ; ++s) {
-      mbar_init(&qdo_full[s], kCmProducers);
+      mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_free[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -619,61 +744,58 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_bwd_cm_kernel(SparsePara
   const uint32_t tmem = tmem_base_s;
   const uint32_t tdK = tmem + C_DK, tdV = tmem + C_DV;
 
-  if (warp >= 9) {
-    // =============================== gather producers ===========================================
-    const int pt = tid - 9 * 32;
-    const int piece = pt % PIECES, row0 = pt / PIECES;
-    const uint32_t qs_base = smem_u32(Qs), dos_base = smem_u32(dOs);
-    const size_t head_off = ((size_t)b * p.L * p.h_q + (size_t)h * G) * D + piece * 8;
-    const bf16* qbase = static_cast<const bf16*>(p.q) + head_off;
-    const bf16* dobase = static_cast<const bf16*>(p.d_o) + head_off;
-    bool ok = true, pending = false;
+  if (warp == 9) {
+    // =============================== gather producer (one warp) =================================
+    // The rows of a tile are fetched by TMA gather instructions, four rows each: lane l issues the gathers of rows
+    // 4 l .. 4 l + 3 (one per 64-column block).  The TMA unit keeps the requests of several tiles in flight; this
+    // warp only reads the tile's list entries and waits for a free ring stage.
+    // Metadata block m = tiles kTB m .. kTB m + kTB - 1, slot m % kMS, fetched by bulk copies.  Block m + 1 is requested
+    // when block m starts: its slot was last used by block m - 3, i.e. by tiles up to kTB (m - 2) - 1.  The ring wait of
+    // tile kTB m has passed by then, which puts the row threads past tile kTB m - NQ - 2 at least, so with NQ <= 4 no
+    // thread still reads that slot or waits on its barrier (a waiter two phases behind would never wake).
+    const int TBQ = kTB * QB, nblk = (ntile + kTB - 1) / kTB;
+    auto request_meta = [&](int m) {
+      const int e0 = m * TBQ, ne = min(n_ent - e0, TBQ);
+      const uint32_t eb = (uint32_t)(ne * 4 + 15) & ~15u, wb = (uint32_t)(ne * G * 2 + 15) & ~15u;
+      mbar_expect_tx(&meta_full[m % kMS], eb + wb);
+      bulk_load(ent_ring[m % kMS], lst + e0, eb, &meta_full[m % kMS]);
+      bulk_load(w_ring[m % kMS], wl + (size_t)e0 * G, wb, &meta_full[m % kMS]);
+    };
+    if (lane == 0) {
+      request_meta(0);
+      if (nblk > 1) request_meta(1);
+    }
+    const int row_base = (b * p.L) * p.h_q + h * G;      // tensor row of (token 0, first query head of the group)
+    bool ok = true;
     for (int j = 0; j < ntile; ++j) {
       const int s = j % NQ;
       if (j >= NQ) {
-        // The stage is released by the products of tile j - NQ, which the MMA warp issues only after it has seen
-        // tile j - 1 arrive: a tile that is still in flight here must be published before this thread may block.
-        if (pending && !cm_try(&qdo_free[s], ((j / NQ) - 1) & 1)) {
-          cp_async_wait<0>();
-          fence_async_smem();
-          mbar_arrive(&qdo_full[(j - 1) % NQ]);
-          pending = false;
-        }
         ok = cm_wait(&qdo_free[s], ((j / NQ) - 1) & 1) && !abort_s;
         if (!ok) { cm_fail(5010000 + j); break; }
       }
-      int ent[NPASS];
+      const int m = j / kTB;
+      if (j % kTB == 0) {
+        if (m >= 1 && m + 1 < nblk && lane == 0) request_meta(m + 1);
+        ok = cm_wait(&meta_full[m % kMS], (m / kMS) & 1);
+        if (!ok) { cm_fail(5011000 + j); break; }
+      }
+      const int* ents = ent_ring[m % kMS] + (j % kTB) * QB;
+      int rr[4];
 #pragma unroll
-      for (int i = 0; i < NPASS; ++i) {
-        const int e = j * QB + (i * RPP + row0) / G;
-        ent[i] = e < n_ent ? __ldg(lst + e) : -1;
+      for (int i = 0; i < 4; ++i) {
+        const int row = 4 * lane + i;
+        const bool live = j * QB + (row >> gs) < n_ent;      // rows past the end of the list fetch row 0; their P is zero
+        rr[i] = live ? row_base + (ents[row >> gs] >> kEntShift) * p.h_q + (row & (G - 1)) : row_base;
       }
+      if (lane == 0) mbar_expect_tx(&qdo_full[s], 2 * QBYTES);
+      __syncwarp();
 #pragma unroll
-      for (int i = 0; i < NPASS; ++i) {
-        const int row = i * RPP + row0;
-        const bool live = ent[i] >= 0;
-        const int t = live ? (ent[i] >> kEntShift) : 0;
-        const size_t off = ((size_t)t * p.h_q + (row % G)) * D;
-        const uint32_t dst = s * QBYTES + (piece >> 3) * 16384 + sw128_off(row, piece & 7);
-        cp_async16(qs_base + dst, qbase + off, live ? 16u : 0u);
-        cp_async16(dos_base + dst, dobase + off, live ? 16u : 0u);
+      for (int db = 0; db < DB; ++db) {
+        tma_gather4(Qs + s * QBYTES + db * 16384 + lane * 512, &tmQ, &qdo_full[s], db * 64, rr[0], rr[1], rr[2], rr[3]);
+        tma_gather4(dOs + s * QBYTES + db * 16384 + lane * 512, &tmdO, &qdo_full[s], db * 64, rr[0], rr[1], rr[2], rr[3]);
       }
-      cp_async_commit();
-      if (pending) {                      // tile j - 1 has landed once at most this tile's group is outstanding
-        cp_async_wait<1>();
-        fence_async_smem();
-        mbar_arrive(&qdo_full[(j - 1) % NQ]);
-      }
-      pending = true;
     }
-    cp_async_wait<0>();
-    if (ok) {
-      fence_async_smem();
-      mbar_arrive(&qdo_full[(ntile - 1) % NQ]);
-    } else if (lane == 0) {
-      abort_s = 1;
-      cm_fail(5019999);
-    }
+    if (!ok && lane == 0) abort_s = 1;
   } else if (warp == 8) {
     // =============================== TMA (once) + MMA issuer ====================================
     if (lane == 0) {
@@ -723,10 +845,6 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_bwd_cm_kernel(SparsePara
         if (abort_s) { ok = false; break; }
         ok = cm_wait(&ds_full[j & 1], (j >> 1) & 1);   // rows of tile j have read S/dP and written dS, wP
         if (!ok) { cm_fail(5022000 + j); break; }
-        if (j + NSB < ntile) {                            // the accumulator of tile j is free again
-          issue_sdp(j + NSB);
-          if (!ok) break;
-        }
         if (j >= NDQ) {                                   // the dQ tile's previous user (tile j - NDQ) has been read out
           ok = cm_wait(&dq_free[(j - NDQ) & 1], ((j - NDQ) >> 1) & 1);
           if (!ok) { cm_fail(5023000 + j); break; }
@@ -760,6 +878,9 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_bwd_cm_kernel(SparsePara
         }
         mma_commit(&ds_free[j & 1]);
         mma_commit(&qdo_free[sq]);
+        // The S/dP accumulator of tile j is free again.  Tile j + NSB goes after tile j's products, so the release of
+        // tile j's ring stage never waits for a gather.
+        if (j + NSB < ntile) issue_sdp(j + NSB);
       }
       if (ok) mma_commit(&all_done);
       if (!ok) { abort_s = 1; cm_fail(5029999); }
@@ -767,26 +888,28 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_bwd_cm_kernel(SparsePara
   } else {
     // =============================== row warpgroups ==============================================
     const int r = tid & 127, wg = tid >> 7;                 // warpgroup wg takes tiles wg, wg + 2, ...
-    const int g = r % G, hq = h * G + g;
+    const int g = r & (G - 1), hq = h * G + g, rp = r >> gs;
     const float scale_log2 = p.scale * kLog2e;
     const float slope = p.slope ? p.slope[hq] : 0.f;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const bf16* wbase = static_cast<const bf16*>(p.w);
     bf16* dwbase = static_cast<bf16*>(p.d_w);
     bool ok = true;
     for (int j = wg, u = 0; j < ntile; j += 2, ++u) {
       const int sb = j % NSB, db = j % NDS, qb = j % NDQ;
-      const int e = j * QB + r / G;
-      const bool live = e < n_ent;
-      const int ent = live ? __ldg(lst + e) : 0;
-      const int t = ent >> kEntShift, k = ent & kEntSlotMask;
-      const int64_t rowi = ((int64_t)b * p.L + t) * p.h_q + hq;
-      const float wv = live ? to_f(wbase[rowi * p.num_weights + k]) : 0.f;
       ok = cm_wait(&sd_full[wg], u & 1);
       if (!ok) cm_fail(5031000 + j);
       ok = __all_sync(0xffffffffu, ok) && !abort_s;
       if (!ok) break;
       tc_fence_after();
+      const int m = j / kTB;
+      ok = cm_wait(&meta_full[m % kMS], (m / kMS) & 1);
+      ok = __all_sync(0xffffffffu, ok) && !abort_s;
+      if (!ok) break;
+      const bool live = j * QB + rp < n_ent;
+      const int ent = live ? ent_ring[m % kMS][(j % kTB) * QB + rp] : 0;
+      const int k = ent & kEntSlotMask;
+      const float wv = live ? to_f(w_ring[m % kMS][(j % kTB) * 128 + r]) : 0.f;
+      const int rowt = live ? (int)(((int64_t)b * p.L + (ent >> kEntShift)) * p.h_q + hq) : -1;
       float sv[64], dp[64];
       const uint32_t tsd = tmem + lane_base + sb * 128;
       tmem_ld32(tsd, sv);
@@ -808,44 +931,24 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_bwd_cm_kernel(SparsePara
       if (live) {
         store_row_bf16_sw128(dSs + db * 16384, r, sv);
         store_row_bf16_sw128(Pws + db * 16384, r, dp);
-        dwbase[rowi * p.num_weights + k] = __float2bfloat16_rn(dw);
+        dwbase[(int64_t)rowt * p.num_weights + k] = __float2bfloat16_rn(dw);
       } else {
         store_row_zero_sw128(dSs + db * 16384, r);
         store_row_zero_sw128(Pws + db * 16384, r);
       }
-      tgt_s[wg][u & 1][r] = live ? (int)rowi : -1;
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(&ds_full[wg]);
-      // all 128 arrivals also mean that tgt_s of this tile is complete
-      ok = cm_wait(&ds_full[wg], u & 1);
-      if (!ok) cm_fail(5033000 + j);
-      if (ok) {
-        ok = cm_wait(&dq_full[wg], u & 1);
-        if (!ok) cm_fail(5034000 + j);
-      }
+      ok = cm_wait(&dq_full[wg], u & 1);
+      if (!ok) cm_fail(5034000 + j);
       ok = __all_sync(0xffffffffu, ok) && !abort_s;
       if (!ok) break;
       tc_fence_after();
-      // dQ tile -> fp32 accumulator rows: 4 neighbouring lanes add 32 consecutive bytes of one row
+      // dQ tile -> fp32 accumulator rows of the tokens, SLW columns at a time
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int ra = (warp & 3) * 32 + half * 16 + (lane >> 2);
-        const int ta = tgt_s[wg][u & 1][ra], tb = tgt_s[wg][u & 1][ra + 8];
-        float* pa = dq_acc + (int64_t)(ta < 0 ? 0 : ta) * D + 2 * (lane & 3);
-        float* pb = dq_acc + (int64_t)(tb < 0 ? 0 : tb) * D + 2 * (lane & 3);
-#pragma unroll
-        for (int cb = 0; cb < D / 64; ++cb) {
-          float ov[32];
-          tmem_ld_16x256b_x8(tmem + lane_base + ((uint32_t)(half * 16) << 16) + C_DQ + qb * D + cb * 64, ov);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (ta >= 0) red_add_v2(pa + cb * 64 + 8 * i, ov[4 * i], ov[4 * i + 1]);
-            if (tb >= 0) red_add_v2(pb + cb * 64 + 8 * i, ov[4 * i + 2], ov[4 * i + 3]);
-          }
-        }
-      }
+      for (int sl = 0; sl < NS; ++sl)
+        scatter_slice<SLW>(StgB + warp * StgGeom<SLW>::kWarpBytes, tmem + lane_base + C_DQ + qb * D + sl * SLW, rowt, dq_acc, D,
+                           sl * SLW, lane);
       tc_fence_before();
       mbar_arrive(&dq_free[wg]);
     }
@@ -899,13 +1002,14 @@ __global__ void __launch_bounds__(kCmThreads, 1) sparse_bwd_cm_kernel(SparsePara
 
 static size_t cm_bwd_smem(int D) {
   const int NQ = (D == 64) ? 3 : 2, NDS = (D == 64) ? 2 : 1;
-  return 1024 + 2 * (size_t)NQ * (D / 64) * 16384 + 2 * (size_t)(D / 64) * 8192 + 2 * (size_t)NDS * 16384;
+  return 1024 + 2 * (size_t)NQ * (D / 64) * 16384 + 2 * (size_t)(D / 64) * 8192 + 2 * (size_t)NDS * 16384 +
+         8 * (D == 64 ? (size_t)StgGeom<32>::kWarpBytes : (size_t)StgGeom<16>::kWarpBytes);
 }
 
 // workspace of the chunk-major backward: inverse index + fp32 dQ accumulator (0: shape outside this path)
 size_t sparse_bwd_cm_workspace(const SparseParams& p) {
   if (!cm_shape_ok(p)) return 0;
-  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.K, p.T / 64);
+  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.h_q / p.h_kv, p.K, p.T / 64);
   return l.total + (size_t)p.B * p.L * p.h_q * p.D * sizeof(float);
 }
 
@@ -915,7 +1019,7 @@ int sparse_bwd_cm_launch(const SparseParams& p, void* d_k, void* d_v, void* work
        (uintptr_t)workspace) & 15)
     return HILS_ERR_UNSUPPORTED;
   const int D = p.D, nchunk = p.T / 64;
-  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.K, nchunk);
+  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.h_q / p.h_kv, p.K, nchunk);
   InvIndex ix;
   if (int rc = build_inverse_index(p, workspace, &ix, st)) return rc;
   float* dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + l.total);
@@ -933,14 +1037,17 @@ int sparse_bwd_cm_launch(const SparseParams& p, void* d_k, void* d_v, void* work
   CUtensorMap tmK, tmV;
   if (int rc = make_tmap_bf16_rows(&tmK, p.k, (uint64_t)p.B * p.T, (uint64_t)p.h_kv * D, (uint64_t)p.h_kv * D, 64)) return rc;
   if (int rc = make_tmap_bf16_rows(&tmV, p.v, (uint64_t)p.B * p.T, (uint64_t)p.h_kv * D, (uint64_t)p.h_kv * D, 64)) return rc;
+  CUtensorMap tmQ, tmdO;   // rows = (batch, token, query head), one row per box: the sources of the row gathers
+  if (int rc = make_tmap_bf16_rows(&tmQ, p.q, (uint64_t)p.B * p.L * p.h_q, D, D, 1)) return rc;
+  if (int rc = make_tmap_bf16_rows(&tmdO, p.d_o, (uint64_t)p.B * p.L * p.h_q, D, D, 1)) return rc;
   const size_t smem = cm_bwd_smem(D);
   dim3 grid(nchunk, p.h_kv, p.B);
   if (D == 64) {
     cudaFuncSetAttribute(sparse_bwd_cm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sparse_bwd_cm_kernel<64><<<grid, kCmThreads, smem, st>>>(pp, ix, dq_acc, tmK, tmV);
+    sparse_bwd_cm_kernel<64><<<grid, kCmThreads, smem, st>>>(pp, ix, dq_acc, tmK, tmV, tmQ, tmdO);
   } else {
     cudaFuncSetAttribute(sparse_bwd_cm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sparse_bwd_cm_kernel<128><<<grid, kCmThreads, smem, st>>>(pp, ix, dq_acc, tmK, tmV);
+    sparse_bwd_cm_kernel<128><<<grid, kCmThreads, smem, st>>>(pp, ix, dq_acc, tmK, tmV, tmQ, tmdO);
   }
   cm_round_kernel<<<(unsigned)((n_q / 8 + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<bf16*>(p.d_q), (int64_t)(n_q / 8));
   HILS_LAUNCH_CHECK("sparse_attn_bwd (chunk-major path)");

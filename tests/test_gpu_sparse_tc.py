@@ -65,11 +65,25 @@ def test_tc_forward_slope_and_no_last_mask():
 
 
 def test_tc_forward_is_deterministic():
+    """Dense selections (few chunks per selected slot) run the query-block-major kernel, which sums in a fixed order."""
     import hils_attention_b200 as hb
     q, k, v, w, idx = [t.cuda() for t in _case(1, 512, 512, 2, 1, 64, 8, 9)]
     o1 = hb.HiLS_block_M_head(q, k, v, w, idx, block_size=64, is_training=False)
     o2 = hb.HiLS_block_M_head(q, k, v, w, idx, block_size=64, is_training=False)
     assert torch.equal(o1, o2)
+
+
+def test_chunk_major_forward_matches_oracle_on_sparse_selections():
+    """Many candidate chunks per selected slot (64 chunks, 4 slots): the chunk-major forward kernel (inverse index,
+    gathered owner rows, fp32 scatter-add of the slots' partial outputs)."""
+    import hils_attention_b200 as hb
+    from hils_attention_b200 import _lib
+    for (B, L, T, H, G, D, K) in [(1, 4096, 4096, 2, 1, 64, 4), (2, 2100, 4096, 1, 4, 128, 8)]:
+        q, k, v, w, idx = _case(B, L, T, H, G, D, K, 55)
+        ref = orc.sparse_attn(q, k, v, w, idx, chunk_size=64, mask_last_token=True)
+        o = hb.HiLS_block_M_head(q.cuda(), k.cuda(), v.cuda(), w.cuda(), idx.cuda(), block_size=64, is_training=False)
+        assert _lib.load().hils_take_device_status() == 0
+        check(o, ref, BF, "chunk-major forward")
 
 
 @pytest.mark.parametrize("cfg", [
@@ -104,6 +118,9 @@ def test_tc_backward_matches_oracle(cfg):
 
 
 def test_tc_backward_is_deterministic():
+    """dK, dV and dW come out bit-identical from run to run: they are summed inside one CTA per chunk in the order of
+    the inverse index.  dQ is the sum of a token's slot contributions added to an fp32 accumulator in global memory in
+    whatever order the chunks' CTAs reach it; two runs agree to fp32 rounding of at most K terms."""
     import hils_attention_b200 as hb
     q, k, v, w, idx = [t.cuda() for t in _case(1, 512, 512, 2, 2, 64, 8, 19)]
     do = torch.randn(q.shape, generator=torch.Generator().manual_seed(4)).to(BF).cuda()
@@ -112,5 +129,6 @@ def test_tc_backward_is_deterministic():
         qd, kd, vd, wd = [t.clone().requires_grad_(True) for t in (q, k, v, w)]
         hb.HiLS_block_M_head(qd, kd, vd, wd, idx, block_size=64).backward(do)
         grads.append([t.grad.clone() for t in (qd, kd, vd, wd)])
-    for a, b in zip(*grads):
-        assert torch.equal(a, b)
+    (dq1, dk1, dv1, dw1), (dq2, dk2, dv2, dw2) = grads
+    assert torch.equal(dk1, dk2) and torch.equal(dv1, dv2) and torch.equal(dw1, dw2)
+    assert float((dq1.float() - dq2.float()).abs().max()) <= 2 ** -7 * float(dq1.float().abs().max())
