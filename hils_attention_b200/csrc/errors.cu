@@ -25,6 +25,7 @@ namespace hils {
 int take_status_sparse_tc();
 int take_status_swa_tc();
 int take_status_sparse_cm();
+int take_status_topk_tc();
 }  // namespace hils
 
 extern "C" int hils_version(void) { return 100; }
@@ -35,7 +36,8 @@ extern "C" int hils_take_device_status(void) {
   const int a = hils::take_status_sparse_tc();
   const int b = hils::take_status_swa_tc();
   const int c = hils::take_status_sparse_cm();
-  if (a < 0 || b < 0 || c < 0) return -1;
-  return a != 0 ? a : (b != 0 ? b : c);
+  const int d = hils::take_status_topk_tc();
+  if (a < 0 || b < 0 || c < 0 || d < 0) return -1;
+  return a != 0 ? a : (b != 0 ? b : (c != 0 ? c : d));
 }
 extern "C" const char* hils_last_error(void) { return hils::g_err; }

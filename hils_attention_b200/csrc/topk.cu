@@ -19,17 +19,9 @@
 // id").  New candidates are filtered by a warp ballot against the current K-th item.
 #include "common.cuh"
 #include "mma_rows.cuh"
+#include "topk_params.cuh"
 
 namespace hils {
-
-struct TopkParams {
-  const void* q; const void* lmks; const void* lse_swa; const float* bias; const float* gumbel;
-  const int32_t* drop_mask; int32_t* indices; void* scores; float* lse_total; float* rank_keys;
-  int B, L, N, h_kv, G, D, topk, block_size, window_size, is_causal, q_offset, per_qhead, lse_dtype;
-  int RW;
-  float scale;
-  float* dots;   // decode, bf16: raw q.k' of every candidate, written by the streaming kernel (or null)
-};
 
 constexpr int TN = 128;  // candidates per tile
 constexpr int CPT = TN / 16;  // candidates per thread in the score product
@@ -1310,6 +1302,7 @@ __global__ void __launch_bounds__(128) topk_bwd_kernel(
   }
 }
 
+int topk_fwd_tc_launch(const TopkParams& p, cudaStream_t st);   // topk_tc.cu
 int topk_bwd_mma_launch(const void* d_scores, const int32_t* indices, const void* q, const void* lmks, void* d_q,
                         float* dl, int B, int L, int N, int h_kv, int G, int D, int topk, int per_qhead, float scale,
                         cudaStream_t st);  // topk_bwd_mma.cu
@@ -1382,6 +1375,11 @@ extern "C" int hils_topk_fwd(const void* q, const void* lmks, const void* lse_sw
     const int rc = (dtype != HILS_BF16) ? launch_topk_decode<float, 0>(p, st)
                    : (D == 128)         ? launch_topk_decode<bf16, 8>(p, st)
                                         : launch_topk_decode<bf16, 4>(p, st);
+    if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  }
+  // bf16, long candidate lists, one query head per key head: one thread per token, scores by tcgen05
+  if (dtype == HILS_BF16 && topk <= N) {
+    const int rc = topk_fwd_tc_launch(p, st);
     if (rc != HILS_ERR_UNSUPPORTED) return rc;
   }
   // bf16: scores on the tensor cores, the CTA's scores resident in shared memory

@@ -1,0 +1,16 @@
+// Arguments of the chunk-selection kernels (topk.cu, topk_tc.cu).
+#pragma once
+#include <stdint.h>
+
+namespace hils {
+
+struct TopkParams {
+  const void* q; const void* lmks; const void* lse_swa; const float* bias; const float* gumbel;
+  const int32_t* drop_mask; int32_t* indices; void* scores; float* lse_total; float* rank_keys;
+  int B, L, N, h_kv, G, D, topk, block_size, window_size, is_causal, q_offset, per_qhead, lse_dtype;
+  int RW;
+  float scale;
+  float* dots;   // decode, bf16: raw q.k' of every candidate, written by the streaming kernel (or null)
+};
+
+}  // namespace hils

@@ -568,3 +568,36 @@ def test_norm_rope_golden(ops, tag):
     ops.single_tensor_rope_autograd(xr, cos.float(), sin.float()).backward(
         ops.single_tensor_rope_autograd(x.detach(), cos.float(), sin.float()))
     check(xr.grad, x.detach(), dt, "rope^T rope = id")
+
+
+@pytest.mark.parametrize("cfg", [
+    # B, L, N, h, D, K, bias, q_offset
+    (1, 1500, 1024, 2, 128, 32, True, 65536 - 1500),     # the 64K-context shape: every chunk a candidate for the last rows
+    (2, 700, 700, 1, 64, 8, False, 44100),               # ragged: 700 keys, 700 rows, head dim 64
+    (1, 300, 2000, 2, 64, 32, True, 40000),              # rows with few and with ~620 candidates
+    (1, 260, 600, 1, 128, 16, True, 0),                  # training offsets: the first rows have no candidate at all
+])
+def test_topk_long_candidate_lists_one_thread_per_token(ops, cfg):
+    """Long candidate lists (N >= 512), one query head per key head: the kernel with one thread per token and tcgen05
+    scores.  ids bit-exact on the kernel's own ranking values, those values / lse_total / scores within tolerance of the
+    oracle, ids >= 99 % equal to the oracle's."""
+    from hils_attention_b200 import _lib
+    B, L, N, h, D, K, with_bias, q_offset = cfg
+    S, W = 64, 512
+    g = torch.Generator().manual_seed(61)
+    q = torch.randn(B, L, h, 1, D, generator=g).to(BF)
+    lm = (torch.randn(B, N, h, D, generator=g) + 0.5 * torch.randn(B, N, h, 1, generator=g)).to(BF)
+    lse = torch.randn(B, L, h, generator=g) + 2
+    bias = torch.randn(B, N, h, generator=g) if with_bias else None
+    aux = {}
+    idx, sc = ops.online_softmax_topk_head(q.cuda(), lm.cuda(), lse.cuda(), K, S, W, q_offset=q_offset, is_training=False,
+                                           bias=None if bias is None else bias.cuda(), _aux=aux)
+    assert _lib.load().hils_take_device_status() == 0
+    keys = aux["rank_keys"].cpu()
+    assert torch.equal(idx.cpu(), orc.stable_topk_from_keys(keys, K))
+    ridx, rsc, raux = orc.topk_select(q.float(), lm.float(), lse, K, S, W, True, q_offset, bias=bias, return_aux=True)
+    check(keys, raux["keys"], F32, "rank keys", scale=10.0)   # x10: the keys are differences of values ~10 with the row's lse
+    check(aux["lse_total"], raux["lse_total"], F32, "lse_total", scale=10.0)
+    same = (idx.cpu() == ridx).all(-1)
+    assert same.float().mean().item() >= 0.99
+    check(sc.view(B, L, h, 1, K)[same], rsc[same], BF, "scores")
