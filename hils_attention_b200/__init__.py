@@ -5,6 +5,7 @@
 attention module does; `cache` is the KV store used for prefill and decode.
 """
 from . import _lib
+from .naive_bsa import naive_bsa_kernel
 from .ops import (HiLS_block_M_head, chunk_attn_pool, chunk_attn_pool_tilelang, chunk_mean_pool,
                   exact_chunk_log_z_tl, flex_attn_tl, flex_attn_tl_two_phase, inter_chunk_softmax,
                   online_softmax_topk_head, rmsnorm_rope, rope_rotary_pos_emb, single_tensor_rope_autograd,
@@ -13,4 +14,4 @@ from .ops import (HiLS_block_M_head, chunk_attn_pool, chunk_attn_pool_tilelang, 
 __all__ = ["HiLS_block_M_head", "chunk_attn_pool", "chunk_attn_pool_tilelang", "chunk_mean_pool",
            "exact_chunk_log_z_tl", "flex_attn_tl", "flex_attn_tl_two_phase", "inter_chunk_softmax",
            "online_softmax_topk_head", "rmsnorm_rope", "rope_rotary_pos_emb", "single_tensor_rope_autograd",
-           "sparse_attn_combine"]
+           "sparse_attn_combine", "naive_bsa_kernel"]
