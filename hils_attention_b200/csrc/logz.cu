@@ -9,6 +9,9 @@
 
 namespace hils {
 
+int logz_fwd_tc_launch(const void* q, const void* k, float* log_z, int B, int L, int h_q, int h_kv, int D, int chunk_size,
+                       int window_size, float sm_scale, int mask_lmk, cudaStream_t st);   // logz_tc.cu
+
 struct LogzParams {
   const void* q; const void* k; float* log_z; const float* d_log_z; void* d_q; void* d_k;
   int B, L, h_q, h_kv, D, S, W, mask_lmk, n_chunk;
@@ -197,6 +200,10 @@ extern "C" int hils_chunk_logz_fwd(const void* q, const void* k, float* log_z, i
   const int64_t rows = (int64_t)B * L * h_q;
   const size_t smem = 4 * (size_t)D * sizeof(float);
   cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == HILS_BF16) {   // chunk size 64 on the tensor cores
+    const int rc = logz_fwd_tc_launch(q, k, log_z, B, L, h_q, h_kv, D, chunk_size, window_size, sm_scale, mask_lmk, st);
+    if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  }
   const unsigned blocks = (unsigned)((rows + 3) / 4);
   if (dtype == HILS_BF16) logz_fwd_kernel<bf16><<<blocks, 128, smem, st>>>(p, rows);
   else logz_fwd_kernel<float><<<blocks, 128, smem, st>>>(p, rows);

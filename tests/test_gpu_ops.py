@@ -309,6 +309,26 @@ def test_logz_mask_lmk_forward_only(ops):
         lz[torch.isfinite(lz)].sum().backward()
 
 
+@pytest.mark.parametrize("B,L,hq,hkv,D,W,ml", [
+    (2, 1000, 4, 4, 64, 64, False),      # ragged length, one head per kv head, odd chunk count
+    (1, 2048, 8, 1, 64, 512, True),      # 8 query heads per kv head, masked landmark column
+    (1, 1100, 4, 2, 128, 128, False),    # head dim 128, ragged
+    (2, 256, 2, 2, 128, 64, True),
+    (1, 100, 2, 1, 64, 64, False),       # no chunk is ever defined: all -inf
+])
+def test_logz_tensor_core_forward_matches_oracle(ops, B, L, hq, hkv, D, W, ml):
+    """bf16 at chunk size 64 runs one 128 x 128 tcgen05 product per pair of chunks; every (row, chunk) entry is
+    compared, and the -inf pattern must agree exactly."""
+    g = torch.Generator().manual_seed(L + D)
+    q = torch.randn(B, L, hq, D, generator=g).to(BF)
+    k = torch.randn(B, L, hkv, D, generator=g).to(BF)
+    lz = ops.exact_chunk_log_z_tl(q.cuda(), k.cuda(), chunk_size=64, window_size=W, mask_lmk=ml)
+    ref = orc.exact_chunk_log_z(q.float(), k.float(), chunk_size=64, window_size=W, mask_lmk=ml)
+    assert lz.shape == ref.shape
+    assert torch.equal(torch.isfinite(lz).cpu(), torch.isfinite(ref))
+    check(lz, ref, BF, "log_z (tensor cores)")
+
+
 # ------------------------------------------------------------------ sliding-window branch
 SWA_CASES = [
     # B, Lq, Lk, h_q, h_kv, D, W, S, mask_lmk, expand, kv_start
@@ -601,3 +621,25 @@ def test_topk_long_candidate_lists_one_thread_per_token(ops, cfg):
     same = (idx.cpu() == ridx).all(-1)
     assert same.float().mean().item() >= 0.99
     check(sc.view(B, L, h, 1, K)[same], rsc[same], BF, "scores")
+
+
+@pytest.mark.parametrize("L", [999, 1023, 1100])
+def test_topk_ragged_lengths_and_wide_chunk_keys(ops, L):
+    """Sequence lengths that are no multiple of anything (ops/topk_head_softmax.py:2431-2479) and chunk keys whose last
+    dimension is 2*D, which the wrapper folds into twice as many heads (:1296-1300, test_gqa_d_reshape_correctness)."""
+    B, h_kv, G, D, K, S, W = 2, 2, 2, 64, 16, 64, 64
+    N = L // S
+    g = torch.Generator().manual_seed(L)
+    q = torch.randn(B, L, h_kv * G, D, generator=g).to(BF)
+    lm_wide = torch.randn(B, N, h_kv, 2 * D, generator=g).to(BF)          # (B,N,h_kv,2D) == (B,N,h_kv*2,D): one key per q head
+    lse = torch.randn(B, L, h_kv * G, generator=g) + 2
+    aux = {}
+    idx, sc = ops.online_softmax_topk_head(q.cuda(), lm_wide.cuda(), lse.cuda(), K, S, W, G=G, _aux=aux)
+    idx2, sc2 = ops.online_softmax_topk_head(q.cuda(), lm_wide.view(B, N, h_kv * 2, D).cuda(), lse.cuda(), K, S, W, G=G)
+    assert torch.equal(idx, idx2) and torch.equal(sc, sc2)
+    assert idx.shape == (B, L, h_kv, K) and sc.shape == (B, L, h_kv * G, K)
+    assert torch.equal(idx.cpu(), orc.stable_topk_from_keys(aux["rank_keys"].cpu(), K))
+    ridx, rsc = orc.topk_select(q.float().view(B, L, h_kv, G, D), lm_wide.float().view(B, N, h_kv * G, D), lse, K, S, W)
+    same = (idx.cpu() == ridx).all(-1)
+    assert same.float().mean().item() >= 0.99
+    check(sc.view(B, L, h_kv, G, K)[same], rsc[same], BF, "scores")
