@@ -52,6 +52,9 @@ WORKLOADS = {
     # decode: 32 sequences, one new token each, against a 131072-token KV store
     "c4": dict(B=32, T=131072, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
     "c4_small": dict(B=4, T=16384, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
+    # ultra-long context, forward only, the sequence sharded over the ranks
+    "c5": dict(B=1, T=1048576, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
+    "c5_small": dict(B=1, T=131072, h_q=4, h_kv=4, D=128, S=64, K=32, W=512),
 }
 CPU_SAMPLE = WORKLOADS["c1"]   # the reference's CPU-runnable case
 
@@ -464,6 +467,12 @@ def kernel_rooflines(name, core, q, k, v, do, w, hq, hk, with_overlap):
     row_bytes = float(B * T * hq) * (K * es + K * 4 / G + (K + 1) * es)
     add("chunk_weights_fwd", t_f5, nbytes=row_bytes)
     add("chunk_weights_bwd", t_b5, nbytes=row_bytes + float(B * T * hq) * (K + 1) * es)
+    # ---- exact per-chunk log Z (the NaiveBSA scoring op; not a stage of the HiLS step) ---------------
+    if S == 64:
+        f_lz = 2.0 * float(nvalid.sum()) * S * D * hq * B
+        t_lz = time_op(lambda: hb.exact_chunk_log_z_tl(q, k, chunk_size=S, window_size=W))
+        e = add("exact_chunk_log_z_fwd", t_lz, flops=f_lz)
+        e["output_gbs"] = float(B * T * hq) * N * 4 / (t_lz / 1e3) / 1e9
     require_clean_status(f"the per-kernel timings of {name}")
 
     t_sp, f_sp = t_f + t_b, f_f + f_b
@@ -592,6 +601,92 @@ def run_decode(args, name, ds, steps, warmup):
     torch.cuda.empty_cache()
     return out
 
+# -------------------------------------------------------------------------------------------------
+# ultra-long context: forward of the chain with the sequence sharded over the ranks
+# -------------------------------------------------------------------------------------------------
+def run_context_parallel(args, name, ds, steps, warmup):
+    """Forward of the chain over one sequence of T tokens: on one GPU the plain chain, on N >= 2 GPUs the
+    context-parallel chain (zig-zag blocks; the pooled chunk keys all-gathered, the selected K/V tiles fetched per
+    kv head).  Strong scaling: T is fixed, value = T / slowest rank's step.  Inputs are generated on the device
+    block by block from per-block seeds, so the sequence is the same at every N."""
+    from hils_attention_b200.attention import HiLSAttentionConfig, HiLSAttentionCore
+    from hils_attention_b200.parallel import SeqPartition, context_parallel_forward
+    from hils_attention_b200 import _lib
+
+    w = WORKLOADS[name]
+    B, T, hq, hk, D, S, K, W = (w[x] for x in ("B", "T", "h_q", "h_kv", "D", "S", "K", "W"))
+    world, rank, dev = ds.world, ds.rank, ds.dev
+    part = SeqPartition(world, "zigzag")
+    nblk = 16                                   # generation blocks: a multiple of 2 * world for world <= 8
+    tb = T // nblk
+
+    def gen_block(j):
+        g = torch.Generator(device=dev).manual_seed(5000 + j)
+        qb = torch.randn((B, tb, hq, D), generator=g, device=dev, dtype=torch.bfloat16)
+        kb = torch.randn((B, tb, hk, D), generator=g, device=dev, dtype=torch.bfloat16)
+        off = torch.randn((B, tb // S, 1, hk, D), generator=g, device=dev, dtype=torch.bfloat16) * 0.5
+        kb = (kb.unflatten(1, (tb // S, S)) + off).flatten(1, 2)
+        vb = torch.randn((B, tb, hk, D), generator=g, device=dev, dtype=torch.bfloat16)
+        return qb, kb, vb
+
+    per = nblk // part.n_blocks if world > 1 else nblk
+    mine = [b * per + i for b in (part.blocks(rank) if world > 1 else [0]) for i in range(per)]
+    parts = [gen_block(j) for j in mine]
+    q, k, v = (torch.cat([p[i] for p in parts], 1) for i in range(3))
+    del parts
+    core = HiLSAttentionCore(HiLSAttentionConfig(hq, hk, K, S, W)).eval()
+
+    def step(timings=None, aux=False):
+        with torch.no_grad():
+            if world == 1:
+                return core(q, k, v, q)
+            return context_parallel_forward(q, k, v, q, h_kv=hk, topk=K, chunk_size=S, window_size=W,
+                                            partition="zigzag", return_aux=aux, timings=timings)
+
+    for _ in range(warmup):
+        step()
+    ds.barrier()
+    c0 = _lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(ds.local) as clk:
+        ds.barrier()
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        ds.barrier()
+    launches = _lib.launch_count() - c0
+    require_clean_status(f"the timed steps of {name}")
+    (ms,) = ds.max(e0.elapsed_time(e1))
+    ms_step = ms / steps
+    out = {"metric": "hils_attn_fwd_tokens_per_s", "value": B * T / (ms_step / 1e3), "unit": "tokens/s",
+           "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
+           "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": name, **{x: w[x] for x in ("B", "T", "h_q", "h_kv", "D", "S", "K", "W")},
+                      "tokens_per_gpu": T // world,
+                      "parallelism": "single GPU" if world == 1 else f"context-parallel x{world}, zig-zag blocks",
+                      "l2": "inputs_larger_than_L2"},
+           "gpu_launches": launches, "clocks": clk.summary()}
+    if world > 1:
+        tm = {}
+        _, aux = step(timings=tm, aux=True)
+        stage_max = ds.max(*[tm[x] for x in sorted(tm)])
+        out["stages_ms_max_over_ranks"] = dict(zip(sorted(tm), stage_max))
+        fetch_b, ag_b, halo_b = ds.max(aux["fetch_bytes"], aux["allgather_bytes"], aux["halo_bytes"])
+        t_f = out["stages_ms_max_over_ranks"].get("fetch", 0.0)
+        t_a = out["stages_ms_max_over_ranks"].get("pool+allgather", 0.0)
+        out["exchange"] = {"fetch_bytes_received_per_gpu": fetch_b, "allgather_bytes_received_per_gpu": ag_b,
+                           "halo_bytes_received_per_gpu": halo_b,
+                           "fetch_gbs": fetch_b / (t_f / 1e3) / 1e9 if t_f else None,
+                           "remote_tiles_of_all": aux["remote_tiles"] / float(B * hk * (T // S) * (world - 1) / world),
+                           "collectives": "all_gather (pooled keys), all_to_all (request bitmaps, K/V tiles), "
+                                          "send/recv (halo)",
+                           "allgather_ms": t_a}
+        require_clean_status(f"the staged run of {name}")
+    del q, k, v
+    torch.cuda.empty_cache()
+    return out
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -608,19 +703,23 @@ def main():
     args.warmup = max(args.warmup, 3)
     ds = Dist()
     decode = args.workload.startswith("c4")
-    line = (run_decode(args, args.workload, ds, args.steps, args.warmup) if decode
-            else run_train(args, args.workload, ds, args.steps, args.warmup))
+    if args.workload.startswith("c5"):
+        line = run_context_parallel(args, args.workload, ds, args.steps, args.warmup)
+    elif decode:
+        line = run_decode(args, args.workload, ds, args.steps, args.warmup)
+    else:
+        line = run_train(args, args.workload, ds, args.steps, args.warmup)
     secondary = {}
     if not args.only and args.workload == "c3":
         s2 = run_train(args, "c2", ds, max(args.steps, 10), 3, with_e2e=True)
         s4 = run_decode(args, "c4", ds, max(2 * args.steps, 20), 5)
-        secondary = {"c2": s2, "c4": s4}
+        secondary = {"c2": s2, "c4": s4, "c5": run_context_parallel(args, "c5", ds, 2, 1)}
         if ds.world == 1:
             # the reference arm's configuration on the GPU (fp32 kernels), for a like-for-like CPU/GPU ratio
             secondary["c1"] = run_train(args, "c1", ds, 10, 3, with_e2e=False, with_kernels=False)
     if ds.rank == 0:
         line["cpu_baseline"] = None
-        if ds.world == 1 and not args.no_cpu_baseline and not decode:
+        if ds.world == 1 and not args.no_cpu_baseline and not decode and not args.workload.startswith("c5"):
             tps, cores, dt = cpu_chain_tokens_per_s(1)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
                                     "sample": f"{CPU_SAMPLE_TEXT}, one pass ({dt:.1f} s)"}

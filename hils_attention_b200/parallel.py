@@ -1,157 +1,278 @@
-"""Context-parallel forward of the HiLS attention chain (sequence sharded over the ranks).
+"""Context-parallel forward of the HiLS attention chain: the sequence is sharded over the ranks.
 
-Each rank owns a contiguous range of `Tl` tokens (a multiple of the chunk size) with its q, k, v.
+The sequence is cut into equal blocks (a multiple of the chunk size, at least window + chunk long).  With the
+`zigzag` partition there are 2·world blocks and rank r holds blocks r and 2·world−1−r, so that every rank scores
+the same number of causal candidate chunks; with `contiguous` there are `world` blocks and rank r holds block r.
+A rank's tensors are its blocks concatenated in ascending order.
+
 Per layer the ranks exchange only
-  * the tail of each shard (window + one chunk) as the sliding-window halo of the next rank,
-  * the pooled chunk keys and their bias (all-gather: N*h*D elements in total),
-  * the K/V tiles of the remote chunks a rank actually selected (requested by id, sent point to point),
-and everything else runs on local memory with the single-GPU kernels.  The reference has no
-context-parallel HiLS path; its older HSA model all-gathers every landmark and every chunk's K/V
-(models/HSA_Ultralong/hsa_layers.py:893-898).  Collectives go through torch.distributed (NCCL on
-GPUs, gloo in the CPU tests of the exchange plan); no kernel reads a peer's memory.
+  * the tail of a block (window rounded up to chunks) as the sliding-window halo of the block that follows it:
+    point-to-point between the two owners, nothing else moves;
+  * the pooled chunk keys and their bias: one all-gather of N·h·D elements in total;
+  * the K/V tiles of the remote chunks a rank selected, per kv head: a fixed-width bitmap of wanted chunks goes
+    to each owner (all-to-all), the tile counts come back to the host in ONE small copy (the only host
+    synchronisation of the exchange), the tiles travel in one uneven all-to-all per tensor into a local staging
+    buffer; chunk ids are rewritten to staging slots and the sparse attention then runs on local memory only.
+Everything else runs on local memory with the single-GPU kernels.  The reference has no context-parallel HiLS
+path; its older HSA model all-gathers every landmark and every chunk's K/V
+(models/HSA_Ultralong/hsa_layers.py:893-898).  Collectives go through torch.distributed (NCCL on GPUs, gloo in
+the CPU tests of the exchange); no kernel reads a peer's memory.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
-import torch.nn.functional as F
 
 
 # ------------------------------------------------------------------------------------------
-# exchange plan (pure torch: works on CPU tensors with gloo and on CUDA tensors with NCCL)
+# partition of the sequence
 # ------------------------------------------------------------------------------------------
-def plan_remote_chunks(indices: torch.Tensor, first_local_chunk: int, n_local: int
-                       ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """indices (B, L, h_kv, K) global chunk ids (-1 = padding).  Returns (remote_ids, remapped):
-    the ascending unique ids that live on other ranks, and the ids rewritten as positions in the
-    staging buffer [remote chunks in that order | this rank's n_local chunks]."""
-    valid = indices >= 0
-    is_remote = valid & ((indices < first_local_chunk) | (indices >= first_local_chunk + n_local))
-    remote_ids = torch.unique(indices[is_remote])                                  # ascending
-    pos = torch.searchsorted(remote_ids, indices.clamp_min(0).to(remote_ids.dtype))
-    n_remote = remote_ids.numel()
-    local_pos = indices - first_local_chunk + n_remote
-    remapped = torch.where(is_remote, pos.to(indices.dtype), local_pos.to(indices.dtype))
-    remapped = torch.where(valid, remapped, torch.full_like(indices, -1))
-    return remote_ids, remapped
+@dataclass(frozen=True)
+class SeqPartition:
+    """Which blocks of the sequence a rank holds."""
+    world: int
+    kind: str = "zigzag"          # "zigzag" | "contiguous"
+
+    def __post_init__(self):
+        if self.kind not in ("zigzag", "contiguous"):
+            raise ValueError(f"unknown partition {self.kind!r}")
+
+    @property
+    def n_blocks(self) -> int:
+        return 2 * self.world if self.kind == "zigzag" else self.world
+
+    @property
+    def blocks_per_rank(self) -> int:
+        return 2 if self.kind == "zigzag" else 1
+
+    def blocks(self, rank: int) -> List[int]:
+        return [rank, 2 * self.world - 1 - rank] if self.kind == "zigzag" else [rank]
+
+    def owner(self, block: int) -> int:
+        if self.kind == "contiguous" or block < self.world:
+            return block
+        return 2 * self.world - 1 - block
+
+    def block_order(self) -> List[int]:
+        """Blocks in the order an all-gather over ranks delivers them (rank 0's blocks, rank 1's, ...)."""
+        return [b for r in range(self.world) for b in self.blocks(r)]
+
+    def shard(self, x: torch.Tensor, rank: int, dim: int = 1) -> torch.Tensor:
+        """This rank's part of a full-sequence tensor (for tests and benchmarks that start from the whole)."""
+        tb = x.shape[dim] // self.n_blocks
+        return torch.cat([x.narrow(dim, b * tb, tb) for b in self.blocks(rank)], dim)
 
 
-def exchange_chunks(k_chunks: torch.Tensor, v_chunks: torch.Tensor, remote_ids: torch.Tensor,
-                    chunks_per_rank: int, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """k_chunks, v_chunks (B, n_local, S, h, D): this rank's chunks.  remote_ids: ascending global
-    ids this rank needs from others.  Returns the requested tiles (B, n_remote, S, h, D) for K and V.
-    Request lists travel by all-gather (padded), tiles by point-to-point sends."""
-    world = dist.get_world_size(group)
+# ------------------------------------------------------------------------------------------
+# exchanges (pure torch: CPU tensors with gloo, CUDA tensors with NCCL)
+# ------------------------------------------------------------------------------------------
+def exchange_halo(x: torch.Tensor, part: SeqPartition, halo: int, group=None) -> List[Optional[torch.Tensor]]:
+    """x (B, Tl, h, D) = this rank's blocks.  Returns, per local block, the `halo` tokens that precede it in the
+    sequence (None for block 0), received from the rank that owns the preceding block."""
     rank = dist.get_rank(group)
-    dev = k_chunks.device
-    n_req = torch.tensor([remote_ids.numel()], device=dev, dtype=torch.int64)
-    counts = [torch.zeros_like(n_req) for _ in range(world)]
-    dist.all_gather(counts, n_req, group=group)
-    counts = [int(c.item()) for c in counts]
-    width = max(max(counts), 1)
-    mine = torch.full((width,), -1, device=dev, dtype=torch.int64)
-    mine[:remote_ids.numel()] = remote_ids.to(torch.int64)
-    all_req = [torch.empty_like(mine) for _ in range(world)]
-    dist.all_gather(all_req, mine, group=group)
-    B, _, S, h, D = k_chunks.shape
-    ops: List[dist.P2POp] = []
-    send_keep = []
-    # what every peer wants from me
-    for peer in range(world):
-        if peer == rank:
-            continue
-        req = all_req[peer][:counts[peer]]
-        sel = req[(req >= rank * chunks_per_rank) & (req < (rank + 1) * chunks_per_rank)] - rank * chunks_per_rank
-        if sel.numel():
-            ks = k_chunks.index_select(1, sel).contiguous()
-            vs = v_chunks.index_select(1, sel).contiguous()
-            send_keep += [ks, vs]
-            ops += [dist.P2POp(dist.isend, ks, peer, group), dist.P2POp(dist.isend, vs, peer, group)]
-    # what I want from every peer (remote_ids is ascending, so per-owner groups are contiguous)
-    k_out = torch.empty((B, remote_ids.numel(), S, h, D), dtype=k_chunks.dtype, device=dev)
-    v_out = torch.empty_like(k_out)
-    owner = torch.div(remote_ids, chunks_per_rank, rounding_mode="floor")
-    recv_parts = []
-    for peer in range(world):
-        if peer == rank:
-            continue
-        n = int((owner == peer).sum().item())
-        if n:
-            lo = int((owner < peer).sum().item())
-            kb = torch.empty((B, n, S, h, D), dtype=k_chunks.dtype, device=dev)
-            vb = torch.empty_like(kb)
-            recv_parts.append((lo, n, kb, vb))
-            ops += [dist.P2POp(dist.irecv, kb, peer, group), dist.P2POp(dist.irecv, vb, peer, group)]
+    mine = part.blocks(rank)
+    tb = x.shape[1] // len(mine)
+    tails = {b: x[:, (i + 1) * tb - halo:(i + 1) * tb].contiguous() for i, b in enumerate(mine)}
+    out: List[Optional[torch.Tensor]] = [None] * len(mine)
+    ops, pending = [], []
+    # sends and receives are listed in ascending block order on every rank, so the pairs match up
+    for b in range(1, part.n_blocks):
+        src, dst = part.owner(b - 1), part.owner(b)
+        if src == rank and dst == rank:
+            out[mine.index(b)] = tails[b - 1]
+        elif src == rank:
+            ops.append(dist.P2POp(dist.isend, tails[b - 1], dst, group))
+        elif dst == rank:
+            buf = torch.empty_like(tails[mine[0]])
+            out[mine.index(b)] = buf
+            ops.append(dist.P2POp(dist.irecv, buf, src, group))
     if ops:
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
-    for lo, n, kb, vb in recv_parts:
-        k_out[:, lo:lo + n] = kb
-        v_out[:, lo:lo + n] = vb
-    return k_out, v_out
+        pending = dist.batch_isend_irecv(ops)
+    for req in pending:
+        req.wait()
+    return out
 
 
-def exchange_halo(x: torch.Tensor, halo: int, group=None) -> Optional[torch.Tensor]:
-    """x (B, Tl, h, D).  Returns the last `halo` tokens of the previous rank (None on rank 0)."""
-    world, rank = dist.get_world_size(group), dist.get_rank(group)
-    tail = x[:, -halo:].contiguous()
-    parts = [torch.empty_like(tail) for _ in range(world)]
-    dist.all_gather(parts, tail, group=group)
-    return parts[rank - 1] if rank > 0 else None
+def gather_chunk_keys(lk: torch.Tensor, lb: torch.Tensor, part: SeqPartition, group=None
+                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """lk (B, n_local, h, D'), lb (B, n_local, h): pooled keys and biases of this rank's chunks.  Returns them for
+    the whole sequence in chunk order: (B, N, h, D'), (B, N, h)."""
+    world = part.world
+    lk_all = torch.empty((world,) + tuple(lk.shape), dtype=lk.dtype, device=lk.device)
+    lb_all = torch.empty((world,) + tuple(lb.shape), dtype=lb.dtype, device=lb.device)
+    dist.all_gather(list(lk_all.unbind(0)), lk.contiguous(), group=group)
+    dist.all_gather(list(lb_all.unbind(0)), lb.contiguous(), group=group)
+    nb = lk.shape[1] // part.blocks_per_rank
+    order = part.block_order()                                   # gathered position -> block
+    inv = sorted(range(len(order)), key=lambda i: order[i])      # block -> gathered position
+
+    def reorder(t):
+        t = t.transpose(0, 1)                                    # (B, world, n_local, ...)
+        t = t.reshape(t.shape[0], len(order), nb, *t.shape[3:])
+        return t[:, inv].flatten(1, 2)
+    return reorder(lk_all), reorder(lb_all)
+
+
+@dataclass
+class FetchPlan:
+    """Result of the request exchange: what to send, what arrives, and where it goes."""
+    send_index: torch.Tensor      # (n_send, 3) [b, h, local chunk] of the tiles this rank sends, grouped by peer
+    recv_index: torch.Tensor      # (n_recv, 3) [b, h, staging slot] of the tiles that arrive, in arrival order
+    send_counts: List[int]
+    recv_counts: List[int]
+    n_stage: int                  # staging slots taken by remote chunks (the widest (b, h) list)
+    remapped: torch.Tensor        # ids rewritten to staging slots (local chunks follow the remote slots)
+
+
+def plan_fetch(indices: torch.Tensor, n_chunks: int, part: SeqPartition, group=None) -> FetchPlan:
+    """indices (B, L, h, K): global chunk ids selected by this rank's tokens (−1 = padding), per kv head.
+    Exchanges the per-head sets of wanted chunks with their owners and returns the transfer plan."""
+    world, rank = part.world, dist.get_rank(group)
+    B, L, h, K = indices.shape
+    dev = indices.device
+    nbk = n_chunks // part.n_blocks                              # chunks per block
+    n_local = nbk * part.blocks_per_rank
+    # chunk id -> (owner, position among the owner's chunks), as one index into the rank-major order
+    order = part.block_order()
+    pos_of_block = torch.tensor(sorted(range(len(order)), key=lambda i: order[i]), device=dev)
+    ids = indices.long()
+    valid = ids >= 0
+    safe = ids.clamp_min(0)
+    rank_major = pos_of_block[safe // nbk] * nbk + safe % nbk    # in [0, N): owner·n_local + local chunk
+    # wanted[b, h, rank-major chunk]; column N collects the padding
+    flat = torch.where(valid, rank_major, torch.full_like(rank_major, n_chunks))
+    wanted = torch.zeros((B, h, n_chunks + 1), dtype=torch.bool, device=dev)
+    wanted.scatter_(2, flat.permute(0, 2, 1, 3).reshape(B, h, L * K), True)
+    wanted = wanted[..., :n_chunks].reshape(B, h, world, n_local)
+    wanted[:, :, rank] = False                                   # my own chunks are not fetched
+    need = wanted.permute(2, 0, 1, 3).contiguous()               # (owner, B, h, local chunk)
+    want = torch.empty_like(need)                                # (requester, B, h, my local chunk)
+    dist.all_to_all_single(want.view(torch.uint8), need.view(torch.uint8), group=group)
+    # staging slot of a remote chunk: its rank among the chunks its (b, h) wants, in rank-major order
+    slot = (wanted.reshape(B, h, n_chunks).long().cumsum(-1) - 1)
+    per_head = wanted.reshape(B, h, n_chunks).sum(-1)
+    counts = torch.cat([want.flatten(1).sum(1), need.flatten(1).sum(1), per_head.max().reshape(1)]).to(torch.int64)
+    counts = counts.cpu().tolist()                               # the one host synchronisation of the exchange
+    send_counts, recv_counts, n_stage = counts[:world], counts[world:2 * world], counts[2 * world]
+    snd = torch.nonzero_static(want, size=sum(send_counts))      # rows [peer, b, h, chunk], sorted: grouped by peer
+    rcv = torch.nonzero_static(need, size=sum(recv_counts))      # rows [owner, b, h, chunk]: the arrival order
+    rcv_slot = slot[rcv[:, 1], rcv[:, 2], rcv[:, 0] * n_local + rcv[:, 3]]
+    recv_index = torch.stack([rcv[:, 1], rcv[:, 2], rcv_slot], 1)
+    # ids -> staging slots: remote chunks by their slot, local chunks after the n_stage remote slots
+    is_local = valid & (rank_major // n_local == rank)
+    hh = torch.arange(h, device=dev).view(1, 1, h, 1).expand_as(ids)
+    bb = torch.arange(B, device=dev).view(B, 1, 1, 1).expand_as(ids)
+    remote_slot = slot[bb, hh, rank_major.clamp_max(n_chunks - 1)]
+    remapped = torch.where(is_local, n_stage + rank_major % n_local, remote_slot)
+    remapped = torch.where(valid, remapped, torch.full_like(remapped, -1)).to(indices.dtype)
+    return FetchPlan(snd[:, 1:], recv_index, send_counts, recv_counts, n_stage, remapped)
+
+
+def fetch_chunks(x_chunks: torch.Tensor, plan: FetchPlan, group=None) -> torch.Tensor:
+    """x_chunks (B, n_local, S, h, D): this rank's chunks of K or V.  Returns the staging buffer
+    (B, n_stage + n_local, S, h, D): the fetched remote tiles in their slots, then the local chunks.  Slots that
+    no id refers to stay uninitialised."""
+    B, n_local, S, h, D = x_chunks.shape
+    si, ri = plan.send_index, plan.recv_index
+    send = x_chunks[si[:, 0], si[:, 2], :, si[:, 1], :].contiguous()          # (n_send, S, D)
+    recv = torch.empty((ri.shape[0], S, D), dtype=x_chunks.dtype, device=x_chunks.device)
+    dist.all_to_all_single(recv, send, output_split_sizes=plan.recv_counts, input_split_sizes=plan.send_counts,
+                           group=group)
+    stage = torch.empty((B, plan.n_stage + n_local, S, h, D), dtype=x_chunks.dtype, device=x_chunks.device)
+    stage[ri[:, 0], ri[:, 2], :, ri[:, 1], :] = recv
+    stage[:, plan.n_stage:] = x_chunks
+    return stage
 
 
 # ------------------------------------------------------------------------------------------
 # the chain
 # ------------------------------------------------------------------------------------------
 def context_parallel_forward(q, k, v, lmk_q, *, h_kv: int, topk: int, chunk_size: int = 64,
-                             window_size: int = 512, group=None, return_aux: bool = False):
-    """Forward of the attention chain for this rank's tokens.  q, lmk_q (B, Tl, h_q, D); k, v
-    (B, Tl, h_kv, D); every rank holds the same Tl, a multiple of chunk_size and >= window + chunk."""
+                             window_size: int = 512, partition: str = "zigzag", group=None,
+                             return_aux: bool = False, timings: Optional[Dict[str, float]] = None):
+    """Forward of the attention chain for this rank's tokens.  q, lmk_q (B, Tl, h_q, D); k, v (B, Tl, h_kv, D):
+    the rank's blocks concatenated (see SeqPartition); every block is a multiple of chunk_size and at least
+    window + chunk long.  With `timings` (a dict) the stages are timed with CUDA events, which synchronises."""
     from . import ops
     world, rank = dist.get_world_size(group), dist.get_rank(group)
+    part = SeqPartition(world, partition)
+    mine = part.blocks(rank)
     B, Tl, h_q, D = q.shape
     S, W = chunk_size, window_size
-    assert Tl % S == 0, "the local sequence length must be a multiple of the chunk size"
-    Nl = Tl // S
+    tb = Tl // len(mine)
+    assert tb * len(mine) == Tl and tb % S == 0, "every block must be a whole number of chunks"
     halo = ((W + S - 1) // S) * S
-    assert Tl >= halo, "the local sequence must cover the sliding window"
-    # 1. sliding-window branch with the previous rank's tail as halo
-    hk, hv = exchange_halo(k, halo, group), exchange_halo(v, halo, group)
-    if rank > 0:
-        k_sw, v_sw = torch.cat([hk, k], 1), torch.cat([hv, v], 1)
-        swa_o, lse = ops.flex_attn_tl(q, k_sw, v_sw, W, S, training=False, mask_lmk=True, expand_to_chunk=True,
-                                      kv_start=rank * Tl - halo)
-    else:
-        swa_o, lse = ops.flex_attn_tl(q, k, v, W, S, training=False, mask_lmk=True, expand_to_chunk=True)
-    lse_act = lse.to(q.dtype)
-    # 2. pooled chunk keys of the local chunks, all-gathered
-    kc = k.unflatten(1, (Nl, S))
+    assert tb >= halo, "a block must cover the sliding window"
+    nbk = tb // S
+    n_chunks = nbk * part.n_blocks
+    marks = []
+
+    def mark(name):
+        if timings is not None and q.is_cuda:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            marks.append((name, e))
+
+    mark("start")
+    # 1. pooled chunk keys of the local chunks, all-gathered into chunk order
+    kc = k.unflatten(1, (Tl // S, S))
     lk, lb = ops.chunk_attn_pool(lmk_q[:, S - 1::S], kc)
-    lk_all = [torch.empty_like(lk) for _ in range(world)]
-    lb_all = [torch.empty_like(lb) for _ in range(world)]
-    dist.all_gather(lk_all, lk.contiguous(), group=group)
-    dist.all_gather(lb_all, lb.contiguous(), group=group)
-    lmk_k, prior_b = torch.cat(lk_all, 1), torch.cat(lb_all, 1)
-    # 3. selection over all chunk keys at this rank's absolute positions
-    idx, sc = ops.online_softmax_topk_head(lmk_q, lmk_k, lse_act, topk, block_size=S, window_size=W,
-                                           is_training=False, q_offset=rank * Tl, G=lmk_k.shape[2] // h_kv,
-                                           bias=prior_b)
-    g_b = prior_b.shape[2] // idx.shape[2]
-    idx_hq = idx.repeat_interleave(g_b, dim=2) if g_b != 1 else idx
-    gathered = torch.gather(prior_b.unsqueeze(-1).expand(-1, -1, -1, topk), 1, idx_hq.clamp_min(0).long())
-    w = F.softmax(torch.cat([sc + gathered.to(sc.dtype), lse_act.unsqueeze(-1)], -1), -1).to(q.dtype)
-    # 4. fetch the selected remote chunks into a local staging buffer, rewrite the ids
-    remote_ids, idx_local = plan_remote_chunks(idx, rank * Nl, Nl)
-    vc = v.unflatten(1, (Nl, S))
-    rk, rv = exchange_chunks(kc, vc, remote_ids, Nl, group)
-    k_stage = torch.cat([rk, kc], 1).flatten(1, 2)
-    v_stage = torch.cat([rv, vc], 1).flatten(1, 2)
+    lmk_k, prior_b = gather_chunk_keys(lk, lb, part, group)
+    mark("pool+allgather")
+    # 2. sliding-window branch per block, with the preceding block's tail as halo
+    halos_k, halos_v = exchange_halo(k, part, halo, group), exchange_halo(v, part, halo, group)
+    mark("halo")
+    swa_o, lse = [], []
+    for i, blk in enumerate(mine):
+        sl = slice(i * tb, (i + 1) * tb)
+        if blk > 0:
+            o_i, l_i = ops.flex_attn_tl(q[:, sl], torch.cat([halos_k[i], k[:, sl]], 1),
+                                        torch.cat([halos_v[i], v[:, sl]], 1), W, S, training=False, mask_lmk=True,
+                                        expand_to_chunk=True, kv_start=blk * tb - halo)
+        else:
+            o_i, l_i = ops.flex_attn_tl(q[:, sl], k[:, sl], v[:, sl], W, S, training=False, mask_lmk=True,
+                                        expand_to_chunk=True)
+        swa_o.append(o_i)
+        lse.append(l_i)
+    swa_o, lse = torch.cat(swa_o, 1), torch.cat(lse, 1)
+    lse_act = lse.to(q.dtype)
+    mark("swa")
+    # 3. selection over all chunk keys at each block's absolute positions, inter-chunk softmax
+    idx, sc = [], []
+    for i, blk in enumerate(mine):
+        sl = slice(i * tb, (i + 1) * tb)
+        i_i, s_i = ops.online_softmax_topk_head(lmk_q[:, sl], lmk_k, lse_act[:, sl], topk, block_size=S,
+                                                window_size=W, is_training=False, q_offset=blk * tb,
+                                                G=lmk_k.shape[2] // h_kv, bias=prior_b)
+        idx.append(i_i)
+        sc.append(s_i)
+    idx, sc = torch.cat(idx, 1), torch.cat(sc, 1)
+    w = ops.inter_chunk_softmax(sc, idx, lse_act, prior_b)
+    mark("selection")
+    # 4. fetch the selected remote chunks per kv head into a local staging buffer, rewrite the ids
+    plan = plan_fetch(idx, n_chunks, part, group)
+    mark("plan")
+    k_stage = fetch_chunks(kc, plan, group).flatten(1, 2)
+    v_stage = fetch_chunks(v.unflatten(1, (Tl // S, S)), plan, group).flatten(1, 2)
+    mark("fetch")
     # 5. sparse chunk attention on local memory only, combine
-    o_h = ops.HiLS_block_M_head(q, k_stage, v_stage, w.contiguous(), idx_local.to(torch.int32).contiguous(),
+    o_h = ops.HiLS_block_M_head(q, k_stage, v_stage, w.contiguous(), plan.remapped.to(torch.int32).contiguous(),
                                 block_size=S, mask_last_token=True, is_training=False)
     o = torch.addcmul(o_h, swa_o, w[..., -1:])
+    mark("sparse+combine")
+    if timings is not None and marks:
+        torch.cuda.synchronize()
+        for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+            timings[name] = timings.get(name, 0.0) + a.elapsed_time(b)
     if return_aux:
-        return o, {"indices": idx, "remote_chunks": int(remote_ids.numel()), "lse_swa": lse}
+        es = k.element_size()
+        return o, {"indices": idx, "lse_swa": lse, "remote_tiles": sum(plan.recv_counts),
+                   "staging_slots": plan.n_stage,
+                   "fetch_bytes": 2 * sum(plan.recv_counts) * S * D * es,
+                   "allgather_bytes": (lmk_k.numel() * lmk_k.element_size() + prior_b.numel() * prior_b.element_size())
+                   * (world - 1) // world,
+                   "halo_bytes": 2 * sum(1 for b in mine if b > 0 and part.owner(b - 1) != rank) * B * halo * h_kv * D * es}
     return o

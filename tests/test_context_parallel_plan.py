@@ -1,9 +1,11 @@
-"""Host-side logic of the context-parallel path on CPU: two gloo ranks exchange the K/V tiles of the
-remote chunks they selected; the staged tiles and the rewritten ids must reproduce a gather from the
-full (unsharded) tensors.  Also the halo exchange of the sliding-window branch."""
+"""Host-side logic of the context-parallel path on CPU with gloo ranks: the per-head request exchange and the
+uneven all-to-all of K/V tiles must reproduce a gather from the full (unsharded) tensors through the rewritten
+ids; the halo exchange must deliver the tokens that precede each block; the all-gather of the pooled keys must
+come back in chunk order.  Contiguous and zig-zag partitions, 2 and 4 ranks."""
 import os
 import socket
 
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -17,56 +19,73 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, kind, out):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from hils_attention_b200.parallel import exchange_chunks, exchange_halo, plan_remote_chunks
+        from hils_attention_b200.parallel import SeqPartition, exchange_halo, fetch_chunks, gather_chunk_keys, plan_fetch
+        part = SeqPartition(world, kind)
         g = torch.Generator().manual_seed(5)
-        B, Nl, S, h, D, L, K = 2, 6, 4, 2, 8, 10, 5
-        N = Nl * world
+        B, nbk, S, h, D, K = 2, 3, 4, 2, 8, 5
+        N = nbk * part.n_blocks
+        n_local = nbk * part.blocks_per_rank
+        L = n_local * S
         k_full = torch.randn(B, N, S, h, D, generator=g)
         v_full = torch.randn(B, N, S, h, D, generator=g)
         idx = torch.randint(-1, N, (world, B, L, h, K), generator=g, dtype=torch.int32)[rank]
-        kc, vc = k_full[:, rank * Nl:(rank + 1) * Nl], v_full[:, rank * Nl:(rank + 1) * Nl]
-        remote, remapped = plan_remote_chunks(idx, rank * Nl, Nl)
-        assert bool(((remote < rank * Nl) | (remote >= (rank + 1) * Nl)).all())
-        rk, rv = exchange_chunks(kc, vc, remote, Nl)
-        k_stage, v_stage = torch.cat([rk, kc], 1), torch.cat([rv, vc], 1)
-        ok = True
+        if rank == world - 1:
+            idx[:, :, 1] = -1                       # a head that wants nothing at all
+        kc, vc = part.shard(k_full, rank), part.shard(v_full, rank)
+        plan = plan_fetch(idx, N, part)
+        k_stage, v_stage = fetch_chunks(kc, plan), fetch_chunks(vc, plan)
+        ok = k_stage.shape[1] == plan.n_stage + n_local
+        own = {b * nbk + c for b in part.blocks(rank) for c in range(nbk)}
+        wanted = {(b, hh, int(c)) for b in range(B) for hh in range(h) for c in idx[b, :, hh].flatten().tolist()
+                  if c >= 0 and c not in own}
+        ok &= sum(plan.recv_counts) == len(wanted)           # every remote (head, chunk) tile travels once
         for b in range(B):
             for l in range(L):
                 for hh in range(h):
                     for kk in range(K):
-                        c, s = int(idx[b, l, hh, kk]), int(remapped[b, l, hh, kk])
+                        c, s = int(idx[b, l, hh, kk]), int(plan.remapped[b, l, hh, kk])
                         if c < 0:
                             ok &= s == -1
                         else:
                             ok &= torch.equal(k_stage[b, s, :, hh], k_full[b, c, :, hh])
                             ok &= torch.equal(v_stage[b, s, :, hh], v_full[b, c, :, hh])
-        x = torch.arange(B * 12 * h * D, dtype=torch.float32).view(B, 12, h, D) + 1000 * rank
-        halo = exchange_halo(x, 5)
-        if rank == 0:
-            ok &= halo is None
-        else:
-            ok &= torch.equal(halo, (x - 1000)[:, -5:])
+        # halo: the tokens that precede each of my blocks
+        T = N * S
+        x_full = torch.arange(B * T * h * D, dtype=torch.float32).view(B, T, h, D)
+        halos = exchange_halo(part.shard(x_full, rank), part, 5)
+        tb = T // part.n_blocks
+        for i, blk in enumerate(part.blocks(rank)):
+            if blk == 0:
+                ok &= halos[i] is None
+            else:
+                ok &= torch.equal(halos[i], x_full[:, blk * tb - 5:blk * tb])
+        # pooled keys come back in chunk order
+        lk_full = torch.randn(B, N, h, D, generator=g)
+        lb_full = torch.randn(B, N, h, generator=g)
+        lk, lb = gather_chunk_keys(part.shard(lk_full, rank), part.shard(lb_full, rank), part)
+        ok &= torch.equal(lk, lk_full) and torch.equal(lb, lb_full)
         out[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
 
 
-def test_remote_chunk_exchange_two_ranks():
-    world = 2
+@pytest.mark.parametrize("world,kind", [(2, "contiguous"), (2, "zigzag"), (4, "zigzag")])
+def test_remote_chunk_exchange(world, kind):
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
-    assert out.get(0) is True and out.get(1) is True
+    mp.spawn(_worker, args=(world, _free_port(), kind, out), nprocs=world, join=True)
+    assert all(out.get(r) is True for r in range(world)), dict(out)
 
 
-def test_plan_without_remote_chunks():
-    from hils_attention_b200.parallel import plan_remote_chunks
-    idx = torch.tensor([[[[4, 6, -1]]]], dtype=torch.int32)
-    remote, remapped = plan_remote_chunks(idx, 4, 4)
-    assert remote.numel() == 0
-    assert remapped.tolist() == [[[[0, 2, -1]]]]
+def test_partition_balances_causal_work():
+    from hils_attention_b200.parallel import SeqPartition
+    part = SeqPartition(4, "zigzag")
+    assert sorted(b for r in range(4) for b in part.blocks(r)) == list(range(8))
+    assert all(part.owner(b) == r for r in range(4) for b in part.blocks(r))
+    # candidate chunks scored by a rank are proportional to the sum of its blocks' positions: equal on every rank
+    assert len({sum(part.blocks(r)) for r in range(4)}) == 1
