@@ -96,13 +96,7 @@ __global__ void __launch_bounds__(256) topk_bwd_mma_kernel(TopkBwdMmaParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) dk[nb][e] = 0.f;
   };
-  if (keep_dk) load_keys(0);
-
-  for (int blk = 0; blk < kBwdBlocks; ++blk) {
-    const int r0 = cta_row0 + blk * kBwdRows;
-    if (r0 >= n_rows) break;
-    __syncthreads();                                             // previous block's tiles are consumed
-    if (tid == 0) max_id_s = -1;
+  auto load_q = [&](int r0) {
     for (int i = tid; i < kBwdRows * CPR; i += 256) {
       const int row = i / CPR, col = (i - row * CPR) * 8;
       uint4 x = make_uint4(0u, 0u, 0u, 0u);
@@ -113,104 +107,156 @@ __global__ void __launch_bounds__(256) topk_bwd_mma_kernel(TopkBwdMmaParams p) {
       }
       *reinterpret_cast<uint4*>(q_s + row * RS + col) = x;
     }
+  };
+  // number of candidate tiles the block's rows reach (from its largest selected id); all threads call it
+  auto block_ntile = [&](int r0) -> int {
+    if (tid == 0) max_id_s = -1;
     __syncthreads();
-    {  // largest selected id of the block -> number of candidate tiles to visit
-      const int row = tid >> 2;
-      int mx = -1;
-      if (r0 + row < n_rows) {
-        int64_t ri, th;
-        row_ptrs(r0 + row, ri, th);
-        for (int k = tid & 3; k < p.K; k += 4) mx = max(mx, p.ids[th * p.K + k]);
-      }
-      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      if ((tid & 3) == 0 && mx >= 0) atomicMax(&max_id_s, mx);
+    const int row = tid >> 2;
+    int mx = -1;
+    if (r0 + row < n_rows) {
+      int64_t ri, th;
+      row_ptrs(r0 + row, ri, th);
+      for (int k = tid & 3; k < p.K; k += 4) mx = max(mx, p.ids[th * p.K + k]);
     }
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    if ((tid & 3) == 0 && mx >= 0) atomicMax(&max_id_s, mx);
     __syncthreads();
     const int max_id = max_id_s;
-    const int ntile = max_id < 0 ? 0 : min(ntile_all, max_id / kBwdTile + 1);
-    float dq[NB / 2][4];                                         // warp w: rows 16(w&3).., d-half (w>>2)
+    __syncthreads();                                             // everyone has read it before the next reset
+    return max_id < 0 ? 0 : min(ntile_all, max_id / kBwdTile + 1);
+  };
+  // dense [64 x 128] tile of the block's score gradients that fall into candidates c0..c0+127 (ends with a barrier)
+  auto build_tile = [&](int r0, int c0) {
+    for (int i = tid; i < kBwdRows * kDsStride / 8; i += 256) reinterpret_cast<uint4*>(ds_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    const int row = tid >> 2;                                    // scatter: four threads per row
+    if (r0 + row < n_rows) {
+      int64_t ri, th;
+      row_ptrs(r0 + row, ri, th);
+      for (int k = tid & 3; k < p.K; k += 4) {
+        const int id = p.ids[th * p.K + k];
+        if (id >= c0 && id < c0 + kBwdTile && id < p.N) ds_s[row * kDsStride + id - c0] = p.ds[ri * p.K + k];
+      }
+    }
+    __syncthreads();
+  };
+  // dq += tile . k'     (warp w: rows 16(w&3).., d-half (w>>2))
+  auto mma_dq = [&](float (&dq)[NB / 2][4]) {
+    const int mrow = (warp & 3) * 16, nhalf = (warp >> 2) * (D / 2);
+    const uint32_t a_addr = ds32 + (uint32_t)((mrow + (lane & 7) + ((lane >> 3) & 1) * 8) * kDsStride + (lane >> 4) * 8) * 2u;
+    const uint32_t b_addr = k32 + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * RS + nhalf + ((lane >> 4) & 1) * 8) * 2u;
+#pragma unroll
+    for (int kk = 0; kk < kBwdTile / 16; ++kk) {
+      uint32_t a[4];
+      ldsm4(a, a_addr + kk * 32);
+#pragma unroll
+      for (int np = 0; np < NB / 4; ++np) {
+        uint32_t bb[4];
+        ldsm4_t(bb, b_addr + (uint32_t)(kk * 16 * RS + np * 16) * 2u);
+        mma16816(dq[2 * np], a, bb[0], bb[1]);
+        mma16816(dq[2 * np + 1], a, bb[2], bb[3]);
+      }
+    }
+  };
+  // dk' += tile^T . q   (warp w: candidates 16w..16w+15 of the tile)
+  auto mma_dk = [&]() {
+    const int mcol = warp * 16;
+    const uint32_t a_addr = ds32 + (uint32_t)(((lane & 7) + ((lane >> 4) & 1) * 8) * kDsStride + mcol + ((lane >> 3) & 1) * 8) * 2u;
+    const uint32_t b_addr = q32 + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * RS + ((lane >> 4) & 1) * 8) * 2u;
+#pragma unroll
+    for (int kk = 0; kk < kBwdRows / 16; ++kk) {
+      uint32_t a[4];
+      ldsm4_t(a, a_addr + (uint32_t)(kk * 16 * kDsStride) * 2u);
+#pragma unroll
+      for (int np = 0; np < NB / 2; ++np) {
+        uint32_t bb[4];
+        ldsm4_t(bb, b_addr + (uint32_t)(kk * 16 * RS + np * 16) * 2u);
+        mma16816(dk[2 * np], a, bb[0], bb[1]);
+        mma16816(dk[2 * np + 1], a, bb[2], bb[3]);
+      }
+    }
+  };
+  auto store_dq = [&](int r0, float (&dq)[NB / 2][4]) {
+    const int mrow = (warp & 3) * 16, nhalf = (warp >> 2) * (D / 2);
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      const int r = r0 + mrow + (lane >> 2) + hr * 8;
+      if (r < n_rows) {
+        int64_t ri, th;
+        row_ptrs(r, ri, th);
+        bf16* dst = p.dq + ri * D + nhalf + (lane & 3) * 2;
+#pragma unroll
+        for (int nb = 0; nb < NB / 2; ++nb)
+          *reinterpret_cast<__nv_bfloat162*>(dst + nb * 8) =
+              __floats2bfloat162_rn(dq[nb][2 * hr] * p.scale, dq[nb][2 * hr + 1] * p.scale);
+      }
+    }
+  };
+
+  if (keep_dk) {
+    // one candidate tile: its keys stay in shared memory and the dk' accumulators in registers over all row blocks
+    load_keys(0);
+    for (int blk = 0; blk < kBwdBlocks; ++blk) {
+      const int r0 = cta_row0 + blk * kBwdRows;
+      if (r0 >= n_rows) break;
+      __syncthreads();                                           // previous block's tiles are consumed
+      load_q(r0);
+      const int ntile = block_ntile(r0);
+      float dq[NB / 2][4];
+#pragma unroll
+      for (int nb = 0; nb < NB / 2; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dq[nb][e] = 0.f;
+      if (ntile > 0) {
+        build_tile(r0, 0);
+        mma_dq(dq);
+        mma_dk();
+      }
+      store_dq(r0, dq);
+    }
+    flush_dk(0);
+    return;
+  }
+
+  // Several candidate tiles.  Phase 1, row block outer: dq of a block over the tiles its rows reach.  Phase 2, tile
+  // outer: dk' of a tile accumulates in registers over ALL row blocks of the CTA and leaves as atomics once per
+  // (CTA, tile) - an eighth of the atomic traffic of flushing per (row block, tile).
+  __shared__ int nt_s[kBwdBlocks];
+  int nt_max = 0;
+  for (int blk = 0; blk < kBwdBlocks; ++blk) {
+    const int r0 = cta_row0 + blk * kBwdRows;
+    int ntile = 0;
+    if (r0 < n_rows) ntile = block_ntile(r0);
+    if (tid == 0) nt_s[blk] = ntile;
+    nt_max = max(nt_max, ntile);
+    if (r0 >= n_rows) continue;
+    float dq[NB / 2][4];
 #pragma unroll
     for (int nb = 0; nb < NB / 2; ++nb)
 #pragma unroll
       for (int e = 0; e < 4; ++e) dq[nb][e] = 0.f;
     for (int t = 0; t < ntile; ++t) {
-      const int c0 = t * kBwdTile;
-      if (t > 0 || !keep_dk) {
-        __syncthreads();                                         // the previous tile is consumed
-        if (!keep_dk) load_keys(c0);
-      }
-      for (int i = tid; i < kBwdRows * kDsStride / 8; i += 256) reinterpret_cast<uint4*>(ds_s)[i] = make_uint4(0u, 0u, 0u, 0u);
-      __syncthreads();
-      {  // scatter: four threads per row
-        const int row = tid >> 2;
-        if (r0 + row < n_rows) {
-          int64_t ri, th;
-          row_ptrs(r0 + row, ri, th);
-          for (int k = tid & 3; k < p.K; k += 4) {
-            const int id = p.ids[th * p.K + k];
-            if (id >= c0 && id < c0 + kBwdTile && id < p.N) ds_s[row * kDsStride + id - c0] = p.ds[ri * p.K + k];
-          }
-        }
-      }
-      __syncthreads();
-      // dq += tile . k'
-      {
-        const int mrow = (warp & 3) * 16, nhalf = (warp >> 2) * (D / 2);
-        const uint32_t a_addr = ds32 + (uint32_t)((mrow + (lane & 7) + ((lane >> 3) & 1) * 8) * kDsStride + (lane >> 4) * 8) * 2u;
-        const uint32_t b_addr = k32 + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * RS + nhalf + ((lane >> 4) & 1) * 8) * 2u;
-#pragma unroll
-        for (int kk = 0; kk < kBwdTile / 16; ++kk) {
-          uint32_t a[4];
-          ldsm4(a, a_addr + kk * 32);
-#pragma unroll
-          for (int np = 0; np < NB / 4; ++np) {
-            uint32_t bb[4];
-            ldsm4_t(bb, b_addr + (uint32_t)(kk * 16 * RS + np * 16) * 2u);
-            mma16816(dq[2 * np], a, bb[0], bb[1]);
-            mma16816(dq[2 * np + 1], a, bb[2], bb[3]);
-          }
-        }
-      }
-      // dk' += tile^T . q
-      {
-        const int mcol = warp * 16;                              // candidates of this warp
-        const uint32_t a_addr = ds32 + (uint32_t)(((lane & 7) + ((lane >> 4) & 1) * 8) * kDsStride + mcol + ((lane >> 3) & 1) * 8) * 2u;
-        const uint32_t b_addr = q32 + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * RS + ((lane >> 4) & 1) * 8) * 2u;
-#pragma unroll
-        for (int kk = 0; kk < kBwdRows / 16; ++kk) {
-          uint32_t a[4];
-          ldsm4_t(a, a_addr + (uint32_t)(kk * 16 * kDsStride) * 2u);
-#pragma unroll
-          for (int np = 0; np < NB / 2; ++np) {
-            uint32_t bb[4];
-            ldsm4_t(bb, b_addr + (uint32_t)(kk * 16 * RS + np * 16) * 2u);
-            mma16816(dk[2 * np], a, bb[0], bb[1]);
-            mma16816(dk[2 * np + 1], a, bb[2], bb[3]);
-          }
-        }
-      }
-      if (!keep_dk) flush_dk(c0);
+      __syncthreads();                                           // the previous tile is consumed
+      load_keys(t * kBwdTile);
+      build_tile(r0, t * kBwdTile);
+      mma_dq(dq);
     }
-    // dq rows of the block
-    {
-      const int mrow = (warp & 3) * 16, nhalf = (warp >> 2) * (D / 2);
-#pragma unroll
-      for (int hr = 0; hr < 2; ++hr) {
-        const int r = r0 + mrow + (lane >> 2) + hr * 8;
-        if (r < n_rows) {
-          int64_t ri, th;
-          row_ptrs(r, ri, th);
-          bf16* dst = p.dq + ri * D + nhalf + (lane & 3) * 2;
-#pragma unroll
-          for (int nb = 0; nb < NB / 2; ++nb)
-            *reinterpret_cast<__nv_bfloat162*>(dst + nb * 8) =
-                __floats2bfloat162_rn(dq[nb][2 * hr] * p.scale, dq[nb][2 * hr + 1] * p.scale);
-        }
-      }
-    }
+    store_dq(r0, dq);
   }
-  if (keep_dk) flush_dk(0);
+  __syncthreads();
+  for (int t = 0; t < nt_max; ++t) {
+    for (int blk = 0; blk < kBwdBlocks; ++blk) {
+      const int r0 = cta_row0 + blk * kBwdRows;
+      if (r0 >= n_rows || nt_s[blk] <= t) continue;
+      __syncthreads();                                           // the previous block's tiles are consumed
+      load_q(r0);
+      build_tile(r0, t * kBwdTile);
+      mma_dk();
+    }
+    flush_dk(t * kBwdTile);
+  }
 }
 
 // d_q in bf16; dl: fp32 accumulator of the chunk-key gradient, zeroed by the caller.

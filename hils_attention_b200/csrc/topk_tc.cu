@@ -8,16 +8,20 @@
 // tokens of one (batch, head) and ONE THREAD owns one token: the scores of a tile of 128 chunk keys are a single
 // 128 x 128 tcgen05 product whose accumulator row a thread reads straight from its TMEM lane, so every step of the
 // selection is 128 tokens wide and free of cross-lane traffic.  The scores are never stored: the key tiles are
-// streamed three times (they are small and L2-resident) and the product is recomputed, which costs the tensor pipe
-// next to nothing:
-//   pass 0  log-sum-exp of the row (running maximum and sum per 32 columns);
-//   pass 1  the row's 32 largest keys, exactly: every 32 columns are sorted by a bitonic network in registers and
-//           merged with the running sorted list (max(list[i], chunk[31-i]) is the top half of the union, one more
-//           half-cleaner stage sorts it).  No data-dependent branch, so the 32 rows of a warp never diverge (a
-//           replace-the-minimum list costs six times more: some lane of the warp inserts at almost every step).
-//           The K-th entry is the threshold; the entries above it tell how many candidates EQUAL to it may be taken;
-//   pass 2  candidates are scanned in id order; those above the threshold, and the first ones equal to it, are
-//           written out with their raw scores: ids come out ascending without a sort.
+// streamed twice (they are small and L2-resident) and the product is recomputed, which costs the tensor pipe next
+// to nothing:
+//   pass 0  log-sum-exp of the row (running maximum and sum per 32 columns) AND the row's 32 largest values v, exactly.
+//           key = v - lse_total is a non-decreasing function of v, so the K-th largest key and the number of keys
+//           strictly above it follow from the 32 largest v once lse_total is known.  A value enters the list only if
+//           it beats the current K-th value: such values (a share of K/n of the stream after n candidates) are
+//           appended to a 16-entry buffer per token in shared memory, and only when some token's buffer would
+//           overflow does the warp sort the buffered values in registers (bitonic network) and merge them into the
+//           running sorted lists (max(list[i], sorted[31-i]) is the top half of the union, one half-cleaner stage
+//           sorts it); the 32 columns that caused the overflow go through the same network.  Sorting every 32
+//           columns unconditionally, as an earlier version did, cost three times the instructions: some lane of a
+//           warp has a qualifying value in almost every group, so a data-dependent skip never fires;
+//   pass 1  candidates are scanned in id order; those whose key is above the K-th key, and the first ones equal to
+//           it, are written out with their raw scores: ids come out ascending without a sort.
 // All mbarrier waits are bounded; on expiry the kernel records a status word, every role leaves its loop, TMEM is
 // released and the CTA returns.
 #include "common.cuh"
@@ -95,6 +99,59 @@ __device__ __forceinline__ void sel_merge_top32(float (&top)[32], const float (&
     }
 }
 
+// descending bitonic sort of 16 registers (80 compare-exchanges)
+__device__ __forceinline__ void sel_sort16_desc(float (&x)[16]) {
+#pragma unroll
+  for (int k = 2; k <= 16; k <<= 1)
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1)
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int l = i ^ j;
+        if (l > i) {
+          const bool desc = (i & k) == 0;
+          const float a = x[i], c = x[l];
+          x[i] = desc ? fmaxf(a, c) : fminf(a, c);
+          x[l] = desc ? fminf(a, c) : fmaxf(a, c);
+        }
+      }
+}
+// top[] (sorted descending) <- the 32 largest of top[] and the 16 values c[] (sorted descending)
+__device__ __forceinline__ void sel_merge_top32_16(float (&top)[32], const float (&c)[16]) {
+#pragma unroll
+  for (int i = 16; i < 32; ++i) top[i] = fmaxf(top[i], c[31 - i]);
+#pragma unroll
+  for (int j = 16; j > 0; j >>= 1)
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int l = i ^ j;
+      if (l > i) {
+        const float a = top[i], d = top[l];
+        top[i] = fmaxf(a, d);
+        top[l] = fminf(a, d);
+      }
+    }
+}
+// the K-th entry of a descending list (K is not a compile-time constant: a select chain, no local memory)
+__device__ __forceinline__ float sel_kth(const float (&top)[32], int K) {
+  float kth = top[0];
+#pragma unroll
+  for (int j = 1; j < 32; ++j) kth = (j == K - 1) ? top[j] : kth;
+  return kth;
+}
+
+constexpr int kSelCap = 16;   // buffered qualifying values per token between two merges
+constexpr int kSelDirectTiles = 4;   // tiles at the head of a row's stream that are sorted unconditionally (measured best)
+
+// the first n buffered values of this token (entry j at cand[j * 128]) -> its sorted list
+__device__ __forceinline__ void sel_flush(float (&top)[32], const float* cand, int n) {
+  float c16[16];
+#pragma unroll
+  for (int j = 0; j < kSelCap; ++j) c16[j] = (j < n) ? cand[j * 128] : -CUDART_INF_F;
+  sel_sort16_desc(c16);
+  sel_merge_top32_16(top, c16);
+}
+
 template <int D>
 __global__ void __launch_bounds__(kSelTcThreads, 2) topk_fwd_tc_kernel(TopkParams p, const __grid_constant__ CUtensorMap tmQ,
                                                                       const __grid_constant__ CUtensorMap tmK) {
@@ -108,6 +165,7 @@ __global__ void __launch_bounds__(kSelTcThreads, 2) topk_fwd_tc_kernel(TopkParam
 
   __shared__ uint64_t q_full, kv_full[3], kv_free[3], s_full[2], s_free[2], bias_full[2];
   __shared__ float bias_s[2][128];
+  __shared__ float cand_s[kSelCap * 128];   // [entry][token]: conflict-free for a warp's 32 tokens
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_s;
 
@@ -117,7 +175,7 @@ __global__ void __launch_bounds__(kSelTcThreads, 2) topk_fwd_tc_kernel(TopkParam
   const int K = p.topk;
   const int cta_limit = sel_row_limit(p, min(l0 + 127, p.L - 1));   // limits do not decrease with the position
   const int ntile = (cta_limit + 127) >> 7;
-  const int nitem = 3 * ntile;
+  const int nitem = 2 * ntile;
 
   if (ntile == 0 || *reinterpret_cast<volatile int*>(&g_sel_status) != 0) {
     // no candidates for any token of the block: empty lists, lse_total = lse of the window branch
@@ -230,9 +288,12 @@ __global__ void __launch_bounds__(kSelTcThreads, 2) topk_fwd_tc_kernel(TopkParam
       lse_w = (p.lse_dtype == HILS_BF16) ? to_f(static_cast<const bf16*>(p.lse_swa)[row])
                                          : static_cast<const float*>(p.lse_swa)[row];
     float m_run = -CUDART_INF_F, s_run = 0.f;               // pass 0: running maximum and sum
-    float top[32];                                          // pass 1: the 32 largest keys so far, descending
+    float top[32];                                          // pass 0: the 32 largest values so far, descending
 #pragma unroll
     for (int j = 0; j < 32; ++j) top[j] = -CUDART_INF_F;
+    float thrv = -CUDART_INF_F;                             // the K-th largest value so far
+    int cnt = 0;                                            // buffered values of this token
+    float* cand = cand_s + r;
     float lt = 0.f, thr = -CUDART_INF_F;
     int take = 0, eq_seen = 0, n_out = 0;
     int32_t* out_ids = p.indices + row * K;
@@ -248,16 +309,14 @@ __global__ void __launch_bounds__(kSelTcThreads, 2) topk_fwd_tc_kernel(TopkParam
       if (!ok) break;
       tc_fence_after();
       if (t == 0 && pass == 1) {
-        // between the passes: lse_total
+        // between the passes: lse_total, the lists of values become lists of keys, the K-th key and the ties to take
+        sel_flush(top, cand, cnt);
         const float lh = (s_run > 0.f) ? m_run + logf(s_run) : -CUDART_INF_F;
         lt = sel_log_add_exp(lse_w, lh);
         if (p.lse_total && l < p.L) p.lse_total[row] = lt;
-      }
-      if (t == 0 && pass == 2) {
-        float kth = top[0];                                // the K-th largest key; -inf with fewer than K candidates (all win)
 #pragma unroll
-        for (int j = 1; j < 32; ++j) kth = (j == K - 1) ? top[j] : kth;
-        thr = kth;
+        for (int j = 0; j < 32; ++j) top[j] = top[j] - lt;   // -inf stays -inf
+        thr = sel_kth(top, K);                               // -inf with fewer than K candidates (all win)
         int gt = 0;
 #pragma unroll
         for (int j = 0; j < 32; ++j) gt += (j < K && top[j] > thr) ? 1 : 0;
@@ -270,37 +329,50 @@ __global__ void __launch_bounds__(kSelTcThreads, 2) topk_fwd_tc_kernel(TopkParam
         tmem_ld32(tmem + lane_base + sb * 128 + cb * 32, sv);
         tmem_ld_wait();
         const int c0 = t * 128 + cb * 32;
-        if (c0 >= lim) {                                   // nothing of this row here (the tile may still serve other rows)
-          if (pass == 1 && rk)
-            for (int j = 0; j < 32; ++j)
-              if (c0 + j < p.N) rk[c0 + j] = -CUDART_INF_F;
-        } else if (pass == 0) {
-          float cmax = -CUDART_INF_F;
+        if (pass == 0) {
+          if (c0 < lim) {
+            float cm[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float v = __fmul_rn(sv[j], p.scale);
-            if (has_bias) v += bias_s[sb][cb * 32 + j];
-            v = (c0 + j < lim) ? v : -CUDART_INF_F;
-            sv[j] = v;
-            cmax = fmaxf(cmax, v);
+            for (int j = 0; j < 32; ++j) {
+              float v = __fmul_rn(sv[j], p.scale);
+              if (has_bias) v += bias_s[sb][cb * 32 + j];
+              v = (c0 + j < lim) ? v : -CUDART_INF_F;
+              sv[j] = v;
+              cm[j & 3] = fmaxf(cm[j & 3], v);
+            }
+            const float m_new = fmaxf(m_run, fmaxf(fmaxf(cm[0], cm[1]), fmaxf(cm[2], cm[3])));
+            const float nb = -m_new * kSelLog2e;
+            float ad[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ad[j & 3] += ex2(fmaf(sv[j], kSelLog2e, nb));
+            s_run = s_run * ex2(fmaf(m_run, kSelLog2e, nb)) + ((ad[0] + ad[1]) + (ad[2] + ad[3]));   // ex2(-inf) = 0 at first
+            m_run = m_new;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sv[j] = -CUDART_INF_F;   // nothing of this row here (the tile serves other rows)
           }
-          const float m_new = fmaxf(m_run, cmax);
-          float add = 0.f;
+          // The first tiles of a row's stream go through the sorting network directly (most values still qualify);
+          // later, values that beat the K-th value so far wait in the buffer.
+          const bool direct = t < kSelDirectTiles;
+          const int cnt0 = cnt;
+          if (!direct) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) add += ex2((sv[j] - m_new) * kSelLog2e);
-          s_run = s_run * ex2((m_run - m_new) * kSelLog2e) + add;   // m_run = -inf at first: ex2(-inf) = 0
-          m_run = m_new;
-        } else if (pass == 1) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float v = __fmul_rn(sv[j], p.scale);
-            if (has_bias) v += bias_s[sb][cb * 32 + j];
-            const float key = (c0 + j < lim) ? v - lt : -CUDART_INF_F;
-            if (rk && c0 + j < p.N) rk[c0 + j] = key;
-            sv[j] = key;
+            for (int j = 0; j < 32; ++j) {
+              const bool q = sv[j] > thrv;
+              if (q && cnt < kSelCap) cand[cnt * 128] = sv[j];
+              cnt += q ? 1 : 0;
+            }
           }
-          sel_sort32_desc(sv);
-          sel_merge_top32(top, sv);
+          if (direct || __any_sync(0xffffffffu, cnt > kSelCap)) {
+            // some token's buffer cannot take this group: merge what was buffered before it, then the group itself
+            if (!direct) {
+              sel_flush(top, cand, cnt0);
+              cnt = 0;
+            }
+            sel_sort32_desc(sv);
+            sel_merge_top32(top, sv);
+            thrv = sel_kth(top, K);
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -308,7 +380,8 @@ __global__ void __launch_bounds__(kSelTcThreads, 2) topk_fwd_tc_kernel(TopkParam
             float v = raw;
             if (has_bias) v += bias_s[sb][cb * 32 + j];
             const bool valid = c0 + j < lim;
-            const float key = v - lt;
+            const float key = valid ? v - lt : -CUDART_INF_F;
+            if (rk && c0 + j < p.N) rk[c0 + j] = key;
             const bool is_eq = valid && key == thr && thr > -CUDART_INF_F;
             const bool sel = valid && key > -CUDART_INF_F && (key > thr || (is_eq && eq_seen < take));
             eq_seen += is_eq ? 1 : 0;
