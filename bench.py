@@ -49,6 +49,8 @@ WORKLOADS = {
     "c2_gqa": dict(B=8, T=8192, h_q=16, h_kv=2, D=64, S=64, K=32, W=512),
     "c3": dict(B=1, T=65536, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
     "c3_small": dict(B=1, T=16384, h_q=8, h_kv=8, D=128, S=64, K=32, W=512),
+    # the 64K-token shape with 4 of its 32 heads: every kernel takes the path it takes at c3, a few hundred MB on the device
+    "c3_4h": dict(B=1, T=65536, h_q=4, h_kv=4, D=128, S=64, K=32, W=512),
     # decode: 32 sequences, one new token each, against a 131072-token KV store
     "c4": dict(B=32, T=131072, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
     "c4_small": dict(B=4, T=16384, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),

@@ -1472,7 +1472,9 @@ static __device__ __align__(256) float g_topk_bwd_scratch[kNoAllocFloats];
 constexpr int kMaxDevices = 64;
 static float* g_scratch_ptr[kMaxDevices] = {nullptr};
 
-// device address of the scratch array on the current device (looked up on the first call per device)
+// device address of the scratch array on the current device (looked up on the first call per device).
+// The cache is written without synchronisation: two host threads that race on a device's first call both look the
+// symbol up and both store the same address (an aligned pointer store), so the race is benign.
 static int noalloc_scratch(float** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);

@@ -134,7 +134,12 @@ size_t hils_topk_bwd_noalloc_max_elems(void);
  *   q (B,L,h_q,D), k (B,T,h_kv,D), v (B,T,h_kv,Dv), weights (B,L,h_q,num_weights) (first K
  *   columns used), indices (B,L,h_kv,K); ids < 0 end a row's list.  slope (h_q) fp32 or NULL.
  * Backward: d_q, d_k, d_v, d_w in `dtype`; d_w has num_weights columns, those >= K are zero.
- * workspace: hils_sparse_attn_bwd_workspace_bytes() bytes of scratch (fp32 accumulators).
+ * workspace: forward - hils_sparse_attn_fwd_workspace_bytes() bytes (0 for few query rows, for fp32 and for dense
+ *   selections T/chunk_size <= 4*K; otherwise the inverse index [per (batch, kv head, chunk) the list of
+ *   (token, slot) entries that selected it, with their weights] and an fp32 output accumulator; a missing or
+ *   small workspace returns HILS_ERR_WORKSPACE); backward - hils_sparse_attn_bwd_workspace_bytes() bytes (the
+ *   same index and fp32 accumulators).  d_k, d_v and d_w are bit-reproducible; o (sparse selections) and d_q
+ *   are fp32 scatter-adds whose order varies, so their last bits differ from run to run.
  * ------------------------------------------------------------------------------------- */
 int hils_sparse_attn_fwd(const void* q, const void* k, const void* v, const void* weights,
                          const int32_t* indices, const float* slope, void* o,
