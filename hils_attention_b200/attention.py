@@ -39,6 +39,10 @@ class HiLSAttentionConfig:
     enable_chunk_pooling: bool = False
     enable_softmax1: bool = False
     num_hidden_layers: int = 1
+    shared_q_c: bool = False          # one learned prior query per head instead of the landmark tokens' queries (:271-276)
+    apply_hils_rope: bool = False     # rotate the shared prior query to each chunk's last position (:382-387, :425-430)
+    head_dim: int = 0                 # needed for the shared prior query only
+    initializer_range: float = 0.02
 
 
 class HiLSAttentionCore(torch.nn.Module):
@@ -56,9 +60,34 @@ class HiLSAttentionCore(torch.nn.Module):
         self.enable_softmax1 = config.enable_softmax1
         self.topk_func = ops.online_softmax_topk_head
         self.hils_func = ops.HiLS_block_M_head
+        self.shared_q_c = config.shared_q_c
+        self.apply_hils_rope = config.apply_hils_rope
+        if self.shared_q_c:
+            assert self.enable_prior_query, "shared_q_c requires enable_prior_query=True"
+            assert config.head_dim > 0, "shared_q_c needs head_dim"
+            self.q_c = torch.nn.Parameter(torch.empty(self.h_q, config.head_dim))
+            torch.nn.init.normal_(self.q_c, mean=0.0, std=config.initializer_range)
+
+    def _prior_queries(self, lmk_q, positions, position_embeddings):
+        """Pooling queries of the chunks whose last tokens sit at `positions` (a slice or a list of indices into
+        this call's tokens): the landmark tokens' own queries, or the shared learned query, rotated to those
+        positions when the model rotates its landmark queries (models/FlashHiLS/hils_attention.py:382-389, :425-432)."""
+        if not self.shared_q_c:
+            return lmk_q[:, positions]
+        n = lmk_q[:, positions].shape[1]
+        q_c = self.q_c.to(lmk_q.dtype)
+        if lmk_q.shape[2] != self.h_q:      # the batch is folded into the head dimension (cached decode / prefill)
+            q_c = q_c.repeat(lmk_q.shape[2] // self.h_q, 1)
+        mu = q_c.unsqueeze(0).unsqueeze(0).expand(lmk_q.shape[0], n, -1, -1)
+        if self.apply_hils_rope:
+            assert position_embeddings is not None, "apply_hils_rope needs position_embeddings=(cos, sin)"
+            cos, sin = position_embeddings
+            mu = ops.single_tensor_rope_autograd(mu.contiguous(), cos[:, positions, :], sin[:, positions, :])
+        return mu
 
     # -- chunk keys: models/FlashHiLS/hils_attention.py:342-464 ---------------------------------
-    def _compute_landmark_keys(self, k_src, lmk_q, L, full_seq_len, use_cache, past_key_values):
+    def _compute_landmark_keys(self, k_src, lmk_q, L, full_seq_len, use_cache, past_key_values,
+                               position_embeddings=None):
         S = self.chunk_size
         B = k_src.shape[0]
         prior_b = None
@@ -81,7 +110,7 @@ class HiLSAttentionCore(torch.nn.Module):
             new_chunks = full_chunks - prev_full
             if new_chunks > 0:
                 boundary_local = [S * (prev_full + j) - 1 - prev_len for j in range(1, new_chunks + 1)]
-                new_mu = lmk_q[:, boundary_local]
+                new_mu = self._prior_queries(lmk_q, boundary_local, position_embeddings)
                 new_k = chunked(prev_full, full_chunks)
                 new_lmk_k, new_b = ops.chunk_attn_pool(new_mu, new_k)
                 if self.enable_chunk_pooling:
@@ -98,7 +127,7 @@ class HiLSAttentionCore(torch.nn.Module):
                 lmk_k, prior_b = k_src[:, S - 1::S], None
             return lmk_k, prior_b
 
-        mu_q = lmk_q[:, S - 1::S][:, :full_chunks]
+        mu_q = self._prior_queries(lmk_q, slice(S - 1, full_chunks * S, S), position_embeddings)
         if mu_q.shape[1] == 0:
             if self.enable_chunk_pooling and full_chunks > 0:
                 return ops.chunk_mean_pool(chunked(0, full_chunks)), None
@@ -138,9 +167,10 @@ class HiLSAttentionCore(torch.nn.Module):
         return o.view(B, 1, h_q, D)
 
     def forward(self, q, k, v, lmk_q, past_key_values=None, use_cache: bool = False,
-                return_aux: bool = False):
+                return_aux: bool = False, position_embeddings=None):
         """q, lmk_q (B,L,h_q,D); k, v (B,L,h_kv,D) of the NEW tokens.  Returns (B,L,h_q,Dv), the
-        tensor the reference flattens and feeds to o_proj."""
+        tensor the reference flattens and feeds to o_proj.  position_embeddings = (cos, sin) of this call's
+        tokens, (B or 1, L, D): only read when the shared prior query is rotated."""
         B, L = q.shape[0], q.shape[1]
         S, W = self.chunk_size, self.hils_sliding_window
         caching = use_cache and past_key_values is not None
@@ -167,7 +197,8 @@ class HiLSAttentionCore(torch.nn.Module):
         full_seq_len = k.shape[1]
         aux = {"swa_o": swa_o, "lse_swa": lse_sum}
         if full_seq_len >= S:
-            lmk_k, prior_b = self._compute_landmark_keys(k, lmk_q, L, full_seq_len, use_cache, past_key_values)
+            lmk_k, prior_b = self._compute_landmark_keys(k, lmk_q, L, full_seq_len, use_cache, past_key_values,
+                                                         position_embeddings)
             q_offset = full_seq_len - L if caching else 0
             indices, scores = self.topk_func(
                 lmk_q, lmk_k, lse_sum, self.topk, block_size=S, window_size=W, is_training=self.training,

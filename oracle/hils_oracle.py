@@ -338,8 +338,12 @@ def swa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window_size: int, chu
 def hils_attention_chain(q, k, v, lmk_q, *, chunk_size: int, window_size: int, topk: int,
                          pooling: str = "attn", use_prior_bias: bool = True, softmax1: bool = False,
                          q_offset: Optional[int] = None, act_dtype: Optional[torch.dtype] = None,
-                         return_aux: bool = False, forced_indices: Optional[torch.Tensor] = None):
+                         return_aux: bool = False, forced_indices: Optional[torch.Tensor] = None,
+                         mu_q: Optional[torch.Tensor] = None):
     """SWA -> chunk keys -> selection -> inter-chunk softmax -> sparse attention -> combine.
+
+    mu_q (B,N,h_q,D): pooling queries that replace the landmark tokens' own queries (the module's shared prior
+    query, models/FlashHiLS/hils_attention.py:425-432).
 
     q, lmk_q (B,L,h_q,D); k, v (B,T,h_kv,D) with T >= L (T > L = cached prefix).
     pooling: "attn" (k', b' from chunk_attn_pool with mu = lmk_q at each chunk's last token;
@@ -363,7 +367,7 @@ def hils_attention_chain(q, k, v, lmk_q, *, chunk_size: int, window_size: int, t
     prior_b = None
     if pooling == "attn" or use_prior_bias:
         assert T == L, "attention pooling in the oracle chain needs the full sequence"
-        mu = lmk_q[:, S - 1::S][:, :N]
+        mu = lmk_q[:, S - 1::S][:, :N] if mu_q is None else mu_q
         kq = k_chunked.repeat_interleave(mu.shape[2] // h_kv, dim=3)
         lmk_k, prior_b = chunk_attn_pool(mu, kq)
         if not use_prior_bias:

@@ -22,6 +22,9 @@ def _inputs(B, T, hq, hk, D, S, seed, dtype, scale=1.0):
     return [t.to(dtype) for t in (q, k, v)]
 
 
+from hils_attention_b200.attention import HiLSAttentionConfig, HiLSAttentionCore  # noqa: E402
+
+
 def _core(hq, hk, K, S, W, **kw):
     from hils_attention_b200.attention import HiLSAttentionConfig, HiLSAttentionCore
     return HiLSAttentionCore(HiLSAttentionConfig(hq, hk, K, S, W, **kw))
@@ -201,3 +204,35 @@ def test_host_pipeline_matches_direct_steps():
         for got, want in zip(o, ref):   # fp32 atomics in the key-gradient accumulation: last-bit differences only
             w = want.float().cpu()
             assert (got.float() - w).abs().max() <= 2e-2 * w.abs().max()
+
+
+@pytest.mark.parametrize("rope", [False, True])
+def test_shared_prior_query_replaces_the_landmark_queries(rope):
+    """shared_q_c (models/FlashHiLS/hils_attention.py:271-276, :425-432): the chunk pooling is queried by one
+    learned vector per head, rotated to each chunk's last position when the model rotates its landmark queries.
+    The chain must equal the oracle chain fed the chunk keys pooled with that query, and the learned query must
+    receive a gradient."""
+    from hils_attention_b200 import ops
+    torch.manual_seed(3)
+    B, T, hq, hk, D, S, W, K = 1, 1024, 4, 2, 64, 64, 128, 4
+    g = torch.Generator().manual_seed(21)
+    q, k, v = (torch.randn(B, T, h, D, generator=g) for h in (hq, hk, hk))
+    cfg = HiLSAttentionConfig(hq, hk, K, S, W, shared_q_c=True, apply_hils_rope=rope, head_dim=D, initializer_range=1.0)
+    core = HiLSAttentionCore(cfg).cuda().train()
+    pos = torch.arange(T, dtype=torch.float32)
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = torch.cat([pos[:, None] * inv[None, :]] * 2, -1)
+    cos, sin = ang.cos()[None].cuda(), ang.sin()[None].cuda()
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o, aux = core(qd, kd, vd, qd, return_aux=True, position_embeddings=(cos, sin) if rope else None)
+    o.sum().backward()
+    assert core.q_c.grad is not None and torch.isfinite(core.q_c.grad).all() and core.q_c.grad.abs().sum() > 0
+    # the oracle chain with the same pooling queries (rotation restated in plain torch)
+    mu = core.q_c.detach().float().cpu()[None, None].expand(B, T // S, -1, -1)
+    if rope:
+        c, sn = cos.cpu()[:, S - 1::S, None, :], sin.cpu()[:, S - 1::S, None, :]
+        half = torch.cat([-mu[..., D // 2:], mu[..., :D // 2]], -1)
+        mu = mu * c + half * sn
+    ref = orc.hils_attention_chain(q, k, v, q, chunk_size=S, window_size=W, topk=K, mu_q=mu,
+                                   forced_indices=aux["indices"].cpu())
+    check(o, ref, F32, "chain output with the shared prior query")

@@ -123,7 +123,9 @@ def test_topk_golden(ops, tag, dtype):
 
 
 @pytest.mark.parametrize("cfg", [(2, 1000, 2, 8, 64, 16, 64, 64), (1, 1024, 4, 1, 128, 32, 64, 512),
-                                 (1, 700, 1, 2, 64, 64, 32, 96)])
+                                 (1, 700, 1, 2, 64, 64, 32, 96),
+                                 # the reference's own robustness shapes (ops/topk_head_softmax.py:1807-1811)
+                                 (2, 4096, 2, 8, 64, 16, 64, 64), (2, 4096, 8, 8, 64, 16, 64, 64)])
 def test_topk_selector_exact_and_match_rate(ops, cfg):
     """Larger seeded cases: ids bit-exact against the stable selector fed the kernel's own fp32
     ranking values; ranking values within tolerance of the oracle; >= 99% of the ids equal to the
@@ -254,6 +256,30 @@ def test_sparse_golden(ops, tag, dtype):
     for n, t in (("dq", q), ("dk", k), ("dv", v), ("dw", w)):
         check(t.grad, ref[n], dtype, n)
         assert rms_ratio(t.grad, ref[n]) < (5e-3 if dtype == F32 else 2e-2), n
+
+
+def test_sparse_head_dim_192_long_kv(ops):
+    """The reference's own correctness shape (ops/hils_fwd_bwd_head.py:980-994): head dim 192, eight query heads on
+    one kv head, 512 query tokens against 612 keys, four chunks per token.  Outside the tensor-core tiles, so the
+    generic kernels run; forward and all gradients against the oracle."""
+    g = torch.Generator().manual_seed(42)
+    B, L, T, H, HQ, D, K, S = 1, 512, 612, 1, 8, 192, 4, 64
+    N = T // S
+    q0 = torch.randn(B, L, HQ, D, generator=g).to(BF)
+    k0 = torch.randn(B, T, H, D, generator=g).to(BF)
+    v0 = torch.randn(B, T, H, D, generator=g).to(BF)
+    w0 = torch.softmax(torch.randn(B, L, HQ, K, generator=g), -1).to(BF)
+    do = torch.randn(B, L, HQ, D, generator=g).to(BF)
+    idx = torch.stack([torch.randperm(N, generator=g)[:K].sort().values for _ in range(B * L * H)]).view(B, L, H, K).int()
+    q, k, v, w = [t.cuda().requires_grad_(True) for t in (q0, k0, v0, w0)]
+    o = ops.HiLS_block_M_head(q, k, v, w, idx.cuda(), block_size=S, mask_last_token=True)
+    o.backward(do.cuda())
+    qr, kr, vr, wr = [t.float().requires_grad_(True) for t in (q0, k0, v0, w0)]
+    ref = orc.sparse_attn(qr, kr, vr, wr, idx, chunk_size=S, mask_last_token=True)
+    ref.backward(do.float())
+    check(o, ref, BF, "o (D=192)")
+    for n, a, b in (("dq", q, qr), ("dk", k, kr), ("dv", v, vr), ("dw", w, wr)):
+        check(a.grad, b.grad, BF, n + " (D=192)")
 
 
 def test_sparse_unsorted_ids_slope_and_eval_mode(ops):
