@@ -475,6 +475,13 @@ def kernel_rooflines(name, core, q, k, v, do, w, hq, hk, with_overlap):
         t_lz = time_op(lambda: hb.exact_chunk_log_z_tl(q, k, chunk_size=S, window_size=W))
         e = add("exact_chunk_log_z_fwd", t_lz, flops=f_lz)
         e["output_gbs"] = float(B * T * hq) * N * 4 / (t_lz / 1e3) / 1e9
+        # backward: S recomputed in both passes, dQ = dS K, dK = dS^T Q (the upstream gradient is zero where log Z is -inf)
+        qz, kz = q.detach().requires_grad_(True), k.detach().requires_grad_(True)
+        lz = hb.exact_chunk_log_z_tl(qz, kz, chunk_size=S, window_size=W)
+        gz = torch.randn_like(lz).masked_fill_(~torch.isfinite(lz), 0.0)
+        t_lzb = time_op(lambda: torch.autograd.grad(lz, (qz, kz), gz, retain_graph=True))
+        add("exact_chunk_log_z_bwd", t_lzb, flops=2.0 * f_lz)
+        del lz, gz, qz, kz
     require_clean_status(f"the per-kernel timings of {name}")
 
     t_sp, f_sp = t_f + t_b, f_f + f_b

@@ -12,6 +12,9 @@ namespace hils {
 int logz_fwd_tc_launch(const void* q, const void* k, float* log_z, int B, int L, int h_q, int h_kv, int D, int chunk_size,
                        int window_size, float sm_scale, int mask_lmk, cudaStream_t st);   // logz_tc.cu
 
+int logz_bwd_tc_launch(const void* q, const void* k, const float* log_z, const float* d_log_z, void* d_q, void* d_k, int B, int L,
+                       int h_q, int h_kv, int D, int chunk_size, int window_size, float sm_scale, cudaStream_t st);   // logz_tc.cu
+
 struct LogzParams {
   const void* q; const void* k; float* log_z; const float* d_log_z; void* d_q; void* d_k;
   int B, L, h_q, h_kv, D, S, W, mask_lmk, n_chunk;
@@ -224,6 +227,10 @@ extern "C" int hils_chunk_logz_bwd(const void* q, const void* k, const float* lo
   const size_t smem = 4 * (size_t)(D + 32) * sizeof(float);
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t rows_q = (int64_t)B * L * h_q, rows_k = (int64_t)B * L * h_kv;
+  if (dtype == HILS_BF16) {   // chunk size 64 on the tensor cores
+    const int rc = logz_bwd_tc_launch(q, k, log_z, d_log_z, d_q, d_k, B, L, h_q, h_kv, D, chunk_size, window_size, sm_scale, st);
+    if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  }
   if (dtype == HILS_BF16) {
     logz_bwd_dq_kernel<bf16><<<(unsigned)((rows_q + 3) / 4), 128, smem, st>>>(p, rows_q);
     logz_bwd_dk_kernel<bf16><<<(unsigned)((rows_k + 3) / 4), 128, smem, st>>>(p, rows_k);

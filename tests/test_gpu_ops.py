@@ -353,6 +353,22 @@ def test_logz_tensor_core_forward_matches_oracle(ops, B, L, hq, hkv, D, W, ml):
     assert lz.shape == ref.shape
     assert torch.equal(torch.isfinite(lz).cpu(), torch.isfinite(ref))
     check(lz, ref, BF, "log_z (tensor cores)")
+    if ml:       # like the reference, the backward exists without the landmark mask only
+        return
+    # backward: two tensor-core passes (dQ query-major, dK key-major)
+    qg, kg = q.cuda().requires_grad_(True), k.cuda().requires_grad_(True)
+    qr, kr = q.float().requires_grad_(True), k.float().requires_grad_(True)
+    lz2 = ops.exact_chunk_log_z_tl(qg, kg, chunk_size=64, window_size=W)
+    ref2 = orc.exact_chunk_log_z(qr, kr, chunk_size=64, window_size=W)
+    fin = torch.isfinite(ref2)
+    gz = torch.randn(ref2.shape, generator=g)
+    (lz2.masked_fill(~fin.cuda(), 0.0) * gz.cuda()).sum().backward()
+    if fin.any():
+        (ref2.masked_fill(~fin, 0.0) * gz).sum().backward()
+        check(qg.grad, qr.grad, BF, "dq (tensor cores)")
+        check(kg.grad, kr.grad, BF, "dk (tensor cores)")
+    else:
+        assert qg.grad.abs().sum() == 0 and kg.grad.abs().sum() == 0
 
 
 # ------------------------------------------------------------------ sliding-window branch
