@@ -37,6 +37,8 @@ SIGNATURES = {
     "hils_sparse_attn_fwd_workspace_bytes": (_SZ, [_I] * 10),
     "hils_sparse_attn_bwd": (_I, [_P] * 11 + [_I] * 10 + [_F, _I, _I, _P, _SZ, _P]),
     "hils_sparse_attn_bwd_workspace_bytes": (_SZ, [_I] * 10),
+    "hils_sparse_attn_index_bytes": (_SZ, [_I] * 10),
+    "hils_sparse_attn_bwd_with_index": (_I, [_P] * 11 + [_I] * 10 + [_F, _I, _I, _P, _SZ, _P, _SZ, _P]),
     "hils_chunk_logz_fwd": (_I, [_P] * 3 + [_I] * 7 + [_F, _I, _I, _P]),
     "hils_chunk_logz_bwd": (_I, [_P] * 6 + [_I] * 7 + [_F, _I, _P]),
     "hils_swa_fwd": (_I, [_P] * 5 + [_I] * 11 + [_F, _I, _I, _P]),
@@ -55,7 +57,7 @@ SIGNATURES = {
 # kernels each entry point launches (memsets excluded); used to report launch counts
 KERNELS_PER_CALL = {
     "hils_pool_fwd": 1, "hils_pool_bwd": 1, "hils_meanpool_fwd": 1, "hils_meanpool_bwd": 1,
-    "hils_topk_fwd": 1, "hils_topk_bwd": 2, "hils_topk_bwd_noalloc": 2, "hils_sparse_attn_fwd": 6, "hils_sparse_attn_bwd": 6,
+    "hils_topk_fwd": 1, "hils_topk_bwd": 2, "hils_topk_bwd_noalloc": 2, "hils_sparse_attn_fwd": 6, "hils_sparse_attn_bwd": 6, "hils_sparse_attn_bwd_with_index": 6,
     "hils_chunk_logz_fwd": 1, "hils_chunk_logz_bwd": 2, "hils_swa_fwd": 1, "hils_swa_bwd": 2,
     "hils_chunk_weights_fwd": 1, "hils_chunk_weights_bwd": 1, "hils_combine_fwd": 1, "hils_combine_bwd": 1,
     "hils_norm_rope_fwd": 1, "hils_norm_rope_bwd": 1,

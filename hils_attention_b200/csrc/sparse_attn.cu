@@ -10,7 +10,8 @@ int sparse_decode_launch(const void* q, const void* k, const void* v, const void
                          void* o, int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights, int S,
                          float scale, int mask_last, int dtype, cudaStream_t st);  // decode_attn.cu
 size_t sparse_bwd_cm_workspace(const SparseParams& p);             // sparse_attn_cm.cu
-int sparse_bwd_cm_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st);
+int sparse_bwd_cm_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st, const void* built_index);
+size_t sparse_cm_index_bytes(const SparseParams& p);
 
 static int check_sparse(int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights,
                         int chunk_size, int dtype) {
@@ -117,12 +118,61 @@ extern "C" int hils_sparse_attn_fwd(const void* q, const void* k, const void* v,
   return HILS_OK;
 }
 
+// True when hils_sparse_attn_fwd of this shape builds the chunk-major index (same tests as its dispatch)
+static bool fwd_builds_index(const SparseParams& p, int L, int T, int K, int chunk_size, int dtype) {
+  if (dtype != HILS_BF16 || L <= 4) return false;
+  if ((int64_t)(T / chunk_size) <= 4 * (int64_t)K) return false;   // dense selections: query-block-major forward
+  return sparse_fwd_cm_workspace(p) > 0;
+}
+
+extern "C" size_t hils_sparse_attn_index_bytes(int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int chunk_size,
+                                               int dtype) {
+  if (B <= 0 || L <= 0 || T <= 0 || h_kv <= 0 || h_q <= 0 || h_q % h_kv != 0 || chunk_size <= 0) return 0;
+  SparseParams p = make_params(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, B, L, T, h_q, h_kv, D, Dv, K, K, chunk_size,
+                               1.f, 1);
+  return fwd_builds_index(p, L, T, K, chunk_size, dtype) ? sparse_cm_index_bytes(p) : 0;
+}
+
+static int sparse_attn_bwd_impl(const void* q, const void* k, const void* v, const void* weights,
+                                const int32_t* indices, const float* slope, const void* d_o, void* d_q,
+                                void* d_k, void* d_v, void* d_w, int B, int L, int T, int h_q, int h_kv,
+                                int D, int Dv, int K, int num_weights, int chunk_size, float sm_scale,
+                                int mask_last_token, int dtype, void* workspace, size_t workspace_bytes,
+                                void* stream, const void* built_index);
+
 extern "C" int hils_sparse_attn_bwd(const void* q, const void* k, const void* v, const void* weights,
                                     const int32_t* indices, const float* slope, const void* d_o, void* d_q,
                                     void* d_k, void* d_v, void* d_w, int B, int L, int T, int h_q, int h_kv,
                                     int D, int Dv, int K, int num_weights, int chunk_size, float sm_scale,
                                     int mask_last_token, int dtype, void* workspace, size_t workspace_bytes,
                                     void* stream) {
+  return sparse_attn_bwd_impl(q, k, v, weights, indices, slope, d_o, d_q, d_k, d_v, d_w, B, L, T, h_q, h_kv, D, Dv, K,
+                              num_weights, chunk_size, sm_scale, mask_last_token, dtype, workspace, workspace_bytes, stream,
+                              nullptr);
+}
+
+extern "C" int hils_sparse_attn_bwd_with_index(const void* q, const void* k, const void* v, const void* weights,
+                                               const int32_t* indices, const float* slope, const void* d_o, void* d_q,
+                                               void* d_k, void* d_v, void* d_w, int B, int L, int T, int h_q, int h_kv,
+                                               int D, int Dv, int K, int num_weights, int chunk_size, float sm_scale,
+                                               int mask_last_token, int dtype, void* workspace, size_t workspace_bytes,
+                                               const void* built_index, size_t built_index_bytes, void* stream) {
+  const size_t want = hils_sparse_attn_index_bytes(B, L, T, h_q, h_kv, D, Dv, K, chunk_size, dtype);
+  if (built_index && (want == 0 || built_index_bytes < want)) {
+    set_error("sparse_attn_bwd_with_index: an index of %zu bytes belongs to this shape, %zu given", want, built_index_bytes);
+    return HILS_ERR_BAD_ARG;
+  }
+  return sparse_attn_bwd_impl(q, k, v, weights, indices, slope, d_o, d_q, d_k, d_v, d_w, B, L, T, h_q, h_kv, D, Dv, K,
+                              num_weights, chunk_size, sm_scale, mask_last_token, dtype, workspace, workspace_bytes, stream,
+                              built_index);
+}
+
+static int sparse_attn_bwd_impl(const void* q, const void* k, const void* v, const void* weights,
+                                const int32_t* indices, const float* slope, const void* d_o, void* d_q,
+                                void* d_k, void* d_v, void* d_w, int B, int L, int T, int h_q, int h_kv,
+                                int D, int Dv, int K, int num_weights, int chunk_size, float sm_scale,
+                                int mask_last_token, int dtype, void* workspace, size_t workspace_bytes,
+                                void* stream, const void* built_index) {
   if (int rc = check_sparse(B, L, T, h_q, h_kv, D, Dv, K, num_weights, chunk_size, dtype)) return rc;
   const size_t need = hils_sparse_attn_bwd_workspace_bytes(B, L, T, h_q, h_kv, D, Dv, K, chunk_size, dtype);
   if (need > 0 && (!workspace || workspace_bytes < need)) {
@@ -136,7 +186,7 @@ extern "C" int hils_sparse_attn_bwd(const void* q, const void* k, const void* v,
     if (sparse_bwd_cm_workspace(p) > 0) {
       HILS_REQUIRE(q && k && v && weights && indices && d_o && d_q && d_k && d_v && d_w, "sparse_attn_bwd: null pointer");
       p.d_o = d_o; p.d_q = d_q; p.d_w = d_w;
-      const int rc = sparse_bwd_cm_launch(p, d_k, d_v, workspace, st);
+      const int rc = sparse_bwd_cm_launch(p, d_k, d_v, workspace, st, built_index);
       if (rc != HILS_ERR_UNSUPPORTED) return rc;
       // the tensor-core path covers this shape but the pointers are not 16-byte aligned: no other kernel is
       // sized for the tensor-core workspace, so the call is refused rather than rerouted

@@ -299,6 +299,17 @@ __global__ void __launch_bounds__(256) inv_offsets_kernel(const uint32_t* __rest
   if (tid == 0) coff[bh * (nchunk + 1) + nchunk] = carry_s;
 }
 
+// the index as a finished forward call left it at the start of its workspace (`built` holds inv_layout().total bytes)
+static void adopt_inverse_index(const SparseParams& p, const void* built, InvIndex* ix) {
+  const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.h_q / p.h_kv, p.K, p.T / 64);
+  const uint8_t* ws = static_cast<const uint8_t*>(built);
+  ix->list = reinterpret_cast<const int32_t*>(ws + l.list_off);
+  ix->wlist = reinterpret_cast<const bf16*>(ws + l.wlist_off);
+  ix->coff = reinterpret_cast<const uint32_t*>(ws + l.coff_off);
+  ix->tot = reinterpret_cast<const uint32_t*>(ws + l.tot_off);
+  ix->cap = l.cap;
+}
+
 static int build_inverse_index(const SparseParams& p, void* workspace, InvIndex* ix, cudaStream_t st) {
   const int nchunk = p.T / 64, G = p.h_q / p.h_kv;
   const InvLayout l = inv_layout(p.B, p.L, p.h_kv, G, p.K, nchunk);
@@ -604,6 +615,12 @@ static bool cm_shape_ok(const SparseParams& p) {
 static size_t cm_fwd_smem(int D) {
   const int NQ = (D == 64) ? 4 : 2;
   return 1024 + 2 * (size_t)(D / 64) * 8192 + (size_t)NQ * (D / 64) * 16384 + 2 * 16384 + 8 * (size_t)StgGeom<64>::kWarpBytes;
+}
+
+// bytes of the inverse index at the start of the chunk-major workspaces (0: shape outside this path)
+size_t sparse_cm_index_bytes(const SparseParams& p) {
+  if (!cm_shape_ok(p)) return 0;
+  return inv_layout(p.B, p.L, p.h_kv, p.h_q / p.h_kv, p.K, p.T / 64).total;
 }
 
 // workspace of the chunk-major forward: inverse index + fp32 output accumulator (0: shape outside this path)
@@ -1013,7 +1030,8 @@ size_t sparse_bwd_cm_workspace(const SparseParams& p) {
   return l.total + (size_t)p.B * p.L * p.h_q * p.D * sizeof(float);
 }
 
-int sparse_bwd_cm_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st) {
+// built_index: the index a forward call over the same ids and weights left in its workspace, or null to build it here
+int sparse_bwd_cm_launch(const SparseParams& p, void* d_k, void* d_v, void* workspace, cudaStream_t st, const void* built_index) {
   if (!cm_shape_ok(p) || !workspace) return HILS_ERR_UNSUPPORTED;
   if (((uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.d_o | (uintptr_t)p.d_q | (uintptr_t)d_k | (uintptr_t)d_v |
        (uintptr_t)workspace) & 15)
@@ -1021,7 +1039,12 @@ int sparse_bwd_cm_launch(const SparseParams& p, void* d_k, void* d_v, void* work
   const int D = p.D, nchunk = p.T / 64;
   const InvLayout l = inv_layout(p.B, p.L, p.h_kv, p.h_q / p.h_kv, p.K, nchunk);
   InvIndex ix;
-  if (int rc = build_inverse_index(p, workspace, &ix, st)) return rc;
+  if (built_index) {
+    if ((uintptr_t)built_index & 15) return HILS_ERR_UNSUPPORTED;
+    adopt_inverse_index(p, built_index, &ix);
+  } else if (int rc = build_inverse_index(p, workspace, &ix, st)) {
+    return rc;
+  }
   float* dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + l.total);
   const size_t n_q = (size_t)p.B * p.L * p.h_q * D;
   cudaError_t e = cudaMemsetAsync(dq_acc, 0, n_q * sizeof(float), st);

@@ -317,8 +317,12 @@ class _SparseChunkAttention(torch.autograd.Function):
             call("hils_combine_fwd", ptr(o), ptr(swa_o), ptr(w), ptr(o), B, L, HQ, Dv, nw, swa_col, dt, stream())
         ctx.is_training = bool(is_training)
         if is_training:
+            # a sparse selection's forward leaves the chunk-major index of the id lists at the start of its workspace:
+            # the backward reuses a copy of it (4 + 2 G bytes per selected slot) instead of building it again
+            ix_bytes = query("hils_sparse_attn_index_bytes", *dims, int(block_size), dt) if ws_bytes > 0 else 0
+            built = ws[:ix_bytes].clone() if 0 < ix_bytes <= ws_bytes else q.new_empty(0)
             ctx.save_for_backward(q, k, v, w, idx, slope_dev if slope_dev is not None else q.new_empty(0),
-                                  swa_o if swa_o is not None else q.new_empty(0))
+                                  swa_o if swa_o is not None else q.new_empty(0), built)
             ctx.meta = (dims, nw, int(block_size), float(sm_scale), int(bool(mask_last_token)), dt,
                         slope_dev is not None, weights.dtype, swa_col)
         return o
@@ -329,7 +333,7 @@ class _SparseChunkAttention(torch.autograd.Function):
             raise RuntimeError(
                 "HiLS_block_M_head: the forward ran with is_training=False, which keeps nothing for "
                 "the backward pass; call it with is_training=True to differentiate.")
-        q, k, v, w, idx, slope_dev, swa_o = ctx.saved_tensors
+        q, k, v, w, idx, slope_dev, swa_o, built = ctx.saved_tensors
         dims, nw, S, scale, mask_last, dt, has_slope, w_dtype, swa_col = ctx.meta
         B, L, T, HQ, H, D, Dv, K = dims
         do = do.contiguous().to(q.dtype)
@@ -339,9 +343,9 @@ class _SparseChunkAttention(torch.autograd.Function):
         d_w = torch.empty((B, L, HQ, nw), dtype=q.dtype, device=q.device)
         ws_bytes = query("hils_sparse_attn_bwd_workspace_bytes", *dims, S, dt)
         ws = _workspace(ws_bytes, q.device)
-        call("hils_sparse_attn_bwd", ptr(q), ptr(k), ptr(v), ptr(w), ptr(idx), ptr(slope_dev) if has_slope else None,
-             ptr(do), ptr(d_q), ptr(d_k), ptr(d_v), ptr(d_w), *dims, nw, S, scale, mask_last, dt, ptr(ws),
-             ws_bytes, stream())
+        call("hils_sparse_attn_bwd_with_index", ptr(q), ptr(k), ptr(v), ptr(w), ptr(idx),
+             ptr(slope_dev) if has_slope else None, ptr(do), ptr(d_q), ptr(d_k), ptr(d_v), ptr(d_w), *dims, nw, S, scale,
+             mask_last, dt, ptr(ws), ws_bytes, ptr(built) if built.numel() else None, built.numel(), stream())
         d_swa_o = None
         if swa_col >= 0:
             d_swa_o = torch.empty_like(swa_o)

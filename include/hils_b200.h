@@ -157,6 +157,22 @@ int hils_sparse_attn_bwd(const void* q, const void* k, const void* v, const void
 size_t hils_sparse_attn_bwd_workspace_bytes(int B, int L, int T, int h_q, int h_kv, int D, int Dv,
                                             int K, int chunk_size, int dtype);
 
+/* The forward of a sparse selection (hils_sparse_attn_fwd_workspace_bytes > 0) leaves the chunk-major index of the id
+ * lists in the first hils_sparse_attn_index_bytes() bytes of its workspace (0: this shape builds none).  A backward
+ * over the same q shape, indices and weights can reuse it instead of building it again: keep those bytes (in place or
+ * copied, 16-byte aligned) and pass them as `built_index`; NULL makes the call identical to hils_sparse_attn_bwd.
+ * `workspace` is still the backward's own, of hils_sparse_attn_bwd_workspace_bytes().  No counterpart in the
+ * reference, whose kernels re-walk the id lists in both passes (ops/hils_fwd_bwd_head.py:337-390, :560-640). */
+size_t hils_sparse_attn_index_bytes(int B, int L, int T, int h_q, int h_kv, int D, int Dv,
+                                    int K, int chunk_size, int dtype);
+int hils_sparse_attn_bwd_with_index(const void* q, const void* k, const void* v, const void* weights,
+                                    const int32_t* indices, const float* slope, const void* d_o,
+                                    void* d_q, void* d_k, void* d_v, void* d_w,
+                                    int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K,
+                                    int num_weights, int chunk_size, float sm_scale, int mask_last_token,
+                                    int dtype, void* workspace, size_t workspace_bytes,
+                                    const void* built_index, size_t built_index_bytes, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Exact per-chunk log Z.  Replaces _ExactChunkLogZ.forward/backward
  * (ops/exact_chunk_log_z_tilelang.py:394-478; kernels :25-137, :148-262, :273-391).
