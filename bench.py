@@ -102,32 +102,45 @@ def make_inputs(w, seed, dtype, heads=None, pin=True):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    """Samples nvidia-smi clocks / throttle reasons of one GPU every 50 ms.  The sampler is started BEFORE the warm-up
+    steps (nvidia-smi needs a few hundred ms to deliver its first line) and the summary keeps the samples that arrived
+    between `start()` and `stop()`, i.e. inside the timed region; if the region was shorter than a sampling period the
+    nearest samples (within 0.5 s, the GPU still busy with the neighbouring steps) are used and the summary says so."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
+        self.t0 = self.t1 = None
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thr = threading.Thread(target=self._read, daemon=True)
             self.thr.start()
         except Exception:
             self.proc = None
+        self.t0 = time.monotonic()          # until start() is called the whole `with` body counts
         return self
+
+    def start(self):
+        self.t0 = time.monotonic()
+
+    def stop(self):
+        self.t1 = time.monotonic()
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.monotonic(), [x.strip() for x in line.split(",")]))
 
     def __exit__(self, *a):
+        if self.t1 is None:
+            self.t1 = time.monotonic()
         if self.proc is not None:
-            time.sleep(0.15)
+            time.sleep(0.12)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -135,9 +148,14 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        inside = [r for t, r in self.rows if self.t0 <= t <= self.t1]
+        window = "timed_region"
+        if not inside:
+            inside = [r for t, r in self.rows if self.t0 - 0.5 <= t <= self.t1 + 0.5]
+            window = "nearest_within_0.5s"
+        sm, mx, reasons = [], [], set()
+        for r in inside:
             try:
                 sm.append(float(r[0])); mx.append(float(r[1]))
                 for n, val in zip(names, r[3:7]):
@@ -146,7 +164,7 @@ class ClockSampler:
             except Exception:
                 pass
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 # -------------------------------------------------------------------------------------------------
@@ -331,18 +349,19 @@ def run_train(args, name, ds, steps, warmup, with_e2e=True, with_kernels=True, w
         o.backward(doi)
         return o, qi.grad, ki.grad, vi.grad
 
-    for _ in range(warmup):
-        step(q, k, v, do)
-    ds.barrier()
-    c0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(ds.local) as clk:
+        for _ in range(warmup):
+            step(q, k, v, do)
         ds.barrier()
+        c0 = _lib.launch_count()
+        clk.start()
         e0.record()
         for _ in range(steps):
             step(q, k, v, do)
         e1.record()
         ds.barrier()
+        clk.stop()
     launches = _lib.launch_count() - c0
     require_clean_status(f"the timed steps of {name}")
     (ms,) = ds.max(e0.elapsed_time(e1))
@@ -555,18 +574,19 @@ def run_decode(args, name, ds, steps, warmup):
         with torch.no_grad():
             return core(q1, k1, v1, q1, past_key_values=cache, use_cache=True)
 
-    for _ in range(warmup):
-        step(qn, kn, vn)
-    ds.barrier()
-    c0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(ds.local) as clk:
+        for _ in range(warmup):
+            step(qn, kn, vn)
         ds.barrier()
+        c0 = _lib.launch_count()
+        clk.start()
         e0.record()
         for _ in range(steps):
             step(qn, kn, vn)
         e1.record()
         ds.barrier()
+        clk.stop()
     launches = _lib.launch_count() - c0
     ms = e0.elapsed_time(e1)
     # end to end: the new token's q, k, v come from pinned host memory, the output row goes back
@@ -652,18 +672,19 @@ def run_context_parallel(args, name, ds, steps, warmup):
             return context_parallel_forward(q, k, v, q, h_kv=hk, topk=K, chunk_size=S, window_size=W,
                                             partition="zigzag", return_aux=aux, timings=timings)
 
-    for _ in range(warmup):
-        step()
-    ds.barrier()
-    c0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(ds.local) as clk:
+        for _ in range(warmup):
+            step()
         ds.barrier()
+        c0 = _lib.launch_count()
+        clk.start()
         e0.record()
         for _ in range(steps):
             step()
         e1.record()
         ds.barrier()
+        clk.stop()
     launches = _lib.launch_count() - c0
     require_clean_status(f"the timed steps of {name}")
     (ms,) = ds.max(e0.elapsed_time(e1))
