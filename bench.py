@@ -709,6 +709,7 @@ def run_context_parallel(args, name, ds, steps, warmup):
                            "halo_bytes_received_per_gpu": halo_b,
                            "fetch_gbs": fetch_b / (t_f / 1e3) / 1e9 if t_f else None,
                            "remote_tiles_of_all": aux["remote_tiles"] / float(B * hk * (T // S) * (world - 1) / world),
+                           "fetch_mode": aux["fetch_mode"], "wanted_fraction_of_group": aux["wanted_fraction"],
                            "collectives": "all_gather (pooled keys), all_to_all (request bitmaps, K/V tiles), "
                                           "send/recv (halo)",
                            "allgather_ms": t_a}

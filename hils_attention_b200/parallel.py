@@ -12,7 +12,10 @@ Per layer the ranks exchange only
   * the K/V tiles of the remote chunks a rank selected, per kv head: a fixed-width bitmap of wanted chunks goes
     to each owner (all-to-all), the tile counts come back to the host in ONE small copy (the only host
     synchronisation of the exchange), the tiles travel in one uneven all-to-all per tensor into a local staging
-    buffer; chunk ids are rewritten to staging slots and the sparse attention then runs on local memory only.
+    buffer; chunk ids are rewritten to staging slots and the sparse attention then runs on local memory only.  When
+    the ranks together want more than half of all remote tiles (independent random queries over a long context want
+    nearly all of them) the exchange falls back to one all-gather of K and of V, which moves the same bytes without
+    the gather and scatter copies on either side.
 Everything else runs on local memory with the single-GPU kernels.  The reference has no context-parallel HiLS
 path; its older HSA model all-gathers every landmark and every chunk's K/V
 (models/HSA_Ultralong/hsa_layers.py:893-898).  Collectives go through torch.distributed (NCCL on GPUs, gloo in
@@ -125,9 +128,15 @@ class FetchPlan:
     recv_counts: List[int]
     n_stage: int                  # staging slots taken by remote chunks (the widest (b, h) list)
     remapped: torch.Tensor        # ids rewritten to staging slots (local chunks follow the remote slots)
+    dense: bool = False           # all-gather instead: the staging buffer holds every chunk in rank-major order
+    wanted_fraction: float = 0.0  # share of all remote (head, chunk) tiles the ranks want, over the whole group
 
 
-def plan_fetch(indices: torch.Tensor, n_chunks: int, part: SeqPartition, group=None) -> FetchPlan:
+DENSE_FETCH_FRACTION = 0.5
+
+
+def plan_fetch(indices: torch.Tensor, n_chunks: int, part: SeqPartition, group=None,
+               dense_fraction: float = DENSE_FETCH_FRACTION) -> FetchPlan:
     """indices (B, L, h, K): global chunk ids selected by this rank's tokens (−1 = padding), per kv head.
     Exchanges the per-head sets of wanted chunks with their owners and returns the transfer plan."""
     world, rank = part.world, dist.get_rank(group)
@@ -154,9 +163,16 @@ def plan_fetch(indices: torch.Tensor, n_chunks: int, part: SeqPartition, group=N
     # staging slot of a remote chunk: its rank among the chunks its (b, h) wants, in rank-major order
     slot = (wanted.reshape(B, h, n_chunks).long().cumsum(-1) - 1)
     per_head = wanted.reshape(B, h, n_chunks).sum(-1)
-    counts = torch.cat([want.flatten(1).sum(1), need.flatten(1).sum(1), per_head.max().reshape(1)]).to(torch.int64)
+    total_need = need.sum().reshape(1).to(torch.int64)           # over the group: decides the all-gather fallback
+    dist.all_reduce(total_need, group=group)
+    counts = torch.cat([want.flatten(1).sum(1), need.flatten(1).sum(1), per_head.max().reshape(1), total_need]).to(torch.int64)
     counts = counts.cpu().tolist()                               # the one host synchronisation of the exchange
     send_counts, recv_counts, n_stage = counts[:world], counts[world:2 * world], counts[2 * world]
+    fraction = counts[2 * world + 1] / max(1, world * B * h * (n_chunks - n_local))
+    if fraction > dense_fraction:
+        remapped = torch.where(valid, rank_major, torch.full_like(rank_major, -1)).to(indices.dtype)
+        empty = torch.empty((0, 3), dtype=torch.int64, device=dev)
+        return FetchPlan(empty, empty, send_counts, recv_counts, n_chunks - n_local, remapped, True, fraction)
     snd = torch.nonzero_static(want, size=sum(send_counts))      # rows [peer, b, h, chunk], sorted: grouped by peer
     rcv = torch.nonzero_static(need, size=sum(recv_counts))      # rows [owner, b, h, chunk]: the arrival order
     rcv_slot = slot[rcv[:, 1], rcv[:, 2], rcv[:, 0] * n_local + rcv[:, 3]]
@@ -168,14 +184,19 @@ def plan_fetch(indices: torch.Tensor, n_chunks: int, part: SeqPartition, group=N
     remote_slot = slot[bb, hh, rank_major.clamp_max(n_chunks - 1)]
     remapped = torch.where(is_local, n_stage + rank_major % n_local, remote_slot)
     remapped = torch.where(valid, remapped, torch.full_like(remapped, -1)).to(indices.dtype)
-    return FetchPlan(snd[:, 1:], recv_index, send_counts, recv_counts, n_stage, remapped)
+    return FetchPlan(snd[:, 1:], recv_index, send_counts, recv_counts, n_stage, remapped, False, fraction)
 
 
 def fetch_chunks(x_chunks: torch.Tensor, plan: FetchPlan, group=None) -> torch.Tensor:
     """x_chunks (B, n_local, S, h, D): this rank's chunks of K or V.  Returns the staging buffer
     (B, n_stage + n_local, S, h, D): the fetched remote tiles in their slots, then the local chunks.  Slots that
-    no id refers to stay uninitialised."""
+    no id refers to stay uninitialised.  In the all-gather fallback the buffer is (B, N, S, h, D) in rank-major order."""
     B, n_local, S, h, D = x_chunks.shape
+    if plan.dense:
+        world = dist.get_world_size(group)
+        every = torch.empty((world,) + tuple(x_chunks.shape), dtype=x_chunks.dtype, device=x_chunks.device)
+        dist.all_gather(list(every.unbind(0)), x_chunks.contiguous(), group=group)
+        return every.transpose(0, 1).reshape(B, world * n_local, S, h, D)     # a view when B == 1
     si, ri = plan.send_index, plan.recv_index
     send = x_chunks[si[:, 0], si[:, 2], :, si[:, 1], :].contiguous()          # (n_send, S, D)
     recv = torch.empty((ri.shape[0], S, D), dtype=x_chunks.dtype, device=x_chunks.device)
@@ -269,9 +290,11 @@ def context_parallel_forward(q, k, v, lmk_q, *, h_kv: int, topk: int, chunk_size
             timings[name] = timings.get(name, 0.0) + a.elapsed_time(b)
     if return_aux:
         es = k.element_size()
+        fetched = B * h_kv * (n_chunks - Tl // S) if plan.dense else sum(plan.recv_counts)
         return o, {"indices": idx, "lse_swa": lse, "remote_tiles": sum(plan.recv_counts),
-                   "staging_slots": plan.n_stage,
-                   "fetch_bytes": 2 * sum(plan.recv_counts) * S * D * es,
+                   "staging_slots": plan.n_stage, "fetch_mode": "all_gather" if plan.dense else "selected_tiles",
+                   "wanted_fraction": plan.wanted_fraction,
+                   "fetch_bytes": 2 * fetched * S * D * es,
                    "allgather_bytes": (lmk_k.numel() * lmk_k.element_size() + prior_b.numel() * prior_b.element_size())
                    * (world - 1) // world,
                    "halo_bytes": 2 * sum(1 for b in mine if b > 0 and part.owner(b - 1) != rank) * B * halo * h_kv * D * es}

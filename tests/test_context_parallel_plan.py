@@ -19,7 +19,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, kind, out):
+def _worker(rank, world, port, kind, dense_fraction, out):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -37,9 +37,10 @@ def _worker(rank, world, port, kind, out):
         if rank == world - 1:
             idx[:, :, 1] = -1                       # a head that wants nothing at all
         kc, vc = part.shard(k_full, rank), part.shard(v_full, rank)
-        plan = plan_fetch(idx, N, part)
+        plan = plan_fetch(idx, N, part, dense_fraction=dense_fraction)
         k_stage, v_stage = fetch_chunks(kc, plan), fetch_chunks(vc, plan)
-        ok = k_stage.shape[1] == plan.n_stage + n_local
+        ok = plan.dense == (dense_fraction == 0.0)
+        ok &= k_stage.shape[1] == (N if plan.dense else plan.n_stage + n_local)
         own = {b * nbk + c for b in part.blocks(rank) for c in range(nbk)}
         wanted = {(b, hh, int(c)) for b in range(B) for hh in range(h) for c in idx[b, :, hh].flatten().tolist()
                   if c >= 0 and c not in own}
@@ -74,11 +75,12 @@ def _worker(rank, world, port, kind, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,kind", [(2, "contiguous"), (2, "zigzag"), (4, "zigzag")])
-def test_remote_chunk_exchange(world, kind):
+@pytest.mark.parametrize("world,kind,dense_fraction", [(2, "contiguous", 2.0), (2, "zigzag", 2.0), (4, "zigzag", 2.0),
+                                                       (2, "zigzag", 0.0)])   # 0.0: always the all-gather fallback
+def test_remote_chunk_exchange(world, kind, dense_fraction):
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), kind, out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), kind, dense_fraction, out), nprocs=world, join=True)
     assert all(out.get(r) is True for r in range(world)), dict(out)
 
 
