@@ -144,18 +144,24 @@ def plan_fetch(indices: torch.Tensor, n_chunks: int, part: SeqPartition, group=N
     dev = indices.device
     nbk = n_chunks // part.n_blocks                              # chunks per block
     n_local = nbk * part.blocks_per_rank
-    # chunk id -> (owner, position among the owner's chunks), as one index into the rank-major order
-    order = part.block_order()
-    pos_of_block = torch.tensor(sorted(range(len(order)), key=lambda i: order[i]), device=dev)
-    ids = indices.long()
+    # chunk id -> owner * n_local + position among the owner's chunks ("rank-major" order), in int32 arithmetic:
+    # block j sits at rank-major block 2 j (j < world) or 2 (2 world - 1 - j) + 1 in the zig-zag partition
+    ids = indices.to(torch.int32)
     valid = ids >= 0
     safe = ids.clamp_min(0)
-    rank_major = pos_of_block[safe // nbk] * nbk + safe % nbk    # in [0, N): owner·n_local + local chunk
-    # wanted[b, h, rank-major chunk]; column N collects the padding
-    flat = torch.where(valid, rank_major, torch.full_like(rank_major, n_chunks))
-    wanted = torch.zeros((B, h, n_chunks + 1), dtype=torch.bool, device=dev)
-    wanted.scatter_(2, flat.permute(0, 2, 1, 3).reshape(B, h, L * K), True)
-    wanted = wanted[..., :n_chunks].reshape(B, h, world, n_local)
+    blk = safe // nbk
+    if part.kind == "zigzag":
+        blk = torch.where(blk < world, 2 * blk, 2 * (2 * world - 1 - blk) + 1)
+    rank_major = blk * nbk + safe % nbk                          # in [0, N)
+    del blk, safe
+    # wanted[b, h, rank-major chunk]; column N collects the padding.  One int64 tensor (the scatter index) is built.
+    row = (torch.arange(B, device=dev, dtype=torch.int32).view(B, 1, 1, 1) * h
+           + torch.arange(h, device=dev, dtype=torch.int32).view(1, 1, h, 1)) * (n_chunks + 1)
+    flat = (torch.where(valid, rank_major, torch.full_like(rank_major, n_chunks)) + row).reshape(-1).long()
+    wanted = torch.zeros(B * h * (n_chunks + 1), dtype=torch.bool, device=dev)
+    wanted.scatter_(0, flat, True)
+    del flat
+    wanted = wanted.view(B, h, n_chunks + 1)[..., :n_chunks].reshape(B, h, world, n_local)
     wanted[:, :, rank] = False                                   # my own chunks are not fetched
     need = wanted.permute(2, 0, 1, 3).contiguous()               # (owner, B, h, local chunk)
     want = torch.empty_like(need)                                # (requester, B, h, my local chunk)
@@ -181,7 +187,7 @@ def plan_fetch(indices: torch.Tensor, n_chunks: int, part: SeqPartition, group=N
     is_local = valid & (rank_major // n_local == rank)
     hh = torch.arange(h, device=dev).view(1, 1, h, 1).expand_as(ids)
     bb = torch.arange(B, device=dev).view(B, 1, 1, 1).expand_as(ids)
-    remote_slot = slot[bb, hh, rank_major.clamp_max(n_chunks - 1)]
+    remote_slot = slot[bb, hh, rank_major.long()]
     remapped = torch.where(is_local, n_stage + rank_major % n_local, remote_slot)
     remapped = torch.where(valid, remapped, torch.full_like(remapped, -1)).to(indices.dtype)
     return FetchPlan(snd[:, 1:], recv_index, send_counts, recv_counts, n_stage, remapped, False, fraction)
