@@ -132,6 +132,12 @@ def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     if not t.is_cuda:
         _pending().clear()
         raise RuntimeError("hils_b200 kernels need CUDA tensors (no CPU fallback exists)")
+    # The kernels read rows with 8- and 16-byte vector loads and through TMA descriptors: a tensor that starts inside
+    # a 16-byte word (an odd slice of a larger buffer) would fault on the device, so it is refused here.
+    if t.data_ptr() % 16 != 0 and t.numel() * t.element_size() >= 16:
+        _pending().clear()
+        raise ValueError(f"hils_b200: tensor of shape {tuple(t.shape)} starts at an address that is not 16-byte aligned "
+                         "(a view into the middle of a buffer?); copy it with .clone() first. Nothing was launched")
     _pending().append(t.device)
     return t.data_ptr()
 

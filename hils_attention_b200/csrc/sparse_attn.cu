@@ -72,6 +72,9 @@ extern "C" int hils_sparse_attn_fwd(const void* q, const void* k, const void* v,
   if (L == 0) return HILS_OK;
   HILS_REQUIRE(q && weights && indices && o, "sparse_attn_fwd: null pointer");
   HILS_REQUIRE(T < chunk_size || (k && v), "sparse_attn_fwd: null k/v");
+  // every kernel behind this entry point reads rows with 8- or 16-byte vector loads
+  HILS_REQUIRE((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)weights | (uintptr_t)indices | (uintptr_t)o) & 15) == 0,
+               "sparse_attn_fwd: tensors must be 16-byte aligned");
   SparseParams p = make_params(q, k, v, weights, indices, slope, B, L, T, h_q, h_kv, D, Dv, K, num_weights,
                                chunk_size, sm_scale, mask_last_token);
   p.o = o;
@@ -91,7 +94,8 @@ extern "C" int hils_sparse_attn_fwd(const void* q, const void* k, const void* v,
       const int rc = sparse_fwd_tc_launch(p, st);
       if (rc != HILS_ERR_UNSUPPORTED) return rc;
     }
-    const size_t need = L > 4 ? sparse_fwd_cm_workspace(p) : 0;
+    // (a dense shape that the kernel above refused - misaligned tensors - has no workspace: it goes to the generic kernel)
+    const size_t need = (L > 4 && !dense) ? sparse_fwd_cm_workspace(p) : 0;
     if (need > 0) {
       if (!workspace || workspace_bytes < need) {
         set_error("sparse_attn_fwd: workspace of %zu bytes needed, %zu given", need, workspace_bytes);

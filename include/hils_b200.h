@@ -7,7 +7,10 @@
  *     indices (B, L, h_kv, K) int32   weights (B, L, h_q, num_weights)
  * `dtype` selects the element type of the activation tensors (HILS_BF16 or HILS_F32); all
  * arithmetic accumulates in fp32.  `stream` is a cudaStream_t passed as void*.  Calls enqueue
- * work on that stream and return without synchronising.
+ * work on that stream and return without synchronising.  Every tensor must start on a 16-byte
+ * boundary (the kernels read rows with 8- and 16-byte vector loads and through TMA descriptors);
+ * the sparse-attention entry points verify it and return HILS_ERR_BAD_ARG, the Python host layer
+ * verifies it for every call before anything is launched.
  *
  * Return value: 0 on success, a negative HILS_ERR_* code on an argument or launch error
  * (hils_last_error() gives the text).  The library never allocates device memory; kernels that

@@ -132,3 +132,29 @@ def test_tc_backward_is_deterministic():
     (dq1, dk1, dv1, dw1), (dq2, dk2, dv2, dw2) = grads
     assert torch.equal(dk1, dk2) and torch.equal(dv1, dv2) and torch.equal(dw1, dw2)
     assert float((dq1.float() - dq2.float()).abs().max()) <= 2 ** -7 * float(dq1.float().abs().max())
+
+
+def test_misaligned_tensors_are_refused_before_any_launch():
+    """A bf16 tensor that starts 2 bytes into its buffer can feed neither the TMA tiles nor the vector loads of the
+    generic kernels: the host layer refuses it with an error before anything is launched, and so does the C entry
+    point for callers that bypass the host layer."""
+    import ctypes
+    import hils_attention_b200 as hb
+    from hils_attention_b200 import _lib
+    q, k, v, w, idx = _case(1, 256, 256, 2, 1, 64, 4, 7)
+    buf = torch.empty(q.numel() + 1, dtype=BF, device="cuda")
+    q_off = buf[1:].view(q.shape)
+    q_off.copy_(q)
+    assert q_off.data_ptr() % 16 != 0 and q_off.is_contiguous()
+    kd, vd, wd, idd = k.cuda(), v.cuda(), w.cuda(), idx.cuda()
+    with pytest.raises(ValueError, match="16-byte aligned"):
+        hb.HiLS_block_M_head(q_off, kd, vd, wd, idd, block_size=64, is_training=False)
+    o = torch.empty_like(q_off.clone())
+    lib = _lib.load()
+    rc = lib.hils_sparse_attn_fwd(q_off.data_ptr(), kd.data_ptr(), vd.data_ptr(), wd.data_ptr(), idd.data_ptr(), None,
+                                  o.data_ptr(), 1, 256, 256, 2, 2, 64, 64, 4, 5, 64, ctypes.c_float(0.125), 1, 1, None, 0,
+                                  torch.cuda.current_stream().cuda_stream)
+    assert rc != 0 and b"16-byte aligned" in lib.hils_last_error()
+    # the aligned call still works afterwards
+    out = hb.HiLS_block_M_head(q.cuda(), kd, vd, wd, idd, block_size=64, is_training=False)
+    check(out, orc.sparse_attn(q.float(), k.float(), v.float(), w.float(), idx, chunk_size=64), BF, "aligned call after a refusal")
