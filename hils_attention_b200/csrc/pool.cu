@@ -244,7 +244,7 @@ __device__ __forceinline__ void prefetch_tile_l2(const bf16* kbase, int64_t row_
 }
 
 template <int NK, int GM>
-__global__ void __launch_bounds__(32 * kPoolWarps) pool_fwd_bf16_kernel(
+__global__ void __launch_bounds__(32 * kPoolWarps, 3) pool_fwd_bf16_kernel(
     const bf16* __restrict__ mu_q, const bf16* __restrict__ k, bf16* __restrict__ lmk_k, float* __restrict__ lmk_b,
     int N, int S, int h_q, int h_kv, int64_t k_batch_stride, float scale, int compact) {
   constexpr int D = NK * 16, LPR = 2 * NK;
