@@ -16,7 +16,10 @@ Per layer the ranks exchange only
     the ranks together want more than half of all remote tiles (independent random queries over a long context want
     nearly all of them) the exchange falls back to one all-gather of K and of V, which moves the same bytes without
     the gather and scatter copies on either side.
-Everything else runs on local memory with the single-GPU kernels.  The reference has no context-parallel HiLS
+Everything else runs on local memory with the single-GPU kernels.  With `training=True` the chain is differentiable:
+the three exchanges are autograd functions whose backward runs the reverse exchange (reduce-scatter of the chunk-key
+gradients, halo gradients back to the block they came from, tile gradients back to their owners and summed there), as
+the reference's older HSA model does for its all-gather (models/HSA_Ultralong/gather_with_grad.py:9-31).  The reference has no context-parallel HiLS
 path; its older HSA model all-gathers every landmark and every chunk's K/V
 (models/HSA_Ultralong/hsa_layers.py:893-898).  Collectives go through torch.distributed (NCCL on GPUs, gloo in
 the CPU tests of the exchange); no kernel reads a peer's memory.
@@ -215,14 +218,124 @@ def fetch_chunks(x_chunks: torch.Tensor, plan: FetchPlan, group=None) -> torch.T
 
 
 # ------------------------------------------------------------------------------------------
+# the same exchanges as differentiable functions
+# ------------------------------------------------------------------------------------------
+def _reduce_scatter_sum(full: torch.Tensor, group) -> torch.Tensor:
+    """full (world, ...) -> sum over ranks of slice [my rank] (gloo has no reduce-scatter: all-reduce and slice)."""
+    rank = dist.get_rank(group)
+    full = full.contiguous()
+    if dist.get_backend(group) == "gloo":
+        dist.all_reduce(full, group=group)
+        return full[rank].clone()
+    out = torch.empty_like(full[0])
+    dist.reduce_scatter_tensor(out, full, group=group)
+    return out
+
+
+class _GatherChunks(torch.autograd.Function):
+    """(B, n_local, ...) of every rank -> (B, N, ...) in chunk order; backward: each rank receives the sum of all
+    ranks' gradients for its own chunks."""
+
+    @staticmethod
+    def forward(ctx, x, part, group):
+        world = part.world
+        every = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+        dist.all_gather(list(every.unbind(0)), x.contiguous(), group=group)
+        nb = x.shape[1] // part.blocks_per_rank
+        order = part.block_order()
+        inv = sorted(range(len(order)), key=lambda i: order[i])      # block -> gathered position
+        ctx.part, ctx.group, ctx.nb, ctx.order = part, group, nb, order
+        t = every.transpose(0, 1)
+        t = t.reshape(t.shape[0], len(order), nb, *t.shape[3:])
+        return t[:, inv].flatten(1, 2)
+
+    @staticmethod
+    def backward(ctx, g):
+        part, nb, order = ctx.part, ctx.nb, ctx.order
+        g = g.reshape(g.shape[0], len(order), nb, *g.shape[2:])[:, order]          # back to rank-major blocks
+        g = g.reshape(g.shape[0], part.world, part.blocks_per_rank * nb, *g.shape[3:]).transpose(0, 1)
+        return _reduce_scatter_sum(g, ctx.group), None, None
+
+
+class _Halo(torch.autograd.Function):
+    """x (B, Tl, h, D) -> the halos of the local blocks, concatenated along dim 1 (zeros for the sequence's first
+    block); backward: a halo's gradient goes back to the block it came from and is added to that block's tail."""
+
+    @staticmethod
+    def forward(ctx, x, part, halo, group):
+        ctx.part, ctx.halo, ctx.group, ctx.xshape = part, halo, group, tuple(x.shape)
+        hs = exchange_halo(x, part, halo, group)
+        ref = x[:, :halo]
+        return torch.cat([h if h is not None else torch.zeros_like(ref) for h in hs], 1)
+
+    @staticmethod
+    def backward(ctx, g):
+        part, halo, group, xshape = ctx.part, ctx.halo, ctx.group, ctx.xshape
+        rank = dist.get_rank(group)
+        mine = part.blocks(rank)
+        tb = xshape[1] // len(mine)
+        gx = g.new_zeros(xshape)
+        ops, recvs = [], []
+        for b in range(1, part.n_blocks):                    # the forward's pairs with the direction reversed
+            src, dst = part.owner(b - 1), part.owner(b)
+            if dst == rank:
+                i = mine.index(b)
+                gh = g[:, i * halo:(i + 1) * halo].contiguous()
+                if src == rank:
+                    j = mine.index(b - 1)
+                    gx[:, (j + 1) * tb - halo:(j + 1) * tb] += gh
+                else:
+                    ops.append(dist.P2POp(dist.isend, gh, src, group))
+            elif src == rank:
+                buf = torch.empty((xshape[0], halo) + xshape[2:], dtype=g.dtype, device=g.device)
+                recvs.append((mine.index(b - 1), buf))
+                ops.append(dist.P2POp(dist.irecv, buf, dst, group))
+        if ops:
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+        for j, buf in recvs:
+            gx[:, (j + 1) * tb - halo:(j + 1) * tb] += buf
+        return gx, None, None, None
+
+
+class _FetchChunks(torch.autograd.Function):
+    """fetch_chunks with a backward: the gradient of every fetched tile returns to its owner, where the gradients of all
+    the ranks that fetched it (and the owner's own) are summed."""
+
+    @staticmethod
+    def forward(ctx, x_chunks, plan, group):
+        ctx.plan, ctx.group, ctx.xshape = plan, group, tuple(x_chunks.shape)
+        return fetch_chunks(x_chunks, plan, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        plan, group = ctx.plan, ctx.group
+        B, n_local, S, h, D = ctx.xshape
+        if plan.dense:
+            world = dist.get_world_size(group)
+            full = g.reshape(B, world, n_local, S, h, D).transpose(0, 1)
+            return _reduce_scatter_sum(full, group), None, None
+        si, ri = plan.send_index, plan.recv_index
+        g_recv = g[ri[:, 0], ri[:, 2], :, ri[:, 1], :].contiguous()              # tiles I fetched, in arrival order
+        g_send = torch.empty((si.shape[0], S, D), dtype=g.dtype, device=g.device)
+        dist.all_to_all_single(g_send, g_recv, output_split_sizes=plan.send_counts, input_split_sizes=plan.recv_counts,
+                               group=group)
+        gx = g[:, plan.n_stage:].clone()
+        gx.permute(0, 1, 3, 2, 4).index_put_((si[:, 0], si[:, 2], si[:, 1]), g_send, accumulate=True)   # a view: in place
+        return gx, None, None
+
+
+# ------------------------------------------------------------------------------------------
 # the chain
 # ------------------------------------------------------------------------------------------
 def context_parallel_forward(q, k, v, lmk_q, *, h_kv: int, topk: int, chunk_size: int = 64,
                              window_size: int = 512, partition: str = "zigzag", group=None,
-                             return_aux: bool = False, timings: Optional[Dict[str, float]] = None):
+                             return_aux: bool = False, timings: Optional[Dict[str, float]] = None,
+                             training: bool = False):
     """Forward of the attention chain for this rank's tokens.  q, lmk_q (B, Tl, h_q, D); k, v (B, Tl, h_kv, D):
     the rank's blocks concatenated (see SeqPartition); every block is a multiple of chunk_size and at least
-    window + chunk long.  With `timings` (a dict) the stages are timed with CUDA events, which synchronises."""
+    window + chunk long.  With `timings` (a dict) the stages are timed with CUDA events, which synchronises.
+    training=True keeps what the backward needs and makes the exchanges differentiable."""
     from . import ops
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     part = SeqPartition(world, partition)
@@ -247,20 +360,37 @@ def context_parallel_forward(q, k, v, lmk_q, *, h_kv: int, topk: int, chunk_size
     # 1. pooled chunk keys of the local chunks, all-gathered into chunk order
     kc = k.unflatten(1, (Tl // S, S))
     lk, lb = ops.chunk_attn_pool(lmk_q[:, S - 1::S], kc)
-    lmk_k, prior_b = gather_chunk_keys(lk, lb, part, group)
+    if training:
+        lmk_k, prior_b = _GatherChunks.apply(lk, part, group), _GatherChunks.apply(lb, part, group)
+    else:
+        lmk_k, prior_b = gather_chunk_keys(lk, lb, part, group)
     mark("pool+allgather")
     # 2. sliding-window branch per block, with the preceding block's tail as halo
-    halos_k, halos_v = exchange_halo(k, part, halo, group), exchange_halo(v, part, halo, group)
+    if training:
+        hk_all, hv_all = _Halo.apply(k, part, halo, group), _Halo.apply(v, part, halo, group)
+        halos_k = [hk_all[:, i * halo:(i + 1) * halo] for i in range(len(mine))]
+        halos_v = [hv_all[:, i * halo:(i + 1) * halo] for i in range(len(mine))]
+    else:
+        halos_k, halos_v = exchange_halo(k, part, halo, group), exchange_halo(v, part, halo, group)
     mark("halo")
     swa_o, lse = [], []
     for i, blk in enumerate(mine):
         sl = slice(i * tb, (i + 1) * tb)
-        if blk > 0:
+        if blk > 0 and training:
+            # The training kernels want as many queries as keys: the halo gets zero queries whose outputs are dropped.
+            # Block starts and the halo are multiples of the chunk size, so positions relative to the start of the
+            # halo have the chunk phase of the absolute ones and the windows of the block's own tokens are unchanged.
+            zq = torch.zeros((B, halo, h_q, D), dtype=q.dtype, device=q.device)
+            o_i, l_i = ops.flex_attn_tl(torch.cat([zq, q[:, sl]], 1), torch.cat([halos_k[i], k[:, sl]], 1),
+                                        torch.cat([halos_v[i], v[:, sl]], 1), W, S, training=True, mask_lmk=True,
+                                        expand_to_chunk=True)
+            o_i, l_i = o_i[:, halo:], l_i[:, halo:]
+        elif blk > 0:
             o_i, l_i = ops.flex_attn_tl(q[:, sl], torch.cat([halos_k[i], k[:, sl]], 1),
                                         torch.cat([halos_v[i], v[:, sl]], 1), W, S, training=False, mask_lmk=True,
                                         expand_to_chunk=True, kv_start=blk * tb - halo)
         else:
-            o_i, l_i = ops.flex_attn_tl(q[:, sl], k[:, sl], v[:, sl], W, S, training=False, mask_lmk=True,
+            o_i, l_i = ops.flex_attn_tl(q[:, sl], k[:, sl], v[:, sl], W, S, training=training, mask_lmk=True,
                                         expand_to_chunk=True)
         swa_o.append(o_i)
         lse.append(l_i)
@@ -272,7 +402,7 @@ def context_parallel_forward(q, k, v, lmk_q, *, h_kv: int, topk: int, chunk_size
     for i, blk in enumerate(mine):
         sl = slice(i * tb, (i + 1) * tb)
         i_i, s_i = ops.online_softmax_topk_head(lmk_q[:, sl], lmk_k, lse_act[:, sl], topk, block_size=S,
-                                                window_size=W, is_training=False, q_offset=blk * tb,
+                                                window_size=W, is_training=training, q_offset=blk * tb,
                                                 G=lmk_k.shape[2] // h_kv, bias=prior_b)
         idx.append(i_i)
         sc.append(s_i)
@@ -282,12 +412,13 @@ def context_parallel_forward(q, k, v, lmk_q, *, h_kv: int, topk: int, chunk_size
     # 4. fetch the selected remote chunks per kv head into a local staging buffer, rewrite the ids
     plan = plan_fetch(idx, n_chunks, part, group)
     mark("plan")
-    k_stage = fetch_chunks(kc, plan, group).flatten(1, 2)
-    v_stage = fetch_chunks(v.unflatten(1, (Tl // S, S)), plan, group).flatten(1, 2)
+    fetch = (lambda x: _FetchChunks.apply(x, plan, group)) if training else (lambda x: fetch_chunks(x, plan, group))
+    k_stage = fetch(kc).flatten(1, 2)
+    v_stage = fetch(v.unflatten(1, (Tl // S, S))).flatten(1, 2)
     mark("fetch")
     # 5. sparse chunk attention on local memory only, combine
     o_h = ops.HiLS_block_M_head(q, k_stage, v_stage, w.contiguous(), plan.remapped.to(torch.int32).contiguous(),
-                                block_size=S, mask_last_token=True, is_training=False)
+                                block_size=S, mask_last_token=True, is_training=training)
     o = torch.addcmul(o_h, swa_o, w[..., -1:])
     mark("sparse+combine")
     if timings is not None and marks:

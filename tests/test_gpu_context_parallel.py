@@ -68,3 +68,49 @@ def test_context_parallel_matches_single_gpu(world, kind, T):
         assert match >= 0.99, (r, match)
         assert err < 2e-2, (r, err)
         assert n_remote > 0 or (kind == "contiguous" and r == 0)   # only the first contiguous shard fetches nothing
+
+
+def _train_worker(rank, world, port, kind, T, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from hils_attention_b200.attention import HiLSAttentionConfig, HiLSAttentionCore
+        from hils_attention_b200.parallel import SeqPartition, context_parallel_forward
+        (q, k, v), (hq, hk, S, W, K) = _inputs(T)
+        do = torch.randn(q.shape, generator=torch.Generator().manual_seed(99)).to(torch.bfloat16)
+        part = SeqPartition(world, kind)
+        qd, kd, vd = (part.shard(t, rank).cuda().contiguous().requires_grad_(True) for t in (q, k, v))
+        o, aux = context_parallel_forward(qd, kd, vd, qd, h_kv=hk, topk=K, chunk_size=S, window_size=W, partition=kind,
+                                          return_aux=True, training=True)
+        o.backward(part.shard(do, rank).cuda())
+        core = HiLSAttentionCore(HiLSAttentionConfig(hq, hk, K, S, W)).train()
+        qf, kf, vf = (t.cuda().requires_grad_(True) for t in (q, k, v))
+        full, faux = core(qf, kf, vf, qf, return_aux=True)
+        full.backward(do.cuda())
+        same = float((aux["indices"] == part.shard(faux["indices"], rank)).all(-1).float().mean())
+        errs = {}
+        for name, a, b in (("o", o, part.shard(full, rank)), ("dq", qd.grad, part.shard(qf.grad, rank)),
+                           ("dk", kd.grad, part.shard(kf.grad, rank)), ("dv", vd.grad, part.shard(vf.grad, rank))):
+            ref = b.float()
+            errs[name] = float(((a.float() - ref).abs().max() / max(1.0, float(ref.abs().max()))))
+        out[rank] = (same, errs)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,kind,T", [(2, "zigzag", 4096), (4, "zigzag", 8192)])
+def test_context_parallel_backward_matches_single_gpu(world, kind, T):
+    """Gradients of the sequence-sharded chain (reverse exchanges included) equal the single-GPU chain's, shard by shard."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_train_worker, args=(world, _free_port(), kind, T, out), nprocs=world, join=True)
+    for r in range(world):
+        same, errs = out[r]
+        assert same >= 0.999, (r, same)          # identical selections: the gradients are then comparable element by element
+        for name, e in errs.items():
+            assert e < 2e-2, (r, name, e)
