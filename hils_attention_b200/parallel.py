@@ -397,12 +397,13 @@ def context_parallel_forward(q, k, v, lmk_q, *, h_kv: int, topk: int, chunk_size
     swa_o, lse = torch.cat(swa_o, 1), torch.cat(lse, 1)
     lse_act = lse.to(q.dtype)
     mark("swa")
-    # 3. selection over all chunk keys at each block's absolute positions, inter-chunk softmax
+    # 3. selection over all chunk keys at each block's absolute positions, inter-chunk softmax.  (is_training=False
+    # only because, as in the reference, the op ignores q_offset otherwise; its scores are differentiable either way.)
     idx, sc = [], []
     for i, blk in enumerate(mine):
         sl = slice(i * tb, (i + 1) * tb)
         i_i, s_i = ops.online_softmax_topk_head(lmk_q[:, sl], lmk_k, lse_act[:, sl], topk, block_size=S,
-                                                window_size=W, is_training=training, q_offset=blk * tb,
+                                                window_size=W, is_training=False, q_offset=blk * tb,
                                                 G=lmk_k.shape[2] // h_kv, bias=prior_b)
         idx.append(i_i)
         sc.append(s_i)
