@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(kSelTcThreads, 2) topk_fwd_tc_kernel(TopkParam
     float thrv = -CUDART_INF_F;                             // the K-th largest value so far
     int cnt = 0;                                            // buffered values of this token
     float* cand = cand_s + r;
-    float lt = 0.f, thr = -CUDART_INF_F;
+    float lt = 0.f, thr = -CUDART_INF_F, cut = -CUDART_INF_F;
     int take = 0, eq_seen = 0, n_out = 0;
     int32_t* out_ids = p.indices + row * K;
     bf16* out_sc = static_cast<bf16*>(p.scores) + row * K;
@@ -321,6 +321,9 @@ __global__ void __launch_bounds__(kSelTcThreads, 2) topk_fwd_tc_kernel(TopkParam
 #pragma unroll
         for (int j = 0; j < 32; ++j) gt += (j < K && top[j] > thr) ? 1 : 0;
         take = (thr > -CUDART_INF_F) ? K - gt : 0;
+        // u >= cut is necessary for key >= thr: the margin is far above the few ulps of lse_total and of the K-th key
+        // that the roundings of fl(fl(s scale) + bias) - lse_total can move a key by
+        cut = (thr + lt) - 1e-5f * (fabsf(lt) + fabsf(thr) + 1.f);
       }
 #pragma unroll 1
       for (int cb = 0; cb < 4; ++cb) {
@@ -374,21 +377,64 @@ __global__ void __launch_bounds__(kSelTcThreads, 2) topk_fwd_tc_kernel(TopkParam
             thrv = sel_kth(top, K);
           }
         } else {
+          // Emit pass.  Only ~K of a row's candidates are selected, so the exact key (two roundings and a subtraction)
+          // is formed for the few that a one-instruction bound lets through: u = fma(s, scale, bias) against
+          // cut = K-th key + lse_total minus a margin that covers every rounding between u and the key.  Those few are
+          // buffered (score, column) and handled after the group.  Groups with columns beyond a row's limit, rows that
+          // take every candidate (fewer than K) and diagnostic runs take the exact path for all 32 columns.
+          bool fast = !rk && thr > -CUDART_INF_F && c0 + 32 <= lim;
+          fast = __all_sync(0xffffffffu, fast);
+          int nb = 0;
+          if (fast) {
+            // The buffer keeps the layout of the first pass - thread r owns the floats r + 128 e - because the row warps
+            // of a CTA can be one tile apart: a warp that is already emitting must not touch the slots in which a
+            // slower warp still holds first-pass values.  Entry n = (score at e = 2 n, column at e = 2 n + 1).
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float raw = __fmul_rn(sv[j], p.scale);
-            float v = raw;
-            if (has_bias) v += bias_s[sb][cb * 32 + j];
-            const bool valid = c0 + j < lim;
-            const float key = valid ? v - lt : -CUDART_INF_F;
-            if (rk && c0 + j < p.N) rk[c0 + j] = key;
-            const bool is_eq = valid && key == thr && thr > -CUDART_INF_F;
-            const bool sel = valid && key > -CUDART_INF_F && (key > thr || (is_eq && eq_seen < take));
-            eq_seen += is_eq ? 1 : 0;
-            if (sel && n_out < K) {
-              out_ids[n_out] = c0 + j;
-              out_sc[n_out] = __float2bfloat16_rn(raw);
-              ++n_out;
+            for (int j = 0; j < 32; ++j) {
+              const float u = has_bias ? fmaf(sv[j], p.scale, bias_s[sb][cb * 32 + j]) : sv[j] * p.scale;
+              const bool q = u >= cut;
+              if (q && nb < kSelCap / 2) {
+                cand[(2 * nb) * 128] = sv[j];
+                cand[(2 * nb + 1) * 128] = __int_as_float(cb * 32 + j);
+              }
+              nb += q ? 1 : 0;
+            }
+            fast = !__any_sync(0xffffffffu, nb > kSelCap / 2);         // a buffer overflowed: the exact path redoes the group
+            if (fast) {
+              for (int e = 0; e < nb; ++e) {
+                const int col = __float_as_int(cand[(2 * e + 1) * 128]) & 127;
+                const float raw = __fmul_rn(cand[(2 * e) * 128], p.scale);
+                float v = raw;
+                if (has_bias) v += bias_s[sb][col];
+                const float key = v - lt;
+                const bool is_eq = key == thr;
+                const bool sel = key > thr || (is_eq && eq_seen < take);
+                eq_seen += is_eq ? 1 : 0;
+                if (sel && n_out < K) {
+                  out_ids[n_out] = t * 128 + col;
+                  out_sc[n_out] = __float2bfloat16_rn(raw);
+                  ++n_out;
+                }
+              }
+            }
+          }
+          if (!fast) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float raw = __fmul_rn(sv[j], p.scale);
+              float v = raw;
+              if (has_bias) v += bias_s[sb][cb * 32 + j];
+              const bool valid = c0 + j < lim;
+              const float key = valid ? v - lt : -CUDART_INF_F;
+              if (rk && c0 + j < p.N) rk[c0 + j] = key;
+              const bool is_eq = valid && key == thr && thr > -CUDART_INF_F;
+              const bool sel = valid && key > -CUDART_INF_F && (key > thr || (is_eq && eq_seen < take));
+              eq_seen += is_eq ? 1 : 0;
+              if (sel && n_out < K) {
+                out_ids[n_out] = c0 + j;
+                out_sc[n_out] = __float2bfloat16_rn(raw);
+                ++n_out;
+              }
             }
           }
         }

@@ -663,6 +663,12 @@ def test_topk_long_candidate_lists_one_thread_per_token(ops, cfg):
     same = (idx.cpu() == ridx).all(-1)
     assert same.float().mean().item() >= 0.99
     check(sc.view(B, L, h, 1, K)[same], rsc[same], BF, "scores")
+    # the production call (no diagnostics) emits through a cheap bound and evaluates only the candidates it lets
+    # through exactly: ids and scores must be bit-identical to the diagnostic run, which evaluates every candidate
+    idx2, sc2 = ops.online_softmax_topk_head(q.cuda(), lm.cuda(), lse.cuda(), K, S, W, q_offset=q_offset, is_training=False,
+                                             bias=None if bias is None else bias.cuda())
+    assert _lib.load().hils_take_device_status() == 0
+    assert torch.equal(idx2, idx) and torch.equal(sc2, sc)
 
 
 @pytest.mark.parametrize("L", [999, 1023, 1100])
