@@ -335,13 +335,23 @@ __global__ void __launch_bounds__(kSelTcThreads, 2) topk_fwd_tc_kernel(TopkParam
         if (pass == 0) {
           if (c0 < lim) {
             float cm[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            if (c0 + 32 <= lim) {                      // the whole group lies inside the row's range: no column test
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float v = __fmul_rn(sv[j], p.scale);
-              if (has_bias) v += bias_s[sb][cb * 32 + j];
-              v = (c0 + j < lim) ? v : -CUDART_INF_F;
-              sv[j] = v;
-              cm[j & 3] = fmaxf(cm[j & 3], v);
+              for (int j = 0; j < 32; ++j) {
+                float v = __fmul_rn(sv[j], p.scale);
+                if (has_bias) v += bias_s[sb][cb * 32 + j];
+                sv[j] = v;
+                cm[j & 3] = fmaxf(cm[j & 3], v);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float v = __fmul_rn(sv[j], p.scale);
+                if (has_bias) v += bias_s[sb][cb * 32 + j];
+                v = (c0 + j < lim) ? v : -CUDART_INF_F;
+                sv[j] = v;
+                cm[j & 3] = fmaxf(cm[j & 3], v);
+              }
             }
             const float m_new = fmaxf(m_run, fmaxf(fmaxf(cm[0], cm[1]), fmaxf(cm[2], cm[3])));
             const float nb = -m_new * kSelLog2e;
