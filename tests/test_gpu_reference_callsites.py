@@ -5,7 +5,7 @@
   models/NaiveBSA/naive_bsa_kernel.py   imports the ops lazily inside `naive_bsa_kernel` (:169-171)
   models/FlashHiLS/hils_attention.py    binds them at import and in `HiLSAttention.__init__` (:9-10, :264-267)
 and run the reference's code on top of the B200 kernels.  The files are looked for under $HILS_REFERENCE_ROOT,
-baseline/_ref/ (filled by baseline/install_reference.py) and /root/reference; the tests skip when none has them.
+baseline/_ref/ (filled by baseline/install_reference.py); the tests skip when neither has them.
 Needs a B200.
 """
 import importlib.util
@@ -25,7 +25,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _reference_file(rel):
-    for base in (os.environ.get("HILS_REFERENCE_ROOT"), os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
+    for base in (os.environ.get("HILS_REFERENCE_ROOT"), os.path.join(ROOT, "baseline", "_ref")):
         if base and os.path.exists(os.path.join(base, rel)):
             return os.path.join(base, rel)
     pytest.skip(f"reference file {rel} not available on this machine")
