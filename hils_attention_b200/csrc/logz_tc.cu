@@ -410,6 +410,17 @@ __global__ void __launch_bounds__(kLzThreads, 2) logz_bwd_dk_tc_kernel(LogzBwdPa
   uint8_t* Qs = smem;                     // 2 stages
   uint8_t* Ks = Qs + 2 * QBYTES;
   uint8_t* dSs = Ks + KBYTES;             // 2 x [128 x 64] bf16
+  {
+    // At D = 128 two CTAs per SM need the tiles, the static variables in front of them and the alignment gap to fit
+    // 115,712 bytes, which the launch sizes to the byte: refuse to run rather than write past the dynamic region if
+    // the layout is ever different.
+    uint32_t dyn_bytes;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    if ((size_t)(dSs + 2 * 16384 - smem_raw) > dyn_bytes) {
+      if (threadIdx.x == 0) atomicCAS(&g_logz_status, 0, 7200001);
+      return;
+    }
+  }
 
   __shared__ uint64_t k_full, q_full[2], s_full[2], ds_full[2], dk_done[2];
   __shared__ uint32_t tmem_base_s;
@@ -576,7 +587,10 @@ int logz_bwd_tc_launch(const void* q, const void* k, const float* log_z, const f
   if (int rc = make_tmap_bf16_thd(&tmQ, q, (uint64_t)B * L, h_q, D, G, QB)) return rc;
   const size_t DBb = (size_t)(D / 64);
   const size_t smem_dq = 1024 + DBb * 16384 + 2 * DBb * 8192 + 2 * 16384;
-  const size_t smem_dk = 1024 + 2 * DBb * 16384 + DBb * 8192 + 2 * 16384;
+  // key-major pass at D = 128: two CTAs per SM have (228 KB / 2 - 1 KB reserved) = 115,712 bytes each, static variables
+  // (80 bytes, in front of the dynamic region) included; the tiles take 114,688, so the gap to the next 1 KB boundary
+  // is 944 bytes, not 1024 (the kernel checks that the layout fits)
+  const size_t smem_dk = (D == 128 ? 944 : 1024) + 2 * DBb * 16384 + DBb * 8192 + 2 * 16384;
   dim3 grid_q((L + QB - 1) / QB, h_kv, B), grid_k((L + 63) / 64, h_kv, B);
   if (D == 64) {
     cudaFuncSetAttribute(logz_bwd_dq_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq);
