@@ -49,25 +49,33 @@ __device__ __forceinline__ unsigned long long lmk_bits(const SwaTcParams& p, int
 
 // ================================================================================================
 template <int D>
-__global__ void __launch_bounds__(kThreads, (D == 64) ? 3 : 1) swa_fwd_tc_kernel(SwaTcParams p, const __grid_constant__ CUtensorMap tmK,
+__global__ void __launch_bounds__(kThreads, (D == 64) ? 3 : 2) swa_fwd_tc_kernel(SwaTcParams p, const __grid_constant__ CUtensorMap tmK,
                                                               const __grid_constant__ CUtensorMap tmV) {
   constexpr int DB = D / 64;
   constexpr int QBYTES = DB * 16384;
   constexpr int KVBYTES = DB * 8192;
   // A block's window is ~10 key tiles swept twice, so CTA prologue, pipeline fill and epilogue weigh as much
   // as the loop: at D = 64 three CTAs share an SM (one S accumulator, one P tile, 128 TMEM columns and
-  // 65 KB of shared memory each) and hide them for one another; D = 128 double-buffers S and P instead.
-  constexpr int NSB = (D == 64) ? 1 : 2;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* Qs = smem;
+  // 65 KB of shared memory each) and hide them for one another; at D = 128 two do (256 TMEM columns each).  Two CTAs of
+  // D = 128 have 115,712 bytes each and the tiles alone take 114,688: the barriers live behind the tiles in the dynamic
+  // region, which starts on a 1 KB boundary because nothing static precedes it, so no alignment gap is lost.
+  constexpr int NSB = 1;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* Qs = smem_raw;
   uint8_t* Ks = Qs + QBYTES;
   uint8_t* Vs = Ks + 2 * KVBYTES;
   uint8_t* Ps = Vs + 2 * KVBYTES;
-
-  __shared__ uint64_t kv_full[2], s_full[2], p_full[2], pv_done[2];
-  __shared__ uint32_t tmem_base_s;
-  __shared__ volatile int abort_s;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + NSB * 16384);
+  uint64_t* kv_full = bars;          // [2]
+  uint64_t* s_full = bars + 2;       // [2]
+  uint64_t* p_full = bars + 4;       // [2]
+  uint64_t* pv_done = bars + 6;      // [2]
+  uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int& abort_s = *reinterpret_cast<volatile int*>(reinterpret_cast<uint32_t*>(bars + 8) + 1);
+  if ((reinterpret_cast<uintptr_t>(smem_raw) & 1023) != 0) {   // the tiles need the 1 KB alignment of their swizzle
+    if (threadIdx.x == 0) atomicExch(&g_device_status, 405);
+    return;
+  }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.h_q / p.h_kv, QB = 128 / G;
@@ -84,7 +92,7 @@ __global__ void __launch_bounds__(kThreads, (D == 64) ? 3 : 1) swa_fwd_tc_kernel
     mbar_init_fence();
     abort_s = 0;
   }
-  if (warp == 4) tmem_alloc(&tmem_base_s, NSB == 1 ? 128 : 256);
+  if (warp == 4) tmem_alloc(&tmem_base_s, D == 64 ? 128 : 256);
 
   const int r = tid, ql = r / G, g = r % G, i = q0 + ql;
   const bool is_row = tid < 128;
@@ -241,7 +249,7 @@ __global__ void __launch_bounds__(kThreads, (D == 64) ? 3 : 1) swa_fwd_tc_kernel
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, NSB == 1 ? 128 : 256);
+  if (warp == 4) tmem_dealloc(tmem, D == 64 ? 128 : 256);
 }
 
 // Backward row arithmetic in two phases, so that the dP row can still be in flight from TMEM while the
@@ -753,7 +761,7 @@ int swa_fwd_tc_launch(const void* q, const void* k, const void* v, void* o, floa
   if (int rc = make_tmap_bf16_rows(&tmK, k, (uint64_t)B * Lk, (uint64_t)h_kv * D, (uint64_t)h_kv * D, 64)) return rc;
   if (int rc = make_tmap_bf16_rows(&tmV, v, (uint64_t)B * Lk, (uint64_t)h_kv * D, (uint64_t)h_kv * D, 64)) return rc;
   const int QB = 128 / (h_q / h_kv);
-  const size_t smem = 1024 + (size_t)(D / 64) * 16384 + 4 * (size_t)(D / 64) * 8192 + (D == 64 ? 1 : 2) * 16384;
+  const size_t smem = (size_t)(D / 64) * 16384 + 4 * (size_t)(D / 64) * 8192 + 16384 + 128;   // tiles + barriers
   dim3 grid(ceil_div(Lq, QB), h_kv, B);
   if (D == 64) {
     cudaFuncSetAttribute(swa_fwd_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
