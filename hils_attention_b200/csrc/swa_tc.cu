@@ -60,8 +60,11 @@ __global__ void __launch_bounds__(kThreads, (D == 64) ? 3 : 2) swa_fwd_tc_kernel
   // D = 128 have 115,712 bytes each and the tiles alone take 114,688: the barriers live behind the tiles in the dynamic
   // region, which starts on a 1 KB boundary because nothing static precedes it, so no alignment gap is lost.
   constexpr int NSB = 1;
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* Qs = smem_raw;
+  // (No alignment attribute: it would apply to the dynamic region of every kernel of this file and cost the backward
+  // kernels, which budget their shared memory to the byte, their second CTA.  With nothing static in front, the region
+  // starts at the CTA's shared-memory window, which is 1 KB aligned; the kernel verifies it.)
+  extern __shared__ uint8_t swa_fwd_smem[];
+  uint8_t* Qs = swa_fwd_smem;
   uint8_t* Ks = Qs + QBYTES;
   uint8_t* Vs = Ks + 2 * KVBYTES;
   uint8_t* Ps = Vs + 2 * KVBYTES;
@@ -72,7 +75,7 @@ __global__ void __launch_bounds__(kThreads, (D == 64) ? 3 : 2) swa_fwd_tc_kernel
   uint64_t* pv_done = bars + 6;      // [2]
   uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + 8);
   volatile int& abort_s = *reinterpret_cast<volatile int*>(reinterpret_cast<uint32_t*>(bars + 8) + 1);
-  if ((reinterpret_cast<uintptr_t>(smem_raw) & 1023) != 0) {   // the tiles need the 1 KB alignment of their swizzle
+  if ((reinterpret_cast<uintptr_t>(swa_fwd_smem) & 1023) != 0) {   // the tiles need the 1 KB alignment of their swizzle
     if (threadIdx.x == 0) atomicExch(&g_device_status, 405);
     return;
   }
