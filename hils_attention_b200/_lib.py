@@ -50,6 +50,8 @@ SIGNATURES = {
     "hils_combine_bwd": (_I, [_P] * 5 + [_I] * 7 + [_P]),
     "hils_decode_step": (_I, [_P] * 6 + [_I] + [_P] * 2 + [_I] + [_P] * 2 + [_I] * 8 + [_F, _I, _P, _SZ, _P]),
     "hils_decode_step_workspace_bytes": (_SZ, [_I] * 8),
+    "hils_decode_step_paged": (_I, [_P] * 7 + [_I] * 2 + [_P, _I] + [_P] * 2 + [_I] + [_P] * 2 + [_I] * 9 + [_F, _I, _P, _SZ, _P]),
+    "hils_decode_step_paged_workspace_bytes": (_SZ, [_I] * 9),
     "hils_norm_rope_fwd": (_I, [_P] * 6 + [_I] * 5 + [_F, _I, _I, _P]),
     "hils_norm_rope_bwd": (_I, [_P] * 8 + [_I] * 7 + [_P]),
 }
@@ -61,6 +63,7 @@ KERNELS_PER_CALL = {
     "hils_chunk_logz_fwd": 1, "hils_chunk_logz_bwd": 2, "hils_swa_fwd": 1, "hils_swa_bwd": 2,
     "hils_chunk_weights_fwd": 1, "hils_chunk_weights_bwd": 1, "hils_combine_fwd": 1, "hils_combine_bwd": 1,
     "hils_norm_rope_fwd": 1, "hils_norm_rope_bwd": 1,
+    "hils_decode_step_paged": 8,   # append, then as below
     "hils_decode_step": 7,   # window, cast, key stream, selection, weights, sparse, combine (the 2 copies not counted)
 }
 _launches = 0

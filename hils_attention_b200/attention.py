@@ -166,6 +166,41 @@ class HiLSAttentionCore(torch.nn.Module):
         layer._publish()
         return o.view(B, 1, h_q, D)
 
+    def decode_paged(self, q, k, v, lmk_q, store, position_embeddings=None, return_indices: bool = False):
+        """One new token per sequence against a paged store (kv_store.PagedKVStore), sequences of different lengths
+        in one batch: q, lmk_q (B, 1, h_q, D), k, v (B, 1, h_kv, D) with B = store.batch, between store.begin_step()
+        and store.end_step().  The whole step is one library call; a sequence whose chunk this token completes then
+        gets the chunk's pooled key and prior bias (models/FlashHiLS/hils_attention.py:364-410), formed from the
+        page the chunk lives in.  Inference only."""
+        if not self.enable_prior_query:
+            raise NotImplementedError("decode_paged needs enable_prior_query=True (the pooled chunk keys live in the store)")
+        B = q.shape[0]
+        if B != store.batch:
+            raise ValueError(f"decode_paged: {B} rows given, the store's batch is {store.batch}")
+        layer = self.layer_idx
+        k_pages, v_pages, table, lens, lmk_k, prior_b = store.step_args(layer)
+        max_len = max((store.length(b) for b in store.active_slots()), default=0)
+        out = ops.decode_step_paged(
+            q[:, 0].contiguous(), lmk_q[:, 0].contiguous(), k[:, 0].contiguous(), v[:, 0].contiguous(), k_pages, v_pages,
+            table, lens, max_len, lmk_k, prior_b, self.topk, self.chunk_size, self.hils_sliding_window,
+            self.enable_softmax1, workspace=getattr(self, "_paged_ws", None), return_indices=return_indices)
+        o, self._paged_ws = out[0], out[-1]
+        done = store.completing()
+        if done:
+            rows = torch.tensor(done, dtype=torch.long, device=q.device)
+            pe = None
+            if position_embeddings is not None:
+                cos, sin = position_embeddings
+                pe = (cos if cos.shape[0] == 1 else cos.index_select(0, rows), sin if sin.shape[0] == 1 else sin.index_select(0, rows))
+            mu = self._prior_queries(lmk_q.index_select(0, rows), slice(0, 1), pe)           # (n, 1, h_q, D)
+            kc = store.chunk_keys(layer, done).unsqueeze(1)                                   # (n, 1, 64, h_kv, D)
+            new_k, new_b = ops.chunk_attn_pool(mu.contiguous(), kc)
+            if self.enable_chunk_pooling:
+                new_k = ops.chunk_mean_pool(kc)
+            store.put_chunk_keys(layer, done, new_k[:, 0], new_b[:, 0])
+        o = o.unsqueeze(1)
+        return (o, out[1].unsqueeze(1)) if return_indices else o
+
     def forward(self, q, k, v, lmk_q, past_key_values=None, use_cache: bool = False,
                 return_aux: bool = False, position_embeddings=None):
         """q, lmk_q (B,L,h_q,D); k, v (B,L,h_kv,D) of the NEW tokens.  Returns (B,L,h_q,Dv), the

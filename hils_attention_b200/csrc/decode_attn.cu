@@ -4,6 +4,8 @@
 // query row) reads each K/V row once with 16-byte loads (16 lanes per row) and serves all G query
 // heads of the group from it.  Same contracts as the sparse chunk attention
 // (ops/hils_fwd_bwd_head.py:404-485) and the sliding-window branch (ops/flex_attn_tilelang.py:115-253).
+#include <algorithm>
+
 #include "common.cuh"
 #include "mma_rows.cuh"
 
@@ -18,7 +20,32 @@ struct DecodeParams {
   int B, L, T, h_q, h_kv, D, K, num_weights, S, mask_last;       // sparse
   int W, mask_lmk, expand, kv_start;                              // sliding window
   float scale;
+  // Paged store (pages != null): K/V are a pool of pages of S tokens, (num_pages, S, h_kv, D); chunk c of sequence b
+  // lives in page pages[b * page_stride + c]; sequence b holds lens[b] + len_add tokens (T is ignored).
+  const int32_t* pages; const int32_t* lens;
+  int page_stride, num_pages, len_add;
 };
+
+// Set when a page table holds an id outside the pool or a chunk past the table's width; the access is skipped.
+__device__ int g_paged_status = 0;
+
+__device__ __forceinline__ int seq_tokens(const DecodeParams& p, int b) { return p.lens ? p.lens[b] + p.len_add : p.T; }
+
+// Row `tok` of sequence b (holding T tokens), kv-head h.  Paged: rows that follow it in the same chunk are contiguous
+// at the usual stride h_kv * D; a run of rows must not leave its chunk.  Null when the page table is inconsistent.
+template <typename T>
+__device__ __forceinline__ const T* kv_rows_at(const DecodeParams& p, const void* base, int b, int T_b, int tok, int h) {
+  if (p.pages) {
+    const int c = tok / p.S;
+    const int pg = (c < p.page_stride) ? p.pages[(int64_t)b * p.page_stride + c] : -1;
+    if ((unsigned)pg >= (unsigned)p.num_pages) {
+      atomicExch(&g_paged_status, 8000000 + (c < p.page_stride ? 1 : 2));
+      return nullptr;
+    }
+    return static_cast<const T*>(base) + (((int64_t)pg * p.S + (tok - c * p.S)) * p.h_kv + h) * p.D;
+  }
+  return static_cast<const T*>(base) + (((int64_t)b * T_b + tok) * p.h_kv + h) * p.D;
+}
 
 // scores of `n` consecutive key rows (row stride rs elements) against the G query rows in q_s:
 // out[g * ostride + j] = <q_g, K_j>.  Half-warp per key row, four rows in flight per half-warp.
@@ -113,7 +140,8 @@ __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_kernel(DecodePar
   __syncthreads();
   const int32_t* ids = p.idx + (((int64_t)b * p.L + l) * p.h_kv + h) * p.K;
   const T* wts = static_cast<const T*>(p.w) + row0 * p.num_weights;
-  const int nchunk = p.T / p.S;
+  const int T_b = seq_tokens(p, b);
+  const int nchunk = T_b / p.S;
   int nvalid = 0;
   while (nvalid < p.K && ids[nvalid] >= 0) ++nvalid;
   float acc[kDecMaxG][PER];
@@ -126,9 +154,9 @@ __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_kernel(DecodePar
   for (int kk = warp; kk < nvalid; kk += kDecWarps) {
     const int c = ids[kk];
     if (c >= nchunk) continue;
-    const int64_t tok0 = (int64_t)b * p.T + (int64_t)c * p.S;
-    const T* kb = static_cast<const T*>(p.k) + (tok0 * p.h_kv + h) * D;
-    const T* vb = static_cast<const T*>(p.v) + (tok0 * p.h_kv + h) * D;
+    const T* kb = kv_rows_at<T>(p, p.k, b, T_b, c * p.S, h);
+    const T* vb = kv_rows_at<T>(p, p.v, b, T_b, c * p.S, h);
+    if (!kb || !vb) continue;
     __syncwarp();
     score_rows<T, KPER>(q_s, kb, rs, p.S, G, D, pw, 64, lane);
     __syncwarp();
@@ -180,10 +208,11 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams
   const T* q = static_cast<const T*>(p.q) + row0 * D;
   for (int x = tid; x < G * D; x += kDecWarps * 32) q_s[x] = to_f(q[x]);
   __syncthreads();
-  const int t = p.kv_start + (p.T - p.L) + i;
+  const int T_b = seq_tokens(p, b);
+  const int t = p.kv_start + (T_b - p.L) + i;
   int start = t - p.W + 1;
   if (p.expand) start = floor_div(start, p.S) * p.S;
-  const int lo = max(0, start - p.kv_start), hi = min(p.T - 1, t - p.kv_start);
+  const int lo = max(0, start - p.kv_start), hi = min(T_b - 1, t - p.kv_start);
   float acc[kDecMaxG][PER], m[kDecMaxG], lsum[kDecMaxG];
 #pragma unroll
   for (int g = 0; g < kDecMaxG; ++g) {
@@ -193,12 +222,14 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams
   }
   float* pw = p_s + warp * G * 64;
   const int64_t rs = (int64_t)p.h_kv * D;
-  const T* kb0 = static_cast<const T*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
-  const T* vb0 = static_cast<const T*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
+  // paged: lo is a multiple of S = 64 (the window's left edge is snapped to its chunk), so a step stays in one page
   for (int j0 = lo + warp * 64; j0 <= hi; j0 += kDecWarps * 64) {   // 64 keys per warp step
     const int n = min(64, hi - j0 + 1);
+    const T* kb = kv_rows_at<T>(p, p.k, b, T_b, j0, h);
+    const T* vb = kv_rows_at<T>(p, p.v, b, T_b, j0, h);
+    if (!kb || !vb) continue;
     __syncwarp();
-    score_rows<T, KPER>(q_s, kb0 + (int64_t)j0 * rs, rs, n, G, D, pw, 64, lane);
+    score_rows<T, KPER>(q_s, kb, rs, n, G, D, pw, 64, lane);
     __syncwarp();
 #pragma unroll
     for (int g = 0; g < kDecMaxG; ++g) {
@@ -222,7 +253,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams
       }
     }
     __syncwarp();
-    pv_rows<T, PER>(pw, 64, vb0 + (int64_t)j0 * rs, rs, n, G, acc, lane);
+    pv_rows<T, PER>(pw, 64, vb, rs, n, G, acc, lane);
   }
   float* ow = o_s + warp * G * D;
 #pragma unroll
@@ -274,7 +305,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) sparse_decode_bf16_kernel(D
   make_q_frags<NK>(q_s, lane, af, [G](int r) { return r < G ? r : -1; });
   const int32_t* ids = p.idx + (((int64_t)b * p.L + l) * p.h_kv + h) * p.K;
   const bf16* wts = static_cast<const bf16*>(p.w) + row0 * p.num_weights;
-  const int nchunk = p.T / p.S;
+  const int T_b = seq_tokens(p, b);
+  const int nchunk = T_b / p.S;
   int nvalid = p.K;                                   // ids are valid up to the first negative one
   for (int k0 = 0; k0 < p.K; k0 += 32) {
     const int id = (k0 + lane < p.K) ? ids[k0 + lane] : -1;
@@ -291,9 +323,9 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) sparse_decode_bf16_kernel(D
   for (int kk = warp; kk < nvalid; kk += kDecWarps) {
     const int c = ids[kk];
     if (c >= nchunk) continue;
-    const int64_t tok0 = (int64_t)b * p.T + (int64_t)c * p.S;
-    const bf16* kb = static_cast<const bf16*>(p.k) + (tok0 * p.h_kv + h) * D;
-    const bf16* vb = static_cast<const bf16*>(p.v) + (tok0 * p.h_kv + h) * D;
+    const bf16* kb = kv_rows_at<bf16>(p, p.k, b, T_b, c * p.S, h);
+    const bf16* vb = kv_rows_at<bf16>(p, p.v, b, T_b, c * p.S, h);
+    if (!kb || !vb) continue;
     __syncwarp();
     score_rows_mma<NK>(af, kb, rs, p.S, G, pw, 64, lane);
     __syncwarp();
@@ -350,10 +382,11 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(Deco
   __syncthreads();
   uint32_t af[NK][4];
   make_q_frags<NK>(q_s, lane, af, [G](int r) { return r < G ? r : -1; });
-  const int t = p.kv_start + (p.T - p.L) + i;
+  const int T_b = seq_tokens(p, b);
+  const int t = p.kv_start + (T_b - p.L) + i;
   int start = t - p.W + 1;
   if (p.expand) start = floor_div(start, p.S) * p.S;
-  const int lo = max(0, start - p.kv_start), hi = min(p.T - 1, t - p.kv_start);
+  const int lo = max(0, start - p.kv_start), hi = min(T_b - 1, t - p.kv_start);
   float acc[GM][8], m[GM], lsum[GM];
 #pragma unroll
   for (int g = 0; g < GM; ++g) {
@@ -363,12 +396,14 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(Deco
   }
   float* pw = p_s + warp * G * 64;
   const int64_t rs = (int64_t)p.h_kv * D;
-  const bf16* kb0 = static_cast<const bf16*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
-  const bf16* vb0 = static_cast<const bf16*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
+  // paged: lo is a multiple of S = 64 and the step is 32 keys, so a step stays in one page
   for (int j0 = lo + warp * kSwaDecTile; j0 <= hi; j0 += kDecWarps * kSwaDecTile) {
     const int n = min(kSwaDecTile, hi - j0 + 1);
+    const bf16* kb = kv_rows_at<bf16>(p, p.k, b, T_b, j0, h);
+    const bf16* vb = kv_rows_at<bf16>(p, p.v, b, T_b, j0, h);
+    if (!kb || !vb) continue;
     __syncwarp();
-    score_rows_mma<NK>(af, kb0 + (int64_t)j0 * rs, rs, n, G, pw, 64, lane);
+    score_rows_mma<NK>(af, kb, rs, n, G, pw, 64, lane);
     __syncwarp();
 #pragma unroll
     for (int g = 0; g < GM; ++g) {
@@ -389,7 +424,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(Deco
       }
     }
     __syncwarp();
-    pv_rows16<NK, GM>(pw, 64, vb0 + (int64_t)j0 * rs, rs, n, G, acc, lane);
+    pv_rows16<NK, GM>(pw, 64, vb, rs, n, G, acc, lane);
   }
   pv_reduce<NK, GM>(acc);
   float* ow = o_s + warp * G * D;
@@ -472,28 +507,121 @@ static bool decode_shape_ok(int B, int L, int h_q, int h_kv, int D, int Dv) {
 }
 
 // HILS_ERR_UNSUPPORTED when the shape is not a decode shape
-int sparse_decode_launch(const void* q, const void* k, const void* v, const void* w, const int32_t* idx, const float* slope,
-                         void* o, int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights, int S,
-                         float scale, int mask_last, int dtype, cudaStream_t st) {
+struct PagedArgs { const int32_t* pages; const int32_t* lens; int page_stride, num_pages, len_add; };
+
+static void set_paged(DecodeParams& p, const PagedArgs* pa) {
+  if (!pa) return;
+  p.pages = pa->pages; p.lens = pa->lens; p.page_stride = pa->page_stride; p.num_pages = pa->num_pages; p.len_add = pa->len_add;
+}
+
+static int sparse_decode_impl(const void* q, const void* k, const void* v, const void* w, const int32_t* idx, const float* slope,
+                              void* o, int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights, int S,
+                              float scale, int mask_last, int dtype, cudaStream_t st, const PagedArgs* pa) {
   if (!decode_shape_ok(B, L, h_q, h_kv, D, Dv) || S > 64) return HILS_ERR_UNSUPPORTED;
   if (dtype == HILS_BF16 && (((uintptr_t)k | (uintptr_t)v) & 15)) return HILS_ERR_UNSUPPORTED;   // 16-byte row loads
   DecodeParams p = {};
   p.q = q; p.k = k; p.v = v; p.w = w; p.idx = idx; p.slope = slope; p.o = o;
   p.B = B; p.L = L; p.T = T; p.h_q = h_q; p.h_kv = h_kv; p.D = D; p.K = K; p.num_weights = num_weights; p.S = S;
   p.mask_last = mask_last; p.scale = scale;
+  set_paged(p, pa);
   return dtype == HILS_BF16 ? launch_decode<bf16>(p, false, st) : launch_decode<float>(p, false, st);
 }
 
-int swa_decode_launch(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Lq, int Lk, int h_q,
-                      int h_kv, int D, int Dv, int W, int S, int mask_lmk, int expand, float scale, int kv_start, int dtype,
-                      cudaStream_t st) {
+static int swa_decode_impl(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Lq, int Lk, int h_q,
+                           int h_kv, int D, int Dv, int W, int S, int mask_lmk, int expand, float scale, int kv_start, int dtype,
+                           cudaStream_t st, const PagedArgs* pa) {
   if (!decode_shape_ok(B, Lq, h_q, h_kv, D, Dv)) return HILS_ERR_UNSUPPORTED;
   if (dtype == HILS_BF16 && (((uintptr_t)k | (uintptr_t)v) & 15)) return HILS_ERR_UNSUPPORTED;   // 16-byte row loads
   DecodeParams p = {};
   p.q = q; p.k = k; p.v = v; p.o = o; p.lse = lse;
   p.B = B; p.L = Lq; p.T = Lk; p.h_q = h_q; p.h_kv = h_kv; p.D = D; p.S = S; p.W = W; p.mask_lmk = mask_lmk;
   p.expand = expand; p.kv_start = kv_start; p.scale = scale;
+  set_paged(p, pa);
   return dtype == HILS_BF16 ? launch_decode<bf16>(p, true, st) : launch_decode<float>(p, true, st);
+}
+
+int sparse_decode_launch(const void* q, const void* k, const void* v, const void* w, const int32_t* idx, const float* slope,
+                         void* o, int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights, int S,
+                         float scale, int mask_last, int dtype, cudaStream_t st) {
+  return sparse_decode_impl(q, k, v, w, idx, slope, o, B, L, T, h_q, h_kv, D, Dv, K, num_weights, S, scale, mask_last, dtype,
+                            st, nullptr);
+}
+
+int swa_decode_launch(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Lq, int Lk, int h_q,
+                      int h_kv, int D, int Dv, int W, int S, int mask_lmk, int expand, float scale, int kv_start, int dtype,
+                      cudaStream_t st) {
+  return swa_decode_impl(q, k, v, o, lse, B, Lq, Lk, h_q, h_kv, D, Dv, W, S, mask_lmk, expand, scale, kv_start, dtype, st,
+                         nullptr);
+}
+
+// One new query row per sequence against a paged store: sequence b holds lens[b] + len_add tokens, chunk c of it lives in
+// page pages[b * page_stride + c] of the pools k_pages / v_pages (num_pages, 64, h_kv, D).  The page is the chunk (S = 64)
+// and the window's left edge is snapped to its chunk, so no run of rows a warp reads crosses a page.
+int sparse_decode_paged_launch(const void* q, const void* k_pages, const void* v_pages, const void* w, const int32_t* idx,
+                               void* o, const int32_t* pages, const int32_t* lens, int page_stride, int num_pages,
+                               int len_add, int B, int h_q, int h_kv, int D, int K, int num_weights, int S, float scale,
+                               int mask_last, int dtype, cudaStream_t st) {
+  if (S != 64) return HILS_ERR_UNSUPPORTED;
+  const PagedArgs pa = {pages, lens, page_stride, num_pages, len_add};
+  return sparse_decode_impl(q, k_pages, v_pages, w, idx, nullptr, o, B, 1, 0, h_q, h_kv, D, D, K, num_weights, S, scale,
+                            mask_last, dtype, st, &pa);
+}
+
+int swa_decode_paged_launch(const void* q, const void* k_pages, const void* v_pages, void* o, float* lse,
+                            const int32_t* pages, const int32_t* lens, int page_stride, int num_pages, int len_add, int B,
+                            int h_q, int h_kv, int D, int W, int S, int mask_lmk, float scale, int dtype, cudaStream_t st) {
+  if (S != 64) return HILS_ERR_UNSUPPORTED;
+  const PagedArgs pa = {pages, lens, page_stride, num_pages, len_add};
+  return swa_decode_impl(q, k_pages, v_pages, o, lse, B, 1, 0, h_q, h_kv, D, D, W, S, mask_lmk, /*expand=*/1, scale, 0, dtype,
+                         st, &pa);
+}
+
+// The new token of every sequence goes to row lens[b] % S of page pages[b * page_stride + lens[b] / S].
+template <typename T>
+__global__ void paged_append_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new, T* __restrict__ k_pages,
+                                    T* __restrict__ v_pages, const int32_t* __restrict__ pages,
+                                    const int32_t* __restrict__ lens, int page_stride, int num_pages, int S, int row_elems) {
+  const int b = blockIdx.x;
+  const int len = lens[b], c = len / S;
+  const int pg = (len >= 0 && c < page_stride) ? pages[(int64_t)b * page_stride + c] : -1;
+  if ((unsigned)pg >= (unsigned)num_pages) {
+    if (threadIdx.x == 0) atomicExch(&g_paged_status, 8000003);
+    return;
+  }
+  const int64_t dst = ((int64_t)pg * S + (len - c * S)) * row_elems, src = (int64_t)b * row_elems;
+  for (int i = threadIdx.x * 4; i < row_elems; i += blockDim.x * 4) {     // row_elems = h_kv * D, a multiple of 4
+    if constexpr (sizeof(T) == 2) {
+      *reinterpret_cast<uint2*>(k_pages + dst + i) = *reinterpret_cast<const uint2*>(k_new + src + i);
+      *reinterpret_cast<uint2*>(v_pages + dst + i) = *reinterpret_cast<const uint2*>(v_new + src + i);
+    } else {
+      *reinterpret_cast<float4*>(k_pages + dst + i) = *reinterpret_cast<const float4*>(k_new + src + i);
+      *reinterpret_cast<float4*>(v_pages + dst + i) = *reinterpret_cast<const float4*>(v_new + src + i);
+    }
+  }
+}
+
+int paged_append_launch(const void* k_new, const void* v_new, void* k_pages, void* v_pages, const int32_t* pages,
+                        const int32_t* lens, int page_stride, int num_pages, int S, int B, int h_kv, int D, int dtype,
+                        cudaStream_t st) {
+  const int row = h_kv * D;
+  if (row % 4 != 0) return HILS_ERR_UNSUPPORTED;
+  const int threads = std::min(256, std::max(32, (row / 4 + 31) / 32 * 32));
+  if (dtype == HILS_BF16)
+    paged_append_kernel<bf16><<<B, threads, 0, st>>>((const bf16*)k_new, (const bf16*)v_new, (bf16*)k_pages, (bf16*)v_pages,
+                                                     pages, lens, page_stride, num_pages, S, row);
+  else
+    paged_append_kernel<float><<<B, threads, 0, st>>>((const float*)k_new, (const float*)v_new, (float*)k_pages,
+                                                      (float*)v_pages, pages, lens, page_stride, num_pages, S, row);
+  HILS_LAUNCH_CHECK("decode_step_paged (append)");
+  return HILS_OK;
+}
+
+int take_status_paged() {
+  int v = 0, zero = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(&v, g_paged_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_paged_status, &zero, sizeof(int));
+  return v;
 }
 
 }  // namespace hils

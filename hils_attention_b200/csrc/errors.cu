@@ -27,6 +27,7 @@ int take_status_swa_tc();
 int take_status_sparse_cm();
 int take_status_topk_tc();
 int take_status_logz_tc();
+int take_status_paged();
 }  // namespace hils
 
 extern "C" int hils_version(void) { return 100; }
@@ -39,7 +40,8 @@ extern "C" int hils_take_device_status(void) {
   const int c = hils::take_status_sparse_cm();
   const int d = hils::take_status_topk_tc();
   const int e = hils::take_status_logz_tc();
-  if (a < 0 || b < 0 || c < 0 || d < 0 || e < 0) return -1;
-  return a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : e)));
+  const int f = hils::take_status_paged();
+  if (a < 0 || b < 0 || c < 0 || d < 0 || e < 0 || f < 0) return -1;
+  return a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : (e != 0 ? e : f))));
 }
 extern "C" const char* hils_last_error(void) { return hils::g_err; }

@@ -45,6 +45,16 @@ __host__ __device__ __forceinline__ int row_limit(const TopkParams& p, int l) {
   return max(0, min(lim, p.N));
 }
 
+// decode kernels: sequences of one batch may stand at different positions
+__device__ __forceinline__ int row_limit_b(const TopkParams& p, int b, int l) {
+  if (!p.q_offsets) return row_limit(p, l);
+  if (l >= p.L) return 0;
+  if (!p.is_causal) return p.N;
+  const int t = p.q_offsets[b] + l;
+  const int lim = (p.window_size > 0) ? floor_div(t - p.window_size + 1, p.block_size) : floor_div(t, p.block_size);
+  return max(0, min(lim, p.N));
+}
+
 typedef unsigned long long u64;
 
 __device__ __forceinline__ u64 shfl_xor64(u64 v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
@@ -809,7 +819,7 @@ __global__ void __launch_bounds__(256, 1) topk_decode_dots_kernel(TopkParams p, 
       const int g0 = x % ng, row = x / ng;                 // row = (b*L + l)*h_kv + h
       const int h = row % p.h_kv, bl = row / p.h_kv, l = bl % p.L;
       const int64_t b = bl / p.L;
-      const int lim = row_limit(p, l);
+      const int lim = row_limit_b(p, (int)b, l);
       c.key_lo = r * kDotKeys;
       c.key_hi = min(lim, c.key_lo + kDotKeys);
       c.tile = 0;
@@ -989,7 +999,7 @@ __global__ void __launch_bounds__(256, kDots ? 4 : 1) topk_decode_kernel(TopkPar
   const T* q = static_cast<const T*>(p.q) + ((((int64_t)b * p.L + l) * p.h_kv + h) * G) * D;
   const T* lmks = static_cast<const T*>(p.lmks);
   const int HL = p.per_qhead ? p.h_kv * G : p.h_kv;
-  const int lim = row_limit(p, l);
+  const int lim = row_limit_b(p, b, l);
   float ls_mine = 0.f;                        // thread g < G: lse of the sliding-window branch of member g
   if (tid < G) {
     const int64_t o = (((int64_t)b * p.L + l) * p.h_kv + h) * G + tid;
@@ -1365,7 +1375,7 @@ extern "C" int hils_topk_fwd(const void* q, const void* lmks, const void* lse_sw
   p.indices = indices; p.scores = scores; p.lse_total = lse_total; p.rank_keys = rank_keys;
   p.B = B; p.L = L; p.N = N; p.h_kv = h_kv; p.G = G; p.D = D; p.topk = topk; p.block_size = block_size;
   p.window_size = window_size; p.is_causal = is_causal; p.q_offset = q_offset; p.per_qhead = per_qhead;
-  p.lse_dtype = lse_dtype; p.RW = 4; p.scale = sm_scale; p.dots = nullptr;
+  p.lse_dtype = lse_dtype; p.RW = 4; p.scale = sm_scale; p.dots = nullptr; p.q_offsets = nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   // few query rows against many chunk keys (decode, short chunk-prefill): stream the keys once per row
   if (L <= 4 && N >= 512 && topk <= 32 && (D == 64 || D == 128) && L <= 65535) {
@@ -1397,6 +1407,30 @@ extern "C" int hils_topk_fwd(const void* q, const void* lmks, const void* lse_sw
   if (kpl == 2) return launch_topk<float, 2>(p, st);
   return launch_topk<float, 4>(p, st);
 }
+
+namespace hils {
+// Selection of one new query row per sequence when the sequences stand at different positions: q_offsets[b] is the
+// position of sequence b's row (device memory), max_offset the largest of them (host; it sizes the key stream).
+// The chunk keys are (B, N, heads, D) with N the row stride of every sequence; rows at or past a sequence's own limit
+// are never read.  Only the decode kernels take per-sequence positions, so shapes they do not cover are refused.
+int topk_decode_ragged_launch(const void* q, const void* lmks, const void* lse_swa, const float* bias, int32_t* indices,
+                              void* scores, const int32_t* q_offsets, int max_offset, int B, int N, int h_kv, int G, int D,
+                              int topk, int block_size, int window_size, int per_qhead, float sm_scale, int dtype,
+                              int lse_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (!(D == 64 || D == 128) || topk > 32 || B > 65535 || h_kv > 65535) return HILS_ERR_UNSUPPORTED;
+  TopkParams p;
+  p.q = q; p.lmks = lmks; p.lse_swa = lse_swa; p.bias = bias; p.gumbel = nullptr; p.drop_mask = nullptr;
+  p.indices = indices; p.scores = scores; p.lse_total = nullptr; p.rank_keys = nullptr;
+  p.B = B; p.L = 1; p.N = N; p.h_kv = h_kv; p.G = G; p.D = D; p.topk = topk; p.block_size = block_size;
+  p.window_size = window_size; p.is_causal = 1; p.q_offset = max_offset; p.per_qhead = per_qhead;
+  p.lse_dtype = lse_dtype; p.RW = 4; p.scale = sm_scale; p.dots = nullptr; p.q_offsets = q_offsets;
+  const size_t need = hils_topk_fwd_workspace_bytes(B, 1, N, h_kv, G, D, dtype);
+  if (workspace && need > 0 && workspace_bytes >= need && (int64_t)B * h_kv <= 65535) p.dots = static_cast<float*>(workspace);
+  return (dtype != HILS_BF16) ? launch_topk_decode<float, 0>(p, st)
+         : (D == 128)         ? launch_topk_decode<bf16, 8>(p, st)
+                              : launch_topk_decode<bf16, 4>(p, st);
+}
+}  // namespace hils
 
 extern "C" int hils_topk_bwd(const void* d_scores, const int32_t* indices, const void* q, const void* lmks,
                              void* d_q, float* d_lmks_f32, void* d_lmks, int B, int L, int N, int h_kv, int G,

@@ -11,6 +11,7 @@ struct TopkParams {
   int RW;
   float scale;
   float* dots;   // decode, bf16: raw q.k' of every candidate, written by the streaming kernel (or null)
+  const int32_t* q_offsets;   // decode kernels only: position of query row 0 of each batch entry (null: q_offset for all)
 };
 
 }  // namespace hils

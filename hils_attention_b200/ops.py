@@ -470,6 +470,45 @@ def decode_step(q, lmk_q, k_new, v_new, k_store, v_store, length: int, lmk_k, pr
     return (o, idx, workspace) if return_indices else (o, workspace)
 
 
+def decode_step_paged(q, lmk_q, k_new, v_new, k_pages, v_pages, page_table, lens, max_len: int, lmk_k, prior_b, topk: int,
+                      chunk_size: int = 64, window_size: int = 512, softmax1: bool = False,
+                      sm_scale: Optional[float] = None, workspace: Optional[torch.Tensor] = None,
+                      return_indices: bool = False):
+    """One decode step of the whole chain over a paged store, for sequences of different lengths
+    (models/FlashHiLS/hils_attention.py:512-633 with one new token per sequence; inference only).
+
+    q, lmk_q (B, h_q, D); k_new, v_new (B, h_kv, D); k_pages, v_pages (num_pages, 64, h_kv, D) the pool;
+    page_table (B, max_pages) int32 and lens (B) int32 on the device: sequence b holds lens[b] tokens, chunk c
+    of it lives in page page_table[b, c], and the page of position lens[b] is already in the table; max_len is
+    a host-side upper bound of lens.  lmk_k (B, N, h_lmk, D) pooled chunk keys, prior_b (B, N, h_q) fp32 or
+    None.  The new token is written into its page; lens is left as it is.
+    Returns o (B, h_q, D) [, indices (B, h_kv, topk)] and the workspace for reuse."""
+    B, h_q, D = q.shape
+    h_kv = k_new.shape[1]
+    N, h_lmk = lmk_k.shape[1], lmk_k.shape[2]
+    num_pages = k_pages.shape[0]
+    assert k_pages.shape == v_pages.shape == (num_pages, chunk_size, h_kv, D)
+    assert page_table.dtype == torch.int32 and lens.dtype == torch.int32 and page_table.shape[0] == B == lens.shape[0]
+    assert lmk_q.shape == q.shape and k_new.shape == v_new.shape == (B, h_kv, D) and lmk_k.shape[0] == B
+    for t in (q, lmk_q, k_new, v_new, k_pages, v_pages, page_table, lens, lmk_k):
+        assert t.is_contiguous()
+    dt = dtype_code(q)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    pb = None if prior_b is None else prior_b.to(torch.float32).contiguous()
+    assert pb is None or pb.shape == (B, N, h_q)
+    need = query("hils_decode_step_paged_workspace_bytes", B, h_q, h_kv, h_lmk, D, int(topk), N, int(bool(softmax1)), dt)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=q.device)
+    o = torch.empty_like(q)
+    idx = torch.empty((B, h_kv, topk), dtype=torch.int32, device=q.device) if return_indices else None
+    call("hils_decode_step_paged", ptr(q), ptr(lmk_q), ptr(k_new), ptr(v_new), ptr(k_pages), ptr(v_pages), ptr(page_table),
+         int(page_table.shape[1]), int(num_pages), ptr(lens), int(max_len), ptr(lmk_k), ptr(pb), N, ptr(o), ptr(idx),
+         B, h_q, h_kv, h_lmk, D, int(topk), int(chunk_size), int(window_size), int(bool(softmax1)), float(sm_scale), dt,
+         ptr(workspace), workspace.numel(), stream())
+    return (o, idx, workspace) if return_indices else (o, workspace)
+
+
 # ------------------------------------------------------------------------------------------
 # per-head RMSNorm + rotary embedding
 # ------------------------------------------------------------------------------------------

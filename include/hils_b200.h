@@ -265,6 +265,35 @@ size_t hils_decode_step_workspace_bytes(int heads_q, int heads_kv, int heads_lmk
                                         int softmax1, int dtype);
 
 /* ---------------------------------------------------------------------------------------
+ * The same decode step over a PAGED store, for sequences of different lengths in one batch.  The page
+ * is the chunk (64 tokens; the page size the reference's serving notes ask of the serving engine,
+ * README.md:255,262), so a selected chunk is one page and the step never gathers across pages.
+ * Replaces the growth by torch.cat and the CPU round trip of the reference's cache layer
+ * (utils/hils_cache_utils.py:19-23, :45-62): a sequence grows by taking a page from the pool.
+ *   k_pages, v_pages (num_pages, 64, h_kv, D): the pool, shared by all sequences;
+ *   page_table (B, page_stride) int32, device: page of chunk c of sequence b (entries past the
+ *   sequence's last chunk are not read); lens (B) int32, device: tokens sequence b holds BEFORE this
+ *   step; max_len: a host-side upper bound of lens (it sizes the launches; (max_len+1+63)/64 <=
+ *   page_stride, and the page for position lens[b] must already be in the table);
+ *   q, lmk_q, o (B, h_q, D); k_new, v_new (B, h_kv, D), written to row lens[b] % 64 of page
+ *   page_table[b][lens[b] / 64]; lmk_k (B, N, h_lmk, D) pooled chunk keys, row stride N for every
+ *   sequence, rows at or past a sequence's selectable chunks are not read; prior_b (B, N, h_q) fp32 or
+ *   NULL; indices_out (B, h_kv, K) int32 or NULL.  lens is NOT advanced (a model runs this once per
+ *   layer with the same table).  A page id outside [0, num_pages) is skipped and reported through
+ *   hils_take_device_status (8000001..8000003).
+ * ------------------------------------------------------------------------------------- */
+int hils_decode_step_paged(const void* q, const void* lmk_q, const void* k_new, const void* v_new,
+                           void* k_pages, void* v_pages,
+                           const int32_t* page_table, int page_stride, int num_pages,
+                           const int32_t* lens, int max_len,
+                           const void* lmk_k, const float* prior_b, int N, void* o, int32_t* indices_out,
+                           int B, int h_q, int h_kv, int h_lmk, int D, int K, int chunk_size, int window_size,
+                           int softmax1, float sm_scale, int dtype,
+                           void* workspace, size_t workspace_bytes, void* stream);
+size_t hils_decode_step_paged_workspace_bytes(int B, int h_q, int h_kv, int h_lmk, int D, int K, int N,
+                                              int softmax1, int dtype);
+
+/* ---------------------------------------------------------------------------------------
  * Per-head RMSNorm followed by the rotary embedding in one pass (upstream of the attention path).
  * Replaces rms_norm (models/FlashHiLS/modeling_olmo_hils.py:105-111, per-head q_norm / k_norm /
  * lmk_q_norm of hils_attention.py:250-253, :296-321) chained with single_tensor_rope_autograd
