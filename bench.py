@@ -54,6 +54,11 @@ WORKLOADS = {
     # decode: 32 sequences, one new token each, against a 131072-token KV store
     "c4": dict(B=32, T=131072, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
     "c4_small": dict(B=4, T=16384, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
+    # the same decode through the paged store (page = chunk, pages of the sequences interleaved in the pool);
+    # "ragged": sequence lengths spread evenly from T/2 to T in one batch
+    "c4_paged": dict(B=32, T=131072, h_q=32, h_kv=32, D=128, S=64, K=32, W=512, ragged=False),
+    "c4_paged_ragged": dict(B=32, T=131072, h_q=32, h_kv=32, D=128, S=64, K=32, W=512, ragged=True),
+    "c4_paged_small": dict(B=4, T=16384, h_q=32, h_kv=32, D=128, S=64, K=32, W=512, ragged=True),
     # ultra-long context, forward only, the sequence sharded over the ranks
     "c5": dict(B=1, T=1048576, h_q=32, h_kv=32, D=128, S=64, K=32, W=512),
     "c5_small": dict(B=1, T=131072, h_q=4, h_kv=4, D=128, S=64, K=32, W=512),
@@ -630,6 +635,113 @@ def run_decode(args, name, ds, steps, warmup):
     torch.cuda.empty_cache()
     return out
 
+def run_decode_paged(args, name, ds, steps, warmup):
+    """The decode step of run_decode through the paged store: K/V in a pool of 64-token pages, the pages of the
+    sequences interleaved at random in the pool, page tables and lengths read on the device; optionally with
+    sequences of different lengths in the batch.  Sharded over the ranks by sequence (no collective)."""
+    from hils_attention_b200 import _lib
+    from hils_attention_b200.attention import HiLSAttentionConfig, HiLSAttentionCore
+    from hils_attention_b200.kv_store import PagedKVStore
+    import hils_attention_b200 as hb
+
+    world, rank, dev = ds.world, ds.rank, ds.dev
+    w = WORKLOADS[name]
+    Bt, T, hq, hk, D, S, K, W = (w[x] for x in ("B", "T", "h_q", "h_kv", "D", "S", "K", "W"))
+    B = max(1, Bt // world)
+    dtype = torch.bfloat16
+    n_e2e = 16
+    lens0 = [T - (T // 2) * b // max(1, B - 1) if w["ragged"] else T for b in range(B)]
+    lens0 = [t - t % S + 7 for t in lens0]       # with the default step counts nobody completes a chunk while timed
+    max_pages = T // S + 2
+    store = PagedKVStore(B * max_pages + 1, B, max_pages, hk, D, hq, dtype=dtype, device=dev)
+    store.pool.shuffle(11 + rank)                                   # a sequence's pages lie scattered over the pool
+    g = torch.Generator(device=dev).manual_seed(4 + rank)
+    P = store.k_pages.shape[1]
+    for p0 in range(0, P, 1024):                                    # fill in slices: no second copy of the pool
+        n = min(1024, P - p0)
+        off = torch.randn((n, 1, hk, D), generator=g, device=dev) * 0.5
+        store.k_pages[0, p0:p0 + n] = (torch.randn((n, S, hk, D), generator=g, device=dev) + off).to(dtype)
+        store.v_pages[0, p0:p0 + n] = torch.randn((n, S, hk, D), generator=g, device=dev).to(dtype)
+    with torch.no_grad():
+        for b in range(B):
+            slot = store.allocate(lens0[b])
+            N = lens0[b] // S                                        # pooled chunk keys of the cached prefix
+            ids = torch.tensor(store.pages_of(slot)[:N], dtype=torch.long, device=dev)
+            mu = torch.randn((1, N, hq, D), generator=g, device=dev).to(dtype)
+            lk, pb = hb.chunk_attn_pool(mu, store.k_pages[0].index_select(0, ids).unsqueeze(0))
+            store.lmk_k[0, slot, :N].copy_(lk[0])
+            store.prior_b[0, slot, :N].copy_(pb[0])
+            del ids, mu, lk, pb
+    core = HiLSAttentionCore(HiLSAttentionConfig(hq, hk, K, S, W)).eval()
+    host = [torch.randn((B, 1, h, D), generator=torch.Generator().manual_seed(9 + i)).to(dtype).pin_memory()
+            for i, h in enumerate((hq, hk, hk))]
+    qn, kn, vn = (t.to(dev) for t in host)
+    out_host = torch.empty((B, 1, hq, D), dtype=dtype).pin_memory()
+
+    def step(q1, k1, v1):
+        with torch.no_grad():
+            store.begin_step()
+            o = core.decode_paged(q1, k1, v1, q1, store)
+            store.end_step()
+            return o
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(ds.local) as clk:
+        for _ in range(warmup):
+            step(qn, kn, vn)
+        ds.barrier()
+        c0 = _lib.launch_count()
+        clk.start()
+        e0.record()
+        for _ in range(steps):
+            step(qn, kn, vn)
+        e1.record()
+        ds.barrier()
+        clk.stop()
+    launches = _lib.launch_count() - c0
+    ms = e0.elapsed_time(e1)
+    dq_, dk_, dv_ = (torch.empty_like(t) for t in (qn, kn, vn))
+
+    def e2e_step():
+        for d_, h_ in zip((dq_, dk_, dv_), host):
+            d_.copy_(h_, non_blocking=True)
+        out_host.copy_(step(dq_, dk_, dv_), non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    ds.barrier()
+    e0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    ds.barrier()
+    require_clean_status(f"the decode steps of {name}")
+    ms, ms_e2e = ds.max(ms, e0.elapsed_time(e1) / n_e2e)
+    us_step = 1e3 * ms / steps
+    pk = peaks()
+    # bytes a step must touch: pooled keys + bias of each sequence's chunks, the K selected pages, the sliding window
+    alg = sum(hk * ((t // S) * D * 2 + (t // S) * 4 * (hq // hk) + K * S * D * 2 * 2 + (W + S) * D * 2 * 2) for t in lens0)
+    achieved = alg / (us_step * 1e-6) / 1e9
+    out = {
+        "metric": "hils_decode_us_per_step", "value": us_step, "unit": "us/step", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": us_step / 1e3, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": name, **w, "sequences_per_gpu": B, "lengths": [min(lens0), max(lens0)],
+                   "store": f"paged, {P} pages of {S} tokens, {store.bytes_held() / 2**30:.1f} GiB",
+                   "parallelism": f"batch-sharded x{world}, no collective", "l2": "kv_store_larger_than_L2"},
+        "e2e": {"value": 1e3 * ms_e2e, "unit": "us/step",
+                "h2d_bytes_per_step": sum(h.numel() * 2 for h in host), "d2h_bytes_per_step": out_host.numel() * 2},
+        "gpu_launches": launches, "clocks": clk.summary(),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "traffic": None,
+                     "kernel": "paged decode step (all kernels)", "algorithmic_bytes_per_step": alg,
+                     "peak_source": pk["source"]},
+    }
+    del store, core
+    torch.cuda.empty_cache()
+    return out
+
+
 # -------------------------------------------------------------------------------------------------
 # ultra-long context: forward of the chain with the sequence sharded over the ranks
 # -------------------------------------------------------------------------------------------------
@@ -736,6 +848,8 @@ def main():
     decode = args.workload.startswith("c4")
     if args.workload.startswith("c5"):
         line = run_context_parallel(args, args.workload, ds, args.steps, args.warmup)
+    elif args.workload.startswith("c4_paged"):
+        line = run_decode_paged(args, args.workload, ds, args.steps, args.warmup)
     elif decode:
         line = run_decode(args, args.workload, ds, args.steps, args.warmup)
     else:
@@ -751,6 +865,8 @@ def main():
                 torch.cuda.empty_cache()
         attempt("c2", lambda: run_train(args, "c2", ds, max(args.steps, 10), 3, with_e2e=True))
         attempt("c4", lambda: run_decode(args, "c4", ds, max(2 * args.steps, 20), 5))
+        attempt("c4_paged", lambda: run_decode_paged(args, "c4_paged", ds, max(2 * args.steps, 20), 5))
+        attempt("c4_paged_ragged", lambda: run_decode_paged(args, "c4_paged_ragged", ds, max(2 * args.steps, 20), 5))
         attempt("c5", lambda: run_context_parallel(args, "c5", ds, 2, 1))
         if ds.world == 1:
             # the reference arm's configuration on the GPU (fp32 kernels), for a like-for-like CPU/GPU ratio

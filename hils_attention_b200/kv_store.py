@@ -36,6 +36,12 @@ class PagePool:
     def free(self) -> int:
         return len(self._free)
 
+    def shuffle(self, seed: int) -> None:
+        """Hand the free pages out in a random order from now on (what a pool looks like after many sequences came
+        and went); used to measure with a sequence's pages scattered over the pool."""
+        import random
+        random.Random(seed).shuffle(self._free)
+
     def take(self, n: int = 1) -> List[int]:
         if n > len(self._free):
             raise MemoryError(f"paged store: {n} pages wanted, {len(self._free)} free of {self.num_pages - 1}")
