@@ -63,8 +63,8 @@ KERNELS_PER_CALL = {
     "hils_chunk_logz_fwd": 1, "hils_chunk_logz_bwd": 2, "hils_swa_fwd": 1, "hils_swa_bwd": 2,
     "hils_chunk_weights_fwd": 1, "hils_chunk_weights_bwd": 1, "hils_combine_fwd": 1, "hils_combine_bwd": 1,
     "hils_norm_rope_fwd": 1, "hils_norm_rope_bwd": 1,
-    "hils_decode_step_paged": 8,   # append, then as below
-    "hils_decode_step": 7,   # window, cast, key stream, selection, weights, sparse, combine (the 2 copies not counted)
+    "hils_decode_step_paged": 5,   # append, then as below
+    "hils_decode_step": 4,   # window, key stream, selection + inter-chunk softmax, sparse + combine (the 2 copies not counted)
 }
 _launches = 0
 # HILS_B200_CHECK_STATUS=1: read the device status word after every call (synchronises; for debugging)

@@ -24,6 +24,10 @@ struct DecodeParams {
   // lives in page pages[b * page_stride + c]; sequence b holds lens[b] + len_add tokens (T is ignored).
   const int32_t* pages; const int32_t* lens;
   int page_stride, num_pages, len_add;
+  // Decode step fusions.  Window kernel: lse_act (or null) receives the log-sum-exp again, rounded to the activation
+  // dtype the chain carries it in.  Sparse kernel: with swa_o given, o = round(o_hils) + w[swa_col] * swa_o, the
+  // combination of the two branches with the rounding of the separate kernels.
+  void* lse_act; const void* swa_o; int swa_col;
 };
 
 // Set when a page table holds an id outside the pool or a chunk past the table's width; the access is skipped.
@@ -188,6 +192,9 @@ __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_kernel(DecodePar
   for (int i = tid; i < G * D; i += kDecWarps * 32) {
     float s = 0.f;
     for (int w = 0; w < kDecWarps; ++w) s += o_s[w * G * D + i];
+    if (p.swa_o)
+      s = fmaf(to_f(static_cast<const T*>(p.swa_o)[row0 * D + i]), to_f(wts[(i / D) * p.num_weights + p.swa_col]),
+               to_f(from_f<T>(s)));
     o[i] = from_f<T>(s);
   }
 }
@@ -278,7 +285,11 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams
         s += o_s[w * G * D + x] * c;
       }
     o[x] = from_f<T>(tot > 0.f ? s / tot : 0.f);
-    if (x % D == 0) p.lse[row0 + g] = (tot > 0.f) ? mm + logf(tot) : -CUDART_INF_F;
+    if (x % D == 0) {
+      const float lse = (tot > 0.f) ? mm + logf(tot) : -CUDART_INF_F;
+      p.lse[row0 + g] = lse;
+      if (p.lse_act) static_cast<T*>(p.lse_act)[row0 + g] = from_f<T>(lse);
+    }
   }
 }
 
@@ -359,6 +370,9 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) sparse_decode_bf16_kernel(D
   for (int i = tid; i < G * D; i += kDecWarps * 32) {
     float sacc = 0.f;
     for (int w = 0; w < kDecWarps; ++w) sacc += o_s[w * G * D + i];
+    if (p.swa_o)
+      sacc = fmaf(to_f(static_cast<const bf16*>(p.swa_o)[row0 * D + i]), to_f(wts[(i / D) * p.num_weights + p.swa_col]),
+                  to_f(__float2bfloat16_rn(sacc)));
     o[i] = __float2bfloat16_rn(sacc);
   }
 }
@@ -451,7 +465,11 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(Deco
         sacc += o_s[w * G * D + x] * c;
       }
     o[x] = __float2bfloat16_rn(tot > 0.f ? sacc / tot : 0.f);
-    if (x % D == 0) p.lse[row0 + g] = (tot > 0.f) ? mm + logf(tot) : -CUDART_INF_F;
+    if (x % D == 0) {
+      const float lse = (tot > 0.f) ? mm + logf(tot) : -CUDART_INF_F;
+      p.lse[row0 + g] = lse;
+      if (p.lse_act) static_cast<bf16*>(p.lse_act)[row0 + g] = __float2bfloat16_rn(lse);
+    }
   }
 }
 
@@ -516,26 +534,27 @@ static void set_paged(DecodeParams& p, const PagedArgs* pa) {
 
 static int sparse_decode_impl(const void* q, const void* k, const void* v, const void* w, const int32_t* idx, const float* slope,
                               void* o, int B, int L, int T, int h_q, int h_kv, int D, int Dv, int K, int num_weights, int S,
-                              float scale, int mask_last, int dtype, cudaStream_t st, const PagedArgs* pa) {
+                              float scale, int mask_last, int dtype, cudaStream_t st, const PagedArgs* pa,
+                              const void* swa_o = nullptr, int swa_col = 0) {
   if (!decode_shape_ok(B, L, h_q, h_kv, D, Dv) || S > 64) return HILS_ERR_UNSUPPORTED;
   if (dtype == HILS_BF16 && (((uintptr_t)k | (uintptr_t)v) & 15)) return HILS_ERR_UNSUPPORTED;   // 16-byte row loads
   DecodeParams p = {};
   p.q = q; p.k = k; p.v = v; p.w = w; p.idx = idx; p.slope = slope; p.o = o;
   p.B = B; p.L = L; p.T = T; p.h_q = h_q; p.h_kv = h_kv; p.D = D; p.K = K; p.num_weights = num_weights; p.S = S;
-  p.mask_last = mask_last; p.scale = scale;
+  p.mask_last = mask_last; p.scale = scale; p.swa_o = swa_o; p.swa_col = swa_col;
   set_paged(p, pa);
   return dtype == HILS_BF16 ? launch_decode<bf16>(p, false, st) : launch_decode<float>(p, false, st);
 }
 
 static int swa_decode_impl(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Lq, int Lk, int h_q,
                            int h_kv, int D, int Dv, int W, int S, int mask_lmk, int expand, float scale, int kv_start, int dtype,
-                           cudaStream_t st, const PagedArgs* pa) {
+                           cudaStream_t st, const PagedArgs* pa, void* lse_act = nullptr) {
   if (!decode_shape_ok(B, Lq, h_q, h_kv, D, Dv)) return HILS_ERR_UNSUPPORTED;
   if (dtype == HILS_BF16 && (((uintptr_t)k | (uintptr_t)v) & 15)) return HILS_ERR_UNSUPPORTED;   // 16-byte row loads
   DecodeParams p = {};
   p.q = q; p.k = k; p.v = v; p.o = o; p.lse = lse;
   p.B = B; p.L = Lq; p.T = Lk; p.h_q = h_q; p.h_kv = h_kv; p.D = D; p.S = S; p.W = W; p.mask_lmk = mask_lmk;
-  p.expand = expand; p.kv_start = kv_start; p.scale = scale;
+  p.expand = expand; p.kv_start = kv_start; p.scale = scale; p.lse_act = lse_act;
   set_paged(p, pa);
   return dtype == HILS_BF16 ? launch_decode<bf16>(p, true, st) : launch_decode<float>(p, true, st);
 }
@@ -560,20 +579,37 @@ int swa_decode_launch(const void* q, const void* k, const void* v, void* o, floa
 int sparse_decode_paged_launch(const void* q, const void* k_pages, const void* v_pages, const void* w, const int32_t* idx,
                                void* o, const int32_t* pages, const int32_t* lens, int page_stride, int num_pages,
                                int len_add, int B, int h_q, int h_kv, int D, int K, int num_weights, int S, float scale,
-                               int mask_last, int dtype, cudaStream_t st) {
+                               int mask_last, int dtype, cudaStream_t st, const void* swa_o, int swa_col) {
   if (S != 64) return HILS_ERR_UNSUPPORTED;
   const PagedArgs pa = {pages, lens, page_stride, num_pages, len_add};
   return sparse_decode_impl(q, k_pages, v_pages, w, idx, nullptr, o, B, 1, 0, h_q, h_kv, D, D, K, num_weights, S, scale,
-                            mask_last, dtype, st, &pa);
+                            mask_last, dtype, st, &pa, swa_o, swa_col);
+}
+
+// The two decode kernels as the one-call decode step uses them over the token-major store: the window kernel also
+// writes the log-sum-exp in the activation dtype, the sparse kernel also combines the two branches.
+int sparse_decode_combine_launch(const void* q, const void* k, const void* v, const void* w, const int32_t* idx, void* o,
+                                 int B, int T, int h_q, int h_kv, int D, int K, int num_weights, int S, float scale,
+                                 int mask_last, int dtype, cudaStream_t st, const void* swa_o, int swa_col) {
+  return sparse_decode_impl(q, k, v, w, idx, nullptr, o, B, 1, T, h_q, h_kv, D, D, K, num_weights, S, scale, mask_last, dtype,
+                            st, nullptr, swa_o, swa_col);
+}
+
+int swa_decode_lse_launch(const void* q, const void* k, const void* v, void* o, float* lse, void* lse_act, int B, int Lk,
+                          int h_q, int h_kv, int D, int W, int S, int mask_lmk, int expand, float scale, int dtype,
+                          cudaStream_t st) {
+  return swa_decode_impl(q, k, v, o, lse, B, 1, Lk, h_q, h_kv, D, D, W, S, mask_lmk, expand, scale, 0, dtype, st, nullptr,
+                         lse_act);
 }
 
 int swa_decode_paged_launch(const void* q, const void* k_pages, const void* v_pages, void* o, float* lse,
                             const int32_t* pages, const int32_t* lens, int page_stride, int num_pages, int len_add, int B,
-                            int h_q, int h_kv, int D, int W, int S, int mask_lmk, float scale, int dtype, cudaStream_t st) {
+                            int h_q, int h_kv, int D, int W, int S, int mask_lmk, float scale, int dtype, cudaStream_t st,
+                            void* lse_act) {
   if (S != 64) return HILS_ERR_UNSUPPORTED;
   const PagedArgs pa = {pages, lens, page_stride, num_pages, len_add};
   return swa_decode_impl(q, k_pages, v_pages, o, lse, B, 1, 0, h_q, h_kv, D, D, W, S, mask_lmk, /*expand=*/1, scale, 0, dtype,
-                         st, &pa);
+                         st, &pa, lse_act);
 }
 
 // The new token of every sequence goes to row lens[b] % S of page pages[b * page_stride + lens[b] / S].

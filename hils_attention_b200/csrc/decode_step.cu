@@ -50,15 +50,22 @@ int paged_append_launch(const void* k_new, const void* v_new, void* k_pages, voi
                         cudaStream_t st);
 int swa_decode_paged_launch(const void* q, const void* k_pages, const void* v_pages, void* o, float* lse,
                             const int32_t* pages, const int32_t* lens, int page_stride, int num_pages, int len_add, int B,
-                            int h_q, int h_kv, int D, int W, int S, int mask_lmk, float scale, int dtype, cudaStream_t st);
+                            int h_q, int h_kv, int D, int W, int S, int mask_lmk, float scale, int dtype, cudaStream_t st,
+                            void* lse_act);
 int sparse_decode_paged_launch(const void* q, const void* k_pages, const void* v_pages, const void* w, const int32_t* idx,
                                void* o, const int32_t* pages, const int32_t* lens, int page_stride, int num_pages,
                                int len_add, int B, int h_q, int h_kv, int D, int K, int num_weights, int S, float scale,
-                               int mask_last, int dtype, cudaStream_t st);
-int topk_decode_ragged_launch(const void* q, const void* lmks, const void* lse_swa, const float* bias, int32_t* indices,
-                              void* scores, const int32_t* q_offsets, int max_offset, int B, int N, int h_kv, int G, int D,
-                              int topk, int block_size, int window_size, int per_qhead, float sm_scale, int dtype,
-                              int lse_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st);
+                               int mask_last, int dtype, cudaStream_t st, const void* swa_o, int swa_col);
+int swa_decode_lse_launch(const void* q, const void* k, const void* v, void* o, float* lse, void* lse_act, int B, int Lk,
+                          int h_q, int h_kv, int D, int W, int S, int mask_lmk, int expand, float scale, int dtype,
+                          cudaStream_t st);
+int sparse_decode_combine_launch(const void* q, const void* k, const void* v, const void* w, const int32_t* idx, void* o,
+                                 int B, int T, int h_q, int h_kv, int D, int K, int num_weights, int S, float scale,
+                                 int mask_last, int dtype, cudaStream_t st, const void* swa_o, int swa_col);
+int topk_decode_step_launch(const void* q, const void* lmks, const void* lse_swa, const float* bias, int32_t* indices,
+                            void* scores, void* weights, int softmax1, const int32_t* q_offsets, int q_offset, int B, int N,
+                            int h_kv, int G, int D, int topk, int block_size, int window_size, int per_qhead, float sm_scale,
+                            int dtype, int lse_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 // workspace of the paged step: the same pieces, per sequence
 static StepLayout paged_layout(int B, int h_q, int h_kv, int D, int K, int N, int softmax1, int dtype) {
@@ -123,39 +130,30 @@ extern "C" int hils_decode_step_paged(const void* q, const void* lmk_q, const vo
   void* scores = ws + lay.scores;
   void* weights = ws + lay.weights;
   int32_t* indices = indices_out ? indices_out : reinterpret_cast<int32_t*>(ws + lay.indices);
-  const int rows = B * h_q, G = h_q / h_kv;
+  const int G = h_q / h_kv;
   // 1. every sequence's new token goes to row lens[b] of its own pages
   if (int rc = paged_append_launch(k_new, v_new, k_pages, v_pages, page_table, lens, page_stride, num_pages, chunk_size, B,
                                    h_kv, D, dtype, st))
     return rc;
   // 2. sliding-window branch over lens[b] + 1 tokens, landmark columns masked, left edge snapped to the chunk
   if (int rc = swa_decode_paged_launch(q, k_pages, v_pages, swa_o, lse32, page_table, lens, page_stride, num_pages, 1, B, h_q,
-                                       h_kv, D, window_size, chunk_size, 1, sm_scale, dtype, st)) {
+                                       h_kv, D, window_size, chunk_size, 1, sm_scale, dtype, st, lse_act)) {
     if (rc == HILS_ERR_UNSUPPORTED) set_error("decode_step_paged: shape not covered by the decode kernels");
     return rc;
   }
-  // 3. the chain carries the log-sum-exp in the activation dtype
-  if (dtype == HILS_BF16) cast_rows_kernel<bf16><<<(rows + 255) / 256, 256, 0, st>>>(lse32, (bf16*)lse_act, rows);
-  else cast_rows_kernel<float><<<(rows + 255) / 256, 256, 0, st>>>(lse32, (float*)lse_act, rows);
-  HILS_LAUNCH_CHECK("decode_step_paged (lse cast)");
-  // 4. chunk selection, sequence b at position lens[b]
-  if (int rc = topk_decode_ragged_launch(lmk_q, lmk_k, lse_act, prior_b, indices, scores, lens, max_len, B, N, h_kv, G, D, K,
-                                         chunk_size, window_size, h_lmk == h_q && h_q != h_kv, sm_scale, dtype, dtype,
-                                         ws + lay.topk_ws, lay.total - lay.topk_ws, st)) {
+  // 3. chunk selection, sequence b at position lens[b], then prior-bias gather + softmax over [chunks, window(, 0)]
+  const int nw = K + 1 + (softmax1 ? 1 : 0);
+  if (int rc = topk_decode_step_launch(lmk_q, lmk_k, lse_act, prior_b, indices, scores, weights, softmax1, lens, max_len, B, N,
+                                       h_kv, G, D, K, chunk_size, window_size, h_lmk == h_q && h_q != h_kv, sm_scale, dtype,
+                                       dtype, ws + lay.topk_ws, lay.total - lay.topk_ws, st)) {
     if (rc == HILS_ERR_UNSUPPORTED) set_error("decode_step_paged: selection shape not covered by the decode kernels");
     return rc;
   }
-  // 5. prior-bias gather + softmax over [chunks, window(, 0)]
-  const int nw = K + 1 + (softmax1 ? 1 : 0);
-  if (int rc = hils_chunk_weights_fwd(scores, indices, prior_b, lse_act, weights, B, 1, N, h_q, h_kv, K, softmax1, dtype, stream))
-    return rc;
-  // 6. sparse chunk attention over the selected pages, then o += w_swa * o_swa
-  if (int rc = sparse_decode_paged_launch(q, k_pages, v_pages, weights, indices, o, page_table, lens, page_stride, num_pages, 1,
-                                          B, h_q, h_kv, D, K, nw, chunk_size, sm_scale, 1, dtype, st)) {
-    if (rc == HILS_ERR_UNSUPPORTED) set_error("decode_step_paged: shape not covered by the decode kernels");
-    return rc;
-  }
-  return hils_combine_fwd(o, swa_o, weights, o, B, 1, h_q, D, nw, K, dtype, stream);
+  // 4. sparse chunk attention over the selected pages, and o = o_hils + w_swa * o_swa
+  const int rc = sparse_decode_paged_launch(q, k_pages, v_pages, weights, indices, o, page_table, lens, page_stride, num_pages,
+                                            1, B, h_q, h_kv, D, K, nw, chunk_size, sm_scale, 1, dtype, st, swa_o, K);
+  if (rc == HILS_ERR_UNSUPPORTED) set_error("decode_step_paged: shape not covered by the decode kernels");
+  return rc;
 }
 
 extern "C" size_t hils_decode_step_workspace_bytes(int heads_q, int heads_kv, int heads_lmk, int D, int K, int N,
@@ -204,27 +202,48 @@ extern "C" int hils_decode_step(const void* q, const void* lmk_q, const void* k_
                         cudaMemcpyDeviceToDevice, st);
   if (e != cudaSuccess) return cuda_fail(e, "decode_step (store append)");
   const int T = len + 1;
-  // 2. sliding-window branch over the store, landmark columns masked, left edge snapped to the chunk
-  if (int rc = hils_swa_fwd(q, k_store, v_store, swa_o, lse32, 1, 1, T, heads_q, heads_kv, D, D, window_size, chunk_size, 1,
-                            1, sm_scale, 0, dtype, stream))
+  HILS_REQUIRE(((((uintptr_t)q) | ((uintptr_t)lmk_q) | ((uintptr_t)k_store) | ((uintptr_t)v_store) | ((uintptr_t)lmk_k) |
+                 ((uintptr_t)o) | ((uintptr_t)workspace)) & 15) == 0, "decode_step: tensors must be 16-byte aligned");
+  // Four kernels where the shapes allow: the decode kernels take over the small element-wise stages between them (the
+  // cast of the log-sum-exp, the inter-chunk softmax, the combination of the branches); shapes they do not cover run
+  // the stage's general entry point and its follow-up kernel instead.
+  // 2. sliding-window branch over the store, landmark columns masked, left edge snapped to the chunk; the chain
+  //    carries its log-sum-exp in the activation dtype
+  int rc = swa_decode_lse_launch(q, k_store, v_store, swa_o, lse32, lse_act, 1, T, heads_q, heads_kv, D, window_size,
+                                 chunk_size, 1, 1, sm_scale, dtype, st);
+  if (rc == HILS_ERR_UNSUPPORTED) {
+    if ((rc = hils_swa_fwd(q, k_store, v_store, swa_o, lse32, 1, 1, T, heads_q, heads_kv, D, D, window_size, chunk_size, 1, 1,
+                           sm_scale, 0, dtype, stream)))
+      return rc;
+    if (dtype == HILS_BF16) cast_rows_kernel<bf16><<<(heads_q + 255) / 256, 256, 0, st>>>(lse32, (bf16*)lse_act, heads_q);
+    else cast_rows_kernel<float><<<(heads_q + 255) / 256, 256, 0, st>>>(lse32, (float*)lse_act, heads_q);
+    HILS_LAUNCH_CHECK("decode_step (lse cast)");
+  } else if (rc) {
     return rc;
-  // 3. the chain carries the log-sum-exp in the activation dtype
-  if (dtype == HILS_BF16) cast_rows_kernel<bf16><<<(heads_q + 255) / 256, 256, 0, st>>>(lse32, (bf16*)lse_act, heads_q);
-  else cast_rows_kernel<float><<<(heads_q + 255) / 256, 256, 0, st>>>(lse32, (float*)lse_act, heads_q);
-  HILS_LAUNCH_CHECK("decode_step (lse cast)");
-  // 4. chunk selection at absolute position `len`
-  if (int rc = hils_topk_fwd(lmk_q, lmk_k, lse_act, prior_b, nullptr, nullptr, indices, scores, nullptr, nullptr, 1, 1, N, h_t, g_t,
-                             D, K, chunk_size, window_size, 1, len, per_qhead, sm_scale, dtype, dtype, ws + lay.topk_ws,
-                             lay.total - lay.topk_ws, stream))
-    return rc;
-  // 5. prior-bias gather + softmax over [chunks, window(, 0)]
+  }
+  // 3. chunk selection at absolute position `len`, then prior-bias gather + softmax over [chunks, window(, 0)]
   const int nw = K + 1 + (softmax1 ? 1 : 0);
-  if (int rc = hils_chunk_weights_fwd(scores, indices, prior_b, lse_act, weights, 1, 1, N, heads_q, heads_kv, K, softmax1,
-                                      dtype, stream))
+  rc = topk_decode_step_launch(lmk_q, lmk_k, lse_act, prior_b, indices, scores, weights, softmax1, nullptr, len, 1, N, h_t,
+                               g_t, D, K, chunk_size, window_size, per_qhead, sm_scale, dtype, dtype, ws + lay.topk_ws,
+                               lay.total - lay.topk_ws, st);
+  if (rc == HILS_ERR_UNSUPPORTED) {
+    if ((rc = hils_topk_fwd(lmk_q, lmk_k, lse_act, prior_b, nullptr, nullptr, indices, scores, nullptr, nullptr, 1, 1, N, h_t,
+                            g_t, D, K, chunk_size, window_size, 1, len, per_qhead, sm_scale, dtype, dtype, ws + lay.topk_ws,
+                            lay.total - lay.topk_ws, stream)))
+      return rc;
+    if ((rc = hils_chunk_weights_fwd(scores, indices, prior_b, lse_act, weights, 1, 1, N, heads_q, heads_kv, K, softmax1,
+                                     dtype, stream)))
+      return rc;
+  } else if (rc) {
     return rc;
-  // 6. sparse chunk attention over the store, then o += w_swa * o_swa
-  if (int rc = hils_sparse_attn_fwd(q, k_store, v_store, weights, indices, nullptr, o, 1, 1, T, heads_q, heads_kv, D, D, K, nw,
-                                    chunk_size, sm_scale, 1, dtype, nullptr, 0, stream))
+  }
+  // 4. sparse chunk attention over the store, and o = o_hils + w_swa * o_swa
+  rc = (chunk_size <= 64) ? sparse_decode_combine_launch(q, k_store, v_store, weights, indices, o, 1, T, heads_q, heads_kv, D,
+                                                         K, nw, chunk_size, sm_scale, 1, dtype, st, swa_o, K)
+                          : HILS_ERR_UNSUPPORTED;
+  if (rc != HILS_ERR_UNSUPPORTED) return rc;
+  if ((rc = hils_sparse_attn_fwd(q, k_store, v_store, weights, indices, nullptr, o, 1, 1, T, heads_q, heads_kv, D, D, K, nw,
+                                 chunk_size, sm_scale, 1, dtype, nullptr, 0, stream)))
     return rc;
   return hils_combine_fwd(o, swa_o, weights, o, 1, 1, heads_q, D, nw, K, dtype, stream);
 }

@@ -985,7 +985,7 @@ __device__ __forceinline__ void decode_logits_bf16(const TopkParams& p, const bf
 // key row, 16-byte loads), logits go to shared memory, then log-sum-exp, ranking keys and the same
 // sort/merge selection as above, with the candidate tiles spread over the CTA's 8 warps.
 template <typename T, int NK, bool kDots>   // kDots: the logits come from topk_decode_dots_kernel's output
-__global__ void __launch_bounds__(256, kDots ? 4 : 1) topk_decode_kernel(TopkParams p) {
+__global__ void __launch_bounds__(256, kDots ? 8 : 1) topk_decode_kernel(TopkParams p) {
   extern __shared__ __align__(16) float smem[];
   const int G = p.G, D = p.D, N = p.N, K = p.topk;
   const int Npad = (N + 127) & ~127;
@@ -1224,9 +1224,45 @@ __global__ void __launch_bounds__(256, kDots ? 4 : 1) topk_decode_kernel(TopkPar
       acc += __shfl_xor_sync(0xffffffffu, acc, 4);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      if (sub == 0 && k < K)
-        scores[((((int64_t)b * p.L + l) * p.h_kv + h) * G + g) * K + k] =
-            from_f<T>(id >= 0 ? acc * p.scale : -CUDART_INF_F);
+      if (sub == 0 && k < K) {
+        const T sc = from_f<T>(id >= 0 ? acc * p.scale : -CUDART_INF_F);
+        scores[((((int64_t)b * p.L + l) * p.h_kv + h) * G + g) * K + k] = sc;
+        if (p.weights) v_s[g * 32 + k] = to_f(sc);        // the logits in v_s are no longer needed (K <= 32 here)
+      }
+    }
+  }
+  // ---- the step's inter-chunk softmax (glue.cu: chunk_weights_fwd_kernel, same roundings): one warp per member ------
+  if (p.weights) {
+    if (tid < G) v_s[G * 32 + tid] = ls_mine;             // lse of the window branch, already in the chain's dtype
+    __syncthreads();
+    const int ncol = K + 1 + (p.softmax1 ? 1 : 0);
+    for (int g = warp; g < G; g += 8) {
+      float x[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int c = lane + 32 * i;
+        x[i] = -CUDART_INF_F;
+        if (c < K) {
+          x[i] = v_s[g * 32 + c];
+          if (p.bias) {
+            const float bv = p.bias[(((int64_t)b * N + max(sel_ids[c], 0)) * p.h_kv + h) * G + g];
+            x[i] = to_f(from_f<T>(x[i] + to_f(from_f<T>(bv))));
+          }
+        } else if (c == K) {
+          x[i] = v_s[G * 32 + g];
+        } else if (c < ncol) {
+          x[i] = 0.f;
+        }
+      }
+      const float m = warp_max(fmaxf(x[0], x[1]));
+      float e[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) e[i] = (lane + 32 * i < ncol && m > -CUDART_INF_F) ? __expf(x[i] - m) : 0.f;
+      const float inv = 1.f / warp_sum(e[0] + e[1]);      // all -inf: 0/0 = NaN, as the reference's softmax
+      T* wrow = static_cast<T*>(p.weights) + ((((int64_t)b * p.L + l) * p.h_kv + h) * G + g) * ncol;
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        if (lane + 32 * i < ncol) wrow[lane + 32 * i] = from_f<T>(e[i] * inv);
     }
   }
 }
@@ -1376,6 +1412,7 @@ extern "C" int hils_topk_fwd(const void* q, const void* lmks, const void* lse_sw
   p.B = B; p.L = L; p.N = N; p.h_kv = h_kv; p.G = G; p.D = D; p.topk = topk; p.block_size = block_size;
   p.window_size = window_size; p.is_causal = is_causal; p.q_offset = q_offset; p.per_qhead = per_qhead;
   p.lse_dtype = lse_dtype; p.RW = 4; p.scale = sm_scale; p.dots = nullptr; p.q_offsets = nullptr;
+  p.weights = nullptr; p.softmax1 = 0;
   cudaStream_t st = (cudaStream_t)stream;
   // few query rows against many chunk keys (decode, short chunk-prefill): stream the keys once per row
   if (L <= 4 && N >= 512 && topk <= 32 && (D == 64 || D == 128) && L <= 65535) {
@@ -1409,21 +1446,24 @@ extern "C" int hils_topk_fwd(const void* q, const void* lmks, const void* lse_sw
 }
 
 namespace hils {
-// Selection of one new query row per sequence when the sequences stand at different positions: q_offsets[b] is the
-// position of sequence b's row (device memory), max_offset the largest of them (host; it sizes the key stream).
+// Selection of the decode step: one new query row per sequence, always on the decode kernels, with the step's
+// inter-chunk softmax fused behind it (weights, or null).  q_offsets (device, or null) holds each sequence's position
+// when the sequences stand at different ones; q_offset is then the largest of them (host; it sizes the key stream).
 // The chunk keys are (B, N, heads, D) with N the row stride of every sequence; rows at or past a sequence's own limit
-// are never read.  Only the decode kernels take per-sequence positions, so shapes they do not cover are refused.
-int topk_decode_ragged_launch(const void* q, const void* lmks, const void* lse_swa, const float* bias, int32_t* indices,
-                              void* scores, const int32_t* q_offsets, int max_offset, int B, int N, int h_kv, int G, int D,
-                              int topk, int block_size, int window_size, int per_qhead, float sm_scale, int dtype,
-                              int lse_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st) {
-  if (!(D == 64 || D == 128) || topk > 32 || B > 65535 || h_kv > 65535) return HILS_ERR_UNSUPPORTED;
+// are never read.  Shapes the decode kernels do not cover are refused (HILS_ERR_UNSUPPORTED).
+int topk_decode_step_launch(const void* q, const void* lmks, const void* lse_swa, const float* bias, int32_t* indices,
+                            void* scores, void* weights, int softmax1, const int32_t* q_offsets, int q_offset, int B, int N,
+                            int h_kv, int G, int D, int topk, int block_size, int window_size, int per_qhead, float sm_scale,
+                            int dtype, int lse_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (!(D == 64 || D == 128) || topk > 32 || B > 65535 || h_kv > 65535 || N <= 0) return HILS_ERR_UNSUPPORTED;
+  if (weights && lse_dtype != dtype) return HILS_ERR_UNSUPPORTED;
   TopkParams p;
   p.q = q; p.lmks = lmks; p.lse_swa = lse_swa; p.bias = bias; p.gumbel = nullptr; p.drop_mask = nullptr;
   p.indices = indices; p.scores = scores; p.lse_total = nullptr; p.rank_keys = nullptr;
   p.B = B; p.L = 1; p.N = N; p.h_kv = h_kv; p.G = G; p.D = D; p.topk = topk; p.block_size = block_size;
-  p.window_size = window_size; p.is_causal = 1; p.q_offset = max_offset; p.per_qhead = per_qhead;
+  p.window_size = window_size; p.is_causal = 1; p.q_offset = q_offset; p.per_qhead = per_qhead;
   p.lse_dtype = lse_dtype; p.RW = 4; p.scale = sm_scale; p.dots = nullptr; p.q_offsets = q_offsets;
+  p.weights = weights; p.softmax1 = softmax1;
   const size_t need = hils_topk_fwd_workspace_bytes(B, 1, N, h_kv, G, D, dtype);
   if (workspace && need > 0 && workspace_bytes >= need && (int64_t)B * h_kv <= 65535) p.dots = static_cast<float*>(workspace);
   return (dtype != HILS_BF16) ? launch_topk_decode<float, 0>(p, st)

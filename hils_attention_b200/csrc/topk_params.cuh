@@ -11,6 +11,9 @@ struct TopkParams {
   int RW;
   float scale;
   float* dots;   // decode, bf16: raw q.k' of every candidate, written by the streaming kernel (or null)
+  // decode kernels only: the inter-chunk softmax of the step fused behind the selection.  weights (B, L, h_kv*G, K+1(+1))
+  // in the element type, or null: softmax over [scores + bias of the selected chunks, lse_swa(, 0 when softmax1)]
+  void* weights; int softmax1;
   const int32_t* q_offsets;   // decode kernels only: position of query row 0 of each batch entry (null: q_offset for all)
 };
 
