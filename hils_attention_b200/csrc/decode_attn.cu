@@ -33,13 +33,20 @@ struct DecodeParams {
 // Set when a page table holds an id outside the pool or a chunk past the table's width; the access is skipped.
 __device__ int g_paged_status = 0;
 
-__device__ __forceinline__ int seq_tokens(const DecodeParams& p, int b) { return p.lens ? p.lens[b] + p.len_add : p.T; }
+template <bool PG>
+__device__ __forceinline__ int seq_tokens(const DecodeParams& p, int b) {
+  if constexpr (PG) return p.lens[b] + p.len_add;
+  else return p.T;
+}
 
 // Row `tok` of sequence b (holding T tokens), kv-head h.  Paged: rows that follow it in the same chunk are contiguous
 // at the usual stride h_kv * D; a run of rows must not leave its chunk.  Null when the page table is inconsistent.
-template <typename T>
-__device__ __forceinline__ const T* kv_rows_at(const DecodeParams& p, const void* base, int b, int T_b, int tok, int h) {
-  if (p.pages) {
+// `seq0` is row 0 of (sequence b, head h) in the token-major store; the paged kernels do not use it.  The two forms are
+// separate instantiations (PG), so the kernels over the token-major store carry none of the table look-ups.
+template <typename T, bool PG>
+__device__ __forceinline__ const T* kv_rows_at(const DecodeParams& p, const void* base, const T* seq0, int64_t rs, int b,
+                                               int tok, int h) {
+  if constexpr (PG) {
     const int c = tok / p.S;
     const int pg = (c < p.page_stride) ? p.pages[(int64_t)b * p.page_stride + c] : -1;
     if ((unsigned)pg >= (unsigned)p.num_pages) {
@@ -47,8 +54,9 @@ __device__ __forceinline__ const T* kv_rows_at(const DecodeParams& p, const void
       return nullptr;
     }
     return static_cast<const T*>(base) + (((int64_t)pg * p.S + (tok - c * p.S)) * p.h_kv + h) * p.D;
+  } else {
+    return seq0 + (int64_t)tok * rs;
   }
-  return static_cast<const T*>(base) + (((int64_t)b * T_b + tok) * p.h_kv + h) * p.D;
 }
 
 // scores of `n` consecutive key rows (row stride rs elements) against the G query rows in q_s:
@@ -128,7 +136,7 @@ __device__ __forceinline__ void pv_rows(const float* p_s, int pstride, const T* 
 }
 
 // ---- sparse chunk attention, decode shape: D = 32 * PER columns, keys per chunk S <= 64 -------------
-template <typename T, int PER>
+template <typename T, int PER, bool PG>
 __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_kernel(DecodeParams p) {
   constexpr int D = 32 * PER, KPER = D / 16;
   extern __shared__ __align__(16) float smem[];
@@ -144,7 +152,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_kernel(DecodePar
   __syncthreads();
   const int32_t* ids = p.idx + (((int64_t)b * p.L + l) * p.h_kv + h) * p.K;
   const T* wts = static_cast<const T*>(p.w) + row0 * p.num_weights;
-  const int T_b = seq_tokens(p, b);
+  const int T_b = seq_tokens<PG>(p, b);
   const int nchunk = T_b / p.S;
   int nvalid = 0;
   while (nvalid < p.K && ids[nvalid] >= 0) ++nvalid;
@@ -155,12 +163,16 @@ __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_kernel(DecodePar
     for (int e = 0; e < PER; ++e) acc[g][e] = 0.f;
   float* pw = p_s + warp * G * 64;
   const int64_t rs = (int64_t)p.h_kv * D;
+  const T* kb0 = static_cast<const T*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
+  const T* vb0 = static_cast<const T*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
   for (int kk = warp; kk < nvalid; kk += kDecWarps) {
     const int c = ids[kk];
     if (c >= nchunk) continue;
-    const T* kb = kv_rows_at<T>(p, p.k, b, T_b, c * p.S, h);
-    const T* vb = kv_rows_at<T>(p, p.v, b, T_b, c * p.S, h);
-    if (!kb || !vb) continue;
+    const T* kb = kv_rows_at<T, PG>(p, p.k, kb0, rs, b, c * p.S, h);
+    const T* vb = kv_rows_at<T, PG>(p, p.v, vb0, rs, b, c * p.S, h);
+    if constexpr (PG) {
+      if (!kb || !vb) continue;
+    }
     __syncwarp();
     score_rows<T, KPER>(q_s, kb, rs, p.S, G, D, pw, 64, lane);
     __syncwarp();
@@ -200,7 +212,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_kernel(DecodePar
 }
 
 // ---- sliding-window branch, decode shape ------------------------------------------------------------
-template <typename T, int PER>
+template <typename T, int PER, bool PG>
 __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams p) {
   constexpr int D = 32 * PER, KPER = D / 16;
   extern __shared__ __align__(16) float smem[];
@@ -215,7 +227,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams
   const T* q = static_cast<const T*>(p.q) + row0 * D;
   for (int x = tid; x < G * D; x += kDecWarps * 32) q_s[x] = to_f(q[x]);
   __syncthreads();
-  const int T_b = seq_tokens(p, b);
+  const int T_b = seq_tokens<PG>(p, b);
   const int t = p.kv_start + (T_b - p.L) + i;
   int start = t - p.W + 1;
   if (p.expand) start = floor_div(start, p.S) * p.S;
@@ -229,12 +241,16 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams
   }
   float* pw = p_s + warp * G * 64;
   const int64_t rs = (int64_t)p.h_kv * D;
+  const T* kb0 = static_cast<const T*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
+  const T* vb0 = static_cast<const T*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
   // paged: lo is a multiple of S = 64 (the window's left edge is snapped to its chunk), so a step stays in one page
   for (int j0 = lo + warp * 64; j0 <= hi; j0 += kDecWarps * 64) {   // 64 keys per warp step
     const int n = min(64, hi - j0 + 1);
-    const T* kb = kv_rows_at<T>(p, p.k, b, T_b, j0, h);
-    const T* vb = kv_rows_at<T>(p, p.v, b, T_b, j0, h);
-    if (!kb || !vb) continue;
+    const T* kb = kv_rows_at<T, PG>(p, p.k, kb0, rs, b, j0, h);
+    const T* vb = kv_rows_at<T, PG>(p, p.v, vb0, rs, b, j0, h);
+    if constexpr (PG) {
+      if (!kb || !vb) continue;
+    }
     __syncwarp();
     score_rows<T, KPER>(q_s, kb, rs, n, G, D, pw, 64, lane);
     __syncwarp();
@@ -298,7 +314,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams
 // global memory (mma_rows.cuh): no shared-memory staging, no barrier.  P.V runs on the CUDA cores with
 // 16-byte loads: D/8 lanes cover one value row, 32/(D/8) rows per instruction, eight loads in flight.
 // =================================================================================================
-template <int NK, int GM>
+template <int NK, int GM, bool PG>
 __global__ void __launch_bounds__(kDecWarps * 32, 2) sparse_decode_bf16_kernel(DecodeParams p) {
   constexpr int D = NK * 16, LPR = 2 * NK;
   extern __shared__ __align__(16) float smem[];
@@ -316,7 +332,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) sparse_decode_bf16_kernel(D
   make_q_frags<NK>(q_s, lane, af, [G](int r) { return r < G ? r : -1; });
   const int32_t* ids = p.idx + (((int64_t)b * p.L + l) * p.h_kv + h) * p.K;
   const bf16* wts = static_cast<const bf16*>(p.w) + row0 * p.num_weights;
-  const int T_b = seq_tokens(p, b);
+  const int T_b = seq_tokens<PG>(p, b);
   const int nchunk = T_b / p.S;
   int nvalid = p.K;                                   // ids are valid up to the first negative one
   for (int k0 = 0; k0 < p.K; k0 += 32) {
@@ -331,12 +347,16 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) sparse_decode_bf16_kernel(D
     for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
   float* pw = p_s + warp * G * 64;
   const int64_t rs = (int64_t)p.h_kv * D;
+  const bf16* kb0 = static_cast<const bf16*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
+  const bf16* vb0 = static_cast<const bf16*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
   for (int kk = warp; kk < nvalid; kk += kDecWarps) {
     const int c = ids[kk];
     if (c >= nchunk) continue;
-    const bf16* kb = kv_rows_at<bf16>(p, p.k, b, T_b, c * p.S, h);
-    const bf16* vb = kv_rows_at<bf16>(p, p.v, b, T_b, c * p.S, h);
-    if (!kb || !vb) continue;
+    const bf16* kb = kv_rows_at<bf16, PG>(p, p.k, kb0, rs, b, c * p.S, h);
+    const bf16* vb = kv_rows_at<bf16, PG>(p, p.v, vb0, rs, b, c * p.S, h);
+    if constexpr (PG) {
+      if (!kb || !vb) continue;
+    }
     __syncwarp();
     score_rows_mma<NK>(af, kb, rs, p.S, G, pw, 64, lane);
     __syncwarp();
@@ -379,7 +399,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) sparse_decode_bf16_kernel(D
 
 constexpr int kSwaDecTile = 32;      // keys per warp step
 
-template <int NK, int GM>
+template <int NK, int GM, bool PG>
 __global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(DecodeParams p) {
   constexpr int D = NK * 16, LPR = 2 * NK;
   extern __shared__ __align__(16) float smem[];
@@ -396,7 +416,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(Deco
   __syncthreads();
   uint32_t af[NK][4];
   make_q_frags<NK>(q_s, lane, af, [G](int r) { return r < G ? r : -1; });
-  const int T_b = seq_tokens(p, b);
+  const int T_b = seq_tokens<PG>(p, b);
   const int t = p.kv_start + (T_b - p.L) + i;
   int start = t - p.W + 1;
   if (p.expand) start = floor_div(start, p.S) * p.S;
@@ -410,12 +430,16 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(Deco
   }
   float* pw = p_s + warp * G * 64;
   const int64_t rs = (int64_t)p.h_kv * D;
+  const bf16* kb0 = static_cast<const bf16*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
+  const bf16* vb0 = static_cast<const bf16*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
   // paged: lo is a multiple of S = 64 and the step is 32 keys, so a step stays in one page
   for (int j0 = lo + warp * kSwaDecTile; j0 <= hi; j0 += kDecWarps * kSwaDecTile) {
     const int n = min(kSwaDecTile, hi - j0 + 1);
-    const bf16* kb = kv_rows_at<bf16>(p, p.k, b, T_b, j0, h);
-    const bf16* vb = kv_rows_at<bf16>(p, p.v, b, T_b, j0, h);
-    if (!kb || !vb) continue;
+    const bf16* kb = kv_rows_at<bf16, PG>(p, p.k, kb0, rs, b, j0, h);
+    const bf16* vb = kv_rows_at<bf16, PG>(p, p.v, vb0, rs, b, j0, h);
+    if constexpr (PG) {
+      if (!kb || !vb) continue;
+    }
     __syncwarp();
     score_rows_mma<NK>(af, kb, rs, n, G, pw, 64, lane);
     __syncwarp();
@@ -473,15 +497,21 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(Deco
   }
 }
 
+template <int NK, int GM, bool PG>
+static void launch_decode_bf16_pg(const DecodeParams& p, bool swa, dim3 grid, size_t smem, cudaStream_t st) {
+  if (swa) {
+    cudaFuncSetAttribute(swa_decode_bf16_kernel<NK, GM, PG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    swa_decode_bf16_kernel<NK, GM, PG><<<grid, kDecWarps * 32, smem, st>>>(p);
+  } else {
+    cudaFuncSetAttribute(sparse_decode_bf16_kernel<NK, GM, PG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sparse_decode_bf16_kernel<NK, GM, PG><<<grid, kDecWarps * 32, smem, st>>>(p);
+  }
+}
+
 template <int NK, int GM>
 static void launch_decode_bf16_g(const DecodeParams& p, bool swa, dim3 grid, size_t smem, cudaStream_t st) {
-  if (swa) {
-    cudaFuncSetAttribute(swa_decode_bf16_kernel<NK, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    swa_decode_bf16_kernel<NK, GM><<<grid, kDecWarps * 32, smem, st>>>(p);
-  } else {
-    cudaFuncSetAttribute(sparse_decode_bf16_kernel<NK, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sparse_decode_bf16_kernel<NK, GM><<<grid, kDecWarps * 32, smem, st>>>(p);
-  }
+  if (p.pages) launch_decode_bf16_pg<NK, GM, true>(p, swa, grid, smem, st);
+  else launch_decode_bf16_pg<NK, GM, false>(p, swa, grid, smem, st);
 }
 
 template <int NK>
@@ -504,10 +534,15 @@ static int launch_decode(const DecodeParams& p, bool swa, cudaStream_t st) {
     HILS_LAUNCH_CHECK(swa ? "swa_fwd (decode)" : "sparse_attn_fwd (decode)");
     return HILS_OK;
   }
-#define HILS_DEC_LAUNCH(KERNEL, PER)                                                              \
-  do {                                                                                            \
-    cudaFuncSetAttribute(KERNEL<T, PER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    KERNEL<T, PER><<<grid, kDecWarps * 32, smem, st>>>(p);                                        \
+#define HILS_DEC_LAUNCH(KERNEL, PER)                                                                       \
+  do {                                                                                                     \
+    if (p.pages) {                                                                                         \
+      cudaFuncSetAttribute(KERNEL<T, PER, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+      KERNEL<T, PER, true><<<grid, kDecWarps * 32, smem, st>>>(p);                                         \
+    } else {                                                                                               \
+      cudaFuncSetAttribute(KERNEL<T, PER, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      KERNEL<T, PER, false><<<grid, kDecWarps * 32, smem, st>>>(p);                                        \
+    }                                                                                                      \
   } while (0)
   if (swa) {
     if (p.D == 128) HILS_DEC_LAUNCH(swa_decode_kernel, 4); else HILS_DEC_LAUNCH(swa_decode_kernel, 2);
