@@ -41,22 +41,27 @@ __device__ __forceinline__ int seq_tokens(const DecodeParams& p, int b) {
 
 // Row `tok` of sequence b (holding T tokens), kv-head h.  Paged: rows that follow it in the same chunk are contiguous
 // at the usual stride h_kv * D; a run of rows must not leave its chunk.  Null when the page table is inconsistent.
-// `seq0` is row 0 of (sequence b, head h) in the token-major store; the paged kernels do not use it.  The two forms are
-// separate instantiations (PG), so the kernels over the token-major store carry none of the table look-ups.
+// Key and value rows `tok` of (sequence b, head h): k0 / v0 are row 0 of that (sequence, head) in the token-major store;
+// the paged kernels look the chunk's page up once for both.  The two forms are separate instantiations (PG), so the
+// kernels over the token-major store carry none of the table look-ups.  False when the page table is inconsistent.
 template <typename T, bool PG>
-__device__ __forceinline__ const T* kv_rows_at(const DecodeParams& p, const void* base, const T* seq0, int64_t rs, int b,
-                                               int tok, int h) {
+__device__ __forceinline__ bool kv_rows_at(const DecodeParams& p, const T* k0, const T* v0, int64_t rs, int b, int tok, int h,
+                                           const T*& kb, const T*& vb) {
   if constexpr (PG) {
     const int c = tok / p.S;
     const int pg = (c < p.page_stride) ? p.pages[(int64_t)b * p.page_stride + c] : -1;
     if ((unsigned)pg >= (unsigned)p.num_pages) {
       atomicExch(&g_paged_status, 8000000 + (c < p.page_stride ? 1 : 2));
-      return nullptr;
+      return false;
     }
-    return static_cast<const T*>(base) + (((int64_t)pg * p.S + (tok - c * p.S)) * p.h_kv + h) * p.D;
+    const int64_t off = (((int64_t)pg * p.S + (tok - c * p.S)) * p.h_kv + h) * p.D;
+    kb = static_cast<const T*>(p.k) + off;
+    vb = static_cast<const T*>(p.v) + off;
   } else {
-    return seq0 + (int64_t)tok * rs;
+    kb = k0 + (int64_t)tok * rs;
+    vb = v0 + (int64_t)tok * rs;
   }
+  return true;
 }
 
 // scores of `n` consecutive key rows (row stride rs elements) against the G query rows in q_s:
@@ -168,11 +173,9 @@ __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_kernel(DecodePar
   for (int kk = warp; kk < nvalid; kk += kDecWarps) {
     const int c = ids[kk];
     if (c >= nchunk) continue;
-    const T* kb = kv_rows_at<T, PG>(p, p.k, kb0, rs, b, c * p.S, h);
-    const T* vb = kv_rows_at<T, PG>(p, p.v, vb0, rs, b, c * p.S, h);
-    if constexpr (PG) {
-      if (!kb || !vb) continue;
-    }
+    const T* kb;
+    const T* vb;
+    if (!kv_rows_at<T, PG>(p, kb0, vb0, rs, b, c * p.S, h, kb, vb)) continue;
     __syncwarp();
     score_rows<T, KPER>(q_s, kb, rs, p.S, G, D, pw, 64, lane);
     __syncwarp();
@@ -246,11 +249,9 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams
   // paged: lo is a multiple of S = 64 (the window's left edge is snapped to its chunk), so a step stays in one page
   for (int j0 = lo + warp * 64; j0 <= hi; j0 += kDecWarps * 64) {   // 64 keys per warp step
     const int n = min(64, hi - j0 + 1);
-    const T* kb = kv_rows_at<T, PG>(p, p.k, kb0, rs, b, j0, h);
-    const T* vb = kv_rows_at<T, PG>(p, p.v, vb0, rs, b, j0, h);
-    if constexpr (PG) {
-      if (!kb || !vb) continue;
-    }
+    const T* kb;
+    const T* vb;
+    if (!kv_rows_at<T, PG>(p, kb0, vb0, rs, b, j0, h, kb, vb)) continue;
     __syncwarp();
     score_rows<T, KPER>(q_s, kb, rs, n, G, D, pw, 64, lane);
     __syncwarp();
@@ -352,11 +353,9 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) sparse_decode_bf16_kernel(D
   for (int kk = warp; kk < nvalid; kk += kDecWarps) {
     const int c = ids[kk];
     if (c >= nchunk) continue;
-    const bf16* kb = kv_rows_at<bf16, PG>(p, p.k, kb0, rs, b, c * p.S, h);
-    const bf16* vb = kv_rows_at<bf16, PG>(p, p.v, vb0, rs, b, c * p.S, h);
-    if constexpr (PG) {
-      if (!kb || !vb) continue;
-    }
+    const bf16* kb;
+    const bf16* vb;
+    if (!kv_rows_at<bf16, PG>(p, kb0, vb0, rs, b, c * p.S, h, kb, vb)) continue;
     __syncwarp();
     score_rows_mma<NK>(af, kb, rs, p.S, G, pw, 64, lane);
     __syncwarp();
@@ -399,20 +398,22 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) sparse_decode_bf16_kernel(D
 
 constexpr int kSwaDecTile = 32;      // keys per warp step
 
-template <int NK, int GM, bool PG>
-__global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(DecodeParams p) {
+// NW warps per CTA: the window is at most (W + S) / 32 steps of 32 keys, and 18 steps (W = 512) split evenly over 6 warps
+// but 3 + 2 over 8.
+template <int NK, int GM, bool PG, int NW>
+__global__ void __launch_bounds__(NW * 32, NW == 6 ? 3 : 2) swa_decode_bf16_kernel(DecodeParams p) {
   constexpr int D = NK * 16, LPR = 2 * NK;
   extern __shared__ __align__(16) float smem[];
   const int G = p.h_q / p.h_kv;
   float* q_s = smem;                                  // [G][D]
   float* p_s = q_s + G * D;                           // [warps][G][64]
-  float* o_s = p_s + kDecWarps * G * 64;              // [warps][G][D]
-  float* ml_s = o_s + kDecWarps * G * D;              // [warps][G][2]  running max, sum
+  float* o_s = p_s + NW * G * 64;              // [warps][G][D]
+  float* ml_s = o_s + NW * G * D;              // [warps][G][2]  running max, sum
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int h = blockIdx.x, b = blockIdx.y, i = blockIdx.z;
   const int64_t row0 = (((int64_t)b * p.L + i) * p.h_q + h * G);
   const bf16* q = static_cast<const bf16*>(p.q) + row0 * D;
-  for (int x = tid; x < G * D; x += kDecWarps * 32) q_s[x] = to_f(q[x]);
+  for (int x = tid; x < G * D; x += NW * 32) q_s[x] = to_f(q[x]);
   __syncthreads();
   uint32_t af[NK][4];
   make_q_frags<NK>(q_s, lane, af, [G](int r) { return r < G ? r : -1; });
@@ -433,13 +434,11 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(Deco
   const bf16* kb0 = static_cast<const bf16*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
   const bf16* vb0 = static_cast<const bf16*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
   // paged: lo is a multiple of S = 64 and the step is 32 keys, so a step stays in one page
-  for (int j0 = lo + warp * kSwaDecTile; j0 <= hi; j0 += kDecWarps * kSwaDecTile) {
+  for (int j0 = lo + warp * kSwaDecTile; j0 <= hi; j0 += NW * kSwaDecTile) {
     const int n = min(kSwaDecTile, hi - j0 + 1);
-    const bf16* kb = kv_rows_at<bf16, PG>(p, p.k, kb0, rs, b, j0, h);
-    const bf16* vb = kv_rows_at<bf16, PG>(p, p.v, vb0, rs, b, j0, h);
-    if constexpr (PG) {
-      if (!kb || !vb) continue;
-    }
+    const bf16* kb;
+    const bf16* vb;
+    if (!kv_rows_at<bf16, PG>(p, kb0, vb0, rs, b, j0, h, kb, vb)) continue;
     __syncwarp();
     score_rows_mma<NK>(af, kb, rs, n, G, pw, 64, lane);
     __syncwarp();
@@ -476,13 +475,13 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(Deco
     }
   __syncthreads();
   bf16* o = static_cast<bf16*>(p.o) + row0 * D;
-  for (int x = tid; x < G * D; x += kDecWarps * 32) {
+  for (int x = tid; x < G * D; x += NW * 32) {
     const int g = x / D;
     float mm = -CUDART_INF_F;
-    for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, ml_s[(w * G + g) * 2]);
+    for (int w = 0; w < NW; ++w) mm = fmaxf(mm, ml_s[(w * G + g) * 2]);
     float tot = 0.f, sacc = 0.f;
     if (mm > -CUDART_INF_F)
-      for (int w = 0; w < kDecWarps; ++w) {
+      for (int w = 0; w < NW; ++w) {
         const float mw = ml_s[(w * G + g) * 2];
         const float c = (mw > -CUDART_INF_F) ? expf(mw - mm) : 0.f;
         tot += ml_s[(w * G + g) * 2 + 1] * c;
@@ -500,8 +499,15 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) swa_decode_bf16_kernel(Deco
 template <int NK, int GM, bool PG>
 static void launch_decode_bf16_pg(const DecodeParams& p, bool swa, dim3 grid, size_t smem, cudaStream_t st) {
   if (swa) {
-    cudaFuncSetAttribute(swa_decode_bf16_kernel<NK, GM, PG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    swa_decode_bf16_kernel<NK, GM, PG><<<grid, kDecWarps * 32, smem, st>>>(p);
+    // warps per CTA that leave the fewest idle warp steps
+    const int nstep = (p.W + p.S + kSwaDecTile - 1) / kSwaDecTile;
+    if ((nstep + 5) / 6 * 6 < (nstep + 7) / 8 * 8) {
+      cudaFuncSetAttribute(swa_decode_bf16_kernel<NK, GM, PG, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      swa_decode_bf16_kernel<NK, GM, PG, 6><<<grid, 6 * 32, smem, st>>>(p);
+    } else {
+      cudaFuncSetAttribute(swa_decode_bf16_kernel<NK, GM, PG, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      swa_decode_bf16_kernel<NK, GM, PG, 8><<<grid, 8 * 32, smem, st>>>(p);
+    }
   } else {
     cudaFuncSetAttribute(sparse_decode_bf16_kernel<NK, GM, PG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     sparse_decode_bf16_kernel<NK, GM, PG><<<grid, kDecWarps * 32, smem, st>>>(p);
