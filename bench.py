@@ -659,16 +659,16 @@ def run_decode_paged(args, name, ds, steps, warmup):
     P = store.k_pages.shape[1]
     for p0 in range(0, P, 1024):                                    # fill in slices: no second copy of the pool
         n = min(1024, P - p0)
-        off = torch.randn((n, 1, hk, D), generator=g, device=dev) * 0.5
-        store.k_pages[0, p0:p0 + n] = (torch.randn((n, S, hk, D), generator=g, device=dev) + off).to(dtype)
-        store.v_pages[0, p0:p0 + n] = torch.randn((n, S, hk, D), generator=g, device=dev).to(dtype)
+        off = torch.randn((n, hk, 1, D), generator=g, device=dev) * 0.5
+        store.k_pages[0, p0:p0 + n] = (torch.randn((n, hk, S, D), generator=g, device=dev) + off).to(dtype)
+        store.v_pages[0, p0:p0 + n] = torch.randn((n, hk, S, D), generator=g, device=dev).to(dtype)
     with torch.no_grad():
         for b in range(B):
             slot = store.allocate(lens0[b])
             N = lens0[b] // S                                        # pooled chunk keys of the cached prefix
             ids = torch.tensor(store.pages_of(slot)[:N], dtype=torch.long, device=dev)
             mu = torch.randn((1, N, hq, D), generator=g, device=dev).to(dtype)
-            lk, pb = hb.chunk_attn_pool(mu, store.k_pages[0].index_select(0, ids).unsqueeze(0))
+            lk, pb = hb.chunk_attn_pool(mu, store.k_pages[0].index_select(0, ids).transpose(1, 2).unsqueeze(0).contiguous())
             store.lmk_k[0, slot, :N].copy_(lk[0])
             store.prior_b[0, slot, :N].copy_(pb[0])
             del ids, mu, lk, pb

@@ -20,8 +20,10 @@ struct DecodeParams {
   int B, L, T, h_q, h_kv, D, K, num_weights, S, mask_last;       // sparse
   int W, mask_lmk, expand, kv_start;                              // sliding window
   float scale;
-  // Paged store (pages != null): K/V are a pool of pages of S tokens, (num_pages, S, h_kv, D); chunk c of sequence b
-  // lives in page pages[b * page_stride + c]; sequence b holds lens[b] + len_add tokens (T is ignored).
+  // Paged store (pages != null): K/V are a pool of pages of S tokens, (num_pages, h_kv, S, D) - inside a page the rows
+  // of one head are contiguous, so a chunk of one head is one 16 KB run (D = 128) instead of 64 rows h_kv * D apart;
+  // chunk c of sequence b lives in page pages[b * page_stride + c]; sequence b holds lens[b] + len_add tokens (T is
+  // ignored).  The paged kernels walk rows with stride D.
   const int32_t* pages; const int32_t* lens;
   int page_stride, num_pages, len_add;
   // Decode step fusions.  Window kernel: lse_act (or null) receives the log-sum-exp again, rounded to the activation
@@ -54,7 +56,7 @@ __device__ __forceinline__ bool kv_rows_at(const DecodeParams& p, const T* k0, c
       atomicExch(&g_paged_status, 8000000 + (c < p.page_stride ? 1 : 2));
       return false;
     }
-    const int64_t off = (((int64_t)pg * p.S + (tok - c * p.S)) * p.h_kv + h) * p.D;
+    const int64_t off = (((int64_t)pg * p.h_kv + h) * p.S + (tok - c * p.S)) * p.D;
     kb = static_cast<const T*>(p.k) + off;
     vb = static_cast<const T*>(p.v) + off;
   } else {
@@ -167,7 +169,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) sparse_decode_kernel(DecodePar
 #pragma unroll
     for (int e = 0; e < PER; ++e) acc[g][e] = 0.f;
   float* pw = p_s + warp * G * 64;
-  const int64_t rs = (int64_t)p.h_kv * D;
+  const int64_t rs = PG ? (int64_t)D : (int64_t)p.h_kv * D;
   const T* kb0 = static_cast<const T*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
   const T* vb0 = static_cast<const T*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
   for (int kk = warp; kk < nvalid; kk += kDecWarps) {
@@ -243,7 +245,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) swa_decode_kernel(DecodeParams
     for (int e = 0; e < PER; ++e) acc[g][e] = 0.f;
   }
   float* pw = p_s + warp * G * 64;
-  const int64_t rs = (int64_t)p.h_kv * D;
+  const int64_t rs = PG ? (int64_t)D : (int64_t)p.h_kv * D;
   const T* kb0 = static_cast<const T*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
   const T* vb0 = static_cast<const T*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
   // paged: lo is a multiple of S = 64 (the window's left edge is snapped to its chunk), so a step stays in one page
@@ -347,7 +349,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) sparse_decode_bf16_kernel(D
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
   float* pw = p_s + warp * G * 64;
-  const int64_t rs = (int64_t)p.h_kv * D;
+  const int64_t rs = PG ? (int64_t)D : (int64_t)p.h_kv * D;
   const bf16* kb0 = static_cast<const bf16*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
   const bf16* vb0 = static_cast<const bf16*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
   for (int kk = warp; kk < nvalid; kk += kDecWarps) {
@@ -430,7 +432,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 6 ? 3 : 2) swa_decode_bf16_kern
     for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
   }
   float* pw = p_s + warp * G * 64;
-  const int64_t rs = (int64_t)p.h_kv * D;
+  const int64_t rs = PG ? (int64_t)D : (int64_t)p.h_kv * D;
   const bf16* kb0 = static_cast<const bf16*>(p.k) + ((int64_t)b * p.T * p.h_kv + h) * D;
   const bf16* vb0 = static_cast<const bf16*>(p.v) + ((int64_t)b * p.T * p.h_kv + h) * D;
   // paged: lo is a multiple of S = 64 and the step is 32 keys, so a step stays in one page
@@ -615,7 +617,7 @@ int swa_decode_launch(const void* q, const void* k, const void* v, void* o, floa
 }
 
 // One new query row per sequence against a paged store: sequence b holds lens[b] + len_add tokens, chunk c of it lives in
-// page pages[b * page_stride + c] of the pools k_pages / v_pages (num_pages, 64, h_kv, D).  The page is the chunk (S = 64)
+// page pages[b * page_stride + c] of the pools k_pages / v_pages (num_pages, h_kv, 64, D).  The page is the chunk (S = 64)
 // and the window's left edge is snapped to its chunk, so no run of rows a warp reads crosses a page.
 int sparse_decode_paged_launch(const void* q, const void* k_pages, const void* v_pages, const void* w, const int32_t* idx,
                                void* o, const int32_t* pages, const int32_t* lens, int page_stride, int num_pages,
@@ -653,11 +655,12 @@ int swa_decode_paged_launch(const void* q, const void* k_pages, const void* v_pa
                          st, &pa, lse_act);
 }
 
-// The new token of every sequence goes to row lens[b] % S of page pages[b * page_stride + lens[b] / S].
+// The new token of every sequence goes to row lens[b] % S (of every head) of page pages[b * page_stride + lens[b] / S].
 template <typename T>
 __global__ void paged_append_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new, T* __restrict__ k_pages,
                                     T* __restrict__ v_pages, const int32_t* __restrict__ pages,
-                                    const int32_t* __restrict__ lens, int page_stride, int num_pages, int S, int row_elems) {
+                                    const int32_t* __restrict__ lens, int page_stride, int num_pages, int S, int row_elems,
+                                    int D) {
   const int b = blockIdx.x;
   const int len = lens[b], c = len / S;
   const int pg = (len >= 0 && c < page_stride) ? pages[(int64_t)b * page_stride + c] : -1;
@@ -665,14 +668,16 @@ __global__ void paged_append_kernel(const T* __restrict__ k_new, const T* __rest
     if (threadIdx.x == 0) atomicExch(&g_paged_status, 8000003);
     return;
   }
-  const int64_t dst = ((int64_t)pg * S + (len - c * S)) * row_elems, src = (int64_t)b * row_elems;
-  for (int i = threadIdx.x * 4; i < row_elems; i += blockDim.x * 4) {     // row_elems = h_kv * D, a multiple of 4
+  const int64_t page0 = (int64_t)pg * S * row_elems + (int64_t)(len - c * S) * D, src = (int64_t)b * row_elems;
+  for (int i = threadIdx.x * 4; i < row_elems; i += blockDim.x * 4) {     // row_elems = h_kv * D; D is a multiple of 4
+    const int h = i / D;
+    const int64_t dst = page0 + (int64_t)h * S * D + (i - h * D);
     if constexpr (sizeof(T) == 2) {
-      *reinterpret_cast<uint2*>(k_pages + dst + i) = *reinterpret_cast<const uint2*>(k_new + src + i);
-      *reinterpret_cast<uint2*>(v_pages + dst + i) = *reinterpret_cast<const uint2*>(v_new + src + i);
+      *reinterpret_cast<uint2*>(k_pages + dst) = *reinterpret_cast<const uint2*>(k_new + src + i);
+      *reinterpret_cast<uint2*>(v_pages + dst) = *reinterpret_cast<const uint2*>(v_new + src + i);
     } else {
-      *reinterpret_cast<float4*>(k_pages + dst + i) = *reinterpret_cast<const float4*>(k_new + src + i);
-      *reinterpret_cast<float4*>(v_pages + dst + i) = *reinterpret_cast<const float4*>(v_new + src + i);
+      *reinterpret_cast<float4*>(k_pages + dst) = *reinterpret_cast<const float4*>(k_new + src + i);
+      *reinterpret_cast<float4*>(v_pages + dst) = *reinterpret_cast<const float4*>(v_new + src + i);
     }
   }
 }
@@ -685,10 +690,10 @@ int paged_append_launch(const void* k_new, const void* v_new, void* k_pages, voi
   const int threads = std::min(256, std::max(32, (row / 4 + 31) / 32 * 32));
   if (dtype == HILS_BF16)
     paged_append_kernel<bf16><<<B, threads, 0, st>>>((const bf16*)k_new, (const bf16*)v_new, (bf16*)k_pages, (bf16*)v_pages,
-                                                     pages, lens, page_stride, num_pages, S, row);
+                                                     pages, lens, page_stride, num_pages, S, row, D);
   else
     paged_append_kernel<float><<<B, threads, 0, st>>>((const float*)k_new, (const float*)v_new, (float*)k_pages,
-                                                      (float*)v_pages, pages, lens, page_stride, num_pages, S, row);
+                                                      (float*)v_pages, pages, lens, page_stride, num_pages, S, row, D);
   HILS_LAUNCH_CHECK("decode_step_paged (append)");
   return HILS_OK;
 }

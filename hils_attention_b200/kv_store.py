@@ -10,7 +10,8 @@ read the page table and the per-sequence lengths from device memory (ops.decode_
 
 Because a page is a chunk, the sparse branch reads each selected chunk as ONE page, and the sliding
 window (whose left edge is snapped to a chunk boundary) walks whole pages: no kernel gathers rows across
-a page boundary.  The pooled chunk keys and their prior bias - one row per completed chunk, 1/64 of the
+a page boundary.  Inside a page the rows of one head are contiguous, (h_kv, 64, D): the chunk of one head
+is a single 16 KB run (D = 128) where the token-major layout has 64 rows h_kv * D apart.  The pooled chunk keys and their prior bias - one row per completed chunk, 1/64 of the
 store - are kept dense per sequence slot, since the selection streams all of them on every step.
 
 Host-side bookkeeping (free list, tables, lengths) is plain Python and mirrors what sits on the device;
@@ -58,7 +59,7 @@ class PagedKVStore:
     """K/V pages, page tables, lengths and pooled chunk keys of up to `max_seqs` sequences and `num_layers` layers.
 
     Device tensors (all preallocated):
-      k_pages, v_pages (num_layers, num_pages, S, h_kv, D)   the pool; one table serves every layer
+      k_pages, v_pages (num_layers, num_pages, h_kv, S, D)   the pool; one table serves every layer
       page_table       (max_seqs, max_pages) int32            page of chunk c of the sequence in slot b
       lens             (max_seqs) int32                       tokens the sequence in slot b holds
       lmk_k            (num_layers, max_seqs, max_pages, h_lmk, D)   pooled chunk keys
@@ -79,7 +80,7 @@ class PagedKVStore:
         self.pool = PagePool(num_pages)
         dev = torch.device(device)
         self.device, self.dtype = dev, dtype
-        self.k_pages = torch.zeros((num_layers, num_pages, self.S, h_kv, head_dim), dtype=dtype, device=dev)
+        self.k_pages = torch.zeros((num_layers, num_pages, h_kv, self.S, head_dim), dtype=dtype, device=dev)
         self.v_pages = torch.zeros_like(self.k_pages)
         self.page_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32, device=dev)   # 0 = scratch page
         self.lens = torch.zeros((max_seqs,), dtype=torch.int32, device=dev)
@@ -165,11 +166,13 @@ class PagedKVStore:
         full, rem = T // self.S, T % self.S
         if full:
             ids = torch.tensor(pages[:full], dtype=torch.long, device=self.device)
-            self.k_pages[layer].index_copy_(0, ids, k[:full * self.S].reshape(full, self.S, self.h_kv, self.D).to(self.dtype))
-            self.v_pages[layer].index_copy_(0, ids, v[:full * self.S].reshape(full, self.S, self.h_kv, self.D).to(self.dtype))
+            def paged(x):   # (full * S, h, D) -> (full, h, S, D)
+                return x[:full * self.S].reshape(full, self.S, self.h_kv, self.D).transpose(1, 2).to(self.dtype)
+            self.k_pages[layer].index_copy_(0, ids, paged(k))
+            self.v_pages[layer].index_copy_(0, ids, paged(v))
         if rem:
-            self.k_pages[layer, pages[full], :rem].copy_(k[full * self.S:])
-            self.v_pages[layer, pages[full], :rem].copy_(v[full * self.S:])
+            self.k_pages[layer, pages[full], :, :rem].copy_(k[full * self.S:].transpose(0, 1))
+            self.v_pages[layer, pages[full], :, :rem].copy_(v[full * self.S:].transpose(0, 1))
         if lmk_k is not None and full:
             if lmk_k.shape[0] != full:
                 raise ValueError(f"write_prefill: {full} complete chunks but {lmk_k.shape[0]} chunk keys")
@@ -182,8 +185,8 @@ class PagedKVStore:
         T = self._lens[slot]
         n = (T + self.S - 1) // self.S
         ids = torch.tensor(self._tables[slot][:n], dtype=torch.long, device=self.device)
-        k = self.k_pages[layer].index_select(0, ids).reshape(n * self.S, self.h_kv, self.D)[:T]
-        v = self.v_pages[layer].index_select(0, ids).reshape(n * self.S, self.h_kv, self.D)[:T]
+        k = self.k_pages[layer].index_select(0, ids).transpose(1, 2).reshape(n * self.S, self.h_kv, self.D)[:T]
+        v = self.v_pages[layer].index_select(0, ids).transpose(1, 2).reshape(n * self.S, self.h_kv, self.D)[:T]
         return k, v
 
     # ---- the decode step -----------------------------------------------------------------------------
@@ -218,9 +221,9 @@ class PagedKVStore:
         return [b for b in range(self.max_seqs) if self._active[b] and (self._lens[b] + 1) % self.S == 0]
 
     def chunk_keys(self, layer: int, slots: Sequence[int]) -> torch.Tensor:
-        """(n, 64, h_kv, D): the keys of the last chunk of each of `slots`."""
+        """(n, 64, h_kv, D): the keys of the last chunk of each of `slots` (a token-major view of the pages)."""
         ids = torch.tensor([self._tables[b][self._lens[b] // self.S] for b in slots], dtype=torch.long, device=self.device)
-        return self.k_pages[layer].index_select(0, ids)
+        return self.k_pages[layer].index_select(0, ids).transpose(1, 2)
 
     def put_chunk_keys(self, layer: int, slots: Sequence[int], lmk_k: torch.Tensor, prior_b: Optional[torch.Tensor]) -> None:
         """Store the pooled key (n, h_lmk, D) and prior bias (n, h_q) of the chunk each of `slots` is completing."""

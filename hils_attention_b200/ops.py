@@ -477,7 +477,7 @@ def decode_step_paged(q, lmk_q, k_new, v_new, k_pages, v_pages, page_table, lens
     """One decode step of the whole chain over a paged store, for sequences of different lengths
     (models/FlashHiLS/hils_attention.py:512-633 with one new token per sequence; inference only).
 
-    q, lmk_q (B, h_q, D); k_new, v_new (B, h_kv, D); k_pages, v_pages (num_pages, 64, h_kv, D) the pool;
+    q, lmk_q (B, h_q, D); k_new, v_new (B, h_kv, D); k_pages, v_pages (num_pages, h_kv, 64, D) the pool;
     page_table (B, max_pages) int32 and lens (B) int32 on the device: sequence b holds lens[b] tokens, chunk c
     of it lives in page page_table[b, c], and the page of position lens[b] is already in the table; max_len is
     a host-side upper bound of lens.  lmk_k (B, N, h_lmk, D) pooled chunk keys, prior_b (B, N, h_q) fp32 or
@@ -487,7 +487,7 @@ def decode_step_paged(q, lmk_q, k_new, v_new, k_pages, v_pages, page_table, lens
     h_kv = k_new.shape[1]
     N, h_lmk = lmk_k.shape[1], lmk_k.shape[2]
     num_pages = k_pages.shape[0]
-    assert k_pages.shape == v_pages.shape == (num_pages, chunk_size, h_kv, D)
+    assert k_pages.shape == v_pages.shape == (num_pages, h_kv, chunk_size, D)
     assert page_table.dtype == torch.int32 and lens.dtype == torch.int32 and page_table.shape[0] == B == lens.shape[0]
     assert lmk_q.shape == q.shape and k_new.shape == v_new.shape == (B, h_kv, D) and lmk_k.shape[0] == B
     for t in (q, lmk_q, k_new, v_new, k_pages, v_pages, page_table, lens, lmk_k):

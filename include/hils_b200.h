@@ -270,13 +270,15 @@ size_t hils_decode_step_workspace_bytes(int heads_q, int heads_kv, int heads_lmk
  * README.md:255,262), so a selected chunk is one page and the step never gathers across pages.
  * Replaces the growth by torch.cat and the CPU round trip of the reference's cache layer
  * (utils/hils_cache_utils.py:19-23, :45-62): a sequence grows by taking a page from the pool.
- *   k_pages, v_pages (num_pages, 64, h_kv, D): the pool, shared by all sequences;
+ *   k_pages, v_pages (num_pages, h_kv, 64, D): the pool, shared by all sequences; inside a page the 64
+ *   rows of one head are contiguous (one 16 KB run at D = 128), so a selected chunk of a head is read as
+ *   one run and not as 64 rows h_kv*D apart;
  *   page_table (B, page_stride) int32, device: page of chunk c of sequence b (entries past the
  *   sequence's last chunk are not read); lens (B) int32, device: tokens sequence b holds BEFORE this
  *   step; max_len: a host-side upper bound of lens (it sizes the launches; (max_len+1+63)/64 <=
  *   page_stride, and the page for position lens[b] must already be in the table);
- *   q, lmk_q, o (B, h_q, D); k_new, v_new (B, h_kv, D), written to row lens[b] % 64 of page
- *   page_table[b][lens[b] / 64]; lmk_k (B, N, h_lmk, D) pooled chunk keys, row stride N for every
+ *   q, lmk_q, o (B, h_q, D); k_new, v_new (B, h_kv, D), written to row lens[b] % 64 of every head of
+ *   page page_table[b][lens[b] / 64]; lmk_k (B, N, h_lmk, D) pooled chunk keys, row stride N for every
  *   sequence, rows at or past a sequence's selectable chunks are not read; prior_b (B, N, h_q) fp32 or
  *   NULL; indices_out (B, h_kv, K) int32 or NULL.  lens is NOT advanced (a model runs this once per
  *   layer with the same table).  A page id outside [0, num_pages) is skipped and reported through

@@ -145,7 +145,7 @@ def test_a_page_id_outside_the_pool_is_skipped_and_reported():
     hq, hk, D, N = 2, 2, 64, 16
     g = torch.Generator().manual_seed(3)
     mk = lambda *s: torch.randn(*s, generator=g).to(BF).cuda()
-    k_pages, v_pages = mk(8, 64, hk, D), mk(8, 64, hk, D)
+    k_pages, v_pages = mk(8, hk, 64, D), mk(8, hk, 64, D)
     table = torch.tensor([[1, 2, 99, 3] + [0] * 12], dtype=torch.int32, device="cuda")     # chunk 2 points nowhere
     lens = torch.tensor([250], dtype=torch.int32, device="cuda")
     o, _ = ops.decode_step_paged(mk(1, hq, D), mk(1, hq, D), mk(1, hk, D), mk(1, hk, D), k_pages, v_pages, table, lens, 250,
