@@ -147,10 +147,20 @@ struct InvLayout {
   int TT, ntile;
 };
 
+// The staged build (inv_tile_kernel): a CTA of 8 warps owns a tile of 256 tokens and sorts the tile's entries by chunk
+// in shared memory before they leave, so that a chunk's entries of the tile go out as one contiguous run.  It covers
+// one query head per kv head, up to 32 slots per token and chunk counts whose histograms fit shared memory.
+constexpr int kStageWarps = 8, kStageTW = 32, kStageTT = kStageWarps * kStageTW;
+static bool inv_staged(int G, int K, int nchunk) { return G == 1 && K <= 32 && nchunk <= 2048; }
+static size_t inv_staged_smem(int K, int nchunk, bool fill) {
+  // per-warp histograms, tile totals, run offsets (+ the staged entries and weights)
+  return (size_t)(kStageWarps + 2) * nchunk * 4 + 64 + (fill ? (size_t)kStageTT * K * 6 : 0);
+}
+
 static InvLayout inv_layout(int B, int L, int h_kv, int G, int K, int nchunk) {
   InvLayout l;
   int tt = (nchunk + K - 1) / K;              // keeps the per-tile histograms no larger than the list
-  l.TT = max(128, (tt + 31) / 32 * 32);
+  l.TT = inv_staged(G, K, nchunk) ? kStageTT : max(128, (tt + 31) / 32 * 32);
   l.ntile = (L + l.TT - 1) / l.TT;
   const size_t bh = (size_t)B * h_kv;
   auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
@@ -254,20 +264,168 @@ __global__ void __launch_bounds__(32) inv_walk_kernel(const int32_t* __restrict_
   }
 }
 
-// per (b, h, chunk): exclusive prefix of the tile histograms over the tiles (in place) and the chunk's total
-__global__ void __launch_bounds__(256) inv_scan_kernel(uint32_t* __restrict__ cnt, uint32_t* __restrict__ tot, int nchunk, int ntile) {
-  const int c = blockIdx.x * 256 + threadIdx.x;
+// Staged form of the walk for G = 1, K <= 32: one CTA per (token tile of 256, kv head, batch), warp w owns tokens
+// 32w .. 32w+31 of the tile and holds their ids in registers (one token per lane-wide load, lane = slot).
+// kFill = false: the tile's histogram.  kFill = true: per-warp histograms -> each warp's start inside every chunk's run
+// of the tile (warps in token order) -> entries and weights placed in shared memory sorted by chunk, in the order of the
+// plain walk (tokens ascending, slots ascending) -> every chunk's run copied out contiguously.  The plain walk writes
+// every entry and weight to its own address: 4- and 2-byte stores scattered over the (b, h) segment, each a partial
+// 32-byte sector that the memory system has to read, merge and write back.
+template <bool kFill>
+__global__ void __launch_bounds__(32 * kStageWarps) inv_tile_kernel(const int32_t* __restrict__ idx, uint32_t* __restrict__ cnt,
+                                                                   const uint32_t* __restrict__ coff, InvFill f, size_t cap,
+                                                                   int L, int h_kv, int K, int nchunk, int ntile) {
+  extern __shared__ __align__(16) uint8_t inv_smem[];
+  uint32_t* wcnt = reinterpret_cast<uint32_t*>(inv_smem);               // [warps][nchunk]
+  uint32_t* tot_s = wcnt + (size_t)kStageWarps * nchunk;                // [nchunk] entries of the tile per chunk
+  uint32_t* run_s = tot_s + nchunk;                                     // [nchunk] start of the chunk's run in the stage
+  uint32_t* wsum = run_s + nchunk;                                      // [8] + carry
+  int32_t* stage_l = reinterpret_cast<int32_t*>(wsum + 16);             // [256 * K]
+  bf16* stage_w = reinterpret_cast<bf16*>(stage_l + (size_t)kStageTT * K);
+  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t bh = (size_t)b * h_kv + h;
+  for (int i = tid; i < (kFill ? kStageWarps : 1) * nchunk; i += 32 * kStageWarps) wcnt[i] = 0u;
+  __syncthreads();
+  const int t0 = tile * kStageTT + warp * kStageTW, t1 = min(L, t0 + kStageTW);
+  const int32_t* base = idx + (((size_t)b * L) * h_kv + h) * K;
+  const size_t tstride = (size_t)h_kv * K;
+  // ids of the warp's 32 tokens; `take` bit u of lane k: slot k of token t0 + u is an entry
+  int v[kStageTW];
+#pragma unroll
+  for (int u = 0; u < kStageTW; ++u) v[u] = (t0 + u < t1 && lane < K) ? __ldg(base + (size_t)(t0 + u) * tstride + lane) : -1;
+  uint32_t take = 0u;
+  uint32_t* my = kFill ? wcnt + (size_t)warp * nchunk : wcnt;
+#pragma unroll
+  for (int u = 0; u < kStageTW; ++u) {
+    const unsigned neg = __ballot_sync(0xffffffffu, v[u] < 0);          // a row's list ends at its first negative id
+    const bool live = neg == 0u || lane < (__ffs(neg) - 1);
+    if (live && v[u] < nchunk) {
+      take |= 1u << u;
+      atomicAdd(&my[v[u]], 1u);
+    }
+  }
+  __syncthreads();
+  if constexpr (!kFill) {
+    uint32_t* out = cnt + (bh * ntile + tile) * nchunk;
+    for (int c = tid; c < nchunk; c += 32 * kStageWarps) out[c] = wcnt[c];
+  } else {
+  // each warp's start inside the chunk's run, the tile's total per chunk
+  for (int c = tid; c < nchunk; c += 32 * kStageWarps) {
+    uint32_t run = 0u;
+#pragma unroll
+    for (int w = 0; w < kStageWarps; ++w) {
+      const uint32_t x = wcnt[(size_t)w * nchunk + c];
+      wcnt[(size_t)w * nchunk + c] = run;
+      run += x;
+    }
+    tot_s[c] = run;
+  }
+  __syncthreads();
+  // exclusive scan of the totals over the chunks: thread i owns `per` consecutive chunks
+  {
+    const int per = (nchunk + 32 * kStageWarps - 1) / (32 * kStageWarps), c0 = tid * per, c1 = min(nchunk, c0 + per);
+    uint32_t mine = 0u;
+    for (int c = c0; c < c1; ++c) mine += tot_s[c];
+    uint32_t inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t x = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += x;
+    }
+    if (lane == 31) wsum[warp] = inc;
+    __syncthreads();
+    uint32_t run = inc - mine;
+    for (int w = 0; w < warp; ++w) run += wsum[w];
+    for (int c = c0; c < c1; ++c) {
+      run_s[c] = run;
+      run += tot_s[c];
+    }
+  }
+  __syncthreads();
+  // placement in the order of the plain walk
+  const bf16* wbase = f.w + (((size_t)b * L) * h_kv + h) * f.num_weights;       // G = 1: h_q = h_kv
+  const size_t wstride = (size_t)h_kv * f.num_weights;
+  uint32_t* mine_cnt = wcnt + (size_t)warp * nchunk;
+#pragma unroll
+  for (int u0 = 0; u0 < kStageTW; u0 += 8) {
+    bf16 wv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      wv[u] = ((take >> (u0 + u)) & 1u) ? wbase[(size_t)(t0 + u0 + u) * wstride + lane] : __float2bfloat16_rn(0.f);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const bool tk = (take >> (u0 + u)) & 1u;
+      const int id = v[u0 + u];
+      // equal ids inside one token (repeated slots) take consecutive positions in slot order
+      const unsigned peers = __match_any_sync(0xffffffffu, tk ? id : -1 - lane);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      uint32_t pos = 0u;
+      if (tk) pos = run_s[id] + mine_cnt[id] + rank;
+      __syncwarp();
+      if (tk) {
+        stage_l[pos] = ((t0 + u0 + u) << kEntShift) | lane;
+        stage_w[pos] = wv[u];
+        if (rank == __popc(peers) - 1) mine_cnt[id] += (uint32_t)__popc(peers);
+      }
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+  // copy-out: 32 chunks per warp step, one chunk's run at a time
+  int32_t* list = f.list + bh * cap;
+  bf16* wlist = f.wlist + bh * cap;
+  const uint32_t* tile_pre = cnt + (bh * ntile + tile) * nchunk;        // entries of the chunk in the tiles before this one
+  for (int c0 = warp * 32; c0 < nchunk; c0 += 32 * kStageWarps) {
+    const int c = c0 + lane;
+    const uint32_t n_l = c < nchunk ? tot_s[c] : 0u;
+    const uint32_t src_l = c < nchunk ? run_s[c] : 0u;
+    const uint32_t dst_l = (c < nchunk && n_l) ? coff[bh * (nchunk + 1) + c] + tile_pre[c] : 0u;
+    unsigned any = __ballot_sync(0xffffffffu, n_l != 0u);
+    while (any) {
+      const int j = __ffs(any) - 1;
+      any &= any - 1;
+      const uint32_t n = __shfl_sync(0xffffffffu, n_l, j), src = __shfl_sync(0xffffffffu, src_l, j);
+      const uint32_t dst = __shfl_sync(0xffffffffu, dst_l, j);
+      for (uint32_t e = lane; e < n; e += 32) {
+        list[dst + e] = stage_l[src + e];
+        wlist[dst + e] = stage_w[src + e];
+      }
+    }
+  }
+  }
+}
+
+// per (b, h, chunk): exclusive prefix of the tile histograms over the tiles (in place) and the chunk's total.
+// A CTA takes 64 chunks; the tiles are cut into four segments walked by four groups of threads (segment sums first,
+// then the prefixes: the second read of a segment comes from L2), so four times as many loads are in flight as with
+// one thread per chunk.
+constexpr int kScanChunks = 64, kScanSegs = 4;
+__global__ void __launch_bounds__(kScanChunks * kScanSegs) inv_scan_kernel(uint32_t* __restrict__ cnt, uint32_t* __restrict__ tot,
+                                                                         int nchunk, int ntile) {
+  __shared__ uint32_t seg_sum[kScanSegs][kScanChunks];
+  const int cl = threadIdx.x % kScanChunks, seg = threadIdx.x / kScanChunks;
+  const int c = blockIdx.x * kScanChunks + cl;
   const size_t bh = blockIdx.y;
-  if (c >= nchunk) return;
-  uint32_t* p = cnt + bh * ntile * nchunk + c;
-  uint32_t run = 0;
+  const int per = (ntile + kScanSegs - 1) / kScanSegs, ta = min(ntile, seg * per), tb = min(ntile, ta + per);
+  uint32_t* p = cnt + bh * ntile * nchunk + min(c, nchunk - 1);
+  uint32_t s = 0;
+  if (c < nchunk) {
 #pragma unroll 8
-  for (int t = 0; t < ntile; ++t) {
+    for (int t = ta; t < tb; ++t) s += p[(size_t)t * nchunk];
+  }
+  seg_sum[seg][cl] = s;
+  __syncthreads();
+  if (c >= nchunk) return;
+  uint32_t run = 0;
+  for (int i = 0; i < seg; ++i) run += seg_sum[i][cl];
+#pragma unroll 8
+  for (int t = ta; t < tb; ++t) {
     const uint32_t v = p[(size_t)t * nchunk];
     p[(size_t)t * nchunk] = run;
     run += v;
   }
-  tot[bh * nchunk + c] = run;
+  if (seg == kScanSegs - 1) tot[bh * nchunk + c] = run;
 }
 
 // per (b, h): exclusive prefix of the chunk totals, each rounded up to the list alignment
@@ -323,17 +481,28 @@ static int build_inverse_index(const SparseParams& p, void* workspace, InvIndex*
   f.w = static_cast<const bf16*>(p.w);
   f.G = G;
   f.num_weights = p.num_weights;
-  const size_t smem = (size_t)nchunk * 4;
-  if (smem > 48 * 1024) {
-    cudaFuncSetAttribute(inv_walk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaFuncSetAttribute(inv_walk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  }
   dim3 gw(l.ntile, p.h_kv, p.B);
-  inv_walk_kernel<false><<<gw, 32, smem, st>>>(p.idx, cnt, nullptr, f, l.cap, p.L, p.h_kv, p.K, nchunk, l.TT, l.ntile);
-  inv_scan_kernel<<<dim3((nchunk + 255) / 256, p.B * p.h_kv), 256, 0, st>>>(cnt, tot, nchunk, l.ntile);
-  inv_offsets_kernel<<<p.B * p.h_kv, 256, 0, st>>>(tot, coff, nchunk);
-  inv_walk_kernel<true><<<gw, 32, smem, st>>>(p.idx, cnt, coff, f, l.cap, p.L, p.h_kv, p.K, nchunk, l.TT, l.ntile);
-  HILS_LAUNCH_CHECK("sparse_attn inverse index");
+  if (inv_staged(G, p.K, nchunk)) {
+    const size_t smem_c = inv_staged_smem(p.K, nchunk, false), smem_f = inv_staged_smem(p.K, nchunk, true);
+    cudaFuncSetAttribute(inv_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c);
+    cudaFuncSetAttribute(inv_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_f);
+    inv_tile_kernel<false><<<gw, 32 * kStageWarps, smem_c, st>>>(p.idx, cnt, nullptr, f, l.cap, p.L, p.h_kv, p.K, nchunk, l.ntile);
+    inv_scan_kernel<<<dim3((nchunk + kScanChunks - 1) / kScanChunks, p.B * p.h_kv), kScanChunks * kScanSegs, 0, st>>>(cnt, tot, nchunk, l.ntile);
+    inv_offsets_kernel<<<p.B * p.h_kv, 256, 0, st>>>(tot, coff, nchunk);
+    inv_tile_kernel<true><<<gw, 32 * kStageWarps, smem_f, st>>>(p.idx, cnt, coff, f, l.cap, p.L, p.h_kv, p.K, nchunk, l.ntile);
+    HILS_LAUNCH_CHECK("sparse_attn inverse index (staged)");
+  } else {
+    const size_t smem = (size_t)nchunk * 4;
+    if (smem > 48 * 1024) {
+      cudaFuncSetAttribute(inv_walk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaFuncSetAttribute(inv_walk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    inv_walk_kernel<false><<<gw, 32, smem, st>>>(p.idx, cnt, nullptr, f, l.cap, p.L, p.h_kv, p.K, nchunk, l.TT, l.ntile);
+    inv_scan_kernel<<<dim3((nchunk + kScanChunks - 1) / kScanChunks, p.B * p.h_kv), kScanChunks * kScanSegs, 0, st>>>(cnt, tot, nchunk, l.ntile);
+    inv_offsets_kernel<<<p.B * p.h_kv, 256, 0, st>>>(tot, coff, nchunk);
+    inv_walk_kernel<true><<<gw, 32, smem, st>>>(p.idx, cnt, coff, f, l.cap, p.L, p.h_kv, p.K, nchunk, l.TT, l.ntile);
+    HILS_LAUNCH_CHECK("sparse_attn inverse index");
+  }
   ix->list = f.list;
   ix->wlist = f.wlist;
   ix->coff = coff;
