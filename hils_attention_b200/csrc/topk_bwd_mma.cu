@@ -259,6 +259,280 @@ __global__ void __launch_bounds__(256) topk_bwd_mma_kernel(TopkBwdMmaParams p) {
   }
 }
 
+// -------------------------------------------------------------------------------------------------
+// The same two products for several candidate tiles (N > 128) and up to 32 slots per token, software-pipelined.
+// In the kernel above every (row block, tile) pair waits in turn for its key tile, for the ids and for the score
+// gradients (global loads issued when they are needed) and clears the whole dense tile between block-wide barriers.
+// Here a thread keeps the K/4 (id, gradient) pairs of its row in registers for as long as the block is worked on,
+// the key tiles (phase 1) and the query blocks (phase 2) arrive through cp.async in two buffers one step ahead, the
+// ids of the next block are loaded while the current one multiplies, and only the cells a thread scattered are cleared
+// again afterwards.
+// -------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait0() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+constexpr int kPipeSlots = 8;      // (id, gradient) pairs per thread: four threads per row, K <= 32
+
+template <int NK>   // NK = D / 16
+__global__ void __launch_bounds__(256, 2) topk_bwd_pipe_kernel(TopkBwdMmaParams p) {
+  constexpr int D = NK * 16, RS = D + 8, NB = D / 8, CPR = D / 8;
+  constexpr uint32_t kKeyBuf = kBwdTile * RS * 2, kQBuf = kBwdRows * RS * 2;   // bytes
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* ds_s = reinterpret_cast<bf16*>(smem_raw);                // [64][136] score gradients, dense over one tile
+  unsigned char* buf = smem_raw + kBwdRows * kDsStride * 2;      // phase 1: two key tiles; phase 2: two query blocks
+  __shared__ int max_id_s;
+  __shared__ int nt_s[kBwdBlocks];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int members = p.per_qhead ? 1 : p.G;
+  const int hl = blockIdx.y;
+  const int h = p.per_qhead ? hl / p.G : hl, g_fixed = p.per_qhead ? hl % p.G : 0;
+  const int HL = p.per_qhead ? p.h_kv * p.G : p.h_kv;
+  const int64_t b = blockIdx.z;
+  const int n_rows = p.L * members;
+  const int cta_row0 = blockIdx.x * kBwdRows * kBwdBlocks;
+  const int ntile_all = (p.N + kBwdTile - 1) / kBwdTile;
+  const uint32_t ds32 = (uint32_t)__cvta_generic_to_shared(ds_s);
+  const uint32_t buf32 = (uint32_t)__cvta_generic_to_shared(buf);
+  const int KPT = p.K >> 2, srow = tid >> 2, k0 = (tid & 3) * KPT;   // this thread's slots of row srow: k0 .. k0+KPT-1
+
+  auto row_ptrs = [&](int r, int64_t& row_index, int64_t& tok_head) {
+    const int l = r / members, gi = p.per_qhead ? g_fixed : r - l * members;
+    tok_head = (b * p.L + l) * p.h_kv + h;
+    row_index = tok_head * p.G + gi;
+  };
+  auto issue_keys = [&](int c0, int which) {
+    const uint32_t base = buf32 + (uint32_t)which * kKeyBuf;
+    for (int i = tid; i < kBwdTile * CPR; i += 256) {
+      const int row = i / CPR, col = (i - row * CPR) * 8;
+      const uint32_t dst = base + (uint32_t)(row * RS + col) * 2u;
+      if (c0 + row < p.N) cp_async16(dst, p.lmks + ((b * p.N + c0 + row) * HL + hl) * D + col);
+      else *reinterpret_cast<uint4*>(buf + (size_t)which * kKeyBuf + (size_t)(row * RS + col) * 2) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  auto issue_q = [&](int r0, int which) {
+    const uint32_t base = buf32 + (uint32_t)which * kQBuf;
+    for (int i = tid; i < kBwdRows * CPR; i += 256) {
+      const int row = i / CPR, col = (i - row * CPR) * 8;
+      const uint32_t dst = base + (uint32_t)(row * RS + col) * 2u;
+      if (r0 + row < n_rows) {
+        int64_t ri, th;
+        row_ptrs(r0 + row, ri, th);
+        cp_async16(dst, p.q + ri * D + col);
+      } else {
+        *reinterpret_cast<uint4*>(buf + (size_t)which * kQBuf + (size_t)(row * RS + col) * 2) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+  // the thread's (id, gradient) pairs of row r0 + srow; ids outside [0, N) become -1
+  auto load_pairs = [&](int r0, int (&id)[kPipeSlots], bf16 (&g)[kPipeSlots]) {
+#pragma unroll
+    for (int j = 0; j < kPipeSlots; ++j) { id[j] = -1; g[j] = __float2bfloat16_rn(0.f); }
+    if (r0 + srow < n_rows) {
+      int64_t ri, th;
+      row_ptrs(r0 + srow, ri, th);
+      const int32_t* ip = p.ids + th * p.K + k0;
+      const bf16* gp = p.ds + ri * p.K + k0;
+#pragma unroll
+      for (int j = 0; j < kPipeSlots; ++j)
+        if (j < KPT) {
+          const int v = ip[j];
+          id[j] = (v >= 0 && v < p.N) ? v : -1;
+          g[j] = gp[j];
+        }
+    }
+  };
+  auto scatter = [&](int c0, const int (&id)[kPipeSlots], const bf16 (&g)[kPipeSlots]) {
+#pragma unroll
+    for (int j = 0; j < kPipeSlots; ++j)
+      if (id[j] >= c0 && id[j] < c0 + kBwdTile) ds_s[srow * kDsStride + id[j] - c0] = g[j];
+  };
+  auto unscatter = [&](int c0, const int (&id)[kPipeSlots]) {
+#pragma unroll
+    for (int j = 0; j < kPipeSlots; ++j)
+      if (id[j] >= c0 && id[j] < c0 + kBwdTile) ds_s[srow * kDsStride + id[j] - c0] = __float2bfloat16_rn(0.f);
+  };
+  float dk[NB][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dk[nb][e] = 0.f;
+  auto flush_dk = [&](int c0) {
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      const int c = c0 + warp * 16 + (lane >> 2) + hr * 8;
+      if (c < p.N) {
+        float* dst = p.dl + ((b * p.N + c) * HL + hl) * D + (lane & 3) * 2;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          const float2 v = make_float2(dk[nb][2 * hr] * p.scale, dk[nb][2 * hr + 1] * p.scale);
+          if (v.x != 0.f || v.y != 0.f) atomicAdd(reinterpret_cast<float2*>(dst + nb * 8), v);
+        }
+      }
+    }
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dk[nb][e] = 0.f;
+  };
+  auto block_ntile = [&](int r0) -> int {
+    if (tid == 0) max_id_s = -1;
+    __syncthreads();
+    int mx = -1;
+    if (r0 + srow < n_rows) {
+      int64_t ri, th;
+      row_ptrs(r0 + srow, ri, th);
+      for (int k = tid & 3; k < p.K; k += 4) mx = max(mx, p.ids[th * p.K + k]);
+    }
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    if ((tid & 3) == 0 && mx >= 0) atomicMax(&max_id_s, mx);
+    __syncthreads();
+    const int max_id = max_id_s;
+    __syncthreads();
+    return max_id < 0 ? 0 : min(ntile_all, max_id / kBwdTile + 1);
+  };
+  auto mma_dq = [&](float (&dq)[NB / 2][4], int which) {
+    const int mrow = (warp & 3) * 16, nhalf = (warp >> 2) * (D / 2);
+    const uint32_t k32 = buf32 + (uint32_t)which * kKeyBuf;
+    const uint32_t a_addr = ds32 + (uint32_t)((mrow + (lane & 7) + ((lane >> 3) & 1) * 8) * kDsStride + (lane >> 4) * 8) * 2u;
+    const uint32_t b_addr = k32 + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * RS + nhalf + ((lane >> 4) & 1) * 8) * 2u;
+#pragma unroll
+    for (int kk = 0; kk < kBwdTile / 16; ++kk) {
+      uint32_t a[4];
+      ldsm4(a, a_addr + kk * 32);
+#pragma unroll
+      for (int np = 0; np < NB / 4; ++np) {
+        uint32_t bb[4];
+        ldsm4_t(bb, b_addr + (uint32_t)(kk * 16 * RS + np * 16) * 2u);
+        mma16816(dq[2 * np], a, bb[0], bb[1]);
+        mma16816(dq[2 * np + 1], a, bb[2], bb[3]);
+      }
+    }
+  };
+  auto mma_dk = [&](int which) {
+    const int mcol = warp * 16;
+    const uint32_t q32 = buf32 + (uint32_t)which * kQBuf;
+    const uint32_t a_addr = ds32 + (uint32_t)(((lane & 7) + ((lane >> 4) & 1) * 8) * kDsStride + mcol + ((lane >> 3) & 1) * 8) * 2u;
+    const uint32_t b_addr = q32 + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * RS + ((lane >> 4) & 1) * 8) * 2u;
+#pragma unroll
+    for (int kk = 0; kk < kBwdRows / 16; ++kk) {
+      uint32_t a[4];
+      ldsm4_t(a, a_addr + (uint32_t)(kk * 16 * kDsStride) * 2u);
+#pragma unroll
+      for (int np = 0; np < NB / 2; ++np) {
+        uint32_t bb[4];
+        ldsm4_t(bb, b_addr + (uint32_t)(kk * 16 * RS + np * 16) * 2u);
+        mma16816(dk[2 * np], a, bb[0], bb[1]);
+        mma16816(dk[2 * np + 1], a, bb[2], bb[3]);
+      }
+    }
+  };
+  auto store_dq = [&](int r0, float (&dq)[NB / 2][4]) {
+    const int mrow = (warp & 3) * 16, nhalf = (warp >> 2) * (D / 2);
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      const int r = r0 + mrow + (lane >> 2) + hr * 8;
+      if (r < n_rows) {
+        int64_t ri, th;
+        row_ptrs(r, ri, th);
+        bf16* dst = p.dq + ri * D + nhalf + (lane & 3) * 2;
+#pragma unroll
+        for (int nb = 0; nb < NB / 2; ++nb)
+          *reinterpret_cast<__nv_bfloat162*>(dst + nb * 8) =
+              __floats2bfloat162_rn(dq[nb][2 * hr] * p.scale, dq[nb][2 * hr + 1] * p.scale);
+      }
+    }
+  };
+
+  for (int i = tid; i < kBwdRows * kDsStride / 8; i += 256) reinterpret_cast<uint4*>(ds_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+  // Phase 1, row block outer: dq of a block over the tiles its rows reach; key tile t + 1 arrives while tile t multiplies.
+  int nt_max = 0;
+  int id[kPipeSlots];
+  bf16 g[kPipeSlots];
+  for (int blk = 0; blk < kBwdBlocks; ++blk) {
+    const int r0 = cta_row0 + blk * kBwdRows;
+    int ntile = 0;
+    if (r0 < n_rows) ntile = block_ntile(r0);                    // (barriers: the previous block is finished with everything)
+    if (tid == 0) nt_s[blk] = ntile;
+    nt_max = max(nt_max, ntile);
+    if (r0 >= n_rows || ntile == 0) {
+      if (r0 < n_rows) {                                         // rows without a selected chunk: dq = 0
+        float dq0[NB / 2][4];
+#pragma unroll
+        for (int nb = 0; nb < NB / 2; ++nb)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) dq0[nb][e] = 0.f;
+        store_dq(r0, dq0);
+      }
+      continue;
+    }
+    issue_keys(0, 0);
+    cp_async_commit();
+    load_pairs(r0, id, g);
+    float dq[NB / 2][4];
+#pragma unroll
+    for (int nb = 0; nb < NB / 2; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dq[nb][e] = 0.f;
+    for (int t = 0; t < ntile; ++t) {
+      if (t + 1 < ntile) issue_keys((t + 1) * kBwdTile, (t + 1) & 1);   // its buffer was last read two tiles ago
+      cp_async_commit();
+      cp_async_wait1();                                          // this thread's pieces of key tile t have landed
+      __syncwarp();                                              // the row's four threads are done clearing the last tile
+      scatter(t * kBwdTile, id, g);
+      __syncthreads();                                           // tile built, key tile t complete
+      mma_dq(dq, t & 1);
+      __syncthreads();                                           // everyone has read the tile and the keys
+      unscatter(t * kBwdTile, id);
+    }
+    store_dq(r0, dq);
+  }
+  cp_async_wait0();
+  __syncthreads();
+  // Phase 2, tile outer: dk' of a tile accumulates in registers over ALL row blocks of the CTA and leaves as atomics once
+  // per (CTA, tile); the next block's queries and (id, gradient) pairs arrive while the current block multiplies.
+  auto next_block = [&](int after, int t) -> int {
+    for (int blk = after + 1; blk < kBwdBlocks; ++blk)
+      if (cta_row0 + blk * kBwdRows < n_rows && nt_s[blk] > t) return blk;
+    return -1;
+  };
+  for (int t = 0; t < nt_max; ++t) {
+    int cur = next_block(-1, t);
+    if (cur < 0) continue;
+    issue_q(cta_row0 + cur * kBwdRows, 0);
+    cp_async_commit();
+    load_pairs(cta_row0 + cur * kBwdRows, id, g);
+    for (int i = 0; cur >= 0; ++i) {
+      const int nxt = next_block(cur, t);
+      int nid[kPipeSlots];
+      bf16 ng[kPipeSlots];
+      if (nxt >= 0) {
+        issue_q(cta_row0 + nxt * kBwdRows, (i + 1) & 1);         // its buffer was last read two blocks ago
+        load_pairs(cta_row0 + nxt * kBwdRows, nid, ng);
+      }
+      cp_async_commit();
+      cp_async_wait1();
+      __syncwarp();
+      scatter(t * kBwdTile, id, g);
+      __syncthreads();
+      mma_dk(i & 1);
+      __syncthreads();
+      unscatter(t * kBwdTile, id);
+      if (nxt >= 0) {
+#pragma unroll
+        for (int j = 0; j < kPipeSlots; ++j) { id[j] = nid[j]; g[j] = ng[j]; }
+      }
+      cur = nxt;
+    }
+    cp_async_wait0();
+    flush_dk(t * kBwdTile);
+  }
+}
+
 // d_q in bf16; dl: fp32 accumulator of the chunk-key gradient, zeroed by the caller.
 int topk_bwd_mma_launch(const void* d_scores, const int32_t* indices, const void* q, const void* lmks, void* d_q,
                         float* dl, int B, int L, int N, int h_kv, int G, int D, int topk, int per_qhead, float scale,
@@ -272,6 +546,18 @@ int topk_bwd_mma_launch(const void* d_scores, const int32_t* indices, const void
   p.L = L; p.N = N; p.h_kv = h_kv; p.G = G; p.K = topk; p.per_qhead = per_qhead; p.scale = scale;
   const int n_rows = L * (per_qhead ? 1 : G);
   dim3 grid((n_rows + kBwdRows * kBwdBlocks - 1) / (kBwdRows * kBwdBlocks), HL, B);
+  if (N > kBwdTile && topk <= 4 * kPipeSlots && topk % 4 == 0) {   // several tiles: the pipelined kernel
+    const size_t smem_p = (size_t)(kBwdRows * kDsStride + 2 * kBwdTile * (D + 8)) * sizeof(bf16);
+    if (D == 64) {
+      cudaFuncSetAttribute(topk_bwd_pipe_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p);
+      topk_bwd_pipe_kernel<4><<<grid, 256, smem_p, st>>>(p);
+    } else {
+      cudaFuncSetAttribute(topk_bwd_pipe_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p);
+      topk_bwd_pipe_kernel<8><<<grid, 256, smem_p, st>>>(p);
+    }
+    HILS_LAUNCH_CHECK("topk_bwd (tensor-core, pipelined)");
+    return HILS_OK;
+  }
   const size_t smem = (size_t)(kBwdRows * kDsStride + (kBwdTile + kBwdRows) * (D + 8)) * sizeof(bf16);
   if (D == 64) {
     cudaFuncSetAttribute(topk_bwd_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -461,6 +461,10 @@ def test_naive_bsa_identity_on_gpu(ops, tag):
     (1, 384, 2, 4, 64, 4, False),     # shared keys, GQA: gradients of the group add up
     (1, 300, 1, 2, 128, 8, True),     # per-q-head keys
     (1, 1024, 1, 1, 64, 32, False),
+    # more than 128 candidates: several key tiles, the software-pipelined kernel
+    (1, 16421, 1, 1, 128, 32, False),  # N = 256, ragged last row block
+    (1, 12800, 1, 4, 64, 8, False),    # N = 200, shared keys, four rows per token
+    (1, 9000, 1, 2, 128, 16, True),    # N = 140, per-q-head keys
 ])
 def test_topk_backward_bf16_tensor_core_path(ops, cfg):
     """bf16 gradients of the returned scores (tensor-core chunk-key gradient, K-sparse gather for
