@@ -17,7 +17,9 @@ public API with pinned HOST buffers (q, k, v, dO copied in; o, dq, dk, dv copied
 neighbouring steps overlapped with compute).  `roofline` is for sparse chunk attention forward + backward,
 each timed alone with CUDA events, and carries a per-kernel list for the other stages.  `secondary` holds
 the same measurements for workload c2 (B=8, T=8192, 16 heads, D=64: the 345M model's attention shape) and
-c4 (decode: 32 sequences x one new token against a 131072-token KV store, batch split over the ranks), and
+c4 (decode: 32 sequences x one new token against a 131072-token KV store, batch split over the ranks),
+c4_paged / c4_paged_ragged (the same decode through the paged store, pages scattered over the pool; sequence
+lengths from 64K to 128K tokens in one batch), c5 (forward at 1,048,576 tokens, sequence-sharded for N > 1), and
 the sparse op alone on index sets with the reference's own overlap generator.
 `--impl reference` times the CPU restatement of the reference's PyTorch path (oracle/) on the host cores
 at its CPU-runnable configuration c1 (B=1, T=2048, 16 heads, D=64, top-k 8, fp32).
