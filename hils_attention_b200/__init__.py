@@ -2,7 +2,8 @@
 
 `ops` mirrors the reference's ``ops/`` call signatures on top of the C-ABI CUDA library
 (libhils_b200.so, declared in include/hils_b200.h); `attention` chains them the way the reference's
-attention module does; `cache` is the KV store used for prefill and decode.
+attention module does; `cache` is the KV store used for prefill and decode, `kv_store` the paged store
+(64-token pages = chunks) for decode batches of sequences of different lengths.
 """
 from . import _lib
 from .naive_bsa import naive_bsa_kernel
