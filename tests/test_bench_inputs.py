@@ -37,3 +37,26 @@ def test_workload_table_matches_the_baseline_configs():
     assert (w["c3"]["T"], w["c3"]["h_q"], w["c3"]["D"], w["c3"]["K"]) == (65536, 32, 128, 32)
     assert (w["c4"]["B"], w["c4"]["T"]) == (32, 131072)
     assert (w["c5"]["T"], w["c5"]["T"] // w["c5"]["S"]) == (1048576, 16384)
+
+
+def test_reference_arm_prints_one_contract_line():
+    """`bench.py --impl reference` (the CPU restatement on the host cores) prints one JSON line with the keys the
+    comparison needs; no GPU is touched."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, env=env, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["higher_is_better"] is True and d["n_gpus"] == 1 and d["steps"] == 1
+    assert d["metric"] == "hils_attn_fwd_bwd_tokens_per_s" and d["unit"] == "tokens/s" and d["value"] > 0
+    assert d["config"]["workload"] == "c1" and d["dtype"] == "f32"
+    cb = d["cpu_baseline"]
+    assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == d["value"] and cb["sample"]
+    assert d["e2e"] == {"value": d["value"], "unit": d["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
